@@ -1,0 +1,27 @@
+// Interface of the tcgen05 / TMEM convolution kernels.
+#pragma once
+
+#include "conv_simt.cuh"
+
+namespace dcb
+{
+
+struct TcPlan;
+
+// Creates tensor-core state for the problems the kernels cover; *out stays
+// null (and DCB_OK is returned) when none of them applies.  `fwd` is the
+// forward geometry, `bwd` the forward-shaped geometry that computes backward
+// data (only meaningful when bwd_is_fwd).
+int32_t tc_plan_create(const ConvGeom& fwd, const ConvGeom& bwd,
+                       bool bwd_is_fwd, int math_mode, TcPlan** out);
+void tc_plan_destroy(TcPlan* p);
+// which: 0 forward, 1 backward data, 2 backward filter
+bool tc_supports(const TcPlan* p, int which);
+// slot 0 runs the forward geometry, slot 1 the backward-data one.
+int32_t tc_conv_fwd(TcPlan* p, int slot, float alpha, const float* x,
+                    const float* w, float beta, float* y, cudaStream_t stream);
+int32_t tc_conv_bwd_filter(TcPlan* p, float alpha, const float* x,
+                           const float* dy, float beta, float* dw,
+                           cudaStream_t stream);
+
+} // namespace dcb

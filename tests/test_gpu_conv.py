@@ -1,0 +1,168 @@
+"""Convolution kernels against the oracle and against outputs of the
+reference's own ref::Backend (golden fixtures).  fp32: 1e-5 relative."""
+import ctypes
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import dihydrogen_b200 as dc
+from dihydrogen_b200 import _abi
+from oracle import oracle as O
+
+import emu
+from conftest import GOLDEN, conv_fixtures
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-5
+MODES = [_abi.MATH_FP32_SIMT, _abi.MATH_FP32]
+
+
+def _nd(a: torch.Tensor) -> _abi.NdDesc:
+    d = _abi.NdDesc()
+    nsd = a.dim() - 2
+    d.nsd = nsd
+    d.n, d.c = a.shape[0], a.shape[1]
+    d.sn, d.sc = a.stride(0), a.stride(1)
+    for i in range(3):
+        d.dims[i], d.strides[i] = 1, 0
+    for i in range(nsd):
+        d.dims[3 - nsd + i] = a.shape[2 + i]
+        d.strides[3 - nsd + i] = a.stride(2 + i)
+    return d
+
+
+def _cd(K, C, f, pads, strides, dil, mode):
+    nsd = len(f)
+    cd = _abi.ConvDesc()
+    cd.nsd, cd.k, cd.c, cd.groups, cd.math_mode = nsd, K, C, 1, mode
+    for i in range(3):
+        cd.filter[i], cd.pads[i], cd.strides[i], cd.dilations[i] = 1, 0, 1, 1
+    for i in range(nsd):
+        cd.filter[3 - nsd + i], cd.pads[3 - nsd + i] = f[i], pads[i]
+        cd.strides[3 - nsd + i], cd.dilations[3 - nsd + i] = strides[i], dil[i]
+    return cd
+
+
+class Plan:
+    def __init__(self, x, w, y, pads, strides, dil, mode):
+        cd = _cd(w.shape[0], w.shape[1], list(w.shape[2:]), pads, strides, dil, mode)
+        xd, yd = _nd(x), _nd(y)
+        self.p = ctypes.c_void_p()
+        _abi.call("dcb_conv_plan_create", ctypes.byref(cd), ctypes.byref(xd), ctypes.byref(yd), ctypes.byref(self.p))
+
+    def __del__(self):
+        _abi.lib().dcb_conv_plan_destroy(self.p)
+
+    def fwd(self, alpha, x, w, beta, y):
+        _abi.call("dcb_conv_fwd", self.p, alpha, ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(w.data_ptr()), beta,
+                  ctypes.c_void_p(y.data_ptr()), None)
+
+    def bwd_data(self, alpha, w, dy, beta, dx):
+        _abi.call("dcb_conv_bwd_data", self.p, alpha, ctypes.c_void_p(w.data_ptr()), ctypes.c_void_p(dy.data_ptr()),
+                  beta, ctypes.c_void_p(dx.data_ptr()), None)
+
+    def bwd_filter(self, alpha, x, dy, beta, dw):
+        _abi.call("dcb_conv_bwd_filter", self.p, alpha, ctypes.c_void_p(x.data_ptr()),
+                  ctypes.c_void_p(dy.data_ptr()), beta, ctypes.c_void_p(dw.data_ptr()), None)
+
+
+def run_all(x, w, dy, pads, strides, dil, mode, alpha=1.0, beta=0.0, y0=None, dx0=None, dw0=None):
+    xs, ws, dys = (torch.from_numpy(a).cuda() for a in (x, w, dy))
+    y = torch.from_numpy(y0).cuda() if y0 is not None else torch.zeros(dy.shape, device="cuda")
+    dx = torch.from_numpy(dx0).cuda() if dx0 is not None else torch.zeros(x.shape, device="cuda")
+    dw = torch.from_numpy(dw0).cuda() if dw0 is not None else torch.zeros(w.shape, device="cuda")
+    p = Plan(xs, ws, y, pads, strides, dil, mode)
+    p.fwd(alpha, xs, ws, beta, y)
+    p.bwd_data(alpha, ws, dys, beta, dx)
+    p.bwd_filter(alpha, xs, dys, beta, dw)
+    torch.cuda.synchronize()
+    return y.cpu().numpy(), dx.cpu().numpy(), dw.cpu().numpy()
+
+
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("fname", conv_fixtures())
+def test_against_reference_backend_outputs(fname, mode):
+    z = np.load(os.path.join(GOLDEN, fname))
+    x, w, dy = z["x"], z["w"], z["dy"]
+    f = w.shape[-1]
+    p = (f - 1) // 2
+    y, dx, dw = run_all(x, w, dy, [p, p], [1, 1], [1, 1], mode)
+    # ref::Backend itself rounds in fp32 per step: allow 2e-5 against it
+    emu.assert_close(y, z["y"], 2e-5, "y")
+    emu.assert_close(dx, z["dx"], 2e-5, "dx")
+    emu.assert_close(dw, z["dw"], 2e-5, "dw")
+
+
+# N, C, K, spatial, filter, pads, strides, dilations
+GEOMS = [
+    (1, 4, 16, (12, 16, 40), (3, 3, 3), (1, 1, 1), (1, 1, 1), (1, 1, 1)),     # cfg2 shape family
+    (2, 3, 5, (7, 9, 33), (3, 3, 3), (1, 1, 1), (1, 1, 1), (1, 1, 1)),        # ragged
+    (1, 16, 32, (9, 10, 36), (3, 3, 3), (1, 1, 1), (2, 2, 2), (1, 1, 1)),     # cfg3 layer 2 (stride 2)
+    (2, 8, 8, (20, 70), (5, 5), (2, 2), (1, 1), (1, 1)),                      # cfg4 family
+    (1, 4, 6, (8, 9, 34), (3, 3, 3), (0, 0, 0), (1, 1, 1), (1, 1, 1)),        # no padding
+    (1, 2, 3, (15, 31), (3, 3), (2, 2), (1, 1), (2, 2)),                      # dilation 2
+    (1, 3, 4, (11, 12, 130), (1, 1, 1), (0, 0, 0), (1, 1, 1), (1, 1, 1)),     # 1x1x1
+    (1, 4, 16, (6, 6, 260), (3, 3, 3), (1, 1, 1), (1, 1, 1), (1, 1, 1)),      # wide rows, several W tiles
+    (3, 5, 7, (9, 21), (3, 3), (1, 1), (2, 2), (1, 1)),                       # 2-D stride 2, odd extents
+]
+
+
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("geom", GEOMS)
+def test_against_oracle(geom, mode):
+    N, C, K, sp, f, pads, strides, dil = geom
+    rng = np.random.default_rng(hash(geom) % 2**32)
+    x = rng.normal(0, 1, (N, C, *sp)).astype(np.float32)
+    w = rng.normal(0, np.sqrt(2.0 / (C * np.prod(f))), (K, C, *f)).astype(np.float32)
+    osp = [O.conv_out_extent(i, ff, p, s, d) for i, ff, p, s, d in zip(sp, f, pads, strides, dil)]
+    dy = rng.normal(0, 1, (N, K, *osp)).astype(np.float32)
+    y, dx, dw = run_all(x, w, dy, list(pads), list(strides), list(dil), mode)
+    emu.assert_close(y, O.conv_fwd(x, w, list(pads), list(strides), list(dil)), TOL, "y")
+    dx_ref = np.zeros_like(x)
+    O.conv_bwd_data(w, dy, dx_ref, list(pads), list(strides), list(dil))
+    emu.assert_close(dx, dx_ref, TOL, "dx")
+    emu.assert_close(dw, O.conv_bwd_filter(x, dy, f, list(pads), list(strides), list(dil)), TOL, "dw")
+
+
+@pytest.mark.parametrize("mode", MODES)
+def test_alpha_beta_blend(mode):
+    N, C, K, sp, f = 1, 4, 16, (6, 8, 36), (3, 3, 3)
+    rng = np.random.default_rng(9)
+    x = rng.normal(size=(N, C, *sp)).astype(np.float32)
+    w = rng.normal(0, 0.1, (K, C, *f)).astype(np.float32)
+    dy = rng.normal(size=(N, K, *sp)).astype(np.float32)
+    y0 = rng.normal(size=dy.shape).astype(np.float32)
+    dx0 = rng.normal(size=x.shape).astype(np.float32)
+    dw0 = rng.normal(size=w.shape).astype(np.float32)
+    y, dx, dw = run_all(x, w, dy, [1] * 3, [1] * 3, [1] * 3, mode, alpha=0.5, beta=2.0, y0=y0, dx0=dx0, dw0=dw0)
+    emu.assert_close(y, O.conv_fwd(x, w, [1] * 3, [1] * 3, alpha=0.5, beta=2.0, y=y0.copy()), TOL, "y")
+    emu.assert_close(dx, O.conv_bwd_data(w, dy, dx0.copy(), [1] * 3, [1] * 3, alpha=0.5, beta=2.0), TOL, "dx")
+    emu.assert_close(dw, O.conv_bwd_filter(x, dy, f, [1] * 3, [1] * 3, alpha=0.5, beta=2.0, dw=dw0.copy()), TOL, "dw")
+
+
+def test_plan_rejects_inconsistent_output_extent():
+    x = torch.zeros(1, 2, 8, 8, device="cuda")
+    w = torch.zeros(3, 2, 3, 3, device="cuda")
+    y = torch.zeros(1, 3, 7, 8, device="cuda")
+    with pytest.raises(_abi.DcbError) as e:
+        Plan(x, w, y, [1, 1], [1, 1], [1, 1], _abi.MATH_FP32)
+    assert e.value.status == _abi.BAD_ARG
+
+
+def test_bias_forward_backward():
+    rng = np.random.default_rng(2)
+    y0 = rng.normal(size=(2, 5, 6, 7, 9)).astype(np.float32)
+    b = rng.normal(size=5).astype(np.float32)
+    y = torch.from_numpy(y0).cuda()
+    bt = torch.from_numpy(b).cuda()
+    yd = _nd(y)
+    _abi.call("dcb_bias_fwd", 1.0, ctypes.c_void_p(bt.data_ptr()), 1.0, ctypes.byref(yd),
+              ctypes.c_void_p(y.data_ptr()), None)
+    emu.assert_close(y.cpu().numpy(), y0 + b.reshape(1, 5, 1, 1, 1), 1e-6, "bias fwd")
+    db = torch.zeros(5, device="cuda")
+    _abi.call("dcb_bias_bwd", 1.0, ctypes.byref(yd), ctypes.c_void_p(y.data_ptr()), 0.0,
+              ctypes.c_void_p(db.data_ptr()), None)
+    emu.assert_close(db.cpu().numpy(), y.cpu().numpy().astype(np.float64).sum(axis=(0, 2, 3, 4)), 1e-5, "bias bwd")

@@ -1,0 +1,181 @@
+"""The whole path -- halo exchange, convolution forward / backward-data /
+backward-filter on the halo-extended shard, distributed batch-norm -- on
+emulated ranks, against the single-domain oracle and, for the 2-D case, against
+outputs of the reference's own ref::Backend."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import dihydrogen_b200 as dc
+from dihydrogen_b200 import _abi
+from oracle import oracle as O
+
+import emu
+from conftest import GOLDEN
+
+pytestmark = pytest.mark.gpu
+
+
+class Layer:
+    """conv -> BN on n emulated ranks, phase-ordered."""
+
+    def __init__(self, shape, locale, K, f, strides, pad, mode=_abi.MATH_FP32):
+        self.nd = len(shape)
+        nsd = self.nd - 2
+        self.n = int(np.prod(locale))
+        self.bes = emu.make_backends(self.n, options=dc.Options(math_mode=mode))
+        dil = [1] * nsd
+        self.K, self.C = K, shape[-2]
+        fshape = list(f) + [self.C, K]
+        pads = [(ff - 1) // 2 if pad else 0 for ff in f]
+        self.x, self.dx, self.y, self.dy, self.z, self.dz, self.convs, self.bns = ([] for _ in range(8))
+        w0 = torch.zeros((K, self.C, *reversed(f)), device="cuda")
+        for be in self.bes:
+            x = dc.create_input_tensor(shape, locale, f, strides, dil, be.locale)
+            y = dc.create_convolution_output_tensor(x, fshape, strides, pads, dil)
+            dy = dc.create_convolution_d_output_tensor(y, fshape, dil)
+            dx = dc.create_d_input_tensor(x)
+            z = dc.Tensor(y.shape, be.locale, y.dist, y._local_of)
+            dz = dc.Tensor(y.shape, be.locale, y.dist, y._local_of)
+            for t in (x, y, dy, dx, z, dz):
+                t.allocate()
+            conv = dc.Convolution(be, self.nd)
+            conv.setup(x, w0, y, dx, None, dy, pads, strides, dil, connect=False)
+            self.x.append(x), self.dx.append(dx), self.y.append(y), self.dy.append(dy)
+            self.z.append(z), self.dz.append(dz), self.convs.append(conv)
+            self.bns.append(dc.BatchNormalization(be, self.nd, 0.9, 1e-5, True))
+        emu.connect_halo([c.halo_xch_input for c in self.convs])
+        emu.connect_halo([c.halo_xch_d_output for c in self.convs])
+        self.out_shape = self.y[0].shape
+
+    def forward(self, gx, w, scale, bias):
+        K = self.K
+        self.w = torch.from_numpy(w).cuda()
+        for x in self.x:
+            x.buffer.fill_(float("nan"))  # halos must be produced by the exchange
+            src = tuple(slice(o, o + l) for o, l in reversed(list(zip(x.offset, x.local_shape))))
+            x.owned().copy_(torch.from_numpy(np.ascontiguousarray(gx[src])))
+            for d in range(self.nd - 2):
+                x.clear_halo(d)
+        emu.exchange_all([c.halo_xch_input for c in self.convs])
+        for c, x, y in zip(self.convs, self.x, self.y):
+            c.forward(1.0, x, self.w, 0.0, y, skip_halo_exchange=True)
+        self.stats = [torch.zeros(2 * K, device="cuda") for _ in self.bes]
+        self.rm = [torch.zeros(K, device="cuda") for _ in self.bes]
+        self.rv = [torch.ones(K, device="cuda") for _ in self.bes]
+        self.scale, self.bias = torch.from_numpy(scale).cuda(), torch.from_numpy(bias).cuda()
+        for bn, y, st in zip(self.bns, self.y, self.stats):
+            bn.forward_stage1(y, st[:K], st[K:], True)
+        emu.allreduce_all(self.bes, self.stats)
+        for bn, y, z, st, rm, rv in zip(self.bns, self.y, self.z, self.stats, self.rm, self.rv):
+            bn.forward_stage2(y, st[:K], st[K:], rm, rv, self.scale, self.bias, z, True)
+        torch.cuda.synchronize()
+
+    def backward(self, gdz):
+        K = self.K
+        for dz in self.dz:
+            emu.scatter_owned(dz, gdz)
+        ga = [torch.zeros(2 * K, device="cuda") for _ in self.bes]
+        gb = [torch.zeros(2 * K, device="cuda") for _ in self.bes]
+        for bn, y, dz, st, a, b in zip(self.bns, self.y, self.dz, self.stats, ga, gb):
+            bn.backward_stage1(y, dz, st[:K], st[K:], self.scale, b[:K], b[K:], a[:K], a[K:])
+        emu.allreduce_all(self.bes, ga)
+        emu.allreduce_all(self.bes, gb)
+        for bn, y, dz, dy, st, a in zip(self.bns, self.y, self.dz, self.dy, self.stats, ga):
+            dy.buffer.fill_(float("nan"))
+            bn.backward_stage2(y, dz, st[:K], st[K:], self.scale, a[:K], a[K:], dy)
+        self.dscale, self.dbias = gb[0][:K], gb[0][K:]
+        # backward filter first (it zero-clears dy's halo), then exchange, then
+        # backward data -- the driver's order (distconv_benchmark.cpp:569-589)
+        self.dw = [torch.zeros_like(self.w) for _ in self.bes]
+        for c, x, dy, dw in zip(self.convs, self.x, self.dy, self.dw):
+            c.backward_filter(1.0, x, dy, 0.0, dw, reduce=False)
+        emu.allreduce_all(self.bes, self.dw)
+        emu.exchange_all([c.halo_xch_d_output for c in self.convs])
+        for c, dy, dx in zip(self.convs, self.dy, self.dx):
+            c.backward_data(1.0, self.w, dy, 0.0, dx, skip_halo_exchange=True)
+        torch.cuda.synchronize()
+
+
+def oracle_layer(gx, w, scale, bias, gdz, pads, strides):
+    K = w.shape[0]
+    y = O.conv_fwd(gx, w, pads, strides)
+    s, q = O.bn_sums(y)
+    nps = y.size // K
+    m, v, rm, rv = O.bn_sums_to_statistics(s, q, nps, 0.9, np.zeros(K), np.ones(K))
+    z = O.bn_normalize(y, m, v, scale, bias, 1e-5)
+    dsc, dbi, dme, dva = O.bn_backprop1(y, gdz, m, v, scale, 1e-5)
+    dy = O.bn_backprop2(y, gdz, m, v, scale, np.float32(dme), np.float32(dva), 1e-5, nps)
+    dw = O.conv_bwd_filter(gx, dy, w.shape[2:], pads, strides)
+    dx = np.zeros_like(gx)
+    O.conv_bwd_data(w, dy, dx, pads, strides)
+    return dict(y=y, z=z, mean=m, var=v, dscale=dsc, dbias=dbi, dy=dy, dw=dw, dx=dx)
+
+
+LAYERS = [
+    # shape (W..N), locale, K, filter (W..), strides, name
+    ([32, 32, 8, 2], [1, 2, 1, 1], 8, [3, 3], [1, 1]),                 # BASELINE config 1 geometry, reduced
+    ([24, 20, 6, 2], [2, 2, 1, 1], 5, [5, 5], [1, 1]),                 # config 4 family: 5x5, H x W partition
+    ([20, 16, 12, 4, 1], [1, 1, 4, 1, 1], 16, [3, 3, 3], [1, 1, 1]),   # config 2: D partition
+    ([16, 16, 16, 4, 1], [2, 2, 2, 1, 1], 16, [3, 3, 3], [1, 1, 1]),   # config 3 layer 1: 2x2x2
+    ([16, 16, 16, 8, 1], [2, 2, 2, 1, 1], 8, [3, 3, 3], [2, 2, 2]),    # config 3 layer 2: stride 2
+    ([18, 14, 13, 3, 2], [1, 2, 3, 1, 1], 4, [3, 3, 3], [1, 1, 1]),    # uneven split
+]
+
+
+@pytest.mark.parametrize("mode", [_abi.MATH_FP32_SIMT, _abi.MATH_FP32])
+@pytest.mark.parametrize("shape,locale,K,f,strides", LAYERS)
+def test_layer_matches_single_domain_oracle(shape, locale, K, f, strides, mode):
+    rng = np.random.default_rng(11)
+    C = shape[-2]
+    gx = rng.normal(0, 1, tuple(reversed(shape))).astype(np.float32)
+    w = rng.normal(0, np.sqrt(2.0 / (C * np.prod(f))), (K, C, *reversed(f))).astype(np.float32)
+    scale = rng.uniform(0.5, 1.5, K).astype(np.float32)
+    bias = rng.normal(0, 0.5, K).astype(np.float32)
+    L = Layer(shape, locale, K, f, strides, pad=1, mode=mode)
+    gdz = rng.normal(0, 1, tuple(reversed(L.out_shape))).astype(np.float32)
+    L.forward(gx, w, scale, bias)
+    L.backward(gdz)
+    pads = [(ff - 1) // 2 for ff in reversed(f)]
+    ref = oracle_layer(gx, w, scale, bias, gdz, pads, list(reversed(strides)))
+    osh = tuple(reversed(L.out_shape))
+    emu.assert_close(emu.gather_owned(L.y, osh), ref["y"], 1e-5, "conv output")
+    emu.assert_close(L.stats[0][:K].cpu().numpy(), ref["mean"], 2e-5, "mean")
+    emu.assert_close(L.stats[0][K:].cpu().numpy(), ref["var"], 3e-5, "var")
+    emu.assert_close(emu.gather_owned(L.z, osh), ref["z"], 3e-5, "bn output")
+    emu.assert_close(L.dscale.cpu().numpy(), ref["dscale"], 5e-5, "dscale")
+    emu.assert_close(L.dbias.cpu().numpy(), ref["dbias"], 5e-5, "dbias")
+    emu.assert_close(emu.gather_owned(L.dy, osh), ref["dy"], 5e-5, "bn dx")
+    for dw in L.dw:
+        assert torch.equal(dw, L.dw[0])  # all ranks hold the same reduced gradient
+    emu.assert_close(L.dw[0].cpu().numpy(), ref["dw"], 5e-5, "filter gradient")
+    emu.assert_close(emu.gather_owned(L.dx, gx.shape), ref["dx"], 5e-5, "input gradient")
+
+
+def test_config1_against_reference_backend_outputs():
+    """2-D layer split along H over 2 ranks: conv outputs and gradients equal
+    what Convolution<ref::Backend> produced for the same seeded inputs."""
+    z = np.load(os.path.join(GOLDEN, "conv_cfg1_lite_h2.npz"))
+    x, w, dy = z["x"], z["w"], z["dy"]
+    N, C, H, W = x.shape
+    K = w.shape[0]
+    L = Layer([W, H, C, N], [1, 2, 1, 1], K, [3, 3], [1, 1], pad=1)
+    L.forward(x, w, np.ones(K, np.float32), np.zeros(K, np.float32))
+    emu.assert_close(emu.gather_owned(L.y, z["y"].shape), z["y"], 2e-5, "y vs ref::Backend")
+    # backward conv on the reference's dy (bypassing BN)
+    for t in L.dy:
+        t.buffer.zero_()
+        src = tuple(slice(o, o + l) for o, l in reversed(list(zip(t.offset, t.local_shape))))
+        t.owned().copy_(torch.from_numpy(np.ascontiguousarray(dy[src])))
+    dws = [torch.zeros_like(L.w) for _ in L.bes]
+    for c, xt, dyt, dw in zip(L.convs, L.x, L.dy, dws):
+        c.backward_filter(1.0, xt, dyt, 0.0, dw, reduce=False)
+    emu.allreduce_all(L.bes, dws)
+    emu.exchange_all([c.halo_xch_d_output for c in L.convs])
+    for c, dyt, dx in zip(L.convs, L.dy, L.dx):
+        c.backward_data(1.0, L.w, dyt, 0.0, dx, skip_halo_exchange=True)
+    torch.cuda.synchronize()
+    emu.assert_close(dws[0].cpu().numpy(), z["dw"], 2e-5, "dw vs ref::Backend")
+    emu.assert_close(emu.gather_owned(L.dx, x.shape), z["dx"], 2e-5, "dx vs ref::Backend")
