@@ -83,7 +83,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50",
                  "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -277,7 +277,6 @@ def run_ours(args):
         sampler.start()
     ms_step = timed(step, args.steps, max(args.warmup, 3))
     n_launch = launches["n"]
-    clocks = sampler.stop() if rank == 0 else None
     ms_e2e = timed(e2e_step, max(2, min(args.steps, 5)), 2)
 
     # per-kernel timing of the forward pass on this rank (rank 0 reports)
@@ -298,6 +297,7 @@ def run_ours(args):
     t_conv = time_call(lambda: conv.forward(1.0, x, w, 0.0, y, skip_halo_exchange=True))
     t_stats = time_call(lambda: bn.forward_stage1(y, mean, var, True))
     t_apply = time_call(lambda: bn.forward_stage2(y, mean, var, rm, rv, scale, bias, z, True))
+    clocks = sampler.stop() if rank == 0 else None
     st = conv.halo_xch_input.status()
     if st != _abi.OK:
         raise SystemExit("halo exchange reported " + str(st))
@@ -363,7 +363,7 @@ def run_ours(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     args = ap.parse_args()

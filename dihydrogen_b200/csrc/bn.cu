@@ -1,7 +1,7 @@
 // Batch-normalisation kernels (and LeakyReLU): HBM-bound streaming kernels.
 //
 // Every (n, c) plane of an NC[D]HW window is a set of contiguous runs (see
-// RunGeom).  A "unit" is up to BN_UNIT consecutive elements of one run; blocks
+// RunGeom).  A "unit" is up to BN_UNIT_VECS vector elements of one run; blocks
 // of channel c (blockIdx.y) stride over that channel's units with 16-byte
 // vector accesses where the strides allow.
 //
@@ -16,20 +16,22 @@ namespace dcb
 
 constexpr int BN_THREADS = 256;
 constexpr int BN_UNROLL = 4;
-constexpr int BN_UNIT = BN_THREADS * BN_UNROLL * 4; // scalars per unit
+constexpr int BN_UNIT_VECS = BN_THREADS * BN_UNROLL; // vector elements per unit
 
 struct UnitGeom
 {
     RunGeom g;
     long long upr;   // units per run
     long long upc;   // units per channel
+    int unit;        // scalars per unit = BN_UNIT_VECS * vector width
 };
 
-static UnitGeom make_units(const RunGeom& g)
+static UnitGeom make_units(const RunGeom& g, int vec)
 {
     UnitGeom u;
     u.g = g;
-    u.upr = (g.len + BN_UNIT - 1) / BN_UNIT;
+    u.unit = BN_UNIT_VECS * vec;
+    u.upr = (g.len + u.unit - 1) / u.unit;
     u.upc = g.n * g.rows * u.upr;
     return u;
 }
@@ -47,9 +49,9 @@ __device__ __forceinline__ UnitPos decode_unit(const UnitGeom& ug, long long u)
     const long long t = u / ug.upr;
     p.row = t % ug.g.rows;
     p.nn = t / ug.g.rows;
-    p.e0 = chunk * BN_UNIT;
+    p.e0 = chunk * ug.unit;
     const long long rem = ug.g.len - p.e0;
-    p.count = rem < BN_UNIT ? (int) rem : BN_UNIT;
+    p.count = rem < ug.unit ? (int) rem : ug.unit;
     return p;
 }
 
@@ -503,7 +505,7 @@ static int32_t make_multi(const dcb_nd_desc* const* descs,
         const int v = run_vec(g, mv->s[i], ptrs[i]);
         vec = v < vec ? v : vec;
     }
-    mv->ug = make_units(g);
+    mv->ug = make_units(g, vec);
     mv->vec = vec;
     DCB_REQUIRE(g.c <= 65535, "too many channels");
     return DCB_OK;

@@ -593,6 +593,20 @@ int32_t dcb_halo_wait_unpack(dcb_halo_plan* p, void* tensor, int32_t dim,
         const int v = pick_vec(geoms[s], tensor, j.packed);
         vec = v < vec ? v : vec;
     }
+    // A shard narrower than two halo widths has overlapping inner slabs: the
+    // two sides then accumulate into the same cells and must not run
+    // concurrently.  Unpack LHS, then RHS.
+    if (reverse && p->desc.local_shape[dim] < 2ll * width && a.side[0].active
+        && a.side[1].active)
+    {
+        HaloArgs lhs = a, rhs = a;
+        lhs.side[1].active = 0;
+        rhs.side[0].active = 0;
+        int32_t st = launch_halo<MODE_UNPACK>(lhs, vec, geoms, as_stream(stream));
+        if (st != DCB_OK)
+            return st;
+        return launch_halo<MODE_UNPACK>(rhs, vec, geoms, as_stream(stream));
+    }
     return launch_halo<MODE_UNPACK>(a, vec, geoms, as_stream(stream));
 }
 
