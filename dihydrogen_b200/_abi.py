@@ -95,6 +95,7 @@ _SIGS = {
     "dcb_conv_bwd_data": (c_int32, [_P, c_double, _P, _P, c_double, _P, _P]),
     "dcb_conv_bwd_filter": (c_int32, [_P, c_double, _P, _P, c_double, _P, _P]),
     "dcb_conv_plan_kernel_kind": (c_int32, [_P, c_int32]),
+    "dcb_conv_plan_status": (c_int32, [_P, _P]),
     "dcb_bias_fwd": (c_int32, [c_double, _P, c_double, POINTER(NdDesc), _P, _P]),
     "dcb_bias_bwd": (c_int32, [c_double, POINTER(NdDesc), _P, c_double, _P, _P]),
     "dcb_bn_plan_create": (c_int32, [POINTER(NdDesc), POINTER(_P)]),

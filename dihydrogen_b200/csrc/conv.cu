@@ -161,6 +161,24 @@ int32_t dcb_conv_plan_destroy(dcb_conv_plan* p)
     return DCB_OK;
 }
 
+int32_t dcb_conv_plan_status(dcb_conv_plan* p, void* stream)
+{
+    DCB_REQUIRE(p, "null argument");
+    DCB_CUDA_TRY(cudaStreamSynchronize(as_stream(stream)));
+    int* word = tc_status_word(p->tc);
+    if (!word)
+        return DCB_OK;
+    int st = 0;
+    DCB_CUDA_TRY(cudaMemcpy(&st, word, sizeof(int), cudaMemcpyDeviceToHost));
+    if (st != 0)
+    {
+        DCB_CUDA_TRY(cudaMemset(word, 0, sizeof(int)));
+        set_last_error("a tensor-core convolution kernel gave up on a pipeline wait");
+        return DCB_CUDA_ERROR;
+    }
+    return DCB_OK;
+}
+
 int32_t dcb_conv_plan_kernel_kind(const dcb_conv_plan* p, int32_t which)
 {
     if (!p || which < 0 || which > 2)

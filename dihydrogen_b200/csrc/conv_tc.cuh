@@ -20,6 +20,8 @@ bool tc_supports(const TcPlan* p, int which);
 // slot 0 runs the forward geometry, slot 1 the backward-data one.
 int32_t tc_conv_fwd(TcPlan* p, int slot, float alpha, const float* x,
                     const float* w, float beta, float* y, cudaStream_t stream);
+// Device word that kernels set when a bounded wait expires (null if no plan).
+int* tc_status_word(TcPlan* p);
 int32_t tc_conv_bwd_filter(TcPlan* p, float alpha, const float* x,
                            const float* dy, float beta, float* dw,
                            cudaStream_t stream);

@@ -201,6 +201,11 @@ int32_t dcb_conv_bwd_data(dcb_conv_plan* plan, double alpha, const void* w,
 int32_t dcb_conv_bwd_filter(dcb_conv_plan* plan, double alpha, const void* x,
                             const void* dy, double beta, void* dw,
                             void* stream);
+/* Synchronises `stream`, then reports whether a tensor-core kernel of this
+ * plan gave up on one of its bounded pipeline waits since the last call
+ * (DCB_CUDA_ERROR, record cleared) or not (DCB_OK).  Such a launch leaves its
+ * output incomplete. */
+int32_t dcb_conv_plan_status(dcb_conv_plan* plan, void* stream);
 /* Which kernel family the plan resolved to for (0 fwd, 1 bwd-data,
  * 2 bwd-filter): 0 = fp32 CUDA-core, 1 = tcgen05 tensor-core. */
 int32_t dcb_conv_plan_kernel_kind(const dcb_conv_plan* plan, int32_t which);
