@@ -26,15 +26,22 @@
 // releases its TMEM and returns.
 #include "conv_tc.cuh"
 
+#include <cuda.h>
+
 namespace dcb
 {
 
 namespace
 {
 
-constexpr int TC_THREADS = 128;
+constexpr int TC_PRODUCERS = 12;             // warps 0..11 convert staged rows
+constexpr int TC_MMA_WARP = TC_PRODUCERS;     // warp 12 issues the MMAs
+constexpr int TC_TMA_WARP = TC_PRODUCERS + 1; // warp 13 issues the bulk tensor loads
+constexpr int TC_THREADS = (TC_PRODUCERS + 6) * 32; // + epilogue warps 14..17
 constexpr int TC_M = 128;
-constexpr uint32_t TC_TMEM_COLS = 256;
+constexpr int TC_RAW_W = TC_M + 8;     // staged raw row: 4 cells left, 4 right
+constexpr uint32_t TC_TMEM_COLS = 512; // two accumulator buffers
+constexpr int TC_ACC_COLS = 256;
 
 struct TcGeom
 {
@@ -55,6 +62,10 @@ struct TcGeom
     int b_bytes;
     int tiles_w, tiles_h;
     long long tiles;
+    int nprod;          // producer warps in use (= stages, see the kernel)
+    int use_tma;        // raw rows arrive by bulk tensor copies
+    int raw_slots;      // ring of raw rows
+    int raw_slot_bytes; // c * TC_RAW_W floats, rounded up to 128 bytes
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p)
@@ -74,28 +85,27 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count)
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
 }
 
-// Bounded parity wait.  Returns false when the budget ran out.
+// Bounded parity wait.  Returns false when the budget ran out.  try_wait itself
+// suspends the thread for a hardware-chosen interval, so the loop is not hot.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag)
 {
     const uint32_t addr = smem_u32(bar);
-    for (uint32_t it = 0; it < (1u << 24); ++it)
+    for (uint32_t it = 0; it < (1u << 22); ++it)
     {
         uint32_t done;
         asm volatile(
             "{\n\t"
             ".reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
             "selp.b32 %0, 1, 0, p;\n\t"
             "}"
             : "=r"(done)
-            : "r"(addr), "r"(parity)
+            : "r"(addr), "r"(parity), "r"(1000u)
             : "memory");
         if (done)
             return true;
-        if (*abort_flag)
+        if ((it & 15) == 15 && *abort_flag)
             return false;
-        if (it > 1024)
-            __nanosleep(128);
     }
     *abort_flag = 1;
     return false;
@@ -201,10 +211,194 @@ __global__ void tc_pack_filter_kernel(const float* __restrict__ w, float* __rest
     }
 }
 
-template <int NB>
-__global__ void __launch_bounds__(TC_THREADS)
+// The staged input rows of one tile, in issue order: filter planes kd in
+// [kd_lo, kd_hi) x rows i in [i_lo, i_hi); everything outside lies in the zero
+// padding and contributes nothing.
+struct TileRows
+{
+    int n, od, oh0, ow0;
+    int kd_lo, kd_hi, i_lo, i_hi;
+    int nrows_i, count;
+};
+
+__device__ __forceinline__ TileRows tile_rows(const TcGeom& g, long long tile)
+{
+    TileRows t;
+    const int tw = (int) (tile % g.tiles_w);
+    long long t2 = tile / g.tiles_w;
+    const int thi = (int) (t2 % g.tiles_h);
+    t2 /= g.tiles_h;
+    t.od = (int) (t2 % g.out[0]);
+    t.n = (int) (t2 / g.out[0]);
+    t.ow0 = tw * TC_M;
+    t.oh0 = thi * g.th;
+    t.kd_lo = max(0, g.pad[0] - t.od);
+    t.kd_hi = min(g.f[0], g.in[0] + g.pad[0] - t.od);
+    t.i_lo = max(0, g.pad[1] - t.oh0);
+    t.i_hi = min(g.th + g.f[1] - 1, g.in[1] + g.pad[1] - t.oh0);
+    t.nrows_i = max(0, t.i_hi - t.i_lo);
+    t.count = max(0, t.kd_hi - t.kd_lo) * t.nrows_i;
+    return t;
+}
+
+// ext = {l2, l3, v0, v1, v2, v3, r0, r1}; the chunk for a tap shifted by s
+// cells is ext[2 + s .. 5 + s].
+__device__ __forceinline__ uint4 pick_shift(const uint32_t (&e)[8], int s)
+{
+    switch (s)
+    {
+    case -2: return make_uint4(e[0], e[1], e[2], e[3]);
+    case -1: return make_uint4(e[1], e[2], e[3], e[4]);
+    case 1: return make_uint4(e[3], e[4], e[5], e[6]);
+    case 2: return make_uint4(e[4], e[5], e[6], e[7]);
+    default: return make_uint4(e[2], e[3], e[4], e[5]);
+    }
+}
+
+// Byte offset of a lane's 16-byte chunk inside a stage for k-row kr:
+// [k-group][m-atom][4 k-rows][128 B] with the 32-byte-base XOR swizzle.
+// lane_part holds the lane-dependent bits (m-atom, 32-byte chunk, 16-byte
+// half); the k-row phase r = kr & 3 is XORed into the 32-byte chunk index.
+__device__ __forceinline__ uint32_t a_chunk_off(int kr, uint32_t lane_part)
+{
+    const uint32_t r = (uint32_t) (kr & 3);
+    return (uint32_t) ((kr >> 2) << 11) + (r << 7) + (lane_part ^ (r << 5));
+}
+
+// One channel of one staged row: ext holds the 8 cells around the lane's
+// chunk.  Writes the fw shifted copies of hi (and lo) into the stage.
+template <int FW, int PW>
+__device__ __forceinline__ void store_channel(const TcGeom& g, uint8_t* a_stage, int c, const float (&ext)[8],
+                                              uint32_t lane_part)
+{
+    uint32_t hi[8], lo[8];
+#pragma unroll
+    for (int t = 0; t < 8; ++t)
+    {
+        hi[t] = tf32_rna(ext[t]);
+        lo[t] = tf32_rna(ext[t] - __uint_as_float(hi[t]));
+    }
+    if (FW > 0)
+    {
+#pragma unroll
+        for (int kw = 0; kw < FW; ++kw)
+        {
+            const int kr = c * FW + kw;
+            *reinterpret_cast<uint4*>(a_stage + a_chunk_off(kr, lane_part)) = pick_shift(hi, kw - PW);
+            if (g.split)
+                *reinterpret_cast<uint4*>(a_stage + a_chunk_off(g.crows + kr, lane_part)) = pick_shift(lo, kw - PW);
+        }
+    }
+    else
+    {
+        const int fw = g.f[2], pw = g.pad[2];
+        for (int kw = 0; kw < fw; ++kw)
+        {
+            const int kr = c * fw + kw;
+            *reinterpret_cast<uint4*>(a_stage + a_chunk_off(kr, lane_part)) = pick_shift(hi, kw - pw);
+            if (g.split)
+                *reinterpret_cast<uint4*>(a_stage + a_chunk_off(g.crows + kr, lane_part)) = pick_shift(lo, kw - pw);
+        }
+    }
+}
+
+// Row fed from a raw copy in shared memory: raw[j] = x[ow0 - 4 + j], zero
+// outside the tensor (the bulk tensor copy fills out-of-range cells).
+template <int FW, int PW>
+__device__ __forceinline__ void convert_row_smem(const TcGeom& g, const float* raw, uint8_t* a_stage, int lane,
+                                                 uint32_t lane_part)
+{
+    for (int c = 0; c < g.c; ++c)
+    {
+        const float4* rr = reinterpret_cast<const float4*>(raw + (size_t) c * TC_RAW_W);
+        const float4 a = rr[lane], b = rr[lane + 1], d = rr[lane + 2];
+        const float ext[8] = {a.z, a.w, b.x, b.y, b.z, b.w, d.x, d.y};
+        store_channel<FW, PW>(g, a_stage, c, ext, lane_part);
+    }
+}
+
+// Row fed straight from global memory (any alignment): the lane loads its
+// chunk, the neighbours' cells come by shuffle, the tile edges by extra loads.
+template <int FW, int PW>
+__device__ __forceinline__ void convert_row_gmem(const TcGeom& g, const float* __restrict__ x, int n, int id,
+                                                 int ih, int ow0, uint8_t* a_stage, int lane,
+                                                 uint32_t lane_part)
+{
+    const float* base = x + (size_t) n * g.xs_n + (size_t) id * g.xs[0] + (size_t) ih * g.xs[1];
+    const int iw0 = ow0 + 4 * lane;
+    const int wi = g.in[2];
+    for (int c = 0; c < g.c; ++c)
+    {
+        const float* xr = base + (size_t) c * g.xs_c;
+        float4 v;
+        if (iw0 + 3 < wi && (reinterpret_cast<uintptr_t>(xr + iw0) & 15) == 0)
+        {
+            v = *reinterpret_cast<const float4*>(xr + iw0);
+        }
+        else
+        {
+            v.x = iw0 + 0 < wi ? xr[iw0 + 0] : 0.f;
+            v.y = iw0 + 1 < wi ? xr[iw0 + 1] : 0.f;
+            v.z = iw0 + 2 < wi ? xr[iw0 + 2] : 0.f;
+            v.w = iw0 + 3 < wi ? xr[iw0 + 3] : 0.f;
+        }
+        float ext[8];
+        ext[2] = v.x;
+        ext[3] = v.y;
+        ext[4] = v.z;
+        ext[5] = v.w;
+        ext[1] = __shfl_up_sync(0xffffffffu, v.w, 1);
+        ext[0] = __shfl_up_sync(0xffffffffu, v.z, 1);
+        ext[6] = __shfl_down_sync(0xffffffffu, v.x, 1);
+        ext[7] = __shfl_down_sync(0xffffffffu, v.y, 1);
+        if (lane == 0)
+        {
+            ext[1] = (iw0 - 1 >= 0 && iw0 - 1 < wi) ? xr[iw0 - 1] : 0.f;
+            ext[0] = (iw0 - 2 >= 0 && iw0 - 2 < wi) ? xr[iw0 - 2] : 0.f;
+        }
+        if (lane == 31)
+        {
+            ext[6] = iw0 + 4 < wi ? xr[iw0 + 4] : 0.f;
+            ext[7] = iw0 + 5 < wi ? xr[iw0 + 5] : 0.f;
+        }
+        store_channel<FW, PW>(g, a_stage, c, ext, lane_part);
+    }
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+
+// 5-D tiled bulk copy global -> shared (no multicast), completion on an mbarrier.
+__device__ __forceinline__ void tma_load_5d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, int c3,
+                                            int c4, uint64_t* bar)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%3, %4, %5, %6, %7}], [%2];" ::"r"(smem_u32(dst)),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+        : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// Warp roles.  Warps 0..TC_PRODUCERS-1 each convert whole staged rows (row
+// number `it` of the CTA's sequence belongs to warp it % TC_PRODUCERS, so that
+// many rows are converted concurrently and the converting warps hide each
+// other's instruction latency); the MMA warp issues tcgen05.mma in sequence
+// order; the copy warp streams raw rows in with bulk tensor copies; four
+// epilogue warps drain the accumulators.  Two accumulator buffers of 256 TMEM
+// columns alternate between tiles, so a tile's epilogue overlaps the next
+// tile's main loop.
+template <int NB, int FW, int PW>
+__global__ void __launch_bounds__(TC_THREADS, 1)
     tc_conv_kernel(TcGeom g, float alpha, float beta, const float* __restrict__ x, const float* __restrict__ bimg,
-                   float* y, int* status)
+                   float* y, int* status, const __grid_constant__ CUtensorMap xmap)
 {
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment keeps the hardware swizzle phase equal to the one
@@ -212,24 +406,41 @@ __global__ void __launch_bounds__(TC_THREADS)
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* a_ring = smem;
     float* b_smem = reinterpret_cast<float*>(smem + (size_t) g.stages * g.a_stage_bytes);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(b_smem) + g.b_bytes);
-    uint64_t* empty_bar = bars;              // [stages]
-    uint64_t* acc_bar = bars + g.stages;     // [1]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + g.stages + 1);
+    const int b_region = (g.b_bytes + 127) / 128 * 128;
+    uint8_t* raw_ring = reinterpret_cast<uint8_t*>(b_smem) + b_region;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(raw_ring + (size_t) g.raw_slots * g.raw_slot_bytes);
+    uint64_t* full_bar = bars;                     // [stages] producer -> MMA
+    uint64_t* empty_bar = bars + g.stages;         // [stages] MMA -> producer
+    uint64_t* acc_full = bars + 2 * g.stages;      // [2] MMA -> epilogue
+    uint64_t* acc_empty = bars + 2 * g.stages + 2; // [2] epilogue -> MMA
+    uint64_t* raw_full = bars + 2 * g.stages + 4;                // [raw_slots] copy -> producer
+    uint64_t* raw_empty = bars + 2 * g.stages + 4 + g.raw_slots; // [raw_slots] producer -> copy
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * g.stages + 4 + 2 * g.raw_slots);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int fd = g.f[0], fh = g.f[1], fw = g.f[2];
 
     if (tid == 0)
     {
         for (int s = 0; s < g.stages; ++s)
+        {
+            mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], 1);
-        mbar_init(acc_bar, 1);
+        }
+        for (int b = 0; b < 2; ++b)
+        {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], 4);
+        }
+        for (int r = 0; r < g.raw_slots; ++r)
+        {
+            mbar_init(&raw_full[r], 1);
+            mbar_init(&raw_empty[r], 1);
+        }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 0)
+    if (warp == TC_MMA_WARP)
     {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
                      "r"(TC_TMEM_COLS)
@@ -246,185 +457,233 @@ __global__ void __launch_bounds__(TC_THREADS)
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t lane_addr = tmem_base + ((uint32_t) (warp * 32) << 16);
-
-    // instruction descriptor without N: fp32 accumulate, tf32 x tf32,
-    // A MN-major, B K-major, M = 128
-    const uint32_t idesc_base = (1u << 4) | (2u << 7) | (2u << 10) | (1u << 15) | (0u << 16) | ((TC_M >> 4) << 24);
-    const uint32_t a_base = smem_u32(a_ring);
-    const uint32_t b_base = smem_u32(b_smem);
-    const uint32_t b_lbo = (uint32_t) (g.ntot / 8) * 128u;
-    const uint32_t b_kstep_bytes = (uint32_t) g.ntot * 32u;
-
-    uint32_t it = 0;        // staged rows so far (ring position and parity)
-    uint32_t acc_phase = 0; // completed tiles
     bool ok = true;
 
-    for (long long tile = blockIdx.x; tile < g.tiles && ok; tile += gridDim.x)
+    if (warp < g.nprod)
     {
-        const int tw = (int) (tile % g.tiles_w);
-        long long t2 = tile / g.tiles_w;
-        const int thi = (int) (t2 % g.tiles_h);
-        t2 /= g.tiles_h;
-        const int od = (int) (t2 % g.out[0]);
-        const int n = (int) (t2 / g.out[0]);
-        const int ow0 = tw * TC_M, oh0 = thi * g.th;
-
-        // ---- zero the accumulators ----
-        for (int col = 0; col < g.th * NB; col += 16)
-            tmem_st16_zero(lane_addr + col);
-        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-        tc_fence_before();
-        __syncthreads();
-
-        // ---- main loop over staged input rows ----
-        for (int kd = 0; kd < fd && ok; ++kd)
+        // ------------------------------------------------------------------
+        // producers: raw row -> hi / lo split -> fw shifted copies in the
+        // swizzled stage.  Row `it` belongs to warp it % nprod, and with
+        // stages == nprod and raw_slots a multiple of nprod every stage and
+        // raw slot is only ever touched by one producer warp, in order.  That
+        // matters: a parity wait is only meaningful for the current or the
+        // previous phase of a barrier, so a warp must never wait on a barrier
+        // whose earlier phase another, possibly slower, warp still owes.
+        // ------------------------------------------------------------------
+        const int nprod = g.nprod;
+        const uint32_t lane_part =
+            (uint32_t) ((lane >> 3) << 9) + (uint32_t) (((lane & 7) >> 1) << 5) + (uint32_t) ((lane & 1) << 4);
+        uint32_t base = 0; // sequence number of the tile's first row
+        for (long long tile = blockIdx.x; tile < g.tiles && ok; tile += gridDim.x)
         {
-            const int id = od - g.pad[0] + kd;
-            if (id < 0 || id >= g.in[0])
-                continue;
-            for (int i = 0; i < g.th + fh - 1 && ok; ++i)
+            const TileRows t = tile_rows(g, tile);
+            // first row of this tile that belongs to this warp
+            uint32_t q = (uint32_t) ((warp + nprod - (int) (base % nprod)) % nprod);
+            for (; q < (uint32_t) t.count && ok; q += nprod)
             {
-                const int ih = oh0 - g.pad[1] + i;
-                if (ih < 0 || ih >= g.in[1])
-                    continue;
-                int j_lo = fh - 1 - i;
-                j_lo = j_lo < 0 ? 0 : j_lo;
-                int j_hi = g.th + fh - 1 - i;
-                j_hi = j_hi > fh ? fh : j_hi;
-                if (j_hi <= j_lo)
-                    continue;
+                const uint32_t it = base + q;
+                const int kd = t.kd_lo + (int) q / t.nrows_i;
+                const int i = t.i_lo + (int) q % t.nrows_i;
+                const int id = t.od - g.pad[0] + kd, ih = t.oh0 - g.pad[1] + i;
                 const uint32_t s = it % g.stages;
+                uint32_t slot = 0;
+                if (g.use_tma)
+                {
+                    slot = it % g.raw_slots;
+                    ok = mbar_wait(&raw_full[slot], (it / g.raw_slots) & 1, abort_flag);
+                    if (!ok)
+                        break;
+                }
                 if (it >= (uint32_t) g.stages)
                     ok = mbar_wait(&empty_bar[s], ((it / g.stages) - 1) & 1, abort_flag);
                 if (!ok)
                     break;
-                // ---- stage: hi / lo split and the fw shifted copies ----
                 uint8_t* a_stage = a_ring + (size_t) s * g.a_stage_bytes;
-                const float* xrow_base = x + (size_t) n * g.xs_n + (size_t) id * g.xs[0] + (size_t) ih * g.xs[1];
-                const int ntask = g.crows * 32;
-                for (int task = tid; task < ntask; task += TC_THREADS)
-                {
-                    const int q = task & 31;       // 16-byte chunk along M
-                    const int cr = task >> 5;      // (c, kw)
-                    const int c = cr / fw, kw = cr - c * fw;
-                    const float* xr = xrow_base + (size_t) c * g.xs_c;
-                    const int iw0 = ow0 + 4 * q - g.pad[2] + kw;
-                    float v[4];
-#pragma unroll
-                    for (int e = 0; e < 4; ++e)
-                    {
-                        const int iw = iw0 + e;
-                        v[e] = (iw >= 0 && iw < g.in[2]) ? xr[iw] : 0.f;
-                    }
-                    uint32_t hi[4], lo[4];
-#pragma unroll
-                    for (int e = 0; e < 4; ++e)
-                    {
-                        hi[e] = tf32_rna(v[e]);
-                        lo[e] = tf32_rna(v[e] - __uint_as_float(hi[e]));
-                    }
-                    const int matom = q >> 3, qq = q & 7;
-                    {
-                        const int kr = cr;
-                        const int r = kr & 3;
-                        uint8_t* dst = a_stage + ((size_t) ((kr >> 2) * 4 + matom) << 9) + (r << 7)
-                                       + (((qq >> 1) ^ r) << 5) + ((qq & 1) << 4);
-                        *reinterpret_cast<uint4*>(dst) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-                    }
-                    if (g.split)
-                    {
-                        const int kr = g.crows + cr;
-                        const int r = kr & 3;
-                        uint8_t* dst = a_stage + ((size_t) ((kr >> 2) * 4 + matom) << 9) + (r << 7)
-                                       + (((qq >> 1) ^ r) << 5) + ((qq & 1) << 4);
-                        *reinterpret_cast<uint4*>(dst) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-                    }
-                }
+                if (g.use_tma)
+                    convert_row_smem<FW, PW>(g, reinterpret_cast<const float*>(raw_ring + (size_t) slot * g.raw_slot_bytes),
+                                             a_stage, lane, lane_part);
+                else
+                    convert_row_gmem<FW, PW>(g, x, t.n, id, ih, t.ow0, a_stage, lane, lane_part);
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                __syncthreads();
-                // ---- issue ----
-                if (tid == 0)
+                __syncwarp();
+                if (lane == 0)
                 {
-                    tc_fence_after();
-                    const int nblocks = j_hi - j_lo;
-                    const uint32_t idesc = idesc_base | ((uint32_t) ((nblocks * NB) >> 3) << 17);
-                    const uint32_t d_addr = tmem_base + (uint32_t) ((i - fh + 1 + j_lo) * NB);
-                    const uint32_t a_addr = a_base + s * (uint32_t) g.a_stage_bytes;
-                    const uint32_t b_addr = b_base + (uint32_t) (kd * g.ksteps) * b_kstep_bytes
-                                            + (uint32_t) (j_lo * (NB / 8)) * 128u;
-                    for (int ks = 0; ks < g.ksteps; ++ks)
-                    {
-                        const uint64_t ad = make_desc(a_addr + ks * 4096u, 512u, 2048u, 1u);
-                        const uint64_t bd = make_desc(b_addr + ks * b_kstep_bytes, b_lbo, 128u, 0u);
-                        mma_tf32(d_addr, ad, bd, idesc, 1u);
-                    }
-                    mma_commit(&empty_bar[s]);
+                    mbar_arrive(&full_bar[s]);
+                    if (g.use_tma)
+                        mbar_arrive(&raw_empty[slot]);
                 }
-                ++it;
             }
+            base += (uint32_t) t.count;
         }
-        if (!ok)
-            break;
-        if (tid == 0)
-            mma_commit(acc_bar);
-        ok = mbar_wait(acc_bar, acc_phase & 1, abort_flag);
-        ++acc_phase;
-        if (!ok)
-            break;
-        tc_fence_after();
-
-        // ---- epilogue: TMEM -> registers -> global ----
-        const int ow = ow0 + warp * 32 + lane;
-        for (int r = 0; r < g.th; ++r)
+    }
+    else if (warp == TC_TMA_WARP)
+    {
+        // ------------------------------------------------------------------
+        // bulk tensor copies of raw input rows, raw_slots rows ahead
+        // ------------------------------------------------------------------
+        if (lane == 0 && g.use_tma)
         {
-            const int oh = oh0 + r;
-            if (oh >= g.out[1])
-                break; // uniform
-            uint32_t v[NB];
-#pragma unroll
-            for (int q = 0; q < NB / 16; ++q)
-                tmem_ld16(lane_addr + (uint32_t) (r * NB + q * 16), *reinterpret_cast<uint32_t(*)[16]>(&v[q * 16]));
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-            if (ow < g.out[2])
+            uint32_t it = 0;
+            const uint32_t bytes = (uint32_t) g.c * TC_RAW_W * 4u;
+            for (long long tile = blockIdx.x; tile < g.tiles && ok; tile += gridDim.x)
             {
-                float* yp = y + (size_t) n * g.ys_n + (size_t) od * g.ys[0] + (size_t) oh * g.ys[1] + ow;
-                const int kp = g.split ? NB / 2 : NB;
-#pragma unroll
-                for (int k = 0; k < NB; ++k)
-                {
-                    if (k < kp && k < g.k)
+                const TileRows t = tile_rows(g, tile);
+                for (int kd = t.kd_lo; kd < t.kd_hi && ok; ++kd)
+                    for (int i = t.i_lo; i < t.i_hi; ++i, ++it)
                     {
-                        float acc = __uint_as_float(v[k]);
-                        if (g.split)
-                            acc += __uint_as_float(v[(k + NB / 2) % NB]);
-                        float* p = yp + (size_t) k * g.ys_c;
-                        const float prev = beta != 0.f ? *p : 0.f;
-                        *p = alpha * acc + beta * prev;
+                        const uint32_t slot = it % g.raw_slots;
+                        if (it >= (uint32_t) g.raw_slots)
+                            ok = mbar_wait(&raw_empty[slot], ((it / g.raw_slots) - 1) & 1, abort_flag);
+                        if (!ok)
+                            break;
+                        mbar_expect_tx(&raw_full[slot], bytes);
+                        // x starts 4 cells left of the tile: a multiple of 4
+                        // floats, as the 16-byte rule for the innermost
+                        // coordinate demands
+                        tma_load_5d(raw_ring + (size_t) slot * g.raw_slot_bytes, &xmap, t.ow0 - 4,
+                                    t.oh0 - g.pad[1] + i, t.od - g.pad[0] + kd, 0, t.n, &raw_full[slot]);
+                    }
+            }
+        }
+    }
+    else if (warp == TC_MMA_WARP)
+    {
+        // ------------------------------------------------------------------
+        // MMA issue: one thread
+        // ------------------------------------------------------------------
+        if (lane == 0)
+        {
+            // instruction descriptor without N: fp32 accumulate, tf32 x tf32,
+            // A MN-major, B K-major, M = 128
+            const uint32_t idesc_base =
+                (1u << 4) | (2u << 7) | (2u << 10) | (1u << 15) | (0u << 16) | ((TC_M >> 4) << 24);
+            const uint32_t a_base = smem_u32(a_ring);
+            const uint32_t b_base = smem_u32(b_smem);
+            const uint32_t b_lbo = (uint32_t) (g.ntot / 8) * 128u;
+            const uint32_t b_kstep_bytes = (uint32_t) g.ntot * 32u;
+            const int fh = g.f[1];
+            uint32_t it = 0, tcount = 0;
+            for (long long tile = blockIdx.x; tile < g.tiles && ok; tile += gridDim.x, ++tcount)
+            {
+                const TileRows t = tile_rows(g, tile);
+                const uint32_t buf = tcount & 1;
+                ok = mbar_wait(&acc_empty[buf], (tcount >> 1) & 1, abort_flag);
+                if (!ok)
+                    break;
+                for (int kd = t.kd_lo; kd < t.kd_hi && ok; ++kd)
+                    for (int i = t.i_lo; i < t.i_hi; ++i, ++it)
+                    {
+                        const uint32_t s = it % g.stages;
+                        ok = mbar_wait(&full_bar[s], (it / g.stages) & 1, abort_flag);
+                        if (!ok)
+                            break;
+                        tc_fence_after();
+                        const int j_lo = max(0, fh - 1 - i);
+                        const int j_hi = min(fh, g.th + fh - 1 - i);
+                        const uint32_t idesc = idesc_base | ((uint32_t) (((j_hi - j_lo) * NB) >> 3) << 17);
+                        const uint32_t d_addr =
+                            tmem_base + buf * (uint32_t) TC_ACC_COLS + (uint32_t) ((i - fh + 1 + j_lo) * NB);
+                        const uint32_t a_addr = a_base + s * (uint32_t) g.a_stage_bytes;
+                        const uint32_t b_addr = b_base + (uint32_t) (kd * g.ksteps) * b_kstep_bytes
+                                                + (uint32_t) (j_lo * (NB / 8)) * 128u;
+                        for (int ks = 0; ks < g.ksteps; ++ks)
+                        {
+                            const uint64_t ad = make_desc(a_addr + ks * 4096u, 512u, 2048u, 1u);
+                            const uint64_t bd = make_desc(b_addr + ks * b_kstep_bytes, b_lbo, 128u, 0u);
+                            mma_tf32(d_addr, ad, bd, idesc, 1u);
+                        }
+                        mma_commit(&empty_bar[s]);
+                    }
+                if (ok)
+                    mma_commit(&acc_full[buf]);
+            }
+        }
+    }
+    else if (warp > TC_TMA_WARP)
+    {
+        // ------------------------------------------------------------------
+        // epilogue: TMEM -> registers -> global, then re-zero the buffer
+        // ------------------------------------------------------------------
+        const int quad = warp & 3; // TMEM lanes this warp may touch
+        const uint32_t lane_addr = tmem_base + ((uint32_t) (quad * 32) << 16);
+        for (int col = 0; col < (int) TC_TMEM_COLS; col += 16)
+            tmem_st16_zero(lane_addr + col);
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0)
+        {
+            mbar_arrive(&acc_empty[0]);
+            mbar_arrive(&acc_empty[1]);
+        }
+        uint32_t tcount = 0;
+        for (long long tile = blockIdx.x; tile < g.tiles && ok; tile += gridDim.x, ++tcount)
+        {
+            const TileRows t = tile_rows(g, tile);
+            const int ow = t.ow0 + quad * 32 + lane;
+            const uint32_t buf = tcount & 1;
+            ok = mbar_wait(&acc_full[buf], (tcount >> 1) & 1, abort_flag);
+            if (!ok)
+                break;
+            tc_fence_after();
+            const uint32_t acc_addr = lane_addr + buf * (uint32_t) TC_ACC_COLS;
+            for (int r = 0; r < g.th; ++r)
+            {
+                const int oh = t.oh0 + r;
+                if (oh >= g.out[1])
+                    break; // uniform
+                uint32_t v[NB];
+#pragma unroll
+                for (int q = 0; q < NB / 16; ++q)
+                    tmem_ld16(acc_addr + (uint32_t) (r * NB + q * 16),
+                              *reinterpret_cast<uint32_t(*)[16]>(&v[q * 16]));
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (ow < g.out[2])
+                {
+                    float* yp = y + (size_t) t.n * g.ys_n + (size_t) t.od * g.ys[0] + (size_t) oh * g.ys[1] + ow;
+                    const int kp = g.split ? NB / 2 : NB;
+#pragma unroll
+                    for (int k = 0; k < NB; ++k)
+                    {
+                        if (k < kp && k < g.k)
+                        {
+                            float acc = __uint_as_float(v[k]);
+                            if (g.split)
+                                acc += __uint_as_float(v[(k + NB / 2) % NB]);
+                            float* p = yp + (size_t) k * g.ys_c;
+                            const float prev = beta != 0.f ? *p : 0.f;
+                            *p = alpha * acc + beta * prev;
+                        }
                     }
                 }
             }
+            for (int col = 0; col < g.th * NB; col += 16)
+                tmem_st16_zero(acc_addr + col);
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0)
+                mbar_arrive(&acc_empty[buf]);
         }
-        tc_fence_before();
-        __syncthreads();
     }
 
-    if (!ok && tid == 0)
+    if (!ok && lane == 0)
         atomicExch(status, 1);
-    // Teardown.  On the error path threads may leave at different points, so
-    // no block-wide barrier is used there: the allocating warp waits for its
-    // own lanes and frees the columns.
-    if (ok)
+    // Every role leaves its loop after a bounded time (all waits are bounded
+    // and watch the abort flag), so the block-wide barrier is always reached.
+    tc_fence_before();
+    __syncthreads();
+    if (warp == TC_MMA_WARP)
     {
-        tc_fence_before();
-        __syncthreads();
-    }
-    if (warp == 0)
-    {
-        __syncwarp();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TC_TMEM_COLS)
                      : "memory");
     }
+}
+
+size_t tc_smem_need(const TcGeom& g)
+{
+    return (size_t) g.stages * g.a_stage_bytes + (size_t) (g.b_bytes + 127) / 128 * 128
+           + (size_t) g.raw_slots * g.raw_slot_bytes + (size_t) (2 * g.stages + 4 + 2 * g.raw_slots) * 8 + 64 + 1024;
 }
 
 bool tc_geom(const ConvGeom& cg, int math_mode, TcGeom* out)
@@ -461,17 +720,39 @@ bool tc_geom(const ConvGeom& cg, int math_mode, TcGeom* out)
     g.ntot = g.f[1] * g.nb;
     if (g.ntot > 256 || g.ntot % 16)
         return false;
-    g.th = (int) TC_TMEM_COLS / g.nb;
+    g.th = TC_ACC_COLS / g.nb;
     if (g.th > 16)
         g.th = 16;
+    if (g.c > 16)
+        return false;
+    for (int i = 0; i < 3; ++i)
+        if (g.pad[i] > g.f[i] - 1)
+            return false; // a window entirely inside the padding
+    // taps are taken from the two cells either side of a lane's chunk
+    if (g.pad[2] > 2 || g.f[2] - 1 - g.pad[2] > 2)
+        return false;
     g.crows = g.c * g.f[2];
     g.kr = ((g.crows * (g.split ? 2 : 1)) + 7) / 8 * 8;
     g.ksteps = g.kr / 8;
     g.a_stage_bytes = g.kr * 512;
     g.b_bytes = g.f[0] * g.kr * g.ntot * 4;
-    g.stages = g.a_stage_bytes <= 16 * 1024 ? 4 : (g.a_stage_bytes <= 32 * 1024 ? 3 : 2);
-    const size_t need = (size_t) g.stages * g.a_stage_bytes + g.b_bytes + 256 + 1024;
-    if (need > 200 * 1024)
+    g.stages = (144 * 1024) / g.a_stage_bytes;
+    g.stages = g.stages > TC_PRODUCERS ? TC_PRODUCERS : g.stages;
+    if (g.stages < 2)
+        return false;
+    g.nprod = g.stages;
+    // Bulk tensor copies need 16-byte aligned strides (the base address is
+    // checked per call).
+    g.use_tma = (cg.xs[1] % 4 == 0 && cg.xs[0] % 4 == 0 && cg.xs_c % 4 == 0 && cg.xs_n % 4 == 0) ? 1 : 0;
+    g.raw_slot_bytes = (g.c * TC_RAW_W * 4 + 127) / 128 * 128;
+    // a multiple of nprod (see the kernel), about 36 KiB at most
+    g.raw_slots = g.use_tma ? ((36 * 1024) / g.raw_slot_bytes) / g.nprod * g.nprod : 0;
+    if (g.raw_slots > 2 * g.nprod)
+        g.raw_slots = 2 * g.nprod;
+    if (g.use_tma && g.raw_slots < g.nprod)
+        g.use_tma = 0, g.raw_slots = 0;
+    const size_t need = tc_smem_need(g);
+    if (need > 220 * 1024)
         return false;
     g.tiles_w = (g.out[2] + TC_M - 1) / TC_M;
     g.tiles_h = (g.out[1] + g.th - 1) / g.th;
@@ -482,7 +763,10 @@ bool tc_geom(const ConvGeom& cg, int math_mode, TcGeom* out)
 
 size_t tc_smem_bytes(const TcGeom& g)
 {
-    return (size_t) g.stages * g.a_stage_bytes + g.b_bytes + 256 + 1024;
+    // At least 120 KiB so that a second CTA can never share the SM: the
+    // kernel owns all 512 TMEM columns.
+    const size_t need = tc_smem_need(g);
+    return need < 120 * 1024 ? 120 * 1024 : need;
 }
 
 } // namespace
@@ -548,22 +832,85 @@ bool tc_supports(const TcPlan* p, int which)
     return false;
 }
 
-template <int NB>
-static int32_t tc_launch(const TcGeom& g, float alpha, const float* x, const float* bimg, float beta, float* y,
-                         int* status, cudaStream_t stream)
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn()
+{
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried)
+    {
+        tried = true;
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess
+            && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+        else
+            (void) cudaGetLastError();
+    }
+    return fn;
+}
+
+// Descriptor of the input window as a 5-D tensor (W, H, D, C, N) whose box is
+// one raw row of every channel.  Returns false when the window cannot be
+// described (alignment), in which case the register-fed producers run.
+static bool make_x_map(const TcGeom& g, const float* x, CUtensorMap* map)
+{
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn || (reinterpret_cast<uintptr_t>(x) & 15) != 0)
+        return false;
+    const cuuint64_t dims[5] = {(cuuint64_t) g.in[2], (cuuint64_t) g.in[1], (cuuint64_t) g.in[0], (cuuint64_t) g.c,
+                                (cuuint64_t) g.n};
+    // a dimension of extent 1 may carry any stride; give it a valid one
+    const long long s1 = g.xs[1], s0 = g.in[0] > 1 ? g.xs[0] : g.xs[1] * g.in[1];
+    const cuuint64_t strides[4] = {(cuuint64_t) s1 * 4, (cuuint64_t) s0 * 4, (cuuint64_t) g.xs_c * 4,
+                                   (cuuint64_t) (g.n > 1 ? g.xs_n : g.xs_c * g.c) * 4};
+    for (int i = 0; i < 4; ++i)
+        if (strides[i] % 16 != 0 || strides[i] == 0)
+            return false;
+    const cuuint32_t box[5] = {(cuuint32_t) TC_RAW_W, 1, 1, (cuuint32_t) g.c, 1};
+    const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 5, const_cast<float*>(x), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE)
+           == CUDA_SUCCESS;
+}
+
+template <int NB, int FW, int PW>
+static int32_t tc_launch2(const TcGeom& g, float alpha, const float* x, const float* bimg, float beta, float* y,
+                          int* status, const CUtensorMap& map, cudaStream_t stream)
 {
     const size_t smem = tc_smem_bytes(g);
-    DCB_CUDA_TRY(cudaFuncSetAttribute(tc_conv_kernel<NB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      (int) (200 * 1024)));
-    // Two CTAs per SM when shared memory allows: one stages and issues while
-    // the other drains its accumulators.
-    const int per_sm = smem <= 100 * 1024 ? 2 : 1;
-    long long grid = (long long) num_sms() * per_sm;
+    DCB_CUDA_TRY(cudaFuncSetAttribute(tc_conv_kernel<NB, FW, PW>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      (int) (224 * 1024)));
+    long long grid = (long long) num_sms();
     if (grid > g.tiles)
         grid = g.tiles;
-    tc_conv_kernel<NB><<<(unsigned) grid, TC_THREADS, smem, stream>>>(g, alpha, beta, x, bimg, y, status);
+    tc_conv_kernel<NB, FW, PW><<<(unsigned) grid, TC_THREADS, smem, stream>>>(g, alpha, beta, x, bimg, y, status,
+                                                                             map);
     DCB_LAUNCH_CHECK();
     return DCB_OK;
+}
+
+template <int NB>
+static int32_t tc_launch(const TcGeom& g_in, float alpha, const float* x, const float* bimg, float beta, float* y,
+                         int* status, cudaStream_t stream)
+{
+    TcGeom g = g_in;
+    CUtensorMap map;
+    std::memset(&map, 0, sizeof(map));
+    if (g.use_tma && !make_x_map(g, x, &map))
+        g.use_tma = 0; // the raw ring stays allocated but unused
+    if (g.f[2] == 3 && g.pad[2] == 1)
+        return tc_launch2<NB, 3, 1>(g, alpha, x, bimg, beta, y, status, map, stream);
+    if (g.f[2] == 5 && g.pad[2] == 2)
+        return tc_launch2<NB, 5, 2>(g, alpha, x, bimg, beta, y, status, map, stream);
+    if (g.f[2] == 1 && g.pad[2] == 0)
+        return tc_launch2<NB, 1, 0>(g, alpha, x, bimg, beta, y, status, map, stream);
+    return tc_launch2<NB, 0, 0>(g, alpha, x, bimg, beta, y, status, map, stream);
 }
 
 int32_t tc_conv_fwd(TcPlan* p, int slot, float alpha, const float* x, const float* w, float beta, float* y,
