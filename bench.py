@@ -37,12 +37,13 @@ FILTER = [3, 3, 3]
 EPS, DECAY = 1e-5, 0.9
 
 
-def layer_geometry(n_gpus, locale, extent=EXTENT):
+def layer_geometry(n_gpus, locale, extent=EXTENT, local_d=None):
     """Tensors (unallocated) of the benchmark layer for this rank: the global
-    volume grows with the GPU count along D (weak scaling)."""
+    volume grows with the GPU count along D (weak scaling).  local_d shrinks
+    the per-GPU D extent (profiling captures only)."""
     import dihydrogen_b200 as dc
 
-    shape = [extent, extent, extent * n_gpus, C_IN, 1]  # W, H, D, C, N
+    shape = [extent, extent, (local_d or extent) * n_gpus, C_IN, 1]  # W, H, D, C, N
     locale_shape = [1, 1, n_gpus, 1, 1]
     strides, dil = [1, 1, 1], [1, 1, 1]
     x = dc.create_input_tensor(shape, locale_shape, FILTER, strides, dil, locale)
@@ -211,8 +212,13 @@ def run_ours(args):
     else:
         locale = dc.Locale(0, 1)
     _abi.lib()
+    # nvidia-smi needs a few hundred ms to start: sample from here on, the
+    # timed regions below are what runs while it samples
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
 
-    geo = layer_geometry(world, locale)
+    geo = layer_geometry(world, locale, local_d=args.local_d)
     x, y, z = geo["input"], geo["conv_out"], geo["bn_out"]
     for t in (x, y, z):
         t.allocate()
@@ -272,9 +278,6 @@ def run_ours(args):
             ms = float(tt.item())
         return ms / steps
 
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
     ms_step = timed(step, args.steps, max(args.warmup, 3))
     n_launch = launches["n"]
     ms_e2e = timed(e2e_step, max(2, min(args.steps, 5)), 2)
@@ -329,7 +332,7 @@ def run_ours(args):
                 "conv_kernel": "tcgen05" if conv.kernel_kind(0) == 1 else "fp32-simt"}
 
     cpu = None
-    if world == 1:
+    if world == 1 and not args.skip_cpu:
         sample_d = pick_cpu_sample(extent, target_s=8.0)
         t_cpu, threads = cpu_layer_pass(sample_d, extent)
         cpu = {"value": sample_d * extent * extent / t_cpu, "unit": "voxels/s", "cores": threads, "kind": "port",
@@ -342,7 +345,8 @@ def run_ours(args):
         "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": "BASELINE configs[1]: 3-D conv+BN layer, N=1 C=4 256^3 per GPU -> K=16 3x3x3 s1 p1, "
-                               "halo exchange + conv fwd + BN fwd (global stats)",
+                               "halo exchange + conv fwd + BN fwd (global stats)"
+                               + ("" if args.local_d is None else f" [REDUCED local D={args.local_d}: profiling only]"),
                    "partition": f"D over {world} GPU(s), halo width 1", "global_volume": geo["shape"][:3],
                    "l2": "inputs larger than L2 (268 MB in, 1 GiB conv out per GPU)",
                    "allreduce": "peer-memory kernel, 2C floats"},
@@ -366,6 +370,9 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--local-d", type=int, default=None,
+                    help="per-GPU D extent instead of 256 (small case for profiler captures; not a bench value)")
+    ap.add_argument("--skip-cpu", action="store_true", help="skip the CPU baseline leg (profiler captures)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
