@@ -765,3 +765,91 @@ int32_t dcb_leaky_relu_bwd(const dcb_nd_desc* xd, const void* x,
 }
 
 } // extern "C"
+
+// ---------------------------------------------------------------------------
+// Per-channel statistics without any device allocation.
+//
+// Some hosts cannot let a library call cudaMalloc: a training framework whose
+// caching allocator already owns the whole device, code that runs between
+// cudaStreamBeginCapture and EndCapture (allocation is illegal there), or a
+// latency-critical loop where cudaMalloc's implicit device synchronisation is
+// not acceptable.  For them this variant of dcb_bn_stats keeps its reduction
+// scratch (per-block partial sums and the per-channel arrival tickets) in a
+// fixed array that is part of the library image.  Every GPU that loads the
+// library carries the array until the process exits.
+// ---------------------------------------------------------------------------
+namespace
+{
+constexpr int NOALLOC_MAX_CHANNELS = 1024;
+constexpr int NOALLOC_MAX_BLOCKS = 4096; // blocks of one launch, all channels together
+constexpr size_t NOALLOC_TICKET_BYTES = NOALLOC_MAX_CHANNELS * sizeof(unsigned);
+constexpr size_t NOALLOC_PARTIAL_BYTES = (size_t) NOALLOC_MAX_BLOCKS * 2 * sizeof(double);
+constexpr int NOALLOC_MAX_DEVICES = 64;
+
+// Layout: [tickets: 1024 x u32][partials: 4096 x 2 x f64] = 68 KiB.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_TICKET_BYTES + NOALLOC_PARTIAL_BYTES];
+
+// Device address of the array on each device, resolved on first use.  In host
+// code the symbol itself is only a handle, never a pointer a kernel may use.
+static void* g_noalloc_addr[NOALLOC_MAX_DEVICES] = {};
+} // namespace
+
+extern "C" int32_t dcb_bn_stats_noalloc(const dcb_nd_desc* xd, const void* x, void* sums, void* sqsums,
+                                        void* stream)
+{
+    DCB_REQUIRE(xd && x && sums && sqsums, "null argument");
+    const dcb_nd_desc* descs[1] = {xd};
+    const void* ptrs[1] = {x};
+    MultiView mv;
+    int32_t st = make_multi(descs, ptrs, 1, &mv);
+    if (st != DCB_OK)
+        return st;
+    if (xd->c < 1 || xd->c > NOALLOC_MAX_CHANNELS)
+    {
+        set_last_error("dcb_bn_stats_noalloc handles 1..1024 channels; use dcb_bn_stats with a plan beyond that");
+        return DCB_UNSUPPORTED;
+    }
+    int dev = 0;
+    DCB_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= NOALLOC_MAX_DEVICES)
+    {
+        set_last_error("dcb_bn_stats_noalloc: device ordinal beyond 63");
+        return DCB_UNSUPPORTED;
+    }
+    if (g_noalloc_addr[dev] == nullptr)
+    {
+        // once per device, with that device current
+        void* p = nullptr;
+        DCB_CUDA_TRY(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+        g_noalloc_addr[dev] = p;
+    }
+    unsigned char* base = static_cast<unsigned char*>(g_noalloc_addr[dev]);
+    unsigned* tickets = reinterpret_cast<unsigned*>(base);
+    double* partial = reinterpret_cast<double*>(base + NOALLOC_TICKET_BYTES);
+    if (mv.ug.upc == 0)
+    {
+        DCB_CUDA_TRY(cudaMemsetAsync(sums, 0, xd->c * sizeof(float), as_stream(stream)));
+        DCB_CUDA_TRY(cudaMemsetAsync(sqsums, 0, xd->c * sizeof(float), as_stream(stream)));
+        return DCB_OK;
+    }
+    dim3 grid = bn_grid(mv.ug);
+    // stay inside the fixed scratch: fewer blocks per channel if need be
+    if ((long long) grid.x * grid.y > NOALLOC_MAX_BLOCKS)
+        grid.x = (unsigned) (NOALLOC_MAX_BLOCKS / grid.y);
+    if (grid.x < 1)
+    {
+        set_last_error("dcb_bn_stats_noalloc: launch does not fit the fixed scratch");
+        return DCB_UNSUPPORTED;
+    }
+    // The array keeps whatever the previous call (or an interrupted one) left:
+    // the arrival tickets must start at zero.  Partials are overwritten.
+    DCB_CUDA_TRY(cudaMemsetAsync(tickets, 0, xd->c * sizeof(unsigned), as_stream(stream)));
+#define CALL(VV)                                                               \
+    bn_stats_kernel<VV><<<grid, BN_THREADS, 0, as_stream(stream)>>>(           \
+        static_cast<const float*>(x), mv.s[0], mv.ug, partial, tickets,        \
+        static_cast<float*>(sums), static_cast<float*>(sqsums))
+    DCB_VEC_DISPATCH(mv.vec, CALL);
+#undef CALL
+    DCB_LAUNCH_CHECK();
+    return DCB_OK;
+}

@@ -232,6 +232,19 @@ int32_t dcb_bn_plan_destroy(dcb_bn_plan* plan);
  * (channel_sums_and_sqsums, batchnorm.cu:192-249).  Overwrites. */
 int32_t dcb_bn_stats(dcb_bn_plan* plan, const void* x, void* sums,
                      void* sqsums, void* stream);
+/* The same statistics for callers that must not trigger a device allocation
+ * (no counterpart in the reference; added for hosts whose allocator owns the
+ * whole GPU, for code running inside a stream capture, and for loops that
+ * cannot afford cudaMalloc's device-wide synchronisation).  Needs no plan: the
+ * reduction scratch is a fixed 68 KiB array inside the library image, present
+ * on every GPU that loads the library.  Limits: at most 1024 channels
+ * (DCB_UNSUPPORTED beyond).  The first call on each device looks up the
+ * array's device address; make that call outside any stream capture.  All
+ * calls share the one array, so two calls whose kernels may overlap on the
+ * same GPU (different streams) race: serialise them.  Results equal those of
+ * dcb_bn_stats. */
+int32_t dcb_bn_stats_noalloc(const dcb_nd_desc* xd, const void* x, void* sums,
+                             void* sqsums, void* stream);
 /* In place sums -> mean, sqsums -> unbiased variance, update running stats
  * (sums_to_statistics, batchnorm.cu:288-346).  num_per_sum <= 0 sets var=1. */
 int32_t dcb_bn_finalize(int32_t channels, int64_t num_per_sum, float decay,
