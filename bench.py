@@ -322,10 +322,17 @@ def run_ours(args):
         "bn_stats": {"ms": t_stats, "bytes": 4 * out_el},
         "bn_finalize_apply": {"ms": t_apply, "bytes": 8 * out_el},
     }
+    # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the
+    # ncu capture of a 64 x 256 x 256 shard, which scales with the D extent:
+    # bytes per shard voxel times this launch's voxels.
+    ncu_vox = 64 * 256 * 256
+    traffic_per_voxel = {"conv_fwd": (67.25e6 + 210.80e6) / ncu_vox, "bn_stats": (268.46e6 + 4.05e6) / ncu_vox,
+                         "bn_finalize_apply": (268.53e6 + 222.07e6) / ncu_vox}
     dom = max(kernels, key=lambda k: kernels[k]["ms"])
     ach = kernels[dom]["bytes"] / (kernels[dom]["ms"] * 1e-3) / 1e9
     roofline = {"kernel": dom, "bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                "frac": ach / peaks["hbm_gbs"], "peak_source": peak_kind, "traffic": None,
+                "frac": ach / peaks["hbm_gbs"], "peak_source": peak_kind, "traffic": traffic_per_voxel[dom] * vox_local,
+                "traffic_source": "ncu capture of a 64x256x256 shard scaled by voxels (profiles/)",
                 "kernels_ms": {k: round(v["ms"], 4) for k, v in kernels.items()},
                 "kernels_gbs": {k: round(v["bytes"] / (v["ms"] * 1e-3) / 1e9, 1) for k, v in kernels.items()},
                 "conv_tflops": kernels["conv_fwd"]["flops"] / (t_conv * 1e-3) / 1e12,

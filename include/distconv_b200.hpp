@@ -1,0 +1,1101 @@
+// distconv_b200.hpp -- header-only C++ host side of the B200 DistConv path.
+//
+// Keeps DistConv's namespaces, class names, method names and argument order
+// for the spatially-parallel conv + batch-norm path and forwards every device
+// operation to the C ABI of libdistconv_b200 (dcb.h).  Reference interfaces
+// (paths relative to the DiHydrogen tree):
+//   tensor::Shape / IntVector / IndexVector   legacy/include/distconv/tensor/tensor_base.hpp, vector.hpp
+//   tensor::Distribution                      legacy/include/distconv/tensor/distribution.hpp:14-270
+//   tensor::LocaleMPI                         legacy/include/distconv/tensor/tensor_mpi.hpp:18-93
+//   tensor::Tensor<T, LocaleMPI, CUDAAllocator>  tensor.hpp:38-653, tensor_mpi.hpp:98-574
+//   internal::get_halo_sizes, create_*_tensor legacy/include/distconv/distconv.hpp:21-99, 253-515
+//   tensor::HaloExchange                      halo_exchange_cuda.hpp:18-423
+//   BackendDNNLib                             dnn_backend/dnn_backend.hpp:635-980
+//   Convolution<BackendDNNLib, T>             dnn_backend/convolution.hpp:19-3003
+//   BatchNormalization<BackendDNNLib, T>      dnn_backend/batchnorm.hpp:100-581
+//
+// Dimension order is DistConv's: index 0 is W, then H, [D], C, N; negative
+// indices count from the end (-2 is C, -1 is N).  Only float tensors and
+// spatial parallelism (no channel/filter parallelism) are provided.
+//
+// The header needs cuda_runtime_api.h for device memory; it needs no mpi.h:
+// LocaleMPI takes the rank, the size and an allgather callback.
+#pragma once
+
+#include "dcb.h"
+
+#include <cuda_runtime_api.h>
+
+#include <algorithm>
+#include <cstdint>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <functional>
+#include <memory>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+namespace distconv
+{
+
+using index_t = int64_t;
+using int_vector = std::vector<int>;
+
+enum Side
+{
+    LHS = 0,
+    RHS = 1
+};
+
+enum class HaloExchangeMethod
+{
+    MPI,
+    AL,
+    P2P,
+    HYBRID
+}; // all map to the one peer-store transport
+
+enum class BatchnormImpl
+{
+    MPI,
+    AL_NCCL,
+    PEER
+};
+
+enum class ChannelParallelismAlgorithm
+{
+    NONE,
+    AUTO
+};
+
+namespace util
+{
+inline void check(int32_t st, const char* what)
+{
+    if (st != DCB_OK)
+        throw std::runtime_error(std::string(what) + ": " + dcb_status_string(st) + " (" + dcb_last_error() + ")");
+}
+} // namespace util
+
+namespace tensor
+{
+
+// Vector with DistConv's negative indexing.
+template <typename T>
+class Vector : public std::vector<T>
+{
+public:
+    using std::vector<T>::vector;
+    Vector() = default;
+    Vector(const std::vector<T>& v) : std::vector<T>(v) {}
+    T& operator[](int i) { return std::vector<T>::operator[](i < 0 ? (int) this->size() + i : i); }
+    const T& operator[](int i) const { return std::vector<T>::operator[](i < 0 ? (int) this->size() + i : i); }
+    int num_dims() const { return (int) this->size(); }
+    T get_size() const
+    {
+        T p = 1;
+        for (auto v : *this)
+            p *= v;
+        return p;
+    }
+};
+
+using Shape = Vector<index_t>;
+using IndexVector = Vector<index_t>;
+using IntVector = Vector<int>;
+
+class Distribution
+{
+public:
+    Distribution() = default;
+    Distribution(const Shape& locale_shape, const Shape& split_shape, const IntVector& overlap)
+        : m_locale_shape(locale_shape), m_split_shape(split_shape), m_overlap(overlap)
+    {
+        fixup_overlap();
+    }
+    static Distribution make_localized_distribution(int nd)
+    {
+        return Distribution(Shape(nd, 1), Shape(nd, 1), IntVector(nd, 0));
+    }
+    static Distribution make_distribution(const Shape& ls) { return Distribution(ls, ls, IntVector(ls.size(), 0)); }
+    static Distribution make_shared_distribution(const Shape& ls)
+    {
+        return Distribution(ls, Shape(ls.size(), 1), IntVector(ls.size(), 0));
+    }
+    static Distribution make_overlapped_distribution(const Shape& ls, const IntVector& overlap)
+    {
+        return Distribution(ls, ls, overlap);
+    }
+    int num_dims() const { return m_locale_shape.num_dims(); }
+    const Shape& get_locale_shape() const { return m_locale_shape; }
+    const Shape& get_split_shape() const { return m_split_shape; }
+    const IntVector& get_overlap() const { return m_overlap; }
+    int get_overlap(int dim) const { return m_overlap[dim]; }
+    index_t get_num_ranks_per_split(int dim) const { return m_locale_shape[dim] / m_split_shape[dim]; }
+    bool is_distributed(int dim) const { return m_split_shape[dim] > 1; }
+    void set_overlap(const IntVector& o) { m_overlap = o; }
+    void clear_overlap() { m_overlap = IntVector(num_dims(), 0); }
+    void fixup_overlap()
+    {
+        for (int i = 0; i < num_dims(); ++i)
+            if (!is_distributed(i))
+                m_overlap[i] = 0;
+    }
+
+private:
+    Shape m_locale_shape, m_split_shape;
+    IntVector m_overlap;
+};
+
+// A rank of a group.  allgather(in, out, n): every rank contributes n bytes,
+// out receives size * n bytes in rank order (MPI_Allgather with MPI_BYTE).
+class LocaleMPI
+{
+public:
+    using Allgather = std::function<void(const void*, void*, size_t)>;
+    LocaleMPI(int rank = 0, int size = 1, Allgather ag = nullptr) : m_rank(rank), m_size(size), m_ag(std::move(ag)) {}
+    int get_rank() const { return m_rank; }
+    int get_size() const { return m_size; }
+    IndexVector get_rank_idx(const Distribution& dist) const
+    {
+        IndexVector idx(dist.num_dims(), 0);
+        int r = m_rank;
+        for (int i = 0; i < dist.num_dims(); ++i)
+        {
+            idx[i] = r % dist.get_locale_shape()[i];
+            r /= (int) dist.get_locale_shape()[i];
+        }
+        return idx;
+    }
+    void allgather(const void* in, void* out, size_t n) const
+    {
+        if (m_size == 1)
+        {
+            std::memcpy(out, in, n);
+            return;
+        }
+        if (!m_ag)
+            throw std::runtime_error("LocaleMPI: no allgather callback for a multi-rank locale");
+        m_ag(in, out, n);
+    }
+
+private:
+    int m_rank, m_size;
+    Allgather m_ag;
+};
+
+struct CUDAAllocator
+{
+};
+
+inline index_t split_extent(index_t total, index_t parts, index_t index)
+{
+    return total / parts + (index < total % parts ? 1 : 0);
+}
+
+} // namespace tensor
+} // namespace distconv
+
+namespace distconv
+{
+namespace tensor
+{
+
+// Block-distributed float tensor shard with halo cells on both sides of every
+// partitioned dimension that has an overlap.  Owns its device memory unless it
+// is a view.  `local_shape_of` (optional) maps a grid index to that rank's
+// local shape -- DistConv's "requested local shape" for convolution outputs.
+template <typename DataType = float, typename Locale = LocaleMPI, typename Allocator = CUDAAllocator>
+class Tensor
+{
+public:
+    using data_type = DataType;
+    using LocalShapeFn = std::function<Shape(const IndexVector&)>;
+
+    Tensor() = default;
+    Tensor(const Shape& shape, const Locale& locale, const Distribution& dist, LocalShapeFn fn = nullptr)
+        : m_shape(shape), m_locale(locale), m_dist(dist), m_fn(std::move(fn))
+    {
+        const int nd = shape.num_dims();
+        m_proc_idx = locale.get_rank_idx(m_dist);
+        m_split_idx = IndexVector(nd, 0);
+        for (int i = 0; i < nd; ++i)
+            m_split_idx[i] = m_proc_idx[i] / m_dist.get_num_ranks_per_split(i);
+        m_local_shape = local_of(m_proc_idx);
+        m_offset = IndexVector(nd, 0);
+        for (int d = 0; d < nd; ++d)
+            m_offset[d] = get_dimension_rank_offset(d, (int) m_proc_idx[d]);
+    }
+
+    Shape local_of(const IndexVector& proc_idx) const
+    {
+        if (m_fn)
+            return m_fn(proc_idx);
+        Shape out(m_shape.size(), 0);
+        for (int d = 0; d < (int) m_shape.size(); ++d)
+            out[d] = m_dist.is_distributed(d)
+                         ? split_extent(m_shape[d], m_dist.get_split_shape()[d],
+                                        proc_idx[d] / m_dist.get_num_ranks_per_split(d))
+                         : m_shape[d];
+        return out;
+    }
+
+    int get_num_dims() const { return m_shape.num_dims(); }
+    int get_num_spatial_dims() const { return get_num_dims() - 2; }
+    const Shape& get_shape() const { return m_shape; }
+    const Shape& get_local_shape() const { return m_local_shape; }
+    Shape get_local_real_shape() const
+    {
+        Shape r = m_local_shape;
+        for (int i = 0; i < get_num_dims(); ++i)
+            r[i] += 2 * m_dist.get_overlap(i);
+        return r;
+    }
+    index_t get_local_size() const { return m_local_shape.get_size(); }
+    index_t get_size() const { return m_shape.get_size(); }
+    const IndexVector& get_global_index() const { return m_offset; }
+    const Distribution& get_distribution() const { return m_dist; }
+    const Locale& get_locale() const { return m_locale; }
+    const IndexVector& get_split_index() const { return m_split_idx; }
+    const IndexVector& get_proc_index() const { return m_proc_idx; }
+    const IntVector& get_overlap() const { return m_dist.get_overlap(); }
+    int get_halo_width(int dim) const { return m_dist.get_overlap(dim); }
+    const LocalShapeFn& get_local_shape_fn() const { return m_fn; }
+    bool is_split_root() const
+    {
+        for (int i = 0; i < get_num_dims(); ++i)
+            if (m_proc_idx[i] % m_dist.get_num_ranks_per_split(i))
+                return false;
+        return true;
+    }
+    index_t get_dimension_rank_offset(int dim, int rank_idx) const
+    {
+        index_t off = 0;
+        if (!m_dist.is_distributed(dim))
+            return 0;
+        const index_t per = m_dist.get_num_ranks_per_split(dim);
+        for (index_t j = 0; j < rank_idx / per; ++j)
+        {
+            IndexVector idx = m_proc_idx;
+            idx[dim] = j * per;
+            off += local_of(idx)[dim];
+        }
+        return off;
+    }
+
+    // memory
+    int allocate()
+    {
+        const size_t bytes = (size_t) get_local_real_shape().get_size() * sizeof(DataType);
+        void* p = nullptr;
+        if (cudaMalloc(&p, bytes ? bytes : 16) != cudaSuccess)
+            return -1;
+        cudaMemset(p, 0, bytes);
+        m_mem = std::shared_ptr<void>(p, [](void* q) { cudaFree(q); });
+        m_buf = static_cast<DataType*>(p);
+        return 0;
+    }
+    void set_view(void* raw) { m_mem.reset(); m_buf = static_cast<DataType*>(raw); } // never frees
+    DataType* get_buffer() { return m_buf; }
+    const DataType* get_const_buffer() const { return m_buf; }
+    Shape get_strides() const
+    {
+        Shape st(m_shape.size(), 1);
+        index_t acc = 1;
+        const Shape real = get_local_real_shape();
+        for (int i = 0; i < get_num_dims(); ++i)
+        {
+            st[i] = acc;
+            acc *= real[i];
+        }
+        return st;
+    }
+    index_t get_local_offset(const IndexVector& idx, bool idx_include_halo = false) const
+    {
+        const Shape st = get_strides();
+        index_t off = 0;
+        for (int i = 0; i < get_num_dims(); ++i)
+            off += (idx[i] + (idx_include_halo ? 0 : m_dist.get_overlap(i))) * st[i];
+        return off;
+    }
+    DataType* get_base_ptr() { return m_buf + get_local_offset(IndexVector(m_shape.size(), 0)); }
+    void zero(cudaStream_t s = 0)
+    {
+        cudaMemsetAsync(m_buf, 0, (size_t) get_local_real_shape().get_size() * sizeof(DataType), s);
+    }
+    void clear_halo(int dim, cudaStream_t s = 0)
+    {
+        if (get_local_size() == 0)
+            return;
+        dcb_tensor_desc d = desc();
+        util::check(dcb_clear_halo(&d, m_buf, dim, s), "clear_halo");
+    }
+
+    // descriptors for the C ABI
+    dcb_tensor_desc desc() const
+    {
+        dcb_tensor_desc d{};
+        d.ndims = get_num_dims();
+        d.dtype = DCB_F32;
+        const Shape real = get_local_real_shape();
+        for (int i = 0; i < d.ndims; ++i)
+        {
+            d.local_shape[i] = m_local_shape[i];
+            d.real_shape[i] = real[i];
+            d.overlap[i] = m_dist.get_overlap(i);
+        }
+        return d;
+    }
+    // owned cells extended by lo / hi halo cells per spatial dimension
+    // (setup_tensor_descriptor, dnn_backend_impl.hpp:31-70)
+    dcb_nd_desc nd_desc(const IntVector& lo, const IntVector& hi) const
+    {
+        const int nsd = get_num_spatial_dims();
+        const Shape st = get_strides();
+        dcb_nd_desc d{};
+        d.nsd = nsd;
+        d.n = m_local_shape[-1];
+        d.c = m_local_shape[-2];
+        d.sn = st[-1];
+        d.sc = st[-2];
+        for (int s = 0; s < 3; ++s)
+        {
+            d.dims[s] = 1;
+            d.strides[s] = 0;
+        }
+        for (int i = 0; i < nsd; ++i)
+        {
+            d.dims[2 - i] = m_local_shape[i] + lo[i] + hi[i];
+            d.strides[2 - i] = st[i];
+        }
+        return d;
+    }
+    dcb_nd_desc nd_desc() const
+    {
+        const IntVector z(get_num_dims(), 0);
+        return nd_desc(z, z);
+    }
+    dcb_nd_desc full_nd_desc() const { return nd_desc(get_overlap(), get_overlap()); }
+    DataType* nd_ptr(const IntVector& lo)
+    {
+        IndexVector idx(m_shape.size(), 0);
+        for (int i = 0; i < get_num_dims(); ++i)
+            idx[i] = m_dist.get_overlap(i) - (i < get_num_spatial_dims() ? lo[i] : 0);
+        return m_buf + get_local_offset(idx, true);
+    }
+
+private:
+    Shape m_shape, m_local_shape;
+    Locale m_locale;
+    Distribution m_dist;
+    LocalShapeFn m_fn;
+    IndexVector m_proc_idx, m_split_idx, m_offset;
+    std::shared_ptr<void> m_mem;
+    DataType* m_buf = nullptr;
+};
+
+} // namespace tensor
+
+using TensorF = tensor::Tensor<float, tensor::LocaleMPI, tensor::CUDAAllocator>;
+
+namespace internal
+{
+inline int get_dilated_filter_size(int f, int d)
+{
+    return f + (f - 1) * (d - 1);
+}
+
+// distconv.hpp:21-99 for the rank whose geometry is given explicitly.
+inline void halo_sizes_for(const tensor::Shape& shape, const tensor::Distribution& dist,
+                           const tensor::IndexVector& split_idx, const tensor::IndexVector& offset,
+                           const tensor::Shape& local_shape, const tensor::IntVector& filter_dims,
+                           const tensor::IntVector& strides, const tensor::IntVector& dilations, bool with_padding,
+                           tensor::IntVector& fwd_send, tensor::IntVector& bwd_send, tensor::IntVector& fwd_recv,
+                           tensor::IntVector& bwd_recv)
+{
+    const int nd = shape.num_dims();
+    fwd_send = bwd_send = fwd_recv = bwd_recv = tensor::IntVector(nd, 0);
+    for (int i = 0; i < nd - 2; ++i)
+    {
+        if (dist.get_split_shape()[i] == 1)
+            continue;
+        const int df = get_dilated_filter_size(filter_dims[i], dilations[i]);
+        if (df % 2 == 0)
+            continue;
+        const int radius = (df - 1) / 2, s = strides[i];
+        const int off = (int) offset[i];
+        if (split_idx[i] == 0)
+        {
+            if (with_padding)
+                bwd_recv[i] = radius;
+        }
+        else
+        {
+            const int x = off - (with_padding ? 0 : radius);
+            bwd_recv[i] = radius - (s - (x % s)) % s;
+            bwd_send[i] = radius - (x - 1) % s;
+        }
+        if (!(split_idx[i] == dist.get_split_shape()[i] - 1 && !with_padding))
+        {
+            const int y = off + (int) local_shape[i] - 1 - (with_padding ? 0 : radius);
+            fwd_recv[i] = radius - y % s;
+            fwd_send[i] = radius - (s - ((y + 1) % s)) % s;
+        }
+        fwd_send[i] = std::max(fwd_send[i], 0);
+        fwd_recv[i] = std::max(fwd_recv[i], 0);
+        bwd_send[i] = std::max(bwd_send[i], 0);
+        bwd_recv[i] = std::max(bwd_recv[i], 0);
+    }
+}
+
+inline void get_halo_sizes(const TensorF& input, const tensor::IntVector& filter_dims,
+                           const tensor::IntVector& strides, const tensor::IntVector& dilations,
+                           tensor::IntVector& fwd_send, tensor::IntVector& bwd_send, tensor::IntVector& fwd_recv,
+                           tensor::IntVector& bwd_recv, bool with_padding)
+{
+    halo_sizes_for(input.get_shape(), input.get_distribution(), input.get_split_index(), input.get_global_index(),
+                   input.get_local_shape(), filter_dims, strides, dilations, with_padding, fwd_send, bwd_send,
+                   fwd_recv, bwd_recv);
+}
+} // namespace internal
+} // namespace distconv
+
+namespace distconv
+{
+
+// ---- tensor factories (distconv.hpp:253-481) -------------------------------
+inline TensorF create_input_tensor(const int_vector& shape, const int_vector& locale_shape,
+                                   const int_vector& filter_dims, const int_vector& strides,
+                                   const int_vector& dilations, bool /*deconv*/, const tensor::LocaleMPI& loc)
+{
+    const int nd = (int) shape.size();
+    tensor::IntVector overlap(nd, 0);
+    for (int i = 0; i < nd - 2; ++i)
+    {
+        if (locale_shape[i] == 1)
+            continue;
+        const int df = internal::get_dilated_filter_size(filter_dims[i], dilations[i]);
+        if (df % 2)
+            overlap[i] = (df - 1) / 2;
+    }
+    tensor::Shape s(shape.begin(), shape.end()), ls(locale_shape.begin(), locale_shape.end());
+    return TensorF(s, loc, tensor::Distribution::make_overlapped_distribution(ls, overlap));
+}
+
+inline TensorF create_d_input_tensor(const TensorF& input)
+{
+    return TensorF(input.get_shape(), input.get_locale(), input.get_distribution(), input.get_local_shape_fn());
+}
+
+// filter_shape is (fw, fh, [fd,] C, K)
+inline TensorF create_convolution_output_tensor(const TensorF& input, const int_vector& filter_shape,
+                                                const int_vector& strides, const int_vector& pad,
+                                                const int_vector& dilations, int /*num_groups*/ = 1)
+{
+    const int nd = input.get_num_dims(), nsd = nd - 2;
+    const bool use_padding = pad[0] != 0;
+    tensor::Shape out_shape(nd, 0);
+    for (int i = 0; i < nsd; ++i)
+    {
+        const int df = internal::get_dilated_filter_size(filter_shape[i], dilations[i]);
+        if (input.get_shape()[i] + 2 * pad[i] >= df)
+            out_shape[i] = (input.get_shape()[i] - df + 1 + 2 * pad[i] + strides[i] - 1) / strides[i];
+    }
+    out_shape[-2] = filter_shape.back();
+    out_shape[-1] = input.get_shape()[-1];
+    tensor::Distribution dist = input.get_distribution();
+    dist.clear_overlap();
+    tensor::IntVector fdims(filter_shape.begin(), filter_shape.begin() + nsd);
+    tensor::IntVector st(strides.begin(), strides.end()), dl(dilations.begin(), dilations.end());
+    const int K = filter_shape.back();
+    // get_convolution_output_local_tensor_shape (distconv.hpp:135-200) per grid index
+    TensorF in_copy = input;
+    auto fn = [in_copy, fdims, st, dl, use_padding, K](const tensor::IndexVector& pidx) {
+        const auto& d = in_copy.get_distribution();
+        const int nd2 = in_copy.get_num_dims();
+        tensor::IndexVector split(nd2, 0), offset(nd2, 0);
+        for (int i = 0; i < nd2; ++i)
+            split[i] = pidx[i] / d.get_num_ranks_per_split(i);
+        tensor::Shape local = in_copy.local_of(pidx);
+        for (int dim = 0; dim < nd2; ++dim)
+        {
+            if (!d.is_distributed(dim))
+                continue;
+            const index_t per = d.get_num_ranks_per_split(dim);
+            for (index_t j = 0; j < split[dim]; ++j)
+            {
+                tensor::IndexVector idx = pidx;
+                idx[dim] = j * per;
+                offset[dim] += in_copy.local_of(idx)[dim];
+            }
+        }
+        tensor::IntVector fs, bs, fr, br;
+        internal::halo_sizes_for(in_copy.get_shape(), d, split, offset, local, fdims, st, dl, use_padding, fs, bs,
+                                 fr, br);
+        tensor::Shape out = local;
+        for (int i = 0; i < nd2 - 2; ++i)
+        {
+            const int df = internal::get_dilated_filter_size(fdims[i], dl[i]);
+            index_t ext = local[i] + br[i] + fr[i];
+            if (use_padding && d.get_split_shape()[i] == 1)
+                ext += df - 1;
+            out[i] = ext < df ? 0 : (ext - df + 1 + st[i] - 1) / st[i];
+        }
+        out[-2] = K;
+        return out;
+    };
+    return TensorF(out_shape, input.get_locale(), dist, fn);
+}
+
+inline TensorF create_convolution_d_output_tensor(const TensorF& output, const int_vector& filter_shape,
+                                                  const int_vector& dilations)
+{
+    const int nd = output.get_num_dims();
+    tensor::Distribution dist = output.get_distribution();
+    tensor::IntVector overlap(nd, 0);
+    for (int i = 0; i < nd - 2; ++i)
+        if (dist.get_locale_shape()[i] > 1)
+            overlap[i] = (internal::get_dilated_filter_size(filter_shape[i], dilations[i]) - 1) / 2;
+    // the overlap only survives on distributed dimensions, as in the reference
+    tensor::Distribution d2(dist.get_locale_shape(), dist.get_split_shape(), overlap);
+    TensorF out_copy = output;
+    return TensorF(output.get_shape(), output.get_locale(), d2,
+                   [out_copy](const tensor::IndexVector& p) { return out_copy.local_of(p); });
+}
+
+namespace tensor
+{
+enum class HaloExchangeAccumOp
+{
+    ID = 0,
+    SUM = 1,
+    MAX = 2,
+    MIN = 3
+};
+
+// tensor::HaloExchange (halo_exchange_cuda.hpp:18-423) on the peer-store
+// transport.  The constructor maps the neighbours' receive slabs through the
+// tensor's locale (one allgather of 256-byte blobs).
+class HaloExchange
+{
+public:
+    explicit HaloExchange(TensorF& t) : m_tensor(t)
+    {
+        int32_t peers[2 * DCB_MAX_DIMS];
+        for (int d = 0; d < DCB_MAX_DIMS; ++d)
+            for (int s = 0; s < 2; ++s)
+                peers[2 * d + s] = find_peer_rank(d, s);
+        dcb_tensor_desc desc = t.desc();
+        util::check(dcb_halo_plan_create(&desc, peers, t.get_locale().get_rank(), &m_plan), "halo plan");
+        const int n = t.get_locale().get_size();
+        std::vector<char> mine(DCB_HALO_BLOB_BYTES), all((size_t) n * DCB_HALO_BLOB_BYTES);
+        util::check(dcb_halo_plan_export(m_plan, mine.data()), "halo export");
+        t.get_locale().allgather(mine.data(), all.data(), DCB_HALO_BLOB_BYTES);
+        util::check(dcb_halo_plan_connect(m_plan, all.data(), n), "halo connect");
+    }
+    HaloExchange(const HaloExchange&) = delete;
+    ~HaloExchange() { dcb_halo_plan_destroy(m_plan); }
+
+    int find_peer_rank(int dim, int side) const
+    {
+        const TensorF& t = m_tensor;
+        if (dim >= t.get_num_dims() || !t.get_distribution().is_distributed(dim) || t.get_halo_width(dim) == 0
+            || t.get_local_size() == 0)
+            return -1;
+        const auto& ls = t.get_distribution().get_locale_shape();
+        const index_t j = t.get_proc_index()[dim] + (side == RHS ? 1 : -1);
+        if (j < 0 || j >= ls[dim])
+            return -1;
+        if (t.get_dimension_rank_offset(dim, (int) j) == t.get_shape()[dim])
+            return -1;
+        IndexVector idx = t.get_proc_index();
+        idx[dim] = j;
+        if (t.local_of(idx).get_size() == 0)
+            return -1;
+        int r = 0, m = 1;
+        for (int i = 0; i < t.get_num_dims(); ++i)
+        {
+            r += (int) idx[i] * m;
+            m *= (int) ls[i];
+        }
+        return r;
+    }
+    // exchange(comms, stream, rendezvous, sync_back, is_reverse, skip_unpack, op)
+    void exchange(cudaStream_t stream, bool is_reverse = false, bool skip_unpack = false,
+                  HaloExchangeAccumOp op = HaloExchangeAccumOp::ID)
+    {
+        util::check(dcb_halo_exchange(m_plan, m_tensor.get_buffer(), flags(is_reverse, skip_unpack, op), stream),
+                    "halo exchange");
+    }
+    void unpack(cudaStream_t stream, bool is_reverse = false, HaloExchangeAccumOp op = HaloExchangeAccumOp::ID)
+    {
+        util::check(dcb_halo_unpack(m_plan, m_tensor.get_buffer(), flags(is_reverse, false, op), stream),
+                    "halo unpack");
+    }
+    // The two halves of one dimension's exchange, for callers that run
+    // several ranks from one process on one device and therefore must launch
+    // every rank's put before any rank's wait.
+    void pack_put(int dim, cudaStream_t stream, bool is_reverse = false,
+                  HaloExchangeAccumOp op = HaloExchangeAccumOp::ID)
+    {
+        util::check(dcb_halo_pack_put(m_plan, m_tensor.get_buffer(), dim, flags(is_reverse, false, op), stream),
+                    "halo pack_put");
+    }
+    void wait_unpack(int dim, cudaStream_t stream, bool is_reverse = false,
+                     HaloExchangeAccumOp op = HaloExchangeAccumOp::ID)
+    {
+        util::check(dcb_halo_wait_unpack(m_plan, m_tensor.get_buffer(), dim, flags(is_reverse, false, op), stream),
+                    "halo wait_unpack");
+    }
+    int32_t status(cudaStream_t stream) { return dcb_halo_plan_status(m_plan, stream); }
+
+private:
+    static uint32_t flags(bool rev, bool skip, HaloExchangeAccumOp op)
+    {
+        return (rev ? DCB_HALO_REVERSE : 0u) | (skip ? DCB_HALO_SKIP_UNPACK : 0u)
+               | ((uint32_t) op << DCB_HALO_OP_SHIFT);
+    }
+    TensorF& m_tensor;
+    dcb_halo_plan* m_plan = nullptr;
+};
+} // namespace tensor
+
+// DNNBackend<GPUDNNBackend> (dnn_backend.hpp:635-980): the main stream (not
+// owned) and a working all-reduce communicator.
+class BackendDNNLib
+{
+public:
+    BackendDNNLib(const tensor::LocaleMPI& loc, cudaStream_t stream = 0, int allreduce_max_count = 32768)
+        : m_loc(loc), m_stream(stream)
+    {
+        util::check(dcb_comm_create_peer(loc.get_rank(), loc.get_size(), allreduce_max_count, &m_comm), "comm");
+        std::vector<char> mine(DCB_COMM_BLOB_BYTES), all((size_t) loc.get_size() * DCB_COMM_BLOB_BYTES);
+        util::check(dcb_comm_export(m_comm, mine.data()), "comm export");
+        loc.allgather(mine.data(), all.data(), DCB_COMM_BLOB_BYTES);
+        util::check(dcb_comm_connect(m_comm, all.data(), loc.get_size()), "comm connect");
+    }
+    BackendDNNLib(const BackendDNNLib&) = delete;
+    ~BackendDNNLib() { dcb_comm_destroy(m_comm); }
+    std::string get_name() const { return "B200"; }
+    cudaStream_t get_stream() const { return m_stream; }
+    const tensor::LocaleMPI& get_comm() const { return m_loc; }
+    void wait() { cudaStreamSynchronize(m_stream); }
+    void allreduce(float* p, index_t count) { util::check(dcb_allreduce_sum(m_comm, p, count, m_stream), "allreduce"); }
+    // the two halves of allreduce (store to every peer / fold what arrived)
+    void allreduce_push(float* p, index_t count)
+    {
+        util::check(dcb_allreduce_push(m_comm, p, count, m_stream), "allreduce push");
+    }
+    void allreduce_pull(float* p, index_t count)
+    {
+        util::check(dcb_allreduce_pull(m_comm, p, count, m_stream), "allreduce pull");
+    }
+
+private:
+    tensor::LocaleMPI m_loc;
+    cudaStream_t m_stream;
+    dcb_comm* m_comm = nullptr;
+};
+
+template <typename Backend, typename DataType>
+class Convolution;
+template <typename Backend, typename DataType>
+class BatchNormalization;
+
+// Convolution<BackendDNNLib, float> (convolution.hpp:19-3003), spatial
+// parallelism only.  Filters, biases and their gradients are dense device
+// arrays: filter [K][C][fd][fh][fw], bias [K].
+template <>
+class Convolution<BackendDNNLib, float>
+{
+public:
+    Convolution(BackendDNNLib& backend, int num_dims, HaloExchangeMethod = HaloExchangeMethod::P2P,
+                ChannelParallelismAlgorithm = ChannelParallelismAlgorithm::NONE)
+        : m_be(backend), m_num_dims(num_dims), m_nsd(num_dims - 2)
+    {}
+    Convolution(const Convolution&) = delete;
+    ~Convolution()
+    {
+        dcb_conv_plan_destroy(m_plan_fwd);
+        dcb_conv_plan_destroy(m_plan_bwd);
+    }
+
+    // convolution.hpp:119-290.  filter_shape is (fw, fh, [fd,] C, K);
+    // pads/strides/dilations are W first.  d_input / d_output may be null
+    // (forward only).
+    void setup(TensorF& input, const int_vector& filter_shape, TensorF& output, TensorF* d_input,
+               TensorF* d_output, const int_vector& pads, const int_vector& strides, const int_vector& dilations,
+               int num_groups = 1, int math_mode = DCB_MATH_FP32)
+    {
+        if (num_groups != 1)
+            throw std::runtime_error("Convolution: grouped convolution is not provided");
+        const int nsd = m_nsd;
+        m_filter_dims = tensor::IntVector(filter_shape.begin(), filter_shape.begin() + nsd);
+        m_C = filter_shape[nsd];
+        m_K = filter_shape[nsd + 1];
+        m_strides = tensor::IntVector(strides.begin(), strides.end());
+        m_dilations = tensor::IntVector(dilations.begin(), dilations.end());
+        m_math = math_mode;
+        // setup_halo_xch (convolution.hpp:2672-2686); the d_output exchanger is
+        // built on d_output, which is what backward data reads.
+        m_halo_xch_input.reset(new tensor::HaloExchange(input));
+        if (d_output)
+            m_halo_xch_d_output.reset(new tensor::HaloExchange(*d_output));
+        m_empty = input.get_local_size() == 0 || output.get_local_size() == 0;
+        if (m_empty)
+            return;
+        tensor::IntVector stencil(nsd, 0);
+        for (int i = 0; i < nsd; ++i)
+        {
+            const int wd = internal::get_dilated_filter_size(m_filter_dims[i], dilations[i]);
+            if (wd % 2)
+                stencil[i] = (wd - 1) / 2;
+            else if (strides[i] != wd)
+                throw std::runtime_error("Convolution: even filters need stride == filter size");
+        }
+        for (int i = 0; i < nsd; ++i)
+            if (pads[i] != pads[0] || !(pads[i] == stencil[i] || pads[i] == 0))
+                throw std::runtime_error("Convolution: padding must be 0 or the stencil radius on every dim");
+        const bool use_padding = pads[0] != 0;
+        internal::get_halo_sizes(input, m_filter_dims, m_strides, m_dilations, m_halo_fwd_send, m_halo_bwd_send,
+                                 m_halo_fwd_recv, m_halo_bwd_recv, use_padding);
+        // setup_convolution_descriptor (convolution.hpp:2541-2670)
+        tensor::IntVector pads_fp(nsd, 0), pads_bp(nsd, 0);
+        for (int i = 0; i < nsd; ++i)
+        {
+            pads_bp[i] = pads[i] == 0 ? stencil[i] : stencil[i] * strides[i];
+            if (input.get_overlap()[i] > 0)
+                pads_fp[i] = 0;
+            else
+                pads_fp[i] = pads_bp[i] = pads[i];
+        }
+        m_x_lo = m_halo_bwd_recv;
+        const dcb_nd_desc xd = input.nd_desc(m_halo_bwd_recv, m_halo_fwd_recv), yd = output.nd_desc();
+        m_plan_fwd = make_plan(xd, yd, pads_fp);
+        if (d_output)
+        {
+            const dcb_nd_desc dyd = d_output->full_nd_desc();
+            const dcb_nd_desc dxd = (d_input ? *d_input : input).nd_desc(m_halo_bwd_recv, m_halo_fwd_recv);
+            m_plan_bwd = make_plan(dxd, dyd, pads_bp);
+        }
+    }
+
+    int kernel_kind(int which) const
+    {
+        return dcb_conv_plan_kernel_kind(which == 0 ? m_plan_fwd : m_plan_bwd, which);
+    }
+    tensor::HaloExchange& input_halo_exchange() { return *m_halo_xch_input; }
+    tensor::HaloExchange& d_output_halo_exchange() { return *m_halo_xch_d_output; }
+    void forward_exchange_halo(TensorF&) { m_halo_xch_input->exchange(m_be.get_stream()); }
+    void backward_data_exchange_halo(TensorF&) { m_halo_xch_d_output->exchange(m_be.get_stream()); }
+
+    // convolution.hpp:342-639, the branch without interior/boundary overlap
+    int forward(float alpha, TensorF& input, const float* filter, float beta, TensorF& output,
+                bool skip_halo_exchange = false)
+    {
+        if (input.get_local_size() == 0 || output.get_local_size() == 0)
+            return 0;
+        if (!skip_halo_exchange)
+        {
+            clear_halos(input);
+            forward_exchange_halo(input);
+        }
+        util::check(dcb_conv_fwd(m_plan_fwd, alpha, input.nd_ptr(m_x_lo), filter, beta, output.get_base_ptr(),
+                                 m_be.get_stream()),
+                    "conv forward");
+        return 0;
+    }
+    // convolution.hpp:682-876
+    int backward_data(float alpha, const float* filter, TensorF& d_output, float beta, TensorF& d_input,
+                      bool skip_halo_exchange = false)
+    {
+        if (d_output.get_local_size() == 0 || d_input.get_local_size() == 0)
+            return 0;
+        if (!skip_halo_exchange)
+            backward_data_exchange_halo(d_output);
+        util::check(dcb_conv_bwd_data(m_plan_bwd, alpha, filter, d_output.get_buffer(), beta,
+                                      d_input.nd_ptr(m_x_lo), m_be.get_stream()),
+                    "conv backward data");
+        return 0;
+    }
+    // convolution.hpp:878-1107: clears d_output's halo, then all-reduces the
+    // filter gradient over every rank.
+    int backward_filter(float alpha, TensorF& input, TensorF& d_output, float beta, float* d_filter,
+                        bool reduce = true)
+    {
+        const index_t count = (index_t) m_K * m_C * m_filter_dims.get_size();
+        if (input.get_local_size() == 0 || d_output.get_local_size() == 0 || !input.is_split_root())
+            cudaMemsetAsync(d_filter, 0, (size_t) count * sizeof(float), m_be.get_stream());
+        else
+        {
+            clear_halos(d_output);
+            util::check(dcb_conv_bwd_filter(m_plan_bwd, alpha, input.nd_ptr(m_x_lo), d_output.get_buffer(), beta,
+                                            d_filter, m_be.get_stream()),
+                        "conv backward filter");
+        }
+        if (reduce)
+            m_be.allreduce(d_filter, count);
+        return 0;
+    }
+    // convolution.hpp:641-659
+    int apply_bias(float alpha, const float* bias, float beta, TensorF& output)
+    {
+        if (output.get_local_size() == 0)
+            return 0;
+        const dcb_nd_desc yd = output.nd_desc();
+        util::check(dcb_bias_fwd(alpha, bias, beta, &yd, output.get_base_ptr(), m_be.get_stream()), "bias");
+        return 0;
+    }
+    // convolution.hpp:1109-1142
+    int backward_bias(float alpha, TensorF& d_output, float beta, float* bias_gradient, bool reduce = true)
+    {
+        if (d_output.get_local_size() == 0)
+            cudaMemsetAsync(bias_gradient, 0, (size_t) m_K * sizeof(float), m_be.get_stream());
+        else
+        {
+            const dcb_nd_desc yd = d_output.nd_desc();
+            util::check(dcb_bias_bwd(alpha, &yd, d_output.get_base_ptr(), beta, bias_gradient, m_be.get_stream()),
+                        "bias backward");
+        }
+        if (reduce)
+            m_be.allreduce(bias_gradient, m_K);
+        return 0;
+    }
+    void wait() { m_be.wait(); }
+    bool is_overlap_fwd_halo_exchange_enabled() const { return false; }
+    bool is_overlap_bwd_halo_exchange_enabled() const { return false; }
+    // DCB_OK unless a kernel of this layer gave up on a bounded wait
+    int32_t status()
+    {
+        int32_t st = m_halo_xch_input ? m_halo_xch_input->status(m_be.get_stream()) : DCB_OK;
+        if (st == DCB_OK && m_plan_fwd)
+            st = dcb_conv_plan_status(m_plan_fwd, m_be.get_stream());
+        return st;
+    }
+
+private:
+    dcb_conv_plan* make_plan(const dcb_nd_desc& xd, const dcb_nd_desc& yd, const tensor::IntVector& pads)
+    {
+        dcb_conv_desc cd{};
+        cd.nsd = m_nsd;
+        cd.k = m_K;
+        cd.c = m_C;
+        cd.groups = 1;
+        cd.math_mode = m_math;
+        for (int s = 0; s < 3; ++s)
+        {
+            cd.filter[s] = 1;
+            cd.pads[s] = 0;
+            cd.strides[s] = 1;
+            cd.dilations[s] = 1;
+        }
+        for (int i = 0; i < m_nsd; ++i)
+        {
+            cd.filter[2 - i] = m_filter_dims[i];
+            cd.pads[2 - i] = pads[i];
+            cd.strides[2 - i] = m_strides[i];
+            cd.dilations[2 - i] = m_dilations[i];
+        }
+        dcb_conv_plan* plan = nullptr;
+        util::check(dcb_conv_plan_create(&cd, &xd, &yd, &plan), "conv plan");
+        return plan;
+    }
+    void clear_halos(TensorF& t)
+    {
+        const auto& d = t.get_distribution();
+        for (int dim = 0; dim < m_nsd; ++dim)
+            if (d.is_distributed(dim) && d.get_locale_shape()[dim] > 1 && d.get_overlap(dim) > 0)
+                t.clear_halo(dim, m_be.get_stream());
+    }
+
+    BackendDNNLib& m_be;
+    int m_num_dims, m_nsd, m_K = 0, m_C = 0, m_math = DCB_MATH_FP32;
+    bool m_empty = true;
+    tensor::IntVector m_filter_dims, m_strides, m_dilations, m_x_lo;
+    tensor::IntVector m_halo_fwd_send, m_halo_bwd_send, m_halo_fwd_recv, m_halo_bwd_recv;
+    std::unique_ptr<tensor::HaloExchange> m_halo_xch_input, m_halo_xch_d_output;
+    dcb_conv_plan* m_plan_fwd = nullptr;
+    dcb_conv_plan* m_plan_bwd = nullptr;
+};
+
+// BatchNormalization<BackendDNNLib, float> (batchnorm.hpp:100-581).  The
+// statistics vectors are C contiguous device floats; pass mean and var (and
+// the gradient pairs) as the two halves of one 2C array and their all-reduce
+// is one call (batchnorm.hpp:191-211).
+template <>
+class BatchNormalization<BackendDNNLib, float>
+{
+public:
+    BatchNormalization(BackendDNNLib& backend, int num_dims, float decay, float epsilon, bool global_stats,
+                       BatchnormImpl = BatchnormImpl::PEER)
+        : m_be(backend), m_num_dims(num_dims), m_decay(decay), m_epsilon(epsilon), m_global_stats(global_stats)
+    {}
+    BatchNormalization(const BatchNormalization&) = delete;
+    ~BatchNormalization() { dcb_bn_plan_destroy(m_plan); }
+
+    int forward_stage1(TensorF& input, float* mean, float* var, bool is_training = true)
+    {
+        if (!is_training)
+            return 0;
+        const index_t C = input.get_local_shape()[-2];
+        if (input.get_local_size() == 0 || !input.is_split_root())
+        {
+            cudaMemsetAsync(mean, 0, (size_t) C * sizeof(float), m_be.get_stream());
+            cudaMemsetAsync(var, 0, (size_t) C * sizeof(float), m_be.get_stream());
+            return 0;
+        }
+        util::check(dcb_bn_stats(plan(input), input.get_base_ptr(), mean, var, m_be.get_stream()), "bn stats");
+        return 0;
+    }
+    int forward_allreduce(TensorF& input, float* mean, float* var, bool is_training = true)
+    {
+        if (is_training && m_global_stats)
+            allreduce_pair(mean, var, input.get_local_shape()[-2]);
+        return 0;
+    }
+    int forward_stage2(TensorF& input, float* mean, float* var, float* running_mean, float* running_var,
+                       const float* scale, const float* bias, TensorF& output, bool is_training = true)
+    {
+        const index_t C = input.get_local_shape()[-2];
+        const float *m = running_mean, *v = running_var;
+        if (is_training)
+        {
+            util::check(dcb_bn_finalize((int32_t) C, num_per_sum(input), m_decay, mean, var, running_mean,
+                                        running_var, m_be.get_stream()),
+                        "bn finalize");
+            m = mean;
+            v = var;
+        }
+        if (input.get_local_size() == 0)
+            return 0;
+        const dcb_nd_desc xd = input.nd_desc(), yd = output.nd_desc();
+        util::check(dcb_bn_apply(&xd, input.get_base_ptr(), m, v, scale, bias, m_epsilon, &yd,
+                                 output.get_base_ptr(), m_be.get_stream()),
+                    "bn apply");
+        return 0;
+    }
+    int forward(TensorF& input, float* mean, float* var, float* running_mean, float* running_var,
+                const float* scale, const float* bias, TensorF& output, bool is_training = true)
+    {
+        forward_stage1(input, mean, var, is_training);
+        forward_allreduce(input, mean, var, is_training);
+        return forward_stage2(input, mean, var, running_mean, running_var, scale, bias, output, is_training);
+    }
+
+    int backward_stage1(TensorF& input, TensorF& d_output, const float* mean, const float* var, const float* scale,
+                        float* scale_gradient, float* bias_gradient, float* mean_gradient, float* var_gradient)
+    {
+        const size_t bytes = (size_t) input.get_local_shape()[-2] * sizeof(float);
+        if (input.get_local_size() == 0 || !input.is_split_root())
+        {
+            for (float* g : {scale_gradient, bias_gradient, mean_gradient, var_gradient})
+                cudaMemsetAsync(g, 0, bytes, m_be.get_stream());
+            return 0;
+        }
+        const dcb_nd_desc dyd = d_output.nd_desc();
+        util::check(dcb_bn_bwd_reduce(plan(input), input.get_base_ptr(), &dyd, d_output.get_base_ptr(), mean, var,
+                                      scale, m_epsilon, scale_gradient, bias_gradient, mean_gradient, var_gradient,
+                                      m_be.get_stream()),
+                    "bn backward reduce");
+        return 0;
+    }
+    // batchnorm.hpp:360-400: dmean||dvar when statistics are global, then dscale||dbias
+    int backward_allreduce(TensorF& input, float* scale_gradient, float* bias_gradient, float* mean_gradient,
+                           float* var_gradient, bool skip_weights = false)
+    {
+        const index_t C = input.get_local_shape()[-2];
+        if (m_global_stats)
+            allreduce_pair(mean_gradient, var_gradient, C);
+        if (!skip_weights)
+            allreduce_pair(scale_gradient, bias_gradient, C);
+        return 0;
+    }
+    int backward_stage2(TensorF& input, TensorF& d_output, const float* mean, const float* var, const float* scale,
+                        const float* mean_gradient, const float* var_gradient, TensorF& d_input)
+    {
+        if (input.get_local_size() == 0)
+            return 0;
+        const dcb_nd_desc xd = input.nd_desc(), dyd = d_output.nd_desc(), dxd = d_input.nd_desc();
+        util::check(dcb_bn_bwd_apply(&xd, input.get_base_ptr(), &dyd, d_output.get_base_ptr(), mean, var, scale,
+                                     mean_gradient, var_gradient, m_epsilon, num_per_sum(input), &dxd,
+                                     d_input.get_base_ptr(), m_be.get_stream()),
+                    "bn backward apply");
+        return 0;
+    }
+    int backward(TensorF& input, TensorF& d_output, const float* mean, const float* var, const float* scale,
+                 float* scale_gradient, float* bias_gradient, float* mean_gradient, float* var_gradient,
+                 TensorF& d_input)
+    {
+        backward_stage1(input, d_output, mean, var, scale, scale_gradient, bias_gradient, mean_gradient,
+                        var_gradient);
+        backward_allreduce(input, scale_gradient, bias_gradient, mean_gradient, var_gradient);
+        return backward_stage2(input, d_output, mean, var, scale, mean_gradient, var_gradient, d_input);
+    }
+
+private:
+    dcb_bn_plan* plan(TensorF& t)
+    {
+        if (!m_plan)
+        {
+            const dcb_nd_desc xd = t.nd_desc();
+            util::check(dcb_bn_plan_create(&xd, &m_plan), "bn plan");
+        }
+        return m_plan;
+    }
+    index_t num_per_sum(const TensorF& t) const
+    {
+        const tensor::Shape& s = m_global_stats ? t.get_shape() : t.get_local_shape();
+        return s.get_size() / s[-2];
+    }
+    void allreduce_pair(float* a, float* b, index_t n)
+    {
+        if (a + n == b)
+            m_be.allreduce(a, 2 * n);
+        else if (b + n == a)
+            m_be.allreduce(b, 2 * n);
+        else
+        {
+            m_be.allreduce(a, n);
+            m_be.allreduce(b, n);
+        }
+    }
+    BackendDNNLib& m_be;
+    int m_num_dims;
+    float m_decay, m_epsilon;
+    bool m_global_stats;
+    dcb_bn_plan* m_plan = nullptr; // one tensor shape per layer object
+};
+
+// LeakyReLU<BackendDNNLib> (leaky_relu.hpp; leaky_relu.cu:14-41)
+class LeakyReLU
+{
+public:
+    explicit LeakyReLU(BackendDNNLib& backend) : m_be(backend) {}
+    int forward(TensorF& input, float negative_slope, TensorF& output)
+    {
+        if (input.get_local_size() == 0)
+            return 0;
+        const dcb_nd_desc xd = input.nd_desc(), yd = output.nd_desc();
+        util::check(dcb_leaky_relu_fwd(&xd, input.get_base_ptr(), negative_slope, &yd, output.get_base_ptr(),
+                                       m_be.get_stream()),
+                    "leaky relu");
+        return 0;
+    }
+    int backward(TensorF& input, TensorF& d_output, float negative_slope, TensorF& d_input)
+    {
+        if (input.get_local_size() == 0)
+            return 0;
+        const dcb_nd_desc xd = input.nd_desc(), dyd = d_output.nd_desc(), dxd = d_input.nd_desc();
+        util::check(dcb_leaky_relu_bwd(&xd, input.get_base_ptr(), &dyd, d_output.get_base_ptr(), negative_slope,
+                                       &dxd, d_input.get_base_ptr(), m_be.get_stream()),
+                    "leaky relu backward");
+        return 0;
+    }
+
+private:
+    BackendDNNLib& m_be;
+};
+
+} // namespace distconv

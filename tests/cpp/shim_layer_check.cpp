@@ -1,0 +1,318 @@
+// Drives one spatially-partitioned conv + batch-norm layer (forward and the
+// three backward passes of the convolution) through the C++ classes of
+// distconv_b200.hpp, with R ranks run as R host threads on one GPU, and checks
+// every result against plain loops over the unpartitioned problem.
+//
+// Because all ranks share one device, a kernel that waits for a peer is only
+// launched after the peer's kernel it waits for: each thread launches its
+// "put" half, synchronises its stream, meets the others at a host barrier and
+// only then launches the "wait" half.
+//
+// usage: shim_layer_check [ranks]   (prints "shim_layer_check OK" and exits 0)
+#include "distconv_b200.hpp"
+
+#include <cmath>
+#include <condition_variable>
+#include <cstdio>
+#include <mutex>
+#include <thread>
+#include <vector>
+
+using namespace distconv;
+
+namespace
+{
+struct Barrier
+{
+    explicit Barrier(int n) : n(n) {}
+    void wait()
+    {
+        std::unique_lock<std::mutex> lk(m);
+        const int gen = generation;
+        if (++count == n)
+        {
+            count = 0;
+            ++generation;
+            cv.notify_all();
+        }
+        else
+            cv.wait(lk, [&] { return gen != generation; });
+    }
+    int n, count = 0, generation = 0;
+    std::mutex m;
+    std::condition_variable cv;
+};
+
+// problem: W,H,D partitioned along D
+constexpr int W = 20, H = 12, D = 16, C = 4, K = 8, N = 2, F = 3;
+constexpr float EPS = 1e-5f, DECAY = 0.9f;
+
+float synth(int64_t i, int salt)
+{
+    uint32_t h = (uint32_t) (i * 2654435761u) ^ (uint32_t) (salt * 40503u);
+    h ^= h >> 15;
+    h *= 2246822519u;
+    h ^= h >> 13;
+    return (float) ((int) (h % 2001) - 1000) / 1000.f;
+}
+inline size_t gi(int n, int c, int d, int h, int w, int Cc)
+{
+    return ((((size_t) n * Cc + c) * D + d) * H + h) * W + w;
+}
+
+struct Global
+{
+    std::vector<float> x, w, dy, y, dx, dw, z; // z = batch-norm output
+    std::vector<float> mean, var;
+};
+
+void reference(Global& g)
+{
+    const size_t nx = (size_t) N * C * D * H * W, ny = (size_t) N * K * D * H * W;
+    g.y.assign(ny, 0.f);
+    g.dx.assign(nx, 0.f);
+    g.dw.assign((size_t) K * C * F * F * F, 0.f);
+    std::vector<double> dxa(nx, 0.0), dwa(g.dw.size(), 0.0);
+    for (int n = 0; n < N; ++n)
+        for (int k = 0; k < K; ++k)
+            for (int d = 0; d < D; ++d)
+                for (int h = 0; h < H; ++h)
+                    for (int w = 0; w < W; ++w)
+                    {
+                        double acc = 0;
+                        const float dyv = g.dy[gi(n, k, d, h, w, K)];
+                        for (int c = 0; c < C; ++c)
+                            for (int fd = 0; fd < F; ++fd)
+                                for (int fh = 0; fh < F; ++fh)
+                                    for (int fw = 0; fw < F; ++fw)
+                                    {
+                                        const int id = d + fd - 1, ih = h + fh - 1, iw = w + fw - 1;
+                                        if (id < 0 || id >= D || ih < 0 || ih >= H || iw < 0 || iw >= W)
+                                            continue;
+                                        const size_t wi = ((((size_t) k * C + c) * F + fd) * F + fh) * F + fw;
+                                        const size_t xi = gi(n, c, id, ih, iw, C);
+                                        acc += (double) g.x[xi] * g.w[wi];
+                                        dxa[xi] += (double) dyv * g.w[wi];
+                                        dwa[wi] += (double) dyv * g.x[xi];
+                                    }
+                        g.y[gi(n, k, d, h, w, K)] = (float) acc;
+                    }
+    for (size_t i = 0; i < nx; ++i)
+        g.dx[i] = (float) dxa[i];
+    for (size_t i = 0; i < dwa.size(); ++i)
+        g.dw[i] = (float) dwa[i];
+    // batch norm over y with unit scale / zero bias, unbiased variance
+    g.z.assign(ny, 0.f);
+    g.mean.assign(K, 0.f);
+    g.var.assign(K, 0.f);
+    const double cnt = (double) N * D * H * W;
+    for (int k = 0; k < K; ++k)
+    {
+        double s = 0, q = 0;
+        for (int n = 0; n < N; ++n)
+            for (size_t i = 0; i < (size_t) D * H * W; ++i)
+            {
+                const double v = g.y[((size_t) n * K + k) * D * H * W + i];
+                s += v;
+                q += v * v;
+            }
+        const double m = s / cnt, var = (q / cnt - m * m) * cnt / (cnt - 1);
+        g.mean[k] = (float) m;
+        g.var[k] = (float) var;
+        const double inv = 1.0 / std::sqrt(var + EPS);
+        for (int n = 0; n < N; ++n)
+            for (size_t i = 0; i < (size_t) D * H * W; ++i)
+            {
+                const size_t j = ((size_t) n * K + k) * D * H * W + i;
+                g.z[j] = (float) ((g.y[j] - m) * inv);
+            }
+    }
+}
+
+// copies between a shard (halo-extended, device) and the global host array
+void scatter(TensorF& t, const std::vector<float>& g, int Cc)
+{
+    const auto real = t.get_local_real_shape();
+    const auto& loc = t.get_local_shape();
+    const auto& off = t.get_global_index();
+    const auto& ov = t.get_overlap();
+    std::vector<float> host((size_t) real.get_size(), 0.f);
+    for (int n = 0; n < loc[4]; ++n)
+        for (int c = 0; c < loc[3]; ++c)
+            for (int d = 0; d < loc[2]; ++d)
+                for (int h = 0; h < loc[1]; ++h)
+                    for (int w = 0; w < loc[0]; ++w)
+                    {
+                        const size_t li = ((((size_t) n * real[3] + c) * real[2] + d + ov[2]) * real[1] + h + ov[1])
+                                              * real[0]
+                                          + w + ov[0];
+                        host[li] = g[gi(n + (int) off[4], c + (int) off[3], d + (int) off[2], h + (int) off[1],
+                                        w + (int) off[0], Cc)];
+                    }
+    cudaMemcpy(t.get_buffer(), host.data(), host.size() * sizeof(float), cudaMemcpyHostToDevice);
+}
+
+double gather_err(TensorF& t, const std::vector<float>& g, int Cc)
+{
+    const auto real = t.get_local_real_shape();
+    const auto& loc = t.get_local_shape();
+    const auto& off = t.get_global_index();
+    const auto& ov = t.get_overlap();
+    std::vector<float> host((size_t) real.get_size());
+    cudaMemcpy(host.data(), t.get_buffer(), host.size() * sizeof(float), cudaMemcpyDeviceToHost);
+    double err = 0;
+    for (int n = 0; n < loc[4]; ++n)
+        for (int c = 0; c < loc[3]; ++c)
+            for (int d = 0; d < loc[2]; ++d)
+                for (int h = 0; h < loc[1]; ++h)
+                    for (int w = 0; w < loc[0]; ++w)
+                    {
+                        const size_t li = ((((size_t) n * real[3] + c) * real[2] + d + ov[2]) * real[1] + h + ov[1])
+                                              * real[0]
+                                          + w + ov[0];
+                        const float ref = g[gi(n + (int) off[4], c + (int) off[3], d + (int) off[2],
+                                               h + (int) off[1], w + (int) off[0], Cc)];
+                        err = std::max(err, (double) std::fabs(host[li] - ref) / (1.0 + std::fabs(ref)));
+                    }
+    return err;
+}
+
+struct Shared
+{
+    explicit Shared(int r) : bar(r), blobs((size_t) r * 256), fail(0) {}
+    Barrier bar;
+    std::vector<char> blobs;
+    std::mutex m;
+    int fail;
+};
+
+void rank_main(int rank, int R, Shared* sh, const Global* g)
+{
+    try
+    {
+        cudaSetDevice(0);
+        cudaStream_t st;
+        cudaStreamCreate(&st);
+        auto ag = [sh, rank](const void* in, void* out, size_t n) {
+            sh->bar.wait();
+            std::memcpy(sh->blobs.data() + (size_t) rank * n, in, n);
+            sh->bar.wait();
+            std::memcpy(out, sh->blobs.data(), sh->blobs.size() / 256 * n);
+        };
+        tensor::LocaleMPI loc(rank, R, ag);
+        BackendDNNLib be(loc, st);
+        const int_vector shape{W, H, D, C, N}, grid{1, 1, R, 1, 1}, fshape{F, F, F, C, K};
+        const int_vector f3{F, F, F}, ones{1, 1, 1}, pads{1, 1, 1};
+        TensorF x = create_input_tensor(shape, grid, f3, ones, ones, false, loc);
+        TensorF dx = create_d_input_tensor(x);
+        TensorF y = create_convolution_output_tensor(x, fshape, ones, pads, ones);
+        TensorF dy = create_convolution_d_output_tensor(y, fshape, ones);
+        TensorF z = create_convolution_output_tensor(x, fshape, ones, pads, ones);
+        for (TensorF* t : {&x, &dx, &y, &dy, &z})
+            if (t->allocate())
+                throw std::runtime_error("allocate");
+        scatter(x, g->x, C);
+        scatter(dy, g->dy, K);
+        const size_t wcount = (size_t) K * C * F * F * F;
+        float *w = nullptr, *dw = nullptr, *stats = nullptr;
+        cudaMalloc((void**) &w, wcount * 4);
+        cudaMalloc((void**) &dw, wcount * 4);
+        cudaMalloc((void**) &stats, 6 * K * 4); // mean|var|running mean|running var|scale|bias
+        cudaMemcpy(w, g->w.data(), wcount * 4, cudaMemcpyHostToDevice);
+        std::vector<float> init(6 * K, 0.f);
+        for (int k = 0; k < K; ++k)
+            init[3 * K + k] = init[4 * K + k] = 1.f; // running var, scale
+        cudaMemcpy(stats, init.data(), init.size() * 4, cudaMemcpyHostToDevice);
+
+        Convolution<BackendDNNLib, float> conv(be, 5, HaloExchangeMethod::P2P);
+        conv.setup(x, fshape, y, &dx, &dy, pads, ones, ones);
+        BatchNormalization<BackendDNNLib, float> bn(be, 5, DECAY, EPS, true);
+
+        auto phase = [&](auto put, auto wait) {
+            put();
+            cudaStreamSynchronize(st);
+            sh->bar.wait();
+            wait();
+            cudaStreamSynchronize(st);
+            sh->bar.wait();
+        };
+        // forward: halo exchange of x (D is the only partitioned dimension)
+        x.clear_halo(2, st);
+        phase([&] { conv.input_halo_exchange().pack_put(2, st); },
+              [&] { conv.input_halo_exchange().wait_unpack(2, st); });
+        conv.forward(1.f, x, w, 0.f, y, /*skip_halo_exchange=*/true);
+        bn.forward_stage1(y, stats, stats + K);
+        phase([&] { be.allreduce_push(stats, 2 * K); }, [&] { be.allreduce_pull(stats, 2 * K); });
+        bn.forward_stage2(y, stats, stats + K, stats + 2 * K, stats + 3 * K, stats + 4 * K, stats + 5 * K, z);
+        // backward of the convolution
+        phase([&] { conv.d_output_halo_exchange().pack_put(2, st); },
+              [&] { conv.d_output_halo_exchange().wait_unpack(2, st); });
+        conv.backward_data(1.f, w, dy, 0.f, dx, /*skip_halo_exchange=*/true);
+        conv.backward_filter(1.f, x, dy, 0.f, dw, /*reduce=*/false);
+        phase([&] { be.allreduce_push(dw, (index_t) wcount); }, [&] { be.allreduce_pull(dw, (index_t) wcount); });
+        if (conv.status() != DCB_OK)
+            throw std::runtime_error("layer status");
+        cudaStreamSynchronize(st);
+
+        std::vector<float> hdw(wcount), hstats(2 * K);
+        cudaMemcpy(hdw.data(), dw, wcount * 4, cudaMemcpyDeviceToHost);
+        cudaMemcpy(hstats.data(), stats, 2 * K * 4, cudaMemcpyDeviceToHost);
+        double e_dw = 0, e_st = 0;
+        for (size_t i = 0; i < wcount; ++i)
+            e_dw = std::max(e_dw, (double) std::fabs(hdw[i] - g->dw[i]) / (1.0 + std::fabs(g->dw[i])));
+        for (int k = 0; k < K; ++k)
+        {
+            e_st = std::max(e_st, (double) std::fabs(hstats[k] - g->mean[k]));
+            e_st = std::max(e_st, (double) std::fabs(hstats[K + k] - g->var[k]) / (1.0 + g->var[k]));
+        }
+        const double e_y = gather_err(y, g->y, K), e_dx = gather_err(dx, g->dx, C), e_z = gather_err(z, g->z, K);
+        std::printf("rank %d/%d: y %.2e  dx %.2e  dw %.2e  stats %.2e  bn %.2e  (fwd kernel kind %d)\n", rank, R,
+                    e_y, e_dx, e_dw, e_st, e_z, conv.kernel_kind(0));
+        const bool ok = e_y < 2e-5 && e_dx < 2e-5 && e_dw < 5e-5 && e_st < 2e-5 && e_z < 1e-4;
+        if (!ok)
+        {
+            std::lock_guard<std::mutex> lk(sh->m);
+            sh->fail = 1;
+        }
+        sh->bar.wait(); // nobody tears its windows down while a peer may still read them
+        cudaFree(w);
+        cudaFree(dw);
+        cudaFree(stats);
+    }
+    catch (const std::exception& e)
+    {
+        std::fprintf(stderr, "rank %d: %s\n", rank, e.what());
+        std::exit(2); // a rank that left would strand the others at the barrier
+    }
+}
+} // namespace
+
+int main(int argc, char** argv)
+{
+    const int R = argc > 1 ? std::atoi(argv[1]) : 2;
+    Global g;
+    const size_t nx = (size_t) N * C * D * H * W, ny = (size_t) N * K * D * H * W;
+    g.x.resize(nx);
+    g.dy.resize(ny);
+    g.w.resize((size_t) K * C * F * F * F);
+    for (size_t i = 0; i < nx; ++i)
+        g.x[i] = synth((int64_t) i, 1);
+    for (size_t i = 0; i < ny; ++i)
+        g.dy[i] = synth((int64_t) i, 2);
+    for (size_t i = 0; i < g.w.size(); ++i)
+        g.w[i] = 0.25f * synth((int64_t) i, 3);
+    reference(g);
+    Shared sh(R);
+    std::vector<std::thread> th;
+    for (int r = 0; r < R; ++r)
+        th.emplace_back(rank_main, r, R, &sh, &g);
+    for (auto& t : th)
+        t.join();
+    if (sh.fail)
+    {
+        std::printf("shim_layer_check FAILED\n");
+        return 1;
+    }
+    std::printf("shim_layer_check OK\n");
+    return 0;
+}
