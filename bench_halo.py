@@ -1,0 +1,226 @@
+#!/usr/bin/env python
+"""Halo-exchange sweep (BASELINE.json configs[4]): fp32 5-D tensors, N=1,
+C in {4,16,64}, S in {128,256,512}, halo width in {1,2,3}.
+
+    python bench_halo.py [--max-gb G] [--reps R]                 # one GPU
+    python -m torch.distributed.run --nproc-per-node P ... bench_halo.py
+
+One GPU: two ranks are emulated in the process (their receive slabs live on the
+same device), partitioned along W, H or D in turn, so every face orientation
+is measured.  The two halves of an exchange are timed apart: "pack+put" reads
+the strided face and stores it into the neighbour's slab, "wait+unpack" copies
+the slab into the halo cells.  Each moves 4E bytes in and 4E out per face
+(E = width x product of the other real extents), so GB/s = 8E x faces / time is
+the HBM figure.  All ranks put before any rank waits, so no kernel ever waits
+for a kernel that has not been launched.
+
+P GPUs (torchrun): real ranks, S^3 split along D; the whole exchange is timed
+(max over ranks) and the bytes each GPU sends per direction (4E) over that time
+is the NVLink figure.
+
+The payload is the global-offset fill of the reference's halo test, and every
+configuration is checked for exact halo contents after the timed runs.
+Prints one JSON line per configuration and a last summary line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def global_offset_fill(t, torch):
+    """Owned cell <- its global linear offset modulo 2^24 (exact in fp32)."""
+    ls = t.local_shape  # W,H,D,C,N
+    idx = [torch.arange(ls[i], device="cuda", dtype=torch.int64) + t.offset[i] for i in range(5)]
+    sh = t.shape
+    lin = idx[4].view(-1, 1, 1, 1, 1)
+    for i in (3, 2, 1, 0):
+        v = [1, 1, 1, 1, 1]
+        v[4 - i] = -1
+        lin = lin * sh[i] + idx[i].view(*v)
+    t.owned().copy_((lin % (1 << 24)).to(torch.float32))
+
+
+def check_halo(t, dim, torch):
+    """The halo cells along `dim` must hold the neighbour's global offsets."""
+    ls, ov, sh = t.local_shape, t.dist.overlap, t.shape
+    w = ov[dim]
+    full = t.buffer.view(tuple(reversed(t.get_local_real_shape())))
+    ok = True
+    for side in (0, 1):
+        lo = t.offset[dim] - w if side == 0 else t.offset[dim] + ls[dim]
+        if lo < 0 or lo + w > sh[dim]:
+            continue
+        rng = [torch.arange(ls[i], device="cuda", dtype=torch.int64) + t.offset[i] for i in range(5)]
+        rng[dim] = torch.arange(w, device="cuda", dtype=torch.int64) + lo
+        lin = rng[4].view(-1, 1, 1, 1, 1)
+        for i in (3, 2, 1, 0):
+            v = [1, 1, 1, 1, 1]
+            v[4 - i] = -1
+            lin = lin * sh[i] + rng[i].view(*v)
+        sl = []
+        for i in (4, 3, 2, 1, 0):
+            if i == dim:
+                start = 0 if side == 0 else ov[i] + ls[i]
+                sl.append(slice(start, start + w))
+            else:
+                sl.append(slice(ov[i], ov[i] + ls[i]))
+        ok = ok and bool(torch.equal(full[tuple(sl)], (lin % (1 << 24)).to(torch.float32)))
+    return ok
+
+
+def make_tensor(dc, shape, locale_shape, width, locale):
+    ov = [width if locale_shape[i] > 1 else 0 for i in range(5)]
+    t = dc.Tensor(shape, locale, dc.Distribution.make_overlapped_distribution(locale_shape, ov))
+    t.allocate()
+    return t
+
+
+def run_emulated(args, torch, dc):
+    from dihydrogen_b200 import _abi
+
+    results = []
+    locs = [dc.Locale(r, 2) for r in range(2)]
+    for C in args.channels:
+        for S in args.sizes:
+            if 2 * C * S ** 3 * 4 / 1e9 > args.max_gb:
+                continue
+            for width in args.widths:
+                for dim in (0, 1, 2):
+                    shape = [S, S, S, C, 1]
+                    ls = [1, 1, 1, 1, 1]
+                    ls[dim] = 2
+                    ts = [make_tensor(dc, shape, ls, width, l) for l in locs]
+                    for t in ts:
+                        global_offset_fill(t, torch)
+                    hx = [dc.HaloExchange(t) for t in ts]
+                    blobs = [h.export() for h in hx]
+                    for h in hx:
+                        h.connect(blobs)
+                    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+                    t_put = t_unpack = 0.0
+                    for it in range(args.reps + 3):
+                        ev[0].record()
+                        for h in hx:
+                            h.pack_put(dim)
+                        ev[1].record()
+                        for h in hx:
+                            h.wait_unpack(dim)
+                        ev[2].record()
+                        torch.cuda.synchronize()
+                        if it >= 3:
+                            t_put += ev[0].elapsed_time(ev[1])
+                            t_unpack += ev[1].elapsed_time(ev[2])
+                    exact = all(check_halo(t, dim, torch) for t in ts)
+                    status = max(h.status() for h in hx)
+                    real = ts[0].get_local_real_shape()
+                    E = width * C
+                    for i in range(3):
+                        if i != dim:
+                            E *= real[i]
+                    faces = 2  # rank 0 sends its RHS face, rank 1 its LHS face
+                    r = {"mode": "1gpu-emulated-2-ranks", "C": C, "S": S, "width": width, "dim": "WHD"[dim],
+                         "face_MB": 4 * E / 1e6,
+                         "pack_put_us": 1e3 * t_put / args.reps, "wait_unpack_us": 1e3 * t_unpack / args.reps,
+                         "pack_put_GBs": 8 * E * faces / (t_put / args.reps * 1e-3) / 1e9,
+                         "wait_unpack_GBs": 8 * E * faces / (t_unpack / args.reps * 1e-3) / 1e9,
+                         "exact": exact, "status": status}
+                    print(json.dumps(r), flush=True)
+                    results.append(r)
+                    del hx, ts
+                    torch.cuda.empty_cache()
+                    if not exact or status != _abi.OK:
+                        raise SystemExit("halo contents differ from the global-offset fill")
+    return results
+
+
+def run_ranks(args, torch, dc, dist, world, rank):
+    from dihydrogen_b200 import _abi
+
+    locale = dc.Locale.from_torch_distributed()
+    results = []
+    for C in args.channels:
+        for S in args.sizes:
+            if C * S ** 3 * 4 / world / 1e9 > args.max_gb:
+                continue
+            for width in args.widths:
+                shape, ls = [S, S, S, C, 1], [1, 1, world, 1, 1]
+                t = make_tensor(dc, shape, ls, width, locale)
+                global_offset_fill(t, torch)
+                hx = dc.HaloExchange(t).setup()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                total = 0.0
+                for it in range(args.reps + 3):
+                    torch.cuda.synchronize()
+                    dist.barrier()
+                    torch.cuda.synchronize()
+                    e0.record()
+                    hx.exchange()
+                    e1.record()
+                    torch.cuda.synchronize()
+                    if it >= 3:
+                        total += e0.elapsed_time(e1)
+                ms = torch.tensor([total / args.reps], device="cuda")
+                dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+                good = torch.tensor([1 if (check_halo(t, 2, torch) and hx.status() == _abi.OK) else 0], device="cuda")
+                dist.all_reduce(good, op=dist.ReduceOp.MIN)
+                E = width * C * S * S
+                r = {"mode": f"{world}gpu-D-partition", "C": C, "S": S, "width": width, "dim": "D",
+                     "face_MB": 4 * E / 1e6, "exchange_us": 1e3 * float(ms.item()),
+                     "nvlink_GBs_per_direction": 4 * E / (float(ms.item()) * 1e-3) / 1e9,
+                     "exact": bool(good.item())}
+                if rank == 0:
+                    print(json.dumps(r), flush=True)
+                results.append(r)
+                dist.barrier()
+                del hx, t
+                torch.cuda.empty_cache()
+                if not r["exact"]:
+                    raise SystemExit("halo contents differ from the global-offset fill")
+    return results
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--channels", type=int, nargs="+", default=[4, 16, 64])
+    ap.add_argument("--sizes", type=int, nargs="+", default=[128, 256, 512])
+    ap.add_argument("--widths", type=int, nargs="+", default=[1, 2, 3])
+    ap.add_argument("--reps", type=int, default=10)
+    ap.add_argument("--max-gb", type=float, default=20.0,
+                    help="skip configurations whose tensors exceed this many GB on one device")
+    args = ap.parse_args()
+    import torch
+
+    import dihydrogen_b200 as dc
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench_halo.py needs a CUDA device")
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
+        res = run_ranks(args, torch, dc, dist, world, rank)
+        key = "nvlink_GBs_per_direction"
+    else:
+        res = run_emulated(args, torch, dc)
+        key = "pack_put_GBs"
+    if rank == 0 and res:
+        best = max(res, key=lambda r: r[key])
+        print(json.dumps({"summary": True, "configs": len(res), "best_" + key: best[key],
+                          "best_config": {k: best[k] for k in ("C", "S", "width", "dim")}}))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

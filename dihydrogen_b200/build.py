@@ -62,8 +62,6 @@ def build(force: bool = False, verbose: bool = False) -> str:
         objs.append(obj)
         if force or not os.path.exists(obj) or os.path.getmtime(obj) < max(os.path.getmtime(src), hdr_t):
             cmd = [nvcc, *NVCC_FLAGS, "-c", src, "-o", obj]
-            if os.environ.get("DCB_TC_PROFILE"):
-                cmd.insert(1, "-DDCB_TC_PROFILE")
             if verbose:
                 cmd.insert(1, "-Xptxas=-v")
             jobs.append(cmd)

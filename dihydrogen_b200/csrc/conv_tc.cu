@@ -38,22 +38,30 @@ size_t tc_smem_need(const TcGeom& g)
            + (size_t) ((g.kr + 1) & ~1) * 4 + (size_t) (2 * g.a_slots + 4 + 2 * g.raw_slots) * 8 + 64 + 1024;
 }
 
-// Raw-row ring: whole rows when bulk copies feed it (as many as ~64 KiB hold,
-// a multiple of the group count), else one private window set per group.
+// Raw-row ring.  When bulk copies feed it, one copy brings chunk_rows rows of
+// every channel (about 17 KiB) and the ring holds up to four such chunks; else
+// it is one private window set per converter group.
 void tc_size_raw_ring(TcGeom& g)
 {
     if (g.use_tma)
     {
-        g.raw_slot_bytes = (g.c * TC_RAW_W * 4 + 127) / 128 * 128;
-        int slots = (64 * 1024) / g.raw_slot_bytes / g.groups * g.groups;
-        slots = slots > 16 * g.groups ? 16 * g.groups : slots;
-        if (slots >= g.groups)
+        const int rows = g.th + g.f[1] - 1, row_bytes = g.c * TC_RAW_W * 4;
+        int rc = (17 * 1024 + 512) / row_bytes;
+        rc = rc < 1 ? 1 : (rc > rows ? rows : rc);
+        g.chunk_rows = rc;
+        g.chunks_pp = (rows + rc - 1) / rc;
+        g.raw_slot_bytes = (rc * row_bytes + 127) / 128 * 128;
+        int slots = (72 * 1024) / g.raw_slot_bytes;
+        slots = slots > 4 ? 4 : slots;
+        if (slots >= 2)
         {
             g.raw_slots = slots;
             return;
         }
         g.use_tma = 0;
     }
+    g.chunk_rows = 0;
+    g.chunks_pp = 1;
     g.raw_slot_bytes = (4 * g.c * TC_RAW_PRIV * 4 + 127) / 128 * 128;
     g.raw_slots = g.groups;
 }
@@ -111,9 +119,8 @@ bool tc_geom(const ConvGeom& cg, int math_mode, TcGeom* out)
     g.groups = 3 * g.kr <= 192 ? 3 : (2 * g.kr <= 192 ? 2 : 1);
     if (g.kr > 192)
         return false;
-    // One slot per group unless the rows are narrow: deeper rings cost
-    // accumulator rows, and the row rate is set by the MMA issue, not by the
-    // ring depth.
+    // One slot per group unless the rows are narrow: a deeper ring costs
+    // accumulator rows and was measured to gain nothing.
     g.a_slots = g.groups * (2 * g.groups * g.kr <= 96 ? 2 : 1);
     g.th = ((int) TC_TMEM_COLS - g.a_slots * g.kr) / (2 * g.nb);
     g.th = g.th > 16 ? 16 : g.th;
@@ -229,7 +236,7 @@ static EncodeTiledFn encode_tiled_fn()
 }
 
 // Descriptor of the input window as a 5-D tensor (W, H, D, C, N) whose box is
-// one raw row of every channel.  Returns false when the window cannot be
+// chunk_rows raw rows of every channel.  Returns false when the window cannot be
 // described (alignment), in which case the register-fed producers run.
 static bool make_x_map(const TcGeom& g, const float* x, CUtensorMap* map)
 {
@@ -245,7 +252,7 @@ static bool make_x_map(const TcGeom& g, const float* x, CUtensorMap* map)
     for (int i = 0; i < 4; ++i)
         if (strides[i] % 16 != 0 || strides[i] == 0)
             return false;
-    const cuuint32_t box[5] = {(cuuint32_t) TC_RAW_W, 1, 1, (cuuint32_t) g.c, 1};
+    const cuuint32_t box[5] = {(cuuint32_t) TC_RAW_W, (cuuint32_t) g.chunk_rows, 1, (cuuint32_t) g.c, 1};
     const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 5, const_cast<float*>(x), dims, strides, box, estr,
               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,

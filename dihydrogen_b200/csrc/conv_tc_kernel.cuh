@@ -13,9 +13,10 @@ namespace
 
 constexpr int TC_GROUPS_MAX = 3;                  // row groups of 4 converter warps
 constexpr int TC_PRODUCERS = 4 * TC_GROUPS_MAX;   // warps 0..11: warp w -> group w / 4, TMEM quadrant w % 4
-constexpr int TC_MMA_WARP = TC_PRODUCERS;         // warp 12 issues the MMAs
-constexpr int TC_TMA_WARP = TC_PRODUCERS + 1;     // warp 13 issues the bulk tensor loads
-constexpr int TC_THREADS = (TC_PRODUCERS + 6) * 32; // + epilogue warps 14..17
+constexpr int TC_MMA_WARP = TC_PRODUCERS;         // warps 12..14: one MMA issuer per converter group
+constexpr int TC_TMA_WARP = TC_PRODUCERS + TC_GROUPS_MAX; // warp 15 issues the bulk tensor loads
+constexpr int TC_EPI_WARPS = 8;                   // warps 16..23 drain the accumulators, two per TMEM quadrant
+constexpr int TC_THREADS = (TC_PRODUCERS + TC_GROUPS_MAX + 1 + TC_EPI_WARPS) * 32;
 constexpr int TC_M = 128;
 constexpr int TC_RAW_W = TC_M + 8;     // staged raw row: 4 cells left, 4 right
 constexpr int TC_RAW_PRIV = 32 + 8;    // per-warp raw window when rows are fetched by the converters
@@ -42,8 +43,11 @@ struct TcGeom
     int tiles_w, tiles_h;
     long long tiles;
     int use_tma;        // raw rows arrive by bulk tensor copies
-    int raw_slots;      // ring of raw rows in shared memory, a multiple of groups
-    int raw_slot_bytes; // c * TC_RAW_W floats, rounded up to 128 bytes
+    int raw_slots;      // ring of raw chunks in shared memory
+    int raw_slot_bytes; // one chunk, rounded up to 128 bytes: c * chunk_rows * TC_RAW_W floats when
+                        // bulk copies feed the ring, else one private window set per converter group
+    int chunk_rows;     // staged rows per bulk copy
+    int chunks_pp;      // bulk copies per filter plane of a tile
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p)
@@ -204,10 +208,6 @@ __global__ void tc_pack_filter_kernel(const float* __restrict__ w, float* __rest
 // The staged input rows of one tile, in issue order: filter planes kd in
 // [kd_lo, kd_hi) x rows i in [i_lo, i_hi); everything outside lies in the zero
 // padding and contributes nothing.
-
-// The staged input rows of one tile, in issue order: filter planes kd in
-// [kd_lo, kd_hi) x rows i in [i_lo, i_hi); everything outside lies in the zero
-// padding and contributes nothing.
 struct TileRows
 {
     int n, od, oh0, ow0;
@@ -338,25 +338,29 @@ __device__ __forceinline__ void convert_c4f3(uint32_t raw_lane, uint32_t pitch, 
 }
 
 // ---------------------------------------------------------------------------
-// The convolution kernel.  One CTA per SM, 18 warps:
-//   warp 13      streams raw input rows (all channels, 4 cells of margin each
-//                side) into a shared-memory ring with bulk tensor copies
+// The convolution kernel.  One CTA per SM, 24 warps:
+//   warp 15      streams raw input rows (all channels, 4 cells of margin each
+//                side) into a shared-memory ring with bulk tensor copies, a
+//                chunk of several rows per copy
 //   warps 0..11  three groups of four; group g converts rows g, g+3, ... of
 //                the CTA's row sequence: each lane takes one output column,
 //                splits its c*fw taps into hi / lo TF32 and writes them as the
 //                A operand straight into tensor memory (warp w may touch TMEM
 //                lanes 32*(w%4).., hence four warps per row)
-//   warp 12      issues tcgen05.mma (A from TMEM, B = filter image in shared
-//                memory), one accumulator block range per staged row
-//   warps 14..17 drain the accumulators: TMEM -> registers -> global
+//   warps 12..14 issue tcgen05.mma (A from TMEM, B = filter image in shared
+//                memory), one accumulator block range per staged row; issuer
+//                q serves converter group q
+//   warps 16..23 drain the accumulators: TMEM -> registers -> global
 // TMEM columns: [acc 0][acc 1][A ring].  Accumulator buffers alternate between
 // tiles, so a tile's epilogue overlaps the next tile's main loop.
 //
 // Barrier ownership.  A parity wait only tells the current phase from the
 // previous one, so a barrier must never have a waiter that is two phases
-// ahead.  Every ring (A slots, raw slots) therefore has a slot count that is
-// a multiple of the group count and slot s is only ever used by group
-// s % groups, whose rows are processed in order.
+// ahead.  The A ring therefore has a slot count that is a multiple of the
+// group count and slot s is only ever used by group s % groups (its converter
+// warps and its issuer), whose rows are processed in order.  A raw chunk is
+// released by all converter warps together, so none of them can be a whole
+// lap behind the copy warp.
 // ---------------------------------------------------------------------------
 template <int NB, bool C4F3>
 __global__ void __launch_bounds__(TC_THREADS, 1)
@@ -390,13 +394,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         }
         for (int b = 0; b < 2; ++b)
         {
-            mbar_init(&acc_full[b], 1);
-            mbar_init(&acc_empty[b], 4);
+            mbar_init(&acc_full[b], g.groups);
+            mbar_init(&acc_empty[b], TC_EPI_WARPS);
         }
         for (int r = 0; r < g.raw_slots; ++r)
         {
             mbar_init(&raw_full[r], 1);
-            mbar_init(&raw_empty[r], 4);
+            mbar_init(&raw_empty[r], 4 * g.groups);
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -414,7 +418,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     {
         const int part = r / g.crows, rem = r % g.crows;
         const int c = rem / g.f[2], kw = rem % g.f[2];
-        const uint32_t off = (uint32_t) (c * (g.use_tma ? TC_RAW_W : TC_RAW_PRIV) + 4 + kw - g.pad[2]);
+        const uint32_t off = (uint32_t) (c * (g.use_tma ? g.chunk_rows * TC_RAW_W : TC_RAW_PRIV) + 4 + kw - g.pad[2]);
         ktab[r] = (part < (g.split ? 2 : 1)) ? (off | ((uint32_t) part << 16)) : ((2u << 16) | 4u);
     }
     for (int i = tid; i < g.b_bytes / 16; i += TC_THREADS)
@@ -436,39 +440,45 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         const int G = g.groups, gq = warp >> 2, quad = warp & 3;
         const int mcol = g.use_tma ? quad * 32 + lane : lane; // column inside the raw window
         const uint32_t lane_addr = tmem_base + ((uint32_t) (quad * 32) << 16);
-        const int laps_a = g.a_slots / G, laps_r = g.raw_slots / G;
+        const int laps_a = g.a_slots / G;
         const uint32_t ktab_s = smem_u32(ktab);
-        int lap_a = 0, lap_r = 0;
-        uint32_t a_phase = 1, raw_phase = 0; // a_phase: parity of the release to wait for
+        // bulk-copy mode: a filter plane of the tile arrives as chunks_pp chunks
+        // of Rc rows; otherwise the plane is one "chunk" that nothing copies
+        const int Rc = g.use_tma ? g.chunk_rows : (1 << 20), chunks_pp = g.use_tma ? g.chunks_pp : 1;
+        const int pitch = g.use_tma ? g.chunk_rows * TC_RAW_W : TC_RAW_PRIV; // channel pitch of a raw window
+        int lap_a = 0;
+        uint32_t cslot = 0, cphase = 0; // position in the chunk ring
+        uint32_t a_phase = 1;           // parity of the A-slot release to wait for
         bool a_first = true;
         uint32_t base = 0; // (sequence number of the tile's first row) % G
-#ifdef DCB_TC_PROFILE
-        long long p_raw = 0, p_conv = 0, p_slot = 0, p_st = 0, p_all = clock64(), pc0, pc1, pc2, pc3;
-        int p_rows = 0;
-#endif
         for (uint32_t tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x)
         {
             const TileRows t = tile_rows(g, tile);
-            int q = (gq + G - (int) base) % G;
-            int kd = t.kd_lo, i = t.i_lo + q;
-            for (; q < t.count && ok; q += G, i += G)
-            {
-                while (i >= t.i_hi)
+            for (int kd = t.kd_lo; kd < t.kd_hi && ok; ++kd)
+                for (int ch = 0; ch < chunks_pp && ok; ++ch)
                 {
-                    i -= t.nrows_i;
-                    ++kd;
-                }
-                const int a_slot = gq + G * lap_a, raw_slot = gq + G * lap_r;
-                // bulk-copy mode: the whole row, indexed by m; otherwise this
-                // warp's private 40-cell window, indexed by lane
-                float* raw = reinterpret_cast<float*>(raw_ring + (size_t) raw_slot * g.raw_slot_bytes)
-                             + (g.use_tma ? 0 : quad * g.c * TC_RAW_PRIV);
-#ifdef DCB_TC_PROFILE
-                pc0 = clock64();
-#endif
+            const int lo = max(t.i_lo, ch * Rc), hi = min(t.i_hi, (ch + 1) * Rc);
+            if (lo >= hi)
+                continue; // nothing but padding: the copy warp skips it too
+            // rows are dealt to the groups in the tile's issue order; this
+            // group's first row of the chunk:
+            const uint32_t first_q = (uint32_t) ((kd - t.kd_lo) * t.nrows_i + (lo - t.i_lo));
+            int i = lo + (gq + G - (int) ((base + first_q) % (uint32_t) G)) % G;
+            bool have = false;
+            for (; i < hi && ok; i += G)
+            {
+                const int a_slot = gq + G * lap_a;
+                // bulk-copy mode: row i of the chunk, indexed by m; otherwise
+                // this warp's private 40-cell window, indexed by lane
+                float* raw = g.use_tma ? reinterpret_cast<float*>(raw_ring + (size_t) cslot * g.raw_slot_bytes)
+                                             + (i - ch * Rc) * TC_RAW_W
+                                       : reinterpret_cast<float*>(raw_ring + (size_t) gq * g.raw_slot_bytes)
+                                             + quad * g.c * TC_RAW_PRIV;
                 if (g.use_tma)
                 {
-                    ok = mbar_wait(&raw_full[raw_slot], raw_phase, abort_flag);
+                    if (!have)
+                        ok = mbar_wait(&raw_full[cslot], cphase, abort_flag);
+                    have = true;
                 }
                 else
                 {
@@ -493,7 +503,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                 if (C4F3)
                 {
                     uint32_t v[3][8];
-                    convert_c4f3(raw_s, g.use_tma ? TC_RAW_W : TC_RAW_PRIV, v);
+                    convert_c4f3(raw_s, (uint32_t) pitch, v);
                     if (!a_first)
                         ok = mbar_wait(&a_empty[a_slot], a_phase, abort_flag);
                     if (!ok)
@@ -508,28 +518,15 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                     // convert into registers first, so the split overlaps the
                     // MMAs that still read this slot's previous row
                     uint32_t v[4][8];
-#ifdef DCB_TC_PROFILE
-                    pc1 = clock64();
-#endif
 #pragma unroll
                     for (int ch = 0; ch < 4; ++ch)
                         if (ch * 8 < g.kr)
                             convert_chunk(ktab_s + 32u * ch, raw_s, v[ch]);
-#ifdef DCB_TC_PROFILE
-                    pc2 = clock64();
-#endif
                     if (!a_first)
                         ok = mbar_wait(&a_empty[a_slot], a_phase, abort_flag);
                     if (!ok)
                         break;
                     tc_fence_after();
-#ifdef DCB_TC_PROFILE
-                    pc3 = clock64();
-                    p_raw += pc1 - pc0;
-                    p_conv += pc2 - pc1;
-                    p_slot += pc3 - pc2;
-                    ++p_rows;
-#endif
 #pragma unroll
                     for (int ch = 0; ch < 4; ++ch)
                         if (ch * 8 < g.kr)
@@ -550,54 +547,57 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                     }
                 }
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-#ifdef DCB_TC_PROFILE
-                p_st += clock64() - pc3;
-#endif
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0)
-                {
                     mbar_arrive(&a_full[a_slot]);
-                    if (g.use_tma)
-                        mbar_arrive(&raw_empty[raw_slot]);
-                }
                 if (++lap_a == laps_a)
                 {
                     lap_a = 0;
                     a_phase ^= 1;
                     a_first = false;
                 }
-                if (++lap_r == laps_r)
+            }
+            if (g.use_tma)
+            {
+                // every converter warp releases every chunk, with or without
+                // rows of its own in it
+                __syncwarp();
+                if (lane == 0)
+                    mbar_arrive(&raw_empty[cslot]);
+                if (++cslot == (uint32_t) g.raw_slots)
                 {
-                    lap_r = 0;
-                    raw_phase ^= 1;
+                    cslot = 0;
+                    cphase ^= 1;
                 }
             }
+                }
             base = (base + (uint32_t) t.count) % (uint32_t) G;
         }
-#ifdef DCB_TC_PROFILE
-        if (blockIdx.x == 0 && warp == 0 && lane == 0)
-            printf("converter: total %lld rows %d raw_wait %lld convert %lld slot_wait %lld store %lld\n",
-                   clock64() - p_all, p_rows, p_raw, p_conv, p_slot, p_st);
-#endif
     }
     else if (warp == TC_TMA_WARP)
     {
         // ------------------------------------------------------------------
-        // bulk tensor copies of raw input rows, raw_slots rows ahead.  The
-        // whole warp walks the schedule, lane 0 issues.
+        // bulk tensor copies of raw input rows, one chunk (chunk_rows rows of
+        // every channel) per instruction, raw_slots chunks ahead.  Issuing a
+        // copy costs this thread a few hundred clocks whatever its size, so
+        // row-sized copies cannot feed the converters.  The whole warp walks
+        // the schedule, lane 0 issues.
         // ------------------------------------------------------------------
         if (g.use_tma)
         {
-            const uint32_t bytes = (uint32_t) g.c * TC_RAW_W * 4u;
+            const uint32_t bytes = (uint32_t) (g.c * g.chunk_rows) * TC_RAW_W * 4u;
+            const int Rc = g.chunk_rows;
             uint32_t slot = 0, empty_phase = 1;
             bool first_lap = true;
             for (uint32_t tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x)
             {
                 const TileRows t = tile_rows(g, tile);
                 for (int kd = t.kd_lo; kd < t.kd_hi && ok; ++kd)
-                    for (int i = t.i_lo; i < t.i_hi; ++i)
+                    for (int ch = 0; ch < g.chunks_pp; ++ch)
                     {
+                        if (max(t.i_lo, ch * Rc) >= min(t.i_hi, (ch + 1) * Rc))
+                            continue; // the converters skip the same chunks
                         if (!first_lap)
                             ok = mbar_wait(&raw_empty[slot], empty_phase, abort_flag);
                         if (!ok)
@@ -607,9 +607,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                             mbar_expect_tx(&raw_full[slot], bytes);
                             // x starts 4 cells left of the tile: a multiple of
                             // 4 floats, as the 16-byte rule for the innermost
-                            // coordinate demands
+                            // coordinate demands; rows above or below the
+                            // image arrive as zeros and are never converted
                             tma_load_5d(raw_ring + (size_t) slot * g.raw_slot_bytes, &xmap, t.ow0 - 4,
-                                        t.oh0 - g.pad[1] + i, t.od - g.pad[0] + kd, 0, t.n, &raw_full[slot]);
+                                        t.oh0 - g.pad[1] + ch * Rc, t.od - g.pad[0] + kd, 0, t.n, &raw_full[slot]);
                         }
                         __syncwarp();
                         if (++slot == (uint32_t) g.raw_slots)
@@ -622,70 +623,70 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
             }
         }
     }
-    else if (warp == TC_MMA_WARP)
+    else if (warp >= TC_MMA_WARP && warp < TC_MMA_WARP + TC_GROUPS_MAX)
     {
         // ------------------------------------------------------------------
-        // MMA issue.  The whole warp walks the schedule; the instructions of
-        // staged row i are issued by lane i, which worked out that row's
-        // instruction descriptor, accumulator offset and filter-image offset
-        // once at kernel start (they depend on i only).  The issuing thread's
-        // own instruction stream is what bounds the row rate, so the per-row
-        // path is kept to a handful of instructions.  Issue order between
-        // lanes is program order, fenced with tcgen05.fence around the warp
-        // barrier.
+        // MMA issue.  Issuing one tcgen05.mma costs the issuing thread about
+        // 150 clocks whatever its shape, three times what the tensor pipe
+        // needs for it here, and several warps can issue concurrently: so
+        // every converter group has an issuer of its own (issuer mq takes the
+        // rows that group mq converts), and a private A slot ring between the
+        // two.  Rows of different issuers reach the pipe in no fixed order;
+        // they only ever add into the accumulators, so the sum is the same up
+        // to fp32 rounding order.
+        // Within an issuer the whole warp walks the schedule and the
+        // instructions of staged row i are issued by lane i, which worked out
+        // that row's instruction descriptor, accumulator offset and filter
+        // image offset once (they depend on i only).
         // ------------------------------------------------------------------
-        const int fh = g.f[1];
-        const int my_i = lane; // the staged row this lane issues
-        const int j_lo = max(0, fh - 1 - my_i);
-        const int j_hi = min(fh, g.th + fh - 1 - my_i);
-        // fp32 accumulate, tf32 x tf32, A K-major (tensor memory), B K-major, M = 128
-        const uint32_t my_idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((TC_M >> 4) << 24)
-                                  | ((uint32_t) ((max(1, j_hi - j_lo) * NB) >> 3) << 17);
-        const uint32_t my_d_off = (uint32_t) ((my_i - fh + 1 + j_lo) * NB);
-        const uint32_t b_lbo = (uint32_t) (g.ntot / 8) * 128u;
-        const uint32_t b_kstep_units = ((uint32_t) g.ntot * 32u) >> 4;
-        const uint64_t my_b_desc = make_desc(smem_u32(b_smem), b_lbo, 128u, 0u) + (uint64_t) ((uint32_t) j_lo * NB);
-        const uint32_t kd_units = (uint32_t) g.ksteps * b_kstep_units;
-        const uint32_t a_ring = tmem_base + a_col0;
-        const int ksteps = g.ksteps;
-        uint32_t slot = 0, full_phase = 0, tcount = 0;
-#ifdef DCB_TC_PROFILE
-        long long m_acc = 0, m_full = 0, m_issue = 0, m_all = clock64(), mc0, mc1;
-#endif
-        for (uint32_t tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++tcount)
+        const int G = g.groups, mq = warp - TC_MMA_WARP;
+        if (mq < G)
         {
-            const TileRows t = tile_rows(g, tile);
-            const uint32_t buf = tcount & 1;
-#ifdef DCB_TC_PROFILE
-            mc0 = clock64();
-#endif
-            ok = mbar_wait_t<0>(&acc_empty[buf], (tcount >> 1) & 1, abort_flag);
-#ifdef DCB_TC_PROFILE
-            m_acc += clock64() - mc0;
-#endif
-            if (!ok)
-                break;
-            const uint32_t my_d = tmem_base + buf * (uint32_t) g.acc_cols + my_d_off;
-            for (int kd = t.kd_lo; kd < t.kd_hi && ok; ++kd)
+            const int fh = g.f[1];
+            const int my_i = lane; // the staged row this lane issues
+            const int j_lo = max(0, fh - 1 - my_i);
+            const int j_hi = min(fh, g.th + fh - 1 - my_i);
+            // fp32 accumulate, tf32 x tf32, A K-major (tensor memory), B K-major, M = 128
+            const uint32_t my_idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((TC_M >> 4) << 24)
+                                      | ((uint32_t) ((max(1, j_hi - j_lo) * NB) >> 3) << 17);
+            const uint32_t my_d_off = (uint32_t) ((my_i - fh + 1 + j_lo) * NB);
+            const uint32_t b_lbo = (uint32_t) (g.ntot / 8) * 128u;
+            const uint32_t b_kstep_units = ((uint32_t) g.ntot * 32u) >> 4;
+            const uint64_t my_b_desc =
+                make_desc(smem_u32(b_smem), b_lbo, 128u, 0u) + (uint64_t) ((uint32_t) j_lo * NB);
+            const uint32_t kd_units = (uint32_t) g.ksteps * b_kstep_units;
+            const uint32_t a_ring = tmem_base + a_col0;
+            const int ksteps = g.ksteps;
+            const int laps_a = g.a_slots / G;
+            int lap_a = 0;
+            uint32_t full_phase = 0, tcount = 0, base = 0;
+            for (uint32_t tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++tcount)
             {
-                const uint64_t my_b = my_b_desc + (uint64_t) ((uint32_t) kd * kd_units);
-                for (int i = t.i_lo; i < t.i_hi; ++i)
+                const TileRows t = tile_rows(g, tile);
+                const uint32_t buf = tcount & 1;
+                ok = mbar_wait_t<0>(&acc_empty[buf], (tcount >> 1) & 1, abort_flag);
+                if (!ok)
+                    break;
+                const uint32_t my_d = tmem_base + buf * (uint32_t) g.acc_cols + my_d_off;
+                int q = (mq + G - (int) base) % G; // this issuer's first row of the tile
+                int kd = t.kd_lo, i = t.i_lo + q;
+                bool any = false;
+                for (; q < t.count && ok; q += G, i += G)
                 {
-#ifdef DCB_TC_PROFILE
-                    mc0 = clock64();
-#endif
+                    while (i >= t.i_hi)
+                    {
+                        i -= t.nrows_i;
+                        ++kd;
+                    }
+                    const uint32_t slot = (uint32_t) (mq + G * lap_a);
                     ok = mbar_wait_t<0>(&a_full[slot], full_phase, abort_flag);
-#ifdef DCB_TC_PROFILE
-                    mc1 = clock64();
-                    m_full += mc1 - mc0;
-#endif
                     if (!ok)
                         break;
                     tc_fence_after();
                     if (lane == i)
                     {
                         uint32_t a_addr = a_ring + slot * (uint32_t) g.kr;
-                        uint64_t bd = my_b;
+                        uint64_t bd = my_b_desc + (uint64_t) ((uint32_t) kd * kd_units);
                         for (int ks = 0; ks < ksteps; ++ks)
                         {
                             mma_tf32_ts(my_d, a_addr, bd, my_idesc);
@@ -693,41 +694,44 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                             bd += b_kstep_units;
                         }
                         mma_commit(&a_empty[slot]);
-                        // The tile's last row also publishes the accumulators:
-                        // the tensor pipe retires MMAs in issue order, so the
-                        // completion of this lane's instructions implies that
-                        // of every earlier row's.
-                        if (kd == t.kd_hi - 1 && i == t.i_hi - 1)
+                        // This issuer's last row of the tile also reports to
+                        // the epilogue; the accumulators are complete once
+                        // every issuer has (the tensor pipe retires MMAs in
+                        // issue order, so a commit covers this warp's earlier
+                        // rows too).
+                        if (q + G >= t.count)
                             mma_commit(&acc_full[buf]);
                         tc_fence_before();
                     }
                     __syncwarp();
-                    if (++slot == (uint32_t) g.a_slots)
+                    any = true;
+                    if (++lap_a == laps_a)
                     {
-                        slot = 0;
+                        lap_a = 0;
                         full_phase ^= 1;
                     }
-#ifdef DCB_TC_PROFILE
-                    m_issue += clock64() - mc1;
-#endif
                 }
+                // an issuer without a row in this tile still has to report
+                if (!any && ok && lane == 0)
+                    mbar_arrive(&acc_full[buf]);
+                base = (base + (uint32_t) t.count) % (uint32_t) G;
             }
         }
-#ifdef DCB_TC_PROFILE
-        if (blockIdx.x == 0 && lane == 0)
-            printf("mma warp: total %lld acc_wait %lld full_wait %lld issue %lld tiles %u\n", clock64() - m_all, m_acc,
-                   m_full, m_issue, tcount);
-#endif
     }
     else if (warp > TC_TMA_WARP)
     {
         // ------------------------------------------------------------------
-        // epilogue: TMEM -> registers -> global, then re-zero the buffer
+        // epilogue: TMEM -> registers -> global, then re-zero what was read.
+        // Two warps per TMEM quadrant share a tile's rows (even / odd): a
+        // tensor-memory load takes long while MMAs are in flight, and eight
+        // warps keep enough of them outstanding.
         // ------------------------------------------------------------------
         const int quad = warp & 3; // TMEM lanes this warp may touch
+        const int half = (warp - TC_TMA_WARP - 1) >> 2, nhalf = TC_EPI_WARPS / 4;
         const uint32_t lane_addr = tmem_base + ((uint32_t) (quad * 32) << 16);
-        for (int col = 0; col < 2 * g.acc_cols; col += 16)
-            tmem_st16_zero(lane_addr + col);
+        if (half == 0)
+            for (int col = 0; col < 2 * g.acc_cols; col += 16)
+                tmem_st16_zero(lane_addr + col);
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         tc_fence_before();
         __syncwarp();
@@ -747,7 +751,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                 break;
             tc_fence_after();
             const uint32_t acc_addr = lane_addr + buf * (uint32_t) g.acc_cols;
-            for (int r = 0; r < g.th; ++r)
+            for (int r = half; r < g.th; r += nhalf)
             {
                 const int oh = t.oh0 + r;
                 if (oh >= g.out[1])
@@ -776,8 +780,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                     }
                 }
             }
-            for (int col = 0; col < g.acc_cols; col += 16)
-                tmem_st16_zero(acc_addr + col);
+            // every warp re-zeroes the rows that are its to read (also those
+            // below the image, which the MMAs wrote all the same)
+            for (int r = half; r < g.th; r += nhalf)
+                for (int col = 0; col < NB; col += 16)
+                    tmem_st16_zero(acc_addr + (uint32_t) (r * NB + col));
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             tc_fence_before();
             __syncwarp();
