@@ -25,6 +25,7 @@
 // releases its tensor memory and returns.
 #include "conv_tc.cuh"
 #include "conv_tc_kernel.cuh"
+#include "conv_tc_sweep.cuh"
 
 namespace dcb
 {
@@ -142,6 +143,120 @@ bool tc_geom(const ConvGeom& cg, int math_mode, TcGeom* out)
     return true;
 }
 
+size_t sw_smem_need(const SwGeom& g)
+{
+    return (size_t) (g.b_bytes + 127) / 128 * 128 + (size_t) g.raw_slots * g.raw_slot_bytes
+           + (size_t) ((g.kr + 1) & ~1) * 4 + (size_t) (2 * g.a_slots + 64 + 2 * g.raw_slots) * 8 + 64 + 1024;
+}
+
+// Geometry of the sweep kernel (filters with depth).  Needs bulk-copy
+// compatible strides; the base address is checked per call.
+bool sw_geom(const ConvGeom& cg, int math_mode, SwGeom* out)
+{
+    SwGeom g;
+    std::memset(&g, 0, sizeof(g));
+    for (int i = 0; i < 3; ++i)
+    {
+        if (cg.stride[i] != 1 || cg.dil[i] != 1)
+            return false;
+        g.in[i] = cg.in[i];
+        g.out[i] = cg.out[i];
+        g.f[i] = cg.f[i];
+        g.pad[i] = cg.pad[i];
+        g.xs[i] = cg.xs[i];
+        g.ys[i] = cg.ys[i];
+        if (g.pad[i] > g.f[i] - 1)
+            return false;
+    }
+    g.n = cg.n;
+    g.c = cg.c;
+    g.k = cg.k;
+    g.xs_n = cg.xs_n;
+    g.xs_c = cg.xs_c;
+    g.ys_n = cg.ys_n;
+    g.ys_c = cg.ys_c;
+    if (g.f[0] < 2 || g.f[0] > 4 || g.k > SW_NBK || g.c > 16)
+        return false;
+    if ((long long) cg.n * cg.out[0] * cg.out[1] * cg.out[2] == 0)
+        return false;
+    if (g.pad[2] > 4 || g.f[2] - 1 - g.pad[2] > 4)
+        return false;
+    if (!(cg.xs[1] % 4 == 0 && cg.xs[0] % 4 == 0 && cg.xs_c % 4 == 0 && cg.xs_n % 4 == 0))
+        return false;
+    g.split = math_mode == DCB_MATH_TF32 ? 0 : 1;
+    g.ntot = g.f[1] * g.f[0] * SW_NBK;
+    if (g.ntot > 256 || (g.f[0] * SW_NBK) % 16)
+        return false;
+    g.crows = g.c * g.f[2];
+    g.kr = (g.crows * (g.split ? 3 : 1) + 7) / 8 * 8;
+    g.ksteps = g.kr / 8;
+    g.b_rot_bytes = g.kr * g.ntot * 4;
+    g.b_bytes = g.f[0] * g.b_rot_bytes;
+    // an issuer must own one of any fh consecutive rows (see the hand-off
+    // notes in the kernel header)
+    g.groups = g.f[1] < TC_GROUPS_MAX ? g.f[1] : TC_GROUPS_MAX;
+    while (g.groups > 1 && g.groups * g.kr > 160)
+        --g.groups;
+    g.a_slots = g.groups;
+    if (g.a_slots * g.kr > 256)
+        return false;
+    int th = ((int) TC_TMEM_COLS - g.a_slots * g.kr) / (g.f[0] * SW_NBK);
+    if (th + g.f[1] - 1 > 32)
+        th = 32 - g.f[1] + 1;
+    if (th > g.out[1])
+    {
+        th = g.out[1];
+    }
+    else
+    {
+        const int nt = (g.out[1] + th - 1) / th; // even out the rows over the columns
+        th = (g.out[1] + nt - 1) / nt;
+    }
+    if (th < 2)
+        return false;
+    g.th = th;
+    g.rows = th + g.f[1] - 1;
+    // chunks of about 17 KiB, evenly sized
+    const int row_bytes = g.c * TC_RAW_W * 4;
+    int rc_max = (17 * 1024 + 512) / row_bytes;
+    rc_max = rc_max < 1 ? 1 : rc_max;
+    g.chunks_pp = (g.rows + rc_max - 1) / rc_max;
+    g.chunk_rows = (g.rows + g.chunks_pp - 1) / g.chunks_pp;
+    g.raw_slot_bytes = (g.chunk_rows * row_bytes + 127) / 128 * 128;
+    int slots = (72 * 1024) / g.raw_slot_bytes;
+    slots = slots > 6 ? 6 : slots;
+    if (slots < 2)
+        return false;
+    g.raw_slots = slots;
+    if (sw_smem_need(g) > 200 * 1024)
+        return false;
+    g.tiles_w = (g.out[2] + TC_M - 1) / TC_M;
+    g.tiles_h = (g.out[1] + g.th - 1) / g.th;
+    // segments along D: whole waves of CTAs, few spill steps
+    const long long cols = (long long) g.n * g.tiles_w * g.tiles_h;
+    const int sms = num_sms();
+    long long best_cost = -1;
+    int best = 1;
+    for (int ns = 1; ns <= g.out[0] && ns <= 64; ++ns)
+    {
+        const long long units = cols * ns;
+        const long long waves = (units + sms - 1) / sms;
+        const long long steps = (g.out[0] + ns - 1) / ns + 2 * (g.f[0] - 1);
+        const long long cost = waves * steps;
+        if (best_cost < 0 || cost < best_cost)
+        {
+            best_cost = cost;
+            best = ns;
+        }
+    }
+    g.nseg = best;
+    g.units = cols * g.nseg;
+    if (g.units >= (1ll << 31))
+        return false;
+    *out = g;
+    return true;
+}
+
 size_t tc_smem_bytes(const TcGeom& g)
 {
     // At least 120 KiB so that a second CTA can never share the SM: the
@@ -157,6 +272,10 @@ struct TcPlan
     bool has[2] = {false, false};
     TcGeom g[2];
     float* bimg[2] = {nullptr, nullptr};
+    // the sweep kernel, preferred where it applies (filters with depth)
+    bool has_sw[2] = {false, false};
+    SwGeom sw[2];
+    float* sw_bimg[2] = {nullptr, nullptr};
     int* status = nullptr;
 };
 
@@ -166,6 +285,10 @@ int32_t tc_plan_create(const ConvGeom& fwd, const ConvGeom& bwd, bool bwd_is_fwd
     auto* p = new TcPlan();
     p->has[0] = tc_geom(fwd, math_mode, &p->g[0]);
     p->has[1] = bwd_is_fwd && tc_geom(bwd, math_mode, &p->g[1]);
+    // the sweep kernel falls back to the row kernel when a call's base address
+    // is not 16-byte aligned, so it is only planned on top of it
+    p->has_sw[0] = p->has[0] && sw_geom(fwd, math_mode, &p->sw[0]);
+    p->has_sw[1] = p->has[1] && sw_geom(bwd, math_mode, &p->sw[1]);
     if (!p->has[0] && !p->has[1])
     {
         delete p;
@@ -174,8 +297,12 @@ int32_t tc_plan_create(const ConvGeom& fwd, const ConvGeom& bwd, bool bwd_is_fwd
     bool ok = cudaMalloc(&p->status, sizeof(int)) == cudaSuccess
               && cudaMemset(p->status, 0, sizeof(int)) == cudaSuccess;
     for (int s = 0; s < 2 && ok; ++s)
+    {
         if (p->has[s])
             ok = cudaMalloc(&p->bimg[s], p->g[s].b_bytes) == cudaSuccess;
+        if (ok && p->has_sw[s])
+            ok = cudaMalloc(&p->sw_bimg[s], p->sw[s].b_bytes) == cudaSuccess;
+    }
     if (!ok)
     {
         (void) cudaGetLastError();
@@ -193,6 +320,8 @@ void tc_plan_destroy(TcPlan* p)
         return;
     cudaFree(p->bimg[0]);
     cudaFree(p->bimg[1]);
+    cudaFree(p->sw_bimg[0]);
+    cudaFree(p->sw_bimg[1]);
     cudaFree(p->status);
     delete p;
 }
@@ -298,11 +427,66 @@ static int32_t tc_launch(const TcGeom& g_in, float alpha, const float* x, const 
     return DCB_OK;
 }
 
+// Descriptor of the input window for the sweep kernel: box = chunk_rows raw rows
+// of every channel.
+static bool sw_make_x_map(const SwGeom& g, const float* x, CUtensorMap* map)
+{
+    TcGeom t;
+    std::memset(&t, 0, sizeof(t));
+    for (int i = 0; i < 3; ++i)
+    {
+        t.in[i] = g.in[i];
+        t.xs[i] = g.xs[i];
+    }
+    t.n = g.n;
+    t.c = g.c;
+    t.xs_n = g.xs_n;
+    t.xs_c = g.xs_c;
+    t.chunk_rows = g.chunk_rows;
+    return make_x_map(t, x, map);
+}
+
+static int32_t sw_launch(const SwGeom& g, float alpha, const float* w, const float* x, float* bimg, float beta,
+                         float* y, int* status, const CUtensorMap& map, cudaStream_t stream)
+{
+    const long long total = (long long) g.b_bytes / 4;
+    sw_pack_filter_kernel<<<(unsigned) ((total + 255) / 256), 256, 0, stream>>>(w, bimg, g);
+    DCB_LAUNCH_CHECK();
+    size_t smem = sw_smem_need(g);
+    smem = smem < 120 * 1024 ? 120 * 1024 : smem; // one CTA per SM: it owns all of tensor memory
+    long long grid = (long long) num_sms();
+    if (grid > g.units)
+        grid = g.units;
+    const bool c4f3 = g.c == 4 && g.f[2] == 3 && g.pad[2] == 1 && g.split;
+    if (c4f3)
+    {
+        DCB_CUDA_TRY(cudaFuncSetAttribute(sw_conv_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          (int) (224 * 1024)));
+        sw_conv_kernel<true><<<(unsigned) grid, TC_THREADS, smem, stream>>>(g, alpha, beta, bimg, y, status, map);
+    }
+    else
+    {
+        DCB_CUDA_TRY(cudaFuncSetAttribute(sw_conv_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          (int) (224 * 1024)));
+        sw_conv_kernel<false><<<(unsigned) grid, TC_THREADS, smem, stream>>>(g, alpha, beta, bimg, y, status, map);
+    }
+    DCB_LAUNCH_CHECK();
+    (void) x;
+    return DCB_OK;
+}
+
 int32_t tc_conv_fwd(TcPlan* p, int slot, float alpha, const float* x, const float* w, float beta, float* y,
                     cudaStream_t stream)
 {
     if (!p || slot < 0 || slot > 1 || !p->has[slot])
         return DCB_UNSUPPORTED;
+    if (p->has_sw[slot])
+    {
+        CUtensorMap map;
+        std::memset(&map, 0, sizeof(map));
+        if (sw_make_x_map(p->sw[slot], x, &map))
+            return sw_launch(p->sw[slot], alpha, w, x, p->sw_bimg[slot], beta, y, p->status, map, stream);
+    }
     const TcGeom& g = p->g[slot];
     const long long total = (long long) g.b_bytes / 4;
     tc_pack_filter_kernel<<<(unsigned) ((total + 255) / 256), 256, 0, stream>>>(w, p->bimg[slot], g);

@@ -77,6 +77,7 @@ template <int SLEEP_NS>
 __device__ __forceinline__ bool mbar_wait_t(uint64_t* bar, uint32_t parity, volatile int* abort_flag)
 {
     const uint32_t addr = smem_u32(bar);
+    long long t0 = 0;
     for (uint32_t it = 0; it < (1u << 24); ++it)
     {
         uint32_t done;
@@ -95,6 +96,15 @@ __device__ __forceinline__ bool mbar_wait_t(uint64_t* bar, uint32_t parity, vola
             __nanosleep(SLEEP_NS);
         if ((it & 15) == 15 && *abort_flag)
             return false;
+        if ((it & 255) == 255)
+        {
+            // a quarter of a second at most, whatever a poll costs
+            const long long now = clock64();
+            if (t0 == 0)
+                t0 = now;
+            else if (now - t0 > 500000000ll)
+                break;
+        }
     }
     *abort_flag = 1;
     return false;

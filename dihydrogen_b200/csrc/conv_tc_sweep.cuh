@@ -1,0 +1,550 @@
+// tcgen05 / TMEM convolution for filters with depth (fd > 1): the "sweep"
+// kernel.  Same GEMM view as conv_tc_kernel.cuh (M = 128 outputs along W, the
+// reduction runs over (c, kw) of one staged input row), but a staged row is
+// converted ONCE and serves every (kd, kh) tap:
+//
+//   * A CTA owns a column of the volume (th output rows x 128 outputs wide)
+//     and sweeps a segment of output planes od0..od1-1 along D, one input
+//     plane ("step") after the other.
+//   * The accumulators of fd consecutive output planes are live at once.
+//     Block (row j, plane slot s = od mod fd) sits at TMEM column
+//     (j * fd + s) * 16, so the fh * fd blocks that input row i feeds (rows
+//     i-fh+1..i, all slots) are one contiguous column range and ONE
+//     instruction of N = fh * fd * 16 updates all of them.  Which kd lands in
+//     which slot depends on d mod fd: the filter image exists in fd rotations.
+//   * 3xTF32 is folded into the reduction: A k-rows [hi ; lo ; hi] against
+//     B k-rows [w_hi ; w_hi ; w_lo], so one accumulator block per output row.
+//   * After step d the plane od = d + pad - (fd-1) has all its terms: the
+//     epilogue warps store it (if it belongs to the segment), re-zero its
+//     blocks and hand them back, row by row, while the issuers carry on with
+//     the next input plane; a row's blocks are only needed again th rows
+//     later.  Planes outside the segment collect terms too (the instruction
+//     cannot skip a slot); they are just zeroed when their turn comes, which
+//     is always before the slot's next owner receives its first term.  The
+//     steps before the first and after the last input plane that exist only
+//     to retire planes are "virtual": nothing is copied, converted or
+//     multiplied in them.
+//
+// Hand-offs (all mbarriers, all waits bounded):
+//   raw_full / raw_empty   copy warp <-> converters, per chunk of raw rows
+//   a_full / a_empty       converter group g <-> issuer g, per A slot
+//   row_done[i]            issuer -> epilogue: the MMAs of input row i of this
+//                          step have completed (tcgen05.commit)
+//   row_free[j]            epilogue -> issuers: the blocks of output row j
+//                          have been retired and are zero again
+// row_done / row_free complete once per step.  A parity wait cannot tell a
+// barrier that is two completions away, so: the epilogue warps wait on the
+// same row_done barriers every step; an issuer's rows change from step to
+// step, but its last row of every step is one of the last fh rows (there are
+// at most fh issuers), whose wait covers the last output row of either
+// epilogue half and with it (each half retires in ascending order) every
+// row_free of the previous step; and a barrier cannot run ahead of a waiter,
+// because its next completion needs a row that this waiter issues after the
+// wait.
+#pragma once
+
+#include "conv_tc_kernel.cuh"
+
+namespace dcb
+{
+namespace
+{
+
+constexpr int SW_NBK = 16; // accumulator columns per (output row, plane slot)
+
+struct SwGeom
+{
+    int n, c, k;
+    int in[3], out[3], f[3], pad[3];
+    long long xs_n, xs_c, xs[3];
+    long long ys_n, ys_c, ys[3];
+    int split;      // 1: 3xTF32, 0: single TF32 pass
+    int th;         // output rows per column
+    int rows;       // staged rows per step = th + fh - 1
+    int crows;      // c * fw
+    int kr, ksteps; // k-rows per staged row (multiple of 8), kr / 8
+    int ntot;       // fh * fd * SW_NBK
+    int b_rot_bytes, b_bytes; // one rotation of the filter image, all fd of them
+    int groups, a_slots;
+    int tiles_w, tiles_h, nseg;
+    long long units;
+    int raw_slots, raw_slot_bytes, chunk_rows, chunks_pp;
+};
+
+struct SwUnit
+{
+    int n, ow0, oh0, od0, od1;
+    int d_first, d_stop; // steps d_first .. d_stop-1
+    int d_real_hi;       // input planes above this one only feed foreign output planes
+};
+
+__device__ __forceinline__ SwUnit sw_unit(const SwGeom& g, uint32_t u)
+{
+    SwUnit t;
+    const uint32_t tw = u % (uint32_t) g.tiles_w;
+    uint32_t r = u / (uint32_t) g.tiles_w;
+    const uint32_t thi = r % (uint32_t) g.tiles_h;
+    r /= (uint32_t) g.tiles_h;
+    const uint32_t seg = r % (uint32_t) g.nseg;
+    t.n = (int) (r / (uint32_t) g.nseg);
+    t.ow0 = (int) tw * TC_M;
+    t.oh0 = (int) thi * g.th;
+    t.od0 = (int) (((long long) seg * g.out[0]) / g.nseg);
+    t.od1 = (int) (((long long) (seg + 1) * g.out[0]) / g.nseg);
+    t.d_first = t.od0 - g.pad[0];
+    t.d_real_hi = t.od1 - 1 + g.f[0] - 1 - g.pad[0];
+    t.d_stop = t.d_real_hi + g.f[0]; // fd - 1 more steps retire the planes the last rows spilled into
+    return t;
+}
+
+__device__ __forceinline__ bool sw_real(const SwGeom& g, const SwUnit& t, int d)
+{
+    return d >= 0 && d < g.in[0] && d <= t.d_real_hi;
+}
+
+__device__ __forceinline__ int sw_mod(int a, int m)
+{
+    const int r = a % m;
+    return r < 0 ? r + m : r;
+}
+
+// Filter image: [rotation][k-step][2 k-chunks][ntot/8][8 n][4 k] floats.
+// Column (j, s, ko): output row offset j (kh = fh-1-j), plane slot s, filter ko.
+// In rotation r (= d mod fd) slot s belongs to the output plane d + pad - kd
+// with kd = (r + pad - s) mod fd.
+__global__ void sw_pack_filter_kernel(const float* __restrict__ w, float* __restrict__ b, SwGeom g)
+{
+    const int fd = g.f[0], fh = g.f[1], fw = g.f[2];
+    const int per_rot = g.kr * g.ntot;
+    const long long total = (long long) fd * per_rot;
+    for (long long i = (long long) blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long) gridDim.x * blockDim.x)
+    {
+        const int rot = (int) (i / per_rot);
+        const int e = (int) (i % per_rot);
+        const int ki = e % 4;
+        const int ni = (e / 4) % 8;
+        const int ngroup = (e / 32) % (g.ntot / 8);
+        const int kchunk = (e / (32 * (g.ntot / 8))) % 2;
+        const int kstep = e / (64 * (g.ntot / 8));
+        const int krow = kstep * 8 + kchunk * 4 + ki;
+        const int ncol = ngroup * 8 + ni;
+        const int j = ncol / (fd * SW_NBK);
+        const int s = (ncol / SW_NBK) % fd;
+        const int ko = ncol % SW_NBK;
+        const int kh = fh - 1 - j;
+        const int kd = sw_mod(rot + g.pad[0] - s, fd);
+        const int part = krow / g.crows; // 0: A_hi x w_hi, 1: A_lo x w_hi, 2: A_hi x w_lo
+        const int rem = krow % g.crows;
+        const int c = rem / fw, kw = rem % fw;
+        float val = 0.f;
+        if (ko < g.k && part < (g.split ? 3 : 1))
+        {
+            const float wv = w[((((size_t) ko * g.c + c) * fd + kd) * fh + kh) * fw + kw];
+            const float hi = __uint_as_float(tf32_rna(wv));
+            val = part < 2 ? hi : __uint_as_float(tf32_rna(wv - hi));
+        }
+        b[i] = val;
+    }
+}
+
+// 4 channels x 3 taps, pad 1, split: k-rows 0..11 hi, 12..23 lo, 24..35 hi, 36..39 zero.
+__device__ __forceinline__ void sw_convert_c4f3(uint32_t raw_lane, uint32_t pitch, uint32_t (&v)[5][8])
+{
+    uint32_t xv[12];
+#pragma unroll
+    for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int kw = 0; kw < 3; ++kw)
+            xv[c * 3 + kw] = lds_u32(raw_lane + 4u * ((uint32_t) c * pitch + 3u + (uint32_t) kw));
+#pragma unroll
+    for (int r = 0; r < 12; ++r)
+    {
+        const float xe = __uint_as_float(xv[r]);
+        const uint32_t hi = tf32_rna(xe);
+        const uint32_t lo = tf32_rna(xe - __uint_as_float(hi));
+        v[r / 8][r % 8] = hi;
+        v[(12 + r) / 8][(12 + r) % 8] = lo;
+        v[(24 + r) / 8][(24 + r) % 8] = hi;
+    }
+#pragma unroll
+    for (int r = 36; r < 40; ++r)
+        v[r / 8][r % 8] = 0u;
+}
+
+// ---------------------------------------------------------------------------
+// Warps: 0..11 converters (three groups of four), 12..14 MMA issuers (issuer q
+// serves group q), 15 bulk copies, 16..23 epilogue (two per TMEM quadrant,
+// even / odd output rows).  TMEM columns: [accumulators th * fd * 16][A ring].
+// ---------------------------------------------------------------------------
+template <bool C4F3>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+    sw_conv_kernel(SwGeom g, float alpha, float beta, const float* __restrict__ bimg, float* y, int* status,
+                   const __grid_constant__ CUtensorMap xmap)
+{
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    float* b_smem = reinterpret_cast<float*>(smem);
+    const int b_region = (g.b_bytes + 127) / 128 * 128;
+    uint8_t* raw_ring = smem + b_region;
+    uint32_t* ktab = reinterpret_cast<uint32_t*>(raw_ring + (size_t) g.raw_slots * g.raw_slot_bytes);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(ktab + ((g.kr + 1) & ~1));
+    uint64_t* a_full = bars;                        // [a_slots]
+    uint64_t* a_empty = a_full + g.a_slots;         // [a_slots]
+    uint64_t* row_done = a_empty + g.a_slots;       // [32]
+    uint64_t* row_free = row_done + 32;             // [32]
+    uint64_t* raw_full = row_free + 32;             // [raw_slots]
+    uint64_t* raw_empty = raw_full + g.raw_slots;   // [raw_slots]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(raw_empty + g.raw_slots);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int fd = g.f[0], fh = g.f[1], R = g.rows, G = g.groups;
+
+    if (tid == 0)
+    {
+        for (int s = 0; s < g.a_slots; ++s)
+        {
+            mbar_init(&a_full[s], 4);
+            mbar_init(&a_empty[s], 1);
+        }
+        for (int r = 0; r < 32; ++r)
+        {
+            mbar_init(&row_done[r], 1);
+            mbar_init(&row_free[r], 4);
+        }
+        for (int r = 0; r < g.raw_slots; ++r)
+        {
+            mbar_init(&raw_full[r], 1);
+            mbar_init(&raw_empty[r], 4 * g.groups);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == TC_MMA_WARP)
+    {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(TC_TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    // k-row table: offset of the tap inside a raw chunk row, and what the row
+    // carries: 0 hi part, 1 lo part, 2 zero
+    for (int r = tid; r < g.kr; r += TC_THREADS)
+    {
+        const int part = r / g.crows, rem = r % g.crows;
+        const int c = rem / g.f[2], kw = rem % g.f[2];
+        const uint32_t off = (uint32_t) (c * g.chunk_rows * TC_RAW_W + 4 + kw - g.pad[2]);
+        const uint32_t sel = part < (g.split ? 3 : 1) ? (part == 1 ? 1u : 0u) : 2u;
+        ktab[r] = sel == 2u ? ((2u << 16) | 4u) : (off | (sel << 16));
+    }
+    for (int i = tid; i < g.b_bytes / 16; i += TC_THREADS)
+        reinterpret_cast<float4*>(b_smem)[i] = reinterpret_cast<const float4*>(bimg)[i];
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t a_col0 = (uint32_t) (g.th * fd * SW_NBK); // first column of the A ring
+    const uint32_t nunits = (uint32_t) g.units;
+    bool ok = true;
+
+    if (warp < 4 * G)
+    {
+        // ------------------------------------------------------------------
+        // converters
+        // ------------------------------------------------------------------
+        const int gq = warp >> 2, quad = warp & 3;
+        const int mcol = quad * 32 + lane;
+        const uint32_t lane_addr = tmem_base + ((uint32_t) (quad * 32) << 16);
+        const int laps_a = g.a_slots / G;
+        const uint32_t ktab_s = smem_u32(ktab);
+        const int Rc = g.chunk_rows;
+        const uint32_t pitch = (uint32_t) (g.chunk_rows * TC_RAW_W);
+        int lap_a = 0;
+        uint32_t cslot = 0, cphase = 0, a_phase = 1, base = 0;
+        bool a_first = true;
+        for (uint32_t u = blockIdx.x; u < nunits && ok; u += gridDim.x)
+        {
+            const SwUnit t = sw_unit(g, u);
+            for (int d = t.d_first; d < t.d_stop && ok; ++d)
+            {
+                if (!sw_real(g, t, d))
+                    continue;
+                for (int ch = 0; ch < g.chunks_pp && ok; ++ch)
+                {
+                    const int lo = ch * Rc, hi = min(R, (ch + 1) * Rc);
+                    int i = lo + (gq + G - (int) ((base + (uint32_t) lo) % (uint32_t) G)) % G;
+                    bool have = false;
+                    for (; i < hi && ok; i += G)
+                    {
+                        const int a_slot = gq + G * lap_a;
+                        if (!have)
+                            ok = mbar_wait(&raw_full[cslot], cphase, abort_flag);
+                        have = true;
+                        if (!ok)
+                            break;
+                        const float* raw = reinterpret_cast<const float*>(raw_ring + (size_t) cslot * g.raw_slot_bytes)
+                                           + (i - lo) * TC_RAW_W;
+                        const uint32_t a_addr = lane_addr + a_col0 + (uint32_t) (a_slot * g.kr);
+                        const uint32_t raw_s = smem_u32(raw) + 4u * (uint32_t) mcol;
+                        if (C4F3)
+                        {
+                            uint32_t v[5][8];
+                            sw_convert_c4f3(raw_s, pitch, v);
+                            if (!a_first)
+                                ok = mbar_wait(&a_empty[a_slot], a_phase, abort_flag);
+                            if (!ok)
+                                break;
+                            tc_fence_after();
+#pragma unroll
+                            for (int ck = 0; ck < 5; ++ck)
+                                tmem_st8(a_addr + (uint32_t) (ck * 8), v[ck]);
+                        }
+                        else
+                        {
+                            if (!a_first)
+                                ok = mbar_wait(&a_empty[a_slot], a_phase, abort_flag);
+                            if (!ok)
+                                break;
+                            tc_fence_after();
+                            for (int r0 = 0; r0 < g.kr; r0 += 8)
+                            {
+                                uint32_t v[8];
+                                convert_chunk(ktab_s + 4u * r0, raw_s, v);
+                                tmem_st8(a_addr + (uint32_t) r0, v);
+                            }
+                        }
+                        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0)
+                            mbar_arrive(&a_full[a_slot]);
+                        if (++lap_a == laps_a)
+                        {
+                            lap_a = 0;
+                            a_phase ^= 1;
+                            a_first = false;
+                        }
+                    }
+                    // every converter warp releases every chunk
+                    __syncwarp();
+                    if (lane == 0)
+                        mbar_arrive(&raw_empty[cslot]);
+                    if (++cslot == (uint32_t) g.raw_slots)
+                    {
+                        cslot = 0;
+                        cphase ^= 1;
+                    }
+                }
+                base = (base + (uint32_t) R) % (uint32_t) G;
+            }
+        }
+    }
+    else if (warp == TC_TMA_WARP)
+    {
+        // ------------------------------------------------------------------
+        // bulk tensor copies: chunk_rows raw rows of every channel per copy.
+        // Rows above or below the image arrive as zeros.
+        // ------------------------------------------------------------------
+        const uint32_t bytes = (uint32_t) (g.c * g.chunk_rows) * TC_RAW_W * 4u;
+        uint32_t slot = 0, empty_phase = 1;
+        bool first_lap = true;
+        for (uint32_t u = blockIdx.x; u < nunits && ok; u += gridDim.x)
+        {
+            const SwUnit t = sw_unit(g, u);
+            for (int d = t.d_first; d < t.d_stop && ok; ++d)
+            {
+                if (!sw_real(g, t, d))
+                    continue;
+                for (int ch = 0; ch < g.chunks_pp; ++ch)
+                {
+                    if (!first_lap)
+                        ok = mbar_wait(&raw_empty[slot], empty_phase, abort_flag);
+                    if (!ok)
+                        break;
+                    if (lane == 0)
+                    {
+                        mbar_expect_tx(&raw_full[slot], bytes);
+                        // x starts 4 cells left of the column: a multiple of 4 floats
+                        tma_load_5d(raw_ring + (size_t) slot * g.raw_slot_bytes, &xmap, t.ow0 - 4,
+                                    t.oh0 - g.pad[1] + ch * g.chunk_rows, d, 0, t.n, &raw_full[slot]);
+                    }
+                    __syncwarp();
+                    if (++slot == (uint32_t) g.raw_slots)
+                    {
+                        slot = 0;
+                        empty_phase ^= 1;
+                        first_lap = false;
+                    }
+                }
+            }
+        }
+    }
+    else if (warp >= TC_MMA_WARP && warp < TC_MMA_WARP + TC_GROUPS_MAX)
+    {
+        // ------------------------------------------------------------------
+        // MMA issue: issuer mq takes the rows converter group mq produced.
+        // Lane i issues staged row i (its descriptors depend on i only).
+        // ------------------------------------------------------------------
+        const int mq = warp - TC_MMA_WARP;
+        if (mq < G)
+        {
+            const int my_i = lane;
+            const int j_lo = max(0, fh - 1 - my_i);
+            const int j_hi = min(fh, g.th + fh - 1 - my_i);
+            const int blk = fd * SW_NBK; // columns of one output row
+            const uint32_t my_idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((TC_M >> 4) << 24)
+                                      | ((uint32_t) ((max(1, j_hi - j_lo) * blk) >> 3) << 17);
+            const uint32_t my_d = tmem_base + (uint32_t) ((my_i - fh + 1 + j_lo) * blk);
+            const uint32_t b_lbo = (uint32_t) (g.ntot / 8) * 128u;
+            const uint32_t b_kstep_units = ((uint32_t) g.ntot * 32u) >> 4;
+            const uint64_t my_b_desc =
+                make_desc(smem_u32(b_smem), b_lbo, 128u, 0u) + (uint64_t) ((uint32_t) (j_lo * blk));
+            const uint32_t rot_units = (uint32_t) g.b_rot_bytes >> 4;
+            const uint32_t a_ring = tmem_base + a_col0;
+            const int ksteps = g.ksteps;
+            const int laps_a = g.a_slots / G;
+            int lap_a = 0;
+            uint32_t full_phase = 0, step = 0, base = 0;
+            for (uint32_t u = blockIdx.x; u < nunits && ok; u += gridDim.x)
+            {
+                const SwUnit t = sw_unit(g, u);
+                for (int d = t.d_first; d < t.d_stop && ok; ++d, ++step)
+                {
+                    const bool real = sw_real(g, t, d);
+                    const uint32_t par = step & 1;
+                    const uint64_t bd0 = my_b_desc + (uint64_t) ((uint32_t) sw_mod(d, fd) * rot_units);
+                    int i = real ? (mq + G - (int) (base % (uint32_t) G)) % G : mq;
+                    for (; i < R && ok; i += G)
+                    {
+                        // the blocks this row adds into must have been retired
+                        const int ja = min(i, g.th - 1);
+                        ok = mbar_wait_t<0>(&row_free[ja], par, abort_flag);
+                        if (ok && ja >= 1)
+                            ok = mbar_wait_t<0>(&row_free[ja - 1], par, abort_flag);
+                        if (!ok)
+                            break;
+                        if (real)
+                        {
+                            const uint32_t slot = (uint32_t) (mq + G * lap_a);
+                            ok = mbar_wait_t<0>(&a_full[slot], full_phase, abort_flag);
+                            if (!ok)
+                                break;
+                            tc_fence_after();
+                            if (lane == i)
+                            {
+                                uint32_t a_addr = a_ring + slot * (uint32_t) g.kr;
+                                uint64_t bd = bd0;
+                                for (int ks = 0; ks < ksteps; ++ks)
+                                {
+                                    mma_tf32_ts(my_d, a_addr, bd, my_idesc);
+                                    a_addr += 8;
+                                    bd += b_kstep_units;
+                                }
+                                mma_commit(&a_empty[slot]);
+                                mma_commit(&row_done[i]);
+                                tc_fence_before();
+                            }
+                            __syncwarp();
+                            if (++lap_a == laps_a)
+                            {
+                                lap_a = 0;
+                                full_phase ^= 1;
+                            }
+                        }
+                        else
+                        {
+                            tc_fence_after();
+                            if (lane == 0)
+                                mbar_arrive(&row_done[i]);
+                            __syncwarp();
+                        }
+                    }
+                    if (real)
+                        base = (base + (uint32_t) R) % (uint32_t) G;
+                }
+            }
+        }
+    }
+    else if (warp > TC_TMA_WARP)
+    {
+        // ------------------------------------------------------------------
+        // epilogue: after step d retire output plane d + pad - (fd-1)
+        // ------------------------------------------------------------------
+        const int quad = warp & 3;
+        const int half = (warp - TC_TMA_WARP - 1) >> 2, nhalf = TC_EPI_WARPS / 4;
+        const uint32_t lane_addr = tmem_base + ((uint32_t) (quad * 32) << 16);
+        // every warp zeroes the blocks of the rows it will retire, then hands
+        // them out for the first step
+        for (int j = half; j < g.th; j += nhalf)
+            for (int col = 0; col < fd * SW_NBK; col += 16)
+                tmem_st16_zero(lane_addr + (uint32_t) (j * fd * SW_NBK + col));
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0)
+            for (int j = half; j < g.th; j += nhalf)
+                mbar_arrive(&row_free[j]);
+        uint32_t step = 0;
+        for (uint32_t u = blockIdx.x; u < nunits && ok; u += gridDim.x)
+        {
+            const SwUnit t = sw_unit(g, u);
+            const int ow = t.ow0 + quad * 32 + lane;
+            for (int d = t.d_first; d < t.d_stop && ok; ++d, ++step)
+            {
+                const int od = d + g.pad[0] - (fd - 1);
+                const bool store = od >= t.od0 && od < t.od1;
+                const uint32_t par = step & 1;
+                const uint32_t slot_col = (uint32_t) (sw_mod(od, fd) * SW_NBK);
+                for (int j = half; j < g.th && ok; j += nhalf)
+                {
+                    for (int i = j; i < j + fh && ok; ++i)
+                        ok = mbar_wait(&row_done[i], par, abort_flag);
+                    if (!ok)
+                        break;
+                    tc_fence_after();
+                    const uint32_t addr = lane_addr + (uint32_t) (j * fd * SW_NBK) + slot_col;
+                    const int oh = t.oh0 + j;
+                    if (store && oh < g.out[1])
+                    {
+                        uint32_t v[16];
+                        tmem_ld16(addr, v);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                        if (ow < g.out[2])
+                        {
+                            float* yp = y + (size_t) t.n * g.ys_n + (size_t) od * g.ys[0] + (size_t) oh * g.ys[1] + ow;
+#pragma unroll
+                            for (int k = 0; k < SW_NBK; ++k)
+                                if (k < g.k)
+                                {
+                                    float* p = yp + (size_t) k * g.ys_c;
+                                    const float prev = beta != 0.f ? *p : 0.f;
+                                    *p = alpha * __uint_as_float(v[k]) + beta * prev;
+                                }
+                        }
+                    }
+                    tmem_st16_zero(addr);
+                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0)
+                        mbar_arrive(&row_free[j]);
+                }
+            }
+        }
+    }
+
+    if (!ok && lane == 0)
+        atomicExch(status, 1);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == TC_MMA_WARP)
+    {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TC_TMEM_COLS)
+                     : "memory");
+    }
+}
+
+} // namespace
+} // namespace dcb

@@ -79,6 +79,8 @@ def run_all(x, w, dy, pads, strides, dil, mode, alpha=1.0, beta=0.0, y0=None, dx
     p.bwd_data(alpha, ws, dys, beta, dx)
     p.bwd_filter(alpha, xs, dys, beta, dw)
     torch.cuda.synchronize()
+    # a tensor-core kernel that gave up on one of its bounded waits says so here
+    assert _abi.lib().dcb_conv_plan_status(p.p, None) == _abi.OK, "a conv kernel gave up on a bounded wait"
     return y.cpu().numpy(), dx.cpu().numpy(), dw.cpu().numpy()
 
 
