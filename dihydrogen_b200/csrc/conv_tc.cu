@@ -146,7 +146,8 @@ bool tc_geom(const ConvGeom& cg, int math_mode, TcGeom* out)
 size_t sw_smem_need(const SwGeom& g)
 {
     return (size_t) (g.b_bytes + 127) / 128 * 128 + (size_t) g.raw_slots * g.raw_slot_bytes
-           + (size_t) ((g.kr + 1) & ~1) * 4 + (size_t) (2 * g.a_slots + 64 + 2 * g.raw_slots) * 8 + 64 + 1024;
+           + (size_t) ((g.kr + 1) & ~1) * 4 + (size_t) (2 * g.a_slots + 64 + 2 * g.raw_slots) * 8 + 64 + 128
+           + (size_t) TC_EPI_WARPS * 2 * SW_NBK * 32 * 4 + 1024;
 }
 
 // Geometry of the sweep kernel (filters with depth).  Needs bulk-copy
@@ -446,9 +447,38 @@ static bool sw_make_x_map(const SwGeom& g, const float* x, CUtensorMap* map)
     return make_x_map(t, x, map);
 }
 
+// Descriptor of the output as a 5-D tensor (W, H, D, K, N) whose box is 32
+// outputs of every filter: what one epilogue warp stores per row.  Returns
+// false when the output cannot be described (alignment); the kernel then
+// stores from registers.
+static bool sw_make_y_map(const SwGeom& g, float* y, CUtensorMap* map)
+{
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn || (reinterpret_cast<uintptr_t>(y) & 15) != 0)
+        return false;
+    const cuuint64_t dims[5] = {(cuuint64_t) g.out[2], (cuuint64_t) g.out[1], (cuuint64_t) g.out[0], (cuuint64_t) g.k,
+                                (cuuint64_t) g.n};
+    const long long s1 = g.out[1] > 1 ? g.ys[1] : g.out[2];
+    const long long s0 = g.out[0] > 1 ? g.ys[0] : s1 * g.out[1];
+    const long long sc = g.k > 1 ? g.ys_c : s0 * g.out[0];
+    const long long sn = g.n > 1 ? g.ys_n : sc * g.k;
+    const cuuint64_t strides[4] = {(cuuint64_t) s1 * 4, (cuuint64_t) s0 * 4, (cuuint64_t) sc * 4, (cuuint64_t) sn * 4};
+    for (int i = 0; i < 4; ++i)
+        if (strides[i] % 16 != 0 || strides[i] == 0)
+            return false;
+    const cuuint32_t box[5] = {32, 1, 1, (cuuint32_t) SW_NBK, 1};
+    const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 5, y, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE)
+           == CUDA_SUCCESS;
+}
+
 static int32_t sw_launch(const SwGeom& g, float alpha, const float* w, const float* x, float* bimg, float beta,
                          float* y, int* status, const CUtensorMap& map, cudaStream_t stream)
 {
+    CUtensorMap ymap;
+    std::memset(&ymap, 0, sizeof(ymap));
+    const int use_ymap = sw_make_y_map(g, y, &ymap) ? 1 : 0;
     const long long total = (long long) g.b_bytes / 4;
     sw_pack_filter_kernel<<<(unsigned) ((total + 255) / 256), 256, 0, stream>>>(w, bimg, g);
     DCB_LAUNCH_CHECK();
@@ -462,13 +492,15 @@ static int32_t sw_launch(const SwGeom& g, float alpha, const float* w, const flo
     {
         DCB_CUDA_TRY(cudaFuncSetAttribute(sw_conv_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           (int) (224 * 1024)));
-        sw_conv_kernel<true><<<(unsigned) grid, TC_THREADS, smem, stream>>>(g, alpha, beta, bimg, y, status, map);
+        sw_conv_kernel<true><<<(unsigned) grid, TC_THREADS, smem, stream>>>(g, alpha, beta, bimg, y, status, map, ymap,
+                                                                           use_ymap);
     }
     else
     {
         DCB_CUDA_TRY(cudaFuncSetAttribute(sw_conv_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           (int) (224 * 1024)));
-        sw_conv_kernel<false><<<(unsigned) grid, TC_THREADS, smem, stream>>>(g, alpha, beta, bimg, y, status, map);
+        sw_conv_kernel<false><<<(unsigned) grid, TC_THREADS, smem, stream>>>(g, alpha, beta, bimg, y, status, map, ymap,
+                                                                            use_ymap);
     }
     DCB_LAUNCH_CHECK();
     (void) x;

@@ -775,18 +775,30 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                 {
                     float* yp = y + (size_t) t.n * g.ys_n + (size_t) t.od * g.ys[0] + (size_t) oh * g.ys[1] + ow;
                     const int kp = g.split ? NB / 2 : NB;
-#pragma unroll
-                    for (int k = 0; k < NB; ++k)
+                    const int nk = g.k < kp ? g.k : kp;
+                    const size_t ysc = (size_t) g.ys_c;
+                    // the hi and lo halves of the split land in separate columns
+                    if (g.split)
                     {
-                        if (k < kp && k < g.k)
-                        {
-                            float acc = __uint_as_float(v[k]);
-                            if (g.split)
-                                acc += __uint_as_float(v[(k + NB / 2) % NB]);
-                            float* p = yp + (size_t) k * g.ys_c;
-                            const float prev = beta != 0.f ? *p : 0.f;
-                            *p = alpha * acc + beta * prev;
-                        }
+#pragma unroll
+                        for (int k = 0; k < NB / 2; ++k)
+                            v[k] = __float_as_uint(__uint_as_float(v[k]) + __uint_as_float(v[k + NB / 2]));
+                    }
+                    // straight-line stores: a test of beta per filter costs
+                    // more than the stores themselves
+                    if (beta == 0.f)
+                    {
+#pragma unroll
+                        for (int k = 0; k < NB; ++k)
+                            if (k < nk)
+                                yp[(size_t) k * ysc] = alpha * __uint_as_float(v[k]);
+                    }
+                    else
+                    {
+#pragma unroll
+                        for (int k = 0; k < NB; ++k)
+                            if (k < nk)
+                                yp[(size_t) k * ysc] = alpha * __uint_as_float(v[k]) + beta * yp[(size_t) k * ysc];
                     }
                 }
             }

@@ -180,7 +180,7 @@ __device__ __forceinline__ void sw_convert_c4f3(uint32_t raw_lane, uint32_t pitc
 template <bool C4F3>
 __global__ void __launch_bounds__(TC_THREADS, 1)
     sw_conv_kernel(SwGeom g, float alpha, float beta, const float* __restrict__ bimg, float* y, int* status,
-                   const __grid_constant__ CUtensorMap xmap)
+                   const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap ymap, int use_ymap)
 {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -197,6 +197,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     uint64_t* raw_empty = raw_full + g.raw_slots;   // [raw_slots]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(raw_empty + g.raw_slots);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    // output staging for bulk stores: two 2 KiB buffers per epilogue warp
+    float* stage_base = reinterpret_cast<float*>(
+        (reinterpret_cast<uintptr_t>(tmem_slot + 2) + 127) & ~uintptr_t(127));
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int fd = g.f[0], fh = g.f[1], R = g.rows, G = g.groups;
@@ -475,6 +478,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         const int quad = warp & 3;
         const int half = (warp - TC_TMA_WARP - 1) >> 2, nhalf = TC_EPI_WARPS / 4;
         const uint32_t lane_addr = tmem_base + ((uint32_t) (quad * 32) << 16);
+        const int nk = g.k;
+        const size_t ysc = (size_t) g.ys_c;
+        // bulk stores overwrite: the blend with the old output takes the plain path
+        const bool bulk = use_ymap != 0 && beta == 0.f;
+        float* stage = stage_base + (warp - TC_TMA_WARP - 1) * (2 * SW_NBK * 32);
+        uint32_t nstored = 0;
         // every warp zeroes the blocks of the rows it will retire, then hands
         // them out for the first step
         for (int j = half; j < g.th; j += nhalf)
@@ -506,33 +515,79 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                     tc_fence_after();
                     const uint32_t addr = lane_addr + (uint32_t) (j * fd * SW_NBK) + slot_col;
                     const int oh = t.oh0 + j;
-                    if (store && oh < g.out[1])
+                    const bool wr = store && oh < g.out[1];
+                    uint32_t v[16];
+                    if (wr)
                     {
-                        uint32_t v[16];
                         tmem_ld16(addr, v);
                         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                        if (ow < g.out[2])
-                        {
-                            float* yp = y + (size_t) t.n * g.ys_n + (size_t) od * g.ys[0] + (size_t) oh * g.ys[1] + ow;
-#pragma unroll
-                            for (int k = 0; k < SW_NBK; ++k)
-                                if (k < g.k)
-                                {
-                                    float* p = yp + (size_t) k * g.ys_c;
-                                    const float prev = beta != 0.f ? *p : 0.f;
-                                    *p = alpha * __uint_as_float(v[k]) + beta * prev;
-                                }
-                        }
                     }
+                    // hand the blocks back first: the issuers wait for that, nobody for the store
                     tmem_st16_zero(addr);
                     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0)
                         mbar_arrive(&row_free[j]);
+                    if (!wr)
+                        continue;
+                    if (bulk)
+                    {
+                        if (t.ow0 + quad * 32 >= g.out[2])
+                            continue; // this warp's 32 outputs lie beyond the row
+                        // registers -> staging buffer [filter][32 outputs] -> one bulk
+                        // tensor store (clipped at the tensor's edges); the buffer
+                        // used two rows ago must have been read by then
+                        float* st = stage + (nstored & 1) * (SW_NBK * 32);
+                        if (nstored >= 2)
+                        {
+                            if (lane == 0)
+                                asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                            __syncwarp();
+                        }
+                        const uint32_t st_s = smem_u32(st) + 4u * (uint32_t) lane;
+#pragma unroll
+                        for (int k = 0; k < SW_NBK; ++k)
+                            asm volatile("st.shared.f32 [%0], %1;" ::"r"(st_s + 128u * k),
+                                         "f"(alpha * __uint_as_float(v[k]))
+                                         : "memory");
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                        __syncwarp();
+                        if (lane == 0)
+                        {
+                            asm volatile(
+                                "cp.async.bulk.tensor.5d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5, %6}], [%1];" ::"l"(
+                                    reinterpret_cast<uint64_t>(&ymap)),
+                                "r"(smem_u32(st)), "r"(t.ow0 + quad * 32), "r"(oh), "r"(od), "r"(0), "r"(t.n)
+                                : "memory");
+                            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                        }
+                        ++nstored;
+                    }
+                    else if (ow < g.out[2])
+                    {
+                        float* p = y + (size_t) t.n * g.ys_n + (size_t) od * g.ys[0] + (size_t) oh * g.ys[1] + ow;
+                        if (beta == 0.f)
+                        {
+#pragma unroll
+                            for (int k = 0; k < SW_NBK; ++k)
+                                if (k < nk)
+                                    p[(size_t) k * ysc] = alpha * __uint_as_float(v[k]);
+                        }
+                        else
+                        {
+#pragma unroll
+                            for (int k = 0; k < SW_NBK; ++k)
+                                if (k < nk)
+                                    p[(size_t) k * ysc] = alpha * __uint_as_float(v[k]) + beta * p[(size_t) k * ysc];
+                        }
+                    }
                 }
             }
         }
+        // the staged rows must have left shared memory before the CTA does
+        if (bulk && lane == 0)
+            asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     }
 
     if (!ok && lane == 0)
