@@ -201,22 +201,40 @@ bool sw_geom(const ConvGeom& cg, int math_mode, SwGeom* out)
     g.a_slots = g.groups;
     if (g.a_slots * g.kr > 256)
         return false;
-    int th = ((int) TC_TMEM_COLS - g.a_slots * g.kr) / (g.f[0] * SW_NBK);
-    if (th + g.f[1] - 1 > 32)
-        th = 32 - g.f[1] + 1;
-    if (th > g.out[1])
-    {
-        th = g.out[1];
-    }
-    else
-    {
-        const int nt = (g.out[1] + th - 1) / th; // even out the rows over the columns
-        th = (g.out[1] + nt - 1) / nt;
-    }
-    if (th < 2)
+    int th_max = ((int) TC_TMEM_COLS - g.a_slots * g.kr) / (g.f[0] * SW_NBK);
+    if (th_max + g.f[1] - 1 > 32)
+        th_max = 32 - g.f[1] + 1;
+    if (th_max > g.out[1])
+        th_max = g.out[1];
+    if (th_max < 2)
         return false;
-    g.th = th;
-    g.rows = th + g.f[1] - 1;
+    // Rows per column (th) and segments along D (nseg) together decide how
+    // evenly the units fill the SMs: take the pair with the fewest staged
+    // rows on the busiest SM.  Fewer rows per column cost more halo rows,
+    // more segments cost more spill steps; both are in the count.
+    const int sms = num_sms();
+    long long best_cost = -1;
+    int best_th = th_max, best_ns = 1;
+    for (int th = th_max; th >= 2 && th >= th_max - 3; --th)
+    {
+        const long long cols = (long long) g.n * ((g.out[2] + TC_M - 1) / TC_M) * ((g.out[1] + th - 1) / th);
+        for (int ns = 1; ns <= g.out[0] && ns <= 64; ++ns)
+        {
+            const long long units = cols * ns;
+            const long long waves = (units + sms - 1) / sms;
+            const long long steps = (g.out[0] + ns - 1) / ns + 2 * (g.f[0] - 1);
+            const long long cost = waves * steps * (th + g.f[1] - 1);
+            if (best_cost < 0 || cost < best_cost)
+            {
+                best_cost = cost;
+                best_th = th;
+                best_ns = ns;
+            }
+        }
+    }
+    g.th = best_th;
+    g.nseg = best_ns;
+    g.rows = g.th + g.f[1] - 1;
     // chunks of about 17 KiB, evenly sized
     const int row_bytes = g.c * TC_RAW_W * 4;
     int rc_max = (17 * 1024 + 512) / row_bytes;
@@ -233,25 +251,7 @@ bool sw_geom(const ConvGeom& cg, int math_mode, SwGeom* out)
         return false;
     g.tiles_w = (g.out[2] + TC_M - 1) / TC_M;
     g.tiles_h = (g.out[1] + g.th - 1) / g.th;
-    // segments along D: whole waves of CTAs, few spill steps
-    const long long cols = (long long) g.n * g.tiles_w * g.tiles_h;
-    const int sms = num_sms();
-    long long best_cost = -1;
-    int best = 1;
-    for (int ns = 1; ns <= g.out[0] && ns <= 64; ++ns)
-    {
-        const long long units = cols * ns;
-        const long long waves = (units + sms - 1) / sms;
-        const long long steps = (g.out[0] + ns - 1) / ns + 2 * (g.f[0] - 1);
-        const long long cost = waves * steps;
-        if (best_cost < 0 || cost < best_cost)
-        {
-            best_cost = cost;
-            best = ns;
-        }
-    }
-    g.nseg = best;
-    g.units = cols * g.nseg;
+    g.units = (long long) g.n * g.tiles_w * g.tiles_h * g.nseg;
     if (g.units >= (1ll << 31))
         return false;
     *out = g;
