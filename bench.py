@@ -206,6 +206,7 @@ def run_ours(args):
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback for the product path")
     torch.cuda.set_device(local_rank)
+    os.environ.setdefault("NCCL_DEBUG", "WARN")  # keep NCCL's version banner off stdout
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
         locale = dc.Locale.from_torch_distributed()
@@ -326,8 +327,8 @@ def run_ours(args):
     # ncu capture of a 64 x 256 x 256 shard, which scales with the D extent:
     # bytes per shard voxel times this launch's voxels.
     ncu_vox = 64 * 256 * 256
-    traffic_per_voxel = {"conv_fwd": (67.25e6 + 210.80e6) / ncu_vox, "bn_stats": (268.46e6 + 4.05e6) / ncu_vox,
-                         "bn_finalize_apply": (268.53e6 + 222.07e6) / ncu_vox}
+    traffic_per_voxel = {"conv_fwd": (69.34e6 + 208.91e6) / ncu_vox, "bn_stats": (268.46e6 + 4.00e6) / ncu_vox,
+                         "bn_finalize_apply": (268.45e6 + 222.17e6) / ncu_vox}
     dom = max(kernels, key=lambda k: kernels[k]["ms"])
     ach = kernels[dom]["bytes"] / (kernels[dom]["ms"] * 1e-3) / 1e9
     roofline = {"kernel": dom, "bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
