@@ -782,6 +782,50 @@ public:
         }
     }
 
+    // The reference's own argument list (convolution.hpp:119-135): filters
+    // and their gradients are tensors of shape (fw, fh, [fd,] C, K) that every
+    // rank holds whole (Distribution::make_shared_distribution).  The
+    // algorithm names and the workspace size are accepted and ignored: there
+    // is one kernel family and plans own their workspace.
+    void setup(TensorF& input, TensorF& filter, TensorF& output, TensorF& d_input, TensorF& /*d_filter*/,
+               TensorF& d_output, const int_vector& pads, const int_vector& strides, const int_vector& dilations,
+               int num_groups, const std::string& /*fwd_algo*/ = "DEFAULT",
+               const std::string& /*bwd_data_algo*/ = "DEFAULT", const std::string& /*bwd_filter_algo*/ = "DEFAULT",
+               size_t /*ws_size*/ = 0, bool skip_bp_data = false, bool deconv = false)
+    {
+        if (deconv)
+            throw std::runtime_error("Convolution: deconvolution is not provided");
+        const tensor::Shape& fs = filter.get_shape();
+        int_vector fshape(fs.begin(), fs.end());
+        setup(input, fshape, output, skip_bp_data ? nullptr : &d_input, &d_output, pads, strides, dilations,
+              num_groups);
+    }
+    int forward(float alpha, TensorF& input, TensorF& filter, float beta, TensorF& output,
+                bool skip_halo_exchange = false, bool /*skip_chanfilt_comm*/ = false, bool /*dump_profile*/ = false,
+                bool /*inference*/ = false)
+    {
+        return forward(alpha, input, filter.get_const_buffer(), beta, output, skip_halo_exchange);
+    }
+    int backward_data(float alpha, TensorF& filter, TensorF& d_output, float beta, TensorF& d_input,
+                      bool skip_halo_exchange = false, bool /*skip_chanfilt_comm*/ = false,
+                      bool /*dump_profile*/ = false)
+    {
+        return backward_data(alpha, filter.get_const_buffer(), d_output, beta, d_input, skip_halo_exchange);
+    }
+    int backward_filter(float alpha, TensorF& input, TensorF& d_output, float beta, TensorF& d_filter,
+                        bool reduce = true, bool /*skip_chanfilt_comm*/ = false, bool /*dump_profile*/ = false)
+    {
+        return backward_filter(alpha, input, d_output, beta, d_filter.get_buffer(), reduce);
+    }
+    int apply_bias(float alpha, TensorF& bias, float beta, TensorF& output)
+    {
+        return apply_bias(alpha, bias.get_const_buffer(), beta, output);
+    }
+    int backward_bias(float alpha, TensorF& d_output, float beta, TensorF& bias_gradient, bool reduce = true)
+    {
+        return backward_bias(alpha, d_output, beta, bias_gradient.get_buffer(), reduce);
+    }
+
     int kernel_kind(int which) const
     {
         return dcb_conv_plan_kernel_kind(which == 0 ? m_plan_fwd : m_plan_bwd, which);
@@ -982,6 +1026,24 @@ public:
         forward_stage1(input, mean, var, is_training);
         forward_allreduce(input, mean, var, is_training);
         return forward_stage2(input, mean, var, running_mean, running_var, scale, bias, output, is_training);
+    }
+
+    // The reference's argument list: statistics, scale and bias are tensors
+    // of shape (1, 1, [1,] C, 1) held whole by every rank.
+    int forward(TensorF& input, TensorF& mean, TensorF& var, TensorF& running_mean, TensorF& running_var,
+                TensorF& scale, TensorF& bias, TensorF& output, bool is_training = true)
+    {
+        return forward(input, mean.get_buffer(), var.get_buffer(), running_mean.get_buffer(),
+                       running_var.get_buffer(), scale.get_const_buffer(), bias.get_const_buffer(), output,
+                       is_training);
+    }
+    int backward(TensorF& input, TensorF& d_output, TensorF& mean, TensorF& var, TensorF& scale,
+                 TensorF& scale_gradient, TensorF& bias_gradient, TensorF& mean_gradient, TensorF& var_gradient,
+                 TensorF& d_input)
+    {
+        return backward(input, d_output, mean.get_const_buffer(), var.get_const_buffer(), scale.get_const_buffer(),
+                        scale_gradient.get_buffer(), bias_gradient.get_buffer(), mean_gradient.get_buffer(),
+                        var_gradient.get_buffer(), d_input);
     }
 
     int backward_stage1(TensorF& input, TensorF& d_output, const float* mean, const float* var, const float* scale,

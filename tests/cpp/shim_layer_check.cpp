@@ -224,8 +224,14 @@ void rank_main(int rank, int R, Shared* sh, const Global* g)
             init[3 * K + k] = init[4 * K + k] = 1.f; // running var, scale
         cudaMemcpy(stats, init.data(), init.size() * 4, cudaMemcpyHostToDevice);
 
+        // filters as the reference passes them: tensors every rank holds whole
+        const tensor::Shape fsh(std::vector<index_t>{F, F, F, C, K});
+        const auto shared = tensor::Distribution::make_shared_distribution(tensor::Shape(std::vector<index_t>{1, 1, R, 1, 1}));
+        TensorF wt(fsh, loc, shared), dwt(fsh, loc, shared);
+        wt.set_view(w);
+        dwt.set_view(dw);
         Convolution<BackendDNNLib, float> conv(be, 5, HaloExchangeMethod::P2P);
-        conv.setup(x, fshape, y, &dx, &dy, pads, ones, ones);
+        conv.setup(x, wt, y, dx, dwt, dy, pads, ones, ones, 1, "DEFAULT", "DEFAULT", "DEFAULT", 0);
         BatchNormalization<BackendDNNLib, float> bn(be, 5, DECAY, EPS, true);
 
         auto phase = [&](auto put, auto wait) {
@@ -240,15 +246,15 @@ void rank_main(int rank, int R, Shared* sh, const Global* g)
         x.clear_halo(2, st);
         phase([&] { conv.input_halo_exchange().pack_put(2, st); },
               [&] { conv.input_halo_exchange().wait_unpack(2, st); });
-        conv.forward(1.f, x, w, 0.f, y, /*skip_halo_exchange=*/true);
+        conv.forward(1.f, x, wt, 0.f, y, /*skip_halo_exchange=*/true);
         bn.forward_stage1(y, stats, stats + K);
         phase([&] { be.allreduce_push(stats, 2 * K); }, [&] { be.allreduce_pull(stats, 2 * K); });
         bn.forward_stage2(y, stats, stats + K, stats + 2 * K, stats + 3 * K, stats + 4 * K, stats + 5 * K, z);
         // backward of the convolution
         phase([&] { conv.d_output_halo_exchange().pack_put(2, st); },
               [&] { conv.d_output_halo_exchange().wait_unpack(2, st); });
-        conv.backward_data(1.f, w, dy, 0.f, dx, /*skip_halo_exchange=*/true);
-        conv.backward_filter(1.f, x, dy, 0.f, dw, /*reduce=*/false);
+        conv.backward_data(1.f, wt, dy, 0.f, dx, /*skip_halo_exchange=*/true);
+        conv.backward_filter(1.f, x, dy, 0.f, dwt, /*reduce=*/false);
         phase([&] { be.allreduce_push(dw, (index_t) wcount); }, [&] { be.allreduce_pull(dw, (index_t) wcount); });
         if (conv.status() != DCB_OK)
             throw std::runtime_error("layer status");
