@@ -243,12 +243,18 @@ def run_ours(args):
     launches = {"n": 0}
     partitioned = world > 1
 
+    fuse = not args.no_fused_stats
+
     def step():
-        conv.forward(1.0, x, w, 0.0, y)
-        bn.forward(y, mean, var, rm, rv, scale, bias, z, True)
+        # the conv epilogue also delivers the BN statistics of its output
+        # (falls back to the separate statistics pass if the plan cannot)
+        got = conv.forward(1.0, x, w, 0.0, y, statistics=(mean, var) if fuse else None)
+        bn.forward(y, mean, var, rm, rv, scale, bias, z, True, statistics_ready=bool(got))
         # clear_halo (1 per partitioned dim), pack+put and wait+unpack (1 each per
-        # partitioned dim), conv, bn stats, all-reduce, finalize, apply
-        launches["n"] += (3 if partitioned else 0) + 5
+        # partitioned dim), filter image, conv, statistics (fold of the epilogue's
+        # partials, or the separate pass), all-reduce, finalize, apply
+        launches["n"] += (3 if partitioned else 0) + 6
+        return got
 
     def e2e_step():
         x.owned().copy_(host_x, non_blocking=True)
@@ -351,7 +357,9 @@ def run_ours(args):
         torch.cuda.synchronize()
         return e0.elapsed_time(e1) / reps
 
-    t_conv = time_call(lambda: conv.forward(1.0, x, w, 0.0, y, skip_halo_exchange=True))
+    fused_ok = bool(step()) if fuse else False
+    t_conv = time_call(lambda: conv.forward(1.0, x, w, 0.0, y, skip_halo_exchange=True,
+                                            statistics=(mean, var) if fused_ok else None))
     t_stats = time_call(lambda: bn.forward_stage1(y, mean, var, True))
     t_apply = time_call(lambda: bn.forward_stage2(y, mean, var, rm, rv, scale, bias, z, True))
     clocks = sampler.stop() if rank == 0 else None
@@ -373,9 +381,10 @@ def run_ours(args):
     conv_bytes = 4 * (in_el + K_OUT * C_IN * 27 + out_el)
     kernels = {
         "conv_fwd": {"ms": t_conv, "bytes": conv_bytes, "flops": 2 * K_OUT * C_IN * 27 * vox_local},
-        "bn_stats": {"ms": t_stats, "bytes": 4 * out_el},
         "bn_finalize_apply": {"ms": t_apply, "bytes": 8 * out_el},
     }
+    if not fused_ok:
+        kernels["bn_stats"] = {"ms": t_stats, "bytes": 4 * out_el}
     # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the
     # ncu capture of a 64 x 256 x 256 shard, which scales with the D extent:
     # bytes per shard voxel times this launch's voxels.
@@ -390,7 +399,9 @@ def run_ours(args):
                 "kernels_ms": {k: round(v["ms"], 4) for k, v in kernels.items()},
                 "kernels_gbs": {k: round(v["bytes"] / (v["ms"] * 1e-3) / 1e9, 1) for k, v in kernels.items()},
                 "conv_tflops": kernels["conv_fwd"]["flops"] / (t_conv * 1e-3) / 1e12,
-                "conv_kernel": "tcgen05" if conv.kernel_kind(0) == 1 else "fp32-simt"}
+                "conv_kernel": "tcgen05" if conv.kernel_kind(0) == 1 else "fp32-simt",
+                "bn_statistics": "from the conv epilogue" if fused_ok else "separate pass",
+                "bn_stats_separate_pass_ms": round(t_stats, 4)}
 
     cpu = None
     if world == 1 and not args.skip_cpu:
@@ -434,6 +445,8 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-fused-stats", action="store_true",
+                    help="run the BN statistics as their own pass instead of taking them from the conv epilogue")
     ap.add_argument("--local-d", type=int, default=None,
                     help="per-GPU D extent instead of 256 (small case for profiler captures; not a bench value)")
     ap.add_argument("--skip-cpu", action="store_true", help="skip the CPU baseline leg (profiler captures)")

@@ -92,6 +92,7 @@ _SIGS = {
     "dcb_conv_plan_create": (c_int32, [POINTER(ConvDesc), POINTER(NdDesc), POINTER(NdDesc), POINTER(_P)]),
     "dcb_conv_plan_destroy": (c_int32, [_P]),
     "dcb_conv_fwd": (c_int32, [_P, c_double, _P, _P, c_double, _P, _P]),
+    "dcb_conv_fwd_stats": (c_int32, [_P, c_double, _P, _P, _P, _P, _P, _P]),
     "dcb_conv_bwd_data": (c_int32, [_P, c_double, _P, _P, c_double, _P, _P]),
     "dcb_conv_bwd_filter": (c_int32, [_P, c_double, _P, _P, c_double, _P, _P]),
     "dcb_conv_plan_kernel_kind": (c_int32, [_P, c_int32]),

@@ -200,6 +200,19 @@ int32_t dcb_conv_fwd(dcb_conv_plan* p, double alpha, const void* x,
                          static_cast<float*>(y), as_stream(stream));
 }
 
+int32_t dcb_conv_fwd_stats(dcb_conv_plan* p, double alpha, const void* x,
+                           const void* w, void* y, void* sums, void* sqsums,
+                           void* stream)
+{
+    DCB_REQUIRE(p && x && w && y && sums && sqsums, "null argument");
+    if (p->kind[0] != 1)
+        return DCB_UNSUPPORTED;
+    return tc_conv_fwd_stats(p->tc, (float) alpha, static_cast<const float*>(x),
+                             static_cast<const float*>(w),
+                             static_cast<float*>(y), static_cast<float*>(sums),
+                             static_cast<float*>(sqsums), as_stream(stream));
+}
+
 int32_t dcb_conv_bwd_data(dcb_conv_plan* p, double alpha, const void* w,
                           const void* dy, double beta, void* dx, void* stream)
 {

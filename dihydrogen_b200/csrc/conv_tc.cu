@@ -195,9 +195,13 @@ bool sw_geom(const ConvGeom& cg, int math_mode, SwGeom* out)
     g.b_bytes = g.f[0] * g.b_rot_bytes;
     // an issuer must own one of any fh consecutive rows (see the hand-off
     // notes in the kernel header)
-    g.groups = g.f[1] < TC_GROUPS_MAX ? g.f[1] : TC_GROUPS_MAX;
-    while (g.groups > 1 && g.groups * g.kr > 160)
-        --g.groups;
+    g.groups = TC_GROUPS_MAX;
+    // Only the three-group arrangement is in use: fewer groups (shallow
+    // filters, or k-rows too wide for three A slots) gave up on a bounded wait
+    // when tried, and those shapes stay with the row kernel until that is
+    // understood.
+    if (g.f[1] < g.groups || g.groups * g.kr > 160)
+        return false;
     g.a_slots = g.groups;
     if (g.a_slots * g.kr > 256)
         return false;
@@ -277,6 +281,7 @@ struct TcPlan
     bool has_sw[2] = {false, false};
     SwGeom sw[2];
     float* sw_bimg[2] = {nullptr, nullptr};
+    float* stat_part = nullptr; // per epilogue warp partial sums of the fused statistics
     int* status = nullptr;
 };
 
@@ -304,6 +309,8 @@ int32_t tc_plan_create(const ConvGeom& fwd, const ConvGeom& bwd, bool bwd_is_fwd
         if (ok && p->has_sw[s])
             ok = cudaMalloc(&p->sw_bimg[s], p->sw[s].b_bytes) == cudaSuccess;
     }
+    if (ok && p->has_sw[0])
+        ok = cudaMalloc(&p->stat_part, (size_t) num_sms() * TC_EPI_WARPS * 32 * sizeof(float)) == cudaSuccess;
     if (!ok)
     {
         (void) cudaGetLastError();
@@ -323,6 +330,7 @@ void tc_plan_destroy(TcPlan* p)
     cudaFree(p->bimg[1]);
     cudaFree(p->sw_bimg[0]);
     cudaFree(p->sw_bimg[1]);
+    cudaFree(p->stat_part);
     cudaFree(p->status);
     delete p;
 }
@@ -474,7 +482,8 @@ static bool sw_make_y_map(const SwGeom& g, float* y, CUtensorMap* map)
 }
 
 static int32_t sw_launch(const SwGeom& g, float alpha, const float* w, const float* x, float* bimg, float beta,
-                         float* y, int* status, const CUtensorMap& map, cudaStream_t stream)
+                         float* y, int* status, const CUtensorMap& map, cudaStream_t stream,
+                         float* stat_part = nullptr, float* sums = nullptr, float* sqsums = nullptr)
 {
     CUtensorMap ymap;
     std::memset(&ymap, 0, sizeof(ymap));
@@ -488,21 +497,26 @@ static int32_t sw_launch(const SwGeom& g, float alpha, const float* w, const flo
     if (grid > g.units)
         grid = g.units;
     const bool c4f3 = g.c == 4 && g.f[2] == 3 && g.pad[2] == 1 && g.split;
+    const bool stats = stat_part != nullptr;
+    auto launch = [&](auto kernel) -> int32_t {
+        DCB_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) (224 * 1024)));
+        kernel<<<(unsigned) grid, TC_THREADS, smem, stream>>>(g, alpha, beta, bimg, y, status, map, ymap, use_ymap,
+                                                            stat_part);
+        return DCB_OK;
+    };
+    int32_t st;
     if (c4f3)
-    {
-        DCB_CUDA_TRY(cudaFuncSetAttribute(sw_conv_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          (int) (224 * 1024)));
-        sw_conv_kernel<true><<<(unsigned) grid, TC_THREADS, smem, stream>>>(g, alpha, beta, bimg, y, status, map, ymap,
-                                                                           use_ymap);
-    }
+        st = stats ? launch(sw_conv_kernel<true, true>) : launch(sw_conv_kernel<true, false>);
     else
-    {
-        DCB_CUDA_TRY(cudaFuncSetAttribute(sw_conv_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          (int) (224 * 1024)));
-        sw_conv_kernel<false><<<(unsigned) grid, TC_THREADS, smem, stream>>>(g, alpha, beta, bimg, y, status, map, ymap,
-                                                                            use_ymap);
-    }
+        st = stats ? launch(sw_conv_kernel<false, true>) : launch(sw_conv_kernel<false, false>);
+    if (st != DCB_OK)
+        return st;
     DCB_LAUNCH_CHECK();
+    if (stats)
+    {
+        sw_stats_fold_kernel<<<1, 32, 0, stream>>>(stat_part, (int) grid * TC_EPI_WARPS, g.k, sums, sqsums);
+        DCB_LAUNCH_CHECK();
+    }
     (void) x;
     return DCB_OK;
 }
@@ -530,6 +544,18 @@ int32_t tc_conv_fwd(TcPlan* p, int slot, float alpha, const float* x, const floa
     case 64: return tc_launch<64>(g, alpha, x, p->bimg[slot], beta, y, p->status, stream);
     default: return DCB_UNSUPPORTED;
     }
+}
+
+int32_t tc_conv_fwd_stats(TcPlan* p, float alpha, const float* x, const float* w, float* y, float* sums,
+                          float* sqsums, cudaStream_t stream)
+{
+    if (!p || !p->has_sw[0] || !p->stat_part)
+        return DCB_UNSUPPORTED;
+    CUtensorMap map;
+    std::memset(&map, 0, sizeof(map));
+    if (!sw_make_x_map(p->sw[0], x, &map))
+        return DCB_UNSUPPORTED;
+    return sw_launch(p->sw[0], alpha, w, x, p->sw_bimg[0], 0.f, y, p->status, map, stream, p->stat_part, sums, sqsums);
 }
 
 int32_t tc_conv_bwd_filter(TcPlan*, float, const float*, const float*, float, float*, cudaStream_t)

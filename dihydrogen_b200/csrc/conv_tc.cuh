@@ -20,6 +20,12 @@ bool tc_supports(const TcPlan* p, int which);
 // slot 0 runs the forward geometry, slot 1 the backward-data one.
 int32_t tc_conv_fwd(TcPlan* p, int slot, float alpha, const float* x,
                     const float* w, float beta, float* y, cudaStream_t stream);
+// Forward convolution (beta = 0) whose epilogue also returns, per filter, the sum
+// and the sum of squares of the outputs.  DCB_UNSUPPORTED when the plan's
+// kernel for this problem cannot do that; nothing has been launched then.
+int32_t tc_conv_fwd_stats(TcPlan* p, float alpha, const float* x,
+                          const float* w, float* y, float* sums,
+                          float* sqsums, cudaStream_t stream);
 // Device word that kernels set when a bounded wait expires (null if no plan).
 int* tc_status_word(TcPlan* p);
 int32_t tc_conv_bwd_filter(TcPlan* p, float alpha, const float* x,

@@ -148,6 +148,55 @@ __global__ void sw_pack_filter_kernel(const float* __restrict__ w, float* __rest
     }
 }
 
+// Packed fp32 pairs (two lanes of one 64-bit register): the statistics of the
+// epilogue cost half the instructions this way.
+__device__ __forceinline__ uint64_t f2_pack(float a, float b)
+{
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t v, float& a, float& b)
+{
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ uint64_t f2_mul(uint64_t a, uint64_t b)
+{
+    uint64_t r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b)
+{
+    uint64_t r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c)
+{
+    uint64_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+
+// Adds the epilogue warps' partial sums in index order, in fp64: thread k gives
+// sums[k], thread 16 + k gives sqsums[k].
+__global__ void sw_stats_fold_kernel(const float* __restrict__ part, int nparts, int nk, float* __restrict__ sums,
+                                     float* __restrict__ sqsums)
+{
+    const int t = threadIdx.x;
+    double acc = 0.0;
+    for (int i = 0; i < nparts; ++i)
+        acc += (double) part[(size_t) i * 32 + t];
+    if (t < SW_NBK)
+    {
+        if (t < nk)
+            sums[t] = (float) acc;
+    }
+    else if (t - SW_NBK < nk)
+        sqsums[t - SW_NBK] = (float) acc;
+}
+
 // 4 channels x 3 taps, pad 1, split: k-rows 0..11 hi, 12..23 lo, 24..35 hi, 36..39 zero.
 __device__ __forceinline__ void sw_convert_c4f3(uint32_t raw_lane, uint32_t pitch, uint32_t (&v)[5][8])
 {
@@ -177,10 +226,16 @@ __device__ __forceinline__ void sw_convert_c4f3(uint32_t raw_lane, uint32_t pitc
 // serves group q), 15 bulk copies, 16..23 epilogue (two per TMEM quadrant,
 // even / odd output rows).  TMEM columns: [accumulators th * fd * 16][A ring].
 // ---------------------------------------------------------------------------
-template <bool C4F3>
+// STATS: the epilogue also adds up, per filter, the outputs it stores and their
+// squares (what a batch-norm statistics pass over y would read again): each
+// lane keeps its own fp32 sums, every epilogue warp leaves 32 partials in
+// `stat_part` at the end, and sw_stats_fold_kernel adds those in a fixed order
+// in fp64.
+template <bool C4F3, bool STATS>
 __global__ void __launch_bounds__(TC_THREADS, 1)
     sw_conv_kernel(SwGeom g, float alpha, float beta, const float* __restrict__ bimg, float* y, int* status,
-                   const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap ymap, int use_ymap)
+                   const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap ymap, int use_ymap,
+                   float* __restrict__ stat_part)
 {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -484,6 +539,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         const bool bulk = use_ymap != 0 && beta == 0.f;
         float* stage = stage_base + (warp - TC_TMA_WARP - 1) * (2 * SW_NBK * 32);
         uint32_t nstored = 0;
+        uint64_t s1[STATS ? SW_NBK / 2 : 1], s2[STATS ? SW_NBK / 2 : 1]; // packed pairs of filters
+#pragma unroll
+        for (int k = 0; k < (STATS ? SW_NBK / 2 : 1); ++k)
+            s1[k] = s2[k] = 0ull; // two +0.0f
+        const uint64_t alpha2 = f2_pack(alpha, alpha);
         // every warp zeroes the blocks of the rows it will retire, then hands
         // them out for the first step
         for (int j = half; j < g.th; j += nhalf)
@@ -531,6 +591,18 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                         mbar_arrive(&row_free[j]);
                     if (!wr)
                         continue;
+                    if (STATS && ow < g.out[2])
+                    {
+                        // beta is zero whenever statistics are asked for
+#pragma unroll
+                        for (int k = 0; k < (STATS ? SW_NBK / 2 : 1); ++k)
+                        {
+                            const uint64_t o = f2_mul(
+                                alpha2, f2_pack(__uint_as_float(v[2 * k]), __uint_as_float(v[2 * k + 1])));
+                            s1[k] = f2_add(s1[k], o);
+                            s2[k] = f2_fma(o, o, s2[k]);
+                        }
+                    }
                     if (bulk)
                     {
                         if (t.ow0 + quad * 32 >= g.out[2])
@@ -588,6 +660,34 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         // the staged rows must have left shared memory before the CTA does
         if (bulk && lane == 0)
             asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+        if (STATS)
+        {
+            // lane k ends up with filter k's sum, lane 16 + k with its squares
+            float mine = 0.f;
+#pragma unroll
+            for (int k = 0; k < (STATS ? SW_NBK : 1); ++k)
+            {
+                float a, b, a_odd, b_odd;
+                f2_unpack(s1[k / 2], a, a_odd);
+                f2_unpack(s2[k / 2], b, b_odd);
+                if (k & 1)
+                {
+                    a = a_odd;
+                    b = b_odd;
+                }
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1)
+                {
+                    a += __shfl_xor_sync(0xffffffffu, a, off);
+                    b += __shfl_xor_sync(0xffffffffu, b, off);
+                }
+                if (lane == k)
+                    mine = a;
+                if (lane == SW_NBK + k)
+                    mine = b;
+            }
+            stat_part[((size_t) blockIdx.x * TC_EPI_WARPS + (warp - TC_TMA_WARP - 1)) * 32 + lane] = mine;
+        }
     }
 
     if (!ok && lane == 0)

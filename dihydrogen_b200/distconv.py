@@ -786,14 +786,31 @@ class Convolution:
 
     # -- compute --
     def forward(self, alpha, input: Tensor, filter: torch.Tensor, beta, output: Tensor,
-                skip_halo_exchange=False, skip_chanfilt_comm=False, dump_profile=False, inference=False):
-        """convolution.hpp:342-639 (no-overlap branch)."""
+                skip_halo_exchange=False, skip_chanfilt_comm=False, dump_profile=False, inference=False,
+                statistics=None):
+        """convolution.hpp:342-639 (no-overlap branch).
+
+        ``statistics=(sums, sqsums)`` (two K-float device tensors, beta must be
+        0) asks the convolution's epilogue for the per-filter sum and sum of
+        squares of the output, i.e. what ``BatchNormalization.forward_stage1``
+        would compute from ``output``.  Returns 1 when they were produced
+        (pass ``statistics_ready=True`` to the batch-norm), else 0: the caller
+        then runs stage 1 as usual."""
         if input.get_local_size() == 0 or output.get_local_size() == 0:
             return 0
         s = self.be.stream
         if not skip_halo_exchange:
             self._clear_halos(input, s)
             self.forward_exchange_halo(input, s)
+        if statistics is not None and float(beta) == 0.0 and input.is_split_root():
+            st = _abi.lib().dcb_conv_fwd_stats(self._plan_fwd, float(alpha), _ptr(input.nd_ptr(self._x_lo)),
+                                               _ptr(filter.data_ptr()), _ptr(output.get_base_ptr()),
+                                               _ptr(statistics[0].data_ptr()), _ptr(statistics[1].data_ptr()),
+                                               _stream_ptr(s))
+            if st == _abi.OK:
+                return 1
+            if st != _abi.UNSUPPORTED:
+                _abi.check(st, "dcb_conv_fwd_stats")
         call("dcb_conv_fwd", self._plan_fwd, float(alpha), _ptr(input.nd_ptr(self._x_lo)), _ptr(filter.data_ptr()),
              float(beta), _ptr(output.get_base_ptr()), _stream_ptr(s))
         return 0
@@ -944,8 +961,12 @@ class BatchNormalization:
              _ptr(output.get_base_ptr()), _stream_ptr(s))
         return 0
 
-    def forward(self, input, mean, var, running_mean, running_var, scale, bias, output, is_training=True):
-        self.forward_stage1(input, mean, var, is_training)
+    def forward(self, input, mean, var, running_mean, running_var, scale, bias, output, is_training=True,
+                statistics_ready=False):
+        """``statistics_ready``: mean / var already hold this rank's sums and
+        sums of squares (from ``Convolution.forward(..., statistics=...)``)."""
+        if not statistics_ready:
+            self.forward_stage1(input, mean, var, is_training)
         self.forward_allreduce(mean, var, is_training)
         self.forward_stage2(input, mean, var, running_mean, running_var, scale, bias, output, is_training)
         return 0

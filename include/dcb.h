@@ -196,6 +196,18 @@ int32_t dcb_conv_plan_destroy(dcb_conv_plan* plan);
 /* w is dense [K][C][fd][fh][fw]. */
 int32_t dcb_conv_fwd(dcb_conv_plan* plan, double alpha, const void* x,
                      const void* w, double beta, void* y, void* stream);
+/* y = alpha * conv(x, w), and from the same pass sums[k] = sum of y over filter
+ * k's outputs, sqsums[k] = sum of y^2: what dcb_bn_stats(y) returns, taken from
+ * the epilogue's registers so that a batch-norm that follows need not read y
+ * for its statistics (the reference runs cuDNN's convolution and then
+ * channel_sums_and_sqsums, batchnorm.cu:192-249, as separate passes; this fuses
+ * them, convolution.hpp:342-639 + batchnorm.hpp:171-183).  Each lane adds its
+ * outputs in fp32, the per-warp partials are folded in a fixed order in fp64.
+ * DCB_UNSUPPORTED, with nothing launched, when the plan's kernel for this
+ * problem has no such epilogue: call dcb_conv_fwd and dcb_bn_stats then. */
+int32_t dcb_conv_fwd_stats(dcb_conv_plan* plan, double alpha, const void* x,
+                           const void* w, void* y, void* sums, void* sqsums,
+                           void* stream);
 int32_t dcb_conv_bwd_data(dcb_conv_plan* plan, double alpha, const void* w,
                           const void* dy, double beta, void* dx, void* stream);
 int32_t dcb_conv_bwd_filter(dcb_conv_plan* plan, double alpha, const void* x,

@@ -168,3 +168,40 @@ def test_bias_forward_backward():
     _abi.call("dcb_bias_bwd", 1.0, ctypes.byref(yd), ctypes.c_void_p(y.data_ptr()), 0.0,
               ctypes.c_void_p(db.data_ptr()), None)
     emu.assert_close(db.cpu().numpy(), y.cpu().numpy().astype(np.float64).sum(axis=(0, 2, 3, 4)), 1e-5, "bias bwd")
+
+
+def test_forward_with_fused_statistics_matches_separate_pass():
+    """dcb_conv_fwd_stats: same output as dcb_conv_fwd, and the per-filter sums
+    the epilogue returns equal a statistics pass over that output."""
+    N, C, K, sp, f = 2, 4, 16, (10, 23, 152), (3, 3, 3)
+    rng = np.random.default_rng(31)
+    x = torch.from_numpy(rng.normal(0.3, 1, (N, C, *sp)).astype(np.float32)).cuda()
+    w = torch.from_numpy(rng.normal(0, 0.1, (K, C, *f)).astype(np.float32)).cuda()
+    y0 = torch.zeros(N, K, *sp, device="cuda")
+    y1 = torch.full((N, K, *sp), 7.0, device="cuda")
+    p = Plan(x, w, y0, [1] * 3, [1] * 3, [1] * 3, _abi.MATH_FP32)
+    p.fwd(1.0, x, w, 0.0, y0)
+    sums = torch.zeros(K, device="cuda")
+    sq = torch.zeros(K, device="cuda")
+    st = _abi.lib().dcb_conv_fwd_stats(p.p, 1.0, ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(w.data_ptr()),
+                                       ctypes.c_void_p(y1.data_ptr()), ctypes.c_void_p(sums.data_ptr()),
+                                       ctypes.c_void_p(sq.data_ptr()), None)
+    assert st == _abi.OK, st
+    torch.cuda.synchronize()
+    assert _abi.lib().dcb_conv_plan_status(p.p, None) == _abi.OK
+    emu.assert_close(y1.cpu().numpy(), y0.cpu().numpy(), 2e-6, "y with statistics")
+    ref = y0.double()
+    emu.assert_close(sums.cpu().numpy(), ref.sum(dim=(0, 2, 3, 4)).cpu().numpy(), 1e-5, "sums")
+    emu.assert_close(sq.cpu().numpy(), (ref * ref).sum(dim=(0, 2, 3, 4)).cpu().numpy(), 1e-5, "sqsums")
+
+
+def test_fused_statistics_unsupported_for_2d():
+    x = torch.zeros(1, 4, 16, 32, device="cuda")
+    w = torch.zeros(8, 4, 3, 3, device="cuda")
+    y = torch.zeros(1, 8, 16, 32, device="cuda")
+    p = Plan(x, w, y, [1, 1], [1, 1], [1, 1], _abi.MATH_FP32)
+    s = torch.zeros(8, device="cuda")
+    st = _abi.lib().dcb_conv_fwd_stats(p.p, 1.0, ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(w.data_ptr()),
+                                       ctypes.c_void_p(y.data_ptr()), ctypes.c_void_p(s.data_ptr()),
+                                       ctypes.c_void_p(s.data_ptr()), None)
+    assert st == _abi.UNSUPPORTED
