@@ -170,21 +170,36 @@ bool sw_geom(const ConvGeom& cg, int math_mode, SwGeom* out)
             return false;
     }
     g.n = cg.n;
-    g.c = cg.c;
     g.k = cg.k;
     g.xs_n = cg.xs_n;
     g.xs_c = cg.xs_c;
     g.ys_n = cg.ys_n;
     g.ys_c = cg.ys_c;
-    if (g.f[0] < 2 || g.f[0] > 4 || g.k > SW_NBK || g.c > 16)
+    if (g.f[0] < 2 || g.f[0] > 4 || g.k > SW_NBK)
         return false;
+    // Three A slots of at most 53 k-rows each fit beside the accumulators: with
+    // more input channels than that allows, the channels are taken in equal
+    // groups, one launch per group, each adding into the output of the one
+    // before (the sum over input channels is what a convolution is).
+    g.split = math_mode == DCB_MATH_TF32 ? 0 : 1;
+    g.w_c_total = cg.c;
+    g.c = 0;
+    for (int cgp = cg.c; cgp >= 1; --cgp)
+        if (cg.c % cgp == 0 && 3 * ((cgp * g.f[2] * (g.split ? 3 : 1) + 7) / 8 * 8) <= 160)
+        {
+            g.c = cgp;
+            break;
+        }
+    if (g.c == 0 || cg.c / g.c > 8)
+        return false;
+    g.cgroups = cg.c / g.c;
+    g.w_c_off = 0;
     if ((long long) cg.n * cg.out[0] * cg.out[1] * cg.out[2] == 0)
         return false;
     if (g.pad[2] > 4 || g.f[2] - 1 - g.pad[2] > 4)
         return false;
     if (!(cg.xs[1] % 4 == 0 && cg.xs[0] % 4 == 0 && cg.xs_c % 4 == 0 && cg.xs_n % 4 == 0))
         return false;
-    g.split = math_mode == DCB_MATH_TF32 ? 0 : 1;
     g.ntot = g.f[1] * g.f[0] * SW_NBK;
     if (g.ntot > 256 || (g.f[0] * SW_NBK) % 16)
         return false;
@@ -504,11 +519,14 @@ static int32_t sw_launch(const SwGeom& g, float alpha, const float* w, const flo
                                                             stat_part);
         return DCB_OK;
     };
+    const bool blend = beta != 0.f;
     int32_t st;
     if (c4f3)
-        st = stats ? launch(sw_conv_kernel<true, true>) : launch(sw_conv_kernel<true, false>);
+        st = stats ? launch(sw_conv_kernel<true, true, false>)
+                   : (blend ? launch(sw_conv_kernel<true, false, true>) : launch(sw_conv_kernel<true, false, false>));
     else
-        st = stats ? launch(sw_conv_kernel<false, true>) : launch(sw_conv_kernel<false, false>);
+        st = stats ? launch(sw_conv_kernel<false, true, false>)
+                   : (blend ? launch(sw_conv_kernel<false, false, true>) : launch(sw_conv_kernel<false, false, false>));
     if (st != DCB_OK)
         return st;
     DCB_LAUNCH_CHECK();
@@ -528,10 +546,26 @@ int32_t tc_conv_fwd(TcPlan* p, int slot, float alpha, const float* x, const floa
         return DCB_UNSUPPORTED;
     if (p->has_sw[slot])
     {
-        CUtensorMap map;
-        std::memset(&map, 0, sizeof(map));
-        if (sw_make_x_map(p->sw[slot], x, &map))
-            return sw_launch(p->sw[slot], alpha, w, x, p->sw_bimg[slot], beta, y, p->status, map, stream);
+        SwGeom sg = p->sw[slot];
+        CUtensorMap maps[8];
+        bool ok = true;
+        for (int grp = 0; grp < sg.cgroups && ok; ++grp)
+        {
+            std::memset(&maps[grp], 0, sizeof(CUtensorMap));
+            ok = sw_make_x_map(sg, x + (size_t) grp * sg.c * sg.xs_c, &maps[grp]);
+        }
+        if (ok)
+        {
+            for (int grp = 0; grp < sg.cgroups; ++grp)
+            {
+                sg.w_c_off = grp * sg.c;
+                const int32_t st = sw_launch(sg, alpha, w, x + (size_t) grp * sg.c * sg.xs_c, p->sw_bimg[slot],
+                                             grp == 0 ? beta : 1.f, y, p->status, maps[grp], stream);
+                if (st != DCB_OK)
+                    return st;
+            }
+            return DCB_OK;
+        }
     }
     const TcGeom& g = p->g[slot];
     const long long total = (long long) g.b_bytes / 4;
@@ -549,7 +583,7 @@ int32_t tc_conv_fwd(TcPlan* p, int slot, float alpha, const float* x, const floa
 int32_t tc_conv_fwd_stats(TcPlan* p, float alpha, const float* x, const float* w, float* y, float* sums,
                           float* sqsums, cudaStream_t stream)
 {
-    if (!p || !p->has_sw[0] || !p->stat_part)
+    if (!p || !p->has_sw[0] || !p->stat_part || p->sw[0].cgroups != 1)
         return DCB_UNSUPPORTED;
     CUtensorMap map;
     std::memset(&map, 0, sizeof(map));

@@ -54,7 +54,10 @@ constexpr int SW_NBK = 16; // accumulator columns per (output row, plane slot)
 
 struct SwGeom
 {
-    int n, c, k;
+    int n, c, k;    // c: input channels of one launch (a group of the filter's w_c_total)
+    int w_c_total;  // input channels of the filter
+    int w_c_off;    // first input channel of this launch's group
+    int cgroups;    // launches per convolution = w_c_total / c
     int in[3], out[3], f[3], pad[3];
     long long xs_n, xs_c, xs[3];
     long long ys_n, ys_c, ys[3];
@@ -140,7 +143,7 @@ __global__ void sw_pack_filter_kernel(const float* __restrict__ w, float* __rest
         float val = 0.f;
         if (ko < g.k && part < (g.split ? 3 : 1))
         {
-            const float wv = w[((((size_t) ko * g.c + c) * fd + kd) * fh + kh) * fw + kw];
+            const float wv = w[((((size_t) ko * g.w_c_total + g.w_c_off + c) * fd + kd) * fh + kh) * fw + kw];
             const float hi = __uint_as_float(tf32_rna(wv));
             val = part < 2 ? hi : __uint_as_float(tf32_rna(wv - hi));
         }
@@ -231,7 +234,8 @@ __device__ __forceinline__ void sw_convert_c4f3(uint32_t raw_lane, uint32_t pitc
 // lane keeps its own fp32 sums, every epilogue warp leaves 32 partials in
 // `stat_part` at the end, and sw_stats_fold_kernel adds those in a fixed order
 // in fp64.
-template <bool C4F3, bool STATS>
+// BLEND: beta != 0, the old output is fetched early and blended in (plain stores).
+template <bool C4F3, bool STATS, bool BLEND>
 __global__ void __launch_bounds__(TC_THREADS, 1)
     sw_conv_kernel(SwGeom g, float alpha, float beta, const float* __restrict__ bimg, float* y, int* status,
                    const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap ymap, int use_ymap,
@@ -536,7 +540,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         const int nk = g.k;
         const size_t ysc = (size_t) g.ys_c;
         // bulk stores overwrite: the blend with the old output takes the plain path
-        const bool bulk = use_ymap != 0 && beta == 0.f;
+        const bool bulk = !BLEND && use_ymap != 0;
         float* stage = stage_base + (warp - TC_TMA_WARP - 1) * (2 * SW_NBK * 32);
         uint32_t nstored = 0;
         uint64_t s1[STATS ? SW_NBK / 2 : 1], s2[STATS ? SW_NBK / 2 : 1]; // packed pairs of filters
@@ -568,14 +572,25 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                 const uint32_t slot_col = (uint32_t) (sw_mod(od, fd) * SW_NBK);
                 for (int j = half; j < g.th && ok; j += nhalf)
                 {
+                    const int oh = t.oh0 + j;
+                    const bool wr = store && oh < g.out[1];
+                    // a blend with the old output: fetch it while the row is still in the works
+                    float old[BLEND ? SW_NBK : 1];
+                    float* const yrow =
+                        y + (size_t) t.n * g.ys_n + (size_t) od * g.ys[0] + (size_t) oh * g.ys[1] + ow;
+                    if (BLEND && wr && ow < g.out[2])
+                    {
+#pragma unroll
+                        for (int k = 0; k < (BLEND ? SW_NBK : 1); ++k)
+                            if (k < nk)
+                                old[k] = yrow[(size_t) k * ysc];
+                    }
                     for (int i = j; i < j + fh && ok; ++i)
                         ok = mbar_wait(&row_done[i], par, abort_flag);
                     if (!ok)
                         break;
                     tc_fence_after();
                     const uint32_t addr = lane_addr + (uint32_t) (j * fd * SW_NBK) + slot_col;
-                    const int oh = t.oh0 + j;
-                    const bool wr = store && oh < g.out[1];
                     uint32_t v[16];
                     if (wr)
                     {
@@ -638,21 +653,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                     }
                     else if (ow < g.out[2])
                     {
-                        float* p = y + (size_t) t.n * g.ys_n + (size_t) od * g.ys[0] + (size_t) oh * g.ys[1] + ow;
-                        if (beta == 0.f)
-                        {
 #pragma unroll
-                            for (int k = 0; k < SW_NBK; ++k)
-                                if (k < nk)
-                                    p[(size_t) k * ysc] = alpha * __uint_as_float(v[k]);
-                        }
-                        else
-                        {
-#pragma unroll
-                            for (int k = 0; k < SW_NBK; ++k)
-                                if (k < nk)
-                                    p[(size_t) k * ysc] = alpha * __uint_as_float(v[k]) + beta * p[(size_t) k * ysc];
-                        }
+                        for (int k = 0; k < SW_NBK; ++k)
+                            if (k < nk)
+                                yrow[(size_t) k * ysc] =
+                                    BLEND ? alpha * __uint_as_float(v[k]) + beta * old[BLEND ? k : 0]
+                                          : alpha * __uint_as_float(v[k]);
                     }
                 }
             }
