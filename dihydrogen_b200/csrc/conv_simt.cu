@@ -380,6 +380,7 @@ static BfTiling bf_tiling(const ConvGeom& g)
     if (t.kg_per_block > kgroups)
         t.kg_per_block = kgroups;
     t.xrow_len = (BF_WT - 1) * g.stride[2] + (g.f[2] - 1) * g.dil[2] + 1;
+    t.xrow_len = (t.xrow_len + 3) / 4 * 4; // rows stay 16-byte aligned for the vector loop
     // Keep shared memory within the default 48 KiB.
     while (true)
     {
@@ -486,6 +487,37 @@ __global__ void __launch_bounds__(BF_THREADS)
             continue;
         const float* dyr = sdy + (size_t) kg * BF_KB * BF_WT;
         const float* xr = sx + ((size_t) cc * rows + row) * xrow_len;
+        if (g.stride[2] == 1 && g.dil[2] == 1 && FW <= 5)
+        {
+            // four outputs per step: one 16-byte load per filter of dy and two of
+            // the input row feed 4 * KB * FW FMAs (the scalar loop below is bound
+            // by its shared-memory loads).  dy is zero beyond wcount, so the
+            // whole tile can be walked.
+            for (int wv = 0; wv < BF_WT; wv += 4)
+            {
+                float4 dv[BF_KB];
+#pragma unroll
+                for (int i = 0; i < BF_KB; ++i)
+                    dv[i] = *reinterpret_cast<const float4*>(dyr + i * BF_WT + wv);
+                const float4 xa = *reinterpret_cast<const float4*>(xr + wv);
+                const float4 xb = wv + 4 < xrow_len ? *reinterpret_cast<const float4*>(xr + wv + 4)
+                                                    : make_float4(0.f, 0.f, 0.f, 0.f);
+                const float xv[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+#pragma unroll
+                for (int j = 0; j < FW; ++j)
+#pragma unroll
+                    for (int i = 0; i < BF_KB; ++i)
+                    {
+                        float a = acc[i][j];
+                        a = fmaf(dv[i].x, xv[j], a);
+                        a = fmaf(dv[i].y, xv[j + 1], a);
+                        a = fmaf(dv[i].z, xv[j + 2], a);
+                        a = fmaf(dv[i].w, xv[j + 3], a);
+                        acc[i][j] = a;
+                    }
+            }
+            continue;
+        }
         for (int wv = 0; wv < wcount; ++wv)
         {
             float dv[BF_KB];
