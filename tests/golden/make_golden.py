@@ -1,6 +1,6 @@
 """Generates the golden fixtures in this folder from the reference itself.
 
-Run in a container that has the reference tree (default /root/reference):
+Run where the DiHydrogen tree is available (the REFERENCE variable of oracle/Makefile):
 
     make -C oracle ref && python tests/golden/make_golden.py
 
