@@ -208,7 +208,21 @@ def run_ours(args):
     torch.cuda.set_device(local_rank)
     os.environ.setdefault("NCCL_DEBUG", "WARN")  # keep NCCL's version banner off stdout
     if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        # NCCL writes its version banner to stdout when the first communicator
+        # comes up; stdout carries the one JSON line, so point fd 1 at stderr
+        # until that has happened
+        sys.stdout.flush()
+        saved_stdout = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+            warm = torch.zeros(1, device="cuda")
+            dist.all_reduce(warm)
+            torch.cuda.synchronize()
+        finally:
+            sys.stdout.flush()
+            os.dup2(saved_stdout, 1)
+            os.close(saved_stdout)
         locale = dc.Locale.from_torch_distributed()
     else:
         locale = dc.Locale(0, 1)
