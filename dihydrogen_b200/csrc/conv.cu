@@ -247,10 +247,14 @@ int32_t dcb_conv_bwd_filter(dcb_conv_plan* p, double alpha, const void* x,
 {
     DCB_REQUIRE(p && x && dy && dw, "null argument");
     if (p->kind[2] == 1)
-        return tc_conv_bwd_filter(p->tc, (float) alpha,
-                                  static_cast<const float*>(x),
-                                  static_cast<const float*>(dy), (float) beta,
-                                  static_cast<float*>(dw), as_stream(stream));
+    {
+        const int32_t st = tc_conv_bwd_filter(
+            p->tc, (float) alpha, static_cast<const float*>(x),
+            static_cast<const float*>(dy), (float) beta,
+            static_cast<float*>(dw), as_stream(stream));
+        if (st != DCB_UNSUPPORTED) // unaligned base pointers take the kernel below
+            return st;
+    }
     return simt_conv_bwd_filter(p->g, (float) alpha,
                                 static_cast<const float*>(x),
                                 static_cast<const float*>(dy), (float) beta,

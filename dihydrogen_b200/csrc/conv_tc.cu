@@ -26,6 +26,7 @@
 #include "conv_tc.cuh"
 #include "conv_tc_kernel.cuh"
 #include "conv_tc_sweep.cuh"
+#include "conv_tc_wgrad.cuh"
 
 namespace dcb
 {
@@ -277,6 +278,60 @@ bool sw_geom(const ConvGeom& cg, int math_mode, SwGeom* out)
     return true;
 }
 
+size_t wg_smem_need(const WgGeom& g)
+{
+    const size_t unit = (size_t) (g.xbuf_bytes + g.dybuf_bytes + 127) / 128 * 128;
+    return 2 * unit + (size_t) WG_A_SLOTS * WG_B_FLOATS * 4 + (2 * WG_A_SLOTS + 5) * 8 + 64 + 1024;
+}
+
+// Geometry of the tensor-core backward filter: x is the forward input window,
+// dy the forward output window.
+bool wg_geom(const ConvGeom& cg, int math_mode, WgGeom* out)
+{
+    WgGeom g;
+    std::memset(&g, 0, sizeof(g));
+    if (math_mode == DCB_MATH_FP32_SIMT)
+        return false;
+    for (int i = 0; i < 3; ++i)
+    {
+        if (cg.stride[i] != 1 || cg.dil[i] != 1)
+            return false;
+        g.in[i] = cg.in[i];
+        g.out[i] = cg.out[i];
+        g.f[i] = cg.f[i];
+        g.pad[i] = cg.pad[i];
+        if (g.pad[i] > g.f[i] - 1)
+            return false;
+    }
+    g.n = cg.n;
+    g.c = cg.c;
+    g.k = cg.k;
+    g.mrows = g.c * g.f[0] * g.f[1] * g.f[2];
+    if (g.mrows > 128 || g.k > 16 || g.mrows == 0)
+        return false;
+    if ((long long) cg.n * cg.out[0] * cg.out[1] * cg.out[2] == 0)
+        return false;
+    if (g.pad[2] > 4 || g.f[2] - 1 - g.pad[2] > 4 || g.f[1] > 16)
+        return false;
+    // bulk-copy compatible strides on both tensors (bases are checked per call)
+    if (!(cg.xs[1] % 4 == 0 && cg.xs[0] % 4 == 0 && cg.xs_c % 4 == 0 && cg.xs_n % 4 == 0))
+        return false;
+    if (!(cg.ys[1] % 4 == 0 && cg.ys[0] % 4 == 0 && cg.ys_c % 4 == 0 && cg.ys_n % 4 == 0))
+        return false;
+    g.xplane_bytes = g.c * g.f[1] * WG_XW * 4;
+    g.xplane_floats = (g.xplane_bytes + 127) / 128 * 128 / 4;
+    g.xbuf_bytes = g.f[0] * g.xplane_floats * 4;
+    g.dybuf_bytes = 16 * WG_TW * 4;
+    if (wg_smem_need(g) > 200 * 1024)
+        return false;
+    g.tiles_w = (g.out[2] + WG_TW - 1) / WG_TW;
+    g.units = (long long) g.n * g.out[0] * g.out[1] * g.tiles_w;
+    if (g.units >= (1ll << 31))
+        return false;
+    *out = g;
+    return true;
+}
+
 size_t tc_smem_bytes(const TcGeom& g)
 {
     // At least 120 KiB so that a second CTA can never share the SM: the
@@ -297,6 +352,11 @@ struct TcPlan
     SwGeom sw[2];
     float* sw_bimg[2] = {nullptr, nullptr};
     float* stat_part = nullptr; // per epilogue warp partial sums of the fused statistics
+    // tensor-core backward filter
+    bool has_wg = false;
+    WgGeom wg;
+    ConvGeom wg_cg;             // strides of x and dy for the tensor maps
+    float* wg_part = nullptr;   // one 128 x 16 partial filter per CTA
     int* status = nullptr;
 };
 
@@ -310,7 +370,9 @@ int32_t tc_plan_create(const ConvGeom& fwd, const ConvGeom& bwd, bool bwd_is_fwd
     // is not 16-byte aligned, so it is only planned on top of it
     p->has_sw[0] = p->has[0] && sw_geom(fwd, math_mode, &p->sw[0]);
     p->has_sw[1] = p->has[1] && sw_geom(bwd, math_mode, &p->sw[1]);
-    if (!p->has[0] && !p->has[1])
+    p->has_wg = wg_geom(fwd, math_mode, &p->wg);
+    p->wg_cg = fwd;
+    if (!p->has[0] && !p->has[1] && !p->has_wg)
     {
         delete p;
         return DCB_OK;
@@ -324,6 +386,8 @@ int32_t tc_plan_create(const ConvGeom& fwd, const ConvGeom& bwd, bool bwd_is_fwd
         if (ok && p->has_sw[s])
             ok = cudaMalloc(&p->sw_bimg[s], p->sw[s].b_bytes) == cudaSuccess;
     }
+    if (ok && p->has_wg)
+        ok = cudaMalloc(&p->wg_part, (size_t) num_sms() * 128 * 16 * sizeof(float)) == cudaSuccess;
     if (ok && p->has_sw[0])
         ok = cudaMalloc(&p->stat_part, (size_t) num_sms() * TC_EPI_WARPS * 32 * sizeof(float)) == cudaSuccess;
     if (!ok)
@@ -346,6 +410,7 @@ void tc_plan_destroy(TcPlan* p)
     cudaFree(p->sw_bimg[0]);
     cudaFree(p->sw_bimg[1]);
     cudaFree(p->stat_part);
+    cudaFree(p->wg_part);
     cudaFree(p->status);
     delete p;
 }
@@ -363,7 +428,7 @@ bool tc_supports(const TcPlan* p, int which)
         return p->has[0];
     if (which == 1)
         return p->has[1];
-    return false;
+    return p->has_wg;
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -592,9 +657,56 @@ int32_t tc_conv_fwd_stats(TcPlan* p, float alpha, const float* x, const float* w
     return sw_launch(p->sw[0], alpha, w, x, p->sw_bimg[0], 0.f, y, p->status, map, stream, p->stat_part, sums, sqsums);
 }
 
-int32_t tc_conv_bwd_filter(TcPlan*, float, const float*, const float*, float, float*, cudaStream_t)
+// 5-D map (W, H, D, channels, N) of a strided window with the given box.
+static bool wg_make_map(const float* base, const int ext[3], int channels, int n, const long long sp[3],
+                        long long s_c, long long s_n, int box_w, int box_h, int box_c, CUtensorMap* map)
 {
-    return DCB_UNSUPPORTED;
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn || (reinterpret_cast<uintptr_t>(base) & 15) != 0)
+        return false;
+    const cuuint64_t dims[5] = {(cuuint64_t) ext[2], (cuuint64_t) ext[1], (cuuint64_t) ext[0], (cuuint64_t) channels,
+                                (cuuint64_t) n};
+    const long long s1 = ext[1] > 1 ? sp[1] : ext[2];
+    const long long s0 = ext[0] > 1 ? sp[0] : s1 * ext[1];
+    const long long sc = channels > 1 ? s_c : s0 * ext[0];
+    const long long sn = n > 1 ? s_n : sc * channels;
+    const cuuint64_t strides[4] = {(cuuint64_t) s1 * 4, (cuuint64_t) s0 * 4, (cuuint64_t) sc * 4, (cuuint64_t) sn * 4};
+    for (int i = 0; i < 4; ++i)
+        if (strides[i] % 16 != 0 || strides[i] == 0)
+            return false;
+    const cuuint32_t box[5] = {(cuuint32_t) box_w, (cuuint32_t) box_h, 1, (cuuint32_t) box_c, 1};
+    const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 5, const_cast<float*>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE)
+           == CUDA_SUCCESS;
+}
+
+int32_t tc_conv_bwd_filter(TcPlan* p, float alpha, const float* x, const float* dy, float beta, float* dw,
+                           cudaStream_t stream)
+{
+    if (!p || !p->has_wg)
+        return DCB_UNSUPPORTED;
+    const WgGeom& g = p->wg;
+    const ConvGeom& cg = p->wg_cg;
+    CUtensorMap xmap, dymap;
+    std::memset(&xmap, 0, sizeof(xmap));
+    std::memset(&dymap, 0, sizeof(dymap));
+    if (!wg_make_map(x, cg.in, cg.c, cg.n, cg.xs, cg.xs_c, cg.xs_n, WG_XW, g.f[1], g.c, &xmap)
+        || !wg_make_map(dy, cg.out, cg.k, cg.n, cg.ys, cg.ys_c, cg.ys_n, WG_TW, 1, 16, &dymap))
+        return DCB_UNSUPPORTED; // the caller falls back to the CUDA-core kernel
+    size_t smem = wg_smem_need(g);
+    smem = smem < 120 * 1024 ? 120 * 1024 : smem; // one CTA per SM
+    long long grid = (long long) num_sms();
+    if (grid > g.units)
+        grid = g.units;
+    DCB_CUDA_TRY(cudaFuncSetAttribute(wg_conv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) (224 * 1024)));
+    wg_conv_kernel<<<(unsigned) grid, WG_THREADS, smem, stream>>>(g, p->wg_part, p->status, xmap, dymap);
+    DCB_LAUNCH_CHECK();
+    const int total = g.mrows * g.k;
+    wg_fold_kernel<<<(total + 255) / 256, 256, 0, stream>>>(p->wg_part, (int) grid, g.mrows, g.k, alpha, beta, dw);
+    DCB_LAUNCH_CHECK();
+    return DCB_OK;
 }
 
 } // namespace dcb

@@ -1,0 +1,368 @@
+// tcgen05 / TMEM backward filter (stride 1, dilation 1, c*fd*fh*fw <= 128 filter
+// taps per output filter, K <= 16):
+//
+//   dw[k][c][kd][kh][kw] = sum over (n, od, oh, ow) dy[n][k][od][oh][ow] *
+//                          x[n][c][od+kd-pd][oh+kh-ph][ow+kw-pw]
+//
+// GEMM view: the reduction runs over the outputs, eight consecutive ow per
+// MMA (the K of a TF32 instruction).  M = the (c, kd, kh, kw) taps (up to 128
+// rows = TMEM lanes), N = the filters.  For one chunk of eight outputs
+//   A[m][kk] = x[c][od+kd-pd][oh+kh-ph][ow0 + kk + kw-pw]     (tensor memory)
+//   B[kk][k] = dy[k][od][oh][ow0 + kk]                        (shared memory)
+// and the accumulator D[m][k] stays in tensor memory for the whole kernel:
+// there is no epilogue until the CTA has walked all its units, then every CTA
+// writes its 128 x 16 partial filter and a second kernel folds the partials in
+// CTA order (fp64) and applies alpha / beta.
+//
+// 3xTF32: D[:, 0:32] += A_hi x [B_hi | B_lo] (one instruction, N = 32) and
+// D[:, 0:16] += A_lo x B_hi (N = 16); the fold adds the two column halves.
+//
+// A unit is 128 outputs of one output row: 16 chunks.  Warp 15 copies the
+// fd * fh input rows (all channels, 4 cells of margin left and right, zeros
+// outside the tensor = the padding) and the dy row (all filters) of the next
+// unit into a two-deep shared-memory ring with bulk tensor copies.  Warps 0..11
+// are three converter groups: group g takes every third chunk, lane m of its
+// four warps writes row m of A (hi and lo parts) into the group's A slot and the
+// group writes the chunk's B tile; warps 12..14 issue, issuer g for group g.
+// All waits are bounded.
+#pragma once
+
+#include "conv_tc_kernel.cuh"
+
+namespace dcb
+{
+namespace
+{
+
+constexpr int WG_THREADS = 20 * 32; // 12 converters, 3 issuers, 1 copy, 4 dump warps
+constexpr int WG_COPY_WARP = 15;
+constexpr int WG_DUMP_WARP = 16;
+constexpr int WG_TW = 128;                 // outputs per unit
+constexpr int WG_CHUNKS = WG_TW / 8;       // chunks per unit
+constexpr int WG_XW = WG_TW + 8;           // staged input row: 4 cells of margin each side
+constexpr int WG_A_SLOTS = 6;              // two per group
+constexpr uint32_t WG_TMEM_COLS = 128;     // 32 accumulator columns + 6 x 16 A columns
+constexpr int WG_B_FLOATS = 256;           // one B tile: 8 x 32 floats
+
+struct WgGeom
+{
+    int n, c, k;
+    int in[3], out[3], f[3], pad[3];
+    int mrows;              // c * fd * fh * fw
+    int tiles_w;
+    long long units;        // n * out_d * out_h * tiles_w
+    int xplane_floats;      // pitch of one filter plane of a unit: c * fh * WG_XW floats rounded up to
+                            // 128 bytes (a bulk copy's destination must be 128-byte aligned)
+    int xplane_bytes;       // bytes one plane's copy brings: c * fh * WG_XW * 4
+    int xbuf_bytes;         // fd plane pitches
+    int dybuf_bytes;        // 16 x WG_TW floats
+};
+
+__global__ void wg_fold_kernel(const float* __restrict__ part, int nparts, int mrows, int k, float alpha, float beta,
+                               float* dw)
+{
+    const int i = blockIdx.x * blockDim.x + threadIdx.x; // (filter, tap row)
+    if (i >= mrows * k)
+        return;
+    const int kk = i / mrows, m = i % mrows;
+    double s = 0.0;
+    for (int p = 0; p < nparts; ++p)
+        s += (double) part[((size_t) p * 128 + m) * 16 + kk];
+    const float prev = beta != 0.f ? dw[i] : 0.f;
+    dw[i] = alpha * (float) s + beta * prev;
+}
+
+__global__ void __launch_bounds__(WG_THREADS, 1)
+    wg_conv_kernel(WgGeom g, float* __restrict__ part, int* status, const __grid_constant__ CUtensorMap xmap,
+                   const __grid_constant__ CUtensorMap dymap)
+{
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int unit_bytes = (g.xbuf_bytes + g.dybuf_bytes + 127) / 128 * 128;
+    uint8_t* ubuf = smem;                                        // [2] unit buffers: x planes, then the dy row
+    float* bring = reinterpret_cast<float*>(smem + 2 * unit_bytes); // [WG_A_SLOTS] B tiles
+    uint64_t* bars = reinterpret_cast<uint64_t*>(bring + WG_A_SLOTS * WG_B_FLOATS);
+    uint64_t* a_full = bars;                 // [6]
+    uint64_t* a_empty = a_full + WG_A_SLOTS; // [6]
+    uint64_t* u_full = a_empty + WG_A_SLOTS; // [2]
+    uint64_t* u_empty = u_full + 2;          // [2]
+    uint64_t* all_done = u_empty + 2;        // [1]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(all_done + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0)
+    {
+        for (int s = 0; s < WG_A_SLOTS; ++s)
+        {
+            mbar_init(&a_full[s], 4);
+            mbar_init(&a_empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b)
+        {
+            mbar_init(&u_full[b], 1);
+            mbar_init(&u_empty[b], 12);
+        }
+        mbar_init(all_done, 3);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == TC_MMA_WARP)
+    {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(WG_TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    // zero the accumulators (the dump warps own all four lane quadrants)
+    if (warp >= WG_DUMP_WARP)
+    {
+        const uint32_t la = tmem_base + ((uint32_t) ((warp & 3) * 32) << 16);
+        tmem_st16_zero(la);
+        tmem_st16_zero(la + 16);
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+
+    const uint32_t nunits = (uint32_t) g.units;
+    bool ok = true;
+
+    if (warp < 12)
+    {
+        // ------------------------------------------------------------------
+        // converters
+        // ------------------------------------------------------------------
+        const int gq = warp >> 2, quad = warp & 3;
+        const int m = quad * 32 + lane;
+        const uint32_t lane_addr = tmem_base + ((uint32_t) (quad * 32) << 16);
+        // where this lane's tap sits in a unit buffer (floats)
+        int src = -1;
+        if (m < g.mrows)
+        {
+            const int kw = m % g.f[2];
+            int r = m / g.f[2];
+            const int kh = r % g.f[1];
+            r /= g.f[1];
+            const int kd = r % g.f[0];
+            const int c = r / g.f[0];
+            src = kd * g.xplane_floats + (c * g.f[1] + kh) * WG_XW + 4 - g.pad[2] + kw;
+        }
+        // this lane's element of the B tile: filter quad*4 + lane/8, output lane%8
+        const int bk = quad * 4 + (lane >> 3), bkk = lane & 7;
+        const int b_off = (bkk >> 2) * 128 + (bk >> 3) * 32 + (bk & 7) * 4 + (bkk & 3); // + 64 for the lo half
+        int lap = 0;
+        uint32_t a_phase = 1, seq = 0;
+        bool a_first = true;
+        uint32_t ul = 0; // units done by this CTA
+        for (uint32_t u = blockIdx.x; u < nunits && ok; u += gridDim.x, ++ul)
+        {
+            const uint32_t b = ul & 1;
+            ok = mbar_wait(&u_full[b], (ul >> 1) & 1, abort_flag);
+            if (!ok)
+                break;
+            const float* xb = reinterpret_cast<const float*>(ubuf + (size_t) b * unit_bytes);
+            const float* dyb = reinterpret_cast<const float*>(ubuf + (size_t) b * unit_bytes + g.xbuf_bytes);
+            // chunks are dealt to the groups in sequence over the whole run
+            int q = (gq + 3 - (int) (seq % 3u)) % 3;
+            for (; q < WG_CHUNKS && ok; q += 3)
+            {
+                const int slot = gq + 3 * lap;
+                uint32_t hi[8], lo[8];
+                if (src >= 0)
+                {
+                    const uint32_t s0 = smem_u32(xb + src + q * 8);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e)
+                    {
+                        const float xe = __uint_as_float(lds_u32(s0 + 4u * e));
+                        hi[e] = tf32_rna(xe);
+                        lo[e] = tf32_rna(xe - __uint_as_float(hi[e]));
+                    }
+                }
+                else
+                {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e)
+                        hi[e] = lo[e] = 0u;
+                }
+                const float dv = dyb[bk * WG_TW + q * 8 + bkk];
+                const uint32_t dhi = tf32_rna(dv);
+                const uint32_t dlo = tf32_rna(dv - __uint_as_float(dhi));
+                if (!a_first)
+                    ok = mbar_wait(&a_empty[slot], a_phase, abort_flag);
+                if (!ok)
+                    break;
+                tc_fence_after();
+                const uint32_t a_addr = lane_addr + 32u + (uint32_t) (slot * 16);
+                tmem_st8(a_addr, hi);
+                tmem_st8(a_addr + 8, lo);
+                float* bt = bring + slot * WG_B_FLOATS;
+                bt[b_off] = __uint_as_float(dhi);
+                bt[b_off + 64] = __uint_as_float(dlo);
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0)
+                    mbar_arrive(&a_full[slot]);
+                if (++lap == 2)
+                {
+                    lap = 0;
+                    a_phase ^= 1;
+                    a_first = false;
+                }
+            }
+            seq += WG_CHUNKS;
+            __syncwarp();
+            if (lane == 0)
+                mbar_arrive(&u_empty[b]);
+        }
+    }
+    else if (warp == WG_COPY_WARP)
+    {
+        // ------------------------------------------------------------------
+        // bulk tensor copies, one unit ahead
+        // ------------------------------------------------------------------
+        const uint32_t bytes = (uint32_t) (g.f[0] * g.xplane_bytes + g.dybuf_bytes);
+        uint32_t ul = 0;
+        for (uint32_t u = blockIdx.x; u < nunits && ok; u += gridDim.x, ++ul)
+        {
+            const uint32_t b = ul & 1;
+            if (ul >= 2)
+                ok = mbar_wait(&u_empty[b], ((ul >> 1) + 1) & 1, abort_flag);
+            if (!ok)
+                break;
+            if (lane == 0)
+            {
+                const uint32_t tw = u % (uint32_t) g.tiles_w;
+                uint32_t r = u / (uint32_t) g.tiles_w;
+                const int oh = (int) (r % (uint32_t) g.out[1]);
+                r /= (uint32_t) g.out[1];
+                const int od = (int) (r % (uint32_t) g.out[0]);
+                const int n = (int) (r / (uint32_t) g.out[0]);
+                const int ow0 = (int) tw * WG_TW;
+                uint8_t* dst = ubuf + (size_t) b * unit_bytes;
+                mbar_expect_tx(&u_full[b], bytes);
+                for (int kd = 0; kd < g.f[0]; ++kd)
+                    tma_load_5d(dst + (size_t) kd * g.xplane_floats * 4, &xmap, ow0 - 4, oh - g.pad[1],
+                                od - g.pad[0] + kd, 0, n, &u_full[b]);
+                tma_load_5d(dst + g.xbuf_bytes, &dymap, ow0, oh, od, 0, n, &u_full[b]);
+            }
+            __syncwarp();
+        }
+    }
+    else if (warp >= TC_MMA_WARP && warp < TC_MMA_WARP + 3)
+    {
+        // ------------------------------------------------------------------
+        // MMA issue
+        // ------------------------------------------------------------------
+        const int mq = warp - TC_MMA_WARP;
+        // fp32 accumulate, tf32 x tf32, A K-major (tensor memory), B K-major, M = 128
+        const uint32_t idesc32 = (1u << 4) | (2u << 7) | (2u << 10) | ((128u >> 4) << 24) | ((32u >> 3) << 17);
+        const uint32_t idesc16 = (1u << 4) | (2u << 7) | (2u << 10) | ((128u >> 4) << 24) | ((16u >> 3) << 17);
+        int lap = 0;
+        uint32_t full_phase = 0, seq = 0;
+        for (uint32_t u = blockIdx.x; u < nunits && ok; u += gridDim.x)
+        {
+            int q = (mq + 3 - (int) (seq % 3u)) % 3;
+            for (; q < WG_CHUNKS && ok; q += 3)
+            {
+                const int slot = mq + 3 * lap;
+                ok = mbar_wait_t<0>(&a_full[slot], full_phase, abort_flag);
+                if (!ok)
+                    break;
+                tc_fence_after();
+                if (lane == 0)
+                {
+                    const uint32_t a_addr = tmem_base + 32u + (uint32_t) (slot * 16);
+                    // B tile: [2 k-chunks][4 filter groups][8][4]: 512 bytes between the
+                    // k-chunks, 128 between the filter groups
+                    const uint64_t bd = make_desc(smem_u32(bring + slot * WG_B_FLOATS), 512u, 128u, 0u);
+                    mma_tf32_ts(tmem_base, a_addr, bd, idesc32);     // A_hi x [B_hi | B_lo]
+                    mma_tf32_ts(tmem_base, a_addr + 8, bd, idesc16); // A_lo x B_hi
+                    mma_commit(&a_empty[slot]);
+                    tc_fence_before();
+                }
+                __syncwarp();
+                if (++lap == 2)
+                {
+                    lap = 0;
+                    full_phase ^= 1;
+                }
+            }
+            seq += WG_CHUNKS;
+        }
+        // everything this issuer sent has completed when this arrives
+        if (lane == 0)
+        {
+            tc_fence_after();
+            mma_commit(all_done);
+        }
+        __syncwarp();
+    }
+    else if (warp >= WG_DUMP_WARP)
+    {
+        // ------------------------------------------------------------------
+        // the CTA's partial filter: D[:, 0:16] + D[:, 16:32]
+        // ------------------------------------------------------------------
+        // This wait spans the whole run, so it has no clock budget of its own:
+        // it ends when the issuers are done or when any role has given up (every
+        // other wait is bounded and raises the abort flag), and after at most
+        // 2^26 polls.
+        ok = false;
+        for (uint32_t it = 0; it < (1u << 26); ++it)
+        {
+            uint32_t done;
+            asm volatile(
+                "{\n\t"
+                ".reg .pred p;\n\t"
+                "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                "selp.b32 %0, 1, 0, p;\n\t"
+                "}"
+                : "=r"(done)
+                : "r"(smem_u32(all_done)), "r"(0u)
+                : "memory");
+            if (done)
+            {
+                ok = true;
+                break;
+            }
+            if (*abort_flag)
+                break;
+            __nanosleep(1000);
+        }
+        if (ok)
+        {
+            tc_fence_after();
+            const int quad = warp & 3;
+            const uint32_t la = tmem_base + ((uint32_t) (quad * 32) << 16);
+            uint32_t v0[16], v1[16];
+            tmem_ld16(la, v0);
+            tmem_ld16(la + 16, v1);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            float* o = part + ((size_t) blockIdx.x * 128 + quad * 32 + lane) * 16;
+#pragma unroll
+            for (int k = 0; k < 16; ++k)
+                o[k] = __uint_as_float(v0[k]) + __uint_as_float(v1[k]);
+        }
+    }
+
+    if (!ok && lane == 0)
+        atomicExch(status, 1);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == TC_MMA_WARP)
+    {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(WG_TMEM_COLS)
+                     : "memory");
+    }
+}
+
+} // namespace
+} // namespace dcb

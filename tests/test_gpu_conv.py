@@ -205,3 +205,31 @@ def test_fused_statistics_unsupported_for_2d():
                                        ctypes.c_void_p(y.data_ptr()), ctypes.c_void_p(s.data_ptr()),
                                        ctypes.c_void_p(s.data_ptr()), None)
     assert st == _abi.UNSUPPORTED
+
+
+def test_tensor_core_kernels_are_the_ones_running():
+    """For the bench layer's shape family all three passes resolve to tcgen05
+    kernels; a plan whose tap count does not fit the backward-filter kernel
+    (C * taps > 128) keeps the fp32 one for that pass."""
+    x = torch.zeros(1, 4, 8, 16, 128, device="cuda")
+    w = torch.zeros(16, 4, 3, 3, 3, device="cuda")
+    y = torch.zeros(1, 16, 8, 16, 128, device="cuda")
+    p = Plan(x, w, y, [1] * 3, [1] * 3, [1] * 3, _abi.MATH_FP32)
+    assert [_abi.lib().dcb_conv_plan_kernel_kind(p.p, i) for i in range(3)] == [1, 1, 1]
+    x2 = torch.zeros(1, 8, 8, 16, 128, device="cuda")
+    w2 = torch.zeros(16, 8, 3, 3, 3, device="cuda")
+    p2 = Plan(x2, w2, y, [1] * 3, [1] * 3, [1] * 3, _abi.MATH_FP32)
+    assert _abi.lib().dcb_conv_plan_kernel_kind(p2.p, 2) == 0
+
+
+def test_backward_filter_tensor_core_ragged_tiles_and_batch():
+    """Several W tiles with a ragged last one, N > 1, alpha / beta blend."""
+    N, C, K, sp, f = 2, 4, 13, (5, 7, 268), (3, 3, 3)
+    rng = np.random.default_rng(77)
+    x = rng.normal(size=(N, C, *sp)).astype(np.float32)
+    w = rng.normal(0, 0.1, (K, C, *f)).astype(np.float32)
+    dy = rng.normal(size=(N, K, *sp)).astype(np.float32)
+    dw0 = rng.normal(size=w.shape).astype(np.float32)
+    _, _, dw = run_all(x, w, dy, [1] * 3, [1] * 3, [1] * 3, _abi.MATH_FP32, alpha=0.5, beta=2.0,
+                       y0=np.zeros(dy.shape, np.float32), dx0=np.zeros(x.shape, np.float32), dw0=dw0)
+    emu.assert_close(dw, O.conv_bwd_filter(x, dy, f, [1] * 3, [1] * 3, alpha=0.5, beta=2.0, dw=dw0.copy()), TOL, "dw")
