@@ -851,6 +851,34 @@ public:
                     "conv forward");
         return 0;
     }
+    // Forward pass (beta = 0) that also leaves, per filter, the sum and the sum
+    // of squares of this rank's output in sums / sqsums (K device floats
+    // each): what BatchNormalization::forward_stage1 would compute from
+    // `output`.  Returns 1 when the convolution's epilogue produced them, 0
+    // when the plain forward pass ran and stage 1 is still to do.  No
+    // counterpart in the reference, which always runs the two passes.
+    int forward_with_statistics(float alpha, TensorF& input, const float* filter, TensorF& output, float* sums,
+                                float* sqsums, bool skip_halo_exchange = false)
+    {
+        if (input.get_local_size() == 0 || output.get_local_size() == 0)
+            return 0;
+        if (!skip_halo_exchange)
+        {
+            clear_halos(input);
+            forward_exchange_halo(input);
+        }
+        if (input.is_split_root())
+        {
+            const int32_t st = dcb_conv_fwd_stats(m_plan_fwd, alpha, input.nd_ptr(m_x_lo), filter,
+                                                  output.get_base_ptr(), sums, sqsums, m_be.get_stream());
+            if (st == DCB_OK)
+                return 1;
+            if (st != DCB_UNSUPPORTED)
+                util::check(st, "conv forward with statistics");
+        }
+        forward(alpha, input, filter, 0.f, output, /*skip_halo_exchange=*/true);
+        return 0;
+    }
     // convolution.hpp:682-876
     int backward_data(float alpha, const float* filter, TensorF& d_output, float beta, TensorF& d_input,
                       bool skip_halo_exchange = false)
@@ -1020,10 +1048,14 @@ public:
                     "bn apply");
         return 0;
     }
+    // statistics_ready: mean / var already hold this rank's sums and sums of
+    // squares (Convolution::forward_with_statistics returned 1)
     int forward(TensorF& input, float* mean, float* var, float* running_mean, float* running_var,
-                const float* scale, const float* bias, TensorF& output, bool is_training = true)
+                const float* scale, const float* bias, TensorF& output, bool is_training = true,
+                bool statistics_ready = false)
     {
-        forward_stage1(input, mean, var, is_training);
+        if (!statistics_ready)
+            forward_stage1(input, mean, var, is_training);
         forward_allreduce(input, mean, var, is_training);
         return forward_stage2(input, mean, var, running_mean, running_var, scale, bias, output, is_training);
     }

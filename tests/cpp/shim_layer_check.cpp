@@ -246,8 +246,10 @@ void rank_main(int rank, int R, Shared* sh, const Global* g)
         x.clear_halo(2, st);
         phase([&] { conv.input_halo_exchange().pack_put(2, st); },
               [&] { conv.input_halo_exchange().wait_unpack(2, st); });
-        conv.forward(1.f, x, wt, 0.f, y, /*skip_halo_exchange=*/true);
-        bn.forward_stage1(y, stats, stats + K);
+        // the statistics come from the convolution's epilogue where its kernel has one
+        const int fused = conv.forward_with_statistics(1.f, x, w, y, stats, stats + K, /*skip_halo_exchange=*/true);
+        if (!fused)
+            bn.forward_stage1(y, stats, stats + K);
         phase([&] { be.allreduce_push(stats, 2 * K); }, [&] { be.allreduce_pull(stats, 2 * K); });
         bn.forward_stage2(y, stats, stats + K, stats + 2 * K, stats + 3 * K, stats + 4 * K, stats + 5 * K, z);
         // backward of the convolution
@@ -272,8 +274,8 @@ void rank_main(int rank, int R, Shared* sh, const Global* g)
             e_st = std::max(e_st, (double) std::fabs(hstats[K + k] - g->var[k]) / (1.0 + g->var[k]));
         }
         const double e_y = gather_err(y, g->y, K), e_dx = gather_err(dx, g->dx, C), e_z = gather_err(z, g->z, K);
-        std::printf("rank %d/%d: y %.2e  dx %.2e  dw %.2e  stats %.2e  bn %.2e  (fwd kernel kind %d)\n", rank, R,
-                    e_y, e_dx, e_dw, e_st, e_z, conv.kernel_kind(0));
+        std::printf("rank %d/%d: y %.2e  dx %.2e  dw %.2e  stats %.2e  bn %.2e  (fwd kernel kind %d, statistics %s)\n",
+                    rank, R, e_y, e_dx, e_dw, e_st, e_z, conv.kernel_kind(0), fused ? "fused" : "separate");
         const bool ok = e_y < 2e-5 && e_dx < 2e-5 && e_dw < 5e-5 && e_st < 2e-5 && e_z < 1e-4;
         if (!ok)
         {

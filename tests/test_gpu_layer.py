@@ -50,7 +50,7 @@ class Layer:
         emu.connect_halo([c.halo_xch_d_output for c in self.convs])
         self.out_shape = self.y[0].shape
 
-    def forward(self, gx, w, scale, bias):
+    def forward(self, gx, w, scale, bias, fused_stats=False):
         K = self.K
         self.w = torch.from_numpy(w).cuda()
         for x in self.x:
@@ -60,14 +60,17 @@ class Layer:
             for d in range(self.nd - 2):
                 x.clear_halo(d)
         emu.exchange_all([c.halo_xch_input for c in self.convs])
-        for c, x, y in zip(self.convs, self.x, self.y):
-            c.forward(1.0, x, self.w, 0.0, y, skip_halo_exchange=True)
         self.stats = [torch.zeros(2 * K, device="cuda") for _ in self.bes]
+        self.fused = []
+        for c, x, y, st in zip(self.convs, self.x, self.y, self.stats):
+            self.fused.append(c.forward(1.0, x, self.w, 0.0, y, skip_halo_exchange=True,
+                                        statistics=(st[:K], st[K:]) if fused_stats else None))
         self.rm = [torch.zeros(K, device="cuda") for _ in self.bes]
         self.rv = [torch.ones(K, device="cuda") for _ in self.bes]
         self.scale, self.bias = torch.from_numpy(scale).cuda(), torch.from_numpy(bias).cuda()
-        for bn, y, st in zip(self.bns, self.y, self.stats):
-            bn.forward_stage1(y, st[:K], st[K:], True)
+        for bn, y, st, got in zip(self.bns, self.y, self.stats, self.fused):
+            if not got:  # the conv epilogue did not deliver them
+                bn.forward_stage1(y, st[:K], st[K:], True)
         emu.allreduce_all(self.bes, self.stats)
         for bn, y, z, st, rm, rv in zip(self.bns, self.y, self.z, self.stats, self.rm, self.rv):
             bn.forward_stage2(y, st[:K], st[K:], rm, rv, self.scale, self.bias, z, True)
@@ -179,3 +182,28 @@ def test_config1_against_reference_backend_outputs():
     torch.cuda.synchronize()
     emu.assert_close(dws[0].cpu().numpy(), z["dw"], 2e-5, "dw vs ref::Backend")
     emu.assert_close(emu.gather_owned(L.dx, x.shape), z["dx"], 2e-5, "dx vs ref::Backend")
+
+
+@pytest.mark.parametrize("shape,locale", [([32, 16, 12, 4, 1], [1, 1, 2, 1, 1]), ([24, 20, 9, 4, 2], [1, 1, 3, 1, 1])])
+def test_layer_with_statistics_from_the_conv_epilogue(shape, locale):
+    """D-partitioned layers whose shards the sweep kernel takes: the BN
+    statistics come out of the convolution's epilogue on every rank and the
+    normalised output still matches the single-domain oracle."""
+    K, f, strides = 16, [3, 3, 3], [1, 1, 1]
+    rng = np.random.default_rng(5)
+    C = shape[-2]
+    gx = rng.normal(0.2, 1, tuple(reversed(shape))).astype(np.float32)
+    w = rng.normal(0, np.sqrt(2.0 / (C * 27)), (K, C, 3, 3, 3)).astype(np.float32)
+    scale = rng.uniform(0.5, 1.5, K).astype(np.float32)
+    bias = rng.normal(0, 0.5, K).astype(np.float32)
+    L = Layer(shape, locale, K, f, strides, pad=1)
+    L.forward(gx, w, scale, bias, fused_stats=True)
+    assert all(L.fused), "the sweep kernel should have produced the statistics"
+    y = O.conv_fwd(gx, w, [1] * 3, [1] * 3)
+    s, q = O.bn_sums(y)
+    m, v, _, _ = O.bn_sums_to_statistics(s, q, y.size // K, 0.9, np.zeros(K), np.ones(K))
+    z = O.bn_normalize(y, m, v, scale, bias, 1e-5)
+    osh = tuple(reversed(L.out_shape))
+    emu.assert_close(L.stats[0][:K].cpu().numpy(), m, 2e-5, "mean")
+    emu.assert_close(L.stats[0][K:].cpu().numpy(), v, 3e-5, "var")
+    emu.assert_close(emu.gather_owned(L.z, osh), z, 3e-5, "bn output")
