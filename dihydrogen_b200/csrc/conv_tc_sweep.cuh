@@ -33,14 +33,19 @@
 //   row_free[j]            epilogue -> issuers: the blocks of output row j
 //                          have been retired and are zero again
 // row_done / row_free complete once per step.  A parity wait cannot tell a
-// barrier that is two completions away, so: the epilogue warps wait on the
-// same row_done barriers every step; an issuer's rows change from step to
-// step, but its last row of every step is one of the last fh rows (there are
-// at most fh issuers), whose wait covers the last output row of either
-// epilogue half and with it (each half retires in ascending order) every
-// row_free of the previous step; and a barrier cannot run ahead of a waiter,
-// because its next completion needs a row that this waiter issues after the
-// wait.
+// barrier that is two completions away, in either direction.
+//  * Not behind: the epilogue warps wait on the same row_done barriers every
+//    step.  An issuer's rows change from step to step, but with at most fh
+//    issuers its last two rows of every step lie among the last fh + 1 rows,
+//    and their waits cover the last output row of either epilogue half, hence
+//    (each half retires in ascending order) every row_free of the previous step.
+//  * Not ahead: an issuer only waits for output rows that its own row adds
+//    into, and an epilogue warp only for input rows that feed its output row,
+//    so the barrier's next completion needs something the waiter does after
+//    the wait.  (Waiting for a row that one's own row does not touch breaks
+//    this: the barrier may complete again first and the wait never ends.)
+// The protocol was checked for fh in {1,2,3,5}, up to fh issuers and 2..13 rows
+// per column under random schedules in a host-side model.
 #pragma once
 
 #include "conv_tc_kernel.cuh"
@@ -342,7 +347,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                     {
                         const int a_slot = gq + G * lap_a;
                         if (!have)
-                            ok = mbar_wait(&raw_full[cslot], cphase, abort_flag);
+                            ok = mbar_wait(&raw_full[cslot], cphase, abort_flag, 11);
                         have = true;
                         if (!ok)
                             break;
@@ -355,7 +360,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                             uint32_t v[5][8];
                             sw_convert_c4f3(raw_s, pitch, v);
                             if (!a_first)
-                                ok = mbar_wait(&a_empty[a_slot], a_phase, abort_flag);
+                                ok = mbar_wait(&a_empty[a_slot], a_phase, abort_flag, 12);
                             if (!ok)
                                 break;
                             tc_fence_after();
@@ -366,7 +371,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                         else
                         {
                             if (!a_first)
-                                ok = mbar_wait(&a_empty[a_slot], a_phase, abort_flag);
+                                ok = mbar_wait(&a_empty[a_slot], a_phase, abort_flag, 12);
                             if (!ok)
                                 break;
                             tc_fence_after();
@@ -422,7 +427,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                 for (int ch = 0; ch < g.chunks_pp; ++ch)
                 {
                     if (!first_lap)
-                        ok = mbar_wait(&raw_empty[slot], empty_phase, abort_flag);
+                        ok = mbar_wait(&raw_empty[slot], empty_phase, abort_flag, 21);
                     if (!ok)
                         break;
                     if (lane == 0)
@@ -480,17 +485,22 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                     int i = real ? (mq + G - (int) (base % (uint32_t) G)) % G : mq;
                     for (; i < R && ok; i += G)
                     {
-                        // the blocks this row adds into must have been retired
-                        const int ja = min(i, g.th - 1);
-                        ok = mbar_wait_t<0>(&row_free[ja], par, abort_flag);
-                        if (ok && ja >= 1)
-                            ok = mbar_wait_t<0>(&row_free[ja - 1], par, abort_flag);
+                        // The blocks this row adds into (output rows r_lo..r_hi) must
+                        // have been retired.  Each epilogue half retires in ascending
+                        // order, so the top two rows stand for all of them.  Only rows
+                        // this row adds into may be waited for: their next retirement
+                        // needs this very row, so such a barrier cannot complete again
+                        // before this wait has seen it.
+                        const int r_hi = min(i, g.th - 1), r_lo = max(0, i - fh + 1);
+                        ok = mbar_wait_t<0>(&row_free[r_hi], par, abort_flag, 31);
+                        if (ok && r_hi - 1 >= r_lo)
+                            ok = mbar_wait_t<0>(&row_free[r_hi - 1], par, abort_flag, 32);
                         if (!ok)
                             break;
                         if (real)
                         {
                             const uint32_t slot = (uint32_t) (mq + G * lap_a);
-                            ok = mbar_wait_t<0>(&a_full[slot], full_phase, abort_flag);
+                            ok = mbar_wait_t<0>(&a_full[slot], full_phase, abort_flag, 33);
                             if (!ok)
                                 break;
                             tc_fence_after();
@@ -586,7 +596,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                                 old[k] = yrow[(size_t) k * ysc];
                     }
                     for (int i = j; i < j + fh && ok; ++i)
-                        ok = mbar_wait(&row_done[i], par, abort_flag);
+                        ok = mbar_wait(&row_done[i], par, abort_flag, 41);
                     if (!ok)
                         break;
                     tc_fence_after();
@@ -697,7 +707,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     }
 
     if (!ok && lane == 0)
-        atomicExch(status, 1);
+        atomicExch(status, *abort_flag ? *abort_flag : 1); // which wait gave up first
     tc_fence_before();
     __syncthreads();
     if (warp == TC_MMA_WARP)

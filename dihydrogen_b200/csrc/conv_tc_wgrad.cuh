@@ -17,7 +17,7 @@
 // 3xTF32: D[:, 0:32] += A_hi x [B_hi | B_lo] (one instruction, N = 32) and
 // D[:, 0:16] += A_lo x B_hi (N = 16); the fold adds the two column halves.
 //
-// A unit is 128 outputs of one output row: 16 chunks.  Warp 15 copies the
+// A unit is 128 outputs of one output row: 8 chunks of two k-steps.  Warp 15 copies the
 // fd * fh input rows (all channels, 4 cells of margin left and right, zeros
 // outside the tensor = the padding) and the dy row (all filters) of the next
 // unit into a two-deep shared-memory ring with bulk tensor copies.  Warps 0..11
@@ -38,11 +38,13 @@ constexpr int WG_THREADS = 20 * 32; // 12 converters, 3 issuers, 1 copy, 4 dump 
 constexpr int WG_COPY_WARP = 15;
 constexpr int WG_DUMP_WARP = 16;
 constexpr int WG_TW = 128;                 // outputs per unit
-constexpr int WG_CHUNKS = WG_TW / 8;       // chunks per unit
+constexpr int WG_KS = 2;                   // k-steps (of eight outputs) per chunk: one hand-off per chunk
+constexpr int WG_CHUNKS = WG_TW / (8 * WG_KS); // chunks per unit
 constexpr int WG_XW = WG_TW + 8;           // staged input row: 4 cells of margin each side
 constexpr int WG_A_SLOTS = 6;              // two per group
-constexpr uint32_t WG_TMEM_COLS = 128;     // 32 accumulator columns + 6 x 16 A columns
-constexpr int WG_B_FLOATS = 256;           // one B tile: 8 x 32 floats
+constexpr int WG_A_COLS = 16 * WG_KS;      // an A slot: per k-step 8 hi + 8 lo columns
+constexpr uint32_t WG_TMEM_COLS = 256;     // 32 accumulator columns + 6 A slots
+constexpr int WG_B_FLOATS = 256 * WG_KS;   // the B tiles of a chunk: per k-step 8 x 32 floats
 
 struct WgGeom
 {
@@ -173,38 +175,46 @@ __global__ void __launch_bounds__(WG_THREADS, 1)
             for (; q < WG_CHUNKS && ok; q += 3)
             {
                 const int slot = gq + 3 * lap;
-                uint32_t hi[8], lo[8];
-                if (src >= 0)
-                {
-                    const uint32_t s0 = smem_u32(xb + src + q * 8);
+                uint32_t hi[WG_KS][8], lo[WG_KS][8], dhi[WG_KS], dlo[WG_KS];
 #pragma unroll
-                    for (int e = 0; e < 8; ++e)
+                for (int ks = 0; ks < WG_KS; ++ks)
+                {
+                    if (src >= 0)
                     {
-                        const float xe = __uint_as_float(lds_u32(s0 + 4u * e));
-                        hi[e] = tf32_rna(xe);
-                        lo[e] = tf32_rna(xe - __uint_as_float(hi[e]));
-                    }
-                }
-                else
-                {
+                        const uint32_t s0 = smem_u32(xb + src + (q * WG_KS + ks) * 8);
 #pragma unroll
-                    for (int e = 0; e < 8; ++e)
-                        hi[e] = lo[e] = 0u;
+                        for (int e = 0; e < 8; ++e)
+                        {
+                            const float xe = __uint_as_float(lds_u32(s0 + 4u * e));
+                            hi[ks][e] = tf32_rna(xe);
+                            lo[ks][e] = tf32_rna(xe - __uint_as_float(hi[ks][e]));
+                        }
+                    }
+                    else
+                    {
+#pragma unroll
+                        for (int e = 0; e < 8; ++e)
+                            hi[ks][e] = lo[ks][e] = 0u;
+                    }
+                    const float dv = dyb[bk * WG_TW + (q * WG_KS + ks) * 8 + bkk];
+                    dhi[ks] = tf32_rna(dv);
+                    dlo[ks] = tf32_rna(dv - __uint_as_float(dhi[ks]));
                 }
-                const float dv = dyb[bk * WG_TW + q * 8 + bkk];
-                const uint32_t dhi = tf32_rna(dv);
-                const uint32_t dlo = tf32_rna(dv - __uint_as_float(dhi));
                 if (!a_first)
                     ok = mbar_wait(&a_empty[slot], a_phase, abort_flag);
                 if (!ok)
                     break;
                 tc_fence_after();
-                const uint32_t a_addr = lane_addr + 32u + (uint32_t) (slot * 16);
-                tmem_st8(a_addr, hi);
-                tmem_st8(a_addr + 8, lo);
+                const uint32_t a_addr = lane_addr + 32u + (uint32_t) (slot * WG_A_COLS);
                 float* bt = bring + slot * WG_B_FLOATS;
-                bt[b_off] = __uint_as_float(dhi);
-                bt[b_off + 64] = __uint_as_float(dlo);
+#pragma unroll
+                for (int ks = 0; ks < WG_KS; ++ks)
+                {
+                    tmem_st8(a_addr + (uint32_t) (ks * 16), hi[ks]);
+                    tmem_st8(a_addr + (uint32_t) (ks * 16 + 8), lo[ks]);
+                    bt[ks * 256 + b_off] = __uint_as_float(dhi[ks]);
+                    bt[ks * 256 + b_off + 64] = __uint_as_float(dlo[ks]);
+                }
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 tc_fence_before();
@@ -280,12 +290,18 @@ __global__ void __launch_bounds__(WG_THREADS, 1)
                 tc_fence_after();
                 if (lane == 0)
                 {
-                    const uint32_t a_addr = tmem_base + 32u + (uint32_t) (slot * 16);
-                    // B tile: [2 k-chunks][4 filter groups][8][4]: 512 bytes between the
-                    // k-chunks, 128 between the filter groups
+                    const uint32_t a_addr = tmem_base + 32u + (uint32_t) (slot * WG_A_COLS);
+                    // B tile of a k-step: [2 k-chunks][4 filter groups][8][4]: 512 bytes
+                    // between the k-chunks, 128 between the filter groups, 1 KiB per tile
                     const uint64_t bd = make_desc(smem_u32(bring + slot * WG_B_FLOATS), 512u, 128u, 0u);
-                    mma_tf32_ts(tmem_base, a_addr, bd, idesc32);     // A_hi x [B_hi | B_lo]
-                    mma_tf32_ts(tmem_base, a_addr + 8, bd, idesc16); // A_lo x B_hi
+#pragma unroll
+                    for (int ks = 0; ks < WG_KS; ++ks)
+                    {
+                        mma_tf32_ts(tmem_base, a_addr + (uint32_t) (ks * 16), bd + (uint64_t) (ks * 64),
+                                    idesc32); // A_hi x [B_hi | B_lo]
+                        mma_tf32_ts(tmem_base, a_addr + (uint32_t) (ks * 16 + 8), bd + (uint64_t) (ks * 64),
+                                    idesc16); // A_lo x B_hi
+                    }
                     mma_commit(&a_empty[slot]);
                     tc_fence_before();
                 }
@@ -354,7 +370,7 @@ __global__ void __launch_bounds__(WG_THREADS, 1)
     }
 
     if (!ok && lane == 0)
-        atomicExch(status, 1);
+        atomicExch(status, *abort_flag ? *abort_flag : 1);
     tc_fence_before();
     __syncthreads();
     if (warp == TC_MMA_WARP)
