@@ -173,8 +173,7 @@ int32_t dcb_conv_plan_status(dcb_conv_plan* p, void* stream)
     if (st != 0)
     {
         DCB_CUDA_TRY(cudaMemset(word, 0, sizeof(int)));
-        set_last_error("a tensor-core convolution kernel gave up on a pipeline wait (site "
-                       + std::to_string(st) + ")");
+        set_last_error("a tensor-core convolution kernel gave up on a pipeline wait");
         return DCB_CUDA_ERROR;
     }
     return DCB_OK;

@@ -211,12 +211,10 @@ bool sw_geom(const ConvGeom& cg, int math_mode, SwGeom* out)
     g.b_bytes = g.f[0] * g.b_rot_bytes;
     // an issuer must own one of any fh consecutive rows (see the hand-off
     // notes in the kernel header)
-    g.groups = TC_GROUPS_MAX;
-    // Only the three-group arrangement is in use: fewer groups (shallow
-    // filters, or k-rows too wide for three A slots) gave up on a bounded wait
-    // when tried, and those shapes stay with the row kernel until that is
-    // understood.
-    if (g.f[1] < g.groups || g.groups * g.kr > 160)
+    // an issuer must own one of any fh consecutive rows (see the hand-off
+    // notes in the kernel header): at most fh groups
+    g.groups = g.f[1] < TC_GROUPS_MAX ? g.f[1] : TC_GROUPS_MAX;
+    if (g.groups * g.kr > 160)
         return false;
     g.a_slots = g.groups;
     if (g.a_slots * g.kr > 256)

@@ -72,11 +72,9 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count)
 
 // Bounded parity wait.  Returns false when the budget ran out.  Every role but
 // the MMA issuer backs off between polls (SLEEP_NS > 0): a hot polling loop in
-// a dozen warps would take the issue slots the MMA thread needs.  `site` names
-// the wait (role * 10 + which) in the plan's status word if it is the one that
-// gives up.
+// a dozen warps would take the issue slots the MMA thread needs.
 template <int SLEEP_NS>
-__device__ __forceinline__ bool mbar_wait_t(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int site = 1)
+__device__ __forceinline__ bool mbar_wait_t(uint64_t* bar, uint32_t parity, volatile int* abort_flag)
 {
     const uint32_t addr = smem_u32(bar);
     long long t0 = 0;
@@ -108,14 +106,13 @@ __device__ __forceinline__ bool mbar_wait_t(uint64_t* bar, uint32_t parity, vola
                 break;
         }
     }
-    if (*abort_flag == 0)
-        *abort_flag = site;
+    *abort_flag = 1;
     return false;
 }
 
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int site = 1)
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag)
 {
-    return mbar_wait_t<20>(bar, parity, abort_flag, site);
+    return mbar_wait_t<20>(bar, parity, abort_flag);
 }
 
 __device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes,
@@ -819,7 +816,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     }
 
     if (!ok && lane == 0)
-        atomicExch(status, *abort_flag ? *abort_flag : 1);
+        atomicExch(status, 1);
     // Every role leaves its loop after a bounded time (all waits are bounded
     // and watch the abort flag), so the block-wide barrier is always reached.
     tc_fence_before();

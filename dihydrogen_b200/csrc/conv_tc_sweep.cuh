@@ -347,7 +347,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                     {
                         const int a_slot = gq + G * lap_a;
                         if (!have)
-                            ok = mbar_wait(&raw_full[cslot], cphase, abort_flag, 11);
+                            ok = mbar_wait(&raw_full[cslot], cphase, abort_flag);
                         have = true;
                         if (!ok)
                             break;
@@ -360,7 +360,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                             uint32_t v[5][8];
                             sw_convert_c4f3(raw_s, pitch, v);
                             if (!a_first)
-                                ok = mbar_wait(&a_empty[a_slot], a_phase, abort_flag, 12);
+                                ok = mbar_wait(&a_empty[a_slot], a_phase, abort_flag);
                             if (!ok)
                                 break;
                             tc_fence_after();
@@ -371,7 +371,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                         else
                         {
                             if (!a_first)
-                                ok = mbar_wait(&a_empty[a_slot], a_phase, abort_flag, 12);
+                                ok = mbar_wait(&a_empty[a_slot], a_phase, abort_flag);
                             if (!ok)
                                 break;
                             tc_fence_after();
@@ -427,7 +427,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                 for (int ch = 0; ch < g.chunks_pp; ++ch)
                 {
                     if (!first_lap)
-                        ok = mbar_wait(&raw_empty[slot], empty_phase, abort_flag, 21);
+                        ok = mbar_wait(&raw_empty[slot], empty_phase, abort_flag);
                     if (!ok)
                         break;
                     if (lane == 0)
@@ -492,15 +492,15 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                         // needs this very row, so such a barrier cannot complete again
                         // before this wait has seen it.
                         const int r_hi = min(i, g.th - 1), r_lo = max(0, i - fh + 1);
-                        ok = mbar_wait_t<0>(&row_free[r_hi], par, abort_flag, 31);
+                        ok = mbar_wait_t<0>(&row_free[r_hi], par, abort_flag);
                         if (ok && r_hi - 1 >= r_lo)
-                            ok = mbar_wait_t<0>(&row_free[r_hi - 1], par, abort_flag, 32);
+                            ok = mbar_wait_t<0>(&row_free[r_hi - 1], par, abort_flag);
                         if (!ok)
                             break;
                         if (real)
                         {
                             const uint32_t slot = (uint32_t) (mq + G * lap_a);
-                            ok = mbar_wait_t<0>(&a_full[slot], full_phase, abort_flag, 33);
+                            ok = mbar_wait_t<0>(&a_full[slot], full_phase, abort_flag);
                             if (!ok)
                                 break;
                             tc_fence_after();
@@ -596,7 +596,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                                 old[k] = yrow[(size_t) k * ysc];
                     }
                     for (int i = j; i < j + fh && ok; ++i)
-                        ok = mbar_wait(&row_done[i], par, abort_flag, 41);
+                        ok = mbar_wait(&row_done[i], par, abort_flag);
                     if (!ok)
                         break;
                     tc_fence_after();
@@ -707,7 +707,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     }
 
     if (!ok && lane == 0)
-        atomicExch(status, *abort_flag ? *abort_flag : 1); // which wait gave up first
+        atomicExch(status, 1);
     tc_fence_before();
     __syncthreads();
     if (warp == TC_MMA_WARP)

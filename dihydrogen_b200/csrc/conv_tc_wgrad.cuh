@@ -370,7 +370,7 @@ __global__ void __launch_bounds__(WG_THREADS, 1)
     }
 
     if (!ok && lane == 0)
-        atomicExch(status, *abort_flag ? *abort_flag : 1);
+        atomicExch(status, 1);
     tc_fence_before();
     __syncthreads();
     if (warp == TC_MMA_WARP)

@@ -109,6 +109,8 @@ GEOMS = [
     (1, 3, 4, (11, 12, 130), (1, 1, 1), (0, 0, 0), (1, 1, 1), (1, 1, 1)),     # 1x1x1
     (1, 4, 16, (6, 6, 260), (3, 3, 3), (1, 1, 1), (1, 1, 1), (1, 1, 1)),      # wide rows, several W tiles
     (3, 5, 7, (9, 21), (3, 3), (1, 1), (2, 2), (1, 1)),                       # 2-D stride 2, odd extents
+    (1, 4, 8, (6, 9, 36), (3, 2, 3), (1, 0, 1), (1, 1, 1), (1, 1, 1)),        # two filter rows: two converter groups
+    (2, 3, 5, (5, 6, 40), (2, 1, 3), (1, 0, 1), (1, 1, 1), (1, 1, 1)),        # one filter row: one converter group
 ]
 
 
