@@ -340,6 +340,36 @@ size_t tc_smem_bytes(const TcGeom& g)
 
 } // namespace
 
+// One channel group's output, dense, rows padded to 16 bytes.
+static size_t sw_scratch_floats(const SwGeom& g)
+{
+    const size_t wp = (size_t) (g.out[2] + 3) / 4 * 4;
+    return (size_t) g.n * g.k * g.out[0] * g.out[1] * wp;
+}
+
+// y (strided window) += the sum of `nsrc` dense group outputs; one block per
+// output row.
+__global__ void sw_group_sum_kernel(SwGeom g, const float* __restrict__ scratch, size_t slice, int nsrc, float* y)
+{
+    const int wp = (g.out[2] + 3) / 4 * 4;
+    long long r = blockIdx.x; // (n, k, od, oh)
+    const int oh = (int) (r % g.out[1]);
+    r /= g.out[1];
+    const int od = (int) (r % g.out[0]);
+    r /= g.out[0];
+    const int k = (int) (r % g.k);
+    const int n = (int) (r / g.k);
+    const float* s = scratch + (size_t) blockIdx.x * wp;
+    float* yp = y + (size_t) n * g.ys_n + (size_t) k * g.ys_c + (size_t) od * g.ys[0] + (size_t) oh * g.ys[1];
+    for (int w = threadIdx.x; w < g.out[2]; w += blockDim.x)
+    {
+        float acc = yp[w];
+        for (int i = 0; i < nsrc; ++i)
+            acc += s[(size_t) i * slice + w];
+        yp[w] = acc;
+    }
+}
+
 struct TcPlan
 {
     bool has[2] = {false, false};
@@ -349,6 +379,7 @@ struct TcPlan
     bool has_sw[2] = {false, false};
     SwGeom sw[2];
     float* sw_bimg[2] = {nullptr, nullptr};
+    float* grp_scratch[2] = {nullptr, nullptr}; // dense outputs of the channel groups after the first
     float* stat_part = nullptr; // per epilogue warp partial sums of the fused statistics
     // tensor-core backward filter
     bool has_wg = false;
@@ -383,6 +414,9 @@ int32_t tc_plan_create(const ConvGeom& fwd, const ConvGeom& bwd, bool bwd_is_fwd
             ok = cudaMalloc(&p->bimg[s], p->g[s].b_bytes) == cudaSuccess;
         if (ok && p->has_sw[s])
             ok = cudaMalloc(&p->sw_bimg[s], p->sw[s].b_bytes) == cudaSuccess;
+        if (ok && p->has_sw[s] && p->sw[s].cgroups > 1)
+            ok = cudaMalloc(&p->grp_scratch[s], sw_scratch_floats(p->sw[s]) * (p->sw[s].cgroups - 1) * sizeof(float))
+                 == cudaSuccess;
     }
     if (ok && p->has_wg)
         ok = cudaMalloc(&p->wg_part, (size_t) num_sms() * 128 * 16 * sizeof(float)) == cudaSuccess;
@@ -407,6 +441,8 @@ void tc_plan_destroy(TcPlan* p)
     cudaFree(p->bimg[1]);
     cudaFree(p->sw_bimg[0]);
     cudaFree(p->sw_bimg[1]);
+    cudaFree(p->grp_scratch[0]);
+    cudaFree(p->grp_scratch[1]);
     cudaFree(p->stat_part);
     cudaFree(p->wg_part);
     cudaFree(p->status);
@@ -619,13 +655,37 @@ int32_t tc_conv_fwd(TcPlan* p, int slot, float alpha, const float* x, const floa
         }
         if (ok)
         {
+            // The first group writes the output (blending with the old one if
+            // beta asks for it); every further group writes its own dense
+            // scratch slice with the plain, faster kernel, and one pass adds the
+            // slices into the output.
+            const size_t slice = sw_scratch_floats(sg);
             for (int grp = 0; grp < sg.cgroups; ++grp)
             {
-                sg.w_c_off = grp * sg.c;
-                const int32_t st = sw_launch(sg, alpha, w, x + (size_t) grp * sg.c * sg.xs_c, p->sw_bimg[slot],
-                                             grp == 0 ? beta : 1.f, y, p->status, maps[grp], stream);
+                SwGeom lg = sg;
+                lg.w_c_off = grp * sg.c;
+                float* dst = y;
+                if (grp > 0)
+                {
+                    const long long wp = (sg.out[2] + 3) / 4 * 4;
+                    lg.ys[2] = 1;
+                    lg.ys[1] = wp;
+                    lg.ys[0] = wp * sg.out[1];
+                    lg.ys_c = lg.ys[0] * sg.out[0];
+                    lg.ys_n = lg.ys_c * sg.k;
+                    dst = p->grp_scratch[slot] + (size_t) (grp - 1) * slice;
+                }
+                const int32_t st = sw_launch(lg, alpha, w, x + (size_t) grp * sg.c * sg.xs_c, p->sw_bimg[slot],
+                                             grp == 0 ? beta : 0.f, dst, p->status, maps[grp], stream);
                 if (st != DCB_OK)
                     return st;
+            }
+            if (sg.cgroups > 1)
+            {
+                const long long rows = (long long) sg.n * sg.k * sg.out[0] * sg.out[1];
+                sw_group_sum_kernel<<<(unsigned) rows, 128, 0, stream>>>(sg, p->grp_scratch[slot], slice,
+                                                                         sg.cgroups - 1, y);
+                DCB_LAUNCH_CHECK();
             }
             return DCB_OK;
         }
