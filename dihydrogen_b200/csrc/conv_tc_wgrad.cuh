@@ -40,7 +40,9 @@ constexpr int WG_DUMP_WARP = 16;
 constexpr int WG_TW = 128;                 // outputs per unit
 constexpr int WG_KS = 2;                   // k-steps (of eight outputs) per chunk: one hand-off per chunk
 constexpr int WG_CHUNKS = WG_TW / (8 * WG_KS); // chunks per unit
-constexpr int WG_XW = WG_TW + 8;           // staged input row: 4 cells of margin each side
+constexpr int WG_XW = WG_TW + 12;          // staged input row: 4 cells of margin left, 8 right; the 140-float
+                                           // pitch keeps the taps of a warp's 32 lanes (about 11 rows x 3
+                                           // columns) on different banks, 136 would fold them three deep
 constexpr int WG_A_SLOTS = 6;              // two per group
 constexpr int WG_A_COLS = 16 * WG_KS;      // an A slot: per k-step 8 hi + 8 lo columns
 constexpr uint32_t WG_TMEM_COLS = 256;     // 32 accumulator columns + 6 A slots
