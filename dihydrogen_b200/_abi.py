@@ -105,6 +105,8 @@ _SIGS = {
     "dcb_bn_stats_noalloc": (c_int32, [POINTER(NdDesc), _P, _P, _P, _P]),
     "dcb_bn_finalize": (c_int32, [c_int32, c_int64, c_float, _P, _P, _P, _P, _P]),
     "dcb_bn_apply": (c_int32, [POINTER(NdDesc), _P, _P, _P, _P, _P, c_float, POINTER(NdDesc), _P, _P]),
+    "dcb_bn_apply_leaky_relu": (c_int32, [POINTER(NdDesc), _P, _P, _P, _P, _P, c_float, c_float, POINTER(NdDesc), _P,
+                                          _P]),
     "dcb_bn_bwd_reduce": (c_int32, [_P, _P, POINTER(NdDesc), _P, _P, _P, _P, c_float, _P, _P, _P, _P, _P]),
     "dcb_bn_bwd_apply": (c_int32, [POINTER(NdDesc), _P, POINTER(NdDesc), _P, _P, _P, _P, _P, _P, c_float, c_int64,
                                    POINTER(NdDesc), _P, _P]),

@@ -255,14 +255,16 @@ __global__ void bn_finalize_kernel(int channels, long long num_per_sum,
     }
 }
 
-template <int V>
+// LEAKY: the leaky ReLU that follows the batch-norm in the same pass
+// (y > 0 ? y : slope * y), one trip through HBM instead of two.
+template <int V, bool LEAKY>
 __global__ void __launch_bounds__(BN_THREADS)
     bn_apply_kernel(const float* __restrict__ x, RunStrides xs,
                     float* __restrict__ y, RunStrides ys, UnitGeom ug,
                     const float* __restrict__ mean,
                     const float* __restrict__ var,
                     const float* __restrict__ scale,
-                    const float* __restrict__ bias, float eps)
+                    const float* __restrict__ bias, float eps, float slope)
 {
     const int c = blockIdx.y;
     const float m = mean[c];
@@ -292,7 +294,8 @@ __global__ void __launch_bounds__(BN_THREADS)
                 for (int i = 0; i < V; ++i)
                 {
                     const float xhat = (v[k].v[i] - m) * inv_stdev;
-                    v[k].v[i] = sc * xhat + bi;
+                    const float o = sc * xhat + bi;
+                    v[k].v[i] = LEAKY ? (o > 0.f ? o : o * slope) : o;
                 }
                 v[k].store(yp + (size_t) (threadIdx.x + k * BN_THREADS) * V);
             }
@@ -623,9 +626,9 @@ int32_t dcb_bn_finalize(int32_t channels, int64_t num_per_sum, float decay,
     return DCB_OK;
 }
 
-int32_t dcb_bn_apply(const dcb_nd_desc* xd, const void* x, const void* mean,
-                     const void* var, const void* scale, const void* bias,
-                     float eps, const dcb_nd_desc* yd, void* y, void* stream)
+static int32_t bn_apply_impl(const dcb_nd_desc* xd, const void* x, const void* mean, const void* var,
+                             const void* scale, const void* bias, float eps, bool leaky, float slope,
+                             const dcb_nd_desc* yd, void* y, void* stream)
 {
     DCB_REQUIRE(x && y && mean && var && scale && bias, "null argument");
     const dcb_nd_desc* descs[2] = {xd, yd};
@@ -638,15 +641,38 @@ int32_t dcb_bn_apply(const dcb_nd_desc* xd, const void* x, const void* mean,
         return DCB_OK;
     const dim3 grid = bn_grid(mv.ug);
 #define CALL(VV)                                                               \
-    bn_apply_kernel<VV><<<grid, BN_THREADS, 0, as_stream(stream)>>>(           \
-        static_cast<const float*>(x), mv.s[0], static_cast<float*>(y),         \
-        mv.s[1], mv.ug, static_cast<const float*>(mean),                       \
-        static_cast<const float*>(var), static_cast<const float*>(scale),      \
-        static_cast<const float*>(bias), eps)
+    if (leaky)                                                                 \
+        bn_apply_kernel<VV, true><<<grid, BN_THREADS, 0, as_stream(stream)>>>( \
+            static_cast<const float*>(x), mv.s[0], static_cast<float*>(y),     \
+            mv.s[1], mv.ug, static_cast<const float*>(mean),                   \
+            static_cast<const float*>(var), static_cast<const float*>(scale),  \
+            static_cast<const float*>(bias), eps, slope);                      \
+    else                                                                       \
+        bn_apply_kernel<VV, false><<<grid, BN_THREADS, 0, as_stream(stream)>>>(\
+            static_cast<const float*>(x), mv.s[0], static_cast<float*>(y),     \
+            mv.s[1], mv.ug, static_cast<const float*>(mean),                   \
+            static_cast<const float*>(var), static_cast<const float*>(scale),  \
+            static_cast<const float*>(bias), eps, slope)
     DCB_VEC_DISPATCH(mv.vec, CALL);
 #undef CALL
     DCB_LAUNCH_CHECK();
     return DCB_OK;
+}
+
+int32_t dcb_bn_apply(const dcb_nd_desc* xd, const void* x, const void* mean,
+                     const void* var, const void* scale, const void* bias,
+                     float eps, const dcb_nd_desc* yd, void* y, void* stream)
+{
+    return bn_apply_impl(xd, x, mean, var, scale, bias, eps, false, 1.f, yd, y, stream);
+}
+
+int32_t dcb_bn_apply_leaky_relu(const dcb_nd_desc* xd, const void* x,
+                                const void* mean, const void* var,
+                                const void* scale, const void* bias, float eps,
+                                float slope, const dcb_nd_desc* yd, void* y,
+                                void* stream)
+{
+    return bn_apply_impl(xd, x, mean, var, scale, bias, eps, true, slope, yd, y, stream);
 }
 
 int32_t dcb_bn_bwd_reduce(dcb_bn_plan* plan, const void* x,

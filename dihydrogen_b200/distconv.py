@@ -939,7 +939,9 @@ class BatchNormalization:
         return 0
 
     def forward_stage2(self, input: Tensor, mean, var, running_mean, running_var, scale, bias, output: Tensor,
-                       is_training=True):
+                       is_training=True, leaky_relu_slope=None):
+        """``leaky_relu_slope``: also apply the LeakyReLU that follows the
+        batch-norm, in the same pass over the tensor."""
         s = self.be.stream
         C = input.local_shape[-2]
         if is_training:
@@ -956,6 +958,11 @@ class BatchNormalization:
         if input.get_local_size() == 0:
             return 0
         xd, yd = input.nd_desc(), output.nd_desc()
+        if leaky_relu_slope is not None:
+            call("dcb_bn_apply_leaky_relu", ctypes.byref(xd), _ptr(input.get_base_ptr()), _ptr(m.data_ptr()),
+                 _ptr(v.data_ptr()), _ptr(scale.data_ptr()), _ptr(bias.data_ptr()), self.epsilon,
+                 float(leaky_relu_slope), ctypes.byref(yd), _ptr(output.get_base_ptr()), _stream_ptr(s))
+            return 0
         call("dcb_bn_apply", ctypes.byref(xd), _ptr(input.get_base_ptr()), _ptr(m.data_ptr()), _ptr(v.data_ptr()),
              _ptr(scale.data_ptr()), _ptr(bias.data_ptr()), self.epsilon, ctypes.byref(yd),
              _ptr(output.get_base_ptr()), _stream_ptr(s))

@@ -267,6 +267,14 @@ int32_t dcb_bn_finalize(int32_t channels, int64_t num_per_sum, float decay,
 int32_t dcb_bn_apply(const dcb_nd_desc* xd, const void* x, const void* mean,
                      const void* var, const void* scale, const void* bias,
                      float eps, const dcb_nd_desc* yd, void* y, void* stream);
+/* dcb_bn_apply followed by the leaky ReLU y > 0 ? y : slope*y in the same pass
+ * (batch_normalization, batchnorm.cu:369-455, then leaky_relu.cu:14-25): saves
+ * one read and one write of the tensor where a LeakyReLU follows the batch-norm. */
+int32_t dcb_bn_apply_leaky_relu(const dcb_nd_desc* xd, const void* x,
+                                const void* mean, const void* var,
+                                const void* scale, const void* bias, float eps,
+                                float slope, const dcb_nd_desc* yd, void* y,
+                                void* stream);
 /* Local dscale, dbias, dmean, dvar (backprop1, batchnorm.cu:899-1054).
  * Overwrites the four C-vectors. */
 int32_t dcb_bn_bwd_reduce(dcb_bn_plan* plan, const void* x,

@@ -171,3 +171,28 @@ def test_leaky_relu():
     lr.backward(x_t, dy_t, 0.01, dx_t)
     assert np.array_equal(y_t.buffer.cpu().numpy(), np.where(x > 0, x, np.float32(0.01) * x))
     assert np.array_equal(dx_t.buffer.cpu().numpy(), np.where(x > 0, dy, np.float32(0.01) * dy))
+
+
+def test_bn_apply_fused_with_leaky_relu_matches_the_two_passes():
+    rng = np.random.default_rng(3)
+    x = torch.from_numpy(rng.normal(0.1, 1.5, (2, 5, 6, 7, 40)).astype(np.float32)).cuda()
+    C = 5
+    mean = torch.from_numpy(rng.normal(0, 0.3, C).astype(np.float32)).cuda()
+    var = torch.from_numpy(rng.uniform(0.5, 2, C).astype(np.float32)).cuda()
+    scale = torch.from_numpy(rng.uniform(0.5, 1.5, C).astype(np.float32)).cuda()
+    bias = torch.from_numpy(rng.normal(0, 0.5, C).astype(np.float32)).cuda()
+    loc = dc.Locale(0, 1)
+    be = dc.BackendDNNLib(loc, allreduce="peer", allreduce_max_count=64)
+    shape = [40, 7, 6, C, 2]
+    dist = dc.Distribution.make_localized_distribution(5)
+    tx, ty, tz, tf = (dc.Tensor(shape, loc, dist) for _ in range(4))
+    for t in (tx, ty, tz, tf):
+        t.allocate()
+    tx.buffer.copy_(x)
+    bn = dc.BatchNormalization(be, 5, 0.9, 1e-5, True)
+    rm, rv = torch.zeros(C, device="cuda"), torch.ones(C, device="cuda")
+    bn.forward_stage2(tx, mean, var, rm, rv, scale, bias, ty, is_training=False)
+    dc.LeakyReLU(be).forward(ty, 0.01, tz)
+    bn.forward_stage2(tx, mean, var, rm, rv, scale, bias, tf, is_training=False, leaky_relu_slope=0.01)
+    torch.cuda.synchronize()
+    assert torch.equal(tf.buffer, tz.buffer)
