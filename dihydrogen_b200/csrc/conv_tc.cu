@@ -26,6 +26,7 @@
 #include "conv_tc.cuh"
 #include "conv_tc_kernel.cuh"
 #include "conv_tc_sweep.cuh"
+#include "conv_tc_sweep_mg.cuh"
 #include "conv_tc_wgrad.cuh"
 
 namespace dcb
@@ -276,6 +277,125 @@ bool sw_geom(const ConvGeom& cg, int math_mode, SwGeom* out)
     return true;
 }
 
+size_t mg_smem_need(const SwGeom& g)
+{
+    return (size_t) (g.b_bytes + 127) / 128 * 128 + (size_t) g.raw_slots * g.raw_slot_bytes
+           + (size_t) ((g.kr + 1) & ~1) * 4 + (size_t) (2 * g.a_slots + 64 + 2 * g.raw_slots) * 8 + 64 + 128
+           + (size_t) TC_EPI_WARPS * 2 * MG_NBK * 32 * 4 + 1024;
+}
+
+// Geometry of the multi-group sweep kernel: at most four filters, the input
+// channels in two to eight equal groups walked inside one launch.
+bool mg_geom(const ConvGeom& cg, int math_mode, SwGeom* out)
+{
+    SwGeom g;
+    std::memset(&g, 0, sizeof(g));
+    for (int i = 0; i < 3; ++i)
+    {
+        if (cg.stride[i] != 1 || cg.dil[i] != 1)
+            return false;
+        g.in[i] = cg.in[i];
+        g.out[i] = cg.out[i];
+        g.f[i] = cg.f[i];
+        g.pad[i] = cg.pad[i];
+        g.xs[i] = cg.xs[i];
+        g.ys[i] = cg.ys[i];
+        if (g.pad[i] > g.f[i] - 1)
+            return false;
+    }
+    g.n = cg.n;
+    g.k = cg.k;
+    g.xs_n = cg.xs_n;
+    g.xs_c = cg.xs_c;
+    g.ys_n = cg.ys_n;
+    g.ys_c = cg.ys_c;
+    if (g.f[0] < 2 || g.f[0] > MG_SLOTS || g.k > MG_NBK || g.f[1] < TC_GROUPS_MAX)
+        return false;
+    if ((long long) cg.n * cg.out[0] * cg.out[1] * cg.out[2] == 0)
+        return false;
+    if (g.pad[2] > 4 || g.f[2] - 1 - g.pad[2] > 4)
+        return false;
+    if (!(cg.xs[1] % 4 == 0 && cg.xs[0] % 4 == 0 && cg.xs_c % 4 == 0 && cg.xs_n % 4 == 0))
+        return false;
+    g.split = math_mode == DCB_MATH_TF32 ? 0 : 1;
+    g.w_c_total = cg.c;
+    g.c = 0;
+    for (int cgp = cg.c; cgp >= 1; --cgp)
+        if (cg.c % cgp == 0 && 3 * ((cgp * g.f[2] * (g.split ? 3 : 1) + 7) / 8 * 8) <= 160)
+        {
+            g.c = cgp;
+            break;
+        }
+    if (g.c == 0)
+        return false;
+    g.cgroups = cg.c / g.c;
+    // fewer groups than issuers would leave an issuer without a sub-row in some
+    // rows; a single group is the sweep kernel's own case
+    if (g.cgroups < TC_GROUPS_MAX || g.cgroups > 8)
+        return false;
+    g.w_c_off = 0;
+    g.ntot = g.f[1] * MG_BLK;
+    if (g.ntot > 256)
+        return false;
+    g.crows = g.c * g.f[2];
+    g.kr = (g.crows * (g.split ? 3 : 1) + 7) / 8 * 8;
+    g.ksteps = g.kr / 8;
+    g.b_rot_bytes = g.kr * g.ntot * 4;
+    g.b_bytes = g.cgroups * MG_SLOTS * g.b_rot_bytes;
+    g.groups = TC_GROUPS_MAX;
+    g.a_slots = g.groups;
+    int th_max = ((int) TC_TMEM_COLS - g.a_slots * g.kr) / MG_BLK;
+    if (th_max + g.f[1] - 1 > 32)
+        th_max = 32 - g.f[1] + 1;
+    if (th_max > g.out[1])
+        th_max = g.out[1];
+    if (th_max < 2)
+        return false;
+    const int sms = num_sms();
+    long long best_cost = -1;
+    int best_th = th_max, best_ns = 1;
+    for (int th = th_max; th >= 2 && th >= th_max - 6; --th)
+    {
+        const long long cols = (long long) g.n * ((g.out[2] + TC_M - 1) / TC_M) * ((g.out[1] + th - 1) / th);
+        for (int ns = 1; ns <= g.out[0] && ns <= 64; ++ns)
+        {
+            const long long units = cols * ns;
+            const long long waves = (units + sms - 1) / sms;
+            const long long steps = (g.out[0] + ns - 1) / ns + 2 * (g.f[0] - 1);
+            const long long cost = waves * steps * (th + g.f[1] - 1);
+            if (best_cost < 0 || cost < best_cost)
+            {
+                best_cost = cost;
+                best_th = th;
+                best_ns = ns;
+            }
+        }
+    }
+    g.th = best_th;
+    g.nseg = best_ns;
+    g.rows = g.th + g.f[1] - 1;
+    const int row_bytes = g.w_c_total * TC_RAW_W * 4;
+    int rc_max = (17 * 1024 + 512) / row_bytes;
+    rc_max = rc_max < 1 ? 1 : rc_max;
+    g.chunks_pp = (g.rows + rc_max - 1) / rc_max;
+    g.chunk_rows = (g.rows + g.chunks_pp - 1) / g.chunks_pp;
+    g.raw_slot_bytes = (g.chunk_rows * row_bytes + 127) / 128 * 128;
+    int slots = (54 * 1024) / g.raw_slot_bytes;
+    slots = slots > 4 ? 4 : slots;
+    if (slots < 2)
+        return false;
+    g.raw_slots = slots;
+    if (mg_smem_need(g) > 210 * 1024)
+        return false;
+    g.tiles_w = (g.out[2] + TC_M - 1) / TC_M;
+    g.tiles_h = (g.out[1] + g.th - 1) / g.th;
+    g.units = (long long) g.n * g.tiles_w * g.tiles_h * g.nseg;
+    if (g.units >= (1ll << 31))
+        return false;
+    *out = g;
+    return true;
+}
+
 size_t wg_smem_need(const WgGeom& g)
 {
     const size_t unit = (size_t) (g.xbuf_bytes + g.dybuf_bytes + 127) / 128 * 128;
@@ -379,6 +499,10 @@ struct TcPlan
     bool has_sw[2] = {false, false};
     SwGeom sw[2];
     float* sw_bimg[2] = {nullptr, nullptr};
+    // the multi-group sweep kernel (few filters, many input channels: backward data)
+    bool has_mg[2] = {false, false};
+    SwGeom mg[2];
+    float* mg_bimg[2] = {nullptr, nullptr};
     float* grp_scratch[2] = {nullptr, nullptr}; // dense outputs of the channel groups after the first
     float* stat_part = nullptr; // per epilogue warp partial sums of the fused statistics
     // tensor-core backward filter
@@ -399,6 +523,8 @@ int32_t tc_plan_create(const ConvGeom& fwd, const ConvGeom& bwd, bool bwd_is_fwd
     // is not 16-byte aligned, so it is only planned on top of it
     p->has_sw[0] = p->has[0] && sw_geom(fwd, math_mode, &p->sw[0]);
     p->has_sw[1] = p->has[1] && sw_geom(bwd, math_mode, &p->sw[1]);
+    p->has_mg[0] = p->has[0] && mg_geom(fwd, math_mode, &p->mg[0]);
+    p->has_mg[1] = p->has[1] && mg_geom(bwd, math_mode, &p->mg[1]);
     p->has_wg = wg_geom(fwd, math_mode, &p->wg);
     p->wg_cg = fwd;
     if (!p->has[0] && !p->has[1] && !p->has_wg)
@@ -414,7 +540,9 @@ int32_t tc_plan_create(const ConvGeom& fwd, const ConvGeom& bwd, bool bwd_is_fwd
             ok = cudaMalloc(&p->bimg[s], p->g[s].b_bytes) == cudaSuccess;
         if (ok && p->has_sw[s])
             ok = cudaMalloc(&p->sw_bimg[s], p->sw[s].b_bytes) == cudaSuccess;
-        if (ok && p->has_sw[s] && p->sw[s].cgroups > 1)
+        if (ok && p->has_mg[s])
+            ok = cudaMalloc(&p->mg_bimg[s], p->mg[s].b_bytes) == cudaSuccess;
+        if (ok && p->has_sw[s] && p->sw[s].cgroups > 1 && !p->has_mg[s])
             ok = cudaMalloc(&p->grp_scratch[s], sw_scratch_floats(p->sw[s]) * (p->sw[s].cgroups - 1) * sizeof(float))
                  == cudaSuccess;
     }
@@ -441,6 +569,8 @@ void tc_plan_destroy(TcPlan* p)
     cudaFree(p->bimg[1]);
     cudaFree(p->sw_bimg[0]);
     cudaFree(p->sw_bimg[1]);
+    cudaFree(p->mg_bimg[0]);
+    cudaFree(p->mg_bimg[1]);
     cudaFree(p->grp_scratch[0]);
     cudaFree(p->grp_scratch[1]);
     cudaFree(p->stat_part);
@@ -638,11 +768,92 @@ static int32_t sw_launch(const SwGeom& g, float alpha, const float* w, const flo
     return DCB_OK;
 }
 
+// Input map for the multi-group kernel: all channels of a chunk of rows.
+static bool mg_make_x_map(const SwGeom& g, const float* x, CUtensorMap* map)
+{
+    TcGeom t;
+    std::memset(&t, 0, sizeof(t));
+    for (int i = 0; i < 3; ++i)
+    {
+        t.in[i] = g.in[i];
+        t.xs[i] = g.xs[i];
+    }
+    t.n = g.n;
+    t.c = g.w_c_total;
+    t.xs_n = g.xs_n;
+    t.xs_c = g.xs_c;
+    t.chunk_rows = g.chunk_rows;
+    return make_x_map(t, x, map);
+}
+
+// Output map with a box of 32 outputs x MG_NBK filters.
+static bool mg_make_y_map(const SwGeom& g, float* y, CUtensorMap* map)
+{
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn || (reinterpret_cast<uintptr_t>(y) & 15) != 0)
+        return false;
+    const cuuint64_t dims[5] = {(cuuint64_t) g.out[2], (cuuint64_t) g.out[1], (cuuint64_t) g.out[0], (cuuint64_t) g.k,
+                                (cuuint64_t) g.n};
+    const long long s1 = g.out[1] > 1 ? g.ys[1] : g.out[2];
+    const long long s0 = g.out[0] > 1 ? g.ys[0] : s1 * g.out[1];
+    const long long sc = g.k > 1 ? g.ys_c : s0 * g.out[0];
+    const long long sn = g.n > 1 ? g.ys_n : sc * g.k;
+    const cuuint64_t strides[4] = {(cuuint64_t) s1 * 4, (cuuint64_t) s0 * 4, (cuuint64_t) sc * 4, (cuuint64_t) sn * 4};
+    for (int i = 0; i < 4; ++i)
+        if (strides[i] % 16 != 0 || strides[i] == 0)
+            return false;
+    const cuuint32_t box[5] = {32, 1, 1, (cuuint32_t) MG_NBK, 1};
+    const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 5, y, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE)
+           == CUDA_SUCCESS;
+}
+
+static int32_t mg_launch(const SwGeom& g, float alpha, const float* w, float* bimg, float* y, int* status,
+                         const CUtensorMap& xmap, cudaStream_t stream)
+{
+    CUtensorMap ymap;
+    std::memset(&ymap, 0, sizeof(ymap));
+    const int use_ymap = mg_make_y_map(g, y, &ymap) ? 1 : 0;
+    const long long total = (long long) g.b_bytes / 4;
+    mg_pack_filter_kernel<<<(unsigned) ((total + 255) / 256), 256, 0, stream>>>(w, bimg, g);
+    DCB_LAUNCH_CHECK();
+    size_t smem = mg_smem_need(g);
+    smem = smem < 120 * 1024 ? 120 * 1024 : smem;
+    long long grid = (long long) num_sms();
+    if (grid > g.units)
+        grid = g.units;
+    const bool c4f3 = g.c == 4 && g.f[2] == 3 && g.pad[2] == 1 && g.split;
+    if (c4f3)
+    {
+        DCB_CUDA_TRY(cudaFuncSetAttribute(mg_conv_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          (int) (224 * 1024)));
+        mg_conv_kernel<true><<<(unsigned) grid, TC_THREADS, smem, stream>>>(g, alpha, bimg, y, status, xmap, ymap,
+                                                                           use_ymap);
+    }
+    else
+    {
+        DCB_CUDA_TRY(cudaFuncSetAttribute(mg_conv_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          (int) (224 * 1024)));
+        mg_conv_kernel<false><<<(unsigned) grid, TC_THREADS, smem, stream>>>(g, alpha, bimg, y, status, xmap, ymap,
+                                                                            use_ymap);
+    }
+    DCB_LAUNCH_CHECK();
+    return DCB_OK;
+}
+
 int32_t tc_conv_fwd(TcPlan* p, int slot, float alpha, const float* x, const float* w, float beta, float* y,
                     cudaStream_t stream)
 {
     if (!p || slot < 0 || slot > 1 || !p->has[slot])
         return DCB_UNSUPPORTED;
+    if (p->has_mg[slot] && beta == 0.f)
+    {
+        CUtensorMap xmap;
+        std::memset(&xmap, 0, sizeof(xmap));
+        if (mg_make_x_map(p->mg[slot], x, &xmap))
+            return mg_launch(p->mg[slot], alpha, w, p->mg_bimg[slot], y, p->status, xmap, stream);
+    }
     if (p->has_sw[slot])
     {
         SwGeom sg = p->sw[slot];
@@ -658,14 +869,17 @@ int32_t tc_conv_fwd(TcPlan* p, int slot, float alpha, const float* x, const floa
             // The first group writes the output (blending with the old one if
             // beta asks for it); every further group writes its own dense
             // scratch slice with the plain, faster kernel, and one pass adds the
-            // slices into the output.
+            // slices into the output.  (Plans that normally take the
+            // multi-group kernel own no scratch: their rare beta != 0 calls
+            // blend every further group into the output instead.)
             const size_t slice = sw_scratch_floats(sg);
             for (int grp = 0; grp < sg.cgroups; ++grp)
             {
                 SwGeom lg = sg;
                 lg.w_c_off = grp * sg.c;
                 float* dst = y;
-                if (grp > 0)
+                const bool to_scratch = grp > 0 && p->grp_scratch[slot] != nullptr;
+                if (to_scratch)
                 {
                     const long long wp = (sg.out[2] + 3) / 4 * 4;
                     lg.ys[2] = 1;
@@ -676,11 +890,12 @@ int32_t tc_conv_fwd(TcPlan* p, int slot, float alpha, const float* x, const floa
                     dst = p->grp_scratch[slot] + (size_t) (grp - 1) * slice;
                 }
                 const int32_t st = sw_launch(lg, alpha, w, x + (size_t) grp * sg.c * sg.xs_c, p->sw_bimg[slot],
-                                             grp == 0 ? beta : 0.f, dst, p->status, maps[grp], stream);
+                                             grp == 0 ? beta : (to_scratch ? 0.f : 1.f), dst, p->status, maps[grp],
+                                             stream);
                 if (st != DCB_OK)
                     return st;
             }
-            if (sg.cgroups > 1)
+            if (sg.cgroups > 1 && p->grp_scratch[slot] != nullptr)
             {
                 const long long rows = (long long) sg.n * sg.k * sg.out[0] * sg.out[1];
                 sw_group_sum_kernel<<<(unsigned) rows, 128, 0, stream>>>(sg, p->grp_scratch[slot], slice,

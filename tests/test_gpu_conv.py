@@ -111,6 +111,8 @@ GEOMS = [
     (3, 5, 7, (9, 21), (3, 3), (1, 1), (2, 2), (1, 1)),                       # 2-D stride 2, odd extents
     (1, 4, 8, (6, 9, 36), (3, 2, 3), (1, 0, 1), (1, 1, 1), (1, 1, 1)),        # two filter rows: two converter groups
     (2, 3, 5, (5, 6, 40), (2, 1, 3), (1, 0, 1), (1, 1, 1), (1, 1, 1)),        # one filter row: one converter group
+    (2, 3, 12, (7, 10, 132), (3, 3, 3), (1, 1, 1), (1, 1, 1), (1, 1, 1)),     # backward data: 3 channel groups -> 3 filters
+    (1, 4, 16, (9, 30, 64), (3, 3, 3), (0, 1, 1), (1, 1, 1), (1, 1, 1)),      # backward data: tall columns, no padding in D
 ]
 
 

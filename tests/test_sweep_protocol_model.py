@@ -17,8 +17,10 @@ import random
 import pytest
 
 
-def simulate(groups, th, fh, steps, seed, virtual, wait_rows):
-    """Returns ("ok" | "deadlock", wrong_passes)."""
+def simulate(groups, th, fh, steps, seed, virtual, wait_rows, cg=1):
+    """Returns ("ok" | "deadlock", wrong_passes).  cg > 1: the multi-group
+    kernel, where row i is cg sub-rows dealt to the issuers in sequence and
+    row_done[i] needs all of them."""
     rnd = random.Random(seed)
     rows = th + fh - 1
     completions, arrivals = {}, {}
@@ -32,7 +34,10 @@ def simulate(groups, th, fh, steps, seed, virtual, wait_rows):
         barrier(("free", j))
 
     def arrive(name):
-        completions[name] += 1  # every barrier of the model has an arrival count of one
+        arrivals[name] += 1
+        if arrivals[name] == (cg if name[0] == "done" else 1):
+            arrivals[name] = 0
+            completions[name] += 1
 
     def passes(name, parity):
         return (completions[name] & 1) != parity
@@ -45,8 +50,9 @@ def simulate(groups, th, fh, steps, seed, virtual, wait_rows):
         base = 0
         for step in range(steps):
             parity, real = step & 1, step not in virtual
-            i = (mq + groups - base % groups) % groups if real else mq
-            while i < rows:
+            q = (mq + groups - base % groups) % groups if real else mq
+            while q < rows * cg:
+                i = q // cg
                 for j in wait_rows(i, th, fh):
                     while not passes(("free", j), parity):
                         yield "wait"
@@ -54,9 +60,9 @@ def simulate(groups, th, fh, steps, seed, virtual, wait_rows):
                         wrong.append(("issuer", mq, step, i, j))
                 yield "work"
                 arrive(("done", i))
-                i += groups
+                q += groups
             if real:
-                base = (base + rows) % groups
+                base = (base + rows * cg) % groups
 
     def epilogue(half):
         for step in range(steps):
@@ -111,3 +117,11 @@ def test_protocol_never_locks_or_passes_early(fh):
 def test_waiting_for_a_row_one_does_not_touch_locks_up():
     states = {simulate(3, 7, 3, 12, seed, (0, 1, 10, 11), last_two_rows)[0] for seed in range(20)}
     assert "deadlock" in states
+
+
+@pytest.mark.parametrize("cg", [3, 4, 8])
+def test_multi_group_protocol(cg):
+    for th in (2, 3, 7, 12, 24):
+        for seed in range(6):
+            state, wrong = simulate(3, th, 3, 8, seed, (0, 1, 6, 7), touched_rows, cg=cg)
+            assert state == "ok" and not wrong, (cg, th, seed, state, wrong[:2])
