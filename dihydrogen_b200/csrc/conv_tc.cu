@@ -399,7 +399,7 @@ bool mg_geom(const ConvGeom& cg, int math_mode, SwGeom* out)
 size_t wg_smem_need(const WgGeom& g)
 {
     const size_t unit = (size_t) (g.xbuf_bytes + g.dybuf_bytes + 127) / 128 * 128;
-    return 2 * unit + (size_t) WG_A_SLOTS * WG_B_FLOATS * 4 + (2 * WG_A_SLOTS + 5) * 8 + 64 + 1024;
+    return 2 * unit + (size_t) WG_A_SLOTS * WG_B_FLOATS * 4 + (2 * WG_A_SLOTS + 8) * 8 + 64 + 1024;
 }
 
 // Geometry of the tensor-core backward filter: x is the forward input window,

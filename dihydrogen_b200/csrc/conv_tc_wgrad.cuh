@@ -9,10 +9,11 @@
 // rows = TMEM lanes), N = the filters.  For one chunk of eight outputs
 //   A[m][kk] = x[c][od+kd-pd][oh+kh-ph][ow0 + kk + kw-pw]     (tensor memory)
 //   B[kk][k] = dy[k][od][oh][ow0 + kk]                        (shared memory)
-// and the accumulator D[m][k] stays in tensor memory for the whole kernel:
-// there is no epilogue until the CTA has walked all its units, then every CTA
-// writes its 128 x 16 partial filter and a second kernel folds the partials in
-// CTA order (fp64) and applies alpha / beta.
+// and the accumulator D[m][k] stays in tensor memory: two buffers, swapped every
+// WG_FLUSH_UNITS units; four dump warps add the idle one into fp64 registers and
+// zero it.  When the CTA has walked all its units it writes its 128 x 16 partial
+// filter, and a second kernel folds the partials in CTA order (fp64) and applies
+// alpha / beta.
 //
 // 3xTF32: D[:, 0:32] += A_hi x [B_hi | B_lo] (one instruction, N = 32) and
 // D[:, 0:16] += A_lo x B_hi (N = 16); the fold adds the two column halves.
@@ -45,7 +46,15 @@ constexpr int WG_XW = WG_TW + 12;          // staged input row: 4 cells of margi
                                            // columns) on different banks, 136 would fold them three deep
 constexpr int WG_A_SLOTS = 6;              // two per group
 constexpr int WG_A_COLS = 16 * WG_KS;      // an A slot: per k-step 8 hi + 8 lo columns
-constexpr uint32_t WG_TMEM_COLS = 256;     // 32 accumulator columns + 6 A slots
+constexpr uint32_t WG_TMEM_COLS = 256;     // two accumulator buffers of 32 columns + 6 A slots
+constexpr int WG_ACC_COLS = 64;            // the A ring starts here
+// The tensor pipe adds into an fp32 accumulator without rounding to nearest: over
+// a chain of n updates the error grows like n^1.5 * 2^-24 and does not average
+// out.  Measured on a 256^3 shard with one accumulator for the whole run: 4e-4
+// of the gradient's scale.  So a chain is cut after this many units (1024
+// outputs, 128 updates): the dump warps add the buffer into fp64 registers and
+// zero it while the issuers fill the other one (5e-6 by the same estimate).
+constexpr int WG_FLUSH_UNITS = 8;
 constexpr int WG_B_FLOATS = 256 * WG_KS;   // the B tiles of a chunk: per k-step 8 x 32 floats
 
 struct WgGeom
@@ -90,8 +99,9 @@ __global__ void __launch_bounds__(WG_THREADS, 1)
     uint64_t* a_empty = a_full + WG_A_SLOTS; // [6]
     uint64_t* u_full = a_empty + WG_A_SLOTS; // [2]
     uint64_t* u_empty = u_full + 2;          // [2]
-    uint64_t* all_done = u_empty + 2;        // [1]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(all_done + 1);
+    uint64_t* d_full = u_empty + 2;          // [2] issuers -> dump warps: a batch of units is in the buffer
+    uint64_t* d_empty = d_full + 2;          // [2] dump warps -> issuers: the buffer is zero again
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(d_empty + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -107,7 +117,11 @@ __global__ void __launch_bounds__(WG_THREADS, 1)
             mbar_init(&u_full[b], 1);
             mbar_init(&u_empty[b], 12);
         }
-        mbar_init(all_done, 3);
+        for (int b = 0; b < 2; ++b)
+        {
+            mbar_init(&d_full[b], 3);
+            mbar_init(&d_empty[b], 4);
+        }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -122,17 +136,6 @@ __global__ void __launch_bounds__(WG_THREADS, 1)
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    // zero the accumulators (the dump warps own all four lane quadrants)
-    if (warp >= WG_DUMP_WARP)
-    {
-        const uint32_t la = tmem_base + ((uint32_t) ((warp & 3) * 32) << 16);
-        tmem_st16_zero(la);
-        tmem_st16_zero(la + 16);
-        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
 
     const uint32_t nunits = (uint32_t) g.units;
     bool ok = true;
@@ -207,7 +210,7 @@ __global__ void __launch_bounds__(WG_THREADS, 1)
                 if (!ok)
                     break;
                 tc_fence_after();
-                const uint32_t a_addr = lane_addr + 32u + (uint32_t) (slot * WG_A_COLS);
+                const uint32_t a_addr = lane_addr + (uint32_t) WG_ACC_COLS + (uint32_t) (slot * WG_A_COLS);
                 float* bt = bring + slot * WG_B_FLOATS;
 #pragma unroll
                 for (int ks = 0; ks < WG_KS; ++ks)
@@ -279,9 +282,22 @@ __global__ void __launch_bounds__(WG_THREADS, 1)
         const uint32_t idesc32 = (1u << 4) | (2u << 7) | (2u << 10) | ((128u >> 4) << 24) | ((32u >> 3) << 17);
         const uint32_t idesc16 = (1u << 4) | (2u << 7) | (2u << 10) | ((128u >> 4) << 24) | ((16u >> 3) << 17);
         int lap = 0;
-        uint32_t full_phase = 0, seq = 0;
-        for (uint32_t u = blockIdx.x; u < nunits && ok; u += gridDim.x)
+        uint32_t full_phase = 0, seq = 0, ul = 0;
+        bool open = false; // a batch this issuer has added into and not yet handed over
+        uint32_t batch = 0;
+        for (uint32_t u = blockIdx.x; u < nunits && ok; u += gridDim.x, ++ul)
         {
+            batch = ul / WG_FLUSH_UNITS;
+            const uint32_t db = batch & 1;
+            if (ul % WG_FLUSH_UNITS == 0)
+            {
+                // the buffer must have been drained and zeroed (initially: zeroed)
+                ok = mbar_wait_t<0>(&d_empty[db], (batch >> 1) & 1, abort_flag);
+                if (!ok)
+                    break;
+                open = true;
+            }
+            const uint32_t d_addr = tmem_base + db * 32u;
             int q = (mq + 3 - (int) (seq % 3u)) % 3;
             for (; q < WG_CHUNKS && ok; q += 3)
             {
@@ -292,16 +308,16 @@ __global__ void __launch_bounds__(WG_THREADS, 1)
                 tc_fence_after();
                 if (lane == 0)
                 {
-                    const uint32_t a_addr = tmem_base + 32u + (uint32_t) (slot * WG_A_COLS);
+                    const uint32_t a_addr = tmem_base + (uint32_t) WG_ACC_COLS + (uint32_t) (slot * WG_A_COLS);
                     // B tile of a k-step: [2 k-chunks][4 filter groups][8][4]: 512 bytes
                     // between the k-chunks, 128 between the filter groups, 1 KiB per tile
                     const uint64_t bd = make_desc(smem_u32(bring + slot * WG_B_FLOATS), 512u, 128u, 0u);
 #pragma unroll
                     for (int ks = 0; ks < WG_KS; ++ks)
                     {
-                        mma_tf32_ts(tmem_base, a_addr + (uint32_t) (ks * 16), bd + (uint64_t) (ks * 64),
+                        mma_tf32_ts(d_addr, a_addr + (uint32_t) (ks * 16), bd + (uint64_t) (ks * 64),
                                     idesc32); // A_hi x [B_hi | B_lo]
-                        mma_tf32_ts(tmem_base, a_addr + (uint32_t) (ks * 16 + 8), bd + (uint64_t) (ks * 64),
+                        mma_tf32_ts(d_addr, a_addr + (uint32_t) (ks * 16 + 8), bd + (uint64_t) (ks * 64),
                                     idesc16); // A_lo x B_hi
                     }
                     mma_commit(&a_empty[slot]);
@@ -315,59 +331,77 @@ __global__ void __launch_bounds__(WG_THREADS, 1)
                 }
             }
             seq += WG_CHUNKS;
+            if (ok && ul % WG_FLUSH_UNITS == WG_FLUSH_UNITS - 1)
+            {
+                // this issuer's share of the batch has completed when this arrives
+                if (lane == 0)
+                    mma_commit(&d_full[db]);
+                __syncwarp();
+                open = false;
+            }
         }
-        // everything this issuer sent has completed when this arrives
-        if (lane == 0)
+        if (ok && open)
         {
-            tc_fence_after();
-            mma_commit(all_done);
+            if (lane == 0)
+                mma_commit(&d_full[batch & 1]);
+            __syncwarp();
         }
-        __syncwarp();
     }
     else if (warp >= WG_DUMP_WARP)
     {
         // ------------------------------------------------------------------
-        // the CTA's partial filter: D[:, 0:16] + D[:, 16:32]
+        // dump warps: zero both buffers, then per batch add the buffer into
+        // fp64 registers (D[:, 0:16] + D[:, 16:32]) and zero it again; at the
+        // end write the CTA's partial filter
         // ------------------------------------------------------------------
-        // This wait spans the whole run, so it has no clock budget of its own:
-        // it ends when the issuers are done or when any role has given up (every
-        // other wait is bounded and raises the abort flag), and after at most
-        // 2^26 polls.
-        ok = false;
-        for (uint32_t it = 0; it < (1u << 26); ++it)
+        const int quad = warp & 3;
+        const uint32_t la = tmem_base + ((uint32_t) (quad * 32) << 16);
+        for (int col = 0; col < WG_ACC_COLS; col += 16)
+            tmem_st16_zero(la + col);
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0)
         {
-            uint32_t done;
-            asm volatile(
-                "{\n\t"
-                ".reg .pred p;\n\t"
-                "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-                "selp.b32 %0, 1, 0, p;\n\t"
-                "}"
-                : "=r"(done)
-                : "r"(smem_u32(all_done)), "r"(0u)
-                : "memory");
-            if (done)
-            {
-                ok = true;
+            mbar_arrive(&d_empty[0]);
+            mbar_arrive(&d_empty[1]);
+        }
+        double acc[16];
+#pragma unroll
+        for (int k = 0; k < 16; ++k)
+            acc[k] = 0.0;
+        uint32_t my_units = 0;
+        for (uint32_t u = blockIdx.x; u < nunits; u += gridDim.x)
+            ++my_units;
+        const uint32_t nbatches = (my_units + WG_FLUSH_UNITS - 1) / WG_FLUSH_UNITS;
+        for (uint32_t bt = 0; bt < nbatches && ok; ++bt)
+        {
+            const uint32_t db = bt & 1;
+            ok = mbar_wait(&d_full[db], (bt >> 1) & 1, abort_flag);
+            if (!ok)
                 break;
-            }
-            if (*abort_flag)
-                break;
-            __nanosleep(1000);
+            tc_fence_after();
+            uint32_t v0[16], v1[16];
+            tmem_ld16(la + db * 32u, v0);
+            tmem_ld16(la + db * 32u + 16u, v1);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            tmem_st16_zero(la + db * 32u);
+            tmem_st16_zero(la + db * 32u + 16u);
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0)
+                mbar_arrive(&d_empty[db]);
+#pragma unroll
+            for (int k = 0; k < 16; ++k)
+                acc[k] += (double) __uint_as_float(v0[k]) + (double) __uint_as_float(v1[k]);
         }
         if (ok)
         {
-            tc_fence_after();
-            const int quad = warp & 3;
-            const uint32_t la = tmem_base + ((uint32_t) (quad * 32) << 16);
-            uint32_t v0[16], v1[16];
-            tmem_ld16(la, v0);
-            tmem_ld16(la + 16, v1);
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
             float* o = part + ((size_t) blockIdx.x * 128 + quad * 32 + lane) * 16;
 #pragma unroll
             for (int k = 0; k < 16; ++k)
-                o[k] = __uint_as_float(v0[k]) + __uint_as_float(v1[k]);
+                o[k] = (float) acc[k];
         }
     }
 

@@ -237,3 +237,40 @@ def test_backward_filter_tensor_core_ragged_tiles_and_batch():
     _, _, dw = run_all(x, w, dy, [1] * 3, [1] * 3, [1] * 3, _abi.MATH_FP32, alpha=0.5, beta=2.0,
                        y0=np.zeros(dy.shape, np.float32), dx0=np.zeros(x.shape, np.float32), dw0=dw0)
     emu.assert_close(dw, O.conv_bwd_filter(x, dy, f, [1] * 3, [1] * 3, alpha=0.5, beta=2.0, dw=dw0.copy()), TOL, "dw")
+
+
+@pytest.mark.parametrize("mode", MODES)
+def test_backward_filter_full_shard_against_fp64_sums(mode):
+    """The 256^3 shard of the benchmark: every filter gradient is a sum over
+    16.7 M voxels, where an accumulator that truncates instead of rounding shows
+    (4e-4 with one tensor-memory chain for the whole run).  Sampled taps are
+    recomputed as fp64 dot products and must agree within the fp32 contract."""
+    D = 256
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    x = torch.randn(1, 4, D, 256, 256, device="cuda", generator=gen)
+    dy = torch.randn(1, 16, D, 256, 256, device="cuda", generator=gen)
+    dy += 0.5  # a mean, so that sums do not hide a bias behind cancellation
+    x += 0.25
+    w = torch.zeros(16, 4, 3, 3, 3, device="cuda")
+    dw = torch.zeros_like(w)
+    p = Plan(x, w, dy, [1] * 3, [1] * 3, [1] * 3, mode)
+    p.bwd_filter(1.0, x, dy, 0.0, dw)
+    torch.cuda.synchronize()
+    assert _abi.lib().dcb_conv_plan_status(p.p, None) == _abi.OK
+    dyd = dy[0].double()
+    got, ref = [], []
+    for c, (td, th, tw) in [(0, (0, 0, 0)), (1, (1, 1, 1)), (2, (2, 2, 2)), (3, (0, 2, 1)), (1, (2, 0, 1)), (2, (1, 2, 0))]:
+        # dw[k][c][t] = sum_o dy[k][o] * x[c][o + t - 1]
+        xs = torch.zeros(D, 256, 256, device="cuda", dtype=torch.float64)
+        sl_o, sl_i = [], []
+        for t, n in ((td, D), (th, 256), (tw, 256)):
+            lo, hi = max(0, 1 - t), min(n, n + 1 - t)
+            sl_o.append(slice(lo, hi))
+            sl_i.append(slice(lo + t - 1, hi + t - 1))
+        xs[tuple(sl_o)] = x[0, c][tuple(sl_i)].double()
+        ref.append((dyd * xs).sum(dim=(1, 2, 3)))
+        got.append(dw[:, c, td, th, tw].double())
+        del xs
+    got, ref = torch.stack(got), torch.stack(ref)
+    err = ((got - ref).abs() / (ref.abs() + ref.pow(2).mean().sqrt())).max().item()
+    assert err <= TOL, err
