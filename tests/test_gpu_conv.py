@@ -274,3 +274,38 @@ def test_backward_filter_full_shard_against_fp64_sums(mode):
     got, ref = torch.stack(got), torch.stack(ref)
     err = ((got - ref).abs() / (ref.abs() + ref.pow(2).mean().sqrt())).max().item()
     assert err <= TOL, err
+
+
+def test_forward_with_statistics_full_shard():
+    """The benchmark's 256^3 shard: the fused per-filter sums against fp64 sums
+    of the output, and the output on a sampled block against an fp64 convolution."""
+    D = 256
+    gen = torch.Generator(device="cuda").manual_seed(9)
+    x = torch.randn(1, 4, D, 256, 256, device="cuda", generator=gen) + 0.3
+    w = torch.randn(16, 4, 3, 3, 3, device="cuda", generator=gen) * 0.14
+    y = torch.zeros(1, 16, D, 256, 256, device="cuda")
+    p = Plan(x, w, y, [1] * 3, [1] * 3, [1] * 3, _abi.MATH_FP32)
+    sums, sq = torch.zeros(16, device="cuda"), torch.zeros(16, device="cuda")
+    st = _abi.lib().dcb_conv_fwd_stats(p.p, 1.0, ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(w.data_ptr()),
+                                       ctypes.c_void_p(y.data_ptr()), ctypes.c_void_p(sums.data_ptr()),
+                                       ctypes.c_void_p(sq.data_ptr()), None)
+    assert st == _abi.OK, st
+    torch.cuda.synchronize()
+    assert _abi.lib().dcb_conv_plan_status(p.p, None) == _abi.OK
+    s64, q64 = torch.zeros(16, dtype=torch.float64, device="cuda"), torch.zeros(16, dtype=torch.float64, device="cuda")
+    for d0 in range(0, D, 32):
+        blk = y[0, :, d0:d0 + 32].double()
+        s64 += blk.sum(dim=(1, 2, 3))
+        q64 += (blk * blk).sum(dim=(1, 2, 3))
+    emu.assert_close(sums.cpu().numpy(), s64.cpu().numpy(), TOL, "sums")
+    emu.assert_close(sq.cpu().numpy(), q64.cpu().numpy(), TOL, "sqsums")
+    # a block that touches three faces of the shard and its far corner
+    for sl in ((slice(0, 6), slice(0, 40), slice(0, 256)), (slice(D - 6, D), slice(216, 256), slice(0, 256))):
+        lo = [max(0, s.start - 1) for s in sl]
+        hi = [min(n, s.stop + 1) for s, n in zip(sl, (D, 256, 256))]
+        xb = x[:, :, lo[0]:hi[0], lo[1]:hi[1], lo[2]:hi[2]].double()
+        pad = []
+        for s, l, h, n in reversed(list(zip(sl, lo, hi, (D, 256, 256)))):
+            pad += [1 - (s.start - l), 1 - (h - s.stop)]
+        ref = torch.nn.functional.conv3d(torch.nn.functional.pad(xb, pad), w.double())
+        emu.assert_close(y[:, :, sl[0], sl[1], sl[2]].cpu().numpy(), ref.cpu().numpy(), TOL, "y block")
