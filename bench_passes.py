@@ -1,8 +1,14 @@
 #!/usr/bin/env python
-"""Per-pass timing of the layer's operators on one GPU, BASELINE configs[1]
-shard (N=1, C=4 -> K=16, 3x3x3, stride 1, pad 1, fp32, D x 256 x 256):
+"""Per-pass timing of the layer's operators on one GPU, on the per-GPU shard
+of a BASELINE configuration (fp32):
 
-    python bench_passes.py [--local-d D] [--reps R]
+    python bench_passes.py [--shape cfg2|cfg3l2|cfg4] [--local-d D] [--reps R]
+
+    cfg2    N=1, C=4 -> K=16, 3x3x3, stride 1, pad 1, D x 256 x 256 (default; also
+            layer 1 of configs[2] at 8 GPUs)
+    cfg3l2  layer 2 of configs[2] at 8 GPUs: N=1, C=16 -> K=32, 3x3x3, stride 2,
+            pad 1, 256^3 -> 128^3
+    cfg4    configs[3] at 8 GPUs: N=2, C=32 -> K=32, 5x5, pad 2, 2048 x 1024
 
 Times, with CUDA events on the launching stream and inputs resident in HBM:
 convolution forward (with and without the BN statistics in its epilogue),
@@ -18,41 +24,61 @@ import json
 import os
 import sys
 
+import numpy as np
+
 ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 
+# name: (N, C, K, spatial input extents slowest first, filter, stride, pad)
+SHAPES = {
+    "cfg2": (1, 4, 16, [256, 256, 256], [3, 3, 3], 1, 1),
+    "cfg3l2": (1, 16, 32, [256, 256, 256], [3, 3, 3], 2, 1),
+    "cfg4": (2, 32, 32, [2048, 1024], [5, 5], 1, 2),
+}
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--local-d", type=int, default=256)
+    ap.add_argument("--shape", choices=sorted(SHAPES), default="cfg2")
+    ap.add_argument("--local-d", type=int, default=None, help="cfg2 / cfg3l2: D extent of the input shard")
     ap.add_argument("--reps", type=int, default=5)
     args = ap.parse_args()
     import torch
 
     import dihydrogen_b200 as dc
     from dihydrogen_b200 import _abi
-    from bench import C_IN, K_OUT, DECAY, EPS, layer_geometry
+    from bench import DECAY, EPS
 
     if not torch.cuda.is_available():
         raise SystemExit("bench_passes.py needs a CUDA device")
     torch.manual_seed(0)
     locale = dc.Locale(0, 1)
-    geo = layer_geometry(1, locale, local_d=args.local_d)
-    x, y, z = geo["input"], geo["conv_out"], geo["bn_out"]
+    N, C_IN, K_OUT, sp, f, stride, pad = SHAPES[args.shape]
+    sp = list(sp)
+    if args.local_d and len(sp) == 3:
+        sp[0] = args.local_d
+    nsd = len(sp)
+    strides, dil, pads = [stride] * nsd, [1] * nsd, [pad] * nsd
+    fshape = list(reversed(f)) + [C_IN, K_OUT]
+    x = dc.create_input_tensor(list(reversed(sp)) + [C_IN, N], [1] * (nsd + 2), list(reversed(f)), strides, dil,
+                               locale)
+    y = dc.create_convolution_output_tensor(x, fshape, strides, pads, dil)
+    z = dc.Tensor(y.shape, locale, y.dist, y._local_of)
     dx = dc.create_d_input_tensor(x)
-    dy = dc.create_convolution_d_output_tensor(y, geo["filter_shape"], geo["dilations"])
+    dy = dc.create_convolution_d_output_tensor(y, fshape, dil)
     dz = dc.Tensor(y.shape, locale, y.dist, y._local_of)
     for t in (x, y, z, dx, dy, dz):
         t.allocate()
     x.buffer.normal_()
     dz.buffer.normal_()
-    w = torch.randn(K_OUT, C_IN, 3, 3, 3, device="cuda") * 0.14
+    w = torch.randn(K_OUT, C_IN, *f, device="cuda") * (2.0 / (C_IN * int(np.prod(f)))) ** 0.5
     dw = torch.zeros_like(w)
     be = dc.BackendDNNLib(locale, options=dc.Options(), allreduce="peer", allreduce_max_count=4096)
-    conv = dc.Convolution(be, 5)
-    conv.setup(x, w, y, dx, None, dy, geo["pads"], geo["strides"], geo["dilations"])
-    bn = dc.BatchNormalization(be, 5, DECAY, EPS, True)
+    conv = dc.Convolution(be, nsd + 2)
+    conv.setup(x, w, y, dx, None, dy, pads, strides, dil)
+    bn = dc.BatchNormalization(be, nsd + 2, DECAY, EPS, True)
     K = K_OUT
     stats = torch.zeros(2 * K, device="cuda")
     mean, var = stats[:K], stats[K:]
@@ -75,8 +101,10 @@ def main():
 
     ms = {}
     ms["conv_fwd"] = timed(lambda: conv.forward(1.0, x, w, 0.0, y, skip_halo_exchange=True))
-    ms["conv_fwd_with_bn_statistics"] = timed(
-        lambda: conv.forward(1.0, x, w, 0.0, y, skip_halo_exchange=True, statistics=(mean, var)))
+    fused = conv.forward(1.0, x, w, 0.0, y, skip_halo_exchange=True, statistics=(mean, var)) == 1
+    if fused:
+        ms["conv_fwd_with_bn_statistics"] = timed(
+            lambda: conv.forward(1.0, x, w, 0.0, y, skip_halo_exchange=True, statistics=(mean, var)))
     ms["bn_stats"] = timed(lambda: bn.forward_stage1(y, mean, var, True))
     bn.forward(y, mean, var, rm, rv, scale, bias, z, True)
     ms["bn_finalize_apply"] = timed(lambda: bn.forward_stage2(y, mean, var, rm, rv, scale, bias, z, True))
@@ -84,13 +112,18 @@ def main():
     ms["bn_bwd_apply"] = timed(lambda: bn.backward_stage2(y, dz, mean, var, scale, g[2], g[3], dy))
     ms["conv_bwd_filter"] = timed(lambda: conv.backward_filter(1.0, x, dy, 0.0, dw, reduce=False))
     ms["conv_bwd_data"] = timed(lambda: conv.backward_data(1.0, w, dy, 0.0, dx, skip_halo_exchange=True))
-    vox = args.local_d * 256 * 256
-    fwd = ms["conv_fwd_with_bn_statistics"] + ms["bn_finalize_apply"]
+    vox = N * int(np.prod(sp))
+    out_vox = N * int(np.prod([(e + 2 * pad - fe) // stride + 1 for e, fe in zip(sp, f)]))
+    flop = 2.0 * out_vox * K_OUT * C_IN * int(np.prod(f))
+    fwd = (ms["conv_fwd_with_bn_statistics"] if fused else ms["conv_fwd"] + ms["bn_stats"]) + ms["bn_finalize_apply"]
     bwd = ms["bn_bwd_reduce"] + ms["bn_bwd_apply"] + ms["conv_bwd_filter"] + ms["conv_bwd_data"]
     kinds = {n: ("tcgen05" if conv.kernel_kind(i) == 1 else "fp32-simt")
              for i, n in enumerate(("conv_fwd", "conv_bwd_data", "conv_bwd_filter"))}
-    print(json.dumps({"workload": f"configs[1] shard, {args.local_d} x 256 x 256, C=4 -> K=16, 3x3x3",
+    print(json.dumps({"workload": f"{args.shape} shard, N={N}, {' x '.join(map(str, sp))}, C={C_IN} -> K={K_OUT}, "
+                                  f"{'x'.join(map(str, f))}, stride {stride}",
                       "ms": {k: round(v, 4) for k, v in ms.items()}, "kernels": kinds,
+                      "conv_tflops": {k: round(flop / (ms[k] * 1e-3) / 1e12, 2)
+                                      for k in ("conv_fwd", "conv_bwd_data", "conv_bwd_filter")},
                       "forward_ms": round(fwd, 4), "backward_ms": round(bwd, 4),
                       "forward_backward_voxels_per_s": vox / ((fwd + bwd) * 1e-3),
                       "status": [conv.halo_xch_input.status(), int(_abi.lib().dcb_conv_plan_status(conv._plan_fwd, None)),

@@ -26,9 +26,10 @@ __global__ void __launch_bounds__(FWD_TX* FWD_TY)
     const int tid = ty * FWD_TX + tx;
     const int kt = blockIdx.z % ktiles;
     const int n = blockIdx.z / ktiles;
-    const int od = blockIdx.y / oh_tiles;
-    const int oh = (blockIdx.y % oh_tiles) * FWD_TY + ty;
-    const int ow_base = blockIdx.x * (FWD_TX * WT) + tx;
+    // the (plane, row tile) product is the large one: it rides on grid.x
+    const int od = blockIdx.x / oh_tiles;
+    const int oh = (blockIdx.x % oh_tiles) * FWD_TY + ty;
+    const int ow_base = blockIdx.y * (FWD_TX * WT) + tx;
     const bool row_ok = oh < g.out[1];
 
     float acc[WT][KT];
@@ -146,13 +147,13 @@ static int32_t launch_fwd(const ConvGeom& g, float alpha, const float* x,
     const int oh_tiles = (g.out[1] + FWD_TY - 1) / FWD_TY;
     const long long gy = (long long) oh_tiles * g.out[0];
     const long long gz = (long long) g.n * ktiles;
-    if (gy > 65535 || gz > 65535)
+    const long long gw = (g.out[2] + FWD_TX * WT - 1) / (FWD_TX * WT);
+    if (gy > 0x7fffffffll || gw > 65535 || gz > 65535)
     {
         set_last_error("tensor too large for the fp32 forward kernel grid");
         return DCB_UNSUPPORTED;
     }
-    dim3 grid((g.out[2] + FWD_TX * WT - 1) / (FWD_TX * WT), (unsigned) gy,
-              (unsigned) gz);
+    dim3 grid((unsigned) gy, (unsigned) gw, (unsigned) gz);
     dim3 block(FWD_TX, FWD_TY);
     conv_fwd_kernel<KT, WT><<<grid, block, smem, stream>>>(
         g, alpha, beta, x, w, y, ctile, ktiles, oh_tiles);
@@ -214,9 +215,9 @@ __global__ void __launch_bounds__(BWD_THREADS)
 {
     extern __shared__ __align__(16) float ws[]; // [ktile][taps][CT]
     const int taps = g.f[0] * g.f[1] * g.f[2];
-    const int iw = blockIdx.x * BWD_THREADS + threadIdx.x;
-    const int ih = blockIdx.y % g.in[1];
-    const int id = blockIdx.y / g.in[1];
+    const int iw = blockIdx.y * BWD_THREADS + threadIdx.x;
+    const int ih = blockIdx.x % g.in[1];
+    const int id = blockIdx.x / g.in[1];
     const int ct = blockIdx.z % ctiles;
     const int n = blockIdx.z / ctiles;
     float acc[CT];
@@ -317,13 +318,13 @@ static int32_t launch_bwd_data(const ConvGeom& g, float alpha, const float* w,
     const int ctiles = (g.c + CT - 1) / CT;
     const long long gy = (long long) g.in[0] * g.in[1];
     const long long gz = (long long) g.n * ctiles;
-    if (gy > 65535 || gz > 65535)
+    const long long gw = (g.in[2] + BWD_THREADS - 1) / BWD_THREADS;
+    if (gy > 0x7fffffffll || gw > 65535 || gz > 65535)
     {
         set_last_error("tensor too large for the fp32 backward-data grid");
         return DCB_UNSUPPORTED;
     }
-    dim3 grid((g.in[2] + BWD_THREADS - 1) / BWD_THREADS, (unsigned) gy,
-              (unsigned) gz);
+    dim3 grid((unsigned) gy, (unsigned) gw, (unsigned) gz);
     conv_bwd_data_kernel<CT><<<grid, BWD_THREADS, smem, stream>>>(
         g, alpha, beta, w, dy, dx, ktile, ctiles);
     DCB_LAUNCH_CHECK();

@@ -23,6 +23,8 @@
 //
 // Every wait on an mbarrier is bounded; on expiry the kernel records an error,
 // releases its tensor memory and returns.
+#include <vector>
+
 #include "conv_tc.cuh"
 #include "conv_tc_kernel.cuh"
 #include "conv_tc_sweep.cuh"
@@ -85,25 +87,42 @@ bool tc_geom(const ConvGeom& cg, int math_mode, TcGeom* out)
         g.ys[i] = cg.ys[i];
     }
     g.n = cg.n;
-    g.c = cg.c;
-    g.k = cg.k;
     g.xs_n = cg.xs_n;
     g.xs_c = cg.xs_c;
     g.ys_n = cg.ys_n;
     g.ys_c = cg.ys_c;
-    if ((long long) cg.n * cg.out[0] * cg.out[1] * cg.out[2] == 0)
+    if ((long long) cg.n * cg.out[0] * cg.out[1] * cg.out[2] == 0 || cg.c == 0 || cg.k == 0)
         return false;
     g.split = math_mode == DCB_MATH_TF32 ? 0 : 1;
+    const int mult = g.split ? 2 : 1;
+    // Filters per launch: the fh accumulator blocks of an input row are one
+    // instruction's N (<= 256 columns).
+    g.k_total = cg.k;
     g.kpad = cg.k <= 8 ? 8 : (cg.k <= 16 ? 16 : 32);
-    if (cg.k > 32)
-        return false;
-    g.nb = g.kpad * (g.split ? 2 : 1);
+    while (g.kpad > 8 && g.f[1] * g.kpad * mult > 256)
+        g.kpad /= 2;
+    g.k = cg.k < g.kpad ? cg.k : g.kpad;
+    g.kgroups = (cg.k + g.kpad - 1) / g.kpad;
+    g.nb = g.kpad * mult;
     if (g.nb < 16)
         g.nb = 16;
     g.ntot = g.f[1] * g.nb;
     if (g.ntot > 256 || g.ntot % 16)
         return false;
-    if (g.c > 16)
+    // Channels per launch: a staged row is c * fw taps (hi and lo) of k-rows in
+    // tensor memory; at most 96 keeps two converter groups busy.
+    g.c_total = cg.c;
+    g.c = 0;
+    for (int d = cg.c; d >= 1; --d)
+        if (cg.c % d == 0 && (d * g.f[2] * mult + 7) / 8 * 8 <= 96)
+        {
+            g.c = d;
+            break;
+        }
+    if (g.c == 0)
+        return false;
+    g.cgroups = cg.c / g.c;
+    if (g.cgroups * g.kgroups > 64)
         return false;
     for (int i = 0; i < 3; ++i)
         if (g.pad[i] > g.f[i] - 1)
@@ -412,8 +431,9 @@ bool wg_geom(const ConvGeom& cg, int math_mode, WgGeom* out)
         return false;
     for (int i = 0; i < 3; ++i)
     {
-        if (cg.stride[i] != 1 || cg.dil[i] != 1)
+        if (cg.stride[i] < 1 || cg.stride[i] > 2 || cg.dil[i] != 1)
             return false;
+        g.stride[i] = cg.stride[i];
         g.in[i] = cg.in[i];
         g.out[i] = cg.out[i];
         g.f[i] = cg.f[i];
@@ -422,11 +442,24 @@ bool wg_geom(const ConvGeom& cg, int math_mode, WgGeom* out)
             return false;
     }
     g.n = cg.n;
-    g.c = cg.c;
-    g.k = cg.k;
-    g.mrows = g.c * g.f[0] * g.f[1] * g.f[2];
-    if (g.mrows > 128 || g.k > 16 || g.mrows == 0)
+    g.c_total = cg.c;
+    g.k_total = cg.k;
+    const int taps = g.f[0] * g.f[1] * g.f[2];
+    g.c = 0;
+    for (int d = cg.c; d >= 1; --d)
+        if (cg.c % d == 0 && d * taps <= 128)
+        {
+            g.c = d;
+            break;
+        }
+    if (g.c == 0 || cg.k == 0)
         return false;
+    g.cgroups = cg.c / g.c;
+    g.k = cg.k < 16 ? cg.k : 16;
+    g.kgroups = (cg.k + 15) / 16;
+    if (g.cgroups * g.kgroups > 64)
+        return false; // every launch reads dy again: the CUDA-core kernel does better
+    g.mrows = g.c * taps;
     if ((long long) cg.n * cg.out[0] * cg.out[1] * cg.out[2] == 0)
         return false;
     if (g.pad[2] > 4 || g.f[2] - 1 - g.pad[2] > 4 || g.f[1] > 16)
@@ -437,7 +470,8 @@ bool wg_geom(const ConvGeom& cg, int math_mode, WgGeom* out)
     if (!(cg.ys[1] % 4 == 0 && cg.ys[0] % 4 == 0 && cg.ys_c % 4 == 0 && cg.ys_n % 4 == 0))
         return false;
     g.xplane_bytes = g.c * g.f[1] * WG_XW * 4;
-    g.xplane_floats = (g.xplane_bytes + 127) / 128 * 128 / 4;
+    g.xhalf_floats = (g.xplane_bytes + 127) / 128 * 128 / 4;
+    g.xplane_floats = g.stride[2] * g.xhalf_floats;
     g.xbuf_bytes = g.f[0] * g.xplane_floats * 4;
     g.dybuf_bytes = 16 * WG_TW * 4;
     if (wg_smem_need(g) > 200 * 1024)
@@ -905,17 +939,32 @@ int32_t tc_conv_fwd(TcPlan* p, int slot, float alpha, const float* x, const floa
             return DCB_OK;
         }
     }
-    const TcGeom& g = p->g[slot];
-    const long long total = (long long) g.b_bytes / 4;
-    tc_pack_filter_kernel<<<(unsigned) ((total + 255) / 256), 256, 0, stream>>>(w, p->bimg[slot], g);
-    DCB_LAUNCH_CHECK();
-    switch (g.nb)
-    {
-    case 16: return tc_launch<16>(g, alpha, x, p->bimg[slot], beta, y, p->status, stream);
-    case 32: return tc_launch<32>(g, alpha, x, p->bimg[slot], beta, y, p->status, stream);
-    case 64: return tc_launch<64>(g, alpha, x, p->bimg[slot], beta, y, p->status, stream);
-    default: return DCB_UNSUPPORTED;
-    }
+    const TcGeom& g0 = p->g[slot];
+    for (int kg = 0; kg < g0.kgroups; ++kg)
+        for (int cgp = 0; cgp < g0.cgroups; ++cgp)
+        {
+            TcGeom g = g0;
+            g.w_k_off = kg * g0.kpad;
+            g.w_c_off = cgp * g0.c;
+            g.k = g0.k_total - g.w_k_off < g0.kpad ? g0.k_total - g.w_k_off : g0.kpad;
+            const long long total = (long long) g.b_bytes / 4;
+            tc_pack_filter_kernel<<<(unsigned) ((total + 255) / 256), 256, 0, stream>>>(w, p->bimg[slot], g);
+            DCB_LAUNCH_CHECK();
+            const float* xg = x + (size_t) g.w_c_off * g.xs_c;
+            float* yg = y + (size_t) g.w_k_off * g.ys_c;
+            const float b = cgp == 0 ? beta : 1.f; // later channel groups add into the output
+            int32_t st;
+            switch (g.nb)
+            {
+            case 16: st = tc_launch<16>(g, alpha, xg, p->bimg[slot], b, yg, p->status, stream); break;
+            case 32: st = tc_launch<32>(g, alpha, xg, p->bimg[slot], b, yg, p->status, stream); break;
+            case 64: st = tc_launch<64>(g, alpha, xg, p->bimg[slot], b, yg, p->status, stream); break;
+            default: st = DCB_UNSUPPORTED;
+            }
+            if (st != DCB_OK)
+                return st;
+        }
+    return DCB_OK;
 }
 
 int32_t tc_conv_fwd_stats(TcPlan* p, float alpha, const float* x, const float* w, float* y, float* sums,
@@ -962,23 +1011,42 @@ int32_t tc_conv_bwd_filter(TcPlan* p, float alpha, const float* x, const float* 
         return DCB_UNSUPPORTED;
     const WgGeom& g = p->wg;
     const ConvGeom& cg = p->wg_cg;
-    CUtensorMap xmap, dymap;
-    std::memset(&xmap, 0, sizeof(xmap));
-    std::memset(&dymap, 0, sizeof(dymap));
-    if (!wg_make_map(x, cg.in, cg.c, cg.n, cg.xs, cg.xs_c, cg.xs_n, WG_XW, g.f[1], g.c, &xmap)
-        || !wg_make_map(dy, cg.out, cg.k, cg.n, cg.ys, cg.ys_c, cg.ys_n, WG_TW, 1, 16, &dymap))
-        return DCB_UNSUPPORTED; // the caller falls back to the CUDA-core kernel
     size_t smem = wg_smem_need(g);
     smem = smem < 120 * 1024 ? 120 * 1024 : smem; // one CTA per SM
     long long grid = (long long) num_sms();
     if (grid > g.units)
         grid = g.units;
-    DCB_CUDA_TRY(cudaFuncSetAttribute(wg_conv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) (224 * 1024)));
-    wg_conv_kernel<<<(unsigned) grid, WG_THREADS, smem, stream>>>(g, p->wg_part, p->status, xmap, dymap);
-    DCB_LAUNCH_CHECK();
-    const int total = g.mrows * g.k;
-    wg_fold_kernel<<<(total + 255) / 256, 256, 0, stream>>>(p->wg_part, (int) grid, g.mrows, g.k, alpha, beta, dw);
-    DCB_LAUNCH_CHECK();
+    const int taps = g.f[0] * g.f[1] * g.f[2];
+    // all maps first: a pointer that cannot be mapped must refuse before anything ran
+    std::vector<CUtensorMap> xmaps((size_t) g.cgroups), dymaps((size_t) g.kgroups);
+    for (int cgp = 0; cgp < g.cgroups; ++cgp)
+    {
+        std::memset(&xmaps[cgp], 0, sizeof(CUtensorMap));
+        if (!wg_make_map(x + (size_t) cgp * g.c * cg.xs_c, cg.in, g.c, cg.n, cg.xs, cg.xs_c, cg.xs_n, WG_XW, g.f[1],
+                         g.c, &xmaps[cgp]))
+            return DCB_UNSUPPORTED; // the caller falls back to the CUDA-core kernel
+    }
+    for (int kg = 0; kg < g.kgroups; ++kg)
+    {
+        std::memset(&dymaps[kg], 0, sizeof(CUtensorMap));
+        const int kcur = g.k_total - kg * 16 < 16 ? g.k_total - kg * 16 : 16;
+        if (!wg_make_map(dy + (size_t) kg * 16 * cg.ys_c, cg.out, kcur, cg.n, cg.ys, cg.ys_c, cg.ys_n, WG_TW, 1, 16,
+                         &dymaps[kg]))
+            return DCB_UNSUPPORTED;
+    }
+    auto kernel = g.stride[2] == 2 ? wg_conv_kernel<2> : wg_conv_kernel<1>;
+    DCB_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) (224 * 1024)));
+    for (int kg = 0; kg < g.kgroups; ++kg)
+        for (int cgp = 0; cgp < g.cgroups; ++cgp)
+        {
+            const int kcur = g.k_total - kg * 16 < 16 ? g.k_total - kg * 16 : 16;
+            kernel<<<(unsigned) grid, WG_THREADS, smem, stream>>>(g, p->wg_part, p->status, xmaps[cgp], dymaps[kg]);
+            DCB_LAUNCH_CHECK();
+            const int total = g.mrows * kcur;
+            wg_fold_kernel<<<(total + 255) / 256, 256, 0, stream>>>(p->wg_part, (int) grid, g.mrows, kcur, taps,
+                                                                    g.c_total, cgp * g.c, kg * 16, alpha, beta, dw);
+            DCB_LAUNCH_CHECK();
+        }
     return DCB_OK;
 }
 

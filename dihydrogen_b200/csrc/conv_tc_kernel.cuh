@@ -48,6 +48,11 @@ struct TcGeom
                         // bulk copies feed the ring, else one private window set per converter group
     int chunk_rows;     // staged rows per bulk copy
     int chunks_pp;      // bulk copies per filter plane of a tile
+    // One launch covers c input channels and k filters; a convolution with more of
+    // either runs as cgroups x kgroups launches on sub-ranges of the filter tensor
+    // (the later channel groups add into the output).
+    int c_total, k_total, w_c_off, w_k_off;
+    int cgroups, kgroups;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p)
@@ -204,7 +209,8 @@ __global__ void tc_pack_filter_kernel(const float* __restrict__ w, float* __rest
         float val = 0.f;
         if (ko < g.k && part < (g.split ? 2 : 1))
         {
-            const float wv = w[((((size_t) ko * g.c + c) * fd + kd) * fh + kh) * fw + kw];
+            const float wv =
+                w[((((size_t) (ko + g.w_k_off) * g.c_total + (c + g.w_c_off)) * fd + kd) * fh + kh) * fw + kw];
             const float hi = __uint_as_float(tf32_rna(wv));
             if (half == 0)
                 val = hi;

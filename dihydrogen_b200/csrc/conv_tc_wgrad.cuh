@@ -1,8 +1,12 @@
-// tcgen05 / TMEM backward filter (stride 1, dilation 1, c*fd*fh*fw <= 128 filter
-// taps per output filter, K <= 16):
+// tcgen05 / TMEM backward filter (strides 1 or 2, dilation 1, c*fd*fh*fw <= 128
+// filter taps per output filter, K <= 16 per launch):
 //
 //   dw[k][c][kd][kh][kw] = sum over (n, od, oh, ow) dy[n][k][od][oh][ow] *
-//                          x[n][c][od+kd-pd][oh+kh-ph][ow+kw-pw]
+//                          x[n][c][od*sd+kd-pd][oh*sh+kh-ph][ow*sw+kw-pw]
+//
+// (written below for unit strides; with stride 2 along W a unit's input rows
+// arrive as two half windows of the same shape, outputs 0..63 read the first
+// and 64..127 the second, at every second cell)
 //
 // GEMM view: the reduction runs over the outputs, eight consecutive ow per
 // MMA (the K of a TF32 instruction).  M = the (c, kd, kh, kw) taps (up to 128
@@ -64,15 +68,22 @@ struct WgGeom
     int mrows;              // c * fd * fh * fw
     int tiles_w;
     long long units;        // n * out_d * out_h * tiles_w
-    int xplane_floats;      // pitch of one filter plane of a unit: c * fh * WG_XW floats rounded up to
+    int stride[3];          // 1 or 2
+    int xhalf_floats;       // one bulk copy's box in a unit buffer: c * fh * WG_XW floats rounded up to
                             // 128 bytes (a bulk copy's destination must be 128-byte aligned)
-    int xplane_bytes;       // bytes one plane's copy brings: c * fh * WG_XW * 4
+    int xplane_floats;      // pitch of one filter plane of a unit: stride[2] boxes
+    int xplane_bytes;       // bytes one box brings: c * fh * WG_XW * 4
     int xbuf_bytes;         // fd plane pitches
     int dybuf_bytes;        // 16 x WG_TW floats
+    // One launch covers c input channels (c * taps <= 128) and at most 16
+    // filters; a larger filter tensor is cgroups x kgroups launches.
+    int c_total, k_total, cgroups, kgroups;
 };
 
-__global__ void wg_fold_kernel(const float* __restrict__ part, int nparts, int mrows, int k, float alpha, float beta,
-                               float* dw)
+// dw[k_off + kk][c_off + c][tap] (of a [k_total][c_total][taps] filter tensor) from the
+// per-CTA partials of one launch; m = c * taps + tap.
+__global__ void wg_fold_kernel(const float* __restrict__ part, int nparts, int mrows, int k, int taps, int c_total,
+                               int c_off, int k_off, float alpha, float beta, float* dw)
 {
     const int i = blockIdx.x * blockDim.x + threadIdx.x; // (filter, tap row)
     if (i >= mrows * k)
@@ -81,10 +92,12 @@ __global__ void wg_fold_kernel(const float* __restrict__ part, int nparts, int m
     double s = 0.0;
     for (int p = 0; p < nparts; ++p)
         s += (double) part[((size_t) p * 128 + m) * 16 + kk];
-    const float prev = beta != 0.f ? dw[i] : 0.f;
-    dw[i] = alpha * (float) s + beta * prev;
+    float* o = dw + ((size_t) (k_off + kk) * c_total + c_off) * taps + m;
+    const float prev = beta != 0.f ? *o : 0.f;
+    *o = alpha * (float) s + beta * prev;
 }
 
+template <int SW> // stride along W
 __global__ void __launch_bounds__(WG_THREADS, 1)
     wg_conv_kernel(WgGeom g, float* __restrict__ part, int* status, const __grid_constant__ CUtensorMap xmap,
                    const __grid_constant__ CUtensorMap dymap)
@@ -186,11 +199,15 @@ __global__ void __launch_bounds__(WG_THREADS, 1)
                 {
                     if (src >= 0)
                     {
-                        const uint32_t s0 = smem_u32(xb + src + (q * WG_KS + ks) * 8);
+                        // output (q * WG_KS + ks) * 8 of the unit; with SW == 2 the second
+                        // 64 outputs read the second half window
+                        const int o = (q * WG_KS + ks) * 8;
+                        const uint32_t s0 = smem_u32(
+                            xb + src + (SW == 2 ? (o >= 64 ? g.xhalf_floats + (o - 64) * 2 : o * 2) : o));
 #pragma unroll
                         for (int e = 0; e < 8; ++e)
                         {
-                            const float xe = __uint_as_float(lds_u32(s0 + 4u * e));
+                            const float xe = __uint_as_float(lds_u32(s0 + 4u * (uint32_t) (e * SW)));
                             hi[ks][e] = tf32_rna(xe);
                             lo[ks][e] = tf32_rna(xe - __uint_as_float(hi[ks][e]));
                         }
@@ -244,7 +261,7 @@ __global__ void __launch_bounds__(WG_THREADS, 1)
         // ------------------------------------------------------------------
         // bulk tensor copies, one unit ahead
         // ------------------------------------------------------------------
-        const uint32_t bytes = (uint32_t) (g.f[0] * g.xplane_bytes + g.dybuf_bytes);
+        const uint32_t bytes = (uint32_t) (g.f[0] * SW * g.xplane_bytes + g.dybuf_bytes);
         uint32_t ul = 0;
         for (uint32_t u = blockIdx.x; u < nunits && ok; u += gridDim.x, ++ul)
         {
@@ -264,9 +281,13 @@ __global__ void __launch_bounds__(WG_THREADS, 1)
                 const int ow0 = (int) tw * WG_TW;
                 uint8_t* dst = ubuf + (size_t) b * unit_bytes;
                 mbar_expect_tx(&u_full[b], bytes);
+                // the window starts 4 cells left of the first tap: a multiple of 4 floats
                 for (int kd = 0; kd < g.f[0]; ++kd)
-                    tma_load_5d(dst + (size_t) kd * g.xplane_floats * 4, &xmap, ow0 - 4, oh - g.pad[1],
-                                od - g.pad[0] + kd, 0, n, &u_full[b]);
+#pragma unroll
+                    for (int h = 0; h < SW; ++h)
+                        tma_load_5d(dst + ((size_t) kd * g.xplane_floats + (size_t) h * g.xhalf_floats) * 4, &xmap,
+                                    ow0 * SW - 4 + h * 128, oh * g.stride[1] - g.pad[1],
+                                    od * g.stride[0] - g.pad[0] + kd, 0, n, &u_full[b]);
                 tma_load_5d(dst + g.xbuf_bytes, &dymap, ow0, oh, od, 0, n, &u_full[b]);
             }
             __syncwarp();

@@ -113,6 +113,13 @@ GEOMS = [
     (2, 3, 5, (5, 6, 40), (2, 1, 3), (1, 0, 1), (1, 1, 1), (1, 1, 1)),        # one filter row: one converter group
     (2, 3, 12, (7, 10, 132), (3, 3, 3), (1, 1, 1), (1, 1, 1), (1, 1, 1)),     # backward data: 3 channel groups -> 3 filters
     (1, 4, 16, (9, 30, 64), (3, 3, 3), (0, 1, 1), (1, 1, 1), (1, 1, 1)),      # backward data: tall columns, no padding in D
+    (2, 32, 32, (12, 140), (5, 5), (2, 2), (1, 1), (1, 1)),                   # cfg4 channels: 4 channel x 2 filter group launches
+    (1, 24, 40, (10, 70), (3, 3), (1, 1), (1, 1), (1, 1)),                    # ragged last filter group
+    (1, 16, 32, (6, 8, 36), (3, 3, 3), (1, 1, 1), (1, 1, 1), (1, 1, 1)),      # 3-D, 32 filters: row kernel, grouped backward filter
+    (1, 16, 16, (5, 7, 40), (3, 3, 3), (1, 1, 1), (1, 1, 1), (1, 1, 1)),      # 3-D, 4 channel groups in the sweep kernels
+    (1, 8, 20, (7, 12, 280), (3, 3, 3), (1, 1, 1), (2, 2, 2), (1, 1, 1)),     # stride 2, two W tiles (ragged), grouped backward filter
+    (2, 4, 16, (9, 300), (3, 3), (1, 1), (1, 2), (1, 1)),                     # stride 2 along W only
+    (1, 3, 5, (10, 264), (5, 5), (2, 2), (2, 2), (1, 1)),                     # 5x5 stride 2
 ]
 
 
@@ -147,6 +154,25 @@ def test_alpha_beta_blend(mode):
     emu.assert_close(y, O.conv_fwd(x, w, [1] * 3, [1] * 3, alpha=0.5, beta=2.0, y=y0.copy()), TOL, "y")
     emu.assert_close(dx, O.conv_bwd_data(w, dy, dx0.copy(), [1] * 3, [1] * 3, alpha=0.5, beta=2.0), TOL, "dx")
     emu.assert_close(dw, O.conv_bwd_filter(x, dy, f, [1] * 3, [1] * 3, alpha=0.5, beta=2.0, dw=dw0.copy()), TOL, "dw")
+
+
+@pytest.mark.parametrize("mode", MODES)
+def test_alpha_beta_blend_with_channel_groups(mode):
+    """Only the first channel group may scale the old output by beta."""
+    N, C, K, sp, f = 1, 32, 20, (9, 133), (5, 5)
+    rng = np.random.default_rng(19)
+    x = rng.normal(size=(N, C, *sp)).astype(np.float32)
+    w = rng.normal(0, 0.05, (K, C, *f)).astype(np.float32)
+    dy = rng.normal(size=(N, K, *sp)).astype(np.float32)
+    y0 = rng.normal(size=dy.shape).astype(np.float32)
+    dx0 = rng.normal(size=x.shape).astype(np.float32)
+    dw0 = rng.normal(size=w.shape).astype(np.float32)
+    y, dx, dw = run_all(x, w, dy, [2, 2], [1, 1], [1, 1], mode, alpha=0.5, beta=-1.5, y0=y0, dx0=dx0, dw0=dw0)
+    emu.assert_close(y, 0.5 * O.conv_fwd(x, w, [2, 2], [1, 1], [1, 1]) - 1.5 * y0, TOL, "y")
+    dx_ref = np.zeros_like(x)
+    O.conv_bwd_data(w, dy, dx_ref, [2, 2], [1, 1], [1, 1])
+    emu.assert_close(dx, 0.5 * dx_ref - 1.5 * dx0, TOL, "dx")
+    emu.assert_close(dw, 0.5 * O.conv_bwd_filter(x, dy, f, [2, 2], [1, 1]) - 1.5 * dw0, TOL, "dw")
 
 
 def test_plan_rejects_inconsistent_output_extent():
@@ -213,8 +239,9 @@ def test_fused_statistics_unsupported_for_2d():
 
 def test_tensor_core_kernels_are_the_ones_running():
     """For the bench layer's shape family all three passes resolve to tcgen05
-    kernels; a plan whose tap count does not fit the backward-filter kernel
-    (C * taps > 128) keeps the fp32 one for that pass."""
+    kernels (more channels: several launches on channel groups); a filter with
+    more taps than tensor-memory lanes (> 128) keeps the fp32 kernel for the
+    backward filter."""
     x = torch.zeros(1, 4, 8, 16, 128, device="cuda")
     w = torch.zeros(16, 4, 3, 3, 3, device="cuda")
     y = torch.zeros(1, 16, 8, 16, 128, device="cuda")
@@ -223,7 +250,11 @@ def test_tensor_core_kernels_are_the_ones_running():
     x2 = torch.zeros(1, 8, 8, 16, 128, device="cuda")
     w2 = torch.zeros(16, 8, 3, 3, 3, device="cuda")
     p2 = Plan(x2, w2, y, [1] * 3, [1] * 3, [1] * 3, _abi.MATH_FP32)
-    assert _abi.lib().dcb_conv_plan_kernel_kind(p2.p, 2) == 0
+    assert _abi.lib().dcb_conv_plan_kernel_kind(p2.p, 2) == 1
+    x3 = torch.zeros(1, 2, 8, 16, 128, device="cuda")
+    w3 = torch.zeros(16, 2, 5, 5, 7, device="cuda")
+    p3 = Plan(x3, w3, y, [2, 2, 3], [1] * 3, [1] * 3, _abi.MATH_FP32)
+    assert _abi.lib().dcb_conv_plan_kernel_kind(p3.p, 2) == 0
 
 
 def test_backward_filter_tensor_core_ragged_tiles_and_batch():
