@@ -18,10 +18,13 @@ from .distconv import (  # noqa: F401
     LeakyReLU,
     Locale,
     Options,
+    Pooling,
     Tensor,
     create_convolution_d_output_tensor,
     create_convolution_output_tensor,
     create_d_input_tensor,
     create_input_tensor,
+    create_pooling_d_output_tensor,
+    create_pooling_output_tensor,
     get_halo_sizes,
 )

@@ -49,6 +49,21 @@ class NdDesc(ctypes.Structure):
     ]
 
 
+class PoolDesc(ctypes.Structure):
+    _fields_ = [
+        ("nsd", c_int32),
+        ("window", c_int32 * DCB_MAX_SPATIAL),
+        ("pads", c_int32 * DCB_MAX_SPATIAL),
+        ("strides", c_int32 * DCB_MAX_SPATIAL),
+        ("mode", c_int32),
+        ("outside_lo", c_int32 * DCB_MAX_SPATIAL),
+        ("outside_hi", c_int32 * DCB_MAX_SPATIAL),
+    ]
+
+
+POOL_MODES = {"MAX": 0, "AVERAGE": 1, "AVERAGE_NO_PAD": 2}
+
+
 class ConvDesc(ctypes.Structure):
     _fields_ = [
         ("nsd", c_int32),
@@ -112,6 +127,9 @@ _SIGS = {
                                    POINTER(NdDesc), _P, _P]),
     "dcb_leaky_relu_fwd": (c_int32, [POINTER(NdDesc), _P, c_float, POINTER(NdDesc), _P, _P]),
     "dcb_leaky_relu_bwd": (c_int32, [POINTER(NdDesc), _P, POINTER(NdDesc), _P, c_float, POINTER(NdDesc), _P, _P]),
+    "dcb_pool_fwd": (c_int32, [POINTER(PoolDesc), POINTER(NdDesc), POINTER(NdDesc), c_double, _P, c_double, _P, _P]),
+    "dcb_pool_bwd": (c_int32, [POINTER(PoolDesc), POINTER(NdDesc), POINTER(NdDesc), c_double, _P, _P, _P, c_double,
+                               _P, _P]),
     "dcb_nccl_unique_id": (c_int32, [_P]),
     "dcb_comm_create_nccl": (c_int32, [_P, c_int32, c_int32, POINTER(_P)]),
     "dcb_comm_create_peer": (c_int32, [c_int32, c_int32, c_int32, POINTER(_P)]),

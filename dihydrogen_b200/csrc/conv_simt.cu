@@ -215,7 +215,13 @@ __global__ void __launch_bounds__(BWD_THREADS)
 {
     extern __shared__ __align__(16) float ws[]; // [ktile][taps][CT]
     const int taps = g.f[0] * g.f[1] * g.f[2];
-    const int iw = blockIdx.y * BWD_THREADS + threadIdx.x;
+    // With stride 2 along W the taps a cell receives depend on its parity: a warp
+    // takes cells of one parity (every second cell), so that its lanes walk the
+    // same taps and read consecutive dy cells.
+    const int iw = g.stride[2] == 2
+                       ? blockIdx.y * BWD_THREADS + (threadIdx.x >> 6) * 64 + 2 * (threadIdx.x & 31)
+                             + ((threadIdx.x >> 5) & 1)
+                       : blockIdx.y * BWD_THREADS + threadIdx.x;
     const int ih = blockIdx.x % g.in[1];
     const int id = blockIdx.x / g.in[1];
     const int ct = blockIdx.z % ctiles;
@@ -271,9 +277,27 @@ __global__ void __launch_bounds__(BWD_THREADS)
                                        + (size_t) k0 * g.ys_c
                                        + (size_t) od * g.ys[0]
                                        + (size_t) oh * g.ys[1] + ow;
-                    for (int kk = 0; kk < kend; ++kk)
+                    // four loads in flight per thread: one at a time left the loop
+                    // waiting on each dy cell
+                    int kk = 0;
+                    for (; kk + 4 <= kend; kk += 4)
                     {
-                        const float v = dyp[(size_t) kk * g.ys_c];
+                        float v[4];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u)
+                            v[u] = __ldg(dyp + (size_t) (kk + u) * g.ys_c);
+#pragma unroll
+                        for (int u = 0; u < 4; ++u)
+                        {
+                            const float* wp = ws + ((size_t) (kk + u) * taps + tap) * CT;
+#pragma unroll
+                            for (int cc = 0; cc < CT; ++cc)
+                                acc[cc] = fmaf(v[u], wp[cc], acc[cc]);
+                        }
+                    }
+                    for (; kk < kend; ++kk)
+                    {
+                        const float v = __ldg(dyp + (size_t) kk * g.ys_c);
                         const float* wp = ws + ((size_t) kk * taps + tap) * CT;
 #pragma unroll
                         for (int cc = 0; cc < CT; ++cc)
@@ -337,6 +361,8 @@ int32_t simt_conv_bwd_data(const ConvGeom& g, float alpha, const float* w,
 {
     if ((long long) g.n * g.c * g.in[0] * g.in[1] * g.in[2] == 0)
         return DCB_OK;
+    if (g.c > 8)
+        return launch_bwd_data<16>(g, alpha, w, dy, beta, dx, stream);
     if (g.c > 4)
         return launch_bwd_data<8>(g, alpha, w, dy, beta, dx, stream);
     return launch_bwd_data<4>(g, alpha, w, dy, beta, dx, stream);

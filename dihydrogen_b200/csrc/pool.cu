@@ -1,0 +1,279 @@
+// Pooling on a halo-extended shard: stands in for cudnnPoolingForward /
+// cudnnPoolingBackward behind GPUDNNBackend::pooling_forward / _backward as
+// Pooling<BackendDNNLib, T> calls them
+// (legacy/include/distconv/dnn_backend/pooling.hpp:212-283).
+//
+// Both passes are gathers (one thread per result cell, W fastest so that a
+// warp reads and writes consecutive cells) and so are reproducible:
+//
+//   forward   y[o] = alpha * pool(window of o) + beta * y[o]
+//   backward  dx[i] = alpha * sum over the windows o that contain i of
+//                         MAX:  dy[o] if i is the first cell of o's window (scan
+//                               order D, H, W) that holds the maximum, else 0
+//                         AVG:  dy[o] / count(o)
+//                     + beta * dx[i]
+//
+// Cells outside the x window are padding: ignored by MAX and by the
+// count of AVERAGE_NO_PAD, zeros that count for AVERAGE.  Where a dimension is
+// partitioned the caller passes pad 0 and a window that includes the halo
+// cells, and the backward pass writes the halo cells of dx too; the reverse
+// halo exchange with SUM then adds them to their owners
+// (pooling.hpp:281, :450-467).  The halo cells of a rank at the boundary of
+// the global tensor stand for padding (pooling.hpp:189-194); the reference
+// hands them to cuDNN as zero data, which changes MAX and AVERAGE_NO_PAD
+// against the unpartitioned result.  Here the descriptor says how many leading
+// / trailing cells of the window lie outside the global tensor and those are
+// padding like any other, so P ranks give what one rank gives.
+//
+// HBM-bound: algorithmic bytes are 4 * (|x| + |y|) forward and
+// 4 * (|x| + |y| + |dy| + |dx|) backward; the window re-reads hit L1 / L2.
+#include "common.cuh"
+#include "dcb.h"
+
+#include <cfloat>
+
+namespace dcb
+{
+namespace
+{
+
+struct PoolGeom
+{
+    int n, c;
+    int in[3], out[3], win[3], pad[3], stride[3];
+    int lo[3], hi[3]; // real cells of the x window along each axis: [lo, hi)
+    long long xs_n, xs_c, xs[3];
+    long long ys_n, ys_c, ys[3];
+    int mode;
+};
+
+constexpr int POOL_THREADS = 256;
+
+__device__ __forceinline__ float pool_count(const PoolGeom& g, int od, int oh, int ow)
+{
+    if (g.mode == DCB_POOL_AVERAGE)
+        return (float) (g.win[0] * g.win[1] * g.win[2]);
+    int cnt = 1;
+    const int o[3] = {od, oh, ow};
+#pragma unroll
+    for (int i = 0; i < 3; ++i)
+    {
+        const int lo = max(g.lo[i], o[i] * g.stride[i] - g.pad[i]);
+        const int hi = min(g.hi[i], o[i] * g.stride[i] - g.pad[i] + g.win[i]);
+        cnt *= max(0, hi - lo);
+    }
+    return (float) cnt;
+}
+
+__global__ void __launch_bounds__(POOL_THREADS)
+    pool_fwd_kernel(PoolGeom g, float alpha, float beta, const float* __restrict__ x, float* y)
+{
+    const int ow = blockIdx.y * POOL_THREADS + threadIdx.x;
+    if (ow >= g.out[2])
+        return;
+    const int oh = blockIdx.x % g.out[1], od = blockIdx.x / g.out[1];
+    const int c = blockIdx.z % g.c, n = blockIdx.z / g.c;
+    const float* xp = x + (size_t) n * g.xs_n + (size_t) c * g.xs_c;
+    float m = -FLT_MAX, s = 0.f;
+    for (int kd = 0; kd < g.win[0]; ++kd)
+    {
+        const int id = od * g.stride[0] - g.pad[0] + kd;
+        if (id < g.lo[0] || id >= g.hi[0])
+            continue;
+        for (int kh = 0; kh < g.win[1]; ++kh)
+        {
+            const int ih = oh * g.stride[1] - g.pad[1] + kh;
+            if (ih < g.lo[1] || ih >= g.hi[1])
+                continue;
+            const float* row = xp + (size_t) id * g.xs[0] + (size_t) ih * g.xs[1];
+            for (int kw = 0; kw < g.win[2]; ++kw)
+            {
+                const int iw = ow * g.stride[2] - g.pad[2] + kw;
+                if (iw < g.lo[2] || iw >= g.hi[2])
+                    continue;
+                const float v = __ldg(row + iw);
+                m = fmaxf(m, v);
+                s += v;
+            }
+        }
+    }
+    const float r = g.mode == DCB_POOL_MAX ? m : s / fmaxf(pool_count(g, od, oh, ow), 1.f);
+    float* yp = y + (size_t) n * g.ys_n + (size_t) c * g.ys_c + (size_t) od * g.ys[0] + (size_t) oh * g.ys[1] + ow;
+    *yp = beta != 0.f ? alpha * r + beta * *yp : alpha * r;
+}
+
+// The outputs whose window holds input coordinate i: o*stride - pad <= i < o*stride - pad + win.
+__device__ __forceinline__ void pool_cover(int i, int stride, int pad, int win, int nout, int* lo, int* hi)
+{
+    const int t = i + pad;
+    int l = t - win + 1;
+    l = l <= 0 ? 0 : (l + stride - 1) / stride;
+    int h = t / stride;
+    *lo = l;
+    *hi = min(h, nout - 1);
+}
+
+__global__ void __launch_bounds__(POOL_THREADS)
+    pool_bwd_kernel(PoolGeom g, float alpha, float beta, const float* __restrict__ y, const float* __restrict__ dy,
+                    const float* __restrict__ x, float* dx)
+{
+    const int iw = blockIdx.y * POOL_THREADS + threadIdx.x;
+    if (iw >= g.in[2])
+        return;
+    const int ih = blockIdx.x % g.in[1], id = blockIdx.x / g.in[1];
+    const int c = blockIdx.z % g.c, n = blockIdx.z / g.c;
+    const size_t xoff = (size_t) n * g.xs_n + (size_t) c * g.xs_c;
+    const size_t yoff = (size_t) n * g.ys_n + (size_t) c * g.ys_c;
+    const size_t me = xoff + (size_t) id * g.xs[0] + (size_t) ih * g.xs[1] + iw;
+    int dlo, dhi, hlo, hhi, wlo, whi;
+    pool_cover(id, g.stride[0], g.pad[0], g.win[0], g.out[0], &dlo, &dhi);
+    pool_cover(ih, g.stride[1], g.pad[1], g.win[1], g.out[1], &hlo, &hhi);
+    pool_cover(iw, g.stride[2], g.pad[2], g.win[2], g.out[2], &wlo, &whi);
+    const float xv = g.mode == DCB_POOL_MAX ? __ldg(x + me) : 0.f;
+    float acc = 0.f;
+    // a cell outside the global tensor is padding: no window gives it anything
+    const bool real = id >= g.lo[0] && id < g.hi[0] && ih >= g.lo[1] && ih < g.hi[1] && iw >= g.lo[2] && iw < g.hi[2];
+    if (!real)
+        dhi = dlo - 1;
+    for (int od = dlo; od <= dhi; ++od)
+        for (int oh = hlo; oh <= hhi; ++oh)
+            for (int ow = wlo; ow <= whi; ++ow)
+            {
+                const size_t o = yoff + (size_t) od * g.ys[0] + (size_t) oh * g.ys[1] + ow;
+                if (g.mode != DCB_POOL_MAX)
+                {
+                    acc += __ldg(dy + o) / fmaxf(pool_count(g, od, oh, ow), 1.f);
+                    continue;
+                }
+                if (__ldg(y + o) != xv)
+                    continue;
+                // the maximum goes to the first cell that holds it: is one before me?
+                bool first = true;
+                const int d0 = od * g.stride[0] - g.pad[0], h0 = oh * g.stride[1] - g.pad[1],
+                          w0 = ow * g.stride[2] - g.pad[2];
+                for (int jd = max(d0, g.lo[0]); jd <= id && first; ++jd)
+                    for (int jh = max(h0, g.lo[1]); jh < min(h0 + g.win[1], g.hi[1]) && first; ++jh)
+                    {
+                        if (jd == id && jh > ih)
+                            break;
+                        const float* row = x + xoff + (size_t) jd * g.xs[0] + (size_t) jh * g.xs[1];
+                        const int wend = (jd == id && jh == ih) ? iw : min(w0 + g.win[2], g.hi[2]);
+                        for (int jw = max(w0, g.lo[2]); jw < wend; ++jw)
+                            if (__ldg(row + jw) == xv)
+                            {
+                                first = false;
+                                break;
+                            }
+                    }
+                if (first)
+                    acc += __ldg(dy + o);
+            }
+    dx[me] = beta != 0.f ? alpha * acc + beta * dx[me] : alpha * acc;
+}
+
+int32_t pool_geom(const dcb_pool_desc* pd, const dcb_nd_desc* xd, const dcb_nd_desc* yd, PoolGeom* g)
+{
+    DCB_REQUIRE(pd && xd && yd, "null descriptor");
+    DCB_REQUIRE(pd->nsd == 2 || pd->nsd == 3, "nsd must be 2 or 3");
+    DCB_REQUIRE(xd->nsd == pd->nsd && yd->nsd == pd->nsd, "descriptor ranks do not match");
+    DCB_REQUIRE(pd->mode == DCB_POOL_MAX || pd->mode == DCB_POOL_AVERAGE || pd->mode == DCB_POOL_AVERAGE_NO_PAD,
+                "unknown pooling mode");
+    DCB_REQUIRE(xd->n == yd->n && xd->c == yd->c, "sample / channel counts do not match");
+    DCB_REQUIRE(xd->n >= 0 && xd->c >= 0 && xd->n * xd->c < (1ll << 31), "too many (n, c) planes");
+    g->n = (int) xd->n;
+    g->c = (int) xd->c;
+    g->mode = pd->mode;
+    for (int i = 0; i < 3; ++i)
+    {
+        DCB_REQUIRE(pd->window[i] >= 1 && pd->strides[i] >= 1 && pd->pads[i] >= 0, "bad window / stride / pad");
+        DCB_REQUIRE(pd->pads[i] < pd->window[i], "a window entirely inside the padding");
+        DCB_REQUIRE(xd->dims[i] < (1ll << 30) && yd->dims[i] < (1ll << 30), "extent too large");
+        const long long span = xd->dims[i] + 2ll * pd->pads[i] - pd->window[i];
+        DCB_REQUIRE(yd->dims[i] == (span < 0 ? 0 : span / pd->strides[i] + 1),
+                    "output extent does not match input, pad, stride, window");
+        g->in[i] = (int) xd->dims[i];
+        g->out[i] = (int) yd->dims[i];
+        g->win[i] = pd->window[i];
+        g->pad[i] = pd->pads[i];
+        g->stride[i] = pd->strides[i];
+        g->xs[i] = xd->strides[i];
+        g->ys[i] = yd->strides[i];
+        DCB_REQUIRE(pd->outside_lo[i] >= 0 && pd->outside_hi[i] >= 0
+                        && pd->outside_lo[i] + pd->outside_hi[i] <= xd->dims[i],
+                    "outside_lo / outside_hi exceed the window");
+        DCB_REQUIRE(pd->outside_lo[i] < pd->window[i] && pd->outside_hi[i] < pd->window[i],
+                    "a window entirely inside the padding");
+        g->lo[i] = pd->outside_lo[i];
+        g->hi[i] = (int) xd->dims[i] - pd->outside_hi[i];
+    }
+    if (pd->nsd == 2)
+        DCB_REQUIRE(pd->window[0] == 1 && pd->pads[0] == 0 && pd->strides[0] == 1, "slot 0 must be trivial for 2-D");
+    DCB_REQUIRE(xd->strides[2] == 1 || xd->dims[2] <= 1, "W must be unit-stride");
+    DCB_REQUIRE(yd->strides[2] == 1 || yd->dims[2] <= 1, "W must be unit-stride");
+    g->xs_n = xd->sn;
+    g->xs_c = xd->sc;
+    g->ys_n = yd->sn;
+    g->ys_c = yd->sc;
+    return DCB_OK;
+}
+
+// grid.x carries (plane, row), the large product; grid.z (sample, channel)
+bool pool_grid(int w, long long rows, long long planes, dim3* grid)
+{
+    const long long wt = (w + POOL_THREADS - 1) / POOL_THREADS;
+    if (rows > 0x7fffffffll || wt > 65535 || planes > 65535)
+        return false;
+    *grid = dim3((unsigned) rows, (unsigned) wt, (unsigned) planes);
+    return true;
+}
+
+} // namespace
+} // namespace dcb
+
+using namespace dcb;
+
+extern "C" int32_t dcb_pool_fwd(const dcb_pool_desc* pd, const dcb_nd_desc* xd, const dcb_nd_desc* yd, double alpha,
+                                const void* x, double beta, void* y, void* stream)
+{
+    PoolGeom g;
+    const int32_t st = pool_geom(pd, xd, yd, &g);
+    if (st != DCB_OK)
+        return st;
+    if ((long long) g.n * g.c * g.out[0] * g.out[1] * g.out[2] == 0)
+        return DCB_OK;
+    DCB_REQUIRE(x && y, "null argument");
+    dim3 grid;
+    if (!pool_grid(g.out[2], (long long) g.out[0] * g.out[1], (long long) g.n * g.c, &grid))
+    {
+        set_last_error("tensor too large for the pooling grid");
+        return DCB_UNSUPPORTED;
+    }
+    pool_fwd_kernel<<<grid, POOL_THREADS, 0, as_stream(stream)>>>(g, (float) alpha, (float) beta,
+                                                                  static_cast<const float*>(x),
+                                                                  static_cast<float*>(y));
+    DCB_LAUNCH_CHECK();
+    return DCB_OK;
+}
+
+extern "C" int32_t dcb_pool_bwd(const dcb_pool_desc* pd, const dcb_nd_desc* xd, const dcb_nd_desc* yd, double alpha,
+                                const void* y, const void* dy, const void* x, double beta, void* dx, void* stream)
+{
+    PoolGeom g;
+    const int32_t st = pool_geom(pd, xd, yd, &g);
+    if (st != DCB_OK)
+        return st;
+    if ((long long) g.n * g.c * g.in[0] * g.in[1] * g.in[2] == 0)
+        return DCB_OK;
+    DCB_REQUIRE(dy && dx && (pd->mode != DCB_POOL_MAX || (x && y)), "null argument");
+    dim3 grid;
+    if (!pool_grid(g.in[2], (long long) g.in[0] * g.in[1], (long long) g.n * g.c, &grid))
+    {
+        set_last_error("tensor too large for the pooling grid");
+        return DCB_UNSUPPORTED;
+    }
+    pool_bwd_kernel<<<grid, POOL_THREADS, 0, as_stream(stream)>>>(
+        g, (float) alpha, (float) beta, static_cast<const float*>(y), static_cast<const float*>(dy),
+        static_cast<const float*>(x), static_cast<float*>(dx));
+    DCB_LAUNCH_CHECK();
+    return DCB_OK;
+}

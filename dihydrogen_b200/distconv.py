@@ -488,6 +488,35 @@ def create_convolution_d_output_tensor(output: Tensor, filter_shape, dilations) 
     return Tensor(output.shape, output.locale, dist, output._local_of)
 
 
+def create_pooling_output_tensor(input: Tensor, window, strides, pads) -> Tensor:
+    """distconv.hpp:518-565: odd windows with pad 0 or (window-1)/2, even
+    windows with stride == window and no padding; window / strides / pads in
+    reference order (W first)."""
+    nd, nsd = input.nd, input.nd - 2
+    use_padding = pads[0] != 0
+    out_shape = list(input.shape)
+    for i in range(nsd):
+        if input.shape[i] + 2 * pads[i] < window[i]:
+            out_shape[i] = 0
+        elif window[i] % 2:
+            assert pads[i] == 0 or pads[i] * 2 + 1 == window[i]
+            assert (pads[i] != 0) == use_padding
+            out_shape[i] = -(-(input.shape[i] - window[i] + 1 + 2 * pads[i]) // strides[i])
+        else:
+            assert pads[i] == 0 and strides[i] == window[i]
+            out_shape[i] = input.shape[i] // strides[i]
+    dist = input.dist.copy()
+    dist.clear_overlap()
+    wdims, C = list(window[:nsd]), input.shape[-2]
+    return Tensor(out_shape, input.locale, dist,
+                  lambda pidx: _conv_out_local(input, pidx, wdims, strides, [1] * nsd, use_padding, C))
+
+
+def create_pooling_d_output_tensor(output: Tensor) -> Tensor:
+    """distconv.hpp:567-581."""
+    return Tensor(output.shape, output.locale, output.dist.copy(), output._local_of)
+
+
 # ---------------------------------------------------------------------------
 # HaloExchange
 # ---------------------------------------------------------------------------
@@ -1028,6 +1057,105 @@ class BatchNormalization:
         self.backward_allreduce(scale_gradient, bias_gradient, mean_gradient, var_gradient)
         self.backward_stage2(input, d_output, mean, var, scale, mean_gradient, var_gradient, d_input)
         return 0
+
+
+class Pooling:
+    """Pooling<BackendDNNLib, float> (pooling.hpp:70-482): halo exchange of the
+    input, pooling over the halo-extended shard, and in the backward pass the
+    reverse exchange that adds the gradients a rank computed for its
+    neighbours' cells to their owners (HaloExchangeAccumOp::SUM)."""
+
+    def __init__(self, backend: BackendDNNLib, num_dims: int, halo_exchange_method="AL"):
+        self.be = backend
+        self.num_dims = num_dims
+        self.nsd = num_dims - 2
+        self.halo_xch_input = None
+        self.halo_xch_d_input = None
+
+    def setup(self, input: Tensor, output: Tensor, d_input: Tensor, d_output: Tensor, windows, pads, strides,
+              mode: str, connect=True):
+        """pooling.hpp:101-209; windows / pads / strides in reference order (W
+        first), all dimensions equal as the reference demands."""
+        nsd = self.nsd
+        assert len(windows) == nsd and len(pads) == nsd and len(strides) == nsd
+        assert len(set(windows)) == 1 and len(set(pads)) == 1 and len(set(strides)) == 1
+        for w, p, st in zip(windows, pads, strides):
+            if w % 2:
+                stencil = (w - 1) // 2
+                assert p in (0, stencil) and st in (1, stencil + 1)
+            else:
+                assert w == st and p == 0
+        assert input.dist == d_input.dist
+        assert mode in _abi.POOL_MODES
+        self.mode = mode
+        self.input, self.output, self.d_input, self.d_output = input, output, d_input, d_output
+        use_padding = pads[0] != 0
+        self.halo_fwd_send, self.halo_bwd_send, self.halo_fwd_recv, self.halo_bwd_recv = get_halo_sizes(
+            input, list(windows), list(strides), [1] * nsd, use_padding)
+        # where a dimension is split the halo stands in for the padding (pooling.hpp:189-194)
+        eff_pads = [0 if input.dist.split_shape[i] > 1 else pads[i] for i in range(nsd)]
+        self._lo, self._hi = self.halo_bwd_recv[:nsd], self.halo_fwd_recv[:nsd]
+        self._pd = _abi.PoolDesc()
+        self._pd.nsd, self._pd.mode = nsd, _abi.POOL_MODES[mode]
+        for s_ in range(3):
+            self._pd.window[s_], self._pd.pads[s_], self._pd.strides[s_] = 1, 0, 1
+        for i in range(nsd):
+            self._pd.window[2 - i], self._pd.pads[2 - i], self._pd.strides[2 - i] = windows[i], eff_pads[i], strides[i]
+            # The halo of a rank at the boundary of the global tensor stands for
+            # padding.  The reference leaves it to cuDNN as zero data; here the
+            # kernel is told, so that MAX and AVERAGE_NO_PAD agree with one rank.
+            split = input.dist.split_shape[i] > 1
+            first, last = input.split_idx[i] == 0, input.split_idx[i] == input.dist.split_shape[i] - 1
+            self._pd.outside_lo[2 - i] = self._lo[i] if split and first else 0
+            self._pd.outside_hi[2 - i] = self._hi[i] if split and last else 0
+        self.halo_xch_input = HaloExchange(input)
+        self.halo_xch_d_input = HaloExchange(d_input)
+        if connect:
+            self.halo_xch_input.setup()
+            self.halo_xch_d_input.setup()
+
+    def _halo_dims(self, t: Tensor):
+        d = t.dist
+        return [i for i in range(self.nsd) if d.is_distributed(i) and d.locale_shape[i] > 1 and d.get_overlap(i) > 0]
+
+    def forward(self, alpha, input: Tensor, beta, output: Tensor, training=True, skip_halo_exchange=False):
+        """pooling.hpp:212-244.  Ranks with an empty output still take part in
+        the exchange."""
+        s = self.be.stream
+        if not skip_halo_exchange:
+            for dim in self._halo_dims(input):
+                input.clear_halo(dim, s)
+            self.halo_xch_input.exchange(s)
+        if output.get_local_size() == 0:
+            return 0
+        xd, yd = input.nd_desc(self._lo, self._hi), output.nd_desc()
+        call("dcb_pool_fwd", ctypes.byref(self._pd), ctypes.byref(xd), ctypes.byref(yd), float(alpha),
+             _ptr(input.nd_ptr(self._lo)), float(beta), _ptr(output.get_base_ptr()), _stream_ptr(s))
+        return 0
+
+    def backward(self, alpha, output: Tensor, d_output: Tensor, input: Tensor, beta, d_input: Tensor,
+                 skip_halo_exchange=False):
+        """pooling.hpp:246-283: gradients for the halo cells are computed here
+        and travel back with SUM.  The exchange moves whole halos, so the cells
+        of d_input's halo that no local window reaches are cleared first."""
+        if d_input.get_local_size() == 0:
+            return 0
+        s = self.be.stream
+        for dim in self._halo_dims(d_input):
+            d_input.clear_halo(dim, s)
+        if d_output.get_local_size() > 0:
+            xd, yd = input.nd_desc(self._lo, self._hi), output.nd_desc()
+            dxd, dyd = d_input.nd_desc(self._lo, self._hi), d_output.nd_desc()
+            assert list(xd.strides) == list(dxd.strides) and list(yd.strides) == list(dyd.strides)
+            call("dcb_pool_bwd", ctypes.byref(self._pd), ctypes.byref(xd), ctypes.byref(yd), float(alpha),
+                 _ptr(output.get_base_ptr()), _ptr(d_output.get_base_ptr()), _ptr(input.nd_ptr(self._lo)),
+                 float(beta), _ptr(d_input.nd_ptr(self._lo)), _stream_ptr(s))
+        if not skip_halo_exchange:
+            self.halo_xch_d_input.exchange(s, is_reverse=True, op="SUM")
+        return 0
+
+    def wait(self):
+        self.be.wait()
 
 
 class LeakyReLU:

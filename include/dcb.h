@@ -298,6 +298,48 @@ int32_t dcb_leaky_relu_bwd(const dcb_nd_desc* xd, const void* x,
                            const dcb_nd_desc* dxd, void* dx, void* stream);
 
 /* ------------------------------------------------------------------------
+ * Pooling.  Stands in for cudnnPoolingForward / cudnnPoolingBackward behind
+ * GPUDNNBackend::pooling_forward / _backward as Pooling<BackendDNNLib,T> calls
+ * them (legacy/include/distconv/dnn_backend/pooling.hpp:212-283): xd describes
+ * the input window including the halo cells of partitioned dimensions (whose
+ * pad is then 0, pooling.hpp:189-194), yd the output.  Modes as
+ * pooling::get_pooling_mode maps them (pooling.hpp:27-48).
+ * ------------------------------------------------------------------------ */
+#define DCB_POOL_MAX 0            /* "MAX" */
+#define DCB_POOL_AVERAGE 1        /* "AVERAGE": padding cells count */
+#define DCB_POOL_AVERAGE_NO_PAD 2 /* "AVERAGE_NO_PAD" */
+
+typedef struct dcb_pool_desc
+{
+    int32_t nsd;
+    int32_t window[DCB_MAX_SPATIAL]; /* D,H,W (window[0] = 1 if nsd == 2) */
+    int32_t pads[DCB_MAX_SPATIAL];
+    int32_t strides[DCB_MAX_SPATIAL];
+    int32_t mode;
+    /* Leading / trailing cells of the x window that lie outside the global
+     * tensor: the halo of a rank at the domain boundary in a partitioned,
+     * padded dimension.  They are padding (ignored by MAX and by
+     * AVERAGE_NO_PAD's count), not data; 0 everywhere else. */
+    int32_t outside_lo[DCB_MAX_SPATIAL];
+    int32_t outside_hi[DCB_MAX_SPATIAL];
+} dcb_pool_desc;
+
+/* y = alpha * pool(x) + beta * y. */
+int32_t dcb_pool_fwd(const dcb_pool_desc* pd, const dcb_nd_desc* xd,
+                     const dcb_nd_desc* yd, double alpha, const void* x,
+                     double beta, void* y, void* stream);
+/* dx = alpha * pool'(dy) + beta * dx over the whole x window (halo cells
+ * included: a reverse halo exchange with SUM returns them to their owners,
+ * pooling.hpp:281).  x and dx share xd, y and dy share yd.  MAX sends a
+ * window's gradient to the first cell (scan order D, H, W) equal to y, which
+ * must be the unscaled forward result; x and y may be null for the averages.
+ * A gather over the input cells: reproducible. */
+int32_t dcb_pool_bwd(const dcb_pool_desc* pd, const dcb_nd_desc* xd,
+                     const dcb_nd_desc* yd, double alpha, const void* y,
+                     const void* dy, const void* x, double beta, void* dx,
+                     void* stream);
+
+/* ------------------------------------------------------------------------
  * All-reduce of small device vectors (BN statistics, filter gradients).
  * Stands in for tensor::Allreduce<T> and its Aluminum/NCCL, MPI-via-host and
  * NVSHMEM implementations (legacy/include/distconv/tensor/allreduce.hpp:8-19,

@@ -25,6 +25,14 @@ What is restated, and from where:
   answer of legacy/tests/tensor/test_halo_exchange_cuda.cu:52-233 (every halo
   cell inside the global domain equals its global linear offset).
 * convolution / batch-norm arithmetic -- ``conv_oracle.c`` (see its header).
+* pooling -- the arithmetic lives in cuDNN (cudnnPoolingForward / Backward,
+  reached from legacy/include/distconv/dnn_backend/pooling.hpp:212-283; no
+  version pinned), restated below from its documented semantics: modes as
+  pooling.hpp:27-48 maps them, padding ignored by MAX and counted (or not) by
+  the averages, the gradient of a maximum sent to one cell per window.  The
+  reference pins the forward pass against another framework
+  (legacy/tests/dnn_backend/chainer_pooling.py); ``tests/test_oracle_cpu.py``
+  does the same against torch's CPU pooling.
 """
 from __future__ import annotations
 
@@ -146,6 +154,84 @@ def conv_bwd_filter(x, dy, fshape, pads, strides, dilations=None, alpha=1.0, bet
     _lib().oracle_conv_bwd_filter(_ptr(x5), ctypes.byref(xd), _ptr(y5), ctypes.byref(yd), _ptr(dw), ctypes.byref(cd),
                                   ctypes.c_double(alpha), ctypes.c_double(beta))
     return dw
+
+
+# --------------------------------------------------------------------------
+# pooling
+# --------------------------------------------------------------------------
+
+POOL_MODES = ("MAX", "AVERAGE", "AVERAGE_NO_PAD")
+
+
+def _pool_windows(x5, window, pads, strides):
+    """(taps, N, C, oD, oH, oW) stack of the window cells of every output, NaN
+    where a cell is padding, and the flat input index of each (-1 = padding)."""
+    n, c = x5.shape[:2]
+    ext = x5.shape[2:]
+    out = [conv_out_extent(e, w, p, s) for e, w, p, s in zip(ext, window, pads, strides)]
+    idx = np.arange(int(np.prod(ext))).reshape(ext)
+    vals, where = [], []
+    grids = np.meshgrid(*[np.arange(o) for o in out], indexing="ij")
+    for tap in itertools.product(*[range(w) for w in window]):
+        coord = [g * s - p + t for g, s, p, t in zip(grids, strides, pads, tap)]
+        ok = np.ones(out, bool)
+        for cd, e in zip(coord, ext):
+            ok &= (cd >= 0) & (cd < e)
+        cl = [np.clip(cd, 0, e - 1) for cd, e in zip(coord, ext)]
+        flat = np.where(ok, idx[tuple(cl)], -1)
+        v = x5.reshape(n, c, -1)[:, :, np.maximum(flat, 0).ravel()].reshape(n, c, *out).astype(np.float64)
+        v[:, :, ~ok] = np.nan
+        vals.append(v)
+        where.append(flat)
+    return np.stack(vals), np.stack(where), out
+
+
+def _pool_count(where, window, mode):
+    if mode == "AVERAGE":
+        return float(np.prod(window))
+    return np.maximum((where >= 0).sum(axis=0), 1).astype(np.float64)
+
+
+def pool_fwd(x, window, pads, strides, mode="MAX"):
+    """y = pool(x); window / pads / strides per spatial axis, outermost first."""
+    assert mode in POOL_MODES
+    x5 = _as5(x)
+    nsd = x.ndim - 2
+    w3, p3, s3 = ([a] * (3 - nsd) + list(v) for a, v in ((1, window), (0, pads), (1, strides)))
+    vals, where, out = _pool_windows(x5, w3, p3, s3)
+    if mode == "MAX":
+        y = np.nanmax(vals, axis=0)
+    else:
+        y = np.nansum(vals, axis=0) / _pool_count(where, w3, mode)
+    return y.astype(np.float32).reshape(x.shape[:2] + tuple(out[3 - nsd:]))
+
+
+def pool_bwd(x, dy, window, pads, strides, mode="MAX"):
+    """dx of pool_fwd, padding cells dropped.  MAX: the whole of dy[o] goes to
+    the first cell of o's window (scan order outermost axis first) that holds
+    the maximum."""
+    assert mode in POOL_MODES
+    x5, dy5 = _as5(x), _as5(dy)
+    nsd = x.ndim - 2
+    w3, p3, s3 = ([a] * (3 - nsd) + list(v) for a, v in ((1, window), (0, pads), (1, strides)))
+    vals, where, out = _pool_windows(x5, w3, p3, s3)
+    n, c = x5.shape[:2]
+    dx = np.zeros((n, c, int(np.prod(x5.shape[2:]))), np.float64)
+    g = dy5.astype(np.float64)
+    if mode == "MAX":
+        first = np.argmax(np.where(np.isnan(vals), -np.inf, vals), axis=0)  # ties: lowest tap index
+        for i in range(n):
+            for j in range(c):
+                tgt = np.take_along_axis(where, first[i, j][None], axis=0)[0]
+                np.add.at(dx[i, j], tgt.ravel(), g[i, j].ravel())
+    else:
+        share = g / _pool_count(where, w3, mode)
+        for t in range(where.shape[0]):
+            ok = where[t] >= 0
+            for i in range(n):
+                for j in range(c):
+                    np.add.at(dx[i, j], where[t][ok], share[i, j][ok])
+    return dx.astype(np.float32).reshape(x.shape)
 
 
 # --------------------------------------------------------------------------

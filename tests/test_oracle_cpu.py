@@ -168,3 +168,36 @@ def test_bn_oracle_backward_matches_autograd_formula():
     assert np.allclose(dx, dx_ref, rtol=1e-4, atol=1e-5)
     assert np.allclose(dbias, dyd.sum(axis=(0, 2, 3)), rtol=1e-6)
     assert np.allclose(dscale, (dyd * (xd - m) * inv).sum(axis=(0, 2, 3)), rtol=1e-4, atol=1e-5)
+
+
+# --------------------------------------------------------------------------
+# pooling: the restatement against torch's CPU pooling (an independent
+# implementation, as the reference's own test uses another framework:
+# legacy/tests/dnn_backend/chainer_pooling.py)
+# --------------------------------------------------------------------------
+@pytest.mark.parametrize("mode", O.POOL_MODES)
+@pytest.mark.parametrize("shape,window,pads,strides", [
+    ((2, 3, 7, 9, 11), (3, 3, 3), (1, 1, 1), (2, 2, 2)),
+    ((1, 2, 8, 10), (2, 2), (0, 0), (2, 2)),
+    ((2, 2, 6, 7, 8), (3, 3, 3), (1, 1, 1), (1, 1, 1)),
+    ((1, 2, 9, 12), (3, 3), (0, 0), (1, 1)),
+    ((1, 1, 11, 13), (5, 5), (2, 2), (3, 3)),
+])
+def test_pooling_oracle_against_torch(shape, window, pads, strides, mode):
+    import torch
+    import torch.nn.functional as F
+
+    rng = np.random.default_rng(0)
+    x = rng.integers(-3, 4, size=shape).astype(np.float32)  # ties on purpose
+    xt = torch.tensor(x, requires_grad=True)
+    three = len(window) == 3
+    if mode == "MAX":
+        y = (F.max_pool3d if three else F.max_pool2d)(xt, window, strides, pads)
+    else:
+        y = (F.avg_pool3d if three else F.avg_pool2d)(xt, window, strides, pads,
+                                                      count_include_pad=(mode == "AVERAGE"))
+    dy = torch.tensor(rng.normal(size=y.shape).astype(np.float32))
+    y.backward(dy)
+    np.testing.assert_allclose(O.pool_fwd(x, window, pads, strides, mode), y.detach().numpy(), rtol=0, atol=1e-6)
+    np.testing.assert_allclose(O.pool_bwd(x, dy.numpy(), window, pads, strides, mode), xt.grad.numpy(), rtol=0,
+                               atol=2e-6)
