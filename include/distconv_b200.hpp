@@ -77,6 +77,12 @@ inline void check(int32_t st, const char* what)
     if (st != DCB_OK)
         throw std::runtime_error(std::string(what) + ": " + dcb_status_string(st) + " (" + dcb_last_error() + ")");
 }
+// the reference's assert_always: a programmer error
+inline void require(bool cond, const char* what)
+{
+    if (!cond)
+        throw std::invalid_argument(what);
+}
 } // namespace util
 
 namespace tensor
@@ -562,6 +568,26 @@ inline TensorF create_convolution_d_output_tensor(const TensorF& output, const i
     tensor::Distribution d2(dist.get_locale_shape(), dist.get_split_shape(), overlap);
     TensorF out_copy = output;
     return TensorF(output.get_shape(), output.get_locale(), d2,
+                   [out_copy](const tensor::IndexVector& p) { return out_copy.local_of(p); });
+}
+
+// distconv.hpp:518-581.  Odd windows with pad 0 or (window-1)/2, even windows
+// with stride == window: the output extents and the per-rank split follow the
+// convolution's formulas with K = C.
+inline TensorF create_pooling_output_tensor(const TensorF& input, const int_vector& window,
+                                            const int_vector& strides, const int_vector& pad)
+{
+    const int nsd = input.get_num_dims() - 2;
+    int_vector fshape(window.begin(), window.begin() + nsd);
+    fshape.push_back((int) input.get_shape()[-2]);
+    fshape.push_back((int) input.get_shape()[-2]);
+    return create_convolution_output_tensor(input, fshape, strides, pad, int_vector(nsd, 1));
+}
+
+inline TensorF create_pooling_d_output_tensor(const TensorF& output)
+{
+    TensorF out_copy = output;
+    return TensorF(output.get_shape(), output.get_locale(), output.get_distribution(),
                    [out_copy](const tensor::IndexVector& p) { return out_copy.local_of(p); });
 }
 
@@ -1160,6 +1186,130 @@ private:
     float m_decay, m_epsilon;
     bool m_global_stats;
     dcb_bn_plan* m_plan = nullptr; // one tensor shape per layer object
+};
+
+// Pooling<BackendDNNLib, float> (pooling.hpp:70-482).  Modes "MAX", "AVERAGE",
+// "AVERAGE_NO_PAD" (pooling.hpp:27-48).
+template <typename Backend, typename DataType>
+class Pooling;
+
+template <>
+class Pooling<BackendDNNLib, float>
+{
+public:
+    Pooling(BackendDNNLib& backend, int num_dims, HaloExchangeMethod = HaloExchangeMethod::P2P)
+        : m_be(backend), m_num_dims(num_dims), m_nsd(num_dims - 2)
+    {
+    }
+
+    // pooling.hpp:101-209
+    void setup(TensorF& input, TensorF& output, TensorF& d_input, TensorF& d_output, int_vector windows,
+               int_vector pads, int_vector strides, const std::string& mode)
+    {
+        util::require((int) windows.size() == m_nsd && (int) pads.size() == m_nsd && (int) strides.size() == m_nsd,
+                      "pooling: windows / pads / strides must have one entry per spatial dimension");
+        for (int i = 0; i < m_nsd; ++i)
+        {
+            util::require(windows[i] == windows[0] && pads[i] == pads[0] && strides[i] == strides[0],
+                          "pooling: asymmetric windows are not supported");
+            if (windows[i] % 2)
+                util::require((pads[i] == 0 || pads[i] == (windows[i] - 1) / 2)
+                                  && (strides[i] == 1 || strides[i] == (windows[i] - 1) / 2 + 1),
+                              "pooling: unsupported pad / stride for an odd window");
+            else
+                util::require(windows[i] == strides[i] && pads[i] == 0,
+                              "pooling: an even window needs stride == window and no padding");
+        }
+        util::require(mode == "MAX" || mode == "AVERAGE" || mode == "AVERAGE_NO_PAD", "pooling: unknown mode");
+        std::memset(&m_pd, 0, sizeof(m_pd));
+        m_pd.nsd = m_nsd;
+        m_pd.mode = mode == "MAX" ? DCB_POOL_MAX : (mode == "AVERAGE" ? DCB_POOL_AVERAGE : DCB_POOL_AVERAGE_NO_PAD);
+        const bool use_padding = pads[0] != 0;
+        tensor::IntVector w(windows.begin(), windows.end()), st(strides.begin(), strides.end()), dl(m_nsd, 1);
+        internal::get_halo_sizes(input, w, st, dl, m_halo_fwd_send, m_halo_bwd_send, m_halo_fwd_recv,
+                                 m_halo_bwd_recv, use_padding);
+        for (int s = 0; s < 3; ++s)
+        {
+            m_pd.window[s] = 1;
+            m_pd.strides[s] = 1;
+        }
+        const auto& dist = input.get_distribution();
+        for (int i = 0; i < m_nsd; ++i)
+        {
+            const bool split = dist.get_split_shape()[i] > 1;
+            m_pd.window[2 - i] = windows[i];
+            m_pd.strides[2 - i] = strides[i];
+            // where a dimension is split the halo stands in for the padding
+            // (pooling.hpp:189-194); at the boundary of the global tensor it is
+            // padding, and the kernel is told so
+            m_pd.pads[2 - i] = split ? 0 : pads[i];
+            const bool first = input.get_split_index()[i] == 0;
+            const bool last = input.get_split_index()[i] == dist.get_split_shape()[i] - 1;
+            m_pd.outside_lo[2 - i] = split && first ? m_halo_bwd_recv[i] : 0;
+            m_pd.outside_hi[2 - i] = split && last ? m_halo_fwd_recv[i] : 0;
+        }
+        m_halo_xch_input.reset(new tensor::HaloExchange(input));
+        m_halo_xch_d_input.reset(new tensor::HaloExchange(d_input));
+        (void) output;
+        (void) d_output;
+    }
+
+    // pooling.hpp:212-244
+    int forward(float alpha, TensorF& input, float beta, TensorF& output, bool /*training*/ = true,
+                bool skip_halo_exchange = false)
+    {
+        if (!skip_halo_exchange)
+        {
+            clear_halos(input);
+            m_halo_xch_input->exchange(m_be.get_stream());
+        }
+        if (output.get_local_size() == 0)
+            return 0;
+        const dcb_nd_desc xd = input.nd_desc(m_halo_bwd_recv, m_halo_fwd_recv), yd = output.nd_desc();
+        util::check(dcb_pool_fwd(&m_pd, &xd, &yd, alpha, input.nd_ptr(m_halo_bwd_recv), beta, output.get_base_ptr(),
+                                 m_be.get_stream()),
+                    "pooling forward");
+        return 0;
+    }
+
+    // pooling.hpp:246-283: the gradients computed for halo cells return to their
+    // owners with SUM; the halo cells no local window reaches are cleared first.
+    int backward(float alpha, TensorF& output, TensorF& d_output, TensorF& input, float beta, TensorF& d_input,
+                 bool skip_halo_exchange = false)
+    {
+        if (d_input.get_local_size() == 0)
+            return 0;
+        clear_halos(d_input);
+        if (d_output.get_local_size() > 0)
+        {
+            const dcb_nd_desc xd = input.nd_desc(m_halo_bwd_recv, m_halo_fwd_recv), yd = output.nd_desc();
+            util::check(dcb_pool_bwd(&m_pd, &xd, &yd, alpha, output.get_base_ptr(), d_output.get_base_ptr(),
+                                     input.nd_ptr(m_halo_bwd_recv), beta, d_input.nd_ptr(m_halo_bwd_recv),
+                                     m_be.get_stream()),
+                        "pooling backward");
+        }
+        if (!skip_halo_exchange)
+            m_halo_xch_d_input->exchange(m_be.get_stream(), true, false, tensor::HaloExchangeAccumOp::SUM);
+        return 0;
+    }
+
+    void wait() { m_be.wait(); }
+    tensor::HaloExchange& input_halo_exchange() { return *m_halo_xch_input; }
+    tensor::HaloExchange& d_input_halo_exchange() { return *m_halo_xch_d_input; }
+
+private:
+    void clear_halos(TensorF& t)
+    {
+        const auto& d = t.get_distribution();
+        for (int dim = 0; dim < m_nsd; ++dim)
+            if (d.is_distributed(dim) && d.get_locale_shape()[dim] > 1 && d.get_overlap(dim) > 0)
+                t.clear_halo(dim, m_be.get_stream());
+    }
+    BackendDNNLib& m_be;
+    int m_num_dims, m_nsd;
+    dcb_pool_desc m_pd;
+    tensor::IntVector m_halo_fwd_send, m_halo_bwd_send, m_halo_fwd_recv, m_halo_bwd_recv;
+    std::unique_ptr<tensor::HaloExchange> m_halo_xch_input, m_halo_xch_d_input;
 };
 
 // LeakyReLU<BackendDNNLib> (leaky_relu.hpp; leaky_relu.cu:14-41)

@@ -1,5 +1,6 @@
 // Drives one spatially-partitioned conv + batch-norm layer (forward and the
-// three backward passes of the convolution) through the C++ classes of
+// three backward passes of the convolution) and a max-pooling of the same input
+// (forward, backward with the reverse SUM exchange) through the C++ classes of
 // distconv_b200.hpp, with R ranks run as R host threads on one GPU, and checks
 // every result against plain loops over the unpartitioned problem.
 //
@@ -63,8 +64,44 @@ inline size_t gi(int n, int c, int d, int h, int w, int Cc)
 struct Global
 {
     std::vector<float> x, w, dy, y, dx, dw, z; // z = batch-norm output
+    std::vector<float> pdy, py, pdx;           // 3x3x3 max-pooling of x, stride 1, pad 1
     std::vector<float> mean, var;
 };
+
+void pool_reference(Global& g)
+{
+    const size_t nx = (size_t) N * C * D * H * W;
+    g.py.assign(nx, 0.f);
+    g.pdx.assign(nx, 0.f);
+    for (int n = 0; n < N; ++n)
+        for (int c = 0; c < C; ++c)
+            for (int d = 0; d < D; ++d)
+                for (int h = 0; h < H; ++h)
+                    for (int w = 0; w < W; ++w)
+                    {
+                        float best = 0.f;
+                        size_t at = 0;
+                        bool any = false;
+                        for (int kd = -1; kd <= 1; ++kd)
+                            for (int kh = -1; kh <= 1; ++kh)
+                                for (int kw = -1; kw <= 1; ++kw)
+                                {
+                                    const int dd = d + kd, hh = h + kh, ww = w + kw;
+                                    if (dd < 0 || dd >= D || hh < 0 || hh >= H || ww < 0 || ww >= W)
+                                        continue;
+                                    const size_t i = gi(n, c, dd, hh, ww, C);
+                                    if (!any || g.x[i] > best) // the first maximum keeps the gradient
+                                    {
+                                        best = g.x[i];
+                                        at = i;
+                                        any = true;
+                                    }
+                                }
+                        const size_t o = gi(n, c, d, h, w, C);
+                        g.py[o] = best;
+                        g.pdx[at] += g.pdy[o];
+                    }
+}
 
 void reference(Global& g)
 {
@@ -262,6 +299,23 @@ void rank_main(int rank, int R, Shared* sh, const Global* g)
             throw std::runtime_error("layer status");
         cudaStreamSynchronize(st);
 
+        // max-pooling of x (its halos are still in place); the gradients a rank
+        // computes for its neighbours' cells go back with the reverse SUM exchange
+        TensorF py = create_pooling_output_tensor(x, f3, ones, pads);
+        TensorF pdy = create_pooling_d_output_tensor(py);
+        TensorF pdx = create_d_input_tensor(x);
+        for (TensorF* t : {&py, &pdy, &pdx})
+            if (t->allocate())
+                throw std::runtime_error("allocate");
+        scatter(pdy, g->pdy, C);
+        Pooling<BackendDNNLib, float> pool(be, 5);
+        pool.setup(x, py, pdx, pdy, f3, pads, ones, "MAX");
+        pool.forward(1.f, x, 0.f, py, true, /*skip_halo_exchange=*/true);
+        pool.backward(1.f, py, pdy, x, 0.f, pdx, /*skip_halo_exchange=*/true);
+        phase([&] { pool.d_input_halo_exchange().pack_put(2, st, true, tensor::HaloExchangeAccumOp::SUM); },
+              [&] { pool.d_input_halo_exchange().wait_unpack(2, st, true, tensor::HaloExchangeAccumOp::SUM); });
+        const double e_py = gather_err(py, g->py, C), e_pdx = gather_err(pdx, g->pdx, C);
+
         std::vector<float> hdw(wcount), hstats(2 * K);
         cudaMemcpy(hdw.data(), dw, wcount * 4, cudaMemcpyDeviceToHost);
         cudaMemcpy(hstats.data(), stats, 2 * K * 4, cudaMemcpyDeviceToHost);
@@ -274,9 +328,12 @@ void rank_main(int rank, int R, Shared* sh, const Global* g)
             e_st = std::max(e_st, (double) std::fabs(hstats[K + k] - g->var[k]) / (1.0 + g->var[k]));
         }
         const double e_y = gather_err(y, g->y, K), e_dx = gather_err(dx, g->dx, C), e_z = gather_err(z, g->z, K);
-        std::printf("rank %d/%d: y %.2e  dx %.2e  dw %.2e  stats %.2e  bn %.2e  (fwd kernel kind %d, statistics %s)\n",
-                    rank, R, e_y, e_dx, e_dw, e_st, e_z, conv.kernel_kind(0), fused ? "fused" : "separate");
-        const bool ok = e_y < 2e-5 && e_dx < 2e-5 && e_dw < 5e-5 && e_st < 2e-5 && e_z < 1e-4;
+        std::printf("rank %d/%d: y %.2e  dx %.2e  dw %.2e  stats %.2e  bn %.2e  pool %.2e / %.2e  (fwd kernel kind %d, "
+                    "statistics %s)\n",
+                    rank, R, e_y, e_dx, e_dw, e_st, e_z, e_py, e_pdx, conv.kernel_kind(0),
+                    fused ? "fused" : "separate");
+        const bool ok = e_y < 2e-5 && e_dx < 2e-5 && e_dw < 5e-5 && e_st < 2e-5 && e_z < 1e-4 && e_py < 1e-6
+                        && e_pdx < 2e-6;
         if (!ok)
         {
             std::lock_guard<std::mutex> lk(sh->m);
@@ -310,6 +367,10 @@ int main(int argc, char** argv)
     for (size_t i = 0; i < g.w.size(); ++i)
         g.w[i] = 0.25f * synth((int64_t) i, 3);
     reference(g);
+    g.pdy.resize(nx);
+    for (size_t i = 0; i < nx; ++i)
+        g.pdy[i] = synth((int64_t) i, 4);
+    pool_reference(g);
     Shared sh(R);
     std::vector<std::thread> th;
     for (int r = 0; r < R; ++r)
