@@ -20,11 +20,14 @@ from .distconv import (  # noqa: F401
     Options,
     Pooling,
     Tensor,
+    TensorShuffler,
     create_convolution_d_output_tensor,
     create_convolution_output_tensor,
     create_d_input_tensor,
     create_input_tensor,
     create_pooling_d_output_tensor,
     create_pooling_output_tensor,
+    dump_local_tensor,
+    dump_tensor,
     get_halo_sizes,
 )

@@ -49,6 +49,13 @@ class NdDesc(ctypes.Structure):
     ]
 
 
+class Box(ctypes.Structure):
+    _fields_ = [("off", c_int64 * DCB_MAX_DIMS), ("ext", c_int64 * DCB_MAX_DIMS)]
+
+
+SHUFFLE_BLOB_BYTES = 128
+
+
 class PoolDesc(ctypes.Structure):
     _fields_ = [
         ("nsd", c_int32),
@@ -130,6 +137,15 @@ _SIGS = {
     "dcb_pool_fwd": (c_int32, [POINTER(PoolDesc), POINTER(NdDesc), POINTER(NdDesc), c_double, _P, c_double, _P, _P]),
     "dcb_pool_bwd": (c_int32, [POINTER(PoolDesc), POINTER(NdDesc), POINTER(NdDesc), c_double, _P, _P, _P, c_double,
                                _P, _P]),
+    "dcb_shuffle_plan_create": (c_int32, [POINTER(TensorDesc), POINTER(TensorDesc), POINTER(Box), POINTER(Box),
+                                          c_int32, c_int32, POINTER(_P)]),
+    "dcb_shuffle_plan_destroy": (c_int32, [_P]),
+    "dcb_shuffle_plan_export": (c_int32, [_P, _P]),
+    "dcb_shuffle_plan_connect": (c_int32, [_P, _P, c_int32]),
+    "dcb_shuffle_put": (c_int32, [_P, _P, _P]),
+    "dcb_shuffle_wait_unpack": (c_int32, [_P, _P, _P]),
+    "dcb_shuffle": (c_int32, [_P, _P, _P, _P]),
+    "dcb_shuffle_plan_status": (c_int32, [_P, _P]),
     "dcb_nccl_unique_id": (c_int32, [_P]),
     "dcb_comm_create_nccl": (c_int32, [_P, c_int32, c_int32, POINTER(_P)]),
     "dcb_comm_create_peer": (c_int32, [c_int32, c_int32, c_int32, POINTER(_P)]),

@@ -19,7 +19,7 @@ CSRC = os.path.join(PKG, "csrc")
 OBJ = os.path.join(PKG, "build")
 LIB = os.path.join(PKG, "libdistconv_b200.so")
 
-SOURCES = ["runtime.cu", "halo.cu", "bn.cu", "conv.cu", "conv_simt.cu", "conv_tc.cu", "comm.cu", "pool.cu"]
+SOURCES = ["runtime.cu", "halo.cu", "bn.cu", "conv.cu", "conv_simt.cu", "conv_tc.cu", "comm.cu", "pool.cu", "shuffle.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

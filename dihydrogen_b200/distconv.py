@@ -25,6 +25,7 @@ from __future__ import annotations
 import ctypes
 from typing import Callable, List, Optional, Sequence
 
+import numpy as np
 import torch
 
 from . import _abi
@@ -601,6 +602,142 @@ class HaloExchange:
 
     def status(self, stream=None) -> int:
         return _abi.lib().dcb_halo_plan_status(self._plan, _stream_ptr(stream))
+
+
+# ---------------------------------------------------------------------------
+# Re-distribution and dump
+# ---------------------------------------------------------------------------
+def owned_box(t: Tensor, rank: int):
+    """(offset, extent) in global coordinates of what ``rank`` owns of ``t``;
+    extent all zero for a rank that is not the root of a replicated dimension
+    (only roots hold the authoritative copy, tensor_mpi.hpp is_split_root)."""
+    ls = t.dist.locale_shape
+    pidx, r = [], rank
+    for n in ls:
+        pidx.append(r % n)
+        r //= n
+    per = [t.dist.get_num_ranks_per_split(i) for i in range(t.nd)]
+    if any(p % q for p, q in zip(pidx, per)):
+        return [0] * t.nd, [0] * t.nd
+    ext = t._local_of(pidx)
+    off = []
+    for d in range(t.nd):
+        o = 0
+        if t.dist.is_distributed(d):
+            for j in range(pidx[d] // per[d]):
+                idx = list(pidx)
+                idx[d] = j * per[d]
+                o += t._local_of(idx)[d]
+        off.append(o)
+    if 0 in ext:
+        ext = [0] * t.nd
+    return off, list(ext)
+
+
+class TensorShuffler:
+    """tensor::TensorMPICUDAShuffler (shuffle_mpi_cuda.hpp:14-512): moves a
+    tensor between two distributions of the same global shape.  Cells travel
+    as peer stores into the owner's receive window; see csrc/shuffle.cu."""
+
+    def __init__(self, src: Tensor, dst: Tensor, connect=True):
+        assert list(src.shape) == list(dst.shape) and src.locale.size == dst.locale.size
+        self.src, self.dst = src, dst
+        self.locale = src.locale
+        self._plans = {}
+        for key, (a, b) in (("fwd", (src, dst)), ("bwd", (dst, src))):
+            n = self.locale.size
+            sb, db = (_abi.Box * n)(), (_abi.Box * n)()
+            for r in range(n):
+                for boxes, t in ((sb, a), (db, b)):
+                    off, ext = owned_box(t, r)
+                    for i in range(t.nd):
+                        boxes[r].off[i], boxes[r].ext[i] = off[i], ext[i]
+            plan = ctypes.c_void_p()
+            ad, bd = a.desc(), b.desc()
+            call("dcb_shuffle_plan_create", ctypes.byref(ad), ctypes.byref(bd), sb, db, self.locale.rank, n,
+                 ctypes.byref(plan))
+            self._plans[key] = plan
+        if connect:
+            self.setup()
+
+    def __del__(self):
+        try:
+            for p in getattr(self, "_plans", {}).values():
+                _abi.lib().dcb_shuffle_plan_destroy(p)
+        except Exception:
+            pass
+
+    def export(self, which: str) -> bytes:
+        buf = ctypes.create_string_buffer(_abi.SHUFFLE_BLOB_BYTES)
+        call("dcb_shuffle_plan_export", self._plans[which], buf)
+        return buf.raw
+
+    def connect(self, which: str, blobs: Sequence[bytes]):
+        joined = ctypes.create_string_buffer(b"".join(blobs), _abi.SHUFFLE_BLOB_BYTES * len(blobs))
+        call("dcb_shuffle_plan_connect", self._plans[which], joined, len(blobs))
+
+    def setup(self):
+        for which in ("fwd", "bwd"):
+            self.connect(which, self.locale.allgather(self.export(which)))
+        return self
+
+    # src / dst are buffer addresses (Tensor.get_buffer()), as in the reference
+    def shuffle_forward(self, src: int, dst: int, stream=None):
+        call("dcb_shuffle", self._plans["fwd"], _ptr(src), _ptr(dst), _stream_ptr(stream))
+
+    def shuffle_backward(self, src: int, dst: int, stream=None):
+        call("dcb_shuffle", self._plans["bwd"], _ptr(src), _ptr(dst), _stream_ptr(stream))
+
+    # halves, for ranks that share a device (every put before any wait)
+    def put(self, which: str, src: int, stream=None):
+        call("dcb_shuffle_put", self._plans[which], _ptr(src), _stream_ptr(stream))
+
+    def wait_unpack(self, which: str, dst: int, stream=None):
+        call("dcb_shuffle_wait_unpack", self._plans[which], _ptr(dst), _stream_ptr(stream))
+
+    def status(self, which: str, stream=None) -> int:
+        return _abi.lib().dcb_shuffle_plan_status(self._plans[which], _stream_ptr(stream))
+
+
+def dump_tensor(t: Tensor, file_path: str, binary: bool = False) -> int:
+    """distconv.hpp:581-631: rank 0 writes the whole tensor in memory order
+    (dimension 0 fastest, no halos) to ``file_path + ".out"`` as raw float32, or
+    ``+ ".txt"`` one value per line.  Collective: every rank contributes what it
+    owns through the locale's allgather."""
+    off, ext = owned_box(t, t.locale.rank)
+    own = t.owned().detach().cpu().numpy().astype(np.float32) if 0 not in ext else np.zeros(0, np.float32)
+    blobs = t.locale.allgather(own.tobytes())
+    if t.locale.rank != 0:
+        return 0
+    g = np.zeros(tuple(reversed(t.shape)), np.float32)
+    for r, blob in enumerate(blobs):
+        o, e = owned_box(t, r)
+        if 0 in e:
+            continue
+        sl = tuple(slice(a, a + b) for a, b in reversed(list(zip(o, e))))
+        g[sl] = np.frombuffer(blob, np.float32).reshape(tuple(reversed(e)))
+    if binary:
+        g.tofile(file_path + ".out")
+    else:
+        with open(file_path + ".txt", "w") as f:
+            for v in g.ravel():
+                f.write(f"{v:g}\n")
+    return 0
+
+
+def dump_local_tensor(t: Tensor, file_path: str, binary: bool = False) -> int:
+    """distconv.hpp:633-671: every rank writes its own shard (halo cells
+    included, as the reference copies out the whole local buffer) to
+    ``file_path_<rank>``."""
+    a = t.buffer.detach().cpu().numpy().astype(np.float32)
+    path = f"{file_path}_{t.locale.rank}"
+    if binary:
+        a.tofile(path + ".out")
+    else:
+        with open(path + ".txt", "w") as f:
+            for v in a.ravel():
+                f.write(f"{v:g}\n")
+    return 0
 
 
 # ---------------------------------------------------------------------------

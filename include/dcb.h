@@ -340,6 +340,49 @@ int32_t dcb_pool_bwd(const dcb_pool_desc* pd, const dcb_nd_desc* xd,
                      void* stream);
 
 /* ------------------------------------------------------------------------
+ * Re-distribution between two block decompositions of one global tensor.
+ * Stands in for tensor::TensorMPICUDAShuffler
+ * (legacy/include/distconv/tensor/shuffle_mpi_cuda.hpp:14-512; forward =
+ * shuffle_forward, and a second plan with the tensors swapped =
+ * shuffle_backward).  Boxes are in global coordinates, dimension 0 = W; box r
+ * is what rank r owns (empty for a rank that is not the root of a replicated
+ * dimension, tensor_mpi.hpp is_split_root).  Set-up is two-phase like the halo
+ * plan: create on every rank, gather the export blobs, connect.
+ * ------------------------------------------------------------------------ */
+typedef struct dcb_box
+{
+    int64_t off[DCB_MAX_DIMS];
+    int64_t ext[DCB_MAX_DIMS];
+} dcb_box;
+
+typedef struct dcb_shuffle_plan dcb_shuffle_plan;
+#define DCB_SHUFFLE_BLOB_BYTES 128
+
+/* src / dst describe the calling rank's shards (halo included, as
+ * Tensor::get_buffer() sees them); src_boxes / dst_boxes have nranks entries. */
+int32_t dcb_shuffle_plan_create(const dcb_tensor_desc* src,
+                                const dcb_tensor_desc* dst,
+                                const dcb_box* src_boxes,
+                                const dcb_box* dst_boxes, int32_t rank,
+                                int32_t nranks, dcb_shuffle_plan** plan);
+int32_t dcb_shuffle_plan_destroy(dcb_shuffle_plan* plan);
+int32_t dcb_shuffle_plan_export(dcb_shuffle_plan* plan, void* blob);
+int32_t dcb_shuffle_plan_connect(dcb_shuffle_plan* plan, const void* blobs,
+                                 int32_t nranks);
+/* One kernel: this rank's cells go straight into their owners' receive
+ * windows (peer stores), then an epoch flag per destination. */
+int32_t dcb_shuffle_put(dcb_shuffle_plan* plan, const void* src, void* stream);
+/* One kernel: bounded wait for every rank that holds a part of this rank's
+ * block, then window -> dst (halo cells untouched).  On expiry nothing is
+ * copied and dcb_shuffle_plan_status reports DCB_PEER_TIMEOUT. */
+int32_t dcb_shuffle_wait_unpack(dcb_shuffle_plan* plan, void* dst,
+                                void* stream);
+/* put + wait_unpack (ranks on different GPUs). */
+int32_t dcb_shuffle(dcb_shuffle_plan* plan, const void* src, void* dst,
+                    void* stream);
+int32_t dcb_shuffle_plan_status(dcb_shuffle_plan* plan, void* stream);
+
+/* ------------------------------------------------------------------------
  * All-reduce of small device vectors (BN statistics, filter gradients).
  * Stands in for tensor::Allreduce<T> and its Aluminum/NCCL, MPI-via-host and
  * NVSHMEM implementations (legacy/include/distconv/tensor/allreduce.hpp:8-19,

@@ -110,6 +110,21 @@ assert peers == ([-1, 1] if loc.rank == 0 else [0, -1]), peers
 import bench
 g = bench.layer_geometry(2, loc, extent=16)
 assert g["shape"][2] == 32 and g["input"].get_local_shape()[2] == 16
+# dump_tensor: rank 0 writes the global tensor, no halos, dimension 0 fastest
+import numpy as np
+g5 = np.arange(6 * 8 * 4 * 2, dtype=np.float32).reshape(2, 4, 8, 6)  # N, C, H, W
+td = dc.create_input_tensor([6, 8, 4, 2], [1, 2, 1, 1], [3, 3], [1, 1], [1, 1], loc)
+td.allocate(device="cpu")
+td.buffer.fill_(-1.0)
+import torch
+td.owned().copy_(torch.from_numpy(g5[:, :, 4 * loc.rank:4 * loc.rank + 4, :].copy()))
+assert dc.distconv.owned_box(td, 1) == ([0, 4, 0, 0], [6, 4, 4, 2])
+dc.dump_tensor(td, {dump!r}, binary=True)
+dc.dump_tensor(td, {dump!r}, binary=False)
+dist.barrier()
+if loc.rank == 0:
+    assert np.array_equal(np.fromfile({dump!r} + ".out", np.float32), g5.ravel())
+    assert np.array_equal(np.loadtxt({dump!r} + ".txt", dtype=np.float32), g5.ravel())
 dist.barrier()
 print("ok", loc.rank)
 """
@@ -118,7 +133,7 @@ print("ok", loc.rank)
 def test_two_rank_setup_over_gloo(tmp_path):
     port = 29500 + os.getpid() % 2000
     script = tmp_path / "gloo2.py"
-    script.write_text(_GLOO_SCRIPT.format(root=ROOT, port=port))
+    script.write_text(_GLOO_SCRIPT.format(root=ROOT, port=port, dump=str(tmp_path / "dump")))
     procs = [subprocess.Popen([sys.executable, str(script), str(r)], stdout=subprocess.PIPE,
                               stderr=subprocess.STDOUT, cwd=ROOT) for r in range(2)]
     outs = [p.communicate(timeout=240)[0].decode() for p in procs]
