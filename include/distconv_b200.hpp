@@ -686,6 +686,108 @@ private:
     TensorF& m_tensor;
     dcb_halo_plan* m_plan = nullptr;
 };
+// What `rank` owns of t, in global coordinates; empty for a rank that is not
+// the root of a replicated dimension.
+inline dcb_box owned_box(const TensorF& t, int rank)
+{
+    dcb_box b;
+    std::memset(&b, 0, sizeof(b));
+    const int nd = t.get_num_dims();
+    const auto& d = t.get_distribution();
+    IndexVector pidx(nd, 0);
+    int r = rank;
+    bool root = true;
+    for (int i = 0; i < nd; ++i)
+    {
+        pidx[i] = r % d.get_locale_shape()[i];
+        r /= (int) d.get_locale_shape()[i];
+        root = root && pidx[i] % d.get_num_ranks_per_split(i) == 0;
+    }
+    const Shape ext = t.local_of(pidx);
+    if (!root || ext.get_size() == 0)
+        return b;
+    for (int i = 0; i < nd; ++i)
+    {
+        b.ext[i] = ext[i];
+        if (!d.is_distributed(i))
+            continue;
+        const index_t per = d.get_num_ranks_per_split(i);
+        for (index_t j = 0; j < pidx[i] / per; ++j)
+        {
+            IndexVector idx = pidx;
+            idx[i] = j * per;
+            b.off[i] += t.local_of(idx)[i];
+        }
+    }
+    return b;
+}
+
+// tensor::TensorMPICUDAShuffler (shuffle_mpi_cuda.hpp:14-512): re-distribution
+// between the distributions of two tensors of one global shape.  The optional
+// work buffers of the reference's constructor are accepted and unused: cells go
+// straight into the owners' receive windows.
+template <typename DataType>
+class TensorMPICUDAShuffler;
+
+template <>
+class TensorMPICUDAShuffler<float>
+{
+public:
+    TensorMPICUDAShuffler(const TensorF& src_tensor, const TensorF& dst_tensor, float* /*src_buf*/ = nullptr,
+                          float* /*dst_buf*/ = nullptr)
+    {
+        m_fwd = make(src_tensor, dst_tensor);
+        m_bwd = make(dst_tensor, src_tensor);
+    }
+    TensorMPICUDAShuffler(const TensorMPICUDAShuffler&) = delete;
+    ~TensorMPICUDAShuffler()
+    {
+        dcb_shuffle_plan_destroy(m_fwd);
+        dcb_shuffle_plan_destroy(m_bwd);
+    }
+    void shuffle_forward(const float* src, float* dst, cudaStream_t stream = 0)
+    {
+        util::check(dcb_shuffle(m_fwd, src, dst, stream), "shuffle forward");
+    }
+    void shuffle_backward(const float* src, float* dst, cudaStream_t stream = 0)
+    {
+        util::check(dcb_shuffle(m_bwd, src, dst, stream), "shuffle backward");
+    }
+    // The halves of a shuffle, for callers that run several ranks on one device.
+    void put(bool forward, const float* src, cudaStream_t stream)
+    {
+        util::check(dcb_shuffle_put(forward ? m_fwd : m_bwd, src, stream), "shuffle put");
+    }
+    void wait_unpack(bool forward, float* dst, cudaStream_t stream)
+    {
+        util::check(dcb_shuffle_wait_unpack(forward ? m_fwd : m_bwd, dst, stream), "shuffle wait_unpack");
+    }
+    int32_t status(bool forward, cudaStream_t stream) { return dcb_shuffle_plan_status(forward ? m_fwd : m_bwd, stream); }
+    static size_t get_buf_size(const TensorF& tensor) { return (size_t) tensor.get_local_size() * sizeof(float); }
+
+private:
+    static dcb_shuffle_plan* make(const TensorF& a, const TensorF& b)
+    {
+        const int n = a.get_locale().get_size();
+        std::vector<dcb_box> ab((size_t) n), bb((size_t) n);
+        for (int r = 0; r < n; ++r)
+        {
+            ab[r] = owned_box(a, r);
+            bb[r] = owned_box(b, r);
+        }
+        const dcb_tensor_desc ad = a.desc(), bd = b.desc();
+        dcb_shuffle_plan* p = nullptr;
+        util::check(dcb_shuffle_plan_create(&ad, &bd, ab.data(), bb.data(), a.get_locale().get_rank(), n, &p),
+                    "shuffle plan");
+        std::vector<char> mine(DCB_SHUFFLE_BLOB_BYTES), all((size_t) n * DCB_SHUFFLE_BLOB_BYTES);
+        util::check(dcb_shuffle_plan_export(p, mine.data()), "shuffle export");
+        a.get_locale().allgather(mine.data(), all.data(), DCB_SHUFFLE_BLOB_BYTES);
+        util::check(dcb_shuffle_plan_connect(p, all.data(), n), "shuffle connect");
+        return p;
+    }
+    dcb_shuffle_plan* m_fwd = nullptr;
+    dcb_shuffle_plan* m_bwd = nullptr;
+};
 } // namespace tensor
 
 // DNNBackend<GPUDNNBackend> (dnn_backend.hpp:635-980): the main stream (not

@@ -316,6 +316,25 @@ void rank_main(int rank, int R, Shared* sh, const Global* g)
               [&] { pool.d_input_halo_exchange().wait_unpack(2, st, true, tensor::HaloExchangeAccumOp::SUM); });
         const double e_py = gather_err(py, g->py, C), e_pdx = gather_err(pdx, g->pdx, C);
 
+        // re-distribution: x (partitioned along D) -> sample-parallel where N divides, and back
+        double e_shf = 0;
+        if (N % R == 0)
+        {
+            const tensor::Shape gs(std::vector<index_t>{W, H, D, C, N});
+            TensorF xs(gs, loc,
+                       tensor::Distribution::make_overlapped_distribution(
+                           tensor::Shape(std::vector<index_t>{1, 1, 1, 1, R}), tensor::IntVector(5, 0)));
+            TensorF xb = create_d_input_tensor(x);
+            if (xs.allocate() || xb.allocate())
+                throw std::runtime_error("allocate");
+            tensor::TensorMPICUDAShuffler<float> shf(x, xs);
+            phase([&] { shf.put(true, x.get_buffer(), st); }, [&] { shf.wait_unpack(true, xs.get_buffer(), st); });
+            phase([&] { shf.put(false, xs.get_buffer(), st); }, [&] { shf.wait_unpack(false, xb.get_buffer(), st); });
+            if (shf.status(true, st) != DCB_OK || shf.status(false, st) != DCB_OK)
+                throw std::runtime_error("shuffle status");
+            e_shf = std::max(gather_err(xs, g->x, C), gather_err(xb, g->x, C));
+        }
+
         std::vector<float> hdw(wcount), hstats(2 * K);
         cudaMemcpy(hdw.data(), dw, wcount * 4, cudaMemcpyDeviceToHost);
         cudaMemcpy(hstats.data(), stats, 2 * K * 4, cudaMemcpyDeviceToHost);
@@ -328,12 +347,12 @@ void rank_main(int rank, int R, Shared* sh, const Global* g)
             e_st = std::max(e_st, (double) std::fabs(hstats[K + k] - g->var[k]) / (1.0 + g->var[k]));
         }
         const double e_y = gather_err(y, g->y, K), e_dx = gather_err(dx, g->dx, C), e_z = gather_err(z, g->z, K);
-        std::printf("rank %d/%d: y %.2e  dx %.2e  dw %.2e  stats %.2e  bn %.2e  pool %.2e / %.2e  (fwd kernel kind %d, "
-                    "statistics %s)\n",
-                    rank, R, e_y, e_dx, e_dw, e_st, e_z, e_py, e_pdx, conv.kernel_kind(0),
+        std::printf("rank %d/%d: y %.2e  dx %.2e  dw %.2e  stats %.2e  bn %.2e  pool %.2e / %.2e  shuffle %.1e  (fwd "
+                    "kernel kind %d, statistics %s)\n",
+                    rank, R, e_y, e_dx, e_dw, e_st, e_z, e_py, e_pdx, e_shf, conv.kernel_kind(0),
                     fused ? "fused" : "separate");
         const bool ok = e_y < 2e-5 && e_dx < 2e-5 && e_dw < 5e-5 && e_st < 2e-5 && e_z < 1e-4 && e_py < 1e-6
-                        && e_pdx < 2e-6;
+                        && e_pdx < 2e-6 && e_shf == 0.0;
         if (!ok)
         {
             std::lock_guard<std::mutex> lk(sh->m);

@@ -1,6 +1,7 @@
 """Worker run by torchrun (one process per GPU): real peer-store halo exchange,
-peer-memory and NCCL all-reduce, and the conv + BN layer across processes,
-each checked against the single-domain oracle.  Launched by
+peer-memory and NCCL all-reduce, the conv + BN layer, pooling with its reverse
+SUM exchange and the tensor re-distribution across processes, each checked
+against the single-domain oracle.  Launched by
 tests/test_gpu_multiproc.py."""
 import os
 import sys
@@ -114,6 +115,47 @@ def main():
     emu.assert_close(dy.owned().cpu().numpy(), own(dy, dy_ref), 5e-5, "bn dx")
     emu.assert_close(dw.cpu().numpy(), dw_ref, 5e-5, "dw")
     emu.assert_close(dx.owned().cpu().numpy(), own(dx, dx_ref), 5e-5, "dx")
+    dist.barrier()
+
+    # ---- pooling across processes: halo exchange forward, reverse SUM backward ----
+    for mode in ("MAX", "AVERAGE_NO_PAD"):
+        pshape, plocale = [20, 12, 6 * n, 3, 2], [1, 1, n, 1, 1]
+        gpx = rng.integers(-4, 5, size=tuple(reversed(pshape))).astype(np.float32)
+        py_ref = O.pool_fwd(gpx, ones3_w := [3, 3, 3], ones3, ones3, mode)
+        gpdy = rng.normal(size=py_ref.shape).astype(np.float32)
+        pdx_ref = O.pool_bwd(gpx, gpdy, ones3_w, ones3, ones3, mode)
+        px = dc.create_input_tensor(pshape, plocale, ones3_w, ones3, ones3, loc)
+        py = dc.create_pooling_output_tensor(px, ones3_w, ones3, ones3)
+        pdx, pdy = dc.create_d_input_tensor(px), dc.create_pooling_d_output_tensor(py)
+        emu.scatter_owned(px, gpx)
+        emu.scatter_owned(pdy, gpdy)
+        py.allocate(), pdx.allocate()
+        pool = dc.Pooling(be, 5)
+        pool.setup(px, py, pdx, pdy, ones3_w, ones3, ones3, mode)
+        pool.forward(1.0, px, 0.0, py)
+        pool.backward(1.0, py, pdy, px, 0.0, pdx)
+        torch.cuda.synchronize()
+        assert pool.halo_xch_input.status() == _abi.OK and pool.halo_xch_d_input.status() == _abi.OK
+        emu.assert_close(py.owned().cpu().numpy(), own(py, py_ref), 1e-6, "pool y " + mode)
+        emu.assert_close(pdx.owned().cpu().numpy(), own(pdx, pdx_ref), 4e-6, "pool dx " + mode)
+        dist.barrier()
+
+    # ---- re-distribution: sample-parallel <-> D-partitioned, there and back ----
+    sshape = [16, 12, 4 * n, 3, 2 * n]
+    gs = rng.normal(size=tuple(reversed(sshape))).astype(np.float32)
+    ts = dc.Tensor(sshape, loc, dc.Distribution.make_overlapped_distribution([1, 1, 1, 1, n], [0] * 5))
+    td = dc.Tensor(sshape, loc, dc.Distribution.make_overlapped_distribution([1, 1, n, 1, 1], [0, 0, 1, 0, 0]))
+    tb = dc.Tensor(sshape, loc, dc.Distribution.make_overlapped_distribution([1, 1, 1, 1, n], [0] * 5))
+    emu.scatter_owned(ts, gs)
+    td.allocate(), tb.allocate()
+    shf = dc.TensorShuffler(ts, td)
+    for rep in range(3):
+        shf.shuffle_forward(ts.get_buffer(), td.get_buffer())
+        shf.shuffle_backward(td.get_buffer(), tb.get_buffer())
+    torch.cuda.synchronize()
+    assert shf.status("fwd") == _abi.OK and shf.status("bwd") == _abi.OK
+    assert np.array_equal(td.owned().cpu().numpy(), own(td, gs))
+    assert np.array_equal(tb.owned().cpu().numpy(), own(tb, gs))
     dist.barrier()
     print(f"mp ok rank {r} of {n}", flush=True)
     dist.destroy_process_group()
