@@ -13,7 +13,8 @@ of a BASELINE configuration (fp32):
 Times, with CUDA events on the launching stream and inputs resident in HBM:
 convolution forward (with and without the BN statistics in its epilogue),
 backward data, backward filter, BN statistics, BN apply, BN backward reduce and
-BN backward apply.  Prints one JSON line with ms per pass and, for each, the
+BN backward apply; and, on the convolution's output, a max-pooling (3^n window,
+stride 2, forward and backward) and a one-rank re-distribution.  Prints one JSON line with ms per pass and, for each, the
 kernel family the plan resolved to.  `--local-d 64` is the small case used for
 profiler captures.
 """
@@ -112,6 +113,26 @@ def main():
     ms["bn_bwd_apply"] = timed(lambda: bn.backward_stage2(y, dz, mean, var, scale, g[2], g[3], dy))
     ms["conv_bwd_filter"] = timed(lambda: conv.backward_filter(1.0, x, dy, 0.0, dw, reduce=False))
     ms["conv_bwd_data"] = timed(lambda: conv.backward_data(1.0, w, dy, 0.0, dx, skip_halo_exchange=True))
+    # pooling of the conv output (3^n window, stride 2, pad 1, MAX) and a local
+    # re-distribution of it (one rank: the shuffle's put and wait_unpack kernels)
+    win, pp, ps = [3] * nsd, [1] * nsd, [2] * nsd
+    px = dc.create_input_tensor(list(y.shape), [1] * (nsd + 2), win, ps, [1] * nsd, locale)
+    py = dc.create_pooling_output_tensor(px, win, ps, pp)
+    pdx, pdy = dc.create_d_input_tensor(px), dc.create_pooling_d_output_tensor(py)
+    px.set_view(y.buffer)
+    for t in (py, pdx, pdy):
+        t.allocate()
+    pdy.buffer.normal_()
+    pool = dc.Pooling(be, nsd + 2)
+    pool.setup(px, py, pdx, pdy, win, pp, ps, "MAX")
+    ms["pool_max_fwd"] = timed(lambda: pool.forward(1.0, px, 0.0, py, skip_halo_exchange=True))
+    ms["pool_max_bwd"] = timed(lambda: pool.backward(1.0, py, pdy, px, 0.0, pdx, skip_halo_exchange=True))
+    shf = dc.TensorShuffler(px, pdx)
+    ms["shuffle_local"] = timed(lambda: shf.shuffle_forward(px.get_buffer(), pdx.get_buffer()))
+    ybytes = 4.0 * y.buffer.numel()
+    gbs = {"pool_max_fwd": (ybytes + 4.0 * py.buffer.numel()) / (ms["pool_max_fwd"] * 1e-3) / 1e9,
+           "pool_max_bwd": (2 * ybytes + 8.0 * py.buffer.numel()) / (ms["pool_max_bwd"] * 1e-3) / 1e9,
+           "shuffle_local": 4 * ybytes / (ms["shuffle_local"] * 1e-3) / 1e9}
     vox = N * int(np.prod(sp))
     out_vox = N * int(np.prod([(e + 2 * pad - fe) // stride + 1 for e, fe in zip(sp, f)]))
     flop = 2.0 * out_vox * K_OUT * C_IN * int(np.prod(f))
@@ -124,6 +145,7 @@ def main():
                       "ms": {k: round(v, 4) for k, v in ms.items()}, "kernels": kinds,
                       "conv_tflops": {k: round(flop / (ms[k] * 1e-3) / 1e12, 2)
                                       for k in ("conv_fwd", "conv_bwd_data", "conv_bwd_filter")},
+                      "algorithmic_gb_per_s": {k: round(v, 1) for k, v in gbs.items()},
                       "forward_ms": round(fwd, 4), "backward_ms": round(bwd, 4),
                       "forward_backward_voxels_per_s": vox / ((fwd + bwd) * 1e-3),
                       "status": [conv.halo_xch_input.status(), int(_abi.lib().dcb_conv_plan_status(conv._plan_fwd, None)),

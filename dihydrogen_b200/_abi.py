@@ -136,7 +136,8 @@ _SIGS = {
     "dcb_leaky_relu_bwd": (c_int32, [POINTER(NdDesc), _P, POINTER(NdDesc), _P, c_float, POINTER(NdDesc), _P, _P]),
     "dcb_pool_fwd": (c_int32, [POINTER(PoolDesc), POINTER(NdDesc), POINTER(NdDesc), c_double, _P, c_double, _P, _P]),
     "dcb_pool_bwd": (c_int32, [POINTER(PoolDesc), POINTER(NdDesc), POINTER(NdDesc), c_double, _P, _P, _P, c_double,
-                               _P, _P]),
+                               _P, _P, c_int64, _P]),
+    "dcb_pool_bwd_workspace_bytes": (c_int64, [POINTER(PoolDesc), POINTER(NdDesc), POINTER(NdDesc)]),
     "dcb_shuffle_plan_create": (c_int32, [POINTER(TensorDesc), POINTER(TensorDesc), POINTER(Box), POINTER(Box),
                                           c_int32, c_int32, POINTER(_P)]),
     "dcb_shuffle_plan_destroy": (c_int32, [_P]),

@@ -65,8 +65,14 @@ __device__ __forceinline__ float pool_count(const PoolGeom& g, int od, int oh, i
     return (float) cnt;
 }
 
+// Forward: one thread per output cell, the window scanned in D, H, W order.
+// `argmax`, if given, receives the tap index kd * fh * fw + kh * fw + kw of the
+// first maximum (dense [n][c][od][oh][ow]); y may then be null.
+constexpr int POOL_TW = POOL_THREADS;
+
 __global__ void __launch_bounds__(POOL_THREADS)
-    pool_fwd_kernel(PoolGeom g, float alpha, float beta, const float* __restrict__ x, float* y)
+    pool_fwd_kernel(PoolGeom g, float alpha, float beta, const float* __restrict__ x, float* y,
+                    unsigned char* __restrict__ argmax)
 {
     const int ow = blockIdx.y * POOL_THREADS + threadIdx.x;
     if (ow >= g.out[2])
@@ -74,28 +80,39 @@ __global__ void __launch_bounds__(POOL_THREADS)
     const int oh = blockIdx.x % g.out[1], od = blockIdx.x / g.out[1];
     const int c = blockIdx.z % g.c, n = blockIdx.z / g.c;
     const float* xp = x + (size_t) n * g.xs_n + (size_t) c * g.xs_c;
+    const int d0 = od * g.stride[0] - g.pad[0], h0 = oh * g.stride[1] - g.pad[1], w0 = ow * g.stride[2] - g.pad[2];
+    const int kw_lo = max(0, g.lo[2] - w0), kw_hi = min(g.win[2], g.hi[2] - w0);
     float m = -FLT_MAX, s = 0.f;
+    int best = -1;
     for (int kd = 0; kd < g.win[0]; ++kd)
     {
-        const int id = od * g.stride[0] - g.pad[0] + kd;
+        const int id = d0 + kd;
         if (id < g.lo[0] || id >= g.hi[0])
             continue;
         for (int kh = 0; kh < g.win[1]; ++kh)
         {
-            const int ih = oh * g.stride[1] - g.pad[1] + kh;
+            const int ih = h0 + kh;
             if (ih < g.lo[1] || ih >= g.hi[1])
                 continue;
-            const float* row = xp + (size_t) id * g.xs[0] + (size_t) ih * g.xs[1];
-            for (int kw = 0; kw < g.win[2]; ++kw)
+            const float* row = xp + (size_t) id * g.xs[0] + (size_t) ih * g.xs[1] + w0;
+            const int tap0 = (kd * g.win[1] + kh) * g.win[2];
+            for (int kw = kw_lo; kw < kw_hi; ++kw)
             {
-                const int iw = ow * g.stride[2] - g.pad[2] + kw;
-                if (iw < g.lo[2] || iw >= g.hi[2])
-                    continue;
-                const float v = __ldg(row + iw);
-                m = fmaxf(m, v);
+                const float v = __ldg(row + kw);
                 s += v;
+                if (best < 0 || v > m)
+                {
+                    m = v;
+                    best = tap0 + kw;
+                }
             }
         }
+    }
+    if (argmax)
+    {
+        argmax[((((size_t) n * g.c + c) * g.out[0] + od) * g.out[1] + oh) * g.out[2] + ow] = (unsigned char) best;
+        if (!y)
+            return;
     }
     const float r = g.mode == DCB_POOL_MAX ? m : s / fmaxf(pool_count(g, od, oh, ow), 1.f);
     float* yp = y + (size_t) n * g.ys_n + (size_t) c * g.ys_c + (size_t) od * g.ys[0] + (size_t) oh * g.ys[1] + ow;
@@ -106,16 +123,30 @@ __global__ void __launch_bounds__(POOL_THREADS)
 __device__ __forceinline__ void pool_cover(int i, int stride, int pad, int win, int nout, int* lo, int* hi)
 {
     const int t = i + pad;
-    int l = t - win + 1;
-    l = l <= 0 ? 0 : (l + stride - 1) / stride;
-    int h = t / stride;
-    *lo = l;
-    *hi = min(h, nout - 1);
+    const int l = t - win + 1;
+    int lq, hq; // ceil(l / stride) for l > 0, floor(t / stride); strides 1 and 2 without a division
+    if (stride == 1)
+    {
+        lq = l;
+        hq = t;
+    }
+    else if (stride == 2)
+    {
+        lq = (l + 1) >> 1;
+        hq = t >> 1;
+    }
+    else
+    {
+        lq = (l + stride - 1) / stride;
+        hq = t / stride;
+    }
+    *lo = l <= 0 ? 0 : lq;
+    *hi = min(hq, nout - 1);
 }
 
 __global__ void __launch_bounds__(POOL_THREADS)
     pool_bwd_kernel(PoolGeom g, float alpha, float beta, const float* __restrict__ y, const float* __restrict__ dy,
-                    const float* __restrict__ x, float* dx)
+                    const float* __restrict__ x, float* dx, const unsigned char* __restrict__ argmax)
 {
     const int iw = blockIdx.y * POOL_THREADS + threadIdx.x;
     if (iw >= g.in[2])
@@ -129,12 +160,29 @@ __global__ void __launch_bounds__(POOL_THREADS)
     pool_cover(id, g.stride[0], g.pad[0], g.win[0], g.out[0], &dlo, &dhi);
     pool_cover(ih, g.stride[1], g.pad[1], g.win[1], g.out[1], &hlo, &hhi);
     pool_cover(iw, g.stride[2], g.pad[2], g.win[2], g.out[2], &wlo, &whi);
-    const float xv = g.mode == DCB_POOL_MAX ? __ldg(x + me) : 0.f;
+    const float xv = g.mode == DCB_POOL_MAX && !argmax ? __ldg(x + me) : 0.f;
     float acc = 0.f;
     // a cell outside the global tensor is padding: no window gives it anything
     const bool real = id >= g.lo[0] && id < g.hi[0] && ih >= g.lo[1] && ih < g.hi[1] && iw >= g.lo[2] && iw < g.hi[2];
     if (!real)
         dhi = dlo - 1;
+    if (argmax)
+    {
+        // the index pass recorded every window's first maximum: one byte to compare
+        const size_t plane = ((size_t) n * g.c + c) * g.out[0];
+        for (int od = dlo; od <= dhi; ++od)
+            for (int oh = hlo; oh <= hhi; ++oh)
+            {
+                const size_t drow = ((plane + od) * g.out[1] + oh) * g.out[2];
+                const float* dyrow = dy + yoff + (size_t) od * g.ys[0] + (size_t) oh * g.ys[1];
+                const int tap0 = ((id - (od * g.stride[0] - g.pad[0])) * g.win[1] + (ih - (oh * g.stride[1] - g.pad[1])))
+                                 * g.win[2];
+                for (int ow = wlo; ow <= whi; ++ow)
+                    if ((int) __ldg(argmax + drow + ow) == tap0 + iw - (ow * g.stride[2] - g.pad[2]))
+                        acc += __ldg(dyrow + ow);
+            }
+        dlo = dhi + 1;
+    }
     for (int od = dlo; od <= dhi; ++od)
         for (int oh = hlo; oh <= hhi; ++oh)
             for (int ow = wlo; ow <= whi; ++ow)
@@ -227,6 +275,22 @@ bool pool_grid(int w, long long rows, long long planes, dim3* grid)
     return true;
 }
 
+int32_t launch_pool_fwd(const PoolGeom& g, float alpha, float beta, const float* x, float* y, unsigned char* argmax,
+                        cudaStream_t stream)
+{
+    const long long tiles = (g.out[2] + POOL_TW - 1) / POOL_TW;
+    const long long rows = (long long) g.out[0] * g.out[1], planes = (long long) g.n * g.c;
+    if (rows > 0x7fffffffll || tiles > 65535 || planes > 65535)
+    {
+        set_last_error("tensor too large for the pooling grid");
+        return DCB_UNSUPPORTED;
+    }
+    pool_fwd_kernel<<<dim3((unsigned) rows, (unsigned) tiles, (unsigned) planes), POOL_THREADS, 0, stream>>>(
+        g, alpha, beta, x, y, argmax);
+    DCB_LAUNCH_CHECK();
+    return DCB_OK;
+}
+
 } // namespace
 } // namespace dcb
 
@@ -242,21 +306,23 @@ extern "C" int32_t dcb_pool_fwd(const dcb_pool_desc* pd, const dcb_nd_desc* xd, 
     if ((long long) g.n * g.c * g.out[0] * g.out[1] * g.out[2] == 0)
         return DCB_OK;
     DCB_REQUIRE(x && y, "null argument");
-    dim3 grid;
-    if (!pool_grid(g.out[2], (long long) g.out[0] * g.out[1], (long long) g.n * g.c, &grid))
-    {
-        set_last_error("tensor too large for the pooling grid");
-        return DCB_UNSUPPORTED;
-    }
-    pool_fwd_kernel<<<grid, POOL_THREADS, 0, as_stream(stream)>>>(g, (float) alpha, (float) beta,
-                                                                  static_cast<const float*>(x),
-                                                                  static_cast<float*>(y));
-    DCB_LAUNCH_CHECK();
-    return DCB_OK;
+    return launch_pool_fwd(g, (float) alpha, (float) beta, static_cast<const float*>(x), static_cast<float*>(y),
+                           nullptr, as_stream(stream));
+}
+
+extern "C" int64_t dcb_pool_bwd_workspace_bytes(const dcb_pool_desc* pd, const dcb_nd_desc* xd, const dcb_nd_desc* yd)
+{
+    PoolGeom g;
+    if (pool_geom(pd, xd, yd, &g) != DCB_OK)
+        return -1;
+    if (g.mode != DCB_POOL_MAX || g.win[0] * g.win[1] * g.win[2] > 255)
+        return 0;
+    return (int64_t) g.n * g.c * g.out[0] * g.out[1] * g.out[2];
 }
 
 extern "C" int32_t dcb_pool_bwd(const dcb_pool_desc* pd, const dcb_nd_desc* xd, const dcb_nd_desc* yd, double alpha,
-                                const void* y, const void* dy, const void* x, double beta, void* dx, void* stream)
+                                const void* y, const void* dy, const void* x, double beta, void* dx, void* workspace,
+                                int64_t workspace_bytes, void* stream)
 {
     PoolGeom g;
     const int32_t st = pool_geom(pd, xd, yd, &g);
@@ -271,9 +337,25 @@ extern "C" int32_t dcb_pool_bwd(const dcb_pool_desc* pd, const dcb_nd_desc* xd, 
         set_last_error("tensor too large for the pooling grid");
         return DCB_UNSUPPORTED;
     }
+    // With a workspace the position of every window's first maximum is worked out
+    // first, by the forward kernel's separable pass (from x alone: nothing is kept
+    // between calls), and the gather compares one byte per window instead of
+    // scanning the window's earlier cells.
+    const unsigned char* idx = nullptr;
+    const int64_t need = dcb_pool_bwd_workspace_bytes(pd, xd, yd);
+    if (g.mode == DCB_POOL_MAX && workspace && need > 0 && workspace_bytes >= need
+        && (long long) g.n * g.c * g.out[0] * g.out[1] * g.out[2] > 0)
+    {
+        const int32_t st2 =
+            launch_pool_fwd(g, 1.f, 0.f, static_cast<const float*>(x), nullptr, static_cast<unsigned char*>(workspace),
+                            as_stream(stream));
+        if (st2 != DCB_OK)
+            return st2;
+        idx = static_cast<const unsigned char*>(workspace);
+    }
     pool_bwd_kernel<<<grid, POOL_THREADS, 0, as_stream(stream)>>>(
         g, (float) alpha, (float) beta, static_cast<const float*>(y), static_cast<const float*>(dy),
-        static_cast<const float*>(x), static_cast<float*>(dx));
+        static_cast<const float*>(x), static_cast<float*>(dx), idx);
     DCB_LAUNCH_CHECK();
     return DCB_OK;
 }

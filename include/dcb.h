@@ -337,7 +337,17 @@ int32_t dcb_pool_fwd(const dcb_pool_desc* pd, const dcb_nd_desc* xd,
 int32_t dcb_pool_bwd(const dcb_pool_desc* pd, const dcb_nd_desc* xd,
                      const dcb_nd_desc* yd, double alpha, const void* y,
                      const void* dy, const void* x, double beta, void* dx,
-                     void* stream);
+                     void* workspace, int64_t workspace_bytes, void* stream);
+/* Device bytes dcb_pool_bwd can use for MAX (one byte per output cell; 0 for
+ * the averages, -1 for a bad descriptor).  With that workspace the backward
+ * pass first records every window's first maximum from x (nothing is kept
+ * between calls) and the gather compares one byte per window; without it
+ * (null / too small) it scans each window's earlier cells instead, an order of
+ * magnitude slower.  The reference borrows cuDNN workspaces from a caching
+ * pool per call (convolution.hpp:394-398); here the caller owns it. */
+int64_t dcb_pool_bwd_workspace_bytes(const dcb_pool_desc* pd,
+                                     const dcb_nd_desc* xd,
+                                     const dcb_nd_desc* yd);
 
 /* ------------------------------------------------------------------------
  * Re-distribution between two block decompositions of one global tensor.

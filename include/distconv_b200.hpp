@@ -1352,9 +1352,19 @@ public:
         }
         m_halo_xch_input.reset(new tensor::HaloExchange(input));
         m_halo_xch_d_input.reset(new tensor::HaloExchange(d_input));
-        (void) output;
         (void) d_output;
+        // index workspace of the backward pass: one byte per output cell, MAX only
+        release_workspace();
+        if (output.get_local_size() > 0)
+        {
+            const dcb_nd_desc xd = input.nd_desc(m_halo_bwd_recv, m_halo_fwd_recv), yd = output.nd_desc();
+            const int64_t need = dcb_pool_bwd_workspace_bytes(&m_pd, &xd, &yd);
+            if (need > 0 && cudaMalloc(&m_ws, (size_t) need) == cudaSuccess)
+                m_ws_bytes = need;
+        }
     }
+    Pooling(const Pooling&) = delete;
+    ~Pooling() { release_workspace(); }
 
     // pooling.hpp:212-244
     int forward(float alpha, TensorF& input, float beta, TensorF& output, bool /*training*/ = true,
@@ -1386,8 +1396,8 @@ public:
         {
             const dcb_nd_desc xd = input.nd_desc(m_halo_bwd_recv, m_halo_fwd_recv), yd = output.nd_desc();
             util::check(dcb_pool_bwd(&m_pd, &xd, &yd, alpha, output.get_base_ptr(), d_output.get_base_ptr(),
-                                     input.nd_ptr(m_halo_bwd_recv), beta, d_input.nd_ptr(m_halo_bwd_recv),
-                                     m_be.get_stream()),
+                                     input.nd_ptr(m_halo_bwd_recv), beta, d_input.nd_ptr(m_halo_bwd_recv), m_ws,
+                                     m_ws_bytes, m_be.get_stream()),
                         "pooling backward");
         }
         if (!skip_halo_exchange)
@@ -1409,7 +1419,16 @@ private:
     }
     BackendDNNLib& m_be;
     int m_num_dims, m_nsd;
+    void release_workspace()
+    {
+        if (m_ws)
+            cudaFree(m_ws);
+        m_ws = nullptr;
+        m_ws_bytes = 0;
+    }
     dcb_pool_desc m_pd;
+    void* m_ws = nullptr;
+    int64_t m_ws_bytes = 0;
     tensor::IntVector m_halo_fwd_send, m_halo_bwd_send, m_halo_fwd_recv, m_halo_bwd_recv;
     std::unique_ptr<tensor::HaloExchange> m_halo_xch_input, m_halo_xch_d_input;
 };

@@ -58,15 +58,25 @@ def test_kernels_against_oracle(case, mode):
     P = lambda t: ctypes.c_void_p(t.data_ptr())
     _abi.call("dcb_pool_fwd", ctypes.byref(pd), ctypes.byref(xd), ctypes.byref(yd), 1.0, P(xs), 0.0, P(y), None)
     _abi.call("dcb_pool_bwd", ctypes.byref(pd), ctypes.byref(xd), ctypes.byref(yd), 1.0, P(y), P(dys), P(xs), 0.0,
-              P(dx), None)
+              P(dx), None, 0, None)
     torch.cuda.synchronize()
     emu.assert_close(y.cpu().numpy(), y_ref, 1e-6, "y")
     emu.assert_close(dx.cpu().numpy(), dx_ref, 2e-6, "dx")
+    # with the index workspace: the same gradient, bit for bit
+    need = _abi.lib().dcb_pool_bwd_workspace_bytes(ctypes.byref(pd), ctypes.byref(xd), ctypes.byref(yd))
+    assert need == (y.numel() if mode == "MAX" else 0)
+    if need:
+        ws = torch.empty(need, dtype=torch.uint8, device="cuda")
+        dx2 = torch.full_like(xs, 9.0)
+        _abi.call("dcb_pool_bwd", ctypes.byref(pd), ctypes.byref(xd), ctypes.byref(yd), 1.0, P(y), P(dys), P(xs), 0.0,
+                  P(dx2), P(ws), need, None)
+        torch.cuda.synchronize()
+        assert torch.equal(dx2, dx)
     # alpha / beta
     yb, dxb = torch.from_numpy(y0).cuda(), torch.from_numpy(dx0).cuda()
     _abi.call("dcb_pool_fwd", ctypes.byref(pd), ctypes.byref(xd), ctypes.byref(yd), 0.5, P(xs), 2.0, P(yb), None)
     _abi.call("dcb_pool_bwd", ctypes.byref(pd), ctypes.byref(xd), ctypes.byref(yd), 0.5, P(y), P(dys), P(xs), -1.0,
-              P(dxb), None)
+              P(dxb), None, 0, None)
     torch.cuda.synchronize()
     emu.assert_close(yb.cpu().numpy(), 0.5 * y_ref + 2.0 * y0, 2e-6, "y blend")
     emu.assert_close(dxb.cpu().numpy(), 0.5 * dx_ref - dx0, 4e-6, "dx blend")

@@ -70,7 +70,7 @@ def test_distribution_fixup_overlap():
 def test_abi_library_exports_every_declared_symbol():
     lib = _abi.lib()
     hdr = open(os.path.join(ROOT, "include", "dcb.h")).read()
-    declared = set(re.findall(r"^(?:int32_t|const char\*)\s+(dcb_[a-z0-9_]+)\s*\(", hdr, re.M))
+    declared = set(re.findall(r"^(?:int32_t|int64_t|const char\*)\s+(dcb_[a-z0-9_]+)\s*\(", hdr, re.M))
     assert declared, "no declarations found"
     for name in sorted(declared):
         assert hasattr(lib, name), f"{name} is declared in dcb.h but not exported"
