@@ -206,12 +206,28 @@ int32_t flip_transpose_filter(const float* w, float* w2, int k, int c,
 // ---------------------------------------------------------------------------
 constexpr int BWD_THREADS = 128;
 
+// acc[0..CT) += v * w[0..CT): the weights of one (filter, tap) sit in CT
+// consecutive, 16-byte aligned floats of shared memory; read them as vectors.
+template <int CT>
+__device__ __forceinline__ void fma_tile(float (&acc)[CT], float v, const float* __restrict__ w)
+{
+#pragma unroll
+    for (int q = 0; q < CT / 4; ++q)
+    {
+        const float4 w4 = *reinterpret_cast<const float4*>(w + 4 * q);
+        acc[4 * q + 0] = fmaf(v, w4.x, acc[4 * q + 0]);
+        acc[4 * q + 1] = fmaf(v, w4.y, acc[4 * q + 1]);
+        acc[4 * q + 2] = fmaf(v, w4.z, acc[4 * q + 2]);
+        acc[4 * q + 3] = fmaf(v, w4.w, acc[4 * q + 3]);
+    }
+}
+
 template <int CT>
 __global__ void __launch_bounds__(BWD_THREADS)
     conv_bwd_data_kernel(ConvGeom g, float alpha, float beta,
                          const float* __restrict__ w,
                          const float* __restrict__ dy, float* dx, int ktile,
-                         int ctiles)
+                         int ctiles, int rows, int htiles)
 {
     extern __shared__ __align__(16) float ws[]; // [ktile][taps][CT]
     const int taps = g.f[0] * g.f[1] * g.f[2];
@@ -222,14 +238,22 @@ __global__ void __launch_bounds__(BWD_THREADS)
                        ? blockIdx.y * BWD_THREADS + (threadIdx.x >> 6) * 64 + 2 * (threadIdx.x & 31)
                              + ((threadIdx.x >> 5) & 1)
                        : blockIdx.y * BWD_THREADS + threadIdx.x;
-    const int ih = blockIdx.x % g.in[1];
-    const int id = blockIdx.x / g.in[1];
+    // A block stages the filter once and walks `rows` input rows with it (staging
+    // costs more than one row's arithmetic); rows > 1 only when the whole filter
+    // fits (one k0 pass), so that a row's sums never have to outlive a pass.
+    const int ih0 = (blockIdx.x % htiles) * rows;
+    const int id = blockIdx.x / htiles;
     const int ct = blockIdx.z % ctiles;
     const int n = blockIdx.z / ctiles;
+    // Only the taps whose output coordinate is whole: with dilation 1 those are
+    // k = (i + pad) mod stride, then every stride-th (one modulo per dimension
+    // and cell instead of one per tap); a dilated filter walks all taps.
+    const bool d1 = g.dil[0] == 1 && g.dil[1] == 1 && g.dil[2] == 1;
+    const int sd = d1 ? g.stride[0] : 1, sh = d1 ? g.stride[1] : 1, sw = d1 ? g.stride[2] : 1;
+    const int kd0 = d1 ? (id + g.pad[0]) % g.stride[0] : 0;
+    const int kw0 = d1 ? (iw + g.pad[2]) % g.stride[2] : 0;
+    const size_t wstep = (size_t) taps * CT;
     float acc[CT];
-#pragma unroll
-    for (int i = 0; i < CT; ++i)
-        acc[i] = 0.f;
     for (int k0 = 0; k0 < g.k; k0 += ktile)
     {
         __syncthreads();
@@ -248,77 +272,88 @@ __global__ void __launch_bounds__(BWD_THREADS)
         if (iw >= g.in[2])
             continue;
         const int kend = min(ktile, g.k - k0);
-        for (int kd = 0; kd < g.f[0]; ++kd)
+        const float* dyn = dy + (size_t) n * g.ys_n + (size_t) k0 * g.ys_c;
+        for (int r = 0; r < rows; ++r)
         {
-            const int td = id + g.pad[0] - kd * g.dil[0];
-            if (td < 0 || td % g.stride[0])
-                continue;
-            const int od = td / g.stride[0];
-            if (od >= g.out[0])
-                continue;
-            for (int kh = 0; kh < g.f[1]; ++kh)
+            const int ih = ih0 + r;
+            if (ih >= g.in[1])
+                break;
+            if (k0 == 0)
             {
-                const int th = ih + g.pad[1] - kh * g.dil[1];
-                if (th < 0 || th % g.stride[1])
+#pragma unroll
+                for (int i = 0; i < CT; ++i)
+                    acc[i] = 0.f;
+            }
+            const int kh0 = d1 ? (ih + g.pad[1]) % g.stride[1] : 0;
+            for (int kd = kd0; kd < g.f[0]; kd += sd)
+            {
+                const int td = id + g.pad[0] - kd * g.dil[0];
+                if (td < 0 || td % g.stride[0])
                     continue;
-                const int oh = th / g.stride[1];
-                if (oh >= g.out[1])
+                const int od = td / g.stride[0];
+                if (od >= g.out[0])
                     continue;
-                for (int kw = 0; kw < g.f[2]; ++kw)
+                for (int kh = kh0; kh < g.f[1]; kh += sh)
                 {
-                    const int tw = iw + g.pad[2] - kw * g.dil[2];
-                    if (tw < 0 || tw % g.stride[2])
+                    const int th = ih + g.pad[1] - kh * g.dil[1];
+                    if (th < 0 || th % g.stride[1])
                         continue;
-                    const int ow = tw / g.stride[2];
-                    if (ow >= g.out[2])
+                    const int oh = th / g.stride[1];
+                    if (oh >= g.out[1])
                         continue;
-                    const int tap = (kd * g.f[1] + kh) * g.f[2] + kw;
-                    const float* dyp = dy + (size_t) n * g.ys_n
-                                       + (size_t) k0 * g.ys_c
-                                       + (size_t) od * g.ys[0]
-                                       + (size_t) oh * g.ys[1] + ow;
-                    // four loads in flight per thread: one at a time left the loop
-                    // waiting on each dy cell
-                    int kk = 0;
-                    for (; kk + 4 <= kend; kk += 4)
+                    const float* dyrow = dyn + (size_t) od * g.ys[0] + (size_t) oh * g.ys[1];
+                    for (int kw = kw0; kw < g.f[2]; kw += sw)
                     {
-                        float v[4];
-#pragma unroll
-                        for (int u = 0; u < 4; ++u)
-                            v[u] = __ldg(dyp + (size_t) (kk + u) * g.ys_c);
-#pragma unroll
-                        for (int u = 0; u < 4; ++u)
+                        const int tw = iw + g.pad[2] - kw * g.dil[2];
+                        if (tw < 0 || tw % g.stride[2])
+                            continue;
+                        const int ow = tw / g.stride[2];
+                        if (ow >= g.out[2])
+                            continue;
+                        const float* dyp = dyrow + ow;
+                        const float* wp = ws + (size_t) ((kd * g.f[1] + kh) * g.f[2] + kw) * CT;
+                        // four loads in flight per thread: one at a time left the
+                        // loop waiting on each dy cell
+                        int kk = 0;
+                        for (; kk + 4 <= kend; kk += 4)
                         {
-                            const float* wp = ws + ((size_t) (kk + u) * taps + tap) * CT;
+                            float v[4];
 #pragma unroll
-                            for (int cc = 0; cc < CT; ++cc)
-                                acc[cc] = fmaf(v[u], wp[cc], acc[cc]);
+                            for (int u = 0; u < 4; ++u)
+                            {
+                                v[u] = __ldg(dyp);
+                                dyp += g.ys_c;
+                            }
+#pragma unroll
+                            for (int u = 0; u < 4; ++u)
+                            {
+                                fma_tile<CT>(acc, v[u], wp);
+                                wp += wstep;
+                            }
                         }
-                    }
-                    for (; kk < kend; ++kk)
-                    {
-                        const float v = __ldg(dyp + (size_t) kk * g.ys_c);
-                        const float* wp = ws + ((size_t) kk * taps + tap) * CT;
-#pragma unroll
-                        for (int cc = 0; cc < CT; ++cc)
-                            acc[cc] = fmaf(v, wp[cc], acc[cc]);
+                        for (; kk < kend; ++kk)
+                        {
+                            fma_tile<CT>(acc, __ldg(dyp), wp);
+                            dyp += g.ys_c;
+                            wp += wstep;
+                        }
                     }
                 }
             }
-        }
-    }
-    if (iw >= g.in[2])
-        return;
+            if (k0 + ktile < g.k)
+                continue; // rows == 1 here: the sums go on in the next pass
 #pragma unroll
-    for (int cc = 0; cc < CT; ++cc)
-    {
-        const int c = ct * CT + cc;
-        if (c >= g.c)
-            continue;
-        float* xp = dx + (size_t) n * g.xs_n + (size_t) c * g.xs_c
-                    + (size_t) id * g.xs[0] + (size_t) ih * g.xs[1] + iw;
-        const float prev = beta != 0.f ? *xp : 0.f;
-        *xp = alpha * acc[cc] + beta * prev;
+            for (int cc = 0; cc < CT; ++cc)
+            {
+                const int c = ct * CT + cc;
+                if (c >= g.c)
+                    continue;
+                float* xp = dx + (size_t) n * g.xs_n + (size_t) c * g.xs_c
+                            + (size_t) id * g.xs[0] + (size_t) ih * g.xs[1] + iw;
+                const float prev = beta != 0.f ? *xp : 0.f;
+                *xp = alpha * acc[cc] + beta * prev;
+            }
+        }
     }
 }
 
@@ -328,19 +363,22 @@ static int32_t launch_bwd_data(const ConvGeom& g, float alpha, const float* w,
                                cudaStream_t stream)
 {
     const int taps = g.f[0] * g.f[1] * g.f[2];
-    int ktile = (32 * 1024) / (taps * CT * (int) sizeof(float));
+    // the whole filter in shared memory where it fits (up to 96 KiB, two blocks
+    // per SM): then a block reuses it for several rows
+    const size_t per_k = (size_t) taps * CT * sizeof(float);
+    int ktile = g.k;
+    if (per_k * ktile > 96 * 1024)
+        ktile = (int) ((32 * 1024) / per_k);
     if (ktile < 1)
-        ktile = 1;
-    if (ktile > g.k)
-        ktile = g.k;
-    const size_t smem = (size_t) ktile * taps * CT * sizeof(float);
-    if (smem > 48 * 1024)
     {
         set_last_error("filter too large for the fp32 backward-data kernel");
         return DCB_UNSUPPORTED;
     }
+    const size_t smem = per_k * ktile;
+    const int rows = ktile >= g.k ? 8 : 1;
+    const int htiles = (g.in[1] + rows - 1) / rows;
     const int ctiles = (g.c + CT - 1) / CT;
-    const long long gy = (long long) g.in[0] * g.in[1];
+    const long long gy = (long long) g.in[0] * htiles;
     const long long gz = (long long) g.n * ctiles;
     const long long gw = (g.in[2] + BWD_THREADS - 1) / BWD_THREADS;
     if (gy > 0x7fffffffll || gw > 65535 || gz > 65535)
@@ -348,9 +386,12 @@ static int32_t launch_bwd_data(const ConvGeom& g, float alpha, const float* w,
         set_last_error("tensor too large for the fp32 backward-data grid");
         return DCB_UNSUPPORTED;
     }
+    if (smem > 48 * 1024)
+        DCB_CUDA_TRY(cudaFuncSetAttribute(conv_bwd_data_kernel<CT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          (int) (96 * 1024)));
     dim3 grid((unsigned) gy, (unsigned) gw, (unsigned) gz);
     conv_bwd_data_kernel<CT><<<grid, BWD_THREADS, smem, stream>>>(
-        g, alpha, beta, w, dy, dx, ktile, ctiles);
+        g, alpha, beta, w, dy, dx, ktile, ctiles, rows, htiles);
     DCB_LAUNCH_CHECK();
     return DCB_OK;
 }
