@@ -244,7 +244,8 @@ def run_ours(args):
     w = torch.from_numpy(synth_filter(0)).cuda()
     x.owned().copy_(host_x)
 
-    be = dc.BackendDNNLib(locale, options=dc.Options(), allreduce="peer", allreduce_max_count=4096)
+    be = dc.BackendDNNLib(locale, options=dc.Options(overlap_halo_exchange=args.overlap), allreduce="peer",
+                          allreduce_max_count=4096)
     conv = dc.Convolution(be, 5)
     conv.setup(x, w, y, None, None, None, geo["pads"], geo["strides"], geo["dilations"])
     bn = dc.BatchNormalization(be, 5, DECAY, EPS, True)
@@ -258,6 +259,8 @@ def run_ours(args):
     partitioned = world > 1
 
     fuse = not args.no_fused_stats
+    overlapped = conv.is_overlap_fwd_halo_exchange_enabled()
+    extra_launches = 2 * (len(conv._ov[1]) - 1) if overlapped else 0
 
     def step():
         # the conv epilogue also delivers the BN statistics of its output
@@ -267,7 +270,9 @@ def run_ours(args):
         # clear_halo (1 per partitioned dim), pack+put and wait+unpack (1 each per
         # partitioned dim), filter image, conv, statistics (fold of the epilogue's
         # partials, or the separate pass), all-reduce, finalize, apply
-        launches["n"] += (3 if partitioned else 0) + 6
+        # (--overlap: interior + boundary slabs, each with its filter image, and
+        # the statistics as their own pass)
+        launches["n"] += (3 if partitioned else 0) + 6 + extra_launches
         return got
 
     def e2e_step():
@@ -434,6 +439,7 @@ def run_ours(args):
                                "halo exchange + conv fwd + BN fwd (global stats)"
                                + ("" if args.local_d is None else f" [REDUCED local D={args.local_d}: profiling only]"),
                    "partition": f"D over {world} GPU(s), halo width 1", "global_volume": geo["shape"][:3],
+                   "overlap_halo_exchange": bool(overlapped),
                    "l2": "inputs larger than L2 (268 MB in, 1 GiB conv out per GPU)",
                    "allreduce": "peer-memory kernel, 2C floats"},
         "e2e": {"value": vox_total / (ms_e2e * 1e-3), "unit": "voxels/s", "ms_per_step": ms_e2e,
@@ -461,6 +467,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-fused-stats", action="store_true",
                     help="run the BN statistics as their own pass instead of taking them from the conv epilogue")
+    ap.add_argument("--overlap", action="store_true",
+                    help="Options.overlap_halo_exchange: interior convolution while the halo is in flight, then "
+                         "the boundary slabs (off by default, as in the reference)")
     ap.add_argument("--local-d", type=int, default=None,
                     help="per-GPU D extent instead of 256 (small case for profiler captures; not a bench value)")
     ap.add_argument("--skip-cpu", action="store_true", help="skip the CPU baseline leg (profiler captures)")

@@ -849,7 +849,8 @@ class Convolution:
 
     def __del__(self):
         try:
-            for p in (getattr(self, "_plan_fwd", None), getattr(self, "_plan_bwd", None)):
+            for p in [getattr(self, "_plan_fwd", None), getattr(self, "_plan_bwd", None)] + list(
+                    getattr(self, "_ov_plans", [])):
                 if p:
                     _abi.lib().dcb_conv_plan_destroy(p)
         except Exception:
@@ -911,11 +912,78 @@ class Convolution:
         xd = input.nd_desc(lo, hi)
         yd = output.nd_desc()
         self._plan_fwd = self._make_plan(xd, yd, pads_fp)
+        self._setup_overlap(input, xd, yd, pads_fp, lo, hi)
         if d_output is not None:
             dyd = d_output.full_nd_desc()
             dxd = (d_input or input).nd_desc(lo, hi)
             self._plan_bwd = self._make_plan(dxd, dyd, pads_bp)
         self._ready = True
+
+    def _setup_overlap(self, input: Tensor, xd: NdDesc, yd: NdDesc, pads_fp, lo, hi):
+        """setup_tensors_overlap (convolution.hpp:1497-1584), forward pass: the
+        output is cut into an interior that reads no halo cell and one boundary
+        slab per side with a neighbour; the interior runs while the halo is in
+        flight.  As in the reference only with one partitioned dimension
+        (convolution.hpp:212-245 gives the reason: diagonal halo cells), and here
+        only for unit stride and dilation in it."""
+        self._ov = None
+        self._ov_plans = []
+        if not self.be.options.overlap_halo_exchange:
+            return
+        nsd = self.nsd
+        ov = input.get_overlap()
+        dims = [i for i in range(nsd) if ov[i] > 0 and input.dist.locale_shape[i] > 1]
+        if len(dims) != 1 or self.strides[dims[0]] != 1 or self.dilations[dims[0]] != 1:
+            return
+        i = dims[0]
+        slot = 2 - i
+        f, out_ext = self.filter_dims[i], yd.dims[slot]
+        b_lo = lo[i] if self.halo_xch_input.peers[i][0] >= 0 else 0
+        b_hi = hi[i] if self.halo_xch_input.peers[i][1] >= 0 else 0
+        if b_lo + b_hi == 0 or out_ext <= b_lo + b_hi:
+            return  # nothing to wait for, or too thin to have an interior
+        regions = []
+        for a, b in ((b_lo, out_ext - b_hi), (0, b_lo), (out_ext - b_hi, out_ext)):
+            if b <= a:
+                continue
+            xr, yr = NdDesc(), NdDesc()
+            ctypes.memmove(ctypes.byref(xr), ctypes.byref(xd), ctypes.sizeof(NdDesc))
+            ctypes.memmove(ctypes.byref(yr), ctypes.byref(yd), ctypes.sizeof(NdDesc))
+            # no padding in a partitioned dimension: output plane o reads window planes [o, o + f)
+            xr.dims[slot], yr.dims[slot] = (b - a) + f - 1, b - a
+            plan = self._make_plan(xr, yr, pads_fp)
+            self._ov_plans.append(plan)
+            regions.append((plan, 4 * a * xd.strides[slot], 4 * a * yd.strides[slot]))
+        self._ov = (i, regions)
+        self._ov_stream = torch.cuda.Stream(priority=-1)
+        self._ov_events = (torch.cuda.Event(), torch.cuda.Event())
+
+    def _forward_overlapped(self, alpha, input: Tensor, filter: torch.Tensor, beta, output: Tensor):
+        """convolution.hpp:520-600: put the halo, run the interior, then the
+        boundary slabs once the neighbours' cells have been unpacked."""
+        dim, regions = self._ov
+        main = self.be.stream if isinstance(self.be.stream, torch.cuda.Stream) else torch.cuda.current_stream()
+        self._clear_halos(input, main)
+        self.halo_xch_input.pack_put(dim, main)
+        self._ov_events[0].record(main)
+        self._ov_stream.wait_event(self._ov_events[0])
+        self.halo_xch_input.wait_unpack(dim, self._ov_stream)
+        self._ov_events[1].record(self._ov_stream)
+        self.forward_regions(alpha, input, filter, beta, output, main, self._ov_events[1])
+        return 0
+
+    def forward_regions(self, alpha, input: Tensor, filter: torch.Tensor, beta, output: Tensor, stream=None,
+                        halo_ready: Optional[torch.cuda.Event] = None):
+        """The interior and then the boundary slabs of the overlapped forward
+        pass; the boundary slabs wait for ``halo_ready`` (None: the halo is
+        already in place)."""
+        _, regions = self._ov
+        x0, y0 = input.nd_ptr(self._x_lo), output.get_base_ptr()
+        for n, (plan, xoff, yoff) in enumerate(regions):  # the interior comes first
+            if n == 1 and halo_ready is not None:
+                stream.wait_event(halo_ready)  # the boundary slabs read the halo
+            call("dcb_conv_fwd", plan, float(alpha), _ptr(x0 + xoff), _ptr(filter.data_ptr()), float(beta),
+                 _ptr(y0 + yoff), _stream_ptr(stream))
 
     def _make_plan(self, xd: NdDesc, yd: NdDesc, pads):
         nsd = self.nsd
@@ -965,6 +1033,8 @@ class Convolution:
         if input.get_local_size() == 0 or output.get_local_size() == 0:
             return 0
         s = self.be.stream
+        if not skip_halo_exchange and getattr(self, "_ov", None) is not None:
+            return self._forward_overlapped(alpha, input, filter, beta, output)
         if not skip_halo_exchange:
             self._clear_halos(input, s)
             self.forward_exchange_halo(input, s)
@@ -1037,7 +1107,7 @@ class Convolution:
         self.be.wait()
 
     def is_overlap_fwd_halo_exchange_enabled(self):
-        return False
+        return getattr(self, "_ov", None) is not None
 
     def is_overlap_bwd_halo_exchange_enabled(self):
         return False

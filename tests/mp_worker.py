@@ -117,6 +117,21 @@ def main():
     emu.assert_close(dx.owned().cpu().numpy(), own(dx, dx_ref), 5e-5, "dx")
     dist.barrier()
 
+    # ---- the same forward pass with the interior running while the halo is in flight ----
+    be_ov = dc.BackendDNNLib(loc, options=dc.Options(overlap_halo_exchange=True))
+    conv_ov = dc.Convolution(be_ov, 5)
+    y_ov = dc.create_convolution_output_tensor(x, f + [C, K], ones3, ones3, ones3)
+    y_ov.allocate()
+    conv_ov.setup(x, wt, y_ov, None, None, None, ones3, ones3, ones3)
+    assert conv_ov.is_overlap_fwd_halo_exchange_enabled() == (n > 1)
+    for rep in range(3):
+        y_ov.buffer.fill_(float("nan"))
+        conv_ov.forward(1.0, x, wt, 0.0, y_ov)
+    torch.cuda.synchronize()
+    assert conv_ov.halo_xch_input.status() == _abi.OK
+    emu.assert_close(y_ov.owned().cpu().numpy(), own(y_ov, y_ref), 1e-5, "y, overlapped")
+    dist.barrier()
+
     # ---- pooling across processes: halo exchange forward, reverse SUM backward ----
     for mode in ("MAX", "AVERAGE_NO_PAD"):
         pshape, plocale = [20, 12, 6 * n, 3, 2], [1, 1, n, 1, 1]

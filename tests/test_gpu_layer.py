@@ -207,3 +207,42 @@ def test_layer_with_statistics_from_the_conv_epilogue(shape, locale):
     emu.assert_close(L.stats[0][:K].cpu().numpy(), m, 2e-5, "mean")
     emu.assert_close(L.stats[0][K:].cpu().numpy(), v, 3e-5, "var")
     emu.assert_close(emu.gather_owned(L.z, osh), z, 3e-5, "bn output")
+
+
+@pytest.mark.parametrize("shape,locale,K,f", [
+    ([20, 16, 12, 4, 1], [1, 1, 4, 1, 1], 16, [3, 3, 3]),   # D split over 4: two inner ranks with two boundary slabs
+    ([24, 20, 3, 2], [1, 2, 1, 1], 5, [5, 5]),              # 2-D, H split, halo of 2
+    ([24, 16, 6, 3, 2], [2, 1, 1, 1, 1], 8, [3, 3, 3]),     # W split: the slabs are column ranges
+])
+def test_overlap_regions_equal_the_whole_convolution(shape, locale, K, f):
+    """Options.overlap_halo_exchange: the interior and boundary slabs together
+    give the convolution of the whole shard (the hand-offs between the halo
+    exchange and the slabs are exercised across processes in mp_worker.py)."""
+    nd, nsd = len(shape), len(shape) - 2
+    n = int(np.prod(locale))
+    C = shape[-2]
+    rng = np.random.default_rng(21)
+    gx = rng.normal(size=tuple(reversed(shape))).astype(np.float32)
+    w = rng.normal(0, 0.1, (K, C, *reversed(f))).astype(np.float32)
+    wt = torch.from_numpy(w).cuda()
+    pads, ones = [(ff - 1) // 2 for ff in f], [1] * nsd
+    bes = emu.make_backends(n, options=dc.Options(overlap_halo_exchange=True))
+    xs, ys, convs = [], [], []
+    for be in bes:
+        x = dc.create_input_tensor(shape, locale, f, ones, ones, be.locale)
+        y = dc.create_convolution_output_tensor(x, list(f) + [C, K], ones, pads, ones)
+        emu.scatter_owned(x, gx)
+        y.allocate()
+        y.buffer.fill_(float("nan"))
+        conv = dc.Convolution(be, nd)
+        conv.setup(x, wt, y, None, None, None, pads, ones, ones, connect=False)
+        xs.append(x), ys.append(y), convs.append(conv)
+    emu.connect_halo([c.halo_xch_input for c in convs])
+    assert all(c.is_overlap_fwd_halo_exchange_enabled() for c in convs)
+    assert sorted(len(c._ov[1]) for c in convs)[-1] == (3 if n > 2 else 2)
+    emu.exchange_all([c.halo_xch_input for c in convs])
+    for c, x, y in zip(convs, xs, ys):
+        c.forward_regions(1.0, x, wt, 0.0, y, torch.cuda.current_stream())
+    torch.cuda.synchronize()
+    ref = O.conv_fwd(gx, w, list(reversed(pads)), list(reversed(ones)))
+    emu.assert_close(emu.gather_owned(ys, ref.shape), ref, 1e-5, "y")
