@@ -1320,13 +1320,9 @@ class Pooling:
         if connect:
             self.halo_xch_input.setup()
             self.halo_xch_d_input.setup()
-        # index workspace of the backward pass (one byte per output cell, MAX only)
+        # index workspace of the backward pass (one byte per output cell, MAX
+        # only); allocated by the first backward call, when the tensors have memory
         self._ws = None
-        if output.get_local_size() > 0 and input.buffer is not None and input.buffer.is_cuda:
-            xd, yd = input.nd_desc(self._lo, self._hi), output.nd_desc()
-            need = _abi.lib().dcb_pool_bwd_workspace_bytes(ctypes.byref(self._pd), ctypes.byref(xd), ctypes.byref(yd))
-            if need > 0:
-                self._ws = torch.empty(need, dtype=torch.uint8, device=input.buffer.device)
 
     def _halo_dims(self, t: Tensor):
         d = t.dist
@@ -1361,11 +1357,14 @@ class Pooling:
             xd, yd = input.nd_desc(self._lo, self._hi), output.nd_desc()
             dxd, dyd = d_input.nd_desc(self._lo, self._hi), d_output.nd_desc()
             assert list(xd.strides) == list(dxd.strides) and list(yd.strides) == list(dyd.strides)
+            if self._ws is None:
+                need = _abi.lib().dcb_pool_bwd_workspace_bytes(ctypes.byref(self._pd), ctypes.byref(xd),
+                                                               ctypes.byref(yd))
+                self._ws = torch.empty(max(need, 0), dtype=torch.uint8, device=d_input.buffer.device)
             call("dcb_pool_bwd", ctypes.byref(self._pd), ctypes.byref(xd), ctypes.byref(yd), float(alpha),
                  _ptr(output.get_base_ptr()), _ptr(d_output.get_base_ptr()), _ptr(input.nd_ptr(self._lo)),
                  float(beta), _ptr(d_input.nd_ptr(self._lo)),
-                 _ptr(self._ws.data_ptr() if self._ws is not None else 0),
-                 self._ws.numel() if self._ws is not None else 0, _stream_ptr(s))
+                 _ptr(self._ws.data_ptr() if self._ws.numel() else 0), self._ws.numel(), _stream_ptr(s))
         if not skip_halo_exchange:
             self.halo_xch_d_input.exchange(s, is_reverse=True, op="SUM")
         return 0
