@@ -557,7 +557,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
 #pragma unroll
         for (int k = 0; k < (STATS ? SW_NBK / 2 : 1); ++k)
             s1[k] = s2[k] = 0ull; // two +0.0f
-        const uint64_t alpha2 = f2_pack(alpha, alpha);
         // every warp zeroes the blocks of the rows it will retire, then hands
         // them out for the first step
         for (int j = half; j < g.th; j += nhalf)
@@ -620,10 +619,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                     {
                         // beta is zero whenever statistics are asked for
 #pragma unroll
+                        // of the raw accumulators: alpha goes on at the end
                         for (int k = 0; k < (STATS ? SW_NBK / 2 : 1); ++k)
                         {
-                            const uint64_t o = f2_mul(
-                                alpha2, f2_pack(__uint_as_float(v[2 * k]), __uint_as_float(v[2 * k + 1])));
+                            const uint64_t o = f2_pack(__uint_as_float(v[2 * k]), __uint_as_float(v[2 * k + 1]));
                             s1[k] = f2_add(s1[k], o);
                             s2[k] = f2_fma(o, o, s2[k]);
                         }
@@ -698,9 +697,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                     b += __shfl_xor_sync(0xffffffffu, b, off);
                 }
                 if (lane == k)
-                    mine = a;
+                    mine = alpha * a;
                 if (lane == SW_NBK + k)
-                    mine = b;
+                    mine = alpha * alpha * b;
             }
             stat_part[((size_t) blockIdx.x * TC_EPI_WARPS + (warp - TC_TMA_WARP - 1)) * 32 + lane] = mine;
         }
