@@ -642,11 +642,21 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                             __syncwarp();
                         }
                         const uint32_t st_s = smem_u32(st) + 4u * (uint32_t) lane;
+                        if (alpha == 1.f)
+                        {
+                            // the usual case: the accumulator bits as they are
 #pragma unroll
-                        for (int k = 0; k < SW_NBK; ++k)
-                            asm volatile("st.shared.f32 [%0], %1;" ::"r"(st_s + 128u * k),
-                                         "f"(alpha * __uint_as_float(v[k]))
-                                         : "memory");
+                            for (int k = 0; k < SW_NBK; ++k)
+                                asm volatile("st.shared.b32 [%0], %1;" ::"r"(st_s + 128u * k), "r"(v[k]) : "memory");
+                        }
+                        else
+                        {
+#pragma unroll
+                            for (int k = 0; k < SW_NBK; ++k)
+                                asm volatile("st.shared.f32 [%0], %1;" ::"r"(st_s + 128u * k),
+                                             "f"(alpha * __uint_as_float(v[k]))
+                                             : "memory");
+                        }
                         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                         __syncwarp();
                         if (lane == 0)
