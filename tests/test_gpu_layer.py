@@ -54,9 +54,10 @@ class Layer:
         K = self.K
         self.w = torch.from_numpy(w).cuda()
         for x in self.x:
-            x.buffer.fill_(float("nan"))  # halos must be produced by the exchange
-            src = tuple(slice(o, o + l) for o, l in reversed(list(zip(x.offset, x.local_shape))))
-            x.owned().copy_(torch.from_numpy(np.ascontiguousarray(gx[src])))
+            if gx is not None:  # None: the owned cells were written by the layer before
+                x.buffer.fill_(float("nan"))  # halos must be produced by the exchange
+                src = tuple(slice(o, o + l) for o, l in reversed(list(zip(x.offset, x.local_shape))))
+                x.owned().copy_(torch.from_numpy(np.ascontiguousarray(gx[src])))
             for d in range(self.nd - 2):
                 x.clear_halo(d)
         emu.exchange_all([c.halo_xch_input for c in self.convs])
@@ -79,7 +80,8 @@ class Layer:
     def backward(self, gdz):
         K = self.K
         for dz in self.dz:
-            emu.scatter_owned(dz, gdz)
+            if gdz is not None:  # None: filled by the layer after this one
+                emu.scatter_owned(dz, gdz)
         ga = [torch.zeros(2 * K, device="cuda") for _ in self.bes]
         gb = [torch.zeros(2 * K, device="cuda") for _ in self.bes]
         for bn, y, dz, st, a, b in zip(self.bns, self.y, self.dz, self.stats, ga, gb):
@@ -246,3 +248,48 @@ def test_overlap_regions_equal_the_whole_convolution(shape, locale, K, f):
     torch.cuda.synchronize()
     ref = O.conv_fwd(gx, w, list(reversed(pads)), list(reversed(ones)))
     emu.assert_close(emu.gather_owned(ys, ref.shape), ref, 1e-5, "y")
+
+
+def _leaky(a, slope):
+    return np.where(a > 0, a, slope * a).astype(np.float32)
+
+
+def test_config3_two_layer_chain_forward_and_backward():
+    """BASELINE configs[2], reduced: conv(4->16, 3^3, s1) -> BN -> LeakyReLU(0.01)
+    -> conv(16->32, 3^3, s2) -> BN on a 2 x 2 x 2 grid, forward and backward,
+    against the same chain on the unpartitioned tensor."""
+    locale, f, slope = [2, 2, 2, 1, 1], [3, 3, 3], 0.01
+    rng = np.random.default_rng(33)
+    gx = rng.uniform(0, 1, (1, 4, 16, 16, 16)).astype(np.float32)
+    w1 = rng.normal(0, np.sqrt(2.0 / (4 * 27)), (16, 4, 3, 3, 3)).astype(np.float32)
+    w2 = rng.normal(0, np.sqrt(2.0 / (16 * 27)), (32, 16, 3, 3, 3)).astype(np.float32)
+    s1, b1 = rng.uniform(0.5, 1.5, 16).astype(np.float32), rng.normal(0, 0.5, 16).astype(np.float32)
+    s2, b2 = rng.uniform(0.5, 1.5, 32).astype(np.float32), rng.normal(0, 0.5, 32).astype(np.float32)
+    L1 = Layer([16, 16, 16, 4, 1], locale, 16, f, [1, 1, 1], pad=1)
+    L2 = Layer([16, 16, 16, 16, 1], locale, 32, f, [2, 2, 2], pad=1)
+    gdz = rng.normal(0, 1, tuple(reversed(L2.out_shape))).astype(np.float32)
+    relus = [dc.LeakyReLU(be) for be in L1.bes]
+    # forward
+    L1.forward(gx, w1, s1, b1)
+    for lr, z, x2 in zip(relus, L1.z, L2.x):
+        x2.buffer.fill_(float("nan"))
+        lr.forward(z, slope, x2)  # into the halo-extended input of layer 2
+    L2.forward(None, w2, s2, b2)
+    # backward
+    L2.backward(gdz)
+    for lr, z, dx2, dz1 in zip(relus, L1.z, L2.dx, L1.dz):
+        dz1.allocate()
+        lr.backward(z, dx2, slope, dz1)
+    L1.backward(None)
+    # the same chain on one domain
+    p, one, two = [1, 1, 1], [1, 1, 1], [2, 2, 2]
+    r1 = oracle_layer(gx, w1, s1, b1, np.zeros((1, 16, 16, 16, 16), np.float32), p, one)
+    a1 = _leaky(r1["z"], slope)
+    r2 = oracle_layer(a1, w2, s2, b2, gdz, p, two)
+    dz1 = np.where(r1["z"] > 0, r2["dx"], slope * r2["dx"]).astype(np.float32)
+    r1b = oracle_layer(gx, w1, s1, b1, dz1, p, one)
+    emu.assert_close(emu.gather_owned(L2.z, r2["z"].shape), r2["z"], 5e-5, "layer 2 output")
+    emu.assert_close(L2.dw[0].cpu().numpy(), r2["dw"], 1e-4, "layer 2 filter gradient")
+    emu.assert_close(emu.gather_owned(L2.dx, a1.shape), r2["dx"], 1e-4, "layer 2 input gradient")
+    emu.assert_close(L1.dw[0].cpu().numpy(), r1b["dw"], 2e-4, "layer 1 filter gradient")
+    emu.assert_close(emu.gather_owned(L1.dx, gx.shape), r1b["dx"], 2e-4, "layer 1 input gradient")
