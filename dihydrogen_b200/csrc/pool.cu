@@ -70,34 +70,44 @@ __device__ __forceinline__ float pool_count(const PoolGeom& g, int od, int oh, i
 // first maximum (dense [n][c][od][oh][ow]); y may then be null.
 constexpr int POOL_TW = POOL_THREADS;
 
+template <int WD, int W, int S>
 __global__ void __launch_bounds__(POOL_THREADS)
     pool_fwd_kernel(PoolGeom g, float alpha, float beta, const float* __restrict__ x, float* y,
                     unsigned char* __restrict__ argmax)
 {
+    // window / stride as compile-time constants where the launch found a match
+    // (unrolled loops, shifts for the divisions); 0 = read them from the geometry
+    const int w0_ = WD ? WD : g.win[0], w1_ = W ? W : g.win[1], w2_ = W ? W : g.win[2];
+    const int s0_ = S ? (WD == 1 ? 1 : S) : g.stride[0], s1_ = S ? S : g.stride[1], s2_ = S ? S : g.stride[2];
     const int ow = blockIdx.y * POOL_THREADS + threadIdx.x;
     if (ow >= g.out[2])
         return;
     const int oh = blockIdx.x % g.out[1], od = blockIdx.x / g.out[1];
     const int c = blockIdx.z % g.c, n = blockIdx.z / g.c;
     const float* xp = x + (size_t) n * g.xs_n + (size_t) c * g.xs_c;
-    const int d0 = od * g.stride[0] - g.pad[0], h0 = oh * g.stride[1] - g.pad[1], w0 = ow * g.stride[2] - g.pad[2];
-    const int kw_lo = max(0, g.lo[2] - w0), kw_hi = min(g.win[2], g.hi[2] - w0);
+    const int d0 = od * s0_ - g.pad[0], h0 = oh * s1_ - g.pad[1], w0 = ow * s2_ - g.pad[2];
+    const int kw_lo = max(0, g.lo[2] - w0), kw_hi = min(w2_, g.hi[2] - w0);
     float m = -FLT_MAX, s = 0.f;
     int best = -1;
-    for (int kd = 0; kd < g.win[0]; ++kd)
+#pragma unroll
+    for (int kd = 0; kd < w0_; ++kd)
     {
         const int id = d0 + kd;
         if (id < g.lo[0] || id >= g.hi[0])
             continue;
-        for (int kh = 0; kh < g.win[1]; ++kh)
+#pragma unroll
+        for (int kh = 0; kh < w1_; ++kh)
         {
             const int ih = h0 + kh;
             if (ih < g.lo[1] || ih >= g.hi[1])
                 continue;
             const float* row = xp + (size_t) id * g.xs[0] + (size_t) ih * g.xs[1] + w0;
-            const int tap0 = (kd * g.win[1] + kh) * g.win[2];
-            for (int kw = kw_lo; kw < kw_hi; ++kw)
+            const int tap0 = (kd * w1_ + kh) * w2_;
+#pragma unroll
+            for (int kw = 0; kw < w2_; ++kw)
             {
+                if (kw < kw_lo || kw >= kw_hi)
+                    continue;
                 const float v = __ldg(row + kw);
                 s += v;
                 if (best < 0 || v > m)
@@ -144,10 +154,15 @@ __device__ __forceinline__ void pool_cover(int i, int stride, int pad, int win, 
     *hi = min(hq, nout - 1);
 }
 
+template <int WD, int W, int S>
 __global__ void __launch_bounds__(POOL_THREADS)
     pool_bwd_kernel(PoolGeom g, float alpha, float beta, const float* __restrict__ y, const float* __restrict__ dy,
                     const float* __restrict__ x, float* dx, const unsigned char* __restrict__ argmax)
 {
+    // window / stride as compile-time constants where the launch found a match
+    // (unrolled loops, shifts for the divisions); 0 = read them from the geometry
+    const int w0_ = WD ? WD : g.win[0], w1_ = W ? W : g.win[1], w2_ = W ? W : g.win[2];
+    const int s0_ = S ? (WD == 1 ? 1 : S) : g.stride[0], s1_ = S ? S : g.stride[1], s2_ = S ? S : g.stride[2];
     const int iw = blockIdx.y * POOL_THREADS + threadIdx.x;
     if (iw >= g.in[2])
         return;
@@ -157,9 +172,9 @@ __global__ void __launch_bounds__(POOL_THREADS)
     const size_t yoff = (size_t) n * g.ys_n + (size_t) c * g.ys_c;
     const size_t me = xoff + (size_t) id * g.xs[0] + (size_t) ih * g.xs[1] + iw;
     int dlo, dhi, hlo, hhi, wlo, whi;
-    pool_cover(id, g.stride[0], g.pad[0], g.win[0], g.out[0], &dlo, &dhi);
-    pool_cover(ih, g.stride[1], g.pad[1], g.win[1], g.out[1], &hlo, &hhi);
-    pool_cover(iw, g.stride[2], g.pad[2], g.win[2], g.out[2], &wlo, &whi);
+    pool_cover(id, s0_, g.pad[0], w0_, g.out[0], &dlo, &dhi);
+    pool_cover(ih, s1_, g.pad[1], w1_, g.out[1], &hlo, &hhi);
+    pool_cover(iw, s2_, g.pad[2], w2_, g.out[2], &wlo, &whi);
     const float xv = g.mode == DCB_POOL_MAX && !argmax ? __ldg(x + me) : 0.f;
     float acc = 0.f;
     // a cell outside the global tensor is padding: no window gives it anything
@@ -175,10 +190,10 @@ __global__ void __launch_bounds__(POOL_THREADS)
             {
                 const size_t drow = ((plane + od) * g.out[1] + oh) * g.out[2];
                 const float* dyrow = dy + yoff + (size_t) od * g.ys[0] + (size_t) oh * g.ys[1];
-                const int tap0 = ((id - (od * g.stride[0] - g.pad[0])) * g.win[1] + (ih - (oh * g.stride[1] - g.pad[1])))
-                                 * g.win[2];
+                const int tap0 = ((id - (od * s0_ - g.pad[0])) * w1_ + (ih - (oh * s1_ - g.pad[1])))
+                                 * w2_;
                 for (int ow = wlo; ow <= whi; ++ow)
-                    if ((int) __ldg(argmax + drow + ow) == tap0 + iw - (ow * g.stride[2] - g.pad[2]))
+                    if ((int) __ldg(argmax + drow + ow) == tap0 + iw - (ow * s2_ - g.pad[2]))
                         acc += __ldg(dyrow + ow);
             }
         dlo = dhi + 1;
@@ -197,15 +212,15 @@ __global__ void __launch_bounds__(POOL_THREADS)
                     continue;
                 // the maximum goes to the first cell that holds it: is one before me?
                 bool first = true;
-                const int d0 = od * g.stride[0] - g.pad[0], h0 = oh * g.stride[1] - g.pad[1],
-                          w0 = ow * g.stride[2] - g.pad[2];
+                const int d0 = od * s0_ - g.pad[0], h0 = oh * s1_ - g.pad[1],
+                          w0 = ow * s2_ - g.pad[2];
                 for (int jd = max(d0, g.lo[0]); jd <= id && first; ++jd)
-                    for (int jh = max(h0, g.lo[1]); jh < min(h0 + g.win[1], g.hi[1]) && first; ++jh)
+                    for (int jh = max(h0, g.lo[1]); jh < min(h0 + w1_, g.hi[1]) && first; ++jh)
                     {
                         if (jd == id && jh > ih)
                             break;
                         const float* row = x + xoff + (size_t) jd * g.xs[0] + (size_t) jh * g.xs[1];
-                        const int wend = (jd == id && jh == ih) ? iw : min(w0 + g.win[2], g.hi[2]);
+                        const int wend = (jd == id && jh == ih) ? iw : min(w0 + w2_, g.hi[2]);
                         for (int jw = max(w0, g.lo[2]); jw < wend; ++jw)
                             if (__ldg(row + jw) == xv)
                             {
@@ -217,6 +232,73 @@ __global__ void __launch_bounds__(POOL_THREADS)
                     acc += __ldg(dy + o);
             }
     dx[me] = beta != 0.f ? alpha * acc + beta * dx[me] : alpha * acc;
+}
+
+// MAX backward with the index workspace: a thread owns four consecutive cells of
+// an input row, walks the (od, oh) pairs whose windows hold the row once for all
+// four, and compares one byte per (cell, window).  Every instruction here is
+// paid 268 M times on the bench shard: the per-cell version spent 430 per cell.
+template <int WD, int W, int S>
+__global__ void __launch_bounds__(POOL_THREADS)
+    pool_bwd_index_kernel(PoolGeom g, float alpha, float beta, const float* __restrict__ dy, float* dx,
+                          const unsigned char* __restrict__ argmax)
+{
+    const int w0_ = WD ? WD : g.win[0], w1_ = W ? W : g.win[1], w2_ = W ? W : g.win[2];
+    const int s0_ = S ? (WD == 1 ? 1 : S) : g.stride[0], s1_ = S ? S : g.stride[1], s2_ = S ? S : g.stride[2];
+    const int iw0 = (blockIdx.y * POOL_THREADS + threadIdx.x) * 4;
+    if (iw0 >= g.in[2])
+        return;
+    const int ih = blockIdx.x % g.in[1], id = blockIdx.x / g.in[1];
+    const int c = blockIdx.z % g.c, n = blockIdx.z / g.c;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    int dlo, dhi, hlo, hhi;
+    pool_cover(id, s0_, g.pad[0], w0_, g.out[0], &dlo, &dhi);
+    pool_cover(ih, s1_, g.pad[1], w1_, g.out[1], &hlo, &hhi);
+    if (id < g.lo[0] || id >= g.hi[0] || ih < g.lo[1] || ih >= g.hi[1])
+        dhi = dlo - 1; // a row outside the global tensor is padding
+    int wlo[4], whi[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+    {
+        pool_cover(iw0 + e, s2_, g.pad[2], w2_, g.out[2], &wlo[e], &whi[e]);
+        if (iw0 + e < g.lo[2] || iw0 + e >= g.hi[2] || iw0 + e >= g.in[2])
+            whi[e] = wlo[e] - 1;
+    }
+    const size_t plane = ((size_t) n * g.c + c) * g.out[0];
+    const float* dyp = dy + (size_t) n * g.ys_n + (size_t) c * g.ys_c;
+    for (int od = dlo; od <= dhi; ++od)
+        for (int oh = hlo; oh <= hhi; ++oh)
+        {
+            const unsigned char* arow = argmax + ((plane + od) * g.out[1] + oh) * g.out[2];
+            const float* dyrow = dyp + (size_t) od * g.ys[0] + (size_t) oh * g.ys[1];
+            const int tap0 = ((id - (od * s0_ - g.pad[0])) * w1_ + (ih - (oh * s1_ - g.pad[1]))) * w2_ + g.pad[2] + iw0;
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                for (int ow = wlo[e]; ow <= whi[e]; ++ow)
+                    if ((int) __ldg(arow + ow) == tap0 + e - ow * s2_)
+                        acc[e] += __ldg(dyrow + ow);
+        }
+    float* xp = dx + (size_t) n * g.xs_n + (size_t) c * g.xs_c + (size_t) id * g.xs[0] + (size_t) ih * g.xs[1] + iw0;
+    if (iw0 + 4 <= g.in[2] && (reinterpret_cast<uintptr_t>(xp) & 15) == 0)
+    {
+        float4 o = make_float4(alpha * acc[0], alpha * acc[1], alpha * acc[2], alpha * acc[3]);
+        if (beta != 0.f)
+        {
+            const float4 old = *reinterpret_cast<const float4*>(xp);
+            o.x += beta * old.x;
+            o.y += beta * old.y;
+            o.z += beta * old.z;
+            o.w += beta * old.w;
+        }
+        *reinterpret_cast<float4*>(xp) = o;
+    }
+    else
+    {
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+            if (iw0 + e < g.in[2])
+                xp[e] = beta != 0.f ? alpha * acc[e] + beta * xp[e] : alpha * acc[e];
+    }
 }
 
 int32_t pool_geom(const dcb_pool_desc* pd, const dcb_nd_desc* xd, const dcb_nd_desc* yd, PoolGeom* g)
@@ -275,6 +357,32 @@ bool pool_grid(int w, long long rows, long long planes, dim3* grid)
     return true;
 }
 
+// Picks the kernel instance whose compile-time window and stride match: cubic
+// (or, for 2-D, square with a unit D slot) windows of 3 with stride 1 or 2 and of 2
+// with stride 2; anything else runs the generic instance.
+#define DCB_POOL_DISPATCH(g)                                                                                          \
+    do                                                                                                                \
+    {                                                                                                                 \
+        const int w_ = (g).win[2], s_ = (g).stride[2];                                                               \
+        const bool sq_ = (g).win[1] == w_ && (g).stride[1] == s_;                                                    \
+        const bool flat_ = (g).win[0] == 1 && (g).stride[0] == 1;                                                    \
+        const bool cube_ = (g).win[0] == w_ && (g).stride[0] == s_;                                                  \
+        if (sq_ && cube_ && w_ == 3 && s_ == 2)                                                                       \
+            DCB_POOL_CALL(3, 3, 2);                                                                                   \
+        else if (sq_ && cube_ && w_ == 3 && s_ == 1)                                                                  \
+            DCB_POOL_CALL(3, 3, 1);                                                                                   \
+        else if (sq_ && cube_ && w_ == 2 && s_ == 2)                                                                  \
+            DCB_POOL_CALL(2, 2, 2);                                                                                   \
+        else if (sq_ && flat_ && w_ == 3 && s_ == 2)                                                                  \
+            DCB_POOL_CALL(1, 3, 2);                                                                                   \
+        else if (sq_ && flat_ && w_ == 3 && s_ == 1)                                                                  \
+            DCB_POOL_CALL(1, 3, 1);                                                                                   \
+        else if (sq_ && flat_ && w_ == 2 && s_ == 2)                                                                  \
+            DCB_POOL_CALL(1, 2, 2);                                                                                   \
+        else                                                                                                          \
+            DCB_POOL_CALL(0, 0, 0);                                                                                   \
+    } while (0)
+
 int32_t launch_pool_fwd(const PoolGeom& g, float alpha, float beta, const float* x, float* y, unsigned char* argmax,
                         cudaStream_t stream)
 {
@@ -285,8 +393,10 @@ int32_t launch_pool_fwd(const PoolGeom& g, float alpha, float beta, const float*
         set_last_error("tensor too large for the pooling grid");
         return DCB_UNSUPPORTED;
     }
-    pool_fwd_kernel<<<dim3((unsigned) rows, (unsigned) tiles, (unsigned) planes), POOL_THREADS, 0, stream>>>(
-        g, alpha, beta, x, y, argmax);
+    const dim3 grid((unsigned) rows, (unsigned) tiles, (unsigned) planes);
+#define DCB_POOL_CALL(WD, W, S) pool_fwd_kernel<WD, W, S><<<grid, POOL_THREADS, 0, stream>>>(g, alpha, beta, x, y, argmax)
+    DCB_POOL_DISPATCH(g);
+#undef DCB_POOL_CALL
     DCB_LAUNCH_CHECK();
     return DCB_OK;
 }
@@ -353,9 +463,23 @@ extern "C" int32_t dcb_pool_bwd(const dcb_pool_desc* pd, const dcb_nd_desc* xd, 
             return st2;
         idx = static_cast<const unsigned char*>(workspace);
     }
-    pool_bwd_kernel<<<grid, POOL_THREADS, 0, as_stream(stream)>>>(
-        g, (float) alpha, (float) beta, static_cast<const float*>(y), static_cast<const float*>(dy),
-        static_cast<const float*>(x), static_cast<float*>(dx), idx);
+    if (idx)
+    {
+        const dim3 grid4(grid.x, (unsigned) ((g.in[2] + 4 * POOL_THREADS - 1) / (4 * POOL_THREADS)), grid.z);
+#define DCB_POOL_CALL(WD, W, S)                                                                                       \
+    pool_bwd_index_kernel<WD, W, S><<<grid4, POOL_THREADS, 0, as_stream(stream)>>>(                                  \
+        g, (float) alpha, (float) beta, static_cast<const float*>(dy), static_cast<float*>(dx), idx)
+        DCB_POOL_DISPATCH(g);
+#undef DCB_POOL_CALL
+        DCB_LAUNCH_CHECK();
+        return DCB_OK;
+    }
+#define DCB_POOL_CALL(WD, W, S)                                                                                       \
+    pool_bwd_kernel<WD, W, S><<<grid, POOL_THREADS, 0, as_stream(stream)>>>(                                         \
+        g, (float) alpha, (float) beta, static_cast<const float*>(y), static_cast<const float*>(dy),                  \
+        static_cast<const float*>(x), static_cast<float*>(dx), idx)
+    DCB_POOL_DISPATCH(g);
+#undef DCB_POOL_CALL
     DCB_LAUNCH_CHECK();
     return DCB_OK;
 }
