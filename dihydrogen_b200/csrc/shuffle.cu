@@ -114,12 +114,20 @@ __global__ void __launch_bounds__(SHF_THREADS) shuffle_kernel(ShfArgs a)
         shf_locate(j, r, &ao, &bo);
         float* t = a.tensor + ao;
         float* w = (PUT ? j.peer + a.parity * j.parity_pitch : a.window) + bo;
-        for (long long e = lane; e < j.len; e += 32)
+        const float* from = PUT ? t : w;
+        float* to = PUT ? w : t;
+        if ((j.len & 3) == 0 && ((reinterpret_cast<uintptr_t>(from) | reinterpret_cast<uintptr_t>(to)) & 15) == 0)
         {
-            if (PUT)
-                w[e] = t[e];
-            else
-                t[e] = w[e];
+            // 16-byte accesses where the run allows them
+            const float4* f4 = reinterpret_cast<const float4*>(from);
+            float4* t4 = reinterpret_cast<float4*>(to);
+            for (long long e = lane; e < j.len / 4; e += 32)
+                t4[e] = f4[e];
+        }
+        else
+        {
+            for (long long e = lane; e < j.len; e += 32)
+                to[e] = from[e];
         }
     }
     if (PUT)
