@@ -183,7 +183,60 @@ def run_ranks(args, torch, dc, dist, world, rank):
                 torch.cuda.empty_cache()
                 if not r["exact"]:
                     raise SystemExit("halo contents differ from the global-offset fill")
+    results += run_shuffle(args, torch, dc, dist, world, rank, locale)
     return results
+
+
+def run_shuffle(args, torch, dc, dist, world, rank, locale):
+    """Re-distribution sample-parallel -> D-partitioned and back (C=16, N=world
+    samples of 128^3 / 256^3): every rank sends (world-1)/world of its shard over
+    NVLink.  Checked bit-exact against the round trip."""
+    from dihydrogen_b200 import _abi
+
+    out = []
+    for S in (128, 256):
+        shape = [S, S, S, 16, world]
+        if 4.0 * S ** 3 * 16 / 1e9 > args.max_gb:
+            continue
+        ts = dc.Tensor(shape, locale, dc.Distribution.make_overlapped_distribution([1, 1, 1, 1, world], [0] * 5))
+        td = dc.Tensor(shape, locale, dc.Distribution.make_overlapped_distribution([1, 1, world, 1, 1], [0, 0, 1, 0, 0]))
+        tb = dc.Tensor(shape, locale, dc.Distribution.make_overlapped_distribution([1, 1, 1, 1, world], [0] * 5))
+        for t in (ts, td, tb):
+            t.allocate()
+        ts.buffer.normal_()
+        shf = dc.TensorShuffler(ts, td)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        total = 0.0
+        for it in range(args.reps + 3):
+            torch.cuda.synchronize()
+            dist.barrier()
+            torch.cuda.synchronize()
+            e0.record()
+            shf.shuffle_forward(ts.get_buffer(), td.get_buffer())
+            e1.record()
+            torch.cuda.synchronize()
+            if it >= 3:
+                total += e0.elapsed_time(e1)
+            shf.shuffle_backward(td.get_buffer(), tb.get_buffer())
+        torch.cuda.synchronize()
+        ms = torch.tensor([total / args.reps], device="cuda")
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        good = torch.tensor([1 if (torch.equal(tb.buffer, ts.buffer) and shf.status("fwd") == _abi.OK
+                                   and shf.status("bwd") == _abi.OK) else 0], device="cuda")
+        dist.all_reduce(good, op=dist.ReduceOp.MIN)
+        sent = 4.0 * ts.buffer.numel() * (world - 1) / world
+        r = {"mode": f"{world}gpu-shuffle sample->D", "C": 16, "S": S, "width": 0, "dim": "N->D",
+             "shard_MB": 4.0 * ts.buffer.numel() / 1e6, "shuffle_us": 1e3 * float(ms.item()),
+             "nvlink_GBs_per_direction": sent / (float(ms.item()) * 1e-3) / 1e9, "exact": bool(good.item())}
+        if rank == 0:
+            print(json.dumps(r), flush=True)
+        out.append(r)
+        dist.barrier()
+        del shf, ts, td, tb
+        torch.cuda.empty_cache()
+        if not r["exact"]:
+            raise SystemExit("the re-distribution round trip changed the tensor")
+    return out
 
 
 def main():
