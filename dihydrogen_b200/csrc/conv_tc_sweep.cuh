@@ -219,7 +219,9 @@ __device__ __forceinline__ void sw_convert_c4f3(uint32_t raw_lane, uint32_t pitc
     {
         const float xe = __uint_as_float(xv[r]);
         const uint32_t hi = tf32_rna(xe);
-        const uint32_t lo = tf32_rna(xe - __uint_as_float(hi));
+        // x - hi is exact in fp32 and below 2^-11 |x|; the tensor pipe reads the
+        // upper 19 bits of it, an error below 2^-21 |x|: no rounding of its own
+        const uint32_t lo = __float_as_uint(xe - __uint_as_float(hi));
         v[r / 8][r % 8] = hi;
         v[(12 + r) / 8][(12 + r) % 8] = lo;
         v[(24 + r) / 8][(24 + r) % 8] = hi;

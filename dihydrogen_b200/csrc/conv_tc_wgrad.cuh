@@ -209,7 +209,8 @@ __global__ void __launch_bounds__(WG_THREADS, 1)
                         {
                             const float xe = __uint_as_float(lds_u32(s0 + 4u * (uint32_t) (e * SW)));
                             hi[ks][e] = tf32_rna(xe);
-                            lo[ks][e] = tf32_rna(xe - __uint_as_float(hi[ks][e]));
+                            // exact remainder, fed as it is: the pipe reads its upper 19 bits
+                            lo[ks][e] = __float_as_uint(xe - __uint_as_float(hi[ks][e]));
                         }
                     }
                     else
