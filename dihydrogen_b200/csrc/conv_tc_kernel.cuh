@@ -326,7 +326,7 @@ __device__ __forceinline__ void convert_chunk(uint32_t ktab8, uint32_t raw_lane,
         const uint32_t part = tb[e] >> 16;
         const float xe = part < 2 ? __uint_as_float(xv[e]) : 0.f;
         const uint32_t hi = tf32_rna(xe);
-        const uint32_t lo = tf32_rna(xe - __uint_as_float(hi));
+        const uint32_t lo = __float_as_uint(xe - __uint_as_float(hi)); // exact; the pipe reads its upper 19 bits
         v[e] = part == 0 ? hi : lo;
     }
 }
@@ -347,7 +347,7 @@ __device__ __forceinline__ void convert_c4f3(uint32_t raw_lane, uint32_t pitch, 
     {
         const float xe = __uint_as_float(xv[r]);
         const uint32_t hi = tf32_rna(xe);
-        const uint32_t lo = tf32_rna(xe - __uint_as_float(hi));
+        const uint32_t lo = __float_as_uint(xe - __uint_as_float(hi)); // exact; the pipe reads its upper 19 bits
         v[r / 8][r % 8] = hi;
         v[(12 + r) / 8][(12 + r) % 8] = lo;
     }
