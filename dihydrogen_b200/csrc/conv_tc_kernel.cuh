@@ -326,8 +326,29 @@ __device__ __forceinline__ void convert_chunk(uint32_t ktab8, uint32_t raw_lane,
         const uint32_t part = tb[e] >> 16;
         const float xe = part < 2 ? __uint_as_float(xv[e]) : 0.f;
         const uint32_t hi = tf32_rna(xe);
-        const uint32_t lo = __float_as_uint(xe - __uint_as_float(hi)); // exact; the pipe reads its upper 19 bits
+        const uint32_t lo = tf32_rna(xe - __uint_as_float(hi));
         v[e] = part == 0 ? hi : lo;
+    }
+}
+
+// Eight taps at once for rows whose tap count is a multiple of eight: the hi
+// parts go to k-rows r0.., the lo parts to k-rows crows + r0.. (the table's
+// first `crows` entries are the taps' offsets), each cell loaded and split once.
+__device__ __forceinline__ void convert_pair(uint32_t ktab8, uint32_t raw_lane, uint32_t (&hi)[8], uint32_t (&lo)[8])
+{
+    uint32_t tb[8], xv[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e)
+        tb[e] = lds_u32(ktab8 + 4u * e);
+#pragma unroll
+    for (int e = 0; e < 8; ++e)
+        xv[e] = lds_u32(raw_lane + ((tb[e] & 0xffffu) << 2));
+#pragma unroll
+    for (int e = 0; e < 8; ++e)
+    {
+        const float xe = __uint_as_float(xv[e]);
+        hi[e] = tf32_rna(xe);
+        lo[e] = __float_as_uint(xe - __uint_as_float(hi[e]));
     }
 }
 
@@ -555,11 +576,24 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                     if (!ok)
                         break;
                     tc_fence_after();
-                    for (int r0 = 0; r0 < g.kr; r0 += 8)
+                    if (g.split && (g.crows & 7) == 0)
                     {
-                        uint32_t v[8];
-                        convert_chunk(ktab_s + 4u * r0, raw_s, v);
-                        tmem_st8(a_addr + (uint32_t) r0, v);
+                        for (int r0 = 0; r0 < g.crows; r0 += 8)
+                        {
+                            uint32_t hi[8], lo[8];
+                            convert_pair(ktab_s + 4u * r0, raw_s, hi, lo);
+                            tmem_st8(a_addr + (uint32_t) r0, hi);
+                            tmem_st8(a_addr + (uint32_t) (g.crows + r0), lo);
+                        }
+                    }
+                    else
+                    {
+                        for (int r0 = 0; r0 < g.kr; r0 += 8)
+                        {
+                            uint32_t v[8];
+                            convert_chunk(ktab_s + 4u * r0, raw_s, v);
+                            tmem_st8(a_addr + (uint32_t) r0, v);
+                        }
                     }
                 }
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");

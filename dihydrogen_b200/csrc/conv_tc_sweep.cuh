@@ -206,6 +206,11 @@ __global__ void sw_stats_fold_kernel(const float* __restrict__ part, int nparts,
 }
 
 // 4 channels x 3 taps, pad 1, split: k-rows 0..11 hi, 12..23 lo, 24..35 hi, 36..39 zero.
+// ROUND_LO: the lo part rounded to TF32 as well (two more instructions per tap).
+// The multi-group kernel asks for it: its accumulators take 180 and more updates
+// per output, the tensor pipe's accumulation already uses most of the 1e-5 there
+// and the unrounded remainder tipped a case over the bound.
+template <bool ROUND_LO = false>
 __device__ __forceinline__ void sw_convert_c4f3(uint32_t raw_lane, uint32_t pitch, uint32_t (&v)[5][8])
 {
     uint32_t xv[12];
@@ -221,7 +226,8 @@ __device__ __forceinline__ void sw_convert_c4f3(uint32_t raw_lane, uint32_t pitc
         const uint32_t hi = tf32_rna(xe);
         // x - hi is exact in fp32 and below 2^-11 |x|; the tensor pipe reads the
         // upper 19 bits of it, an error below 2^-21 |x|: no rounding of its own
-        const uint32_t lo = __float_as_uint(xe - __uint_as_float(hi));
+        const uint32_t lo =
+            ROUND_LO ? tf32_rna(xe - __uint_as_float(hi)) : __float_as_uint(xe - __uint_as_float(hi));
         v[r / 8][r % 8] = hi;
         v[(12 + r) / 8][(12 + r) % 8] = lo;
         v[(24 + r) / 8][(24 + r) % 8] = hi;

@@ -203,7 +203,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                         if (C4F3)
                         {
                             uint32_t v[5][8];
-                            sw_convert_c4f3(raw_s, pitch, v);
+                            sw_convert_c4f3<true>(raw_s, pitch, v);
                             if (!a_first)
                                 ok = mbar_wait(&a_empty[a_slot], a_phase, abort_flag);
                             if (!ok)
