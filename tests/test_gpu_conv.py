@@ -120,6 +120,7 @@ GEOMS = [
     (1, 8, 20, (7, 12, 280), (3, 3, 3), (1, 1, 1), (2, 2, 2), (1, 1, 1)),     # stride 2, two W tiles (ragged), grouped backward filter
     (2, 4, 16, (9, 300), (3, 3), (1, 1), (1, 2), (1, 1)),                     # stride 2 along W only
     (1, 3, 5, (10, 264), (5, 5), (2, 2), (2, 2), (1, 1)),                     # 5x5 stride 2
+    (1, 4, 32, (6, 9, 40), (3, 3, 3), (1, 1, 1), (1, 1, 1), (1, 1, 1)),       # backward data with 8 channel groups: group launches, not one accumulator chain
 ]
 
 
