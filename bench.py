@@ -3,16 +3,22 @@
 convolution forward + distributed batch-norm forward} layer pass.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--partition auto|d] [--config cfg2|cfg1]
 
-Workload (BASELINE.json configs[1]): input N=1, C=4, 256^3 fp32 ~N(0,1),
-3x3x3 filters K=16 stride 1 pad 1 He-init, BN over the channel dimension with
-per-channel statistics all-reduced over the spatial partition.  Weak scaling:
-every GPU owns a 256^3 shard, the global volume is 256 x 256 x (256*N) split
-along D.  Inputs are seeded, synthetic and independent of the partitioning.
+Workload (BASELINE.json configs[1]): input N=1, C=4, 256^3 fp32 ~N(0,1) per
+GPU, 3x3x3 filters K=16 stride 1 pad 1 He-init, BN over the channel dimension
+with per-channel statistics all-reduced over the spatial partition.  Weak
+scaling: every GPU owns a 256^3 shard; with --partition auto (the default) the
+global volume grows as 256^3 -> 256 x 256 x 512 (D split) -> 256 x 512 x 512
+(D x H) -> 512^3 on a 2 x 2 x 2 grid at 8 GPUs; --partition d grows it along D
+only.  Inputs are seeded, synthetic and keyed on the global index.
 
 Prints ONE JSON line (rank 0).  `value` is voxels/s with inputs resident in
 HBM; `e2e` is the same pass driven from pinned host buffers (H2D of the input
-shard and D2H of the BN output inside the timed region).
+shard and D2H of the BN output inside the timed region).  After the timed
+regions every rank checks its results (halo cells bit for bit, conv / BN
+blocks at every partitioned face against fp64) and the line carries the
+verdict; a failed check exits non-zero.
 """
 from __future__ import annotations
 
@@ -22,6 +28,7 @@ import os
 import statistics
 import subprocess
 import sys
+import tempfile
 import threading
 import time
 
@@ -35,16 +42,25 @@ EXTENT = 256
 C_IN, K_OUT = 4, 16
 FILTER = [3, 3, 3]
 EPS, DECAY = 1e-5, 0.9
+# weak-scaling ladder: process grid (W, H, D) per GPU count
+LADDER = {1: [1, 1, 1], 2: [1, 1, 2], 4: [1, 2, 2], 8: [2, 2, 2]}
 
 
-def layer_geometry(n_gpus, locale, extent=EXTENT, local_d=None):
-    """Tensors (unallocated) of the benchmark layer for this rank: the global
-    volume grows with the GPU count along D (weak scaling).  local_d shrinks
-    the per-GPU D extent (profiling captures only)."""
+def grid_for(n_gpus, partition):
+    if partition == "auto" and n_gpus in LADDER:
+        return list(LADDER[n_gpus])
+    return [1, 1, n_gpus]
+
+
+def layer_geometry(grid, locale, extent=EXTENT, local_d=None):
+    """Tensors (unallocated) of the benchmark layer for this rank: every rank
+    owns an extent^3 shard (local_d shrinks its D extent, profiling captures
+    only), the global volume is the shard times the process grid."""
     import dihydrogen_b200 as dc
 
-    shape = [extent, extent, (local_d or extent) * n_gpus, C_IN, 1]  # W, H, D, C, N
-    locale_shape = [1, 1, n_gpus, 1, 1]
+    local = [extent, extent, local_d or extent]
+    shape = [local[i] * grid[i] for i in range(3)] + [C_IN, 1]  # W, H, D, C, N
+    locale_shape = list(grid) + [1, 1]
     strides, dil = [1, 1, 1], [1, 1, 1]
     x = dc.create_input_tensor(shape, locale_shape, FILTER, strides, dil, locale)
     fshape = FILTER + [C_IN, K_OUT]
@@ -54,14 +70,40 @@ def layer_geometry(n_gpus, locale, extent=EXTENT, local_d=None):
                 dilations=dil, pads=[1, 1, 1], filter_shape=fshape)
 
 
+def synth_plane(seed, c, d, gh, gw):
+    """One (channel, global D index) plane of x ~ N(0,1): the same global
+    tensor whatever the partitioning of a given global volume."""
+    rng = np.random.default_rng([seed, c, d])
+    return rng.standard_normal((gh, gw), dtype=np.float32)
+
+
 def synth_input_shard(seed, offset_d, local_d, extent):
-    """x ~ N(0,1), keyed on (seed, channel, global D index): the same global
-    tensor whatever the partitioning."""
+    """The (1, C, local_d, extent, extent) block at D offset offset_d of a
+    global volume whose planes are extent x extent."""
     out = np.empty((1, C_IN, local_d, extent, extent), np.float32)
     for c in range(C_IN):
         for d in range(local_d):
-            rng = np.random.default_rng([seed, c, offset_d + d])
-            out[0, c, d] = rng.standard_normal((extent, extent), dtype=np.float32)
+            out[0, c, d] = synth_plane(seed, c, offset_d + d, extent, extent)
+    return out
+
+
+def synth_extended_shard(seed, shape, offset, local):
+    """This rank's block of the global input with one more cell on every side
+    of every spatial dimension: the neighbours' cells inside the global volume,
+    zeros outside (the padding).  shape / offset / local in (W, H, D) order;
+    returns (C, D+2, H+2, W+2)."""
+    gw, gh, gd = shape[:3]
+    ow, oh, od = offset[:3]
+    lw, lh, ld = local[:3]
+    out = np.zeros((C_IN, ld + 2, lh + 2, lw + 2), np.float32)
+    h0, h1 = max(oh - 1, 0), min(oh + lh + 1, gh)
+    w0, w1 = max(ow - 1, 0), min(ow + lw + 1, gw)
+    for c in range(C_IN):
+        for d in range(od - 1, od + ld + 1):
+            if d < 0 or d >= gd:
+                continue
+            plane = synth_plane(seed, c, d, gh, gw)
+            out[c, d - (od - 1), h0 - (oh - 1):h1 - (oh - 1), w0 - (ow - 1):w1 - (ow - 1)] = plane[h0:h1, w0:w1]
     return out
 
 
@@ -131,11 +173,20 @@ def measured_peaks():
 # --------------------------------------------------------------------------
 # CPU arm: the oracle port on host cores, on a bounded D-slab of the workload
 # --------------------------------------------------------------------------
+def cpu_threads():
+    """All host cores this process may use, set explicitly: launchers such as
+    torch.distributed.run export OMP_NUM_THREADS=1."""
+    from oracle import oracle as O
+
+    return O.set_num_threads(O.host_cores())
+
+
 def cpu_layer_pass(sample_d, extent, seed=0, repeats=1):
     """One halo-free conv forward + BN forward on a (sample_d x extent x
     extent) slab with the restated CPU arithmetic; returns (seconds, threads)."""
     from oracle import oracle as O
 
+    threads = cpu_threads()
     x = synth_input_shard(seed, 0, sample_d, extent)
     w = synth_filter(seed)
     best = None
@@ -148,7 +199,7 @@ def cpu_layer_pass(sample_d, extent, seed=0, repeats=1):
         O.bn_normalize(y, m, v, np.ones(K_OUT, np.float32), np.zeros(K_OUT, np.float32), EPS)
         dt = time.perf_counter() - t0
         best = dt if best is None else min(best, dt)
-    return best, O.num_threads()
+    return best, threads
 
 
 def pick_cpu_sample(extent, target_s=4.0):
@@ -159,10 +210,62 @@ def pick_cpu_sample(extent, target_s=4.0):
     return d
 
 
+CFG1 = dict(N=4, C=16, H=64, W=64, K=16, f=3)  # BASELINE configs[0]
+
+
+def run_reference_cfg1(args):
+    """BASELINE configs[0] on the reference's own CPU code: the conv forward of
+    Convolution<ref::Backend,float> (legacy/include/distconv/ref/backend.hpp:238-365)
+    under two in-process ranks split along H, through oracle/_ref/ref_driver
+    (the reference's headers compiled where they lie).  A step is one forward
+    pass on a bounded sample: N=1 of the configuration's 4 samples."""
+    exe = os.path.join(ROOT, "oracle", "_ref", "ref_driver")
+    base = {"impl": "reference", "metric": "voxels/s per halo+conv3d+BN layer", "unit": "voxels/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic"}
+    if not os.path.exists(exe):
+        print(json.dumps(dict(base, unavailable="oracle/_ref/ref_driver was not built (needs the reference tree)")))
+        return
+    c = CFG1
+    n_sample = 1
+    rng = np.random.default_rng(0)
+    x = rng.uniform(-1, 1, (n_sample, c["C"], c["H"], c["W"])).astype(np.float32)
+    w = rng.normal(0, 0.1, (c["K"], c["C"], c["f"], c["f"])).astype(np.float32)
+    dy = rng.normal(0, 1, (n_sample, c["K"], c["H"], c["W"])).astype(np.float32)
+    times = []
+    with tempfile.TemporaryDirectory() as d:
+        with open(os.path.join(d, "spec.txt"), "w") as f:
+            # nd, shape (W,H,C,N), locale, filter, strides, pad, K
+            f.write(f"4 {c['W']} {c['H']} {c['C']} {n_sample} 1 2 1 1 {c['f']} {c['f']} 1 1 1 {c['K']}\n")
+        x.tofile(os.path.join(d, "x.bin"))
+        w.tofile(os.path.join(d, "w.bin"))
+        dy.tofile(os.path.join(d, "dy.bin"))
+        for i in range(args.warmup + args.steps):
+            out = subprocess.run([exe, "conv", d], capture_output=True, text=True, check=True).stdout.split()
+            t_fwd = float(out[out.index("fwd_s") + 1])
+            if i >= args.warmup:
+                times.append(t_fwd)
+    mean_t = sum(times) / len(times)
+    vox = n_sample * c["H"] * c["W"]
+    value = vox / mean_t
+    sample = (f"conv forward of Convolution<ref::Backend,float> on N={n_sample} of {c['N']} samples, C=16 64x64 -> "
+              "K=16 3x3, 2 in-process ranks split along H (one thread each: the reference's CPU path is scalar); "
+              "halos filled by definition, no BN (the reference has no CPU BN)")
+    print(json.dumps(dict(base, value=value, ms_per_step=mean_t * 1e3,
+                          config={"workload": "BASELINE configs[0]: 2-D conv layer, CPU ref backend, 2 ranks split H",
+                                  "partition": "1x2 (W,H)"},
+                          cpu_baseline={"value": value, "unit": "voxels/s", "cores": 2, "kind": "reference",
+                                        "sample": sample},
+                          e2e={"value": value, "unit": "voxels/s", "h2d_bytes_per_step": 0,
+                               "d2h_bytes_per_step": 0})))
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    if args.config == "cfg1":
+        return run_reference_cfg1(args)
     extent = EXTENT
     sample_d = pick_cpu_sample(extent, target_s=3.0)
     times = []
@@ -174,14 +277,19 @@ def run_reference(args):
     mean_t = sum(times) / len(times)
     vox = sample_d * extent * extent
     value = vox / mean_t
-    sample = f"conv3d fwd + BN fwd on a {sample_d}x{extent}x{extent} D-slab of the 256^3 shard (C=4->K=16), fp64-accumulate port, OpenMP"
+    grid = grid_for(args.gpus, args.partition)
+    sample = (f"conv3d fwd + BN fwd on a {sample_d}x{extent}x{extent} D-slab of the 256^3 shard (C=4->K=16), "
+              f"fp64-accumulate port, OpenMP on {threads} threads")
     line = {
         "impl": "reference", "metric": "voxels/s per halo+conv3d+BN layer", "value": value, "unit": "voxels/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": mean_t * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "BASELINE configs[1]: 3-D conv+BN layer, N=1 C=4 256^3 -> K=16 3x3x3 s1 p1, fwd",
-                   "partition": "D", "note": "the reference's own CPU backend (ref::Backend) is 4-D/stride-1 only "
-                   "and has no BN, so the 5-D workload is timed with the CPU restatement (oracle/)"},
+        "config": {"workload": "BASELINE configs[1]: 3-D conv+BN layer, N=1 C=4 256^3 per GPU -> K=16 3x3x3 s1 p1, "
+                               "halo exchange + conv fwd + BN fwd (global stats)",
+                   "partition": "x".join(map(str, grid)) + " (W,H,D)",
+                   "note": "the reference's own CPU backend (ref::Backend) is 4-D/stride-1 only and has no BN, so "
+                           "the 5-D workload is timed with the CPU restatement (oracle/) on the host cores of rank "
+                           "0's box; one process whatever N is"},
         "cpu_baseline": {"value": value, "unit": "voxels/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "voxels/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -194,6 +302,7 @@ def run_reference(args):
 def run_ours(args):
     import torch
     import torch.distributed as dist
+    import torch.nn.functional as F
 
     import dihydrogen_b200 as dc
     from dihydrogen_b200 import _abi
@@ -233,30 +342,44 @@ def run_ours(args):
     if rank == 0:
         sampler.start()
 
-    geo = layer_geometry(world, locale, local_d=args.local_d)
+    grid = grid_for(world, args.partition)
+    geo = layer_geometry(grid, locale, local_d=args.local_d)
     x, y, z = geo["input"], geo["conv_out"], geo["bn_out"]
-    for t in (x, y, z):
+    fshape = geo["filter_shape"]
+    dy = dc.create_convolution_d_output_tensor(y, fshape, geo["dilations"])
+    dx = dc.create_d_input_tensor(x)
+    dz = dc.Tensor(y.shape, locale, y.dist, y._local_of)
+    with_bwd = not args.no_backward
+    for t in (x, y, z) + ((dy, dx, dz) if with_bwd else ()):
         t.allocate()
     extent = EXTENT
-    local_d = x.local_shape[2]
-    host_x = torch.from_numpy(synth_input_shard(0, x.offset[2], local_d, extent)).pin_memory()
+    lw, lh, ld = x.local_shape[:3]
+    ext_host = synth_extended_shard(0, geo["shape"], x.offset, x.local_shape)
+    host_x = torch.from_numpy(np.ascontiguousarray(ext_host[None, :, 1:-1, 1:-1, 1:-1])).pin_memory()
     host_z = torch.empty(tuple(reversed(z.local_shape)), dtype=torch.float32).pin_memory()
     w = torch.from_numpy(synth_filter(0)).cuda()
     x.owned().copy_(host_x)
+    if with_bwd:
+        gen = torch.Generator(device="cuda")
+        gen.manual_seed(1234 + rank)
+        dz.owned().normal_(generator=gen)
 
     be = dc.BackendDNNLib(locale, options=dc.Options(overlap_halo_exchange=args.overlap), allreduce="peer",
                           allreduce_max_count=4096)
     conv = dc.Convolution(be, 5)
-    conv.setup(x, w, y, None, None, None, geo["pads"], geo["strides"], geo["dilations"])
+    conv.setup(x, w, y, dx if with_bwd else None, None, dy if with_bwd else None, geo["pads"], geo["strides"],
+               geo["dilations"])
     bn = dc.BatchNormalization(be, 5, DECAY, EPS, True)
     stats = torch.zeros(2 * K_OUT, device="cuda")
     mean, var = stats[:K_OUT], stats[K_OUT:]
     rm, rv = torch.zeros(K_OUT, device="cuda"), torch.ones(K_OUT, device="cuda")
     scale, bias = torch.ones(K_OUT, device="cuda"), torch.zeros(K_OUT, device="cuda")
+    ga, gb = torch.zeros(2 * K_OUT, device="cuda"), torch.zeros(2 * K_OUT, device="cuda")
+    dw = torch.zeros_like(w)
     stream = torch.cuda.current_stream()
 
     launches = {"n": 0}
-    partitioned = world > 1
+    n_part = sum(1 for g in grid if g > 1)  # partitioned dimensions
 
     fuse = not args.no_fused_stats
     overlapped = conv.is_overlap_fwd_halo_exchange_enabled()
@@ -267,13 +390,20 @@ def run_ours(args):
         # (falls back to the separate statistics pass if the plan cannot)
         got = conv.forward(1.0, x, w, 0.0, y, statistics=(mean, var) if fuse else None)
         bn.forward(y, mean, var, rm, rv, scale, bias, z, True, statistics_ready=bool(got))
-        # clear_halo (1 per partitioned dim), pack+put and wait+unpack (1 each per
-        # partitioned dim), filter image, conv, statistics (fold of the epilogue's
-        # partials, or the separate pass), all-reduce, finalize, apply
-        # (--overlap: interior + boundary slabs, each with its filter image, and
-        # the statistics as their own pass)
-        launches["n"] += (3 if partitioned else 0) + 6 + extra_launches
+        # per partitioned dim: clear_halo, pack+put, wait+unpack; then filter
+        # image, conv, statistics (fold of the epilogue's partials, or the
+        # separate pass), all-reduce, finalize, apply (--overlap: interior +
+        # boundary slabs, each with its filter image, statistics as their own pass)
+        launches["n"] += 3 * n_part + 6 + extra_launches
         return got
+
+    def bwd_step():
+        # the driver's order (benchmarks/distconv_benchmark.cpp:569-589): BN
+        # backward, backward filter (clears dy's halo, all-reduces dw), halo
+        # exchange of dy, backward data
+        bn.backward(y, dz, mean, var, scale, gb[:K_OUT], gb[K_OUT:], ga[:K_OUT], ga[K_OUT:], dy)
+        conv.backward_filter(1.0, x, dy, 0.0, dw, reduce=True)
+        conv.backward_data(1.0, w, dy, 0.0, dx)
 
     def e2e_step():
         x.owned().copy_(host_x, non_blocking=True)
@@ -286,6 +416,14 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    def max_over_ranks(ms):
+        if world > 1:
+            tt = torch.tensor(ms if isinstance(ms, list) else [ms], device="cuda", dtype=torch.float64)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            out = [float(v) for v in tt.tolist()]
+            return out if isinstance(ms, list) else out[0]
+        return ms
+
     def timed(fn, steps, warmup):
         for _ in range(warmup):
             fn()
@@ -297,15 +435,31 @@ def run_ours(args):
             fn()
         e1.record(stream)
         barrier()
-        ms = e0.elapsed_time(e1)
-        if world > 1:
-            tt = torch.tensor([ms], device="cuda")
-            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-            ms = float(tt.item())
-        return ms / steps
+        return max_over_ranks(e0.elapsed_time(e1)) / steps
+
+    def timed_per_iteration(fn, runs, reskew=2):
+        """The reference driver's protocol (benchmarks/distconv_benchmark.cpp:288-331,
+        benchmark_common.hpp:82-104): per run a device sync and a barrier, untimed
+        passes to re-skew the ranks, then ONE pass between two events; every
+        run's time is the max over ranks."""
+        ms = []
+        for _ in range(runs):
+            barrier()
+            for _ in range(reskew):
+                fn()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            fn()
+            e1.record(stream)
+            torch.cuda.synchronize()
+            ms.append(e0.elapsed_time(e1))
+        ms = max_over_ranks(ms)
+        return {"runs": runs, "mean": statistics.mean(ms), "median": statistics.median(ms), "min": min(ms),
+                "max": max(ms), "note": "per run: sync + barrier, 2 untimed re-skew passes, one pass between events"}
 
     ms_step = timed(step, args.steps, max(args.warmup, 3))
     n_launch = launches["n"]
+    per_iter = timed_per_iteration(step, max(5, min(args.steps, 10)))
     ms_e2e_serial = timed(e2e_step, max(2, min(args.steps, 5)), 2)
 
     def e2e_pipelined(steps):
@@ -316,8 +470,8 @@ def run_ours(args):
         copies its own input in and its own result out inside the timed
         region, pipeline fill and drain included."""
         s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
-        xb = [x.buffer, torch.zeros_like(x.buffer)]
-        zb = [z.buffer, torch.empty_like(z.buffer)]
+        xb = [x._storage, x.new_storage()]
+        zb = [z._storage, z.new_storage(zero=False)]
         hz = [host_z, torch.empty_like(host_z).pin_memory()]
         comp_done, d2h_done = [None, None], [None, None]
         barrier()
@@ -352,18 +506,28 @@ def run_ours(args):
         barrier()
         x.set_view(xb[0])
         z.set_view(zb[0])
-        ms = e0.elapsed_time(e1)
-        if world > 1:
-            tt = torch.tensor([ms], device="cuda")
-            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-            ms = float(tt.item())
-        return ms / steps
+        return max_over_ranks(e0.elapsed_time(e1)) / steps
 
     ms_e2e = e2e_pipelined(max(4, min(args.steps, 8)))
 
-    # per-kernel timing of the forward pass on this rank (rank 0 reports)
-    import ctypes
+    # forward + backward of the layer (forward as above; backward = BN backward,
+    # backward filter with its all-reduce, halo exchange of dy, backward data)
+    fwd_bwd = None
+    if with_bwd:
+        def fb_step():
+            step()
+            bwd_step()
 
+        k_fb = max(3, min(args.steps, 20))
+        ms_fb = timed(fb_step, k_fb, 3)
+        ms_b = timed(bwd_step, k_fb, 1)
+        names = {0: "fp32 CUDA-core", 1: "tcgen05 row", 2: "tcgen05 row (register-fed)", 3: "tcgen05 sweep",
+                 4: "tcgen05 multi-group sweep", 5: "tcgen05 backward filter"}
+        fwd_bwd = {"ms_per_pass": ms_fb, "backward_ms": ms_b, "steps": k_fb,
+                   "kernels": {n: names.get(conv.kernel_variant(i), "?")
+                               for i, n in enumerate(("conv_fwd", "conv_bwd_data", "conv_bwd_filter"))}}
+
+    # per-kernel timing of the forward pass on this rank (rank 0 reports)
     def time_call(fn, reps=10):
         for _ in range(3):
             fn()
@@ -381,21 +545,101 @@ def run_ours(args):
                                             statistics=(mean, var) if fused_ok else None))
     t_stats = time_call(lambda: bn.forward_stage1(y, mean, var, True))
     t_apply = time_call(lambda: bn.forward_stage2(y, mean, var, rm, rv, scale, bias, z, True))
+    t_halo = None
+    if n_part:
+        def halo_only():
+            conv._clear_halos(x, be.stream)
+            conv.forward_exchange_halo(x, be.stream)
+        barrier()
+        t_halo = max_over_ranks(time_call(halo_only))
     clocks = sampler.stop() if rank == 0 else None
-    st = conv.halo_xch_input.status()
-    if st != _abi.OK:
-        raise SystemExit("halo exchange reported " + str(st))
+
+    # ----------------------------------------------------------------------
+    # Correctness of what was timed, on every rank (P ranks == 1 rank is the
+    # reference's own criterion, legacy/tests/dnn_backend/test_cudnn_util.sh.in:387-425):
+    #  * the halo-extended input shard equals the regenerated global tensor bit
+    #    for bit (faces, edges and corners; zeros outside the global volume),
+    #  * conv output blocks at the low and the high corner of the shard (they
+    #    touch every partitioned face) against an fp64 convolution of the
+    #    regenerated input,
+    #  * the BN mean / variance against fp64 sums of y, all-reduced with NCCL,
+    #  * BN output blocks against the fp64 formula with those statistics,
+    #  * no kernel gave up on a bounded wait.
+    # ----------------------------------------------------------------------
+    x.owned().copy_(host_x)
+    got = step()
+    torch.cuda.synchronize()
+    check = {}
+    exp = torch.from_numpy(ext_host).cuda()  # (C, D+2, H+2, W+2)
+    sl = tuple(slice(0, None) if g > 1 else slice(1, -1) for g in reversed(grid))  # D, H, W
+    check["halo_bit_exact"] = bool(torch.equal(x.buffer[0], exp[(slice(None),) + sl]))
+    w64 = w.double()
+    B = 8
+    conv_err = bn_err = 0.0
+    for corner in (0, 1):
+        lo = [0 if corner == 0 else e - B for e in (ld, lh, lw)]  # D, H, W
+        xin = exp[:, lo[0]:lo[0] + B + 2, lo[1]:lo[1] + B + 2, lo[2]:lo[2] + B + 2].double()
+        ref = F.conv3d(xin[None], w64)[0]
+        blk = (slice(None), slice(lo[0], lo[0] + B), slice(lo[1], lo[1] + B), slice(lo[2], lo[2] + B))
+        got_y = y.owned()[0][blk].double()
+        rms = float(ref.pow(2).mean().sqrt())
+        conv_err = max(conv_err, float(((got_y - ref).abs() / (ref.abs() + rms)).max()))
+        zref = (got_y - mean.double()[:, None, None, None]) * torch.rsqrt(var.double() + EPS)[:, None, None, None]
+        zref = zref * scale.double()[:, None, None, None] + bias.double()[:, None, None, None]
+        got_z = z.owned()[0][blk].double()
+        rmsz = float(zref.pow(2).mean().sqrt())
+        bn_err = max(bn_err, float(((got_z - zref).abs() / (zref.abs() + rmsz)).max()))
+    sums = torch.zeros(2 * K_OUT, device="cuda", dtype=torch.float64)
+    for k in range(K_OUT):
+        yk = y.owned()[0, k].double()
+        sums[k] = yk.sum()
+        sums[K_OUT + k] = (yk * yk).sum()
+        del yk
+    if world > 1:
+        dist.all_reduce(sums)
+    n_glob = float(np.prod(geo["shape"][:3]))
+    m64 = sums[:K_OUT] / n_glob
+    v64 = (sums[K_OUT:] / n_glob - m64 * m64) * (n_glob / (n_glob - 1.0))
+
+    def rel(a, b):
+        return float(((a.double() - b).abs() / (b.abs() + b.pow(2).mean().sqrt())).max())
+
+    stats_err = max(rel(mean, m64), rel(var, v64))
+    statuses = [conv.halo_xch_input.status(), be.allreducer.status(),
+                int(_abi.lib().dcb_conv_plan_status(conv._plan_fwd, None))]
+    if with_bwd:
+        statuses += [conv.halo_xch_d_output.status(), int(_abi.lib().dcb_conv_plan_status(conv._plan_bwd, None))]
+    check.update(conv_max_rel_err=conv_err, bn_stats_max_rel_err=stats_err, bn_out_max_rel_err=bn_err,
+                 tolerance=1e-5, kernel_status_ok=all(s == _abi.OK for s in statuses))
+    ok = (check["halo_bit_exact"] and conv_err <= 1e-5 and stats_err <= 1e-5 and bn_err <= 1e-5
+          and check["kernel_status_ok"])
+    if world > 1:
+        agg = torch.tensor([1.0 if ok else 0.0, -conv_err, -stats_err, -bn_err,
+                            1.0 if check["halo_bit_exact"] else 0.0], device="cuda", dtype=torch.float64)
+        dist.all_reduce(agg, op=dist.ReduceOp.MIN)
+        a = agg.tolist()
+        ok = a[0] > 0.5
+        check.update(conv_max_rel_err=-a[1], bn_stats_max_rel_err=-a[2], bn_out_max_rel_err=-a[3],
+                     halo_bit_exact=a[4] > 0.5)
+    check["ok"] = bool(ok)
+    check["what"] = ("every rank: halo-extended input shard == regenerated global tensor bit for bit; 8^3 conv and "
+                     "BN output blocks at the low and high corner of the shard vs fp64; BN mean/var vs fp64 sums of "
+                     "y all-reduced with NCCL; no bounded wait expired")
+    if not ok:
+        sys.stderr.write(f"rank {rank}: parity check FAILED: {json.dumps(check)} statuses {statuses}\n")
 
     if rank != 0:
         if world > 1:
             dist.barrier()
             dist.destroy_process_group()
+        if not ok:
+            raise SystemExit(3)
         return
 
     peaks, peak_kind = measured_peaks()
-    vox_local = local_d * extent * extent
+    vox_local = ld * lh * lw
     vox_total = vox_local * world
-    in_el = C_IN * (local_d + (2 if partitioned else 0)) * extent * extent
+    in_el = C_IN * int(np.prod(x.get_local_real_shape()[:3]))
     out_el = K_OUT * vox_local
     conv_bytes = 4 * (in_el + K_OUT * C_IN * 27 + out_el)
     kernels = {
@@ -404,23 +648,28 @@ def run_ours(args):
     }
     if not fused_ok:
         kernels["bn_stats"] = {"ms": t_stats, "bytes": 4 * out_el}
-    # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the
-    # ncu capture of a 64 x 256 x 256 shard, which scales with the D extent:
-    # bytes per shard voxel times this launch's voxels.
-    ncu_vox = 64 * 256 * 256
-    traffic_per_voxel = {"conv_fwd": (69.34e6 + 208.91e6) / ncu_vox, "bn_stats": (268.46e6 + 4.00e6) / ncu_vox,
-                         "bn_finalize_apply": (268.45e6 + 222.17e6) / ncu_vox}
+    # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum): the
+    # conv kernel from a one-pass ncu capture of one full 256^3 launch, the BN
+    # kernels from the capture of a 64 x 256 x 256 shard (their traffic is
+    # proportional to the D extent); per shard voxel, times this launch's voxels.
+    traffic_per_voxel = {"conv_fwd": CONV_TRAFFIC_BYTES_PER_VOXEL,
+                         "bn_stats": (268.46e6 + 4.00e6) / (64 * 256 * 256),
+                         "bn_finalize_apply": (268.45e6 + 222.17e6) / (64 * 256 * 256)}
     dom = max(kernels, key=lambda k: kernels[k]["ms"])
     ach = kernels[dom]["bytes"] / (kernels[dom]["ms"] * 1e-3) / 1e9
     roofline = {"kernel": dom, "bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                 "frac": ach / peaks["hbm_gbs"], "peak_source": peak_kind, "traffic": traffic_per_voxel[dom] * vox_local,
-                "traffic_source": "ncu capture of a 64x256x256 shard scaled by voxels (profiles/)",
+                "traffic_source": CONV_TRAFFIC_SOURCE if dom == "conv_fwd" else
+                "ncu capture of a 64x256x256 shard scaled by voxels (profiles/)",
                 "kernels_ms": {k: round(v["ms"], 4) for k, v in kernels.items()},
                 "kernels_gbs": {k: round(v["bytes"] / (v["ms"] * 1e-3) / 1e9, 1) for k, v in kernels.items()},
                 "conv_tflops": kernels["conv_fwd"]["flops"] / (t_conv * 1e-3) / 1e12,
                 "conv_kernel": "tcgen05" if conv.kernel_kind(0) == 1 else "fp32-simt",
+                "conv_kernel_variant": conv.kernel_variant(0),
                 "bn_statistics": "from the conv epilogue" if fused_ok else "separate pass",
                 "bn_stats_separate_pass_ms": round(t_stats, 4)}
+    if t_halo is not None:
+        roofline["halo_exchange_ms"] = round(t_halo, 4)
 
     cpu = None
     if world == 1 and not args.skip_cpu:
@@ -431,6 +680,7 @@ def run_ours(args):
                          f"{t_cpu:.2f} s, fp64-accumulate CPU restatement (the reference's ref::Backend is "
                          "4-D only and has no BN)"}
 
+    part = "x".join(map(str, grid)) + " (W,H,D)"
     line = {
         "metric": "voxels/s per halo+conv3d+BN layer", "value": vox_total / (ms_step * 1e-3), "unit": "voxels/s",
         "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
@@ -438,25 +688,43 @@ def run_ours(args):
         "config": {"workload": "BASELINE configs[1]: 3-D conv+BN layer, N=1 C=4 256^3 per GPU -> K=16 3x3x3 s1 p1, "
                                "halo exchange + conv fwd + BN fwd (global stats)"
                                + ("" if args.local_d is None else f" [REDUCED local D={args.local_d}: profiling only]"),
-                   "partition": f"D over {world} GPU(s), halo width 1", "global_volume": geo["shape"][:3],
+                   "partition": part, "locale_shape": geo["locale_shape"], "global_volume": geo["shape"][:3],
+                   "halo_width": 1, "row_pitch_floats": x.get_pitch(),
                    "overlap_halo_exchange": bool(overlapped),
                    "l2": "inputs larger than L2 (268 MB in, 1 GiB conv out per GPU)",
                    "allreduce": "peer-memory kernel, 2C floats"},
+        "protocol": {"ms_per_step": "mean of K back-to-back passes between two events, max over ranks",
+                     "per_iteration_ms": per_iter},
         "e2e": {"value": vox_total / (ms_e2e * 1e-3), "unit": "voxels/s", "ms_per_step": ms_e2e,
                 "ms_per_step_unpipelined": ms_e2e_serial,
                 "note": "pinned host -> device input copy, layer pass, device -> pinned host result copy every step; "
-                        "copies of neighbouring steps overlap on two copy streams (double-buffered)",
+                        "copies of neighbouring steps overlap on two copy streams (double-buffered)"
+                        + ("; with N > 1 ranks on one host the figure is bound by the host's shared PCIe / memory "
+                           "system (1.34 GB of copies per rank per step), not by the GPUs" if world > 1 else ""),
                 "h2d_bytes_per_step": int(host_x.numel() * 4), "d2h_bytes_per_step": int(host_z.numel() * 4)},
         "gpu_launches": n_launch,
         "roofline": roofline,
+        "parity_check": check,
+        "verified": bool(ok),
         "clocks": clocks,
     }
+    if fwd_bwd is not None:
+        fwd_bwd["voxels_per_s"] = vox_total / (fwd_bwd["ms_per_pass"] * 1e-3)
+        line["fwd_bwd"] = fwd_bwd
     if cpu is not None:
         line["cpu_baseline"] = cpu
     print(json.dumps(line))
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    if not ok:
+        raise SystemExit(3)
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one conv launch per shard
+# voxel, and where the figure comes from (profiles/).
+CONV_TRAFFIC_BYTES_PER_VOXEL = (69.34e6 + 208.91e6) / (64 * 256 * 256)
+CONV_TRAFFIC_SOURCE = "ncu capture of a 64x256x256 shard scaled by voxels (profiles/)"
 
 
 def main():
@@ -465,8 +733,14 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--partition", default="auto", choices=["auto", "d"],
+                    help="auto: the weak-scaling ladder D / D x H / 2 x 2 x 2 at 2 / 4 / 8 GPUs; d: split D only")
+    ap.add_argument("--config", default="cfg2", choices=["cfg2", "cfg1"],
+                    help="cfg2 = BASELINE configs[1] (the metric's workload); cfg1 (--impl reference only) = "
+                         "BASELINE configs[0] on the reference's own ref::Backend through oracle/_ref/ref_driver")
     ap.add_argument("--no-fused-stats", action="store_true",
                     help="run the BN statistics as their own pass instead of taking them from the conv epilogue")
+    ap.add_argument("--no-backward", action="store_true", help="skip the forward+backward block (fwd_bwd)")
     ap.add_argument("--overlap", action="store_true",
                     help="Options.overlap_halo_exchange: interior convolution while the halo is in flight, then "
                          "the boundary slabs (off by default, as in the reference)")
@@ -477,6 +751,8 @@ def main():
     if args.impl == "reference":
         run_reference(args)
     else:
+        if args.config != "cfg2":
+            raise SystemExit("--config cfg1 is a reference-arm option")
         run_ours(args)
 
 

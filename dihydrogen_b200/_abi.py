@@ -34,6 +34,7 @@ class TensorDesc(ctypes.Structure):
         ("local_shape", c_int64 * DCB_MAX_DIMS),
         ("real_shape", c_int64 * DCB_MAX_DIMS),
         ("overlap", c_int32 * DCB_MAX_DIMS),
+        ("pitch", c_int64),
     ]
 
 
@@ -118,6 +119,7 @@ _SIGS = {
     "dcb_conv_bwd_data": (c_int32, [_P, c_double, _P, _P, c_double, _P, _P]),
     "dcb_conv_bwd_filter": (c_int32, [_P, c_double, _P, _P, c_double, _P, _P]),
     "dcb_conv_plan_kernel_kind": (c_int32, [_P, c_int32]),
+    "dcb_conv_plan_kernel_variant": (c_int32, [_P, c_int32]),
     "dcb_conv_plan_status": (c_int32, [_P, _P]),
     "dcb_bias_fwd": (c_int32, [c_double, _P, c_double, POINTER(NdDesc), _P, _P]),
     "dcb_bias_bwd": (c_int32, [c_double, POINTER(NdDesc), _P, c_double, _P, _P]),

@@ -325,14 +325,24 @@ int32_t dcb_allreduce_sum(dcb_comm* c, void* data, int64_t count, void* stream)
                                           ncclSum, c->nccl, as_stream(stream)));
         return DCB_OK;
     }
-    int32_t st = peer_ready(c, count);
+    int32_t st = peer_ready(c, 0);
     if (st != DCB_OK)
         return st;
-    const uint32_t epoch = ++c->epoch;
-    peer_allreduce_kernel<<<1, 256, 0, as_stream(stream)>>>(
-        c->ptrs, c->nranks, c->rank, c->max_count, static_cast<float*>(data),
-        (int) count, epoch, wait_budget_ns());
-    DCB_LAUNCH_CHECK();
+    // A vector longer than the slots (a filter gradient, K*C*taps floats) goes
+    // through in max_count-sized pieces, one epoch each.  The slots are double
+    // buffered by epoch parity, and a rank can only be one epoch ahead of the
+    // slowest (its pull of epoch e needs everybody's push of epoch e), so
+    // back-to-back epochs never overwrite a slot that is still being read.
+    float* p = static_cast<float*>(data);
+    for (int64_t done = 0; done < count; done += c->max_count)
+    {
+        const int64_t n = count - done < c->max_count ? count - done : c->max_count;
+        const uint32_t epoch = ++c->epoch;
+        peer_allreduce_kernel<<<1, 256, 0, as_stream(stream)>>>(
+            c->ptrs, c->nranks, c->rank, c->max_count, p + done, (int) n, epoch,
+            wait_budget_ns());
+        DCB_LAUNCH_CHECK();
+    }
     return DCB_OK;
 }
 

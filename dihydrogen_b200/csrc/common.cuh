@@ -52,6 +52,12 @@ void set_last_error(const std::string& msg);
         }                                                                      \
     } while (0)
 
+// Row pitch of a shard in elements (0 in the descriptor means dense rows).
+inline long long row_pitch(const dcb_tensor_desc& d)
+{
+    return d.pitch > 0 ? (long long) d.pitch : (long long) d.real_shape[0];
+}
+
 inline cudaStream_t as_stream(void* s)
 {
     return reinterpret_cast<cudaStream_t>(s);

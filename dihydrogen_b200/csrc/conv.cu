@@ -186,6 +186,13 @@ int32_t dcb_conv_plan_kernel_kind(const dcb_conv_plan* p, int32_t which)
     return p->kind[which];
 }
 
+int32_t dcb_conv_plan_kernel_variant(const dcb_conv_plan* p, int32_t which)
+{
+    if (!p || which < 0 || which > 2)
+        return -1;
+    return p->kind[which] == 1 ? tc_variant(p->tc, which) : 0;
+}
+
 int32_t dcb_conv_fwd(dcb_conv_plan* p, double alpha, const void* x,
                      const void* w, double beta, void* y, void* stream)
 {

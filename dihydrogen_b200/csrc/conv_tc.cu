@@ -635,6 +635,21 @@ bool tc_supports(const TcPlan* p, int which)
     return p->has_wg;
 }
 
+int tc_variant(const TcPlan* p, int which)
+{
+    if (!p || which < 0 || which > 2)
+        return 0;
+    if (which == 2)
+        return p->has_wg ? 5 : 0;
+    if (!p->has[which])
+        return 0;
+    if (p->has_mg[which])
+        return 4;
+    if (p->has_sw[which])
+        return 3;
+    return p->g[which].use_tma ? 1 : 2;
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);

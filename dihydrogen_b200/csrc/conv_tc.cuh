@@ -17,6 +17,10 @@ int32_t tc_plan_create(const ConvGeom& fwd, const ConvGeom& bwd,
 void tc_plan_destroy(TcPlan* p);
 // which: 0 forward, 1 backward data, 2 backward filter
 bool tc_supports(const TcPlan* p, int which);
+// The kernel the plan prefers for that pass, as dcb_conv_plan_kernel_variant
+// numbers them (1 row kernel fed by bulk copies, 2 row kernel whose converters
+// fetch their own rows, 3 sweep, 4 multi-group sweep, 5 backward filter; 0 none).
+int tc_variant(const TcPlan* p, int which);
 // slot 0 runs the forward geometry, slot 1 the backward-data one.
 int32_t tc_conv_fwd(TcPlan* p, int slot, float alpha, const float* x,
                     const float* w, float beta, float* y, cudaStream_t stream);

@@ -243,9 +243,13 @@ static bool slab_geom(const dcb_tensor_desc& d, int dim, int side, int width,
 {
     if (dim < 0 || dim >= d.ndims || width <= 0)
         return false;
+    // Rows may be padded (desc.pitch): a W face is then `width` cells per row at
+    // stride pitch; H and D faces are whole rows and planes, padding cells
+    // included (nobody reads them).
+    const long long pitch = row_pitch(d);
     long long below = 1, above = 1;
     for (int e = 0; e < dim; ++e)
-        below *= d.real_shape[e];
+        below *= e == 0 ? pitch : d.real_shape[e];
     for (int e = dim + 1; e < d.ndims; ++e)
         above *= d.real_shape[e];
     const long long n = d.real_shape[dim];
@@ -259,7 +263,7 @@ static bool slab_geom(const dcb_tensor_desc& d, int dim, int side, int width,
         return false;
     g->runs = above;
     g->len = (long long) width * below;
-    g->stride = n * below;
+    g->stride = (dim == 0 ? pitch : n) * below;
     g->start = start * below;
     return true;
 }
@@ -346,6 +350,7 @@ static int32_t check_desc(const dcb_tensor_desc* d)
         if (i >= d->ndims - 2)
             DCB_REQUIRE(d->overlap[i] == 0, "no overlap on C and N");
     }
+    DCB_REQUIRE(d->pitch == 0 || d->pitch >= d->real_shape[0], "row pitch shorter than a row");
     return DCB_OK;
 }
 
@@ -428,7 +433,9 @@ int32_t dcb_halo_plan_create(const dcb_tensor_desc* desc, const int32_t* peers,
         for (int d = 0; d < p->nsd; ++d)
             for (int s = 0; s < 2; ++s)
             {
-                p->slab_off[par][d][s] = off;
+                // 0 marks a side without a neighbour: no slab, and a peer that
+                // tries to connect to it is refused
+                p->slab_off[par][d][s] = p->peers[d][s] < 0 ? 0 : off;
                 if (p->peers[d][s] < 0)
                     continue;
                 SlabGeom g;
@@ -493,6 +500,25 @@ int32_t dcb_halo_plan_connect(dcb_halo_plan* p, const void* blobs,
                             + (size_t) peer * DCB_HALO_BLOB_BYTES,
                         sizeof(b));
             DCB_REQUIRE((int) b.rank == peer, "blob order does not match ranks");
+            // What I will store must fit into the slab the peer set aside for
+            // its opposite side: a peer that sees no neighbour there (an empty
+            // shard, an inconsistent peers[] table) reserved nothing, and the
+            // stores would leave its window.
+            SlabGeom sg;
+            DCB_REQUIRE(slab_geom(p->desc, d, s, p->desc.overlap[d], false, &sg), "shard narrower than its halo");
+            const uint64_t need = (uint64_t) sg.runs * (uint64_t) sg.len * sizeof(float);
+            for (int par = 0; par < 2; ++par)
+            {
+                const uint64_t off = b.slab_off[par][d][1 - s];
+                uint64_t next = b.win.bytes;
+                for (int par2 = 0; par2 < 2; ++par2)
+                    for (int d2 = 0; d2 < DCB_MAX_SPATIAL; ++d2)
+                        for (int s2 = 0; s2 < 2; ++s2)
+                            if (b.slab_off[par2][d2][s2] > off && b.slab_off[par2][d2][s2] < next)
+                                next = b.slab_off[par2][d2][s2];
+                DCB_REQUIRE(off >= kHeaderBytes && off + need <= next,
+                            "the peer's receive slab does not match this rank's face");
+            }
             int32_t st = p->peer_map[d][s].open(b.win, p->win.device);
             if (st != DCB_OK)
                 return st;
@@ -728,7 +754,7 @@ static int32_t pack_or_unpack_slab(const dcb_tensor_desc* desc, void* tensor,
     {
         long long below = 1;
         for (int e = 0; e < dim; ++e)
-            below *= d.real_shape[e];
+            below *= e == 0 ? row_pitch(d) : d.real_shape[e];
         const int ov = desc->overlap[dim];
         // Outer slabs hug the owned cells; inner slabs hug the boundary.
         long long shift = 0;

@@ -235,6 +235,7 @@ int32_t check_shard(const dcb_tensor_desc* d, const Box& mine, int nd)
         // a rank that is not the root of a replicated dimension passes an empty box
         DCB_REQUIRE(vol == 0 || mine.ext[i] == d->local_shape[i], "this rank's box does not match its shard");
     }
+    DCB_REQUIRE(d->pitch == 0 || d->pitch >= d->real_shape[0], "row pitch shorter than a row");
     return DCB_OK;
 }
 
@@ -245,7 +246,7 @@ void real_strides(const dcb_tensor_desc& d, long long* s)
     for (int i = 0; i < DCB_MAX_DIMS; ++i)
     {
         s[i] = acc;
-        acc *= i < d.ndims ? d.real_shape[i] : 1;
+        acc *= i < d.ndims ? (i == 0 ? row_pitch(d) : d.real_shape[i]) : 1;
     }
 }
 } // namespace

@@ -189,7 +189,8 @@ class Tensor:
     """
 
     def __init__(self, shape, locale: Locale, dist: Distribution,
-                 local_shape_of: Optional[Callable[[Sequence[int]], Sequence[int]]] = None):
+                 local_shape_of: Optional[Callable[[Sequence[int]], Sequence[int]]] = None,
+                 pitch_align: Optional[int] = None):
         self.shape = list(shape)
         self.locale = locale
         self.dist = dist.copy()
@@ -208,7 +209,21 @@ class Tensor:
                     idx[d] = j * per
                     off += self._local_of(idx)[d]
             self.offset.append(off)
+        # Row pitch (tensor.hpp:184-192 get_pitch; the reference pads rows with
+        # CUDAPitchedAllocator, memory_cuda.hpp:68-104).  A shard with halo
+        # cells along W has rows of local + 2 * overlap cells, rarely a multiple
+        # of 16 bytes; such rows are padded to PITCH_ALIGN floats so that the
+        # bulk-copy fed tensor-core kernels can address them.  Shards without a
+        # W halo stay dense.  pitch_align=1 forces dense rows.
+        if pitch_align is None:
+            pitch_align = self.PITCH_ALIGN if self.dist.overlap[0] > 0 else 1
+        self.pitch_align = max(1, int(pitch_align))
+        real_w = self.local_shape[0] + 2 * self.dist.overlap[0]
+        self.pitch = -(-real_w // self.pitch_align) * self.pitch_align
         self.buffer: Optional[torch.Tensor] = None
+        self._storage: Optional[torch.Tensor] = None
+
+    PITCH_ALIGN = 4  # floats: 16 bytes
 
     def _local_of(self, proc_idx):
         if self._local_shape_of is not None:
@@ -287,13 +302,43 @@ class Tensor:
     def np_real_shape(self):
         return tuple(reversed(self.get_local_real_shape()))
 
+    def get_pitch(self):
+        """Elements between consecutive rows of the buffer (tensor.hpp:184-192)."""
+        return self.pitch
+
+    def get_local_pitched_shape(self):
+        """The halo-extended shape with the row padded to the pitch
+        (tensor.hpp:483-485)."""
+        r = self.get_local_real_shape()
+        r[0] = self.pitch
+        return r
+
+    def new_storage(self, device="cuda", zero=True) -> torch.Tensor:
+        """A device array laid out like this shard's buffer (rows padded to the
+        pitch); pass it to set_view."""
+        shp = tuple(reversed(self.get_local_pitched_shape()))
+        return (torch.zeros if zero else torch.empty)(shp, dtype=torch.float32, device=device)
+
     def allocate(self, device="cuda"):
-        self.buffer = torch.zeros(self.np_real_shape(), dtype=torch.float32, device=device)
+        self.set_view(self.new_storage(device))
         return 0
 
     def set_view(self, buf: torch.Tensor):
-        assert tuple(buf.shape) == self.np_real_shape() and buf.is_contiguous()
-        self.buffer = buf
+        """Use ``buf`` as the shard's memory (tensor.hpp:604-623 View): either
+        a contiguous array of the pitched shape (new_storage) or, for a dense
+        shard, of the halo-extended shape.  ``buffer`` is the halo-extended
+        shard without the row padding, a strided view when rows are padded."""
+        real_w = self.local_shape[0] + 2 * self.dist.overlap[0]
+        if tuple(buf.shape) == self.np_real_shape() and buf.stride(-1) == 1 and (
+                buf.dim() < 2 or buf.stride(-2) == self.pitch):
+            # already the un-padded view of a pitched array (or dense)
+            self._storage = buf
+            self.buffer = buf
+            return
+        assert tuple(buf.shape) == tuple(reversed(self.get_local_pitched_shape())) and buf.is_contiguous(), \
+            "set_view wants an array of the pitched shape"
+        self._storage = buf
+        self.buffer = buf[..., :real_w] if self.pitch != real_w else buf
 
     def get_buffer(self) -> int:
         return self.buffer.data_ptr()
@@ -301,9 +346,9 @@ class Tensor:
     def get_strides(self):
         """Element strides of the halo-extended buffer, reference order."""
         st, acc = [], 1
-        for r in self.get_local_real_shape():
+        for i, r in enumerate(self.get_local_real_shape()):
             st.append(acc)
-            acc *= r
+            acc *= self.pitch if i == 0 else r
         return st
 
     def get_local_offset(self, idx, idx_include_halo=False):
@@ -319,7 +364,7 @@ class Tensor:
         return self.buffer[sl]
 
     def zero(self, stream=None):
-        self.buffer.zero_()
+        self._storage.zero_()
 
     def desc(self) -> TensorDesc:
         d = TensorDesc()
@@ -329,6 +374,7 @@ class Tensor:
             d.local_shape[i] = self.local_shape[i]
             d.real_shape[i] = real[i]
             d.overlap[i] = self.dist.overlap[i]
+        d.pitch = self.pitch
         return d
 
     def clear_halo(self, dim, stream=None):
@@ -1004,6 +1050,13 @@ class Convolution:
     def kernel_kind(self, which: int) -> int:
         plan = self._plan_fwd if which == 0 else self._plan_bwd
         return _abi.lib().dcb_conv_plan_kernel_kind(plan, which)
+
+    def kernel_variant(self, which: int) -> int:
+        """dcb_conv_plan_kernel_variant: 0 fp32 CUDA-core, 1 / 2 tcgen05 row
+        kernel (bulk-copy fed / register fed), 3 sweep, 4 multi-group sweep,
+        5 tcgen05 backward filter."""
+        plan = self._plan_fwd if which == 0 else self._plan_bwd
+        return _abi.lib().dcb_conv_plan_kernel_variant(plan, which)
 
     # -- halo --
     def _clear_halos(self, t: Tensor, stream):

@@ -53,6 +53,15 @@ int32_t dcb_version(void);
  * the distribution's overlap (legacy/include/distconv/tensor/tensor.hpp:171-178,
  * tensor_mpi.hpp:489-498).  The buffer a descriptor describes starts at the
  * first cell of the halo-extended shard (Tensor::get_buffer()).
+ *
+ * `pitch` is the distance in elements between consecutive rows (index 1) of
+ * the buffer, Tensor::get_pitch() of a shard allocated with the reference's
+ * CUDAPitchedAllocator (tensor/memory_cuda.hpp:68-104, tensor.hpp:184-192,
+ * 483-485): 0 or real_shape[0] for a dense shard, larger when rows are padded.
+ * A W-partitioned shard with halo 1 has 258-float rows; padded to 260 its
+ * rows start on 16-byte boundaries, which the bulk-copy (TMA) fed tensor-core
+ * kernels need.  The padding cells belong to nobody: kernels may copy them
+ * along with a face but never interpret them.
  * ------------------------------------------------------------------------ */
 typedef struct dcb_tensor_desc
 {
@@ -61,6 +70,7 @@ typedef struct dcb_tensor_desc
     int64_t local_shape[DCB_MAX_DIMS];
     int64_t real_shape[DCB_MAX_DIMS];
     int32_t overlap[DCB_MAX_DIMS];
+    int64_t pitch; /* row pitch in elements; 0 = real_shape[0] */
 } dcb_tensor_desc;
 
 #define DCB_F32 0
@@ -221,6 +231,14 @@ int32_t dcb_conv_plan_status(dcb_conv_plan* plan, void* stream);
 /* Which kernel family the plan resolved to for (0 fwd, 1 bwd-data,
  * 2 bwd-filter): 0 = fp32 CUDA-core, 1 = tcgen05 tensor-core. */
 int32_t dcb_conv_plan_kernel_kind(const dcb_conv_plan* plan, int32_t which);
+/* The kernel the plan prefers for that pass (cuDNN reports its choice as an
+ * algorithm enum, util_cudnn.hpp:37-60): 0 fp32 CUDA-core; tcgen05 kernels:
+ * 1 row kernel fed by bulk tensor copies, 2 row kernel whose converter warps
+ * fetch their own rows (strides not multiples of 16 bytes), 3 sweep kernel
+ * (filters with depth), 4 multi-group sweep kernel, 5 backward-filter kernel.
+ * A call whose base pointers are not 16-byte aligned may still step down
+ * (3/4 -> 2, 5 -> 0). */
+int32_t dcb_conv_plan_kernel_variant(const dcb_conv_plan* plan, int32_t which);
 /* y[n,k,...] = alpha*bias[k] + beta*y (cudnnAddTensor,
  * dnn_backend_cudnn.cpp.inc:386) and its gradient dbias[k] = alpha*sum dy +
  * beta*dbias (cudnnConvolutionBackwardBias, :397). */
@@ -417,7 +435,9 @@ int32_t dcb_comm_create_peer(int32_t rank, int32_t nranks, int32_t max_count,
 int32_t dcb_comm_export(dcb_comm* comm, void* blob);
 int32_t dcb_comm_connect(dcb_comm* comm, const void* blobs, int32_t nranks);
 int32_t dcb_comm_destroy(dcb_comm* comm);
-/* In-place sum all-reduce of `count` floats. */
+/* In-place sum all-reduce of `count` floats.  The peer flavour takes vectors
+ * longer than max_count in max_count-sized pieces, one kernel each (the
+ * push / pull halves below do not: they are limited to max_count). */
 int32_t dcb_allreduce_sum(dcb_comm* comm, void* data, int64_t count,
                           void* stream);
 /* Peer flavour only, for single-device emulation of several ranks: the two

@@ -192,8 +192,19 @@ private:
     Allgather m_ag;
 };
 
+// Allocator tags (tensor/memory_cuda.hpp:28-104).  They decide the row pitch of
+// a shard.  CUDAAllocator keeps rows dense unless the shard carries halo cells
+// along W: such rows (local + 2 * overlap floats) are padded to 16 bytes, which
+// the bulk-copy fed tensor-core kernels need and costs at most three floats
+// per row.  CUDAPitchedAllocator pads the rows of every shard to 128 bytes, as
+// cudaMallocPitch-style allocation does in the reference.
 struct CUDAAllocator
 {
+    static index_t pitch(index_t row, bool w_halo) { return w_halo ? (row + 3) / 4 * 4 : row; }
+};
+struct CUDAPitchedAllocator
+{
+    static index_t pitch(index_t row, bool) { return (row + 31) / 32 * 32; }
 };
 
 inline index_t split_extent(index_t total, index_t parts, index_t index)
@@ -233,6 +244,7 @@ public:
         m_offset = IndexVector(nd, 0);
         for (int d = 0; d < nd; ++d)
             m_offset[d] = get_dimension_rank_offset(d, (int) m_proc_idx[d]);
+        m_pitch = Allocator::pitch(m_local_shape[0] + 2 * m_dist.get_overlap(0), m_dist.get_overlap(0) > 0);
     }
 
     Shape local_of(const IndexVector& proc_idx) const
@@ -292,9 +304,18 @@ public:
     }
 
     // memory
+    // elements between consecutive rows (tensor.hpp:184-192)
+    index_t get_pitch() const { return m_pitch; }
+    Shape get_local_pitched_shape() const
+    {
+        Shape r = get_local_real_shape();
+        r[0] = m_pitch;
+        return r;
+    }
+    index_t get_local_pitched_size() const { return get_local_pitched_shape().get_size(); }
     int allocate()
     {
-        const size_t bytes = (size_t) get_local_real_shape().get_size() * sizeof(DataType);
+        const size_t bytes = (size_t) get_local_pitched_size() * sizeof(DataType);
         void* p = nullptr;
         if (cudaMalloc(&p, bytes ? bytes : 16) != cudaSuccess)
             return -1;
@@ -303,14 +324,15 @@ public:
         m_buf = static_cast<DataType*>(p);
         return 0;
     }
-    void set_view(void* raw) { m_mem.reset(); m_buf = static_cast<DataType*>(raw); } // never frees
+    // Alias caller memory laid out with this shard's pitch (tensor.hpp:604-623); never frees.
+    void set_view(void* raw) { m_mem.reset(); m_buf = static_cast<DataType*>(raw); }
     DataType* get_buffer() { return m_buf; }
     const DataType* get_const_buffer() const { return m_buf; }
     Shape get_strides() const
     {
         Shape st(m_shape.size(), 1);
         index_t acc = 1;
-        const Shape real = get_local_real_shape();
+        const Shape real = get_local_pitched_shape();
         for (int i = 0; i < get_num_dims(); ++i)
         {
             st[i] = acc;
@@ -329,7 +351,7 @@ public:
     DataType* get_base_ptr() { return m_buf + get_local_offset(IndexVector(m_shape.size(), 0)); }
     void zero(cudaStream_t s = 0)
     {
-        cudaMemsetAsync(m_buf, 0, (size_t) get_local_real_shape().get_size() * sizeof(DataType), s);
+        cudaMemsetAsync(m_buf, 0, (size_t) get_local_pitched_size() * sizeof(DataType), s);
     }
     void clear_halo(int dim, cudaStream_t s = 0)
     {
@@ -352,6 +374,7 @@ public:
             d.real_shape[i] = real[i];
             d.overlap[i] = m_dist.get_overlap(i);
         }
+        d.pitch = m_pitch;
         return d;
     }
     // owned cells extended by lo / hi halo cells per spatial dimension
@@ -400,6 +423,7 @@ private:
     IndexVector m_proc_idx, m_split_idx, m_offset;
     std::shared_ptr<void> m_mem;
     DataType* m_buf = nullptr;
+    index_t m_pitch = 0;
 };
 
 } // namespace tensor
@@ -957,6 +981,11 @@ public:
     int kernel_kind(int which) const
     {
         return dcb_conv_plan_kernel_kind(which == 0 ? m_plan_fwd : m_plan_bwd, which);
+    }
+    // 0 fp32 CUDA-core, 1 / 2 tcgen05 row kernel, 3 sweep, 4 multi-group sweep, 5 tcgen05 backward filter
+    int kernel_variant(int which) const
+    {
+        return dcb_conv_plan_kernel_variant(which == 0 ? m_plan_fwd : m_plan_bwd, which);
     }
     tensor::HaloExchange& input_halo_exchange() { return *m_halo_xch_input; }
     tensor::HaloExchange& d_output_halo_exchange() { return *m_halo_xch_d_output; }

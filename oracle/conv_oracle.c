@@ -60,6 +60,19 @@ int oracle_num_threads(void)
 #endif
 }
 
+/* Thread count for the loops below.  Launchers such as torch.distributed.run
+ * export OMP_NUM_THREADS=1; a CPU baseline timed under them sets its count
+ * explicitly. */
+void oracle_set_num_threads(int n)
+{
+#ifdef _OPENMP
+    if (n > 0)
+        omp_set_num_threads(n);
+#else
+    (void) n;
+#endif
+}
+
 static inline size_t off5(const oracle_tdesc* t, int64_t n, int64_t c,
                           int64_t d, int64_t h, int64_t w)
 {

@@ -82,6 +82,21 @@ def num_threads() -> int:
     return int(_lib().oracle_num_threads())
 
 
+def set_num_threads(n: int) -> int:
+    """OpenMP thread count of the C loops (a launcher may have exported
+    OMP_NUM_THREADS=1); returns the count now in force."""
+    _lib().oracle_set_num_threads(ctypes.c_int(int(n)))
+    return num_threads()
+
+
+def host_cores() -> int:
+    """Cores this process may run on."""
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
 def _as5(a: np.ndarray) -> np.ndarray:
     """View a 4-D (N,C,H,W) array as 5-D (N,C,1,H,W)."""
     assert a.dtype == np.float32

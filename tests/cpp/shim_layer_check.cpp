@@ -169,7 +169,7 @@ void reference(Global& g)
 // copies between a shard (halo-extended, device) and the global host array
 void scatter(TensorF& t, const std::vector<float>& g, int Cc)
 {
-    const auto real = t.get_local_real_shape();
+    const auto real = t.get_local_pitched_shape(); // rows carry padding up to the pitch
     const auto& loc = t.get_local_shape();
     const auto& off = t.get_global_index();
     const auto& ov = t.get_overlap();
@@ -191,7 +191,7 @@ void scatter(TensorF& t, const std::vector<float>& g, int Cc)
 
 double gather_err(TensorF& t, const std::vector<float>& g, int Cc)
 {
-    const auto real = t.get_local_real_shape();
+    const auto real = t.get_local_pitched_shape(); // rows carry padding up to the pitch
     const auto& loc = t.get_local_shape();
     const auto& off = t.get_global_index();
     const auto& ov = t.get_overlap();

@@ -2,7 +2,7 @@
 
 Run where the DiHydrogen tree is available (the REFERENCE variable of oracle/Makefile):
 
-    make -C oracle ref && python tests/golden/make_golden.py
+    make -C oracle ref REFERENCE=<DiHydrogen tree> && python tests/golden/make_golden.py
 
 It drives ``oracle/_ref/ref_driver`` -- the reference's own header-only CPU
 code compiled where it lies (tensor model, get_halo_sizes, output-shape
@@ -88,7 +88,7 @@ def run_conv(N, C, H, W, K, f, locale, seed):
 
 def main():
     if not os.path.exists(DRIVER):
-        sys.exit("build oracle/_ref/ref_driver first: make -C oracle ref")
+        sys.exit("build oracle/_ref/ref_driver first: make -C oracle ref REFERENCE=<DiHydrogen tree>")
     for name, case in GEOM_CASES.items():
         txt = "# " + " ".join(map(str, case)) + "\n" + run_geom(*case)
         with open(os.path.join(HERE, f"geom_{name}.txt"), "w") as f:

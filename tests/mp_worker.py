@@ -57,65 +57,107 @@ def main():
         assert ar.status() == _abi.OK
         dist.barrier()
 
-    # ---- conv + BN layer split along D, forward and backward ----
-    rng = np.random.default_rng(7)
-    shape, locale, K, f = [32, 24, 8 * n, 4, 1], [1, 1, n, 1, 1], 16, [3, 3, 3]
-    C = shape[-2]
-    gx = rng.normal(0, 1, tuple(reversed(shape))).astype(np.float32)
-    w = rng.normal(0, np.sqrt(2.0 / (C * 27)), (K, C, 3, 3, 3)).astype(np.float32)
-    gdz = rng.normal(0, 1, (1, K, 8 * n, 24, 32)).astype(np.float32)
-    scale = rng.uniform(0.5, 1.5, K).astype(np.float32)
-    bias = rng.normal(0, 0.5, K).astype(np.float32)
-    be = dc.BackendDNNLib(loc)
-    ones3 = [1, 1, 1]
-    x = dc.create_input_tensor(shape, locale, f, ones3, ones3, loc)
-    y = dc.create_convolution_output_tensor(x, f + [C, K], ones3, ones3, ones3)
-    dy = dc.create_convolution_d_output_tensor(y, f + [C, K], ones3)
-    dx = dc.create_d_input_tensor(x)
-    z = dc.Tensor(y.shape, loc, y.dist, y._local_of)
-    dz = dc.Tensor(y.shape, loc, y.dist, y._local_of)
-    emu.scatter_owned(x, gx)
-    emu.scatter_owned(dz, gdz)
-    for t in (y, dy, dx, z):
-        t.allocate()
-    wt = torch.from_numpy(w).cuda()
-    conv = dc.Convolution(be, 5)
-    conv.setup(x, wt, y, dx, None, dy, ones3, ones3, ones3)
-    bn = dc.BatchNormalization(be, 5, 0.9, 1e-5, True)
-    st = torch.zeros(2 * K, device="cuda")
-    rm, rv = torch.zeros(K, device="cuda"), torch.ones(K, device="cuda")
-    sc, bi = torch.from_numpy(scale).cuda(), torch.from_numpy(bias).cuda()
-    conv.forward(1.0, x, wt, 0.0, y)
-    bn.forward(y, st[:K], st[K:], rm, rv, sc, bi, z, True)
-    ga, gb = torch.zeros(2 * K, device="cuda"), torch.zeros(2 * K, device="cuda")
-    bn.backward(y, dz, st[:K], st[K:], sc, gb[:K], gb[K:], ga[:K], ga[K:], dy)
-    dw = torch.zeros_like(wt)
-    conv.backward_filter(1.0, x, dy, 0.0, dw)
-    conv.backward_data(1.0, wt, dy, 0.0, dx)
-    torch.cuda.synchronize()
-    assert conv.halo_xch_input.status() == _abi.OK and conv.halo_xch_d_output.status() == _abi.OK
+    # ---- all-reduce of a vector longer than the slots: max_count-sized pieces ----
+    ar = dc.Allreduce(loc, "peer", 256)
+    cnt = 3 * 256 + 5
+    for rep in range(3):
+        v = torch.arange(cnt, dtype=torch.float32, device="cuda") + r + rep
+        ar.allreduce(v.data_ptr(), v.numel())
+        torch.cuda.synchronize()
+        expect = n * (np.arange(cnt, dtype=np.float32) + rep) + n * (n - 1) / 2
+        assert np.array_equal(v.cpu().numpy(), expect), ("chunked", rep)
+    assert ar.status() == _abi.OK
+    dist.barrier()
 
+    # ---- conv + BN layer, forward and backward, on several grids ----
+    rng = np.random.default_rng(7)
+    be = dc.BackendDNNLib(loc)
+
+    def gather_global(t, shape_np):
+        """The global tensor from every rank's owned cells (host side)."""
+        parts = [None] * n
+        dist.all_gather_object(parts, (list(t.offset), list(t.local_shape), t.owned().cpu().numpy()))
+        g = np.zeros(shape_np, np.float32)
+        for off, loc_shape, a in parts:
+            g[tuple(slice(o, o + l) for o, l in reversed(list(zip(off, loc_shape))))] = a
+        return g
+
+    def layer_case(shape, locale, K, f, what):
+        """Halo exchange + conv + BN forward and backward with this process
+        grid; every stage against the single-domain oracle fed with the GPUs'
+        own previous stage, at 1e-5 (P ranks == 1 rank,
+        legacy/tests/dnn_backend/test_cudnn_util.sh.in:387-425)."""
+        nd, nsd = len(shape), len(shape) - 2
+        C = shape[-2]
+        ones, pads = [1] * nsd, [(ff - 1) // 2 for ff in f]
+        gx = rng.normal(0, 1, tuple(reversed(shape))).astype(np.float32)
+        w = rng.normal(0, np.sqrt(2.0 / (C * np.prod(f))), (K, C, *reversed(f))).astype(np.float32)
+        scale = rng.uniform(0.5, 1.5, K).astype(np.float32)
+        bias = rng.normal(0, 0.5, K).astype(np.float32)
+        x = dc.create_input_tensor(shape, locale, f, ones, ones, loc)
+        y = dc.create_convolution_output_tensor(x, list(f) + [C, K], ones, pads, ones)
+        dy = dc.create_convolution_d_output_tensor(y, list(f) + [C, K], ones)
+        dx = dc.create_d_input_tensor(x)
+        z = dc.Tensor(y.shape, loc, y.dist, y._local_of)
+        dz = dc.Tensor(y.shape, loc, y.dist, y._local_of)
+        osh = tuple(reversed(y.shape))
+        gdz = rng.normal(0, 1, osh).astype(np.float32)
+        emu.scatter_owned(x, gx)
+        emu.scatter_owned(dz, gdz)
+        for t in (y, dy, dx, z):
+            t.allocate()
+        x.buffer.fill_(float("nan"))  # the halo must come from the exchange
+        emu.scatter_owned_into(x, gx)
+        dy.buffer.fill_(float("nan"))
+        wt = torch.from_numpy(w).cuda()
+        conv = dc.Convolution(be, nd)
+        conv.setup(x, wt, y, dx, None, dy, pads, ones, ones)
+        bn = dc.BatchNormalization(be, nd, 0.9, 1e-5, True)
+        st = torch.zeros(2 * K, device="cuda")
+        rm, rv = torch.zeros(K, device="cuda"), torch.ones(K, device="cuda")
+        sc, bi = torch.from_numpy(scale).cuda(), torch.from_numpy(bias).cuda()
+        ga, gb = torch.zeros(2 * K, device="cuda"), torch.zeros(2 * K, device="cuda")
+        dw = torch.zeros_like(wt)
+        for rep in range(2):  # twice: the exchange's double buffers and epochs come round
+            conv.forward(1.0, x, wt, 0.0, y)
+            bn.forward(y, st[:K], st[K:], rm, rv, sc, bi, z, True)
+            bn.backward(y, dz, st[:K], st[K:], sc, gb[:K], gb[K:], ga[:K], ga[K:], dy)
+            conv.backward_filter(1.0, x, dy, 0.0, dw)
+            conv.backward_data(1.0, wt, dy, 0.0, dx)
+        torch.cuda.synchronize()
+        assert conv.halo_xch_input.status() == _abi.OK and conv.halo_xch_d_output.status() == _abi.OK
+        assert be.allreducer.status() == _abi.OK
+        assert _abi.lib().dcb_conv_plan_status(conv._plan_fwd, None) == _abi.OK
+        assert _abi.lib().dcb_conv_plan_status(conv._plan_bwd, None) == _abi.OK
+        # the halo-extended input shard, bit for bit (edges and corners included)
+        sh = O.Shard(shape, locale, list(x.dist.overlap), r)
+        assert np.array_equal(x.buffer.cpu().numpy(), O.fill_by_definition(sh, gx)), what + ": halo contents"
+        bwd = dict(gdz=gdz, dscale=gb[:K].cpu().numpy(), dbias=gb[K:].cpu().numpy(), dmean=ga[:K].cpu().numpy(),
+                   dvar=ga[K:].cpu().numpy(), dy=gather_global(dy, osh), dw=dw.cpu().numpy(),
+                   dx=gather_global(dx, gx.shape))
+        emu.check_stages(K, gx, w, scale, bias, list(reversed(pads)), ones, gather_global(y, osh),
+                         st[:K].cpu().numpy(), st[K:].cpu().numpy(), gather_global(z, osh), bwd, 1e-5, what + ": ")
+        dist.barrier()
+        return x, y, wt, conv, gx, w
+
+    # a D split; a W split (rows padded to the pitch); the grid the benchmark's weak-scaling
+    # ladder uses at this rank count (4 -> D x H, 8 -> 2 x 2 x 2); with 8 ranks also the
+    # 2 x 4 grid of the 2-D large-image layer
+    grid = {1: [1, 1, 1], 2: [1, 1, 2], 4: [1, 2, 2], 8: [2, 2, 2]}.get(n, [1, 1, n])
+    ext = [24 * g if i == 0 else (10 * g if i == 1 else 6 * g) for i, g in enumerate(grid)]
+    x, y, wt, conv, gx, w = layer_case([32, 24, 8 * n, 4, 1], [1, 1, n, 1, 1], 16, [3, 3, 3], "D split")
+    if n > 1:
+        layer_case([20 * n, 12, 10, 4, 1], [n, 1, 1, 1, 1], 16, [3, 3, 3], "W split")
+    if n in (4, 8):
+        layer_case(ext + [4, 1], grid + [1, 1], 16, [3, 3, 3], "grid " + "x".join(map(str, grid)))
+    if n == 8:
+        layer_case([32 * 4, 24 * 2, 8, 2], [4, 2, 1, 1], 8, [5, 5], "2-D layer, 2 x 4 grid")
+    ones3, f, C, K = [1, 1, 1], [3, 3, 3], 4, 16
     y_ref = O.conv_fwd(gx, w, ones3, ones3)
-    s, q = O.bn_sums(y_ref)
-    nps = y_ref.size // K
-    m, v, _, _ = O.bn_sums_to_statistics(s, q, nps, 0.9, np.zeros(K), np.ones(K))
-    z_ref = O.bn_normalize(y_ref, m, v, scale, bias, 1e-5)
-    dsc, dbi, dme, dva = O.bn_backprop1(y_ref, gdz, m, v, scale, 1e-5)
-    dy_ref = O.bn_backprop2(y_ref, gdz, m, v, scale, np.float32(dme), np.float32(dva), 1e-5, nps)
-    dw_ref = O.conv_bwd_filter(gx, dy_ref, (3, 3, 3), ones3, ones3)
-    dx_ref = np.zeros_like(gx)
-    O.conv_bwd_data(w, dy_ref, dx_ref, ones3, ones3)
 
     def own(t, g):
         sl = tuple(slice(o, o + l) for o, l in reversed(list(zip(t.offset, t.local_shape))))
         return g[sl]
-
-    emu.assert_close(y.owned().cpu().numpy(), own(y, y_ref), 1e-5, "y")
-    emu.assert_close(z.owned().cpu().numpy(), own(z, z_ref), 3e-5, "z")
-    emu.assert_close(dy.owned().cpu().numpy(), own(dy, dy_ref), 5e-5, "bn dx")
-    emu.assert_close(dw.cpu().numpy(), dw_ref, 5e-5, "dw")
-    emu.assert_close(dx.owned().cpu().numpy(), own(dx, dx_ref), 5e-5, "dx")
-    dist.barrier()
 
     # ---- the same forward pass with the interior running while the halo is in flight ----
     be_ov = dc.BackendDNNLib(loc, options=dc.Options(overlap_halo_exchange=True))

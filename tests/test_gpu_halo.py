@@ -203,3 +203,20 @@ def test_peer_allreduce_emulated():
         for b, t in zip(bes, ts):
             assert b.allreducer.status() == _abi.OK
             assert np.array_equal(t.cpu().numpy(), expect)
+
+
+def test_peer_allreduce_takes_vectors_longer_than_its_slots():
+    """A filter gradient (K*C*taps floats) can exceed the communicator's
+    max_count; dcb_allreduce_sum then goes through in max_count-sized pieces,
+    one epoch each.  One rank here (kernels of several ranks that wait for one
+    another must not share a GPU); tests/mp_worker.py runs it across processes."""
+    be = emu.make_backends(1, max_count=256)[0]
+    count = 3 * 256 + 5
+    for rep in range(3):
+        t = torch.arange(count, dtype=torch.float32, device="cuda") * (rep + 1)
+        be.allreducer.allreduce(t.data_ptr(), t.numel())
+        torch.cuda.synchronize()
+        assert be.allreducer.status() == _abi.OK
+        assert np.array_equal(t.cpu().numpy(), np.arange(count, dtype=np.float32) * (rep + 1))
+    with pytest.raises(_abi.DcbError):  # the emulation halves keep the limit
+        be.allreducer.push(t.data_ptr(), count)

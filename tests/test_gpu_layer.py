@@ -92,6 +92,7 @@ class Layer:
             dy.buffer.fill_(float("nan"))
             bn.backward_stage2(y, dz, st[:K], st[K:], self.scale, a[:K], a[K:], dy)
         self.dscale, self.dbias = gb[0][:K], gb[0][K:]
+        self.dmean, self.dvar = ga[0][:K], ga[0][K:]
         # backward filter first (it zero-clears dy's halo), then exchange, then
         # backward data -- the driver's order (distconv_benchmark.cpp:569-589)
         self.dw = [torch.zeros_like(self.w) for _ in self.bes]
@@ -119,6 +120,25 @@ def oracle_layer(gx, w, scale, bias, gdz, pads, strides):
     return dict(y=y, z=z, mean=m, var=v, dscale=dsc, dbias=dbi, dy=dy, dw=dw, dx=dx)
 
 
+def check_layer_stages(L, gx, w, scale, bias, gdz, pads, strides, tol=1e-5, what=""):
+    """emu.check_stages on the tensors of an emulated-rank Layer: every stage
+    against the oracle fed with the GPU's own previous stage, at 1e-5."""
+    K = L.K
+    osh = tuple(reversed(L.out_shape))
+    for st in L.stats:
+        assert torch.equal(st, L.stats[0])  # identical bits on every rank
+    bwd = None
+    if gdz is not None:
+        for dw in L.dw:
+            assert torch.equal(dw, L.dw[0])  # all ranks hold the same reduced gradient
+        bwd = dict(gdz=gdz, dscale=L.dscale.cpu().numpy(), dbias=L.dbias.cpu().numpy(),
+                   dmean=L.dmean.cpu().numpy(), dvar=L.dvar.cpu().numpy(), dy=emu.gather_owned(L.dy, osh),
+                   dw=L.dw[0].cpu().numpy(), dx=emu.gather_owned(L.dx, gx.shape))
+    emu.check_stages(K, gx, w, scale, bias, pads, strides, emu.gather_owned(L.y, osh),
+                     L.stats[0][:K].cpu().numpy(), L.stats[0][K:].cpu().numpy(), emu.gather_owned(L.z, osh),
+                     bwd, tol, what)
+
+
 LAYERS = [
     # shape (W..N), locale, K, filter (W..), strides, name
     ([32, 32, 8, 2], [1, 2, 1, 1], 8, [3, 3], [1, 1]),                 # BASELINE config 1 geometry, reduced
@@ -144,19 +164,37 @@ def test_layer_matches_single_domain_oracle(shape, locale, K, f, strides, mode):
     L.forward(gx, w, scale, bias)
     L.backward(gdz)
     pads = [(ff - 1) // 2 for ff in reversed(f)]
-    ref = oracle_layer(gx, w, scale, bias, gdz, pads, list(reversed(strides)))
-    osh = tuple(reversed(L.out_shape))
-    emu.assert_close(emu.gather_owned(L.y, osh), ref["y"], 1e-5, "conv output")
-    emu.assert_close(L.stats[0][:K].cpu().numpy(), ref["mean"], 2e-5, "mean")
-    emu.assert_close(L.stats[0][K:].cpu().numpy(), ref["var"], 3e-5, "var")
-    emu.assert_close(emu.gather_owned(L.z, osh), ref["z"], 3e-5, "bn output")
-    emu.assert_close(L.dscale.cpu().numpy(), ref["dscale"], 5e-5, "dscale")
-    emu.assert_close(L.dbias.cpu().numpy(), ref["dbias"], 5e-5, "dbias")
-    emu.assert_close(emu.gather_owned(L.dy, osh), ref["dy"], 5e-5, "bn dx")
-    for dw in L.dw:
-        assert torch.equal(dw, L.dw[0])  # all ranks hold the same reduced gradient
-    emu.assert_close(L.dw[0].cpu().numpy(), ref["dw"], 5e-5, "filter gradient")
-    emu.assert_close(emu.gather_owned(L.dx, gx.shape), ref["dx"], 5e-5, "input gradient")
+    check_layer_stages(L, gx, w, scale, bias, gdz, pads, list(reversed(strides)))
+
+
+def test_w_partitioned_shards_of_the_2x2x2_grid_take_the_tensor_core_kernels():
+    """BASELINE configs[2] layer 1 on its own 2 x 2 x 2 grid, reduced extents:
+    every shard is partitioned along W, so its rows are local + 2 halo cells
+    = 134 floats (2 mod 4) and only the padded row pitch lets the bulk-copy
+    fed tcgen05 kernels take them.  All three passes must run on tensor cores
+    (forward: sweep kernel, backward data: sweep / multi-group sweep, backward
+    filter: the tcgen05 kernel) and meet the 1e-5 contract stage by stage."""
+    shape, locale, K, f, strides = [264, 24, 12, 4, 1], [2, 2, 2, 1, 1], 16, [3, 3, 3], [1, 1, 1]
+    rng = np.random.default_rng(17)
+    gx = rng.uniform(0, 1, tuple(reversed(shape))).astype(np.float32)
+    w = rng.normal(0, np.sqrt(2.0 / (4 * 27)), (K, 4, 3, 3, 3)).astype(np.float32)
+    scale = rng.uniform(0.5, 1.5, K).astype(np.float32)
+    bias = rng.normal(0, 0.5, K).astype(np.float32)
+    L = Layer(shape, locale, K, f, strides, pad=1)
+    for x, dy in zip(L.x, L.dy):
+        assert x.get_local_real_shape()[0] == 134 and x.get_pitch() == 136
+        assert dy.get_pitch() == 136
+    for c in L.convs:
+        assert [c.kernel_kind(i) for i in range(3)] == [1, 1, 1]
+        assert c.kernel_variant(0) == 3 and c.kernel_variant(1) in (3, 4) and c.kernel_variant(2) == 5
+    gdz = rng.normal(0, 1, tuple(reversed(L.out_shape))).astype(np.float32)
+    L.forward(gx, w, scale, bias, fused_stats=True)
+    assert all(L.fused), "the sweep kernel delivers the statistics on W-partitioned shards too"
+    L.backward(gdz)
+    for c in L.convs:
+        assert _abi.lib().dcb_conv_plan_status(c._plan_fwd, None) == _abi.OK
+        assert _abi.lib().dcb_conv_plan_status(c._plan_bwd, None) == _abi.OK
+    check_layer_stages(L, gx, w, scale, bias, gdz, [1, 1, 1], [1, 1, 1])
 
 
 def test_config1_against_reference_backend_outputs():
@@ -201,14 +239,7 @@ def test_layer_with_statistics_from_the_conv_epilogue(shape, locale):
     L = Layer(shape, locale, K, f, strides, pad=1)
     L.forward(gx, w, scale, bias, fused_stats=True)
     assert all(L.fused), "the sweep kernel should have produced the statistics"
-    y = O.conv_fwd(gx, w, [1] * 3, [1] * 3)
-    s, q = O.bn_sums(y)
-    m, v, _, _ = O.bn_sums_to_statistics(s, q, y.size // K, 0.9, np.zeros(K), np.ones(K))
-    z = O.bn_normalize(y, m, v, scale, bias, 1e-5)
-    osh = tuple(reversed(L.out_shape))
-    emu.assert_close(L.stats[0][:K].cpu().numpy(), m, 2e-5, "mean")
-    emu.assert_close(L.stats[0][K:].cpu().numpy(), v, 3e-5, "var")
-    emu.assert_close(emu.gather_owned(L.z, osh), z, 3e-5, "bn output")
+    check_layer_stages(L, gx, w, scale, bias, None, [1] * 3, [1] * 3)
 
 
 @pytest.mark.parametrize("shape,locale,K,f", [
@@ -281,15 +312,14 @@ def test_config3_two_layer_chain_forward_and_backward():
         dz1.allocate()
         lr.backward(z, dx2, slope, dz1)
     L1.backward(None)
-    # the same chain on one domain
+    # the same chain on one domain, stage by stage: every stage is checked
+    # against the oracle fed with what the GPU produced for the stage before
     p, one, two = [1, 1, 1], [1, 1, 1], [2, 2, 2]
-    r1 = oracle_layer(gx, w1, s1, b1, np.zeros((1, 16, 16, 16, 16), np.float32), p, one)
-    a1 = _leaky(r1["z"], slope)
-    r2 = oracle_layer(a1, w2, s2, b2, gdz, p, two)
-    dz1 = np.where(r1["z"] > 0, r2["dx"], slope * r2["dx"]).astype(np.float32)
-    r1b = oracle_layer(gx, w1, s1, b1, dz1, p, one)
-    emu.assert_close(emu.gather_owned(L2.z, r2["z"].shape), r2["z"], 5e-5, "layer 2 output")
-    emu.assert_close(L2.dw[0].cpu().numpy(), r2["dw"], 1e-4, "layer 2 filter gradient")
-    emu.assert_close(emu.gather_owned(L2.dx, a1.shape), r2["dx"], 1e-4, "layer 2 input gradient")
-    emu.assert_close(L1.dw[0].cpu().numpy(), r1b["dw"], 2e-4, "layer 1 filter gradient")
-    emu.assert_close(emu.gather_owned(L1.dx, gx.shape), r1b["dx"], 2e-4, "layer 1 input gradient")
+    z1 = emu.gather_owned(L1.z, (1, 16, 16, 16, 16))
+    a1 = emu.gather_owned(L2.x, (1, 16, 16, 16, 16))
+    assert np.array_equal(a1, _leaky(z1, slope))  # the activation is exact
+    check_layer_stages(L2, a1, w2, s2, b2, gdz, p, two, what="layer 2 ")
+    dx2 = emu.gather_owned(L2.dx, a1.shape)
+    dz1 = emu.gather_owned(L1.dz, a1.shape)
+    assert np.array_equal(dz1, np.where(z1 > 0, dx2, np.float32(slope) * dx2).astype(np.float32))
+    check_layer_stages(L1, gx, w1, s1, b1, dz1, p, one, what="layer 1 ")

@@ -108,8 +108,19 @@ peers = [hx.find_peer_rank(1, s) for s in (0, 1)]
 assert peers == ([-1, 1] if loc.rank == 0 else [0, -1]), peers
 # weak-scaling shard layout used by bench.py
 import bench
-g = bench.layer_geometry(2, loc, extent=16)
+assert bench.grid_for(2, "auto") == [1, 1, 2] and bench.grid_for(4, "auto") == [1, 2, 2]
+assert bench.grid_for(8, "auto") == [2, 2, 2] and bench.grid_for(8, "d") == [1, 1, 8]
+g = bench.layer_geometry(bench.grid_for(2, "auto"), loc, extent=16)
 assert g["shape"][2] == 32 and g["input"].get_local_shape()[2] == 16
+# a W-partitioned shard pads its rows to 16 bytes (the pitch), others stay dense
+tw = dc.create_input_tensor([36, 8, 4, 2], [2, 1, 1, 1], [3, 3], [1, 1], [1, 1], loc)
+assert tw.get_local_real_shape()[0] == 20 and tw.get_pitch() == 20
+tw = dc.create_input_tensor([34, 8, 4, 2], [2, 1, 1, 1], [3, 3], [1, 1], [1, 1], loc)
+assert tw.get_local_real_shape()[0] == 19 and tw.get_pitch() == 20 and tw.get_strides() == [1, 20, 160, 640]
+assert tw.get_local_pitched_shape() == [20, 8, 4, 2] and tw.desc().pitch == 20
+tw.allocate(device="cpu")
+assert tuple(tw.buffer.shape) == (2, 4, 8, 19) and tw.buffer.stride() == (640, 160, 20, 1)
+assert t.get_pitch() == 64 and g["input"].get_pitch() == 16
 # dump_tensor: rank 0 writes the global tensor, no halos, dimension 0 fastest
 import numpy as np
 g5 = np.arange(6 * 8 * 4 * 2, dtype=np.float32).reshape(2, 4, 8, 6)  # N, C, H, W
