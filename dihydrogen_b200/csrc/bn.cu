@@ -9,6 +9,8 @@
 // to scratch, the last block of a channel (ticket) folds the partials in index
 // order, so results are reproducible run to run.  fp32 atomics, as the
 // reference uses (batchnorm.cu:39-132), are not.
+#include <atomic>
+
 #include "common.cuh"
 
 namespace dcb
@@ -817,7 +819,9 @@ static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_TICKET_
 
 // Device address of the array on each device, resolved on first use.  In host
 // code the symbol itself is only a handle, never a pointer a kernel may use.
-static void* g_noalloc_addr[NOALLOC_MAX_DEVICES] = {};
+// Host threads may race on an entry: they would all store the same address,
+// so relaxed atomics are enough.
+static std::atomic<void*> g_noalloc_addr[NOALLOC_MAX_DEVICES] = {};
 } // namespace
 
 extern "C" int32_t dcb_bn_stats_noalloc(const dcb_nd_desc* xd, const void* x, void* sums, void* sqsums,
@@ -842,14 +846,14 @@ extern "C" int32_t dcb_bn_stats_noalloc(const dcb_nd_desc* xd, const void* x, vo
         set_last_error("dcb_bn_stats_noalloc: device ordinal beyond 63");
         return DCB_UNSUPPORTED;
     }
-    if (g_noalloc_addr[dev] == nullptr)
+    void* addr = g_noalloc_addr[dev].load(std::memory_order_relaxed);
+    if (addr == nullptr)
     {
         // once per device, with that device current
-        void* p = nullptr;
-        DCB_CUDA_TRY(cudaGetSymbolAddress(&p, g_noalloc_scratch));
-        g_noalloc_addr[dev] = p;
+        DCB_CUDA_TRY(cudaGetSymbolAddress(&addr, g_noalloc_scratch));
+        g_noalloc_addr[dev].store(addr, std::memory_order_relaxed);
     }
-    unsigned char* base = static_cast<unsigned char*>(g_noalloc_addr[dev]);
+    unsigned char* base = static_cast<unsigned char*>(addr);
     unsigned* tickets = reinterpret_cast<unsigned*>(base);
     double* partial = reinterpret_cast<double*>(base + NOALLOC_TICKET_BYTES);
     if (mv.ug.upc == 0)

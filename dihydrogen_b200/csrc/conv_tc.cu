@@ -763,6 +763,12 @@ static bool sw_make_y_map(const SwGeom& g, float* y, CUtensorMap* map)
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn || (reinterpret_cast<uintptr_t>(y) & 15) != 0)
         return false;
+    // A bulk tensor store was seen to clip a row at the next 16-byte boundary,
+    // not at the tensor's extent: a row of 11 outputs inside a wider allocation
+    // (a column range of a shard) had its 12th cell overwritten.  Rows whose
+    // extent is not a multiple of 4 floats take the register stores.
+    if (g.out[2] % 4 != 0)
+        return false;
     const cuuint64_t dims[5] = {(cuuint64_t) g.out[2], (cuuint64_t) g.out[1], (cuuint64_t) g.out[0], (cuuint64_t) g.k,
                                 (cuuint64_t) g.n};
     const long long s1 = g.out[1] > 1 ? g.ys[1] : g.out[2];
@@ -846,6 +852,12 @@ static bool mg_make_y_map(const SwGeom& g, float* y, CUtensorMap* map)
 {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn || (reinterpret_cast<uintptr_t>(y) & 15) != 0)
+        return false;
+    // A bulk tensor store was seen to clip a row at the next 16-byte boundary,
+    // not at the tensor's extent: a row of 11 outputs inside a wider allocation
+    // (a column range of a shard) had its 12th cell overwritten.  Rows whose
+    // extent is not a multiple of 4 floats take the register stores.
+    if (g.out[2] % 4 != 0)
         return false;
     const cuuint64_t dims[5] = {(cuuint64_t) g.out[2], (cuuint64_t) g.out[1], (cuuint64_t) g.out[0], (cuuint64_t) g.k,
                                 (cuuint64_t) g.n};

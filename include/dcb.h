@@ -271,8 +271,9 @@ int32_t dcb_bn_stats(dcb_bn_plan* plan, const void* x, void* sums,
  * (DCB_UNSUPPORTED beyond).  The first call on each device looks up the
  * array's device address; make that call outside any stream capture.  All
  * calls share the one array, so two calls whose kernels may overlap on the
- * same GPU (different streams) race: serialise them.  Results equal those of
- * dcb_bn_stats. */
+ * same GPU (different streams) race: serialise them.  The looked-up address is
+ * kept per device ordinal for the life of the process: it does not survive a
+ * cudaDeviceReset.  Results equal those of dcb_bn_stats. */
 int32_t dcb_bn_stats_noalloc(const dcb_nd_desc* xd, const void* x, void* sums,
                              void* sqsums, void* stream);
 /* In place sums -> mean, sqsums -> unbiased variance, update running stats

@@ -341,3 +341,50 @@ def test_forward_with_statistics_full_shard():
             pad += [1 - (s.start - l), 1 - (h - s.stop)]
         ref = torch.nn.functional.conv3d(torch.nn.functional.pad(xb, pad), w.double())
         emu.assert_close(y[:, :, sl[0], sl[1], sl[2]].cpu().numpy(), ref.cpu().numpy(), TOL, "y block")
+
+
+@pytest.mark.parametrize("W,pad", [(30, 1), (33, 1), (130, 1), (30, 0), (35, 0)])
+def test_rows_padded_to_a_pitch_with_odd_extents(W, pad):
+    """x, y (and dy, dx) live in allocations whose rows are padded to a pitch
+    of 4 floats while the row EXTENT is not a multiple of 4: the bulk-copy fed
+    kernels take them (strides are 16-byte multiples), so a row's last cells,
+    the zero padding beyond them and the stores at the row's end are exactly
+    what an off-by-a-granule tensor map would get wrong.  The padding cells
+    are poisoned with NaN on the way in and must be untouched on the way out."""
+    rng = np.random.default_rng(W)
+    N, C, K, D, H = 1, 4, 16, 6, 9
+    Wo = W + 2 * pad - 2
+    Do, Ho = D + 2 * pad - 2, H + 2 * pad - 2
+    x = rng.normal(size=(N, C, D, H, W)).astype(np.float32)
+    w = rng.normal(0, 0.2, (K, C, 3, 3, 3)).astype(np.float32)
+    dy = rng.normal(size=(N, K, Do, Ho, Wo)).astype(np.float32)
+
+    def pitched(a):
+        p = -(-a.shape[-1] // 4) * 4
+        st = torch.full(a.shape[:-1] + (p,), float("nan"), device="cuda")
+        v = st[..., :a.shape[-1]]
+        v.copy_(torch.from_numpy(a))
+        return st, v
+
+    xs, xv = pitched(x)
+    ys, yv = pitched(np.zeros(dy.shape, np.float32))
+    dys, dyv = pitched(dy)
+    dxs, dxv = pitched(np.zeros(x.shape, np.float32))
+    wt = torch.from_numpy(w).cuda()
+    dw = torch.zeros_like(wt)
+    p = Plan(xv, wt, yv, [pad] * 3, [1] * 3, [1] * 3, _abi.MATH_FP32)
+    assert [_abi.lib().dcb_conv_plan_kernel_kind(p.p, i) for i in range(3)] == [1, 1, 1]
+    p.fwd(1.0, xv, wt, 0.0, yv)
+    p.bwd_data(1.0, wt, dyv, 0.0, dxv)
+    p.bwd_filter(1.0, xv, dyv, 0.0, dw)
+    torch.cuda.synchronize()
+    assert _abi.lib().dcb_conv_plan_status(p.p, None) == _abi.OK
+    pads = [pad] * 3
+    emu.assert_close(yv.cpu().numpy(), O.conv_fwd(x, w, pads, [1] * 3), TOL, "y")
+    dx_ref = np.zeros_like(x)
+    O.conv_bwd_data(w, dy, dx_ref, pads, [1] * 3)
+    emu.assert_close(dxv.cpu().numpy(), dx_ref, TOL, "dx")
+    emu.assert_close(dw.cpu().numpy(), O.conv_bwd_filter(x, dy, (3, 3, 3), pads, [1] * 3), TOL, "dw")
+    for st, ext in ((ys, Wo), (dxs, W)):
+        if st.shape[-1] > ext:
+            assert bool(torch.isnan(st[..., ext:]).all()), "a store went past the end of a row"

@@ -201,3 +201,95 @@ def test_pooling_oracle_against_torch(shape, window, pads, strides, mode):
     np.testing.assert_allclose(O.pool_fwd(x, window, pads, strides, mode), y.detach().numpy(), rtol=0, atol=1e-6)
     np.testing.assert_allclose(O.pool_bwd(x, dy.numpy(), window, pads, strides, mode), xt.grad.numpy(), rtol=0,
                                atol=2e-6)
+
+
+# --------------------------------------------------------------------------
+# convolution and batch-norm: the restatement against an independent
+# implementation (torch on the CPU, in fp64, gradients by autograd) for the
+# branches the reference's own CPU backend cannot pin: 5-D tensors, strides,
+# dilations, no padding.  What cuDNN computes for the reference at these
+# shapes is the published cross-correlation torch implements too.
+# --------------------------------------------------------------------------
+@pytest.mark.parametrize("shape,K,f,pads,strides,dil", [
+    ((2, 3, 7, 8, 9), 4, (3, 3, 3), (1, 1, 1), (1, 1, 1), (1, 1, 1)),   # 5-D
+    ((1, 4, 9, 10, 12), 5, (3, 3, 3), (1, 1, 1), (2, 2, 2), (1, 1, 1)), # 5-D, stride 2 (configs[2] layer 2)
+    ((1, 2, 11, 9, 13), 3, (3, 3, 3), (2, 2, 2), (1, 1, 1), (2, 2, 2)), # 5-D, dilation 2
+    ((2, 3, 8, 7, 9), 4, (3, 3, 3), (0, 0, 0), (1, 1, 1), (1, 1, 1)),   # 5-D, no padding
+    ((1, 2, 9, 8, 10), 3, (3, 3, 3), (0, 0, 0), (2, 2, 2), (1, 1, 1)),  # 5-D, no padding, stride 2
+    ((2, 3, 12, 14), 4, (5, 5), (2, 2), (1, 1), (1, 1)),                # 4-D, 5 x 5 (configs[3])
+    ((1, 3, 13, 11), 2, (3, 3), (1, 1), (2, 2), (1, 1)),                # 4-D, stride 2
+    ((1, 2, 7, 9, 8), 3, (1, 3, 3), (0, 1, 1), (1, 2, 1), (1, 1, 2)),   # mixed per-dimension settings
+])
+def test_conv_oracle_against_torch_fp64(shape, K, f, pads, strides, dil):
+    import torch
+    import torch.nn.functional as F
+
+    rng = np.random.default_rng(3)
+    C = shape[1]
+    x = rng.normal(size=shape).astype(np.float32)
+    w = rng.normal(0, 0.3, (K, C) + tuple(f)).astype(np.float32)
+    xt = torch.tensor(x, dtype=torch.float64, requires_grad=True)
+    wt = torch.tensor(w, dtype=torch.float64, requires_grad=True)
+    conv = F.conv3d if len(f) == 3 else F.conv2d
+    yt = conv(xt, wt, None, strides, pads, dil)
+    dy = rng.normal(size=tuple(yt.shape)).astype(np.float32)
+    yt.backward(torch.tensor(dy, dtype=torch.float64))
+    y = O.conv_fwd(x, w, list(pads), list(strides), list(dil))
+    assert y.shape == tuple(yt.shape)
+    dx = np.zeros_like(x)
+    O.conv_bwd_data(w, dy, dx, list(pads), list(strides), list(dil))
+    dw = O.conv_bwd_filter(x, dy, tuple(f), list(pads), list(strides), list(dil))
+    # the oracle accumulates in fp64 and rounds once to fp32
+    for got, ref, what in ((y, yt.detach().numpy(), "y"), (dx, xt.grad.numpy(), "dx"), (dw, wt.grad.numpy(), "dw")):
+        assert np.abs(got - ref).max() <= 1.5e-7 * np.abs(ref).max() + 1e-30, what
+    # alpha / beta blend (y = alpha * conv + beta * y)
+    y0 = rng.normal(size=y.shape).astype(np.float32)
+    yb = O.conv_fwd(x, w, list(pads), list(strides), list(dil), alpha=0.5, beta=2.0, y=y0.copy())
+    np.testing.assert_allclose(yb, 0.5 * yt.detach().numpy() + 2.0 * y0, rtol=0, atol=3e-6)
+
+
+@pytest.mark.parametrize("shape", [(2, 3, 5, 6, 7), (3, 4, 9, 8)])
+def test_bn_oracle_against_torch_fp64(shape):
+    """Statistics, normalisation and the backward pass against torch's fp64
+    batch-norm.  The reference normalises with the UNBIASED variance
+    (batchnorm.cu:302-308: var * n / (n - 1)); torch normalises with the biased
+    one, so torch runs with eps' = eps * (n-1)/n on inputs and a scale
+    multiplied by sqrt((n-1)/n), which makes the two forward functions (and
+    hence all gradients) identical."""
+    import torch
+    import torch.nn.functional as F
+
+    rng = np.random.default_rng(4)
+    C = shape[1]
+    n = int(np.prod(shape)) // C
+    eps, decay = 1e-5, 0.9
+    x = rng.normal(0.3, 1.2, shape).astype(np.float32)
+    dy = rng.normal(size=shape).astype(np.float32)
+    scale = rng.uniform(0.5, 1.5, C).astype(np.float32)
+    bias = rng.normal(0, 0.5, C).astype(np.float32)
+    rm0, rv0 = rng.normal(size=C).astype(np.float32), rng.uniform(0.5, 2, C).astype(np.float32)
+    s, q = O.bn_sums(x)
+    mean, var, rm, rv = O.bn_sums_to_statistics(s, q, n, decay, rm0, rv0)
+    y = O.bn_normalize(x, mean, var, scale, bias, eps)
+    dscale, dbias, dmean, dvar = O.bn_backprop1(x, dy, mean, var, scale, eps)
+    dx = O.bn_backprop2(x, dy, mean, var, scale, dmean, dvar, eps, n)
+
+    r = (n - 1.0) / n
+    xt = torch.tensor(x, dtype=torch.float64, requires_grad=True)
+    st = torch.tensor(scale, dtype=torch.float64, requires_grad=True)
+    bt = torch.tensor(bias, dtype=torch.float64, requires_grad=True)
+    rmt, rvt = torch.tensor(rm0, dtype=torch.float64), torch.tensor(rv0, dtype=torch.float64)
+    # (x - m) / sqrt(v_b * n/(n-1) + eps) = sqrt(r) * (x - m) / sqrt(v_b + eps * r)
+    yt = F.batch_norm(xt, rmt, rvt, st * np.sqrt(r), bt, training=True, momentum=1 - decay, eps=eps * r)
+    yt.backward(torch.tensor(dy, dtype=torch.float64))
+    xd = x.astype(np.float64)
+    red = (0,) + tuple(range(2, len(shape)))
+    assert np.allclose(mean, xd.mean(axis=red), rtol=1e-6, atol=1e-7)
+    assert np.allclose(var, xd.var(axis=red, ddof=1), rtol=2e-6)
+    # running statistics: decay * old + (1 - decay) * new, with the unbiased variance (torch does the same)
+    assert np.allclose(rm, rmt.numpy(), rtol=1e-6, atol=1e-7) and np.allclose(rv, rvt.numpy(), rtol=2e-6)
+    # fp32 arithmetic in the reference's operation order against fp64: a few ulp
+    np.testing.assert_allclose(y, yt.detach().numpy(), rtol=0, atol=4e-6)
+    np.testing.assert_allclose(dbias, bt.grad.numpy(), rtol=1e-6, atol=1e-6)
+    np.testing.assert_allclose(dscale, st.grad.numpy(), rtol=1e-5, atol=1e-5)  # d/d(scale) of scale * sqrt(r) * xhat
+    np.testing.assert_allclose(dx, xt.grad.numpy(), rtol=0, atol=1e-5)

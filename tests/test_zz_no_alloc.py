@@ -12,6 +12,7 @@ import torch
 
 import dihydrogen_b200 as dc
 from dihydrogen_b200 import _abi
+from oracle import oracle as O
 
 pytestmark = pytest.mark.gpu
 
@@ -51,6 +52,10 @@ def test_noalloc_matches_planned_stats_twice(shape, locale, overlap):
         got = _stats_noalloc(t)
         # same kernel, same fixed-order reduction: tolerance of the other BN tests
         assert np.allclose(got, ref, rtol=1e-5, atol=1e-5 * np.abs(ref).max()), (rep, got, ref)
+        # and against the CPU restatement of channel_sums_and_sqsums on the owned cells
+        s, q = O.bn_sums(np.ascontiguousarray(t.owned().cpu().numpy()))
+        want = np.concatenate([s, q])
+        assert np.allclose(got, want, rtol=1e-5, atol=1e-5 * np.abs(want).max()), (rep, got, want)
 
 
 def test_noalloc_rejects_too_many_channels():
