@@ -51,7 +51,10 @@ def sources():
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
+    """DCB_BUILD_DEFINES (e.g. "-DDCB_SW_PROFILE=1": per-role clock accounting in
+    the sweep convolution kernel) adds compiler flags; use it with force."""
     os.makedirs(OBJ, exist_ok=True)
+    extra = os.environ.get("DCB_BUILD_DEFINES", "").split()
     hdr_t = _newest_header()
     nvcc = _nvcc()
     jobs = []
@@ -61,7 +64,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         obj = os.path.join(OBJ, s.replace(".cu", ".o"))
         objs.append(obj)
         if force or not os.path.exists(obj) or os.path.getmtime(obj) < max(os.path.getmtime(src), hdr_t):
-            cmd = [nvcc, *NVCC_FLAGS, "-c", src, "-o", obj]
+            cmd = [nvcc, *NVCC_FLAGS, *extra, "-c", src, "-o", obj]
             if verbose:
                 cmd.insert(1, "-Xptxas=-v")
             jobs.append(cmd)

@@ -23,6 +23,8 @@
 //
 // Every wait on an mbarrier is bounded; on expiry the kernel records an error,
 // releases its tensor memory and returns.
+#include <cstdio>
+#include <cstdlib>
 #include <vector>
 
 #include "conv_tc.cuh"
@@ -164,11 +166,39 @@ bool tc_geom(const ConvGeom& cg, int math_mode, TcGeom* out)
     return true;
 }
 
+// Epilogue warps of the sweep kernel: 8, 12 or 16.  DCB_SW_EPI overrides the
+// default (measurements).
+int sw_epi_warps()
+{
+    static int v = 0;
+    if (v == 0)
+    {
+        const char* e = std::getenv("DCB_SW_EPI");
+        const int n = e ? std::atoi(e) : 0;
+        v = (n == 8 || n == 12) ? n : SW_EPI_DEFAULT;
+    }
+    return v;
+}
+
+// MMA-issuing warps per converter group of the sweep kernel: 1 or 2
+// (DCB_SW_ISS overrides the default).
+int sw_issuers()
+{
+    static int v = 0;
+    if (v == 0)
+    {
+        const char* e = std::getenv("DCB_SW_ISS");
+        const int n = e ? std::atoi(e) : 0;
+        v = (n == 1 || n == 2) ? n : SW_ISS_DEFAULT;
+    }
+    return v;
+}
+
 size_t sw_smem_need(const SwGeom& g)
 {
     return (size_t) (g.b_bytes + 127) / 128 * 128 + (size_t) g.raw_slots * g.raw_slot_bytes
            + (size_t) ((g.kr + 1) & ~1) * 4 + (size_t) (2 * g.a_slots + 64 + 2 * g.raw_slots) * 8 + 64 + 128
-           + (size_t) TC_EPI_WARPS * 2 * SW_NBK * 32 * 4 + 1024;
+           + (size_t) sw_epi_warps() * 2 * SW_NBK * 32 * 4 + 1024;
 }
 
 // Geometry of the sweep kernel (filters with depth).  Needs bulk-copy
@@ -236,7 +266,17 @@ bool sw_geom(const ConvGeom& cg, int math_mode, SwGeom* out)
     g.groups = g.f[1] < TC_GROUPS_MAX ? g.f[1] : TC_GROUPS_MAX;
     if (g.groups * g.kr > 160)
         return false;
-    g.a_slots = g.groups;
+    int slots_per_group = 1;
+    {
+        // measurement knobs: converter groups / issuers, A slots per group
+        const char* eg = std::getenv("DCB_SW_GROUPS");
+        const char* es = std::getenv("DCB_SW_SLOTS");
+        if (eg && std::atoi(eg) >= 1 && std::atoi(eg) <= g.groups)
+            g.groups = std::atoi(eg);
+        if (es && std::atoi(es) >= 1 && std::atoi(es) <= 3)
+            slots_per_group = std::atoi(es);
+    }
+    g.a_slots = g.groups * slots_per_group;
     if (g.a_slots * g.kr > 256)
         return false;
     int th_max = ((int) TC_TMEM_COLS - g.a_slots * g.kr) / (g.f[0] * SW_NBK);
@@ -285,6 +325,9 @@ bool sw_geom(const ConvGeom& cg, int math_mode, SwGeom* out)
     if (slots < 2)
         return false;
     g.raw_slots = slots;
+    // more epilogue warps need more staging buffers: a shallower ring pays for them
+    while (g.raw_slots > 3 && sw_smem_need(g) > 200 * 1024)
+        --g.raw_slots;
     if (sw_smem_need(g) > 200 * 1024)
         return false;
     g.tiles_w = (g.out[2] + TC_M - 1) / TC_M;
@@ -348,16 +391,17 @@ bool mg_geom(const ConvGeom& cg, int math_mode, SwGeom* out)
     if (g.c == 0)
         return false;
     g.cgroups = cg.c / g.c;
-    // Exactly three groups.  Fewer than issuers would leave an issuer without a
-    // sub-row in some rows (a single group is the sweep kernel's own case).  More:
-    // the tensor pipe adds into its accumulators by
-    // truncation; all groups share one chain here (45 updates per group), and with
-    // four groups the result sat on the 1e-5 bound (one run in six was 1 % over it,
-    // depending on the order in which the issuers' instructions landed).  Those
-    // shapes take the sweep kernel's group launches, whose partial sums are added
-    // in fp32 with rounding.
-    if (g.cgroups != TC_GROUPS_MAX)
+    // Three to six groups.  Fewer than issuers would leave an issuer without a
+    // sub-row in some rows (a single group is the sweep kernel's own case).  The
+    // tensor pipe adds into its accumulators by truncation, 45 updates per group
+    // and output: three groups on one chain stay inside the 1e-5 contract, four
+    // sat on the bound (one run in six was 1 % over it, depending on the order
+    // in which the issuers' instructions landed).  So more than three groups are
+    // spread over two accumulator sets that the epilogue adds with rounding; more
+    // than six take the sweep kernel's group launches.
+    if (g.cgroups < TC_GROUPS_MAX || g.cgroups > 2 * TC_GROUPS_MAX)
         return false;
+    g.nsets = g.cgroups > TC_GROUPS_MAX ? 2 : 1;
     g.w_c_off = 0;
     g.ntot = g.f[1] * MG_BLK;
     if (g.ntot > 256)
@@ -369,7 +413,7 @@ bool mg_geom(const ConvGeom& cg, int math_mode, SwGeom* out)
     g.b_bytes = g.cgroups * MG_SLOTS * g.b_rot_bytes;
     g.groups = TC_GROUPS_MAX;
     g.a_slots = g.groups;
-    int th_max = ((int) TC_TMEM_COLS - g.a_slots * g.kr) / MG_BLK;
+    int th_max = ((int) TC_TMEM_COLS - g.a_slots * g.kr) / (g.nsets * MG_BLK);
     if (th_max + g.f[1] - 1 > 32)
         th_max = 32 - g.f[1] + 1;
     if (th_max > g.out[1])
@@ -589,7 +633,7 @@ int32_t tc_plan_create(const ConvGeom& fwd, const ConvGeom& bwd, bool bwd_is_fwd
     if (ok && p->has_wg)
         ok = cudaMalloc(&p->wg_part, (size_t) num_sms() * 128 * 16 * sizeof(float)) == cudaSuccess;
     if (ok && p->has_sw[0])
-        ok = cudaMalloc(&p->stat_part, (size_t) num_sms() * TC_EPI_WARPS * 32 * sizeof(float)) == cudaSuccess;
+        ok = cudaMalloc(&p->stat_part, (size_t) num_sms() * 16 * 32 * sizeof(float)) == cudaSuccess;
     if (!ok)
     {
         (void) cudaGetLastError();
@@ -803,26 +847,97 @@ static int32_t sw_launch(const SwGeom& g, float alpha, const float* w, const flo
         grid = g.units;
     const bool c4f3 = g.c == 4 && g.f[2] == 3 && g.pad[2] == 1 && g.split;
     const bool stats = stat_part != nullptr;
+    const int epi = sw_epi_warps(), iss = sw_issuers();
+    long long* prof = nullptr;
+#if DCB_SW_PROFILE
+    // per-role clock accounting: one launch is measured and printed, synchronously
+    static int prof_left = std::getenv("DCB_SW_PROF_LAUNCHES") ? std::atoi(std::getenv("DCB_SW_PROF_LAUNCHES")) : 0;
+    const size_t prof_n = (size_t) grid * 32 * 8;
+    if (prof_left > 0)
+    {
+        DCB_CUDA_TRY(cudaMalloc(&prof, prof_n * sizeof(long long)));
+        DCB_CUDA_TRY(cudaMemsetAsync(prof, 0, prof_n * sizeof(long long), stream));
+    }
+#endif
     auto launch = [&](auto kernel) -> int32_t {
         DCB_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) (224 * 1024)));
-        kernel<<<(unsigned) grid, TC_THREADS, smem, stream>>>(g, alpha, beta, bimg, y, status, map, ymap, use_ymap,
-                                                            stat_part);
+        kernel<<<(unsigned) grid, sw_threads(epi, iss), smem, stream>>>(g, alpha, beta, bimg, y, status, map, ymap,
+                                                                        use_ymap, stat_part, prof);
         return DCB_OK;
     };
     const bool blend = beta != 0.f;
     int32_t st;
-    if (c4f3)
-        st = stats ? launch(sw_conv_kernel<true, true, false>)
-                   : (blend ? launch(sw_conv_kernel<true, false, true>) : launch(sw_conv_kernel<true, false, false>));
+#define DCB_SW_PICK(EPI, ISS)                                                                                         \
+    if (c4f3)                                                                                                         \
+        st = stats ? launch(sw_conv_kernel<true, true, false, EPI, ISS>)                                              \
+                   : (blend ? launch(sw_conv_kernel<true, false, true, EPI, ISS>)                                     \
+                            : launch(sw_conv_kernel<true, false, false, EPI, ISS>));                                  \
+    else                                                                                                              \
+        st = stats ? launch(sw_conv_kernel<false, true, false, EPI, ISS>)                                             \
+                   : (blend ? launch(sw_conv_kernel<false, false, true, EPI, ISS>)                                    \
+                            : launch(sw_conv_kernel<false, false, false, EPI, ISS>));
+    if (epi == 12 && iss == 2)
+    {
+        DCB_SW_PICK(12, 2)
+    }
+    else if (epi == 12)
+    {
+        DCB_SW_PICK(12, 1)
+    }
+    else if (iss == 2)
+    {
+        DCB_SW_PICK(8, 2)
+    }
     else
-        st = stats ? launch(sw_conv_kernel<false, true, false>)
-                   : (blend ? launch(sw_conv_kernel<false, false, true>) : launch(sw_conv_kernel<false, false, false>));
+    {
+        DCB_SW_PICK(8, 1)
+    }
+#undef DCB_SW_PICK
     if (st != DCB_OK)
         return st;
     DCB_LAUNCH_CHECK();
+#if DCB_SW_PROFILE
+    if (prof != nullptr)
+    {
+        --prof_left;
+        std::vector<long long> h(prof_n);
+        DCB_CUDA_TRY(cudaStreamSynchronize(stream));
+        DCB_CUDA_TRY(cudaMemcpy(h.data(), prof, prof_n * sizeof(long long), cudaMemcpyDeviceToHost));
+        cudaFree(prof);
+        const int t0 = sw_tma_warp(iss), e0 = sw_epi_warp0(iss);
+        auto role = [&](const char* name, int w_lo, int w_hi, const char* const* labels) {
+            double acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            long long n = 0;
+            for (long long b = 0; b < grid; ++b)
+                for (int w = w_lo; w < w_hi; ++w)
+                {
+                    const long long* r = &h[((size_t) b * 32 + w) * 8];
+                    if (r[7] == 0)
+                        continue;
+                    for (int i = 0; i < 8; ++i)
+                        acc[i] += (double) r[i];
+                    ++n;
+                }
+            if (n == 0)
+                return;
+            std::fprintf(stderr, "[sw prof] %-10s warps %lld total %.0f:", name, n, acc[7] / n);
+            for (int i = 0; i < 5; ++i)
+                std::fprintf(stderr, " %s %.1f%%", labels[i], 100.0 * acc[i] / acc[7]);
+            std::fprintf(stderr, "\n");
+        };
+        const char* lc[5] = {"wait_raw", "convert", "wait_a_empty", "st+arrive", "other"};
+        const char* li[5] = {"wait_row_free", "wait_a_full", "issue", "-", "other"};
+        const char* lt[5] = {"wait_raw_empty", "copy", "-", "-", "other"};
+        const char* le[5] = {"wait_row_done", "tmem_ld", "zero+arrive", "stats+store", "other"};
+        role("converter", 0, TC_PRODUCERS, lc);
+        role("issuer", TC_MMA_WARP, t0, li);
+        role("copy", t0, t0 + 1, lt);
+        role("epilogue", e0, e0 + epi, le);
+    }
+#endif
     if (stats)
     {
-        sw_stats_fold_kernel<<<1, 32, 0, stream>>>(stat_part, (int) grid * TC_EPI_WARPS, g.k, sums, sqsums);
+        sw_stats_fold_kernel<<<1, 32, 0, stream>>>(stat_part, (int) grid * epi, g.k, sums, sqsums);
         DCB_LAUNCH_CHECK();
     }
     (void) x;

@@ -55,7 +55,36 @@ namespace dcb
 namespace
 {
 
+// Per-role clock accounting (a build with -DDCB_SW_PROFILE=1 only): every warp
+// adds up the clocks it spends in each phase of its loop and leaves eight
+// totals in `prof` at the end; the host prints the per-role averages.
+#ifndef DCB_SW_PROFILE
+#define DCB_SW_PROFILE 0
+#endif
+#if DCB_SW_PROFILE
+#define SW_PROF_DECL long long pf_t = clock64(), pf_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; const long long pf_t0 = pf_t;
+#define SW_PROF_MARK(slot)                                                                                            \
+    {                                                                                                                 \
+        const long long pf_now = clock64();                                                                           \
+        pf_acc[slot] += pf_now - pf_t;                                                                                \
+        pf_t = pf_now;                                                                                                \
+    }
+#define SW_PROF_FLUSH(prof)                                                                                           \
+    if (prof != nullptr && lane == 0)                                                                                 \
+    {                                                                                                                 \
+        pf_acc[7] = clock64() - pf_t0;                                                                                \
+        for (int pf_i = 0; pf_i < 8; ++pf_i)                                                                          \
+            prof[((size_t) blockIdx.x * 32 + warp) * 8 + pf_i] = pf_acc[pf_i];                                        \
+    }
+#else
+#define SW_PROF_DECL
+#define SW_PROF_MARK(slot)
+#define SW_PROF_FLUSH(prof)
+#endif
+
 constexpr int SW_NBK = 16; // accumulator columns per (output row, plane slot)
+constexpr int SW_EPI_DEFAULT = 8;
+constexpr int SW_ISS_DEFAULT = 1;
 
 struct SwGeom
 {
@@ -77,6 +106,7 @@ struct SwGeom
     int tiles_w, tiles_h, nseg;
     long long units;
     int raw_slots, raw_slot_bytes, chunk_rows, chunks_pp;
+    int nsets;      // multi-group kernel: accumulator sets the channel groups are spread over
 };
 
 struct SwUnit
@@ -248,11 +278,35 @@ __device__ __forceinline__ void sw_convert_c4f3(uint32_t raw_lane, uint32_t pitc
 // `stat_part` at the end, and sw_stats_fold_kernel adds those in a fixed order
 // in fp64.
 // BLEND: beta != 0, the old output is fetched early and blended in (plain stores).
-template <bool C4F3, bool STATS, bool BLEND>
-__global__ void __launch_bounds__(TC_THREADS, 1)
+// EPI: epilogue warps, EPI / 4 per TMEM quadrant, each retiring every
+// (EPI / 4)-th output row.  Retiring a row costs its warp a tensor-memory load
+// and a zeroing store back to back, well over a thousand clocks with MMAs in
+// flight, and the issuers wait for the hand-back: the more rows of a plane are
+// in retirement at once, the shorter the step.
+// ISS: MMA-issuing warps per converter group.  One tcgen05.mma keeps its
+// issuing thread busy for 150 to 200 clocks while the tensor pipe needs about 70
+// for it (N = 144): with ISS = 2 the k-steps of a row are split over two warps
+// that issue side by side into the same accumulators.
+// Warps: converters 0..11, issuers 12..12+3*ISS-1, the copy warp, then (from the
+// next multiple of four, so that warp & 3 is the TMEM quadrant) the epilogue.
+__host__ __device__ constexpr int sw_tma_warp(int iss)
+{
+    return TC_MMA_WARP + TC_GROUPS_MAX * iss;
+}
+__host__ __device__ constexpr int sw_epi_warp0(int iss)
+{
+    return (sw_tma_warp(iss) + 1 + 3) & ~3;
+}
+__host__ __device__ constexpr int sw_threads(int epi, int iss)
+{
+    return (sw_epi_warp0(iss) + epi) * 32;
+}
+
+template <bool C4F3, bool STATS, bool BLEND, int EPI, int ISS>
+__global__ void __launch_bounds__(sw_threads(EPI, ISS), 1)
     sw_conv_kernel(SwGeom g, float alpha, float beta, const float* __restrict__ bimg, float* y, int* status,
                    const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap ymap, int use_ymap,
-                   float* __restrict__ stat_part)
+                   float* __restrict__ stat_part, long long* prof)
 {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -281,11 +335,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         for (int s = 0; s < g.a_slots; ++s)
         {
             mbar_init(&a_full[s], 4);
-            mbar_init(&a_empty[s], 1);
+            mbar_init(&a_empty[s], ISS);
         }
         for (int r = 0; r < 32; ++r)
         {
-            mbar_init(&row_done[r], 1);
+            mbar_init(&row_done[r], ISS);
             mbar_init(&row_free[r], 4);
         }
         for (int r = 0; r < g.raw_slots; ++r)
@@ -305,7 +359,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     }
     // k-row table: offset of the tap inside a raw chunk row, and what the row
     // carries: 0 hi part, 1 lo part, 2 zero
-    for (int r = tid; r < g.kr; r += TC_THREADS)
+    for (int r = tid; r < g.kr; r += sw_threads(EPI, ISS))
     {
         const int part = r / g.crows, rem = r % g.crows;
         const int c = rem / g.f[2], kw = rem % g.f[2];
@@ -313,7 +367,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         const uint32_t sel = part < (g.split ? 3 : 1) ? (part == 1 ? 1u : 0u) : 2u;
         ktab[r] = sel == 2u ? ((2u << 16) | 4u) : (off | (sel << 16));
     }
-    for (int i = tid; i < g.b_bytes / 16; i += TC_THREADS)
+    for (int i = tid; i < g.b_bytes / 16; i += sw_threads(EPI, ISS))
         reinterpret_cast<float4*>(b_smem)[i] = reinterpret_cast<const float4*>(bimg)[i];
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     tc_fence_before();
@@ -339,6 +393,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         int lap_a = 0;
         uint32_t cslot = 0, cphase = 0, a_phase = 1, base = 0;
         bool a_first = true;
+        SW_PROF_DECL
         for (uint32_t u = blockIdx.x; u < nunits && ok; u += gridDim.x)
         {
             const SwUnit t = sw_unit(g, u);
@@ -354,9 +409,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                     for (; i < hi && ok; i += G)
                     {
                         const int a_slot = gq + G * lap_a;
+                        SW_PROF_MARK(4)
                         if (!have)
                             ok = mbar_wait(&raw_full[cslot], cphase, abort_flag);
                         have = true;
+                        SW_PROF_MARK(0)
                         if (!ok)
                             break;
                         const float* raw = reinterpret_cast<const float*>(raw_ring + (size_t) cslot * g.raw_slot_bytes)
@@ -367,8 +424,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                         {
                             uint32_t v[5][8];
                             sw_convert_c4f3(raw_s, pitch, v);
+                            SW_PROF_MARK(1)
                             if (!a_first)
                                 ok = mbar_wait(&a_empty[a_slot], a_phase, abort_flag);
+                            SW_PROF_MARK(2)
                             if (!ok)
                                 break;
                             tc_fence_after();
@@ -395,6 +454,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                         __syncwarp();
                         if (lane == 0)
                             mbar_arrive(&a_full[a_slot]);
+                        SW_PROF_MARK(3)
                         if (++lap_a == laps_a)
                         {
                             lap_a = 0;
@@ -415,8 +475,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                 base = (base + (uint32_t) R) % (uint32_t) G;
             }
         }
+        SW_PROF_FLUSH(prof)
     }
-    else if (warp == TC_TMA_WARP)
+    else if (warp == sw_tma_warp(ISS))
     {
         // ------------------------------------------------------------------
         // bulk tensor copies: chunk_rows raw rows of every channel per copy.
@@ -425,6 +486,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         const uint32_t bytes = (uint32_t) (g.c * g.chunk_rows) * TC_RAW_W * 4u;
         uint32_t slot = 0, empty_phase = 1;
         bool first_lap = true;
+        SW_PROF_DECL
         for (uint32_t u = blockIdx.x; u < nunits && ok; u += gridDim.x)
         {
             const SwUnit t = sw_unit(g, u);
@@ -434,8 +496,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                     continue;
                 for (int ch = 0; ch < g.chunks_pp; ++ch)
                 {
+                    SW_PROF_MARK(4)
                     if (!first_lap)
                         ok = mbar_wait(&raw_empty[slot], empty_phase, abort_flag);
+                    SW_PROF_MARK(0)
                     if (!ok)
                         break;
                     if (lane == 0)
@@ -446,6 +510,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                                     t.oh0 - g.pad[1] + ch * g.chunk_rows, d, 0, t.n, &raw_full[slot]);
                     }
                     __syncwarp();
+                    SW_PROF_MARK(1)
                     if (++slot == (uint32_t) g.raw_slots)
                     {
                         slot = 0;
@@ -455,14 +520,16 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                 }
             }
         }
+        SW_PROF_FLUSH(prof)
     }
-    else if (warp >= TC_MMA_WARP && warp < TC_MMA_WARP + TC_GROUPS_MAX)
+    else if (warp >= TC_MMA_WARP && warp < sw_tma_warp(ISS))
     {
         // ------------------------------------------------------------------
-        // MMA issue: issuer mq takes the rows converter group mq produced.
-        // Lane i issues staged row i (its descriptors depend on i only).
+        // MMA issue: the issuers of group mq take the rows converter group mq
+        // produced, each its share of the row's k-steps.  Lane i issues staged
+        // row i (its descriptors depend on i only).
         // ------------------------------------------------------------------
-        const int mq = warp - TC_MMA_WARP;
+        const int mq = (warp - TC_MMA_WARP) % TC_GROUPS_MAX, part = (warp - TC_MMA_WARP) / TC_GROUPS_MAX;
         if (mq < G)
         {
             const int my_i = lane;
@@ -478,10 +545,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                 make_desc(smem_u32(b_smem), b_lbo, 128u, 0u) + (uint64_t) ((uint32_t) (j_lo * blk));
             const uint32_t rot_units = (uint32_t) g.b_rot_bytes >> 4;
             const uint32_t a_ring = tmem_base + a_col0;
-            const int ksteps = g.ksteps;
+            // this warp's k-steps of every row: [ks_lo, ks_hi)
+            const int ks_split = ISS == 1 ? g.ksteps : (g.ksteps + 1) / 2;
+            const int ks_lo = part == 0 ? 0 : ks_split, ks_hi = part == 0 ? ks_split : g.ksteps;
             const int laps_a = g.a_slots / G;
             int lap_a = 0;
             uint32_t full_phase = 0, step = 0, base = 0;
+            SW_PROF_DECL
             for (uint32_t u = blockIdx.x; u < nunits && ok; u += gridDim.x)
             {
                 const SwUnit t = sw_unit(g, u);
@@ -494,29 +564,32 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                     for (; i < R && ok; i += G)
                     {
                         // The blocks this row adds into (output rows r_lo..r_hi) must
-                        // have been retired.  Each epilogue half retires in ascending
-                        // order, so the top two rows stand for all of them.  Only rows
+                        // have been retired.  Each epilogue warp of a quadrant retires
+                        // its rows in ascending order, so the top EPI / 4 rows (one per
+                        // warp) stand for all of them.  Only rows
                         // this row adds into may be waited for: their next retirement
                         // needs this very row, so such a barrier cannot complete again
                         // before this wait has seen it.
                         const int r_hi = min(i, g.th - 1), r_lo = max(0, i - fh + 1);
-                        ok = mbar_wait_t<0>(&row_free[r_hi], par, abort_flag);
-                        if (ok && r_hi - 1 >= r_lo)
-                            ok = mbar_wait_t<0>(&row_free[r_hi - 1], par, abort_flag);
+                        SW_PROF_MARK(4)
+                        for (int r = r_hi; r >= r_lo && r > r_hi - EPI / 4 && ok; --r)
+                            ok = mbar_wait_t<0>(&row_free[r], par, abort_flag);
+                        SW_PROF_MARK(0)
                         if (!ok)
                             break;
                         if (real)
                         {
                             const uint32_t slot = (uint32_t) (mq + G * lap_a);
                             ok = mbar_wait_t<0>(&a_full[slot], full_phase, abort_flag);
+                            SW_PROF_MARK(1)
                             if (!ok)
                                 break;
                             tc_fence_after();
                             if (lane == i)
                             {
-                                uint32_t a_addr = a_ring + slot * (uint32_t) g.kr;
-                                uint64_t bd = bd0;
-                                for (int ks = 0; ks < ksteps; ++ks)
+                                uint32_t a_addr = a_ring + slot * (uint32_t) g.kr + 8u * (uint32_t) ks_lo;
+                                uint64_t bd = bd0 + (uint64_t) (b_kstep_units * (uint32_t) ks_lo);
+                                for (int ks = ks_lo; ks < ks_hi; ++ks)
                                 {
                                     mma_tf32_ts(my_d, a_addr, bd, my_idesc);
                                     a_addr += 8;
@@ -527,6 +600,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                                 tc_fence_before();
                             }
                             __syncwarp();
+                            SW_PROF_MARK(2)
                             if (++lap_a == laps_a)
                             {
                                 lap_a = 0;
@@ -545,21 +619,23 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                         base = (base + (uint32_t) R) % (uint32_t) G;
                 }
             }
+            SW_PROF_FLUSH(prof)
         }
     }
-    else if (warp > TC_TMA_WARP)
+    else if (warp >= sw_epi_warp0(ISS))
     {
         // ------------------------------------------------------------------
         // epilogue: after step d retire output plane d + pad - (fd-1)
         // ------------------------------------------------------------------
         const int quad = warp & 3;
-        const int half = (warp - TC_TMA_WARP - 1) >> 2, nhalf = TC_EPI_WARPS / 4;
+        const int ew = warp - sw_epi_warp0(ISS); // index among the epilogue warps
+        const int half = ew >> 2, nhalf = EPI / 4;
         const uint32_t lane_addr = tmem_base + ((uint32_t) (quad * 32) << 16);
         const int nk = g.k;
         const size_t ysc = (size_t) g.ys_c;
         // bulk stores overwrite: the blend with the old output takes the plain path
         const bool bulk = !BLEND && use_ymap != 0;
-        float* stage = stage_base + (warp - TC_TMA_WARP - 1) * (2 * SW_NBK * 32);
+        float* stage = stage_base + ew * (2 * SW_NBK * 32);
         uint32_t nstored = 0;
         uint64_t s1[STATS ? SW_NBK / 2 : 1], s2[STATS ? SW_NBK / 2 : 1]; // packed pairs of filters
 #pragma unroll
@@ -577,6 +653,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
             for (int j = half; j < g.th; j += nhalf)
                 mbar_arrive(&row_free[j]);
         uint32_t step = 0;
+        SW_PROF_DECL
         for (uint32_t u = blockIdx.x; u < nunits && ok; u += gridDim.x)
         {
             const SwUnit t = sw_unit(g, u);
@@ -602,8 +679,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                             if (k < nk)
                                 old[k] = yrow[(size_t) k * ysc];
                     }
+                    SW_PROF_MARK(4)
                     for (int i = j; i < j + fh && ok; ++i)
                         ok = mbar_wait(&row_done[i], par, abort_flag);
+                    SW_PROF_MARK(0)
                     if (!ok)
                         break;
                     tc_fence_after();
@@ -614,6 +693,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                         tmem_ld16(addr, v);
                         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                     }
+                    SW_PROF_MARK(1)
                     // hand the blocks back first: the issuers wait for that, nobody for the store
                     tmem_st16_zero(addr);
                     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
@@ -621,6 +701,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                     __syncwarp();
                     if (lane == 0)
                         mbar_arrive(&row_free[j]);
+                    SW_PROF_MARK(2)
                     if (!wr)
                         continue;
                     if (STATS && ow < g.out[2])
@@ -677,6 +758,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                         }
                         ++nstored;
+                        SW_PROF_MARK(3)
                     }
                     else if (ow < g.out[2])
                     {
@@ -690,6 +772,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                 }
             }
         }
+        SW_PROF_FLUSH(prof)
         // the staged rows must have left shared memory before the CTA does
         if (bulk && lane == 0)
             asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
@@ -719,7 +802,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                 if (lane == SW_NBK + k)
                     mine = alpha * alpha * b;
             }
-            stat_part[((size_t) blockIdx.x * TC_EPI_WARPS + (warp - TC_TMA_WARP - 1)) * 32 + lane] = mine;
+            stat_part[((size_t) blockIdx.x * EPI + ew) * 32 + lane] = mine;
         }
     }
 

@@ -14,6 +14,13 @@
 //     sequence; row_done[i] completes when all of row i's sub-rows have.
 //   * The filter image holds [channel group][rotation d & 3][k-step]...; bulk
 //     copies bring all channels of a chunk of rows.
+//   * The tensor pipe adds into its fp32 accumulators by truncation, and every
+//     channel group adds 45 updates (27 taps x hi / lo parts in 5 k-steps x 9
+//     row / plane taps) to an output's chain: with more than three groups on one
+//     chain the result reaches the 1e-5 bound.  So the groups are spread over
+//     `nsets` accumulator sets of th rows each (set s at TMEM column
+//     s * th * 16, at most three groups per set), and the epilogue adds the
+//     sets in fp32 with rounding when it retires a row.
 // Hand-offs and their safety argument are those of conv_tc_sweep.cuh (an issuer
 // waits only for output rows its own row adds into).
 #pragma once
@@ -84,7 +91,7 @@ __global__ void mg_pack_filter_kernel(const float* __restrict__ w, float* __rest
 }
 
 // Warps as in the sweep kernel: 0..11 converters, 12..14 issuers, 15 copies,
-// 16..23 epilogue.  TMEM columns: [accumulators th * 16][A ring].
+// 16..23 epilogue.  TMEM columns: [nsets x accumulators th * 16][A ring].
 template <bool C4F3>
 __global__ void __launch_bounds__(TC_THREADS, 1)
     mg_conv_kernel(SwGeom g, float alpha, const float* __restrict__ bimg, float* y, int* status,
@@ -155,7 +162,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t a_col0 = (uint32_t) (g.th * MG_BLK); // first column of the A ring
+    const uint32_t set_cols = (uint32_t) (g.th * MG_BLK);     // columns of one accumulator set
+    const uint32_t a_col0 = (uint32_t) g.nsets * set_cols;    // first column of the A ring
+    const int grp_per_set = (CG + g.nsets - 1) / g.nsets;
     const uint32_t nunits = (uint32_t) g.units;
     bool ok = true;
 
@@ -347,9 +356,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                                 uint32_t a_addr = a_ring + slot * (uint32_t) g.kr;
                                 uint64_t bd = my_b_desc
                                               + (uint64_t) (((uint32_t) grp * MG_SLOTS + rot) * rot_units);
+                                // the group's accumulator set
+                                const uint32_t d_addr = my_d + (uint32_t) (grp / grp_per_set) * set_cols;
                                 for (int ks = 0; ks < ksteps; ++ks)
                                 {
-                                    mma_tf32_ts(my_d, a_addr, bd, my_idesc);
+                                    mma_tf32_ts(d_addr, a_addr, bd, my_idesc);
                                     a_addr += 8;
                                     bd += b_kstep_units;
                                 }
@@ -392,7 +403,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         float* stage = stage_base + (warp - TC_TMA_WARP - 1) * (2 * MG_NBK * 32);
         uint32_t nstored = 0;
         for (int j = half; j < g.th; j += nhalf)
-            tmem_st16_zero(lane_addr + (uint32_t) (j * MG_BLK));
+            for (int s = 0; s < g.nsets; ++s)
+                tmem_st16_zero(lane_addr + (uint32_t) s * set_cols + (uint32_t) (j * MG_BLK));
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         tc_fence_before();
         __syncwarp();
@@ -424,9 +436,22 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                     if (wr)
                     {
                         tmem_ld4(addr, v);
-                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                        if (g.nsets > 1)
+                        {
+                            // the second set's partial sums, added with rounding
+                            uint32_t v2[MG_NBK];
+                            tmem_ld4(addr + set_cols, v2);
+                            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                            for (int k = 0; k < MG_NBK; ++k)
+                                v[k] = __float_as_uint(__uint_as_float(v[k]) + __uint_as_float(v2[k]));
+                        }
+                        else
+                            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                     }
                     tmem_st4_zero(addr);
+                    if (g.nsets > 1)
+                        tmem_st4_zero(addr + set_cols);
                     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                     tc_fence_before();
                     __syncwarp();

@@ -388,3 +388,38 @@ def test_rows_padded_to_a_pitch_with_odd_extents(W, pad):
     for st, ext in ((ys, Wo), (dxs, W)):
         if st.shape[-1] > ext:
             assert bool(torch.isnan(st[..., ext:]).all()), "a store went past the end of a row"
+
+
+def test_backward_data_full_shard_16_channels_against_fp64():
+    """Backward data of the benchmark layer on its 256^3 shard: dy has 16
+    channels, which the multi-group sweep kernel walks as four groups inside one
+    launch, two per accumulator set (a single truncating chain of 180 updates
+    sat on the 1e-5 bound).  dy carries a mean so that a truncation bias cannot
+    hide behind cancellation; sampled blocks of dx (a corner, an edge, the
+    interior) are recomputed in fp64."""
+    import torch.nn.functional as F
+
+    D = 256
+    gen = torch.Generator(device="cuda").manual_seed(13)
+    dy = torch.randn(1, 16, D, 256, 256, device="cuda", generator=gen) + 0.5
+    w = torch.randn(16, 4, 3, 3, 3, device="cuda", generator=gen) * 0.14 + 0.02
+    dx = torch.full((1, 4, D, 256, 256), float("nan"), device="cuda")
+    p = Plan(dx, w, dy, [1] * 3, [1] * 3, [1] * 3, _abi.MATH_FP32)
+    assert _abi.lib().dcb_conv_plan_kernel_variant(p.p, 1) == 4, "expected the multi-group sweep kernel"
+    for rep in range(3):  # the order in which the issuers' instructions land varies from run to run
+        p.bwd_data(1.0, w, dy, 0.0, dx)
+        torch.cuda.synchronize()
+        assert _abi.lib().dcb_conv_plan_status(p.p, None) == _abi.OK
+        assert not bool(torch.isnan(dx).any())
+        worst = 0.0
+        B = 12
+        for o0 in ((0, 0, 0), (100, 0, 117), (244, 244, 244), (31, 200, 64)):
+            lo = [max(0, o - 2) for o in o0]
+            hi = [min(256, o + B + 2) for o in o0]
+            blk = dy[0, :, lo[0]:hi[0], lo[1]:hi[1], lo[2]:hi[2]].double()
+            full = F.conv_transpose3d(blk[None], w.double(), padding=1)[0]
+            sl = tuple(slice(o - l, o - l + B) for o, l in zip(o0, lo))
+            ref = full[(slice(None),) + sl]
+            got = dx[0, :, o0[0]:o0[0] + B, o0[1]:o0[1] + B, o0[2]:o0[2] + B].double()
+            worst = max(worst, ((got - ref).abs() / (ref.abs() + ref.pow(2).mean().sqrt())).max().item())
+        assert worst <= TOL, (rep, worst)

@@ -4,7 +4,8 @@
 mbarrier parity waits only tell a barrier's current phase from the previous
 one.  The model runs the issuers and the two epilogue halves as coroutines
 over barriers with exactly that semantics and checks that no wait passes on
-the wrong completion and that nobody waits for ever:
+the wrong completion, that no issuer adds into a row that has not been retired
+and that nobody waits for ever:
 
 * with the rule the kernel uses (an issuer waits only for output rows its own
   input row adds into) for every filter height, issuer count and column
@@ -17,7 +18,7 @@ import random
 import pytest
 
 
-def simulate(groups, th, fh, steps, seed, virtual, wait_rows, cg=1):
+def simulate(groups, th, fh, steps, seed, virtual, wait_rows, cg=1, nhalf=2):
     """Returns ("ok" | "deadlock", wrong_passes).  cg > 1: the multi-group
     kernel, where row i is cg sub-rows dealt to the issuers in sequence and
     row_done[i] needs all of them."""
@@ -58,6 +59,11 @@ def simulate(groups, th, fh, steps, seed, virtual, wait_rows, cg=1):
                         yield "wait"
                     if completions[("free", j)] != step + 1:
                         wrong.append(("issuer", mq, step, i, j))
+                # data hazard: every output row this input row adds into must have been
+                # retired (zeroed) for this step, whether or not it was waited for
+                for j in range(max(0, i - fh + 1), min(i, th - 1) + 1):
+                    if completions[("free", j)] < step + 1:
+                        wrong.append(("issuer adds into an unretired row", mq, step, i, j))
                 yield "work"
                 arrive(("done", i))
                 q += groups
@@ -67,7 +73,7 @@ def simulate(groups, th, fh, steps, seed, virtual, wait_rows, cg=1):
     def epilogue(half):
         for step in range(steps):
             parity = step & 1
-            for j in range(half, th, 2):
+            for j in range(half, th, nhalf):
                 for i in range(j, j + fh):
                     while not passes(("done", i), parity):
                         yield "wait"
@@ -76,7 +82,7 @@ def simulate(groups, th, fh, steps, seed, virtual, wait_rows, cg=1):
                 yield "work"
                 arrive(("free", j))
 
-    threads = [issuer(m) for m in range(groups)] + [epilogue(0), epilogue(1)]
+    threads = [issuer(m) for m in range(groups)] + [epilogue(h) for h in range(nhalf)]
     alive = [True] * len(threads)
     idle = 0
     while any(alive):
@@ -92,11 +98,12 @@ def simulate(groups, th, fh, steps, seed, virtual, wait_rows, cg=1):
     return "ok", wrong
 
 
-def touched_rows(i, th, fh):
-    """What the kernel waits for: the top two of the output rows that input
-    row i adds into (each epilogue half retires in ascending order)."""
+def touched_rows(i, th, fh, n=2):
+    """What the kernel waits for: the top n (= epilogue warps per quadrant) of
+    the output rows that input row i adds into; each of those warps retires its
+    rows in ascending order, so they stand for all rows below."""
     hi, lo = min(i, th - 1), max(0, i - fh + 1)
-    return [hi, hi - 1] if hi - 1 >= lo else [hi]
+    return list(range(hi, max(lo, hi - n + 1) - 1, -1))
 
 
 def last_two_rows(i, th, fh):
@@ -112,6 +119,23 @@ def test_protocol_never_locks_or_passes_early(fh):
                 virtual = (0, 1, 8, 9) if seed % 2 else (0, 5, 9)
                 state, wrong = simulate(groups, th, fh, 10, seed, virtual, touched_rows)
                 assert state == "ok" and not wrong, (fh, groups, th, seed, state, wrong[:2])
+
+
+@pytest.mark.parametrize("nhalf", [3, 4])
+def test_protocol_with_more_epilogue_warps_per_quadrant(nhalf):
+    """12 or 16 epilogue warps: every (nhalf)-th row per warp, the issuers wait
+    for the top nhalf rows they add into."""
+    for fh in (1, 2, 3, 5):
+        for groups in range(1, min(fh, 3) + 1):
+            for th in range(2, 14):
+                for seed in range(6):
+                    virtual = (0, 1, 8, 9) if seed % 2 else (0, 5, 9)
+                    state, wrong = simulate(groups, th, fh, 10, seed, virtual,
+                                            lambda i, t, f: touched_rows(i, t, f, nhalf), nhalf=nhalf)
+                    assert state == "ok" and not wrong, (nhalf, fh, groups, th, seed, state, wrong[:2])
+    # waiting for two rows only would let an issuer add into a row the third warp has not retired
+    bad = [simulate(3, 7, 3, 10, seed, (0, 1, 8, 9), touched_rows, nhalf=nhalf)[1] for seed in range(10)]
+    assert any(bad)
 
 
 def test_waiting_for_a_row_one_does_not_touch_locks_up():
