@@ -166,30 +166,17 @@ bool tc_geom(const ConvGeom& cg, int math_mode, TcGeom* out)
     return true;
 }
 
-// Epilogue warps of the sweep kernel: 8, 12 or 16.  DCB_SW_EPI overrides the
-// default (measurements).
+// Epilogue warps of the sweep kernel: 12, three per TMEM quadrant (8 were
+// measured slower: 0.449 / 0.542 ms without / with statistics on the 256^3
+// shard against 0.432 / 0.494).  DCB_SW_EPI=8 selects the smaller team
+// (measurements).
 int sw_epi_warps()
 {
     static int v = 0;
     if (v == 0)
     {
         const char* e = std::getenv("DCB_SW_EPI");
-        const int n = e ? std::atoi(e) : 0;
-        v = (n == 8 || n == 12) ? n : SW_EPI_DEFAULT;
-    }
-    return v;
-}
-
-// MMA-issuing warps per converter group of the sweep kernel: 1 or 2
-// (DCB_SW_ISS overrides the default).
-int sw_issuers()
-{
-    static int v = 0;
-    if (v == 0)
-    {
-        const char* e = std::getenv("DCB_SW_ISS");
-        const int n = e ? std::atoi(e) : 0;
-        v = (n == 1 || n == 2) ? n : SW_ISS_DEFAULT;
+        v = (e && std::atoi(e) == 8) ? 8 : 12;
     }
     return v;
 }
@@ -198,7 +185,7 @@ size_t sw_smem_need(const SwGeom& g)
 {
     return (size_t) (g.b_bytes + 127) / 128 * 128 + (size_t) g.raw_slots * g.raw_slot_bytes
            + (size_t) ((g.kr + 1) & ~1) * 4 + (size_t) (2 * g.a_slots + 64 + 2 * g.raw_slots) * 8 + 64 + 128
-           + (size_t) sw_epi_warps() * 2 * SW_NBK * 32 * 4 + 1024;
+           + (size_t) 12 * 2 * SW_NBK * 32 * 4 + 1024; // staging for up to 12 epilogue warps
 }
 
 // Geometry of the sweep kernel (filters with depth).  Needs bulk-copy
@@ -633,7 +620,7 @@ int32_t tc_plan_create(const ConvGeom& fwd, const ConvGeom& bwd, bool bwd_is_fwd
     if (ok && p->has_wg)
         ok = cudaMalloc(&p->wg_part, (size_t) num_sms() * 128 * 16 * sizeof(float)) == cudaSuccess;
     if (ok && p->has_sw[0])
-        ok = cudaMalloc(&p->stat_part, (size_t) num_sms() * 16 * 32 * sizeof(float)) == cudaSuccess;
+        ok = cudaMalloc(&p->stat_part, (size_t) num_sms() * 12 * 32 * sizeof(float)) == cudaSuccess;
     if (!ok)
     {
         (void) cudaGetLastError();
@@ -830,10 +817,15 @@ static bool sw_make_y_map(const SwGeom& g, float* y, CUtensorMap* map)
            == CUDA_SUCCESS;
 }
 
-static int32_t sw_launch(const SwGeom& g, float alpha, const float* w, const float* x, float* bimg, float beta,
+static int32_t sw_launch(const SwGeom& g_in, float alpha, const float* w, const float* x, float* bimg, float beta,
                          float* y, int* status, const CUtensorMap& map, cudaStream_t stream,
                          float* stat_part = nullptr, float* sums = nullptr, float* sqsums = nullptr)
 {
+    SwGeom g = g_in;
+#if DCB_SW_KNOCKOUT
+    // knock-out bits for timing experiments (results are wrong with any of them set)
+    g.nsets = std::getenv("DCB_SW_DBG") ? std::atoi(std::getenv("DCB_SW_DBG")) : 0;
+#endif
     CUtensorMap ymap;
     std::memset(&ymap, 0, sizeof(ymap));
     const int use_ymap = sw_make_y_map(g, y, &ymap) ? 1 : 0;
@@ -847,7 +839,7 @@ static int32_t sw_launch(const SwGeom& g, float alpha, const float* w, const flo
         grid = g.units;
     const bool c4f3 = g.c == 4 && g.f[2] == 3 && g.pad[2] == 1 && g.split;
     const bool stats = stat_part != nullptr;
-    const int epi = sw_epi_warps(), iss = sw_issuers();
+    const int epi = sw_epi_warps();
     long long* prof = nullptr;
 #if DCB_SW_PROFILE
     // per-role clock accounting: one launch is measured and printed, synchronously
@@ -861,36 +853,28 @@ static int32_t sw_launch(const SwGeom& g, float alpha, const float* w, const flo
 #endif
     auto launch = [&](auto kernel) -> int32_t {
         DCB_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) (224 * 1024)));
-        kernel<<<(unsigned) grid, sw_threads(epi, iss), smem, stream>>>(g, alpha, beta, bimg, y, status, map, ymap,
-                                                                        use_ymap, stat_part, prof);
+        kernel<<<(unsigned) grid, sw_threads(epi), smem, stream>>>(g, alpha, beta, bimg, y, status, map, ymap, use_ymap,
+                                                                   stat_part, prof);
         return DCB_OK;
     };
     const bool blend = beta != 0.f;
     int32_t st;
-#define DCB_SW_PICK(EPI, ISS)                                                                                         \
+#define DCB_SW_PICK(EPI)                                                                                              \
     if (c4f3)                                                                                                         \
-        st = stats ? launch(sw_conv_kernel<true, true, false, EPI, ISS>)                                              \
-                   : (blend ? launch(sw_conv_kernel<true, false, true, EPI, ISS>)                                     \
-                            : launch(sw_conv_kernel<true, false, false, EPI, ISS>));                                  \
+        st = stats ? launch(sw_conv_kernel<true, true, false, EPI>)                                                   \
+                   : (blend ? launch(sw_conv_kernel<true, false, true, EPI>)                                          \
+                            : launch(sw_conv_kernel<true, false, false, EPI>));                                       \
     else                                                                                                              \
-        st = stats ? launch(sw_conv_kernel<false, true, false, EPI, ISS>)                                             \
-                   : (blend ? launch(sw_conv_kernel<false, false, true, EPI, ISS>)                                    \
-                            : launch(sw_conv_kernel<false, false, false, EPI, ISS>));
-    if (epi == 12 && iss == 2)
+        st = stats ? launch(sw_conv_kernel<false, true, false, EPI>)                                                  \
+                   : (blend ? launch(sw_conv_kernel<false, false, true, EPI>)                                         \
+                            : launch(sw_conv_kernel<false, false, false, EPI>));
+    if (epi == 12)
     {
-        DCB_SW_PICK(12, 2)
-    }
-    else if (epi == 12)
-    {
-        DCB_SW_PICK(12, 1)
-    }
-    else if (iss == 2)
-    {
-        DCB_SW_PICK(8, 2)
+        DCB_SW_PICK(12)
     }
     else
     {
-        DCB_SW_PICK(8, 1)
+        DCB_SW_PICK(8)
     }
 #undef DCB_SW_PICK
     if (st != DCB_OK)
@@ -904,7 +888,7 @@ static int32_t sw_launch(const SwGeom& g, float alpha, const float* w, const flo
         DCB_CUDA_TRY(cudaStreamSynchronize(stream));
         DCB_CUDA_TRY(cudaMemcpy(h.data(), prof, prof_n * sizeof(long long), cudaMemcpyDeviceToHost));
         cudaFree(prof);
-        const int t0 = sw_tma_warp(iss), e0 = sw_epi_warp0(iss);
+        const int t0 = TC_TMA_WARP, e0 = TC_TMA_WARP + 1;
         auto role = [&](const char* name, int w_lo, int w_hi, const char* const* labels) {
             double acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
             long long n = 0;
@@ -923,7 +907,7 @@ static int32_t sw_launch(const SwGeom& g, float alpha, const float* w, const flo
             std::fprintf(stderr, "[sw prof] %-10s warps %lld total %.0f:", name, n, acc[7] / n);
             for (int i = 0; i < 5; ++i)
                 std::fprintf(stderr, " %s %.1f%%", labels[i], 100.0 * acc[i] / acc[7]);
-            std::fprintf(stderr, "\n");
+            std::fprintf(stderr, " | extra clocks per warp %.0f\n", acc[5] / n);
         };
         const char* lc[5] = {"wait_raw", "convert", "wait_a_empty", "st+arrive", "other"};
         const char* li[5] = {"wait_row_free", "wait_a_full", "issue", "-", "other"};

@@ -115,9 +115,12 @@ __device__ __forceinline__ bool mbar_wait_t(uint64_t* bar, uint32_t parity, vola
     return false;
 }
 
+#ifndef DCB_TC_WAIT_SLEEP_NS
+#define DCB_TC_WAIT_SLEEP_NS 20
+#endif
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag)
 {
-    return mbar_wait_t<20>(bar, parity, abort_flag);
+    return mbar_wait_t<DCB_TC_WAIT_SLEEP_NS>(bar, parity, abort_flag);
 }
 
 __device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes,

@@ -61,6 +61,17 @@ namespace
 #ifndef DCB_SW_PROFILE
 #define DCB_SW_PROFILE 0
 #endif
+// Timing knock-outs (a build with -DDCB_SW_KNOCKOUT=1 only; results are wrong
+// with any bit set): bits of DCB_SW_DBG switch single pieces of work off so
+// that what the kernel's time depends on can be measured.
+#ifndef DCB_SW_KNOCKOUT
+#define DCB_SW_KNOCKOUT 0
+#endif
+#if DCB_SW_KNOCKOUT
+#define SW_DBG(bit) ((g.nsets >> (bit)) & 1)
+#else
+#define SW_DBG(bit) 0
+#endif
 #if DCB_SW_PROFILE
 #define SW_PROF_DECL long long pf_t = clock64(), pf_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; const long long pf_t0 = pf_t;
 #define SW_PROF_MARK(slot)                                                                                            \
@@ -83,8 +94,7 @@ namespace
 #endif
 
 constexpr int SW_NBK = 16; // accumulator columns per (output row, plane slot)
-constexpr int SW_EPI_DEFAULT = 8;
-constexpr int SW_ISS_DEFAULT = 1;
+
 
 struct SwGeom
 {
@@ -283,27 +293,15 @@ __device__ __forceinline__ void sw_convert_c4f3(uint32_t raw_lane, uint32_t pitc
 // and a zeroing store back to back, well over a thousand clocks with MMAs in
 // flight, and the issuers wait for the hand-back: the more rows of a plane are
 // in retirement at once, the shorter the step.
-// ISS: MMA-issuing warps per converter group.  One tcgen05.mma keeps its
-// issuing thread busy for 150 to 200 clocks while the tensor pipe needs about 70
-// for it (N = 144): with ISS = 2 the k-steps of a row are split over two warps
-// that issue side by side into the same accumulators.
-// Warps: converters 0..11, issuers 12..12+3*ISS-1, the copy warp, then (from the
-// next multiple of four, so that warp & 3 is the TMEM quadrant) the epilogue.
-__host__ __device__ constexpr int sw_tma_warp(int iss)
+// Warps: converters 0..11, issuers 12..14, the copy warp 15, epilogue 16..16+EPI-1
+// (warp & 3 is the TMEM quadrant).
+__host__ __device__ constexpr int sw_threads(int epi)
 {
-    return TC_MMA_WARP + TC_GROUPS_MAX * iss;
-}
-__host__ __device__ constexpr int sw_epi_warp0(int iss)
-{
-    return (sw_tma_warp(iss) + 1 + 3) & ~3;
-}
-__host__ __device__ constexpr int sw_threads(int epi, int iss)
-{
-    return (sw_epi_warp0(iss) + epi) * 32;
+    return (TC_TMA_WARP + 1 + epi) * 32;
 }
 
-template <bool C4F3, bool STATS, bool BLEND, int EPI, int ISS>
-__global__ void __launch_bounds__(sw_threads(EPI, ISS), 1)
+template <bool C4F3, bool STATS, bool BLEND, int EPI>
+__global__ void __launch_bounds__(sw_threads(EPI), 1)
     sw_conv_kernel(SwGeom g, float alpha, float beta, const float* __restrict__ bimg, float* y, int* status,
                    const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap ymap, int use_ymap,
                    float* __restrict__ stat_part, long long* prof)
@@ -329,17 +327,20 @@ __global__ void __launch_bounds__(sw_threads(EPI, ISS), 1)
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int fd = g.f[0], fh = g.f[1], R = g.rows, G = g.groups;
+#if DCB_SW_PROFILE
+    __shared__ volatile long long pf_issue_end[32], pf_freed[32]; // clocks: row i issued / row j handed back
+#endif
 
     if (tid == 0)
     {
         for (int s = 0; s < g.a_slots; ++s)
         {
             mbar_init(&a_full[s], 4);
-            mbar_init(&a_empty[s], ISS);
+            mbar_init(&a_empty[s], 1);
         }
         for (int r = 0; r < 32; ++r)
         {
-            mbar_init(&row_done[r], ISS);
+            mbar_init(&row_done[r], 1);
             mbar_init(&row_free[r], 4);
         }
         for (int r = 0; r < g.raw_slots; ++r)
@@ -359,7 +360,7 @@ __global__ void __launch_bounds__(sw_threads(EPI, ISS), 1)
     }
     // k-row table: offset of the tap inside a raw chunk row, and what the row
     // carries: 0 hi part, 1 lo part, 2 zero
-    for (int r = tid; r < g.kr; r += sw_threads(EPI, ISS))
+    for (int r = tid; r < g.kr; r += sw_threads(EPI))
     {
         const int part = r / g.crows, rem = r % g.crows;
         const int c = rem / g.f[2], kw = rem % g.f[2];
@@ -367,7 +368,7 @@ __global__ void __launch_bounds__(sw_threads(EPI, ISS), 1)
         const uint32_t sel = part < (g.split ? 3 : 1) ? (part == 1 ? 1u : 0u) : 2u;
         ktab[r] = sel == 2u ? ((2u << 16) | 4u) : (off | (sel << 16));
     }
-    for (int i = tid; i < g.b_bytes / 16; i += sw_threads(EPI, ISS))
+    for (int i = tid; i < g.b_bytes / 16; i += sw_threads(EPI))
         reinterpret_cast<float4*>(b_smem)[i] = reinterpret_cast<const float4*>(bimg)[i];
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     tc_fence_before();
@@ -391,8 +392,11 @@ __global__ void __launch_bounds__(sw_threads(EPI, ISS), 1)
         const int Rc = g.chunk_rows;
         const uint32_t pitch = (uint32_t) (g.chunk_rows * TC_RAW_W);
         int lap_a = 0;
-        uint32_t cslot = 0, cphase = 0, a_phase = 1, base = 0;
+        uint32_t cslot = 0, cphase = 0, a_phase = 1;
         bool a_first = true;
+        // this group's rows of every step: a contiguous block (see the issuers)
+        const int rpg = (R + G - 1) / G;
+        const int my_lo = gq * rpg, my_hi = min(R, my_lo + rpg);
         SW_PROF_DECL
         for (uint32_t u = blockIdx.x; u < nunits && ok; u += gridDim.x)
         {
@@ -403,14 +407,13 @@ __global__ void __launch_bounds__(sw_threads(EPI, ISS), 1)
                     continue;
                 for (int ch = 0; ch < g.chunks_pp && ok; ++ch)
                 {
-                    const int lo = ch * Rc, hi = min(R, (ch + 1) * Rc);
-                    int i = lo + (gq + G - (int) ((base + (uint32_t) lo) % (uint32_t) G)) % G;
+                    const int lo = ch * Rc, hi = min(min(R, (ch + 1) * Rc), my_hi);
                     bool have = false;
-                    for (; i < hi && ok; i += G)
+                    for (int i = max(lo, my_lo); i < hi && ok; ++i)
                     {
                         const int a_slot = gq + G * lap_a;
                         SW_PROF_MARK(4)
-                        if (!have)
+                        if (!have && !SW_DBG(6))
                             ok = mbar_wait(&raw_full[cslot], cphase, abort_flag);
                         have = true;
                         SW_PROF_MARK(0)
@@ -423,17 +426,29 @@ __global__ void __launch_bounds__(sw_threads(EPI, ISS), 1)
                         if (C4F3)
                         {
                             uint32_t v[5][8];
-                            sw_convert_c4f3(raw_s, pitch, v);
+                            if (!SW_DBG(5))
+                                sw_convert_c4f3(raw_s, pitch, v);
+                            else
+                            {
+#pragma unroll
+                                for (int ck = 0; ck < 5; ++ck)
+#pragma unroll
+                                    for (int e = 0; e < 8; ++e)
+                                        v[ck][e] = 0u;
+                            }
                             SW_PROF_MARK(1)
-                            if (!a_first)
+                            if (!a_first && !SW_DBG(10))
                                 ok = mbar_wait(&a_empty[a_slot], a_phase, abort_flag);
                             SW_PROF_MARK(2)
                             if (!ok)
                                 break;
                             tc_fence_after();
+                            if (!SW_DBG(0))
+                            {
 #pragma unroll
-                            for (int ck = 0; ck < 5; ++ck)
-                                tmem_st8(a_addr + (uint32_t) (ck * 8), v[ck]);
+                                for (int ck = 0; ck < 5; ++ck)
+                                    tmem_st8(a_addr + (uint32_t) (ck * 8), v[ck]);
+                            }
                         }
                         else
                         {
@@ -462,7 +477,11 @@ __global__ void __launch_bounds__(sw_threads(EPI, ISS), 1)
                             a_first = false;
                         }
                     }
-                    // every converter warp releases every chunk
+                    // every converter warp releases every chunk, and only after it
+                    // has seen it arrive (a group without rows in this chunk too:
+                    // no warp runs further ahead of the copies than the ring is deep)
+                    if (!have && ok && !SW_DBG(6))
+                        ok = mbar_wait(&raw_full[cslot], cphase, abort_flag);
                     __syncwarp();
                     if (lane == 0)
                         mbar_arrive(&raw_empty[cslot]);
@@ -472,12 +491,11 @@ __global__ void __launch_bounds__(sw_threads(EPI, ISS), 1)
                         cphase ^= 1;
                     }
                 }
-                base = (base + (uint32_t) R) % (uint32_t) G;
             }
         }
         SW_PROF_FLUSH(prof)
     }
-    else if (warp == sw_tma_warp(ISS))
+    else if (warp == TC_TMA_WARP)
     {
         // ------------------------------------------------------------------
         // bulk tensor copies: chunk_rows raw rows of every channel per copy.
@@ -497,6 +515,8 @@ __global__ void __launch_bounds__(sw_threads(EPI, ISS), 1)
                 for (int ch = 0; ch < g.chunks_pp; ++ch)
                 {
                     SW_PROF_MARK(4)
+                    if (SW_DBG(6))
+                        continue;
                     if (!first_lap)
                         ok = mbar_wait(&raw_empty[slot], empty_phase, abort_flag);
                     SW_PROF_MARK(0)
@@ -522,14 +542,13 @@ __global__ void __launch_bounds__(sw_threads(EPI, ISS), 1)
         }
         SW_PROF_FLUSH(prof)
     }
-    else if (warp >= TC_MMA_WARP && warp < sw_tma_warp(ISS))
+    else if (warp >= TC_MMA_WARP && warp < TC_TMA_WARP)
     {
         // ------------------------------------------------------------------
-        // MMA issue: the issuers of group mq take the rows converter group mq
-        // produced, each its share of the row's k-steps.  Lane i issues staged
-        // row i (its descriptors depend on i only).
+        // MMA issue: issuer mq takes the rows converter group mq produced.
+        // Lane i issues staged row i (its descriptors depend on i only).
         // ------------------------------------------------------------------
-        const int mq = (warp - TC_MMA_WARP) % TC_GROUPS_MAX, part = (warp - TC_MMA_WARP) / TC_GROUPS_MAX;
+        const int mq = warp - TC_MMA_WARP;
         if (mq < G)
         {
             const int my_i = lane;
@@ -545,23 +564,32 @@ __global__ void __launch_bounds__(sw_threads(EPI, ISS), 1)
                 make_desc(smem_u32(b_smem), b_lbo, 128u, 0u) + (uint64_t) ((uint32_t) (j_lo * blk));
             const uint32_t rot_units = (uint32_t) g.b_rot_bytes >> 4;
             const uint32_t a_ring = tmem_base + a_col0;
-            // this warp's k-steps of every row: [ks_lo, ks_hi)
-            const int ks_split = ISS == 1 ? g.ksteps : (g.ksteps + 1) / 2;
-            const int ks_lo = part == 0 ? 0 : ks_split, ks_hi = part == 0 ? ks_split : g.ksteps;
+            const int ks_lo = 0, ks_hi = g.ksteps;
             const int laps_a = g.a_slots / G;
             int lap_a = 0;
-            uint32_t full_phase = 0, step = 0, base = 0;
+            uint32_t full_phase = 0, step = 0;
+            // Rows are dealt to the issuers in contiguous blocks, not round robin.
+            // MMAs whose accumulator columns overlap are executed one after the
+            // other by the tensor pipe, about 150 clocks apart whatever their size;
+            // only MMAs on disjoint columns overlap in the pipe.  A staged row
+            // adds into the fh output rows above it, so rows dealt round robin
+            // (issuers on rows i, i+1, i+2 at any time) always collide, while
+            // blocks keep the issuers at least fh rows apart whenever a block has
+            // fh rows or more.
+            const int rpg = (R + G - 1) / G;
+            const int my_lo = mq * rpg, my_hi = min(R, my_lo + rpg);
+            int rot = 0; // d mod fd, kept by counting
             SW_PROF_DECL
             for (uint32_t u = blockIdx.x; u < nunits && ok; u += gridDim.x)
             {
                 const SwUnit t = sw_unit(g, u);
-                for (int d = t.d_first; d < t.d_stop && ok; ++d, ++step)
+                rot = sw_mod(t.d_first, fd);
+                for (int d = t.d_first; d < t.d_stop && ok; ++d, ++step, rot = rot + 1 == fd ? 0 : rot + 1)
                 {
                     const bool real = sw_real(g, t, d);
                     const uint32_t par = step & 1;
-                    const uint64_t bd0 = my_b_desc + (uint64_t) ((uint32_t) sw_mod(d, fd) * rot_units);
-                    int i = real ? (mq + G - (int) (base % (uint32_t) G)) % G : mq;
-                    for (; i < R && ok; i += G)
+                    const uint64_t bd0 = my_b_desc + (uint64_t) ((uint32_t) rot * rot_units);
+                    for (int i = my_lo; i < my_hi && ok; ++i)
                     {
                         // The blocks this row adds into (output rows r_lo..r_hi) must
                         // have been retired.  Each epilogue warp of a quadrant retires
@@ -572,15 +600,21 @@ __global__ void __launch_bounds__(sw_threads(EPI, ISS), 1)
                         // before this wait has seen it.
                         const int r_hi = min(i, g.th - 1), r_lo = max(0, i - fh + 1);
                         SW_PROF_MARK(4)
-                        for (int r = r_hi; r >= r_lo && r > r_hi - EPI / 4 && ok; --r)
+                        for (int r = r_hi; r >= r_lo && r > r_hi - EPI / 4 && ok && !SW_DBG(8); --r)
                             ok = mbar_wait_t<0>(&row_free[r], par, abort_flag);
                         SW_PROF_MARK(0)
+#if DCB_SW_PROFILE
+                        // how long ago the last row this one needed was handed back
+                        if (step > 2)
+                            pf_acc[5] += clock64() - pf_freed[r_hi];
+#endif
                         if (!ok)
                             break;
                         if (real)
                         {
                             const uint32_t slot = (uint32_t) (mq + G * lap_a);
-                            ok = mbar_wait_t<0>(&a_full[slot], full_phase, abort_flag);
+                            if (!SW_DBG(11))
+                                ok = mbar_wait_t<0>(&a_full[slot], full_phase, abort_flag);
                             SW_PROF_MARK(1)
                             if (!ok)
                                 break;
@@ -589,15 +623,26 @@ __global__ void __launch_bounds__(sw_threads(EPI, ISS), 1)
                             {
                                 uint32_t a_addr = a_ring + slot * (uint32_t) g.kr + 8u * (uint32_t) ks_lo;
                                 uint64_t bd = bd0 + (uint64_t) (b_kstep_units * (uint32_t) ks_lo);
-                                for (int ks = ks_lo; ks < ks_hi; ++ks)
+                                for (int ks = ks_lo; ks < (SW_DBG(3) ? ks_lo + 1 : ks_hi); ++ks)
                                 {
-                                    mma_tf32_ts(my_d, a_addr, bd, my_idesc);
+                                    mma_tf32_ts(my_d, a_addr, bd, SW_DBG(4) ? ((my_idesc & ~(0x3fu << 17)) | (2u << 17)) : my_idesc);
                                     a_addr += 8;
                                     bd += b_kstep_units;
                                 }
-                                mma_commit(&a_empty[slot]);
-                                mma_commit(&row_done[i]);
+                                if (SW_DBG(7))
+                                {
+                                    mbar_arrive(&a_empty[slot]);
+                                    mbar_arrive(&row_done[i]);
+                                }
+                                else
+                                {
+                                    mma_commit(&a_empty[slot]);
+                                    mma_commit(&row_done[i]);
+                                }
                                 tc_fence_before();
+#if DCB_SW_PROFILE
+                                pf_issue_end[i] = clock64();
+#endif
                             }
                             __syncwarp();
                             SW_PROF_MARK(2)
@@ -615,20 +660,18 @@ __global__ void __launch_bounds__(sw_threads(EPI, ISS), 1)
                             __syncwarp();
                         }
                     }
-                    if (real)
-                        base = (base + (uint32_t) R) % (uint32_t) G;
                 }
             }
             SW_PROF_FLUSH(prof)
         }
     }
-    else if (warp >= sw_epi_warp0(ISS))
+    else if (warp >= (TC_TMA_WARP + 1))
     {
         // ------------------------------------------------------------------
         // epilogue: after step d retire output plane d + pad - (fd-1)
         // ------------------------------------------------------------------
         const int quad = warp & 3;
-        const int ew = warp - sw_epi_warp0(ISS); // index among the epilogue warps
+        const int ew = warp - (TC_TMA_WARP + 1); // index among the epilogue warps
         const int half = ew >> 2, nhalf = EPI / 4;
         const uint32_t lane_addr = tmem_base + ((uint32_t) (quad * 32) << 16);
         const int nk = g.k;
@@ -680,9 +723,18 @@ __global__ void __launch_bounds__(sw_threads(EPI, ISS), 1)
                                 old[k] = yrow[(size_t) k * ysc];
                     }
                     SW_PROF_MARK(4)
-                    for (int i = j; i < j + fh && ok; ++i)
+                    for (int i = j; i < j + fh && ok && !SW_DBG(9); ++i)
                         ok = mbar_wait(&row_done[i], par, abort_flag);
                     SW_PROF_MARK(0)
+#if DCB_SW_PROFILE
+                    if (step > 2 && sw_real(g, t, d))
+                    {
+                        long long last = 0;
+                        for (int i = j; i < j + fh; ++i)
+                            last = pf_issue_end[i] > last ? pf_issue_end[i] : last;
+                        pf_acc[5] += clock64() - last; // issue of the last row needed -> seen complete
+                    }
+#endif
                     if (!ok)
                         break;
                     tc_fence_after();
@@ -700,7 +752,12 @@ __global__ void __launch_bounds__(sw_threads(EPI, ISS), 1)
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0)
+                    {
+#if DCB_SW_PROFILE
+                        pf_freed[j] = clock64();
+#endif
                         mbar_arrive(&row_free[j]);
+                    }
                     SW_PROF_MARK(2)
                     if (!wr)
                         continue;

@@ -18,7 +18,7 @@ import random
 import pytest
 
 
-def simulate(groups, th, fh, steps, seed, virtual, wait_rows, cg=1, nhalf=2):
+def simulate(groups, th, fh, steps, seed, virtual, wait_rows, cg=1, nhalf=2, blocked=False):
     """Returns ("ok" | "deadlock", wrong_passes).  cg > 1: the multi-group
     kernel, where row i is cg sub-rows dealt to the issuers in sequence and
     row_done[i] needs all of them."""
@@ -46,6 +46,23 @@ def simulate(groups, th, fh, steps, seed, virtual, wait_rows, cg=1, nhalf=2):
     wrong = []
     for j in range(th):
         arrive(("free", j))  # the epilogue's initial zeroing hands every row out once
+
+    def issuer_blocked(mq):
+        # the sweep kernel: issuer mq owns a contiguous block of rows in every step
+        rpg = -(-rows // groups)
+        for step in range(steps):
+            parity = step & 1
+            for i in range(mq * rpg, min(rows, (mq + 1) * rpg)):
+                for j in wait_rows(i, th, fh):
+                    while not passes(("free", j), parity):
+                        yield "wait"
+                    if completions[("free", j)] != step + 1:
+                        wrong.append(("issuer", mq, step, i, j))
+                for j in range(max(0, i - fh + 1), min(i, th - 1) + 1):
+                    if completions[("free", j)] < step + 1:
+                        wrong.append(("issuer adds into an unretired row", mq, step, i, j))
+                yield "work"
+                arrive(("done", i))
 
     def issuer(mq):
         base = 0
@@ -82,7 +99,7 @@ def simulate(groups, th, fh, steps, seed, virtual, wait_rows, cg=1, nhalf=2):
                 yield "work"
                 arrive(("free", j))
 
-    threads = [issuer(m) for m in range(groups)] + [epilogue(h) for h in range(nhalf)]
+    threads = [(issuer_blocked if blocked else issuer)(m) for m in range(groups)] + [epilogue(h) for h in range(nhalf)]
     alive = [True] * len(threads)
     idle = 0
     while any(alive):
@@ -119,6 +136,19 @@ def test_protocol_never_locks_or_passes_early(fh):
                 virtual = (0, 1, 8, 9) if seed % 2 else (0, 5, 9)
                 state, wrong = simulate(groups, th, fh, 10, seed, virtual, touched_rows)
                 assert state == "ok" and not wrong, (fh, groups, th, seed, state, wrong[:2])
+
+
+@pytest.mark.parametrize("nhalf", [2, 3, 4])
+def test_protocol_with_rows_dealt_in_blocks(nhalf):
+    """The sweep kernel deals a step's rows to its issuers in contiguous blocks
+    (so that concurrent MMAs touch disjoint accumulator columns)."""
+    for fh in (1, 2, 3, 5):
+        for groups in range(1, min(fh, 3) + 1):
+            for th in range(2, 14):
+                for seed in range(6):
+                    state, wrong = simulate(groups, th, fh, 10, seed, (), lambda i, t, f: touched_rows(i, t, f, nhalf),
+                                            nhalf=nhalf, blocked=True)
+                    assert state == "ok" and not wrong, (nhalf, fh, groups, th, seed, state, wrong[:2])
 
 
 @pytest.mark.parametrize("nhalf", [3, 4])
