@@ -23,6 +23,7 @@ kernel on the path is launched by the library.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Callable, List, Optional, Sequence
 
 import numpy as np
@@ -841,13 +842,19 @@ class Allreduce:
 
 
 class Options:
-    """backend::Options (dnn_backend.hpp:46-63); the fields this path reads."""
+    """backend::Options (dnn_backend.hpp:46-63) with the environment overrides
+    of legacy/src/dnn_backend/options.cpp:13-71: a variable that is SET (to
+    anything, as in the reference) turns its option on.  ``math_mode`` has no
+    counterpart there."""
 
     def __init__(self, overlap_halo_exchange=False, deterministic=True, enable_profiling=False,
-                 math_mode=_abi.MATH_FP32):
-        self.overlap_halo_exchange = overlap_halo_exchange
-        self.deterministic = deterministic
-        self.enable_profiling = enable_profiling
+                 math_mode=_abi.MATH_FP32, ws_capacity_factor=1.0):
+        env = os.environ
+        self.overlap_halo_exchange = overlap_halo_exchange or "DISTCONV_OVERLAP_HALO_EXCHANGE" in env
+        self.deterministic = deterministic or "DISTCONV_DETERMINISTIC" in env
+        self.enable_profiling = enable_profiling or any(
+            k in env for k in ("DISTCONV_ENABLE_PROFILING", "DISTCONV_PROFILING", "DISTCONV_NVTX"))
+        self.ws_capacity_factor = float(env.get("DISTCONV_WS_CAPACITY_FACTOR", ws_capacity_factor))
         self.math_mode = math_mode
 
 
@@ -1086,11 +1093,25 @@ class Convolution:
         if input.get_local_size() == 0 or output.get_local_size() == 0:
             return 0
         s = self.be.stream
+        prof = self.be.options.enable_profiling
         if not skip_halo_exchange and getattr(self, "_ov", None) is not None:
             return self._forward_overlapped(alpha, input, filter, beta, output)
+        if prof:  # the reference's range names (convolution.hpp:361-364, 420-423, 2695-2708)
+            torch.cuda.nvtx.range_push("conv/forward")
+        try:
+            return self._forward(alpha, input, filter, beta, output, skip_halo_exchange, statistics, s, prof)
+        finally:
+            if prof:
+                torch.cuda.nvtx.range_pop()
+
+    def _forward(self, alpha, input, filter, beta, output, skip_halo_exchange, statistics, s, prof):
         if not skip_halo_exchange:
+            if prof:
+                torch.cuda.nvtx.range_push("conv/forward/exchange_halo")
             self._clear_halos(input, s)
             self.forward_exchange_halo(input, s)
+            if prof:
+                torch.cuda.nvtx.range_pop()
         if statistics is not None and float(beta) == 0.0 and input.is_split_root():
             st = _abi.lib().dcb_conv_fwd_stats(self._plan_fwd, float(alpha), _ptr(input.nd_ptr(self._x_lo)),
                                                _ptr(filter.data_ptr()), _ptr(output.get_base_ptr()),

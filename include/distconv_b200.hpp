@@ -27,15 +27,29 @@
 #include <cuda_runtime_api.h>
 
 #include <algorithm>
+#include <array>
 #include <cstdint>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <fstream>
 #include <functional>
+#include <iostream>
 #include <memory>
+#include <sstream>
 #include <stdexcept>
 #include <string>
+#include <type_traits>
 #include <vector>
+
+#if defined(DISTCONV_B200_HAS_MPI)
+#include <mpi.h>
+#endif
+#if defined(__has_include)
+#if __has_include(<nvtx3/nvToolsExt.h>) && !defined(DISTCONV_B200_NO_NVTX)
+#include <nvtx3/nvToolsExt.h>
+#endif
+#endif
 
 namespace distconv
 {
@@ -43,35 +57,297 @@ namespace distconv
 using index_t = int64_t;
 using int_vector = std::vector<int>;
 
+// ---- vocabulary of legacy/include/distconv/base.hpp:23-394 ------------------
 enum Side
 {
     LHS = 0,
     RHS = 1
 };
+const Side SIDES[2] = {LHS, RHS};
 
+inline Side operator~(const Side& s)
+{
+    return static_cast<Side>((~static_cast<int>(s)) & 1);
+}
+inline std::ostream& operator<<(std::ostream& os, const Side& s)
+{
+    return os << (s == LHS ? "LHS" : "RHS");
+}
+
+template <int ND, typename F>
+void apply_to_sides(F&& f)
+{
+    for (int i = 0; i < ND; ++i)
+        for (Side side : SIDES)
+            f(i, side);
+}
+template <typename F>
+void apply_to_sides(int num_dims, F&& f)
+{
+    for (int i = 0; i < num_dims; ++i)
+        for (Side side : SIDES)
+            f(i, side);
+}
+template <typename F>
+void apply_to_spatial_sides(int num_dims, F&& f)
+{
+    for (int i = 0; i < num_dims - 2; ++i)
+        for (Side side : SIDES)
+            f(i, side);
+}
+template <int ND, typename F>
+void apply_to_spatial_sides(F&& f)
+{
+    for (int i = 0; i < ND - 2; ++i)
+        for (Side side : SIDES)
+            f(i, side);
+}
+
+// one attribute per side of a boundary (base.hpp:58-79)
+template <typename T>
+struct BoundaryAttributes
+{
+    std::array<T, 2> m_attrs;
+    BoundaryAttributes() = default;
+    BoundaryAttributes(const T& v) : BoundaryAttributes(v, v) {}
+    BoundaryAttributes(const T& lhs, const T& rhs) : m_attrs({lhs, rhs}) {}
+    T& operator()(Side s) { return m_attrs[s]; }
+    const T& operator()(Side s) const { return m_attrs[s]; }
+    T* data() { return m_attrs.data(); }
+    const T* data() const { return m_attrs.data(); }
+};
+
+// per dimension and side, growing on demand (base.hpp:125-173)
+template <typename T>
+class BoundaryAttributesV
+{
+public:
+    BoundaryAttributesV() = default;
+    BoundaryAttributesV(const T& lhs, const T& rhs) : m_default(lhs, rhs) {}
+    BoundaryAttributesV(const T& attr) : BoundaryAttributesV(attr, attr) {}
+    T& operator()(int d, Side s)
+    {
+        expand_if_needed(d);
+        return m_attrs.at(d)(s);
+    }
+    const T& operator()(int d, Side s) const { return m_attrs.at(d)(s); }
+    T* operator()(int d)
+    {
+        expand_if_needed(d);
+        return m_attrs.at(d).data();
+    }
+    const T* operator()(int d) const { return m_attrs.at(d).data(); }
+    void clear() { m_attrs.clear(); }
+
+private:
+    void expand_if_needed(int d)
+    {
+        if (d >= (int) m_attrs.size())
+            m_attrs.resize(d + 1, m_default);
+    }
+    BoundaryAttributes<T> m_default;
+    std::vector<BoundaryAttributes<T>> m_attrs;
+};
+
+// Every method maps to the one peer-store transport (base.hpp:175-240).
 enum class HaloExchangeMethod
 {
     MPI,
     AL,
     P2P,
     HYBRID
-}; // all map to the one peer-store transport
+};
+inline std::ostream& operator<<(std::ostream& os, const HaloExchangeMethod& m)
+{
+    static const char* names[] = {"MPI", "AL", "P2P", "HYBRID"};
+    return os << names[(int) m];
+}
+// Unknown names are a programmer error: the reference aborts, this throws.
+inline HaloExchangeMethod GetHaloExchangeMethod(const std::string& method)
+{
+    if (method == "MPI")
+        return HaloExchangeMethod::MPI;
+    if (method == "AL")
+        return HaloExchangeMethod::AL;
+    if (method == "P2P")
+        return HaloExchangeMethod::P2P;
+    if (method == "HYBRID")
+        return HaloExchangeMethod::HYBRID;
+    throw std::invalid_argument("Unknown method name for halo exchange: " + method);
+}
 
+enum class ShuffleMethod
+{
+    MPI,
+    AL,
+    P2P,
+    HYBRID
+};
+inline std::ostream& operator<<(std::ostream& os, const ShuffleMethod& m)
+{
+    static const char* names[] = {"MPI", "AL", "P2P", "HYBRID"};
+    return os << names[(int) m];
+}
+inline ShuffleMethod GetShuffleMethod(const std::string& method)
+{
+    if (method == "MPI")
+        return ShuffleMethod::MPI;
+    if (method == "AL")
+        return ShuffleMethod::AL;
+    if (method == "P2P")
+        return ShuffleMethod::P2P;
+    if (method == "HYBRID")
+        return ShuffleMethod::HYBRID;
+    throw std::invalid_argument("Unknown shuffle method: " + method);
+}
+
+// Only NONE / AUTO (= none) are provided: spatial parallelism is the path.
+enum class ChannelParallelismAlgorithm
+{
+    NONE,
+    AUTO,
+    X,
+    Y,
+    W
+};
+inline std::ostream& operator<<(std::ostream& os, const ChannelParallelismAlgorithm& a)
+{
+    static const char* names[] = {"NONE", "AUTO", "X", "Y", "W"};
+    return os << names[(int) a];
+}
+
+// MPI and AL_NCCL are the reference's names (base.hpp:308-366); both run the
+// peer-memory all-reduce kernel here, which PEER names directly.
 enum class BatchnormImpl
 {
     MPI,
     AL_NCCL,
     PEER
 };
-
-enum class ChannelParallelismAlgorithm
+inline std::ostream& operator<<(std::ostream& os, const BatchnormImpl& v)
 {
-    NONE,
-    AUTO
-};
+    static const char* names[] = {"MPI", "AL_NCCL", "PEER"};
+    return os << names[(int) v];
+}
+inline BatchnormImpl GetBatchnormImpl(const std::string& impl)
+{
+    if (impl == "MPI")
+        return BatchnormImpl::MPI;
+    if (impl == "AL_NCCL")
+        return BatchnormImpl::AL_NCCL;
+    if (impl == "PEER")
+        return BatchnormImpl::PEER;
+    throw std::invalid_argument("Unknown implementation name for batchnorm: " + impl);
+}
 
 namespace util
 {
+// Rank used as the prefix of the MPI print streams.  LocaleMPI sets it; before
+// that it comes from the launcher's environment.
+inline int& process_rank()
+{
+    static int rank = [] {
+        for (const char* name : {"RANK", "OMPI_COMM_WORLD_RANK", "PMI_RANK", "SLURM_PROCID"})
+            if (const char* v = std::getenv(name))
+                return std::atoi(v);
+        return 0;
+    }();
+    return rank;
+}
+
+// The reference's print streams (legacy/include/distconv/util/util.hpp:142-265,
+// util_mpi.hpp): a line is assembled by operator<< and written with a newline
+// when the temporary dies.  Debug streams print only when DISTCONV_DEBUG is set;
+// MPI streams prefix the rank; MPIRoot streams print on rank 0 only.
+class PrintStream
+{
+public:
+    PrintStream(std::ostream& os, bool enabled, const std::string& prefix = "") : m_os(os), m_enabled(enabled)
+    {
+        if (m_enabled)
+            m_line << prefix;
+    }
+    PrintStream(const PrintStream&) = delete;
+    ~PrintStream()
+    {
+        if (m_enabled)
+            m_os << m_line.str() << std::endl;
+    }
+    template <typename T>
+    PrintStream& operator<<(const T& v)
+    {
+        if (m_enabled)
+            m_line << v;
+        return *this;
+    }
+
+private:
+    std::ostream& m_os;
+    bool m_enabled;
+    std::ostringstream m_line;
+};
+inline bool debug_enabled()
+{
+    static const bool on = std::getenv("DISTCONV_DEBUG") != nullptr;
+    return on;
+}
+inline std::string rank_prefix()
+{
+    return "[" + std::to_string(process_rank()) + "] ";
+}
+struct PrintStreamDebug : PrintStream
+{
+    PrintStreamDebug() : PrintStream(std::cerr, debug_enabled()) {}
+};
+struct PrintStreamInfo : PrintStream
+{
+    PrintStreamInfo() : PrintStream(std::cout, true) {}
+};
+struct PrintStreamWarning : PrintStream
+{
+    PrintStreamWarning() : PrintStream(std::cerr, true, "Warning: ") {}
+};
+struct PrintStreamError : PrintStream
+{
+    PrintStreamError() : PrintStream(std::cerr, true, "Error: ") {}
+};
+struct MPIPrintStreamDebug : PrintStream
+{
+    MPIPrintStreamDebug() : PrintStream(std::cerr, debug_enabled(), rank_prefix()) {}
+};
+struct MPIPrintStreamInfo : PrintStream
+{
+    MPIPrintStreamInfo() : PrintStream(std::cout, true, rank_prefix()) {}
+};
+struct MPIPrintStreamWarning : PrintStream
+{
+    MPIPrintStreamWarning() : PrintStream(std::cerr, true, rank_prefix() + "Warning: ") {}
+};
+struct MPIPrintStreamError : PrintStream
+{
+    MPIPrintStreamError() : PrintStream(std::cerr, true, rank_prefix() + "Error: ") {}
+};
+struct MPIRootPrintStreamDebug : PrintStream
+{
+    MPIRootPrintStreamDebug() : PrintStream(std::cerr, debug_enabled() && process_rank() == 0) {}
+};
+struct MPIRootPrintStreamInfo : PrintStream
+{
+    MPIRootPrintStreamInfo() : PrintStream(std::cout, process_rank() == 0) {}
+};
+
+// Profiler ranges (GPU_PROFILE_RANGE_PUSH / _POP of the reference, which are
+// NVTX ranges): named like the reference's ("conv/forward",
+// "conv/forward/exchange_halo", ...).  NVTX's header-only C API is used when
+// the toolkit ships it; otherwise the ranges are no-ops.
+#if defined(__has_include)
+#if __has_include(<nvtx3/nvToolsExt.h>) && !defined(DISTCONV_B200_NO_NVTX)
+#define DISTCONV_B200_HAS_NVTX 1
+#endif
+#endif
+inline void profile_range_push(const char* name);
+inline void profile_range_pop();
+
 inline void check(int32_t st, const char* what)
 {
     if (st != DCB_OK)
@@ -83,7 +359,71 @@ inline void require(bool cond, const char* what)
     if (!cond)
         throw std::invalid_argument(what);
 }
+inline void profile_range_push(const char* name)
+{
+#ifdef DISTCONV_B200_HAS_NVTX
+    nvtxRangePushA(name);
+#else
+    (void) name;
+#endif
+}
+inline void profile_range_pop()
+{
+#ifdef DISTCONV_B200_HAS_NVTX
+    nvtxRangePop();
+#endif
+}
 } // namespace util
+
+// backend::Options (legacy/include/distconv/dnn_backend/dnn_backend.hpp:46-63)
+// with the environment overrides of legacy/src/dnn_backend/options.cpp:13-71: a
+// variable that is SET (to anything, "0" included, as in the reference) turns
+// its option on.  The workspace factor and the JIT fields are carried for
+// source compatibility; plans own their workspaces and nothing is compiled at
+// run time.  math_mode has no counterpart: DCB_MATH_FP32 (3xTF32 on tensor
+// cores, fp32 quality), DCB_MATH_TF32 or DCB_MATH_FP32_SIMT.
+struct Options
+{
+    bool overlap_halo_exchange;
+    bool m_deterministic;
+    bool enable_profiling;
+    float ws_capacity_factor;
+    bool jit_verbose;
+    std::string jit_cache_path;
+    int math_mode = DCB_MATH_FP32;
+
+    Options(bool overlap_halo_exchange_in = false, bool deterministic_in = false, bool enable_profiling_in = false,
+            float ws_capacity_factor_in = 1.0f, bool jit_verbose_in = false,
+            const std::string& jit_cache_path_in = ".jitcache")
+        : overlap_halo_exchange(overlap_halo_exchange_in), m_deterministic(deterministic_in),
+          enable_profiling(enable_profiling_in), ws_capacity_factor(ws_capacity_factor_in),
+          jit_verbose(jit_verbose_in), jit_cache_path(jit_cache_path_in)
+    {
+        auto detected = [](const char* name) {
+            if (!std::getenv(name))
+                return false;
+            util::MPIRootPrintStreamDebug() << "Environment variable: " << name << " detected";
+            return true;
+        };
+        if (detected("DISTCONV_OVERLAP_HALO_EXCHANGE"))
+            overlap_halo_exchange = true;
+        if (detected("DISTCONV_DETERMINISTIC"))
+            m_deterministic = true;
+        // DISTCONV_PROFILING / DISTCONV_NVTX are the runtime's switches (legacy/src/runtime.cpp:13-21)
+        if (detected("DISTCONV_ENABLE_PROFILING") || detected("DISTCONV_PROFILING") || detected("DISTCONV_NVTX"))
+            enable_profiling = true;
+        if (detected("DISTCONV_WS_CAPACITY_FACTOR"))
+            ws_capacity_factor = (float) std::atof(std::getenv("DISTCONV_WS_CAPACITY_FACTOR"));
+        if (detected("DISTCONV_JIT_VERBOSE"))
+            jit_verbose = true;
+        if (detected("DISTCONV_JIT_CACHEPATH"))
+            jit_cache_path = std::getenv("DISTCONV_JIT_CACHEPATH");
+    }
+};
+namespace backend
+{
+using Options = ::distconv::Options;
+}
 
 namespace tensor
 {
@@ -161,7 +501,25 @@ class LocaleMPI
 {
 public:
     using Allgather = std::function<void(const void*, void*, size_t)>;
-    LocaleMPI(int rank = 0, int size = 1, Allgather ag = nullptr) : m_rank(rank), m_size(size), m_ag(std::move(ag)) {}
+    LocaleMPI(int rank = 0, int size = 1, Allgather ag = nullptr) : m_rank(rank), m_size(size), m_ag(std::move(ag))
+    {
+        util::process_rank() = rank;
+    }
+#if defined(DISTCONV_B200_HAS_MPI)
+    // The reference's constructor (tensor_mpi.hpp:18-36): rank and size of the
+    // communicator, blobs gathered with MPI_Allgather.  Compiled when the host
+    // defines DISTCONV_B200_HAS_MPI (and so provides <mpi.h>).
+    LocaleMPI(MPI_Comm comm, bool /*copy_comm*/ = true) : m_comm(comm)
+    {
+        MPI_Comm_rank(comm, &m_rank);
+        MPI_Comm_size(comm, &m_size);
+        util::process_rank() = m_rank;
+        m_ag = [comm](const void* in, void* out, size_t n) {
+            MPI_Allgather(const_cast<void*>(in), (int) n, MPI_BYTE, out, (int) n, MPI_BYTE, comm);
+        };
+    }
+    MPI_Comm get_comm() const { return m_comm; }
+#endif
     int get_rank() const { return m_rank; }
     int get_size() const { return m_size; }
     IndexVector get_rank_idx(const Distribution& dist) const
@@ -188,8 +546,21 @@ public:
     }
 
 private:
-    int m_rank, m_size;
+    int m_rank = 0, m_size = 1;
     Allgather m_ag;
+#if defined(DISTCONV_B200_HAS_MPI)
+    MPI_Comm m_comm = MPI_COMM_NULL;
+#endif
+};
+
+// A single-process locale (tensor_process.hpp): rank 0 of 1.
+class LocaleProcess
+{
+public:
+    int get_rank() const { return 0; }
+    int get_size() const { return 1; }
+    IndexVector get_rank_idx(const Distribution& dist) const { return IndexVector(dist.num_dims(), 0); }
+    void allgather(const void* in, void* out, size_t n) const { std::memcpy(out, in, n); }
 };
 
 // Allocator tags (tensor/memory_cuda.hpp:28-104).  They decide the row pitch of
@@ -206,6 +577,177 @@ struct CUDAPitchedAllocator
 {
     static index_t pitch(index_t row, bool) { return (row + 31) / 32 * 32; }
 };
+// Host memory (tensor/memory.hpp:25-55); used by the host-side gather of dump_tensor.
+struct BaseAllocator
+{
+    static index_t pitch(index_t row, bool) { return row; }
+};
+
+// Owned or aliased buffer with an allocator's deleter (tensor/memory.hpp:57-300):
+// the shared_ptr frees device (or, for BaseAllocator, host) memory when the last
+// owner goes; an alias never frees.
+template <typename Allocator>
+class Memory
+{
+public:
+    using allocator_type = Allocator;
+    Memory() = default;
+    int allocate(size_t bytes, size_t pitch_bytes = 0, size_t ldim_bytes = 0)
+    {
+        void* p = nullptr;
+        if (std::is_same<Allocator, BaseAllocator>::value)
+        {
+            p = std::malloc(bytes ? bytes : 16);
+            if (!p)
+                return -1;
+            m_managed = std::shared_ptr<void>(p, [](void* q) { std::free(q); });
+        }
+        else
+        {
+            if (cudaMalloc(&p, bytes ? bytes : 16) != cudaSuccess)
+                return -1;
+            m_managed = std::shared_ptr<void>(p, [](void* q) { cudaFree(q); });
+        }
+        m_alias = nullptr;
+        m_bytes = bytes;
+        m_pitch = pitch_bytes;
+        m_ldim = ldim_bytes;
+        return 0;
+    }
+    void alias(void* raw, size_t bytes, size_t pitch_bytes, size_t ldim_bytes)
+    {
+        m_managed.reset();
+        m_alias = raw;
+        m_bytes = bytes;
+        m_pitch = pitch_bytes;
+        m_ldim = ldim_bytes;
+    }
+    void alias(const Memory& parent)
+    {
+        m_managed.reset();
+        m_alias = parent.get();
+        m_bytes = parent.m_bytes;
+        m_pitch = parent.m_pitch;
+        m_ldim = parent.m_ldim;
+    }
+    void nullify()
+    {
+        m_managed.reset();
+        m_alias = nullptr;
+        m_bytes = 0;
+    }
+    void* get() const { return m_alias ? m_alias : m_managed.get(); }
+    bool is_null() const { return get() == nullptr; }
+    size_t get_size() const { return m_bytes; }
+    size_t get_pitch() const { return m_pitch; }
+    size_t get_real_size() const { return m_bytes; }
+    void memset(int v, cudaStream_t stream = 0)
+    {
+        if (is_null())
+            return;
+        if (std::is_same<Allocator, BaseAllocator>::value)
+            std::memset(get(), v, m_bytes);
+        else
+            cudaMemsetAsync(get(), v, m_bytes, stream);
+    }
+    // dense host array <-> this buffer (rows of ldim bytes at pitch bytes)
+    void copyin(const void* host)
+    {
+        if (std::is_same<Allocator, BaseAllocator>::value)
+            std::memcpy(get(), host, m_bytes);
+        else if (m_pitch == m_ldim || m_ldim == 0)
+            cudaMemcpy(get(), host, m_bytes, cudaMemcpyHostToDevice);
+        else
+            cudaMemcpy2D(get(), m_pitch, host, m_ldim, m_ldim, m_bytes / m_pitch, cudaMemcpyHostToDevice);
+    }
+    void copyout(void* host) const
+    {
+        if (std::is_same<Allocator, BaseAllocator>::value)
+            std::memcpy(host, get(), m_bytes);
+        else if (m_pitch == m_ldim || m_ldim == 0)
+            cudaMemcpy(host, get(), m_bytes, cudaMemcpyDeviceToHost);
+        else
+            cudaMemcpy2D(host, m_ldim, get(), m_pitch, m_ldim, m_bytes / m_pitch, cudaMemcpyDeviceToHost);
+    }
+
+private:
+    std::shared_ptr<void> m_managed;
+    void* m_alias = nullptr;
+    size_t m_bytes = 0, m_pitch = 0, m_ldim = 0;
+};
+
+// Fixed-rank index / extent array with DistConv's negative indexing
+// (tensor/tensor_base.hpp:28-250).
+template <int ND, typename DataType = index_t>
+class Array
+{
+public:
+    static constexpr int num_dims = ND;
+    using data_type = DataType;
+    Array() { m_data.fill(DataType(0)); }
+    Array(DataType v) { m_data.fill(v); }
+    Array(std::initializer_list<DataType> l)
+    {
+        util::require((int) l.size() == ND, "Array: wrong number of initialisers");
+        std::copy(l.begin(), l.end(), m_data.begin());
+    }
+    explicit Array(const Vector<DataType>& v)
+    {
+        util::require(v.num_dims() == ND, "Array: wrong rank");
+        std::copy(v.begin(), v.end(), m_data.begin());
+    }
+    DataType& operator[](int i) { return m_data[i < 0 ? ND + i : i]; }
+    const DataType& operator[](int i) const { return m_data[i < 0 ? ND + i : i]; }
+    DataType get_size() const
+    {
+        DataType p = 1;
+        for (auto v : m_data)
+            p *= v;
+        return p;
+    }
+    bool operator==(const Array& o) const { return m_data == o.m_data; }
+    bool operator!=(const Array& o) const { return !(*this == o); }
+    Array operator+(const Array& o) const
+    {
+        Array r;
+        for (int i = 0; i < ND; ++i)
+            r[i] = m_data[i] + o.m_data[i];
+        return r;
+    }
+    Array operator-(const Array& o) const
+    {
+        Array r;
+        for (int i = 0; i < ND; ++i)
+            r[i] = m_data[i] - o.m_data[i];
+        return r;
+    }
+    Vector<DataType> get_vector() const { return Vector<DataType>(std::vector<DataType>(m_data.begin(), m_data.end())); }
+    auto begin() const { return m_data.begin(); }
+    auto end() const { return m_data.end(); }
+
+private:
+    std::array<DataType, ND> m_data;
+};
+
+// offset of an index in a dense array of the given shape / the strides of
+// that shape, dimension 0 fastest (tensor_base.hpp get_offset / get_strides)
+inline index_t get_offset(const IndexVector& idx, const Shape& shape)
+{
+    index_t off = 0, stride = 1;
+    for (int i = 0; i < shape.num_dims(); ++i)
+    {
+        off += idx[i] * stride;
+        stride *= shape[i];
+    }
+    return off;
+}
+inline Shape get_strides(const Shape& shape)
+{
+    Shape st(shape.size(), 1);
+    for (int i = 1; i < shape.num_dims(); ++i)
+        st[i] = st[i - 1] * shape[i - 1];
+    return st;
+}
 
 inline index_t split_extent(index_t total, index_t parts, index_t index)
 {
@@ -316,16 +858,41 @@ public:
     int allocate()
     {
         const size_t bytes = (size_t) get_local_pitched_size() * sizeof(DataType);
-        void* p = nullptr;
-        if (cudaMalloc(&p, bytes ? bytes : 16) != cudaSuccess)
+        if (m_data.allocate(bytes, (size_t) m_pitch * sizeof(DataType),
+                            (size_t) get_local_real_shape()[0] * sizeof(DataType))
+            != 0)
             return -1;
-        cudaMemset(p, 0, bytes);
-        m_mem = std::shared_ptr<void>(p, [](void* q) { cudaFree(q); });
-        m_buf = static_cast<DataType*>(p);
+        m_data.memset(0);
+        if (!std::is_same<Allocator, BaseAllocator>::value)
+            cudaDeviceSynchronize();
+        m_buf = static_cast<DataType*>(m_data.get());
+        m_is_view = false;
         return 0;
     }
-    // Alias caller memory laid out with this shard's pitch (tensor.hpp:604-623); never frees.
-    void set_view(void* raw) { m_mem.reset(); m_buf = static_cast<DataType*>(raw); }
+    // Alias caller memory laid out with this shard's pitch (tensor.hpp:604-623); a
+    // view never frees.
+    void set_view(void* raw)
+    {
+        m_data.alias(raw, (size_t) get_local_pitched_size() * sizeof(DataType), (size_t) m_pitch * sizeof(DataType),
+                     (size_t) get_local_real_shape()[0] * sizeof(DataType));
+        m_buf = static_cast<DataType*>(raw);
+        m_is_view = true;
+    }
+    void set_view(const Memory<Allocator>& parent_mem)
+    {
+        m_data.alias(parent_mem);
+        m_buf = static_cast<DataType*>(m_data.get());
+        m_is_view = true;
+    }
+    bool is_view() const { return m_is_view; }
+    bool is_null() const { return m_buf == nullptr; }
+    Memory<Allocator>& get_data() { return m_data; }
+    const Memory<Allocator>& get_data() const { return m_data; }
+    void nullify()
+    {
+        m_data.nullify();
+        m_buf = nullptr;
+    }
     DataType* get_buffer() { return m_buf; }
     const DataType* get_const_buffer() const { return m_buf; }
     Shape get_strides() const
@@ -349,10 +916,7 @@ public:
         return off;
     }
     DataType* get_base_ptr() { return m_buf + get_local_offset(IndexVector(m_shape.size(), 0)); }
-    void zero(cudaStream_t s = 0)
-    {
-        cudaMemsetAsync(m_buf, 0, (size_t) get_local_pitched_size() * sizeof(DataType), s);
-    }
+    void zero(cudaStream_t s = 0) { m_data.memset(0, s); }
     void clear_halo(int dim, cudaStream_t s = 0)
     {
         if (get_local_size() == 0)
@@ -421,10 +985,25 @@ private:
     Distribution m_dist;
     LocalShapeFn m_fn;
     IndexVector m_proc_idx, m_split_idx, m_offset;
-    std::shared_ptr<void> m_mem;
+    Memory<Allocator> m_data;
     DataType* m_buf = nullptr;
     index_t m_pitch = 0;
+    bool m_is_view = false;
 };
+
+// tensor::View (tensor.hpp): make `t` alias caller memory / another tensor's memory.
+template <typename DataType, typename Locale, typename Allocator>
+inline int View(Tensor<DataType, Locale, Allocator>& t, DataType* raw_ptr)
+{
+    t.set_view(static_cast<void*>(raw_ptr));
+    return 0;
+}
+template <typename DataType, typename Locale, typename Allocator>
+inline int View(Tensor<DataType, Locale, Allocator>& t, const Tensor<DataType, Locale, Allocator>& parent)
+{
+    t.set_view(parent.get_data());
+    return 0;
+}
 
 } // namespace tensor
 
@@ -625,13 +1204,52 @@ enum class HaloExchangeAccumOp
     MIN = 3
 };
 
-// tensor::HaloExchange (halo_exchange_cuda.hpp:18-423) on the peer-store
-// transport.  The constructor maps the neighbours' receive slabs through the
-// tensor's locale (one allgather of 256-byte blobs).
+} // namespace tensor
+} // namespace distconv
+
+// The communication back end is a tag here (the reference instantiates its
+// halo exchange and all-reduce classes with Al::NCCLBackend): its comm_type
+// carries the stream a boundary's work is ordered on.
+#ifndef DISTCONV_B200_NO_AL_TAG
+namespace Al
+{
+struct NCCLBackend
+{
+    class comm_type
+    {
+    public:
+        explicit comm_type(cudaStream_t stream = 0) : m_stream(stream) {}
+        cudaStream_t get_stream() const { return m_stream; }
+
+    private:
+        cudaStream_t m_stream;
+    };
+};
+} // namespace Al
+#endif
+
+namespace distconv
+{
+namespace tensor
+{
+
+// tensor::HaloExchange<DataType, Allocator, AlBackend> (halo_exchange_cuda.hpp:18-423)
+// on the peer-store transport.  The constructor maps the neighbours' receive
+// slabs through the tensor's locale (one allgather of 256-byte blobs).
+// The reference's per-side communicators and boundary streams are accepted by
+// the overloads below; the whole ordered exchange is enqueued on the main
+// stream, which gives the ordering the reference builds with its stream
+// fan-out / fan-in (halo_exchange_cuda.hpp:68-105).
+template <typename DataType = float, typename Allocator = CUDAAllocator, typename AlBackend = Al::NCCLBackend>
 class HaloExchange
 {
+    static_assert(std::is_same<DataType, float>::value, "only float tensors");
+
 public:
-    explicit HaloExchange(TensorF& t) : m_tensor(t)
+    using TensorType = Tensor<DataType, LocaleMPI, Allocator>;
+    using CommType = std::shared_ptr<typename AlBackend::comm_type>;
+
+    explicit HaloExchange(TensorType& t) : m_tensor(t)
     {
         int32_t peers[2 * DCB_MAX_DIMS];
         for (int d = 0; d < DCB_MAX_DIMS; ++d)
@@ -646,11 +1264,11 @@ public:
         util::check(dcb_halo_plan_connect(m_plan, all.data(), n), "halo connect");
     }
     HaloExchange(const HaloExchange&) = delete;
-    ~HaloExchange() { dcb_halo_plan_destroy(m_plan); }
+    virtual ~HaloExchange() { dcb_halo_plan_destroy(m_plan); }
 
     int find_peer_rank(int dim, int side) const
     {
-        const TensorF& t = m_tensor;
+        const TensorType& t = m_tensor;
         if (dim >= t.get_num_dims() || !t.get_distribution().is_distributed(dim) || t.get_halo_width(dim) == 0
             || t.get_local_size() == 0)
             return -1;
@@ -672,7 +1290,54 @@ public:
         }
         return r;
     }
-    // exchange(comms, stream, rendezvous, sync_back, is_reverse, skip_unpack, op)
+    bool is_exchange_required(int dim) const { return find_peer_rank(dim, LHS) >= 0 || find_peer_rank(dim, RHS) >= 0; }
+
+    // ---- the reference's argument lists (halo_exchange_cuda.hpp:56-146) ----
+    // all dimensions, widths = the tensor's halo widths
+    void exchange(BoundaryAttributesV<CommType>& /*comms*/, cudaStream_t stream_main, bool /*rendezvous*/,
+                  bool /*sync_back*/, bool is_reverse, bool skip_unpack,
+                  HaloExchangeAccumOp op = HaloExchangeAccumOp::ID)
+    {
+        exchange(stream_main, is_reverse, skip_unpack, op);
+    }
+    // all dimensions with explicit widths.  The slabs exchanged are always the
+    // tensor's whole halo (a superset of narrower requests, e.g. the one-sided
+    // widths of a strided convolution): widths wider than the halo are refused.
+    void exchange(const IntVector& widths_rhs_send, const IntVector& widths_rhs_recv,
+                  const IntVector& widths_lhs_send, const IntVector& widths_lhs_recv,
+                  BoundaryAttributesV<CommType>& comms, cudaStream_t stream_main, bool rendezvous, bool sync_back,
+                  bool is_reverse, bool skip_unpack, HaloExchangeAccumOp op = HaloExchangeAccumOp::ID)
+    {
+        for (int i = 0; i < m_tensor.get_num_spatial_dims(); ++i)
+            for (int w : {widths_rhs_send[i], widths_rhs_recv[i], widths_lhs_send[i], widths_lhs_recv[i]})
+                util::require(w <= m_tensor.get_halo_width(i), "halo exchange: width exceeds the tensor's overlap");
+        exchange(comms, stream_main, rendezvous, sync_back, is_reverse, skip_unpack, op);
+    }
+    // one dimension
+    void exchange(int dim, CommType& comm_rhs, CommType& /*comm_lhs*/, bool /*rendezvous*/, bool is_reverse,
+                  bool skip_unpack, HaloExchangeAccumOp op = HaloExchangeAccumOp::ID)
+    {
+        const cudaStream_t stream = comm_rhs ? comm_rhs->get_stream() : 0;
+        pack_put(dim, stream, is_reverse, op);
+        if (!skip_unpack)
+            wait_unpack(dim, stream, is_reverse, op);
+    }
+    void exchange(int dim, int width_rhs_send, int width_rhs_recv, int width_lhs_send, int width_lhs_recv,
+                  CommType& comm_rhs, CommType& comm_lhs, bool rendezvous, bool is_reverse, bool skip_unpack,
+                  HaloExchangeAccumOp op = HaloExchangeAccumOp::ID)
+    {
+        for (int w : {width_rhs_send, width_rhs_recv, width_lhs_send, width_lhs_recv})
+            util::require(w <= m_tensor.get_halo_width(dim), "halo exchange: width exceeds the tensor's overlap");
+        exchange(dim, comm_rhs, comm_lhs, rendezvous, is_reverse, skip_unpack, op);
+    }
+    // deferred unpack of a skip_unpack exchange (halo_exchange_cuda.hpp:148-202)
+    void unpack(BoundaryAttributesV<cudaStream_t>& /*streams*/, cudaStream_t stream_main, bool /*sync_back*/,
+                bool is_reverse, HaloExchangeAccumOp op = HaloExchangeAccumOp::ID)
+    {
+        unpack(stream_main, is_reverse, op);
+    }
+
+    // ---- the same on one stream ----
     void exchange(cudaStream_t stream, bool is_reverse = false, bool skip_unpack = false,
                   HaloExchangeAccumOp op = HaloExchangeAccumOp::ID)
     {
@@ -707,9 +1372,22 @@ private:
         return (rev ? DCB_HALO_REVERSE : 0u) | (skip ? DCB_HALO_SKIP_UNPACK : 0u)
                | ((uint32_t) op << DCB_HALO_OP_SHIFT);
     }
-    TensorF& m_tensor;
+    TensorType& m_tensor;
     dcb_halo_plan* m_plan = nullptr;
 };
+
+// The reference's transports (halo_exchange_cuda_{mpi,al,p2p,hybrid}.hpp) are one
+// here: packed faces go straight into the neighbour's receive slab by peer
+// stores.  The names stay so that code that spells a transport compiles.
+template <typename DataType = float, typename Allocator = CUDAAllocator, typename AlBackend = Al::NCCLBackend>
+using HaloExchangeMPI = HaloExchange<DataType, Allocator, AlBackend>;
+template <typename DataType = float, typename Allocator = CUDAAllocator, typename AlBackend = Al::NCCLBackend>
+using HaloExchangeAL = HaloExchange<DataType, Allocator, AlBackend>;
+template <typename DataType = float, typename Allocator = CUDAAllocator, typename AlBackend = Al::NCCLBackend>
+using HaloExchangeP2P = HaloExchange<DataType, Allocator, AlBackend>;
+template <typename DataType = float, typename Allocator = CUDAAllocator, typename AlBackend = Al::NCCLBackend>
+using HaloExchangeHybrid = HaloExchange<DataType, Allocator, AlBackend>;
+
 // What `rank` owns of t, in global coordinates; empty for a rank that is not
 // the root of a replicated dimension.
 inline dcb_box owned_box(const TensorF& t, int rank)
@@ -814,42 +1492,166 @@ private:
 };
 } // namespace tensor
 
-// DNNBackend<GPUDNNBackend> (dnn_backend.hpp:635-980): the main stream (not
-// owned) and a working all-reduce communicator.
+// make_halo_exchange (dnn_backend/halo_exchange_factory.hpp:27-100): every
+// method yields the one transport.
+template <typename DataT, typename AllocT>
+inline std::unique_ptr<tensor::HaloExchange<DataT, AllocT>>
+make_halo_exchange(tensor::Tensor<DataT, tensor::LocaleMPI, AllocT>& t, HaloExchangeMethod method)
+{
+    util::MPIRootPrintStreamDebug() << "Using " << method << " in halo exchange (peer-store transport)";
+    return std::make_unique<tensor::HaloExchange<DataT, AllocT>>(t);
+}
+
+// StreamManager (dnn_backend.hpp:66-117, legacy/src/dnn_backend/stream_manager.cpp):
+// the main stream plus num_internal_streams non-blocking and as many priority
+// streams.  The main stream is the caller's and is never destroyed here.
+class StreamManager
+{
+public:
+    explicit StreamManager(size_t num_internal_streams, cudaStream_t main_stream = 0) : m_stream(main_stream)
+    {
+        int lo = 0, hi = 0;
+        cudaDeviceGetStreamPriorityRange(&lo, &hi);
+        for (size_t i = 0; i < num_internal_streams; ++i)
+        {
+            cudaStream_t a = nullptr, b = nullptr;
+            cudaStreamCreateWithFlags(&a, cudaStreamNonBlocking);
+            cudaStreamCreateWithPriority(&b, cudaStreamNonBlocking, hi);
+            m_internal_streams.push_back(a);
+            m_priority_streams.push_back(b);
+        }
+    }
+    StreamManager(const StreamManager&) = delete;
+    ~StreamManager() noexcept
+    {
+        for (auto st : m_internal_streams)
+            if (st)
+                cudaStreamDestroy(st);
+        for (auto st : m_priority_streams)
+            if (st)
+                cudaStreamDestroy(st);
+    }
+    size_t num_streams() const noexcept { return m_internal_streams.size(); }
+    cudaStream_t stream() const noexcept { return m_stream; }
+    cudaStream_t internal_stream(size_t idx) const { return m_internal_streams.at(idx); }
+    cudaStream_t priority_stream(size_t idx) const { return m_priority_streams.at(idx); }
+
+private:
+    cudaStream_t m_stream;
+    std::vector<cudaStream_t> m_internal_streams, m_priority_streams;
+};
+
+// DNNBackend<GPUDNNBackend> = BackendDNNLib (dnn_backend.hpp:635-980,
+// legacy/src/dnn_backend/dnn_backend.cpp:65-190): options, the main stream (the
+// caller's), eight internal and eight priority streams with one communicator
+// per priority stream, and a working all-reduce communicator (the reference
+// never constructs its own, communicator_manager.cpp:26-57).  Handle_t is
+// opaque and unused: there is no vendor library behind this backend.
 class BackendDNNLib
 {
 public:
-    BackendDNNLib(const tensor::LocaleMPI& loc, cudaStream_t stream = 0, int allreduce_max_count = 32768)
-        : m_loc(loc), m_stream(stream)
+    using Handle_t = void*;
+    using Stream_t = cudaStream_t;
+    using AlCommType = Al::NCCLBackend::comm_type;
+    using InternalCommType = Al::NCCLBackend::comm_type;
+    static constexpr size_t num_internal_streams = 8;
+
+    BackendDNNLib(const tensor::LocaleMPI& loc, cudaStream_t stream = 0, Options opts = Options{},
+                  int allreduce_max_count = 32768)
+        : m_loc(loc), m_opts(opts), m_streams(num_internal_streams, stream), m_al_comm(stream)
     {
+        for (size_t i = 0; i < num_internal_streams; ++i)
+            m_internal_comms.push_back(std::make_shared<InternalCommType>(m_streams.priority_stream(i)));
         util::check(dcb_comm_create_peer(loc.get_rank(), loc.get_size(), allreduce_max_count, &m_comm), "comm");
         std::vector<char> mine(DCB_COMM_BLOB_BYTES), all((size_t) loc.get_size() * DCB_COMM_BLOB_BYTES);
         util::check(dcb_comm_export(m_comm, mine.data()), "comm export");
         loc.allgather(mine.data(), all.data(), DCB_COMM_BLOB_BYTES);
         util::check(dcb_comm_connect(m_comm, all.data(), loc.get_size()), "comm connect");
     }
-    BackendDNNLib(const BackendDNNLib&) = delete;
-    ~BackendDNNLib() { dcb_comm_destroy(m_comm); }
-    std::string get_name() const { return "B200"; }
-    cudaStream_t get_stream() const { return m_stream; }
+    // the earlier three-argument form
+    BackendDNNLib(const tensor::LocaleMPI& loc, cudaStream_t stream, int allreduce_max_count)
+        : BackendDNNLib(loc, stream, Options{}, allreduce_max_count)
+    {}
+#if defined(DISTCONV_B200_HAS_MPI)
+    // The reference's constructors (dnn_backend.hpp:661-665).
+    BackendDNNLib(MPI_Comm comm, Handle_t /*handle*/, Options opts = Options{})
+        : BackendDNNLib(tensor::LocaleMPI(comm), 0, opts)
+    {}
+    BackendDNNLib(MPI_Comm comm, Handle_t /*handle*/, Stream_t stream, Options opts = Options{})
+        : BackendDNNLib(tensor::LocaleMPI(comm), stream, opts)
+    {}
+    MPI_Comm get_comm() const noexcept { return m_loc.get_comm(); }
+#else
     const tensor::LocaleMPI& get_comm() const { return m_loc; }
-    void wait() { cudaStreamSynchronize(m_stream); }
-    void allreduce(float* p, index_t count) { util::check(dcb_allreduce_sum(m_comm, p, count, m_stream), "allreduce"); }
+#endif
+    BackendDNNLib(const BackendDNNLib&) = delete;
+    virtual ~BackendDNNLib() { dcb_comm_destroy(m_comm); }
+
+    std::string get_name() const { return "B200"; }
+    const tensor::LocaleMPI& get_locale() const { return m_loc; }
+    // option queries
+    bool deterministic() const noexcept { return m_opts.m_deterministic; }
+    bool profiling() const noexcept { return m_opts.enable_profiling; }
+    bool overlap_halo_exchange() const noexcept { return m_opts.overlap_halo_exchange; }
+    float ws_capacity_factor() const noexcept { return m_opts.ws_capacity_factor; }
+    int math_mode() const noexcept { return m_opts.math_mode; }
+    // library management
+    Handle_t get_handle() const noexcept { return nullptr; }
+    Stream_t get_stream() const noexcept { return m_streams.stream(); }
+    Stream_t get_internal_priority_stream(size_t idx) const { return m_streams.priority_stream(idx); }
+    Stream_t get_internal_stream(size_t idx) const { return m_streams.internal_stream(idx); }
+    void wait() const { cudaStreamSynchronize(m_streams.stream()); }
+    // communicators
+    AlCommType& get_al_comm() { return m_al_comm; }
+    AlCommType& get_al_nccl_comm() { return m_al_comm; }
+    size_t get_num_internal_comms() const noexcept { return m_internal_comms.size(); }
+    std::shared_ptr<InternalCommType> get_internal_comm(size_t idx) const { return m_internal_comms.at(idx); }
+
+    void allreduce(float* p, index_t count)
+    {
+        util::check(dcb_allreduce_sum(m_comm, p, count, get_stream()), "allreduce");
+    }
     // the two halves of allreduce (store to every peer / fold what arrived)
     void allreduce_push(float* p, index_t count)
     {
-        util::check(dcb_allreduce_push(m_comm, p, count, m_stream), "allreduce push");
+        util::check(dcb_allreduce_push(m_comm, p, count, get_stream()), "allreduce push");
     }
     void allreduce_pull(float* p, index_t count)
     {
-        util::check(dcb_allreduce_pull(m_comm, p, count, m_stream), "allreduce pull");
+        util::check(dcb_allreduce_pull(m_comm, p, count, get_stream()), "allreduce pull");
     }
 
 private:
     tensor::LocaleMPI m_loc;
-    cudaStream_t m_stream;
+    Options m_opts;
+    StreamManager m_streams;
+    AlCommType m_al_comm;
+    std::vector<std::shared_ptr<InternalCommType>> m_internal_comms;
     dcb_comm* m_comm = nullptr;
 };
+template <typename VendorBackend = void>
+using DNNBackend = BackendDNNLib;
+
+// tensor::Allreduce<T> (tensor/allreduce.hpp:8-19) over the backend's communicator.
+namespace tensor
+{
+template <typename DataType>
+class Allreduce
+{
+public:
+    explicit Allreduce(BackendDNNLib& be) : m_be(be) {}
+    void allreduce(DataType* buf, size_t count) { m_be.allreduce(buf, (index_t) count); }
+    void allreduce(const DataType* send_buf, DataType* recv_buf, size_t count)
+    {
+        if (send_buf != recv_buf)
+            cudaMemcpyAsync(recv_buf, send_buf, count * sizeof(DataType), cudaMemcpyDeviceToDevice, m_be.get_stream());
+        m_be.allreduce(recv_buf, (index_t) count);
+    }
+
+private:
+    BackendDNNLib& m_be;
+};
+} // namespace tensor
 
 template <typename Backend, typename DataType>
 class Convolution;
@@ -863,10 +1665,20 @@ template <>
 class Convolution<BackendDNNLib, float>
 {
 public:
-    Convolution(BackendDNNLib& backend, int num_dims, HaloExchangeMethod = HaloExchangeMethod::P2P,
-                ChannelParallelismAlgorithm = ChannelParallelismAlgorithm::NONE)
-        : m_be(backend), m_num_dims(num_dims), m_nsd(num_dims - 2)
+    // convolution.hpp:29-91: the four-argument form takes overlap and profiling
+    // from the backend's options, the six-argument form states them.
+    Convolution(BackendDNNLib& backend, int num_dims, HaloExchangeMethod method = HaloExchangeMethod::P2P,
+                ChannelParallelismAlgorithm chanfilt_algo = ChannelParallelismAlgorithm::NONE)
+        : Convolution(backend, num_dims, method, backend.overlap_halo_exchange(), backend.profiling(), chanfilt_algo)
     {}
+    Convolution(BackendDNNLib& backend, int num_dims, HaloExchangeMethod /*method*/, bool enable_overlap,
+                bool enable_profiling, ChannelParallelismAlgorithm chanfilt_algo = ChannelParallelismAlgorithm::NONE)
+        : m_be(backend), m_num_dims(num_dims), m_nsd(num_dims - 2), m_math(backend.math_mode()),
+          m_enable_overlap(enable_overlap), m_enable_profiling(enable_profiling)
+    {
+        if (chanfilt_algo != ChannelParallelismAlgorithm::NONE && chanfilt_algo != ChannelParallelismAlgorithm::AUTO)
+            throw std::runtime_error("Convolution: channel / filter parallelism is not provided");
+    }
     Convolution(const Convolution&) = delete;
     ~Convolution()
     {
@@ -879,10 +1691,12 @@ public:
     // (forward only).
     void setup(TensorF& input, const int_vector& filter_shape, TensorF& output, TensorF* d_input,
                TensorF* d_output, const int_vector& pads, const int_vector& strides, const int_vector& dilations,
-               int num_groups = 1, int math_mode = DCB_MATH_FP32)
+               int num_groups = 1, int math_mode = -1)
     {
         if (num_groups != 1)
             throw std::runtime_error("Convolution: grouped convolution is not provided");
+        if (math_mode < 0)
+            math_mode = m_math; // the backend's option
         const int nsd = m_nsd;
         m_filter_dims = tensor::IntVector(filter_shape.begin(), filter_shape.begin() + nsd);
         m_C = filter_shape[nsd];
@@ -892,9 +1706,9 @@ public:
         m_math = math_mode;
         // setup_halo_xch (convolution.hpp:2672-2686); the d_output exchanger is
         // built on d_output, which is what backward data reads.
-        m_halo_xch_input.reset(new tensor::HaloExchange(input));
+        m_halo_xch_input.reset(new tensor::HaloExchange<>(input));
         if (d_output)
-            m_halo_xch_d_output.reset(new tensor::HaloExchange(*d_output));
+            m_halo_xch_d_output.reset(new tensor::HaloExchange<>(*d_output));
         m_empty = input.get_local_size() == 0 || output.get_local_size() == 0;
         if (m_empty)
             return;
@@ -924,14 +1738,37 @@ public:
                 pads_fp[i] = pads_bp[i] = pads[i];
         }
         m_x_lo = m_halo_bwd_recv;
-        const dcb_nd_desc xd = input.nd_desc(m_halo_bwd_recv, m_halo_fwd_recv), yd = output.nd_desc();
-        m_plan_fwd = make_plan(xd, yd, pads_fp);
-        if (d_output)
+        m_xd = input.nd_desc(m_halo_bwd_recv, m_halo_fwd_recv);
+        m_yd = output.nd_desc();
+        m_pads_fp = pads_fp;
+        m_pads_bp = pads_bp;
+        m_has_bwd = d_output != nullptr;
+        if (m_has_bwd)
         {
-            const dcb_nd_desc dyd = d_output->full_nd_desc();
-            const dcb_nd_desc dxd = (d_input ? *d_input : input).nd_desc(m_halo_bwd_recv, m_halo_fwd_recv);
-            m_plan_bwd = make_plan(dxd, dyd, pads_bp);
+            m_dyd = d_output->full_nd_desc();
+            m_dxd = (d_input ? *d_input : input).nd_desc(m_halo_bwd_recv, m_halo_fwd_recv);
         }
+        m_num_samples = (int) m_xd.n;
+        make_plans();
+    }
+
+    // convolution.hpp:1147-1180: a mini-batch smaller than the tensors were
+    // set up for (the last one of an epoch) changes the sample extent of every
+    // descriptor; strides stay.  Plans are rebuilt for the new extent.
+    void set_num_samples(int n)
+    {
+        util::require(n != 0, "set_num_samples: zero samples");
+        if (m_empty || n == m_num_samples)
+            return;
+        util::MPIPrintStreamDebug() << "Setting #sample to " << n << " from " << m_num_samples;
+        m_num_samples = n;
+        m_xd.n = m_yd.n = n;
+        if (m_has_bwd)
+            m_dxd.n = m_dyd.n = n;
+        dcb_conv_plan_destroy(m_plan_fwd);
+        dcb_conv_plan_destroy(m_plan_bwd);
+        m_plan_fwd = m_plan_bwd = nullptr;
+        make_plans();
     }
 
     // The reference's own argument list (convolution.hpp:119-135): filters
@@ -987,8 +1824,8 @@ public:
     {
         return dcb_conv_plan_kernel_variant(which == 0 ? m_plan_fwd : m_plan_bwd, which);
     }
-    tensor::HaloExchange& input_halo_exchange() { return *m_halo_xch_input; }
-    tensor::HaloExchange& d_output_halo_exchange() { return *m_halo_xch_d_output; }
+    tensor::HaloExchange<>& input_halo_exchange() { return *m_halo_xch_input; }
+    tensor::HaloExchange<>& d_output_halo_exchange() { return *m_halo_xch_d_output; }
     void forward_exchange_halo(TensorF&) { m_halo_xch_input->exchange(m_be.get_stream()); }
     void backward_data_exchange_halo(TensorF&) { m_halo_xch_d_output->exchange(m_be.get_stream()); }
 
@@ -998,11 +1835,15 @@ public:
     {
         if (input.get_local_size() == 0 || output.get_local_size() == 0)
             return 0;
+        Range whole(m_enable_profiling, "conv/forward");
+        set_num_samples((int) input.get_local_shape()[-1]);
         if (!skip_halo_exchange)
         {
+            Range r(m_enable_profiling, "conv/forward/exchange_halo");
             clear_halos(input);
             forward_exchange_halo(input);
         }
+        Range r(m_enable_profiling, "conv/forward/forward");
         util::check(dcb_conv_fwd(m_plan_fwd, alpha, input.nd_ptr(m_x_lo), filter, beta, output.get_base_ptr(),
                                  m_be.get_stream()),
                     "conv forward");
@@ -1042,8 +1883,13 @@ public:
     {
         if (d_output.get_local_size() == 0 || d_input.get_local_size() == 0)
             return 0;
+        Range whole(m_enable_profiling, "conv/bw_data");
+        set_num_samples((int) d_input.get_local_shape()[-1]);
         if (!skip_halo_exchange)
+        {
+            Range r(m_enable_profiling, "conv/bw_data/exchange_halo");
             backward_data_exchange_halo(d_output);
+        }
         util::check(dcb_conv_bwd_data(m_plan_bwd, alpha, filter, d_output.get_buffer(), beta,
                                       d_input.nd_ptr(m_x_lo), m_be.get_stream()),
                     "conv backward data");
@@ -1055,6 +1901,9 @@ public:
                         bool reduce = true)
     {
         const index_t count = (index_t) m_K * m_C * m_filter_dims.get_size();
+        Range whole(m_enable_profiling, "conv/bw_filter");
+        if (input.get_local_size() != 0)
+            set_num_samples((int) input.get_local_shape()[-1]);
         if (input.get_local_size() == 0 || d_output.get_local_size() == 0 || !input.is_split_root())
             cudaMemsetAsync(d_filter, 0, (size_t) count * sizeof(float), m_be.get_stream());
         else
@@ -1093,8 +1942,13 @@ public:
         return 0;
     }
     void wait() { m_be.wait(); }
+    // Interior / boundary overlap (convolution.hpp:1497-1584) is not scheduled by
+    // this class whatever enable_overlap says: at these sizes the whole exchange
+    // is a few tens of microseconds on NVLink and the split costs more than it
+    // hides (measured); the Python host mirror carries the reference's scheme.
     bool is_overlap_fwd_halo_exchange_enabled() const { return false; }
     bool is_overlap_bwd_halo_exchange_enabled() const { return false; }
+    bool is_overlap_requested() const { return m_enable_overlap; }
     // DCB_OK unless a kernel of this layer gave up on a bounded wait
     int32_t status()
     {
@@ -1105,6 +1959,28 @@ public:
     }
 
 private:
+    // a profiler range that lives as long as the scope it is declared in
+    struct Range
+    {
+        Range(bool on, const char* name) : m_on(on)
+        {
+            if (m_on)
+                util::profile_range_push(name);
+        }
+        ~Range()
+        {
+            if (m_on)
+                util::profile_range_pop();
+        }
+        Range(const Range&) = delete;
+        bool m_on;
+    };
+    void make_plans()
+    {
+        m_plan_fwd = make_plan(m_xd, m_yd, m_pads_fp);
+        if (m_has_bwd)
+            m_plan_bwd = make_plan(m_dxd, m_dyd, m_pads_bp);
+    }
     dcb_conv_plan* make_plan(const dcb_nd_desc& xd, const dcb_nd_desc& yd, const tensor::IntVector& pads)
     {
         dcb_conv_desc cd{};
@@ -1141,10 +2017,14 @@ private:
 
     BackendDNNLib& m_be;
     int m_num_dims, m_nsd, m_K = 0, m_C = 0, m_math = DCB_MATH_FP32;
-    bool m_empty = true;
+    bool m_enable_overlap = false, m_enable_profiling = false;
+    bool m_empty = true, m_has_bwd = false;
+    int m_num_samples = 0;
+    dcb_nd_desc m_xd{}, m_yd{}, m_dxd{}, m_dyd{};
+    tensor::IntVector m_pads_fp, m_pads_bp;
     tensor::IntVector m_filter_dims, m_strides, m_dilations, m_x_lo;
     tensor::IntVector m_halo_fwd_send, m_halo_bwd_send, m_halo_fwd_recv, m_halo_bwd_recv;
-    std::unique_ptr<tensor::HaloExchange> m_halo_xch_input, m_halo_xch_d_output;
+    std::unique_ptr<tensor::HaloExchange<>> m_halo_xch_input, m_halo_xch_d_output;
     dcb_conv_plan* m_plan_fwd = nullptr;
     dcb_conv_plan* m_plan_bwd = nullptr;
 };
@@ -1285,6 +2165,10 @@ public:
         return backward_stage2(input, d_output, mean, var, scale, mean_gradient, var_gradient, d_input);
     }
 
+    // batchnorm.hpp:467-475: nothing is cached per sample count here (descriptors
+    // are built from the tensors at every call); kept for source compatibility.
+    void set_num_samples(int /*n*/) {}
+
 private:
     dcb_bn_plan* plan(TensorF& t)
     {
@@ -1379,8 +2263,8 @@ public:
             m_pd.outside_lo[2 - i] = split && first ? m_halo_bwd_recv[i] : 0;
             m_pd.outside_hi[2 - i] = split && last ? m_halo_fwd_recv[i] : 0;
         }
-        m_halo_xch_input.reset(new tensor::HaloExchange(input));
-        m_halo_xch_d_input.reset(new tensor::HaloExchange(d_input));
+        m_halo_xch_input.reset(new tensor::HaloExchange<>(input));
+        m_halo_xch_d_input.reset(new tensor::HaloExchange<>(d_input));
         (void) d_output;
         // index workspace of the backward pass: one byte per output cell, MAX only
         release_workspace();
@@ -1401,8 +2285,12 @@ public:
     {
         if (!skip_halo_exchange)
         {
+            if (m_be.profiling())
+                util::profile_range_push("pooling/exchange_halo");
             clear_halos(input);
             m_halo_xch_input->exchange(m_be.get_stream());
+            if (m_be.profiling())
+                util::profile_range_pop();
         }
         if (output.get_local_size() == 0)
             return 0;
@@ -1430,13 +2318,19 @@ public:
                         "pooling backward");
         }
         if (!skip_halo_exchange)
+        {
+            if (m_be.profiling())
+                util::profile_range_push("pooling/exchange_halo_rev");
             m_halo_xch_d_input->exchange(m_be.get_stream(), true, false, tensor::HaloExchangeAccumOp::SUM);
+            if (m_be.profiling())
+                util::profile_range_pop();
+        }
         return 0;
     }
 
     void wait() { m_be.wait(); }
-    tensor::HaloExchange& input_halo_exchange() { return *m_halo_xch_input; }
-    tensor::HaloExchange& d_input_halo_exchange() { return *m_halo_xch_d_input; }
+    tensor::HaloExchange<>& input_halo_exchange() { return *m_halo_xch_input; }
+    tensor::HaloExchange<>& d_input_halo_exchange() { return *m_halo_xch_d_input; }
 
 private:
     void clear_halos(TensorF& t)
@@ -1459,7 +2353,7 @@ private:
     void* m_ws = nullptr;
     int64_t m_ws_bytes = 0;
     tensor::IntVector m_halo_fwd_send, m_halo_bwd_send, m_halo_fwd_recv, m_halo_bwd_recv;
-    std::unique_ptr<tensor::HaloExchange> m_halo_xch_input, m_halo_xch_d_input;
+    std::unique_ptr<tensor::HaloExchange<>> m_halo_xch_input, m_halo_xch_d_input;
 };
 
 // LeakyReLU<BackendDNNLib> (leaky_relu.hpp; leaky_relu.cu:14-41)
@@ -1491,5 +2385,137 @@ public:
 private:
     BackendDNNLib& m_be;
 };
+
+// ---- dump_tensor / dump_local_tensor (legacy/include/distconv/distconv.hpp:581-671)
+// rank 0 writes the GLOBAL tensor, dimension 0 fastest, halos and row padding
+// stripped: raw floats to <path>.out (binary) or one value per line to
+// <path>.txt, the formats the reference's validation scripts read.  The owned
+// blocks travel through the locale's allgather (a debugging aid: every rank
+// holds all blocks for a moment).
+namespace internal
+{
+// this rank's owned cells, dense, dimension 0 fastest
+inline std::vector<float> owned_cells_to_host(TensorF& t)
+{
+    const int nd = t.get_num_dims();
+    const tensor::Shape pitched = t.get_local_pitched_shape();
+    const tensor::Shape& loc = t.get_local_shape();
+    std::vector<float> shard((size_t) pitched.get_size()), dense((size_t) loc.get_size());
+    if (dense.empty() || t.get_buffer() == nullptr)
+        return dense;
+    cudaMemcpy(shard.data(), t.get_buffer(), shard.size() * sizeof(float), cudaMemcpyDeviceToHost);
+    const tensor::Shape st = t.get_strides();
+    tensor::IndexVector idx(nd, 0);
+    const index_t rows = loc.get_size() / loc[0];
+    for (index_t r = 0; r < rows; ++r)
+    {
+        index_t off = 0, rem = r;
+        for (int i = 1; i < nd; ++i)
+        {
+            idx[i] = rem % loc[i];
+            rem /= loc[i];
+            off += (idx[i] + t.get_overlap()[i]) * st[i];
+        }
+        std::memcpy(&dense[(size_t) r * loc[0]], &shard[(size_t) off + t.get_overlap()[0]],
+                    (size_t) loc[0] * sizeof(float));
+    }
+    return dense;
+}
+inline void write_floats(const std::string& path, const float* buf, size_t n, bool binary)
+{
+    std::ofstream out;
+    if (!binary)
+    {
+        out.open(path, std::ios::out | std::ios::trunc);
+        for (size_t i = 0; i < n; ++i)
+            out << buf[i] << std::endl;
+    }
+    else
+    {
+        out.open(path, std::ios::out | std::ios::trunc | std::ios::binary);
+        out.write(reinterpret_cast<const char*>(buf), (std::streamsize) (n * sizeof(float)));
+    }
+}
+} // namespace internal
+
+inline int dump_tensor(TensorF& t, std::string file_path, bool binary = false)
+{
+    file_path += binary ? ".out" : ".txt";
+    const tensor::LocaleMPI& loc = t.get_locale();
+    const int n = loc.get_size(), nd = t.get_num_dims();
+    // every rank contributes a block of the same size: the largest shard
+    size_t cells = 0;
+    std::vector<dcb_box> boxes((size_t) n);
+    for (int r = 0; r < n; ++r)
+    {
+        boxes[r] = tensor::owned_box(t, r);
+        size_t c = 1;
+        for (int i = 0; i < nd; ++i)
+            c *= (size_t) boxes[r].ext[i];
+        cells = std::max(cells, c);
+    }
+    std::vector<float> mine = internal::owned_cells_to_host(t);
+    if (!t.is_split_root())
+        mine.clear(); // a replica: rank's box is empty
+    mine.resize(cells, 0.f);
+    std::vector<float> all((size_t) n * cells);
+    loc.allgather(mine.data(), all.data(), cells * sizeof(float));
+    if (loc.get_rank() != 0)
+        return 0;
+    util::MPIPrintStreamDebug() << "Dumping a tensor of shape " << t.get_shape()[0] << " x ... to " << file_path;
+    std::vector<float> global((size_t) t.get_size(), 0.f);
+    const tensor::Shape gst = tensor::get_strides(t.get_shape());
+    for (int r = 0; r < n; ++r)
+    {
+        const dcb_box& b = boxes[r];
+        size_t c = 1;
+        for (int i = 0; i < nd; ++i)
+            c *= (size_t) b.ext[i];
+        if (c == 0)
+            continue;
+        const float* src = &all[(size_t) r * cells];
+        const size_t rows = c / (size_t) b.ext[0];
+        for (size_t row = 0; row < rows; ++row)
+        {
+            size_t rem = row;
+            index_t off = b.off[0];
+            for (int i = 1; i < nd; ++i)
+            {
+                off += (b.off[i] + (index_t) (rem % (size_t) b.ext[i])) * gst[i];
+                rem /= (size_t) b.ext[i];
+            }
+            std::memcpy(&global[(size_t) off], src + row * (size_t) b.ext[0], (size_t) b.ext[0] * sizeof(float));
+        }
+    }
+    internal::write_floats(file_path, global.data(), global.size(), binary);
+    return 0;
+}
+
+// every rank writes its own owned cells to <path>_<rank>.out / .txt
+inline int dump_local_tensor(TensorF& t, std::string file_path, bool binary = false)
+{
+    file_path += "_" + std::to_string(t.get_locale().get_rank()) + (binary ? ".out" : ".txt");
+    const std::vector<float> mine = internal::owned_cells_to_host(t);
+    internal::write_floats(file_path, mine.data(), mine.size(), binary);
+    return 0;
+}
+
+// the channel / sample dimensions of a tensor in DistConv's order (distconv.hpp:103-109)
+inline int get_channel_dim()
+{
+    return -2;
+}
+inline int get_sample_dim()
+{
+    return -1;
+}
+// Every rank keeps whole samples: the distribution of sample-parallel layers
+// (distconv.hpp make_sample_distribution).
+inline tensor::Distribution make_sample_distribution(int num_dims, int num_ranks)
+{
+    tensor::Shape ls(num_dims, 1);
+    ls[-1] = num_ranks;
+    return tensor::Distribution::make_distribution(ls);
+}
 
 } // namespace distconv

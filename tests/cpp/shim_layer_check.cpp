@@ -12,6 +12,8 @@
 // usage: shim_layer_check [ranks]   (prints "shim_layer_check OK" and exits 0)
 #include "distconv_b200.hpp"
 
+#include <unistd.h>
+
 #include <cmath>
 #include <condition_variable>
 #include <cstdio>
@@ -230,14 +232,24 @@ void rank_main(int rank, int R, Shared* sh, const Global* g)
         cudaSetDevice(0);
         cudaStream_t st;
         cudaStreamCreate(&st);
-        auto ag = [sh, rank](const void* in, void* out, size_t n) {
+        auto ag = [sh, rank, R](const void* in, void* out, size_t n) {
+            sh->bar.wait(); // everybody is done with the previous gather
+            if (rank == 0)
+                sh->blobs.resize((size_t) R * n);
             sh->bar.wait();
             std::memcpy(sh->blobs.data() + (size_t) rank * n, in, n);
             sh->bar.wait();
-            std::memcpy(out, sh->blobs.data(), sh->blobs.size() / 256 * n);
+            std::memcpy(out, sh->blobs.data(), (size_t) R * n);
         };
         tensor::LocaleMPI loc(rank, R, ag);
-        BackendDNNLib be(loc, st);
+        // the backend with the reference's option block (dnn_backend.hpp:46-63, 661-725)
+        const Options opts(/*overlap_halo_exchange=*/false, /*deterministic=*/true, /*enable_profiling=*/true);
+        BackendDNNLib be(loc, st, opts);
+        if (be.get_stream() != st || !be.deterministic() || !be.profiling() || be.overlap_halo_exchange()
+            || be.get_num_internal_comms() != 8
+            || be.get_internal_comm(3)->get_stream() != be.get_internal_priority_stream(3)
+            || be.get_al_comm().get_stream() != st || be.get_name() != "B200")
+            throw std::runtime_error("backend accessors");
         const int_vector shape{W, H, D, C, N}, grid{1, 1, R, 1, 1}, fshape{F, F, F, C, K};
         const int_vector f3{F, F, F}, ones{1, 1, 1}, pads{1, 1, 1};
         TensorF x = create_input_tensor(shape, grid, f3, ones, ones, false, loc);
@@ -267,7 +279,9 @@ void rank_main(int rank, int R, Shared* sh, const Global* g)
         TensorF wt(fsh, loc, shared), dwt(fsh, loc, shared);
         wt.set_view(w);
         dwt.set_view(dw);
-        Convolution<BackendDNNLib, float> conv(be, 5, HaloExchangeMethod::P2P);
+        // the six-argument constructor (convolution.hpp:29-60)
+        Convolution<BackendDNNLib, float> conv(be, 5, GetHaloExchangeMethod("P2P"), /*enable_overlap=*/false,
+                                               /*enable_profiling=*/true, ChannelParallelismAlgorithm::NONE);
         conv.setup(x, wt, y, dx, dwt, dy, pads, ones, ones, 1, "DEFAULT", "DEFAULT", "DEFAULT", 0);
         BatchNormalization<BackendDNNLib, float> bn(be, 5, DECAY, EPS, true);
 
@@ -283,6 +297,17 @@ void rank_main(int rank, int R, Shared* sh, const Global* g)
         x.clear_halo(2, st);
         phase([&] { conv.input_halo_exchange().pack_put(2, st); },
               [&] { conv.input_halo_exchange().wait_unpack(2, st); });
+        if (R == 1)
+        {
+            // the reference's argument list (halo_exchange_cuda.hpp:107-113): one
+            // communicator per dimension and side, the backend's internal ones
+            BoundaryAttributesV<std::shared_ptr<BackendDNNLib::InternalCommType>> comms;
+            int k = 0;
+            apply_to_spatial_sides(5, [&](int i, Side side) { comms(i, side) = be.get_internal_comm(k++); });
+            conv.input_halo_exchange().exchange(comms, st, /*rendezvous=*/false, /*sync_back=*/true,
+                                                /*is_reverse=*/false, /*skip_unpack=*/false);
+            conv.set_num_samples(N); // the extent the layer was set up with: nothing to rebuild
+        }
         // the statistics come from the convolution's epilogue where its kernel has one
         const int fused = conv.forward_with_statistics(1.f, x, w, y, stats, stats + K, /*skip_halo_exchange=*/true);
         if (!fused)
@@ -347,12 +372,27 @@ void rank_main(int rank, int R, Shared* sh, const Global* g)
             e_st = std::max(e_st, (double) std::fabs(hstats[K + k] - g->var[k]) / (1.0 + g->var[k]));
         }
         const double e_y = gather_err(y, g->y, K), e_dx = gather_err(dx, g->dx, C), e_z = gather_err(z, g->z, K);
+        // dump_tensor: rank 0 writes the global y as raw floats, W fastest (distconv.hpp:581-631)
+        const std::string dump = "/tmp/shim_dump_" + std::to_string((long) getpid()) + "_" + std::to_string(R);
+        dump_tensor(y, dump, true);
+        double e_dump = 0;
+        if (rank == 0)
+        {
+            std::vector<float> back(g->y.size());
+            std::FILE* f = std::fopen((dump + ".out").c_str(), "rb");
+            if (!f || std::fread(back.data(), sizeof(float), back.size(), f) != back.size())
+                throw std::runtime_error("dump_tensor file");
+            std::fclose(f);
+            std::remove((dump + ".out").c_str());
+            for (size_t i = 0; i < back.size(); ++i)
+                e_dump = std::max(e_dump, (double) std::fabs(back[i] - g->y[i]) / (1.0 + std::fabs(g->y[i])));
+        }
         std::printf("rank %d/%d: y %.2e  dx %.2e  dw %.2e  stats %.2e  bn %.2e  pool %.2e / %.2e  shuffle %.1e  (fwd "
                     "kernel kind %d, statistics %s)\n",
                     rank, R, e_y, e_dx, e_dw, e_st, e_z, e_py, e_pdx, e_shf, conv.kernel_kind(0),
                     fused ? "fused" : "separate");
         const bool ok = e_y < 2e-5 && e_dx < 2e-5 && e_dw < 5e-5 && e_st < 2e-5 && e_z < 1e-4 && e_py < 1e-6
-                        && e_pdx < 2e-6 && e_shf == 0.0;
+                        && e_pdx < 2e-6 && e_shf == 0.0 && e_dump < 2e-5;
         if (!ok)
         {
             std::lock_guard<std::mutex> lk(sh->m);
@@ -371,9 +411,53 @@ void rank_main(int rank, int R, Shared* sh, const Global* g)
 }
 } // namespace
 
+// the vocabulary of base.hpp / tensor_base.hpp / memory.hpp, host side only
+bool vocabulary_check()
+{
+    bool ok = GetHaloExchangeMethod("AL") == HaloExchangeMethod::AL
+              && GetHaloExchangeMethod("HYBRID") == HaloExchangeMethod::HYBRID
+              && GetBatchnormImpl("AL_NCCL") == BatchnormImpl::AL_NCCL && GetShuffleMethod("MPI") == ShuffleMethod::MPI
+              && ~LHS == RHS;
+    try
+    {
+        GetHaloExchangeMethod("carrier pigeon");
+        ok = false;
+    }
+    catch (const std::invalid_argument&)
+    {}
+    int calls = 0;
+    apply_to_sides<3>([&](int, Side) { ++calls; });
+    apply_to_spatial_sides(5, [&](int, Side) { ++calls; });
+    ok = ok && calls == 12;
+    BoundaryAttributesV<int> attrs(7, 9);
+    attrs(2, RHS) = 1;
+    ok = ok && attrs(0, LHS) == 7 && attrs(1, RHS) == 9 && attrs(2, RHS) == 1;
+    tensor::Array<3> a{4, 5, 6};
+    ok = ok && a[-1] == 6 && a.get_size() == 120 && (a + tensor::Array<3>(1))[0] == 5;
+    const tensor::Shape shape(std::vector<index_t>{4, 3, 2});
+    ok = ok && tensor::get_strides(shape)[2] == 12 && tensor::get_offset(tensor::IndexVector(std::vector<index_t>{1, 2, 1}), shape) == 21;
+    // a host tensor on the process locale, aliasing caller memory through View
+    using HostTensor = tensor::Tensor<float, tensor::LocaleProcess, tensor::BaseAllocator>;
+    HostTensor ht(shape, tensor::LocaleProcess(), tensor::Distribution::make_localized_distribution(3));
+    std::vector<float> backing(24, 2.5f);
+    tensor::View(ht, backing.data());
+    ok = ok && ht.is_view() && ht.get_buffer() == backing.data() && ht.get_pitch() == 4;
+    HostTensor owned(shape, tensor::LocaleProcess(), tensor::Distribution::make_localized_distribution(3));
+    ok = ok && owned.allocate() == 0 && owned.get_buffer()[23] == 0.f && !owned.is_view();
+    std::ostringstream os;
+    os << HaloExchangeMethod::P2P << " " << BatchnormImpl::MPI << " " << RHS << " " << ChannelParallelismAlgorithm::AUTO;
+    ok = ok && os.str() == "P2P MPI RHS AUTO";
+    return ok;
+}
+
 int main(int argc, char** argv)
 {
     const int R = argc > 1 ? std::atoi(argv[1]) : 2;
+    if (!vocabulary_check())
+    {
+        std::printf("shim_layer_check FAILED (vocabulary)\n");
+        return 1;
+    }
     Global g;
     const size_t nx = (size_t) N * C * D * H * W, ny = (size_t) N * K * D * H * W;
     g.x.resize(nx);

@@ -15,15 +15,18 @@ PKG = os.path.join(ROOT, "dihydrogen_b200")
 CUDA = os.environ.get("CUDA_HOME", "/usr/local/cuda")
 
 
-def _compile(out):
+def _compile(out, source="shim_layer_check.cpp", extra=()):
     build.build()
-    cmd = ["g++", "-std=c++17", "-O1", "-Wall", "-Werror", "-I", os.path.join(ROOT, "include"),
-           "-I", os.path.join(CUDA, "include"), os.path.join(ROOT, "tests", "cpp", "shim_layer_check.cpp"),
+    cmd = ["g++", "-std=c++17", "-O1", "-Wall", "-Werror", "-I", os.path.join(ROOT, "include"), *extra,
+           "-I", os.path.join(CUDA, "include"), os.path.join(ROOT, "tests", "cpp", source),
            "-o", str(out), "-L", PKG, "-ldistconv_b200", "-L", os.path.join(CUDA, "lib64"), "-lcudart", "-pthread",
            "-Wl,-rpath," + PKG]
     r = subprocess.run(cmd, capture_output=True, text=True)
     assert r.returncode == 0, r.stderr
     return str(out)
+
+
+MPI_SHIM = ("-I", os.path.join(ROOT, "oracle", "mpi_shim"))
 
 
 @pytest.mark.skipif(shutil.which("g++") is None, reason="no g++")
@@ -38,3 +41,19 @@ def test_shim_layer(tmp_path, ranks):
     exe = _compile(tmp_path / "shim_layer_check")
     r = subprocess.run([exe, str(ranks)], capture_output=True, text=True, timeout=300)
     assert r.returncode == 0 and "shim_layer_check OK" in r.stdout, r.stdout + r.stderr
+
+
+@pytest.mark.skipif(shutil.which("g++") is None, reason="no g++")
+def test_shim_with_mpi_constructors_compiles_and_links(tmp_path):
+    """LocaleMPI(MPI_Comm) and DNNBackend(MPI_Comm, Handle_t, Stream_t, Options)
+    exist behind DISTCONV_B200_HAS_MPI; compiled here against the thread-rank
+    mpi.h stand-in that the oracle's reference driver uses."""
+    exe = _compile(tmp_path / "shim_mpi_check", "shim_mpi_check.cpp", MPI_SHIM)
+    assert os.path.exists(exe)
+
+
+@pytest.mark.gpu
+def test_shim_with_mpi_constructors(tmp_path):
+    exe = _compile(tmp_path / "shim_mpi_check", "shim_mpi_check.cpp", MPI_SHIM)
+    r = subprocess.run([exe], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "shim_mpi_check OK" in r.stdout, r.stdout + r.stderr

@@ -151,3 +151,21 @@ def test_two_rank_setup_over_gloo(tmp_path):
     for r, (p, o) in enumerate(zip(procs, outs)):
         assert p.returncode == 0, o
         assert f"ok {r}" in o
+
+
+def test_options_environment_overrides(monkeypatch):
+    """legacy/src/dnn_backend/options.cpp:13-71: a DISTCONV_* variable that is
+    set, whatever its value, switches its option on."""
+    import dihydrogen_b200 as dc
+
+    for k in ("DISTCONV_OVERLAP_HALO_EXCHANGE", "DISTCONV_DETERMINISTIC", "DISTCONV_ENABLE_PROFILING",
+              "DISTCONV_PROFILING", "DISTCONV_NVTX", "DISTCONV_WS_CAPACITY_FACTOR"):
+        monkeypatch.delenv(k, raising=False)
+    o = dc.Options(deterministic=False)
+    assert not (o.overlap_halo_exchange or o.deterministic or o.enable_profiling) and o.ws_capacity_factor == 1.0
+    monkeypatch.setenv("DISTCONV_OVERLAP_HALO_EXCHANGE", "0")
+    monkeypatch.setenv("DISTCONV_DETERMINISTIC", "1")
+    monkeypatch.setenv("DISTCONV_NVTX", "")
+    monkeypatch.setenv("DISTCONV_WS_CAPACITY_FACTOR", "2.5")
+    o = dc.Options(deterministic=False)
+    assert o.overlap_halo_exchange and o.deterministic and o.enable_profiling and o.ws_capacity_factor == 2.5
