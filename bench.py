@@ -390,11 +390,12 @@ def run_ours(args):
         # (falls back to the separate statistics pass if the plan cannot)
         got = conv.forward(1.0, x, w, 0.0, y, statistics=(mean, var) if fuse else None)
         bn.forward(y, mean, var, rm, rv, scale, bias, z, True, statistics_ready=bool(got))
-        # per partitioned dim: clear_halo, pack+put, wait+unpack; then filter
-        # image, conv, statistics (fold of the epilogue's partials, or the
-        # separate pass), all-reduce, finalize, apply (--overlap: interior +
-        # boundary slabs, each with its filter image, statistics as their own pass)
-        launches["n"] += 3 * n_part + 6 + extra_launches
+        # per partitioned dim: pack+put (which also clears the boundary slabs) and
+        # wait+unpack; then filter image, conv, statistics (fold of the epilogue's
+        # partials, or the separate pass), all-reduce, finalize, apply (--overlap:
+        # clear_halo per dim, interior + boundary slabs, each with its filter
+        # image, statistics as their own pass)
+        launches["n"] += (3 if overlapped else 2) * n_part + 6 + extra_launches
         return got
 
     def bwd_step():
@@ -548,8 +549,7 @@ def run_ours(args):
     t_halo = None
     if n_part:
         def halo_only():
-            conv._clear_halos(x, be.stream)
-            conv.forward_exchange_halo(x, be.stream)
+            conv.halo_xch_input.exchange(be.stream, clear_boundary=True)
         barrier()
         t_halo = max_over_ranks(time_call(halo_only))
     clocks = sampler.stop() if rank == 0 else None

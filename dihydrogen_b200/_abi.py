@@ -22,6 +22,7 @@ OK, BAD_ARG, UNSUPPORTED, CUDA_ERROR, PEER_TIMEOUT, NCCL_ERROR, NOT_CONNECTED = 
 
 HALO_REVERSE = 0x1
 HALO_SKIP_UNPACK = 0x2
+HALO_CLEAR_BOUNDARY = 0x4
 HALO_OPS = {"ID": 0 << 4, "SUM": 1 << 4, "MAX": 2 << 4, "MIN": 3 << 4}
 
 MATH_FP32, MATH_TF32, MATH_FP32_SIMT = 0, 1, 2

@@ -45,7 +45,7 @@ struct SideJob
 
 struct HaloArgs
 {
-    SideJob side[2];
+    SideJob side[4]; // [0], [1]: the two sides; [2], [3]: halo slabs a pack launch also clears
     int op;
     long long budget_ns;
     int* status;
@@ -137,6 +137,21 @@ __global__ void __launch_bounds__(HALO_THREADS) halo_kernel(HaloArgs a)
     const SideJob& j = a.side[blockIdx.y];
     if (!j.active)
         return;
+    if (MODE == MODE_PACK && blockIdx.y >= 2)
+    {
+        // a halo slab without a neighbour behind it (the boundary of the global
+        // tensor): zeroed by the launch that packs this dimension, which saves
+        // the separate clear_halo launch (Tensor::clear_halo before every
+        // exchange, convolution.hpp:405-414)
+        const long long total = j.runs * j.len_v;
+        for (long long i = (long long) blockIdx.x * HALO_THREADS + threadIdx.x; i < total;
+             i += (long long) gridDim.x * HALO_THREADS)
+        {
+            const long long r = i / j.len_v;
+            reinterpret_cast<T*>(j.tensor + j.start + r * j.stride)[i - r * j.len_v] = zero_of<T>();
+        }
+        return;
+    }
 
     if (MODE == MODE_UNPACK && j.flag != nullptr)
     {
@@ -297,6 +312,10 @@ static int32_t launch_halo(HaloArgs& a, int vec, const SlabGeom* geoms,
         if (a.side[s].len_v < 64)
             is_long = false;
     }
+    const bool with_clear = MODE == MODE_PACK && (a.side[2].active || a.side[3].active);
+    for (int s = 2; s < 4; ++s)
+        if (a.side[s].active)
+            a.side[s].len_v = a.side[s].len_v / vec; // set in scalar elements by the caller
     for (int s = 0; s < 2; ++s)
     {
         if (!a.side[s].active)
@@ -313,7 +332,7 @@ static int32_t launch_halo(HaloArgs& a, int vec, const SlabGeom* geoms,
     if (max_units == 0)
         return DCB_OK;
     const long long cap = (long long) num_sms() * 8;
-    dim3 grid((unsigned) (max_units < cap ? max_units : cap), 2);
+    dim3 grid((unsigned) (max_units < cap ? max_units : cap), with_clear ? 4 : 2);
 #define DCB_HALO_CASE(VV)                                                      \
     if (is_long)                                                               \
         halo_kernel<VV, MODE, true><<<grid, HALO_THREADS, 0, stream>>>(a);     \
@@ -536,7 +555,12 @@ int32_t dcb_halo_pack_put(dcb_halo_plan* p, const void* tensor, int32_t dim,
     DCB_REQUIRE(p && tensor, "null argument");
     DCB_REQUIRE(dim >= 0 && dim < p->nsd, "dimension out of range");
     if (!p->dim_active(dim))
+    {
+        // nobody to exchange with: only the clearing is left to do
+        if ((flags & DCB_HALO_CLEAR_BOUNDARY) && !(flags & DCB_HALO_REVERSE) && p->desc.overlap[dim] > 0)
+            return dcb_clear_halo(&p->desc, const_cast<void*>(tensor), dim, stream);
         return DCB_OK;
+    }
     if (!p->connected)
     {
         set_last_error("halo plan has peers but was never connected");
@@ -575,6 +599,27 @@ int32_t dcb_halo_pack_put(dcb_halo_plan* p, const void* tensor, int32_t dim,
         j.active = 1;
         const int v = pick_vec(geoms[s], tensor, j.packed);
         vec = v < vec ? v : vec;
+    }
+    if ((flags & DCB_HALO_CLEAR_BOUNDARY) && !reverse)
+    {
+        // the halo slabs of this dimension that no neighbour will fill
+        for (int s = 0; s < 2; ++s)
+        {
+            if (p->peers[dim][s] >= 0)
+                continue;
+            SlabGeom cg;
+            if (!slab_geom(p->desc, dim, s, width, false, &cg))
+                continue;
+            SideJob& j = a.side[2 + s];
+            j.tensor = const_cast<float*>(static_cast<const float*>(tensor));
+            j.runs = cg.runs;
+            j.stride = cg.stride;
+            j.start = cg.start;
+            j.len_v = cg.len; // scalar elements; launch_halo divides by the vector width
+            j.active = cg.runs * cg.len > 0;
+            const int v = pick_vec(cg, tensor, nullptr);
+            vec = v < vec ? v : vec;
+        }
     }
     return launch_halo<MODE_PACK>(a, vec, geoms, as_stream(stream));
 }

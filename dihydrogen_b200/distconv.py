@@ -627,17 +627,21 @@ class HaloExchange:
         return self
 
     @staticmethod
-    def _flags(is_reverse=False, skip_unpack=False, op="ID"):
+    def _flags(is_reverse=False, skip_unpack=False, op="ID", clear_boundary=False):
         return (_abi.HALO_REVERSE if is_reverse else 0) | (_abi.HALO_SKIP_UNPACK if skip_unpack else 0) | \
-            _abi.HALO_OPS[op]
+            (_abi.HALO_CLEAR_BOUNDARY if clear_boundary else 0) | _abi.HALO_OPS[op]
 
-    def exchange(self, stream=None, is_reverse=False, skip_unpack=False, op="ID"):
+    def exchange(self, stream=None, is_reverse=False, skip_unpack=False, op="ID", clear_boundary=False):
+        """All dimensions in order.  ``clear_boundary``: the launch that packs a
+        dimension also zeroes that dimension's halo slabs that have no neighbour
+        (what Tensor::clear_halo before the exchange leaves behind), saving one
+        launch per partitioned dimension."""
         call("dcb_halo_exchange", self._plan, _ptr(self.tensor.get_buffer()),
-             self._flags(is_reverse, skip_unpack, op), _stream_ptr(stream))
+             self._flags(is_reverse, skip_unpack, op, clear_boundary), _stream_ptr(stream))
 
-    def pack_put(self, dim, stream=None, is_reverse=False, op="ID"):
+    def pack_put(self, dim, stream=None, is_reverse=False, op="ID", clear_boundary=False):
         call("dcb_halo_pack_put", self._plan, _ptr(self.tensor.get_buffer()), dim,
-             self._flags(is_reverse, False, op), _stream_ptr(stream))
+             self._flags(is_reverse, False, op, clear_boundary), _stream_ptr(stream))
 
     def wait_unpack(self, dim, stream=None, is_reverse=False, op="ID"):
         call("dcb_halo_wait_unpack", self._plan, _ptr(self.tensor.get_buffer()), dim,
@@ -1108,8 +1112,9 @@ class Convolution:
         if not skip_halo_exchange:
             if prof:
                 torch.cuda.nvtx.range_push("conv/forward/exchange_halo")
-            self._clear_halos(input, s)
-            self.forward_exchange_halo(input, s)
+            # Tensor::clear_halo + exchange (convolution.hpp:405-414, 327-340) in one
+            # launch per half: the pack launch zeroes the boundary slabs
+            self.halo_xch_input.exchange(s, clear_boundary=True)
             if prof:
                 torch.cuda.nvtx.range_pop()
         if statistics is not None and float(beta) == 0.0 and input.is_split_root():

@@ -95,6 +95,11 @@ typedef struct dcb_halo_plan dcb_halo_plan;
 /* flags for exchange / pack_put / wait_unpack */
 #define DCB_HALO_REVERSE 0x1u     /* pack halo cells, accumulate into owned cells */
 #define DCB_HALO_SKIP_UNPACK 0x2u /* start only; call dcb_halo_unpack later */
+#define DCB_HALO_CLEAR_BOUNDARY 0x4u /* forward exchange: the pack launch of a
+                                        dimension also zeroes that dimension's halo
+                                        slabs that have no neighbour (the boundary of
+                                        the global tensor), instead of a separate
+                                        dcb_clear_halo pass before the exchange */
 #define DCB_HALO_OP_SHIFT 4
 #define DCB_HALO_OP_ID (0u << DCB_HALO_OP_SHIFT)
 #define DCB_HALO_OP_SUM (1u << DCB_HALO_OP_SHIFT)

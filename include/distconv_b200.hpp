@@ -1344,6 +1344,14 @@ public:
         util::check(dcb_halo_exchange(m_plan, m_tensor.get_buffer(), flags(is_reverse, skip_unpack, op), stream),
                     "halo exchange");
     }
+    // Tensor::clear_halo of every dimension followed by the forward exchange, with
+    // the clearing done by the pack launches (only slabs without a neighbour need
+    // it: the others are overwritten)
+    void clear_and_exchange(cudaStream_t stream)
+    {
+        util::check(dcb_halo_exchange(m_plan, m_tensor.get_buffer(), DCB_HALO_CLEAR_BOUNDARY, stream),
+                    "halo exchange");
+    }
     void unpack(cudaStream_t stream, bool is_reverse = false, HaloExchangeAccumOp op = HaloExchangeAccumOp::ID)
     {
         util::check(dcb_halo_unpack(m_plan, m_tensor.get_buffer(), flags(is_reverse, false, op), stream),
@@ -1840,8 +1848,7 @@ public:
         if (!skip_halo_exchange)
         {
             Range r(m_enable_profiling, "conv/forward/exchange_halo");
-            clear_halos(input);
-            forward_exchange_halo(input);
+            m_halo_xch_input->clear_and_exchange(m_be.get_stream());
         }
         Range r(m_enable_profiling, "conv/forward/forward");
         util::check(dcb_conv_fwd(m_plan_fwd, alpha, input.nd_ptr(m_x_lo), filter, beta, output.get_base_ptr(),
@@ -1861,10 +1868,7 @@ public:
         if (input.get_local_size() == 0 || output.get_local_size() == 0)
             return 0;
         if (!skip_halo_exchange)
-        {
-            clear_halos(input);
-            forward_exchange_halo(input);
-        }
+            m_halo_xch_input->clear_and_exchange(m_be.get_stream());
         if (input.is_split_root())
         {
             const int32_t st = dcb_conv_fwd_stats(m_plan_fwd, alpha, input.nd_ptr(m_x_lo), filter,
@@ -2287,8 +2291,7 @@ public:
         {
             if (m_be.profiling())
                 util::profile_range_push("pooling/exchange_halo");
-            clear_halos(input);
-            m_halo_xch_input->exchange(m_be.get_stream());
+            m_halo_xch_input->clear_and_exchange(m_be.get_stream());
             if (m_be.profiling())
                 util::profile_range_pop();
         }

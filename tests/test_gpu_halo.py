@@ -58,6 +58,37 @@ def test_exchange_known_answer(shape, locale, overlap):
         assert np.array_equal(t.buffer.cpu().numpy(), O.fill_by_definition(sh, g)), f"rank {sh.rank}"
 
 
+@pytest.mark.parametrize("shape,locale,overlap", CASES)
+def test_exchange_that_clears_the_boundary_slabs_itself(shape, locale, overlap):
+    """DCB_HALO_CLEAR_BOUNDARY: no clear_halo pass before the exchange; the launch
+    that packs a dimension zeroes that dimension's halo slabs at the boundary of
+    the global tensor.  Same known answer, from buffers full of stale values,
+    three exchanges in a row (the double-buffered slabs come round)."""
+    ts = make_ranks(shape, locale, overlap)
+    hxs = None
+    shards = O.make_shards(shape, locale, overlap)
+    for rep in range(3):
+        g = (np.arange(int(np.prod(shape)), dtype=np.float32) * (rep + 1)).reshape(tuple(reversed(shape)))
+        for t in ts:
+            if t.buffer is None:
+                t.allocate()
+            t.buffer.fill_(float("nan"))
+            src = tuple(slice(o, o + l) for o, l in reversed(list(zip(t.offset, t.local_shape))))
+            t.owned().copy_(torch.from_numpy(np.ascontiguousarray(g[src])))
+        if hxs is None:
+            hxs = [dc.HaloExchange(t) for t in ts]
+            emu.connect_halo(hxs)
+        for dim in range(len(shape) - 2):
+            for h in hxs:
+                h.pack_put(dim, clear_boundary=True)
+            for h in hxs:
+                h.wait_unpack(dim)
+        torch.cuda.synchronize()
+        for t, sh, hx in zip(ts, shards, hxs):
+            assert hx.status() == _abi.OK
+            assert np.array_equal(t.buffer.cpu().numpy(), O.fill_by_definition(sh, g)), f"rank {sh.rank} rep {rep}"
+
+
 @pytest.mark.parametrize("shape,locale,overlap", CASES[:8])
 @pytest.mark.parametrize("op", ["SUM", "MAX", "MIN", "ID"])
 def test_reverse_exchange_matches_oracle(shape, locale, overlap, op):
