@@ -47,8 +47,15 @@ LADDER = {1: [1, 1, 1], 2: [1, 1, 2], 4: [1, 2, 2], 8: [2, 2, 2]}
 
 
 def grid_for(n_gpus, partition):
+    """Process grid (W, H, D): the weak-scaling ladder ("auto"), a D-only split
+    ("d"), or an explicit grid "w,h,d" whose product is the GPU count."""
     if partition == "auto" and n_gpus in LADDER:
         return list(LADDER[n_gpus])
+    if "," in partition:
+        grid = [int(v) for v in partition.split(",")]
+        if len(grid) != 3 or grid[0] * grid[1] * grid[2] != n_gpus:
+            raise SystemExit(f"--partition {partition}: need three extents whose product is {n_gpus}")
+        return grid
     return [1, 1, n_gpus]
 
 
@@ -733,8 +740,9 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--partition", default="auto", choices=["auto", "d"],
-                    help="auto: the weak-scaling ladder D / D x H / 2 x 2 x 2 at 2 / 4 / 8 GPUs; d: split D only")
+    ap.add_argument("--partition", default="auto",
+                    help="auto: the weak-scaling ladder D / D x H / 2 x 2 x 2 at 2 / 4 / 8 GPUs; d: split D only; "
+                         "or an explicit process grid w,h,d (e.g. 2,1,1: two GPUs split along W)")
     ap.add_argument("--config", default="cfg2", choices=["cfg2", "cfg1"],
                     help="cfg2 = BASELINE configs[1] (the metric's workload); cfg1 (--impl reference only) = "
                          "BASELINE configs[0] on the reference's own ref::Backend through oracle/_ref/ref_driver")

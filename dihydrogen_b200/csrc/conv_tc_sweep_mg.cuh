@@ -195,10 +195,17 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                     const int lo = ch * Rc, hi = min(R, (ch + 1) * Rc);
                     const int q_lo = lo * CG, q_hi = hi * CG;
                     int q = q_lo + (gq + G - (int) ((base + (uint32_t) q_lo) % (uint32_t) G)) % G;
+                    // (row, channel group) of sub-row q, kept by counting: a division
+                    // per sub-row showed in the converters' and issuers' loop time
+                    int i = q / CG, grp = q - i * CG;
                     bool have = false;
-                    for (; q < q_hi && ok; q += G)
+                    for (; q < q_hi && ok; q += G, grp += G)
                     {
-                        const int i = q / CG, grp = q - i * CG;
+                        while (grp >= CG)
+                        {
+                            grp -= CG;
+                            ++i;
+                        }
                         const int a_slot = gq + G * lap_a;
                         if (!have)
                             ok = mbar_wait(&raw_full[cslot], cphase, abort_flag);
@@ -334,9 +341,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                     const uint32_t par = step & 1;
                     const uint32_t rot = (uint32_t) (d & (MG_SLOTS - 1));
                     int q = real ? (mq + G - (int) (base % (uint32_t) G)) % G : mq;
-                    for (; q < subrows && ok; q += G)
+                    int i = q / CG, grp = q - i * CG;
+                    for (; q < subrows && ok; q += G, grp += G)
                     {
-                        const int i = q / CG, grp = q - i * CG;
+                        while (grp >= CG)
+                        {
+                            grp -= CG;
+                            ++i;
+                        }
                         // only output rows this row adds into may be waited for
                         const int r_hi = min(i, g.th - 1), r_lo = max(0, i - fh + 1);
                         ok = mbar_wait_t<0>(&row_free[r_hi], par, abort_flag);
