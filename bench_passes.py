@@ -45,6 +45,10 @@ def main():
     ap.add_argument("--shape", choices=sorted(SHAPES), default="cfg2")
     ap.add_argument("--local-d", type=int, default=None, help="cfg2 / cfg3l2: D extent of the input shard")
     ap.add_argument("--reps", type=int, default=5)
+    ap.add_argument("--grid", default=None,
+                    help="process grid w,h[,d]: time rank 0's shard of a tensor partitioned this way (the spatial "
+                         "extents above are the SHARD's; halo cells are allocated, rows padded to the pitch, no "
+                         "exchange runs) instead of an unpartitioned tensor")
     args = ap.parse_args()
     import torch
 
@@ -55,16 +59,19 @@ def main():
     if not torch.cuda.is_available():
         raise SystemExit("bench_passes.py needs a CUDA device")
     torch.manual_seed(0)
-    locale = dc.Locale(0, 1)
     N, C_IN, K_OUT, sp, f, stride, pad = SHAPES[args.shape]
     sp = list(sp)
     if args.local_d and len(sp) == 3:
         sp[0] = args.local_d
     nsd = len(sp)
+    grid = [int(v) for v in args.grid.split(",")] if args.grid else [1] * nsd  # W first
+    assert len(grid) == nsd
+    nranks = int(np.prod(grid))
+    locale = dc.Locale(0, nranks)
     strides, dil, pads = [stride] * nsd, [1] * nsd, [pad] * nsd
     fshape = list(reversed(f)) + [C_IN, K_OUT]
-    x = dc.create_input_tensor(list(reversed(sp)) + [C_IN, N], [1] * (nsd + 2), list(reversed(f)), strides, dil,
-                               locale)
+    gshape = [e * g for e, g in zip(reversed(sp), grid)]  # the global tensor: the shard times the grid
+    x = dc.create_input_tensor(gshape + [C_IN, N], grid + [1, 1], list(reversed(f)), strides, dil, locale)
     y = dc.create_convolution_output_tensor(x, fshape, strides, pads, dil)
     z = dc.Tensor(y.shape, locale, y.dist, y._local_of)
     dx = dc.create_d_input_tensor(x)
@@ -76,9 +83,10 @@ def main():
     dz.buffer.normal_()
     w = torch.randn(K_OUT, C_IN, *f, device="cuda") * (2.0 / (C_IN * int(np.prod(f)))) ** 0.5
     dw = torch.zeros_like(w)
-    be = dc.BackendDNNLib(locale, options=dc.Options(), allreduce="peer", allreduce_max_count=4096)
+    be = dc.BackendDNNLib(locale, options=dc.Options(), allreduce="peer", allreduce_max_count=4096,
+                          connect=nranks == 1)
     conv = dc.Convolution(be, nsd + 2)
-    conv.setup(x, w, y, dx, None, dy, pads, strides, dil)
+    conv.setup(x, w, y, dx, None, dy, pads, strides, dil, connect=nranks == 1)
     bn = dc.BatchNormalization(be, nsd + 2, DECAY, EPS, True)
     K = K_OUT
     stats = torch.zeros(2 * K, device="cuda")
@@ -113,26 +121,28 @@ def main():
     ms["bn_bwd_apply"] = timed(lambda: bn.backward_stage2(y, dz, mean, var, scale, g[2], g[3], dy))
     ms["conv_bwd_filter"] = timed(lambda: conv.backward_filter(1.0, x, dy, 0.0, dw, reduce=False))
     ms["conv_bwd_data"] = timed(lambda: conv.backward_data(1.0, w, dy, 0.0, dx, skip_halo_exchange=True))
-    # pooling of the conv output (3^n window, stride 2, pad 1, MAX) and a local
-    # re-distribution of it (one rank: the shuffle's put and wait_unpack kernels)
-    win, pp, ps = [3] * nsd, [1] * nsd, [2] * nsd
-    px = dc.create_input_tensor(list(y.shape), [1] * (nsd + 2), win, ps, [1] * nsd, locale)
-    py = dc.create_pooling_output_tensor(px, win, ps, pp)
-    pdx, pdy = dc.create_d_input_tensor(px), dc.create_pooling_d_output_tensor(py)
-    px.set_view(y.buffer)
-    for t in (py, pdx, pdy):
-        t.allocate()
-    pdy.buffer.normal_()
-    pool = dc.Pooling(be, nsd + 2)
-    pool.setup(px, py, pdx, pdy, win, pp, ps, "MAX")
-    ms["pool_max_fwd"] = timed(lambda: pool.forward(1.0, px, 0.0, py, skip_halo_exchange=True))
-    ms["pool_max_bwd"] = timed(lambda: pool.backward(1.0, py, pdy, px, 0.0, pdx, skip_halo_exchange=True))
-    shf = dc.TensorShuffler(px, pdx)
-    ms["shuffle_local"] = timed(lambda: shf.shuffle_forward(px.get_buffer(), pdx.get_buffer()))
-    ybytes = 4.0 * y.buffer.numel()
-    gbs = {"pool_max_fwd": (ybytes + 4.0 * py.buffer.numel()) / (ms["pool_max_fwd"] * 1e-3) / 1e9,
-           "pool_max_bwd": (2 * ybytes + 8.0 * py.buffer.numel()) / (ms["pool_max_bwd"] * 1e-3) / 1e9,
-           "shuffle_local": 4 * ybytes / (ms["shuffle_local"] * 1e-3) / 1e9}
+    gbs = {}
+    if nranks == 1:
+        # pooling of the conv output (3^n window, stride 2, pad 1, MAX) and a local
+        # re-distribution of it (one rank: the shuffle's put and wait_unpack kernels)
+        win, pp, ps = [3] * nsd, [1] * nsd, [2] * nsd
+        px = dc.create_input_tensor(list(y.shape), [1] * (nsd + 2), win, ps, [1] * nsd, locale)
+        py = dc.create_pooling_output_tensor(px, win, ps, pp)
+        pdx, pdy = dc.create_d_input_tensor(px), dc.create_pooling_d_output_tensor(py)
+        px.set_view(y.buffer)
+        for t in (py, pdx, pdy):
+            t.allocate()
+        pdy.buffer.normal_()
+        pool = dc.Pooling(be, nsd + 2)
+        pool.setup(px, py, pdx, pdy, win, pp, ps, "MAX")
+        ms["pool_max_fwd"] = timed(lambda: pool.forward(1.0, px, 0.0, py, skip_halo_exchange=True))
+        ms["pool_max_bwd"] = timed(lambda: pool.backward(1.0, py, pdy, px, 0.0, pdx, skip_halo_exchange=True))
+        shf = dc.TensorShuffler(px, pdx)
+        ms["shuffle_local"] = timed(lambda: shf.shuffle_forward(px.get_buffer(), pdx.get_buffer()))
+        ybytes = 4.0 * y.buffer.numel()
+        gbs = {"pool_max_fwd": (ybytes + 4.0 * py.buffer.numel()) / (ms["pool_max_fwd"] * 1e-3) / 1e9,
+               "pool_max_bwd": (2 * ybytes + 8.0 * py.buffer.numel()) / (ms["pool_max_bwd"] * 1e-3) / 1e9,
+               "shuffle_local": 4 * ybytes / (ms["shuffle_local"] * 1e-3) / 1e9}
     vox = N * int(np.prod(sp))
     out_vox = N * int(np.prod([(e + 2 * pad - fe) // stride + 1 for e, fe in zip(sp, f)]))
     flop = 2.0 * out_vox * K_OUT * C_IN * int(np.prod(f))

@@ -746,8 +746,8 @@ static int32_t tc_launch(const TcGeom& g_in, float alpha, const float* x, const 
     long long grid = (long long) num_sms();
     if (grid > g.tiles)
         grid = g.tiles;
-    // the spelled-out converter for 4 channels x 3 taps, pad 1, hi / lo split
-    const bool c4f3 = g.c == 4 && g.f[2] == 3 && g.pad[2] == 1 && g.split;
+    // the spelled-out converter for 4 channels x 3 taps, pad 1 or 0 (a shard with its W halo), hi / lo split
+    const bool c4f3 = g.c == 4 && g.f[2] == 3 && g.pad[2] <= 1 && g.split;
     if (c4f3)
     {
         DCB_CUDA_TRY(cudaFuncSetAttribute(tc_conv_kernel<NB, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -837,7 +837,7 @@ static int32_t sw_launch(const SwGeom& g_in, float alpha, const float* w, const 
     long long grid = (long long) num_sms();
     if (grid > g.units)
         grid = g.units;
-    const bool c4f3 = g.c == 4 && g.f[2] == 3 && g.pad[2] == 1 && g.split;
+    const bool c4f3 = g.c == 4 && g.f[2] == 3 && g.pad[2] <= 1 && g.split;
     const bool stats = stat_part != nullptr;
     const int epi = sw_epi_warps();
     long long* prof = nullptr;
@@ -989,7 +989,7 @@ static int32_t mg_launch(const SwGeom& g, float alpha, const float* w, float* bi
     long long grid = (long long) num_sms();
     if (grid > g.units)
         grid = g.units;
-    const bool c4f3 = g.c == 4 && g.f[2] == 3 && g.pad[2] == 1 && g.split;
+    const bool c4f3 = g.c == 4 && g.f[2] == 3 && g.pad[2] <= 1 && g.split;
     if (c4f3)
     {
         DCB_CUDA_TRY(cudaFuncSetAttribute(mg_conv_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,

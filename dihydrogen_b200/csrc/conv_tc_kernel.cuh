@@ -543,7 +543,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                 if (C4F3)
                 {
                     uint32_t v[3][8];
-                    convert_c4f3(raw_s, (uint32_t) pitch, v);
+                    // taps start 4 - pad cells into the staged row: the converter is written for pad 1
+                    convert_c4f3(raw_s + 4u * (uint32_t) (1 - g.pad[2]), (uint32_t) pitch, v);
                     if (!a_first)
                         ok = mbar_wait(&a_empty[a_slot], a_phase, abort_flag);
                     if (!ok)

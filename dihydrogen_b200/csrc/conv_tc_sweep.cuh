@@ -427,7 +427,8 @@ __global__ void __launch_bounds__(sw_threads(EPI), 1)
                         {
                             uint32_t v[5][8];
                             if (!SW_DBG(5))
-                                sw_convert_c4f3(raw_s, pitch, v);
+                                // taps start 4 - pad cells into the staged row: the converter is written for pad 1
+                                sw_convert_c4f3(raw_s + 4u * (uint32_t) (1 - g.pad[2]), pitch, v);
                             else
                             {
 #pragma unroll
