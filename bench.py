@@ -615,7 +615,8 @@ def run_ours(args):
     statuses = [conv.halo_xch_input.status(), be.allreducer.status(),
                 int(_abi.lib().dcb_conv_plan_status(conv._plan_fwd, None))]
     if with_bwd:
-        statuses += [conv.halo_xch_d_output.status(), int(_abi.lib().dcb_conv_plan_status(conv._plan_bwd, None))]
+        statuses += [conv.halo_xch_d_output.status(), int(_abi.lib().dcb_conv_plan_status(conv._plan_bwd, None)),
+                     int(_abi.lib().dcb_conv_plan_status(conv._plan_wgrad, None))]
     check.update(conv_max_rel_err=conv_err, bn_stats_max_rel_err=stats_err, bn_out_max_rel_err=bn_err,
                  tolerance=1e-5, kernel_status_ok=all(s == _abi.OK for s in statuses))
     ok = (check["halo_bit_exact"] and conv_err <= 1e-5 and stats_err <= 1e-5 and bn_err <= 1e-5

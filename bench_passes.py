@@ -115,7 +115,10 @@ def main():
         ms["conv_fwd_with_bn_statistics"] = timed(
             lambda: conv.forward(1.0, x, w, 0.0, y, skip_halo_exchange=True, statistics=(mean, var)))
     ms["bn_stats"] = timed(lambda: bn.forward_stage1(y, mean, var, True))
-    bn.forward(y, mean, var, rm, rv, scale, bias, z, True)
+    if nranks == 1:
+        bn.forward(y, mean, var, rm, rv, scale, bias, z, True)
+    else:  # no peers here: this shard's own sums stand in for the all-reduced ones
+        bn.forward_stage1(y, mean, var, True)
     ms["bn_finalize_apply"] = timed(lambda: bn.forward_stage2(y, mean, var, rm, rv, scale, bias, z, True))
     ms["bn_bwd_reduce"] = timed(lambda: bn.backward_stage1(y, dz, mean, var, scale, g[0], g[1], g[2], g[3]))
     ms["bn_bwd_apply"] = timed(lambda: bn.backward_stage2(y, dz, mean, var, scale, g[2], g[3], dy))
@@ -159,7 +162,8 @@ def main():
                       "forward_ms": round(fwd, 4), "backward_ms": round(bwd, 4),
                       "forward_backward_voxels_per_s": vox / ((fwd + bwd) * 1e-3),
                       "status": [conv.halo_xch_input.status(), int(_abi.lib().dcb_conv_plan_status(conv._plan_fwd, None)),
-                                 int(_abi.lib().dcb_conv_plan_status(conv._plan_bwd, None))]}))
+                                 int(_abi.lib().dcb_conv_plan_status(conv._plan_bwd, None)),
+                                 int(_abi.lib().dcb_conv_plan_status(conv._plan_wgrad, None))]}))
 
 
 if __name__ == "__main__":

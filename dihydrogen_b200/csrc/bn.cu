@@ -1,9 +1,11 @@
 // Batch-normalisation kernels (and LeakyReLU): HBM-bound streaming kernels.
 //
 // Every (n, c) plane of an NC[D]HW window is a set of contiguous runs (see
-// RunGeom).  A "unit" is up to BN_UNIT_VECS vector elements of one run; blocks
-// of channel c (blockIdx.y) stride over that channel's units with 16-byte
-// vector accesses where the strides allow.
+// RunGeom).  A "unit" is up to BN_UNIT_VECS vector elements of one run, or,
+// where runs are short (the rows of a shard with halo cells along W, whose
+// pitch keeps them apart), several consecutive runs; blocks of channel c
+// (blockIdx.y) stride over that channel's units with 16-byte vector accesses
+// where the strides allow.
 //
 // Reductions are two-stage and fixed-order: each block writes its fp64 partial
 // to scratch, the last block of a channel (ticket) folds the partials in index
@@ -23,9 +25,14 @@ constexpr int BN_UNIT_VECS = BN_THREADS * BN_UNROLL; // vector elements per unit
 struct UnitGeom
 {
     RunGeom g;
-    long long upr;   // units per run
+    long long upr;   // units per run (1 when runs are packed)
     long long upc;   // units per channel
     int unit;        // scalars per unit = BN_UNIT_VECS * vector width
+    // Packed short runs: a unit is up to rpu consecutive runs of one outer step,
+    // vpr vector elements each.  Unpacked: rpu = 1, vpr = 0, magic = 0.
+    int rpu, vpr;
+    unsigned magic;  // ceil(2^32 / vpr): e / vpr = umulhi(e, magic) for the e < BN_UNIT_VECS used here
+    long long gpo;   // units per outer step
 };
 
 static UnitGeom make_units(const RunGeom& g, int vec)
@@ -35,18 +42,47 @@ static UnitGeom make_units(const RunGeom& g, int vec)
     u.unit = BN_UNIT_VECS * vec;
     u.upr = (g.len + u.unit - 1) / u.unit;
     u.upc = g.n * g.rows * u.upr;
+    u.rpu = 1;
+    u.vpr = 0;
+    u.magic = 0;
+    u.gpo = 0;
+    const long long vpr = g.len / vec;
+    if (g.rows_inner > 1 && vpr >= 2 && vpr * 2 <= BN_UNIT_VECS)
+    {
+        u.vpr = (int) vpr;
+        u.rpu = (int) (BN_UNIT_VECS / vpr < g.rows_inner ? BN_UNIT_VECS / vpr : g.rows_inner);
+        u.magic = (unsigned) ((0x100000000ull + (unsigned long long) vpr - 1) / (unsigned long long) vpr);
+        u.gpo = (g.rows_inner + u.rpu - 1) / u.rpu;
+        u.upr = 1;
+        u.upc = g.n * (g.rows / g.rows_inner) * u.gpo;
+    }
     return u;
 }
 
 struct UnitPos
 {
     long long nn, row, e0;
-    int count; // scalars in this unit
+    int count; // scalars in this unit (packed: in each of its runs)
+    int nsub;  // runs in this unit
 };
 
 __device__ __forceinline__ UnitPos decode_unit(const UnitGeom& ug, long long u)
 {
     UnitPos p;
+    if (ug.vpr)
+    {
+        const long long grp = u % ug.gpo;
+        const long long t = u / ug.gpo;
+        const long long outers = ug.g.rows / ug.g.rows_inner;
+        const long long first = grp * ug.rpu;
+        p.row = (t % outers) * ug.g.rows_inner + first;
+        p.nn = t / outers;
+        p.e0 = 0;
+        p.count = (int) ug.g.len;
+        const long long left = ug.g.rows_inner - first;
+        p.nsub = left < ug.rpu ? (int) left : ug.rpu;
+        return p;
+    }
     const long long chunk = u % ug.upr;
     const long long t = u / ug.upr;
     p.row = t % ug.g.rows;
@@ -54,7 +90,39 @@ __device__ __forceinline__ UnitPos decode_unit(const UnitGeom& ug, long long u)
     p.e0 = chunk * ug.unit;
     const long long rem = ug.g.len - p.e0;
     p.count = rem < ug.unit ? (int) rem : ug.unit;
+    p.nsub = 1;
     return p;
+}
+
+// Vector element e of a unit: which of the unit's runs it falls into and where.
+struct ElemPos
+{
+    int sub, col;
+    bool on;
+    template <int V>
+    __device__ __forceinline__ long long off(const RunStrides& s) const
+    {
+        return (long long) sub * s.s_inner + (long long) col * V;
+    }
+};
+
+template <bool PACKED>
+__device__ __forceinline__ ElemPos elem_pos(const UnitGeom& ug, const UnitPos& p, int e, int nv)
+{
+    ElemPos q;
+    if (PACKED)
+    {
+        q.sub = (int) __umulhi((unsigned) e, ug.magic);
+        q.col = e - q.sub * ug.vpr;
+        q.on = q.sub < p.nsub;
+    }
+    else
+    {
+        q.sub = 0;
+        q.col = e;
+        q.on = e < nv;
+    }
+    return q;
 }
 
 __device__ __forceinline__ long long unit_offset(const RunStrides& s,
@@ -187,7 +255,7 @@ __device__ __forceinline__ void finish_channel(double (&val)[NV],
     }
 }
 
-template <int V>
+template <int V, bool PACKED>
 __global__ void __launch_bounds__(BN_THREADS)
     bn_stats_kernel(const float* __restrict__ x, RunStrides xs, UnitGeom ug,
                     double* partial, unsigned* tickets,
@@ -205,10 +273,10 @@ __global__ void __launch_bounds__(BN_THREADS)
 #pragma unroll
         for (int k = 0; k < BN_UNROLL; ++k)
         {
-            const int e = threadIdx.x + k * BN_THREADS;
-            on[k] = e < nv;
+            const ElemPos ep = elem_pos<PACKED>(ug, p, threadIdx.x + k * BN_THREADS, nv);
+            on[k] = ep.on;
             if (on[k])
-                v[k].load(xp + (size_t) e * V);
+                v[k].load(xp + ep.template off<V>(xs));
         }
         float s = 0.f, q = 0.f;
 #pragma unroll
@@ -259,7 +327,7 @@ __global__ void bn_finalize_kernel(int channels, long long num_per_sum,
 
 // LEAKY: the leaky ReLU that follows the batch-norm in the same pass
 // (y > 0 ? y : slope * y), one trip through HBM instead of two.
-template <int V, bool LEAKY>
+template <int V, bool LEAKY, bool PACKED>
 __global__ void __launch_bounds__(BN_THREADS)
     bn_apply_kernel(const float* __restrict__ x, RunStrides xs,
                     float* __restrict__ y, RunStrides ys, UnitGeom ug,
@@ -279,18 +347,17 @@ __global__ void __launch_bounds__(BN_THREADS)
         float* yp = y + unit_offset(ys, ug.g, p, c);
         const int nv = p.count / V;
         Vec<V> v[BN_UNROLL];
-        bool on[BN_UNROLL];
+        ElemPos ep[BN_UNROLL];
 #pragma unroll
         for (int k = 0; k < BN_UNROLL; ++k)
         {
-            const int e = threadIdx.x + k * BN_THREADS;
-            on[k] = e < nv;
-            if (on[k])
-                v[k].load(xp + (size_t) e * V);
+            ep[k] = elem_pos<PACKED>(ug, p, threadIdx.x + k * BN_THREADS, nv);
+            if (ep[k].on)
+                v[k].load(xp + ep[k].template off<V>(xs));
         }
 #pragma unroll
         for (int k = 0; k < BN_UNROLL; ++k)
-            if (on[k])
+            if (ep[k].on)
             {
 #pragma unroll
                 for (int i = 0; i < V; ++i)
@@ -299,12 +366,12 @@ __global__ void __launch_bounds__(BN_THREADS)
                     const float o = sc * xhat + bi;
                     v[k].v[i] = LEAKY ? (o > 0.f ? o : o * slope) : o;
                 }
-                v[k].store(yp + (size_t) (threadIdx.x + k * BN_THREADS) * V);
+                v[k].store(yp + ep[k].template off<V>(ys));
             }
     }
 }
 
-template <int V>
+template <int V, bool PACKED>
 __global__ void __launch_bounds__(BN_THREADS)
     bn_bwd_reduce_kernel(const float* __restrict__ x, RunStrides xs,
                          const float* __restrict__ dy, RunStrides ds,
@@ -332,12 +399,12 @@ __global__ void __launch_bounds__(BN_THREADS)
 #pragma unroll
         for (int k = 0; k < BN_UNROLL; ++k)
         {
-            const int e = threadIdx.x + k * BN_THREADS;
-            on[k] = e < nv;
+            const ElemPos ep = elem_pos<PACKED>(ug, p, threadIdx.x + k * BN_THREADS, nv);
+            on[k] = ep.on;
             if (on[k])
             {
-                vx[k].load(xp + (size_t) e * V);
-                vd[k].load(dp + (size_t) e * V);
+                vx[k].load(xp + ep.template off<V>(xs));
+                vd[k].load(dp + ep.template off<V>(ds));
             }
         }
         float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
@@ -370,7 +437,7 @@ __global__ void __launch_bounds__(BN_THREADS)
     });
 }
 
-template <int V>
+template <int V, bool PACKED>
 __global__ void __launch_bounds__(BN_THREADS)
     bn_bwd_apply_kernel(const float* x, RunStrides xs,
                         const float* __restrict__ dy, RunStrides ds, float* dx,
@@ -397,21 +464,20 @@ __global__ void __launch_bounds__(BN_THREADS)
         float* op = dx + unit_offset(os, ug.g, p, c);
         const int nv = p.count / V;
         Vec<V> vx[BN_UNROLL], vd[BN_UNROLL];
-        bool on[BN_UNROLL];
+        ElemPos ep[BN_UNROLL];
 #pragma unroll
         for (int k = 0; k < BN_UNROLL; ++k)
         {
-            const int e = threadIdx.x + k * BN_THREADS;
-            on[k] = e < nv;
-            if (on[k])
+            ep[k] = elem_pos<PACKED>(ug, p, threadIdx.x + k * BN_THREADS, nv);
+            if (ep[k].on)
             {
-                vx[k].load(xp + (size_t) e * V);
-                vd[k].load(dp + (size_t) e * V);
+                vx[k].load(xp + ep[k].template off<V>(xs));
+                vd[k].load(dp + ep[k].template off<V>(ds));
             }
         }
 #pragma unroll
         for (int k = 0; k < BN_UNROLL; ++k)
-            if (on[k])
+            if (ep[k].on)
             {
 #pragma unroll
                 for (int i = 0; i < V; ++i)
@@ -422,13 +488,13 @@ __global__ void __launch_bounds__(BN_THREADS)
                     r += dvar_term * (vx[k].v[i] - m);
                     vd[k].v[i] = r;
                 }
-                vd[k].store(op + (size_t) (threadIdx.x + k * BN_THREADS) * V);
+                vd[k].store(op + ep[k].template off<V>(os));
             }
     }
 }
 
 // mode 0: y = x>0 ? x : slope*x ;  mode 1: dx = x>0 ? dy : slope*dy
-template <int V, int MODE>
+template <int V, int MODE, bool PACKED>
 __global__ void __launch_bounds__(BN_THREADS)
     leaky_relu_kernel(const float* x, RunStrides xs,
                       const float* __restrict__ dy, RunStrides ds, float* out,
@@ -445,20 +511,20 @@ __global__ void __launch_bounds__(BN_THREADS)
 #pragma unroll
         for (int k = 0; k < BN_UNROLL; ++k)
         {
-            const int e = threadIdx.x + k * BN_THREADS;
-            if (e < nv)
+            const ElemPos ep = elem_pos<PACKED>(ug, p, threadIdx.x + k * BN_THREADS, nv);
+            if (ep.on)
             {
                 Vec<V> vx, vd;
-                vx.load(xp + (size_t) e * V);
+                vx.load(xp + ep.template off<V>(xs));
                 if (MODE)
-                    vd.load(dp + (size_t) e * V);
+                    vd.load(dp + ep.template off<V>(ds));
 #pragma unroll
                 for (int i = 0; i < V; ++i)
                 {
                     const float src = MODE ? vd.v[i] : vx.v[i];
                     vx.v[i] = vx.v[i] > 0.f ? src : slope * src;
                 }
-                vx.store(op + (size_t) e * V);
+                vx.store(op + ep.template off<V>(os));
             }
         }
     }
@@ -528,20 +594,37 @@ struct dcb_bn_plan
     int max_blocks = 0;
 };
 
-#define DCB_VEC_DISPATCH(vec, CALL)                                            \
+// PACKED (several short runs per unit) is a template parameter: the kernels that
+// walk long runs keep their plain indexing.
+#define DCB_VEC_DISPATCH(vec, packed, CALL)                                    \
     do                                                                         \
     {                                                                          \
-        if ((vec) == 4)                                                        \
+        if (packed)                                                            \
         {                                                                      \
-            CALL(4);                                                           \
+            if ((vec) == 4)                                                    \
+            {                                                                  \
+                CALL(4, true);                                                 \
+            }                                                                  \
+            else if ((vec) == 2)                                               \
+            {                                                                  \
+                CALL(2, true);                                                 \
+            }                                                                  \
+            else                                                               \
+            {                                                                  \
+                CALL(1, true);                                                 \
+            }                                                                  \
+        }                                                                      \
+        else if ((vec) == 4)                                                   \
+        {                                                                      \
+            CALL(4, false);                                                    \
         }                                                                      \
         else if ((vec) == 2)                                                   \
         {                                                                      \
-            CALL(2);                                                           \
+            CALL(2, false);                                                    \
         }                                                                      \
         else                                                                   \
         {                                                                      \
-            CALL(1);                                                           \
+            CALL(1, false);                                                    \
         }                                                                      \
     } while (0)
 
@@ -604,11 +687,11 @@ int32_t dcb_bn_stats(dcb_bn_plan* plan, const void* x, void* sums,
         return DCB_OK;
     }
     const dim3 grid = bn_grid(mv.ug);
-#define CALL(VV)                                                               \
-    bn_stats_kernel<VV><<<grid, BN_THREADS, 0, as_stream(stream)>>>(           \
+#define CALL(VV, PP)                                                               \
+    bn_stats_kernel<VV, PP><<<grid, BN_THREADS, 0, as_stream(stream)>>>(           \
         static_cast<const float*>(x), mv.s[0], mv.ug, plan->partial,           \
         plan->tickets, static_cast<float*>(sums), static_cast<float*>(sqsums))
-    DCB_VEC_DISPATCH(mv.vec, CALL);
+    DCB_VEC_DISPATCH(mv.vec, mv.ug.vpr != 0, CALL);
 #undef CALL
     DCB_LAUNCH_CHECK();
     return DCB_OK;
@@ -642,20 +725,20 @@ static int32_t bn_apply_impl(const dcb_nd_desc* xd, const void* x, const void* m
     if (mv.ug.upc == 0)
         return DCB_OK;
     const dim3 grid = bn_grid(mv.ug);
-#define CALL(VV)                                                               \
+#define CALL(VV, PP)                                                               \
     if (leaky)                                                                 \
-        bn_apply_kernel<VV, true><<<grid, BN_THREADS, 0, as_stream(stream)>>>( \
+        bn_apply_kernel<VV, true, PP><<<grid, BN_THREADS, 0, as_stream(stream)>>>( \
             static_cast<const float*>(x), mv.s[0], static_cast<float*>(y),     \
             mv.s[1], mv.ug, static_cast<const float*>(mean),                   \
             static_cast<const float*>(var), static_cast<const float*>(scale),  \
             static_cast<const float*>(bias), eps, slope);                      \
     else                                                                       \
-        bn_apply_kernel<VV, false><<<grid, BN_THREADS, 0, as_stream(stream)>>>(\
+        bn_apply_kernel<VV, false, PP><<<grid, BN_THREADS, 0, as_stream(stream)>>>(\
             static_cast<const float*>(x), mv.s[0], static_cast<float*>(y),     \
             mv.s[1], mv.ug, static_cast<const float*>(mean),                   \
             static_cast<const float*>(var), static_cast<const float*>(scale),  \
             static_cast<const float*>(bias), eps, slope)
-    DCB_VEC_DISPATCH(mv.vec, CALL);
+    DCB_VEC_DISPATCH(mv.vec, mv.ug.vpr != 0, CALL);
 #undef CALL
     DCB_LAUNCH_CHECK();
     return DCB_OK;
@@ -700,15 +783,15 @@ int32_t dcb_bn_bwd_reduce(dcb_bn_plan* plan, const void* x,
         return DCB_OK;
     }
     const dim3 grid = bn_grid(mv.ug);
-#define CALL(VV)                                                               \
-    bn_bwd_reduce_kernel<VV><<<grid, BN_THREADS, 0, as_stream(stream)>>>(      \
+#define CALL(VV, PP)                                                               \
+    bn_bwd_reduce_kernel<VV, PP><<<grid, BN_THREADS, 0, as_stream(stream)>>>(      \
         static_cast<const float*>(x), mv.s[0], static_cast<const float*>(dy),  \
         mv.s[1], mv.ug, static_cast<const float*>(mean),                       \
         static_cast<const float*>(var), static_cast<const float*>(scale), eps, \
         plan->partial, plan->tickets, static_cast<float*>(dscale),             \
         static_cast<float*>(dbias), static_cast<float*>(dmean),                \
         static_cast<float*>(dvar))
-    DCB_VEC_DISPATCH(mv.vec, CALL);
+    DCB_VEC_DISPATCH(mv.vec, mv.ug.vpr != 0, CALL);
 #undef CALL
     DCB_LAUNCH_CHECK();
     return DCB_OK;
@@ -732,14 +815,14 @@ int32_t dcb_bn_bwd_apply(const dcb_nd_desc* xd, const void* x,
     if (mv.ug.upc == 0)
         return DCB_OK;
     const dim3 grid = bn_grid(mv.ug);
-#define CALL(VV)                                                               \
-    bn_bwd_apply_kernel<VV><<<grid, BN_THREADS, 0, as_stream(stream)>>>(       \
+#define CALL(VV, PP)                                                               \
+    bn_bwd_apply_kernel<VV, PP><<<grid, BN_THREADS, 0, as_stream(stream)>>>(       \
         static_cast<const float*>(x), mv.s[0], static_cast<const float*>(dy),  \
         mv.s[1], static_cast<float*>(dx), mv.s[2], mv.ug,                      \
         static_cast<const float*>(mean), static_cast<const float*>(var),       \
         static_cast<const float*>(scale), static_cast<const float*>(dmean),    \
         static_cast<const float*>(dvar), eps, (long long) num_per_sum)
-    DCB_VEC_DISPATCH(mv.vec, CALL);
+    DCB_VEC_DISPATCH(mv.vec, mv.ug.vpr != 0, CALL);
 #undef CALL
     DCB_LAUNCH_CHECK();
     return DCB_OK;
@@ -758,11 +841,11 @@ int32_t dcb_leaky_relu_fwd(const dcb_nd_desc* xd, const void* x, float slope,
     if (mv.ug.upc == 0)
         return DCB_OK;
     const dim3 grid = bn_grid(mv.ug);
-#define CALL(VV)                                                               \
-    leaky_relu_kernel<VV, 0><<<grid, BN_THREADS, 0, as_stream(stream)>>>(      \
+#define CALL(VV, PP)                                                               \
+    leaky_relu_kernel<VV, 0, PP><<<grid, BN_THREADS, 0, as_stream(stream)>>>(      \
         static_cast<const float*>(x), mv.s[0], nullptr, mv.s[0],               \
         static_cast<float*>(y), mv.s[1], mv.ug, slope)
-    DCB_VEC_DISPATCH(mv.vec, CALL);
+    DCB_VEC_DISPATCH(mv.vec, mv.ug.vpr != 0, CALL);
 #undef CALL
     DCB_LAUNCH_CHECK();
     return DCB_OK;
@@ -782,11 +865,11 @@ int32_t dcb_leaky_relu_bwd(const dcb_nd_desc* xd, const void* x,
     if (mv.ug.upc == 0)
         return DCB_OK;
     const dim3 grid = bn_grid(mv.ug);
-#define CALL(VV)                                                               \
-    leaky_relu_kernel<VV, 1><<<grid, BN_THREADS, 0, as_stream(stream)>>>(      \
+#define CALL(VV, PP)                                                               \
+    leaky_relu_kernel<VV, 1, PP><<<grid, BN_THREADS, 0, as_stream(stream)>>>(      \
         static_cast<const float*>(x), mv.s[0], static_cast<const float*>(dy),  \
         mv.s[1], static_cast<float*>(dx), mv.s[2], mv.ug, slope)
-    DCB_VEC_DISPATCH(mv.vec, CALL);
+    DCB_VEC_DISPATCH(mv.vec, mv.ug.vpr != 0, CALL);
 #undef CALL
     DCB_LAUNCH_CHECK();
     return DCB_OK;
@@ -874,11 +957,11 @@ extern "C" int32_t dcb_bn_stats_noalloc(const dcb_nd_desc* xd, const void* x, vo
     // The array keeps whatever the previous call (or an interrupted one) left:
     // the arrival tickets must start at zero.  Partials are overwritten.
     DCB_CUDA_TRY(cudaMemsetAsync(tickets, 0, xd->c * sizeof(unsigned), as_stream(stream)));
-#define CALL(VV)                                                               \
-    bn_stats_kernel<VV><<<grid, BN_THREADS, 0, as_stream(stream)>>>(           \
+#define CALL(VV, PP)                                                               \
+    bn_stats_kernel<VV, PP><<<grid, BN_THREADS, 0, as_stream(stream)>>>(           \
         static_cast<const float*>(x), mv.s[0], mv.ug, partial, tickets,        \
         static_cast<float*>(sums), static_cast<float*>(sqsums))
-    DCB_VEC_DISPATCH(mv.vec, CALL);
+    DCB_VEC_DISPATCH(mv.vec, mv.ug.vpr != 0, CALL);
 #undef CALL
     DCB_LAUNCH_CHECK();
     return DCB_OK;

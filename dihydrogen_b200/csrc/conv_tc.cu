@@ -703,16 +703,48 @@ static EncodeTiledFn encode_tiled_fn()
     return fn;
 }
 
+// Floats between the 16-byte boundary at or below x and x.  A shard with halo cells
+// along W is laid out so that its OWNED cells start on a 16-byte boundary (stores and
+// the streaming kernels want that); its window, which starts with the halo cells, then
+// does not.  A bulk copy can over-fetch but not start in between, so such a window is
+// described from the boundary below it and the kernel skips the cells in front.  Those
+// cells lie in the same allocation (allocations start 16-byte aligned) and are only read.
+static inline int x_skip(const float* x)
+{
+    return (int) ((reinterpret_cast<uintptr_t>(x) & 15) / 4);
+}
+
+// Where a staged row starts relative to the first output of a tile (lx) and where tap 0
+// sits in it (rx).  Aligned window: 4 cells of margin on the left for the padding.
+// Skipped cells in front (only with pad 0): the row starts at the tile's first output.
+template <class Geom>
+static void tc_row_window(Geom& g, int skip)
+{
+    g.lx = skip ? 0 : -4;
+    g.rx = skip ? skip : 4 - g.pad[2];
+}
+
+// can a window that starts `skip` floats above a 16-byte boundary be staged in rows of row_w cells?
+static bool skip_ok(int skip, int pad_w, int fw, int tile_w, int row_w)
+{
+    if (skip == 0)
+        return true;
+    // cells left of the window are not zeros here, so nothing may read them as padding
+    return pad_w == 0 && skip + fw - 1 + tile_w <= row_w;
+}
+
 // Descriptor of the input window as a 5-D tensor (W, H, D, C, N) whose box is
 // chunk_rows raw rows of every channel.  Returns false when the window cannot be
 // described (alignment), in which case the register-fed producers run.
 static bool make_x_map(const TcGeom& g, const float* x, CUtensorMap* map)
 {
     EncodeTiledFn fn = encode_tiled_fn();
-    if (!fn || (reinterpret_cast<uintptr_t>(x) & 15) != 0)
+    const int skip = x_skip(x);
+    if (!fn || (reinterpret_cast<uintptr_t>(x) & 3) != 0 || !skip_ok(skip, g.pad[2], g.f[2], TC_M, TC_RAW_W))
         return false;
-    const cuuint64_t dims[5] = {(cuuint64_t) g.in[2], (cuuint64_t) g.in[1], (cuuint64_t) g.in[0], (cuuint64_t) g.c,
-                                (cuuint64_t) g.n};
+    x -= skip;
+    const cuuint64_t dims[5] = {(cuuint64_t) (g.in[2] + skip), (cuuint64_t) g.in[1], (cuuint64_t) g.in[0],
+                                (cuuint64_t) g.c, (cuuint64_t) g.n};
     // a dimension of extent 1 may carry any stride; give it a valid one
     const long long s1 = g.xs[1], s0 = g.in[0] > 1 ? g.xs[0] : g.xs[1] * g.in[1];
     const cuuint64_t strides[4] = {(cuuint64_t) s1 * 4, (cuuint64_t) s0 * 4, (cuuint64_t) g.xs_c * 4,
@@ -740,6 +772,7 @@ static int32_t tc_launch(const TcGeom& g_in, float alpha, const float* x, const 
         g.use_tma = 0; // the converters fetch their own rows
         tc_size_raw_ring(g);
     }
+    tc_row_window(g, g.use_tma ? x_skip(x) : 0);
     const size_t smem = tc_smem_bytes(g);
     if (smem > 220 * 1024)
         return DCB_UNSUPPORTED;
@@ -776,6 +809,8 @@ static bool sw_make_x_map(const SwGeom& g, const float* x, CUtensorMap* map)
     {
         t.in[i] = g.in[i];
         t.xs[i] = g.xs[i];
+        t.pad[i] = g.pad[i];
+        t.f[i] = g.f[i];
     }
     t.n = g.n;
     t.c = g.c;
@@ -822,6 +857,7 @@ static int32_t sw_launch(const SwGeom& g_in, float alpha, const float* w, const 
                          float* stat_part = nullptr, float* sums = nullptr, float* sqsums = nullptr)
 {
     SwGeom g = g_in;
+    tc_row_window(g, x_skip(x));
 #if DCB_SW_KNOCKOUT
     // knock-out bits for timing experiments (results are wrong with any of them set)
     g.nsets = std::getenv("DCB_SW_DBG") ? std::atoi(std::getenv("DCB_SW_DBG")) : 0;
@@ -937,6 +973,8 @@ static bool mg_make_x_map(const SwGeom& g, const float* x, CUtensorMap* map)
     {
         t.in[i] = g.in[i];
         t.xs[i] = g.xs[i];
+        t.pad[i] = g.pad[i];
+        t.f[i] = g.f[i];
     }
     t.n = g.n;
     t.c = g.w_c_total;
@@ -975,9 +1013,11 @@ static bool mg_make_y_map(const SwGeom& g, float* y, CUtensorMap* map)
            == CUDA_SUCCESS;
 }
 
-static int32_t mg_launch(const SwGeom& g, float alpha, const float* w, float* bimg, float* y, int* status,
-                         const CUtensorMap& xmap, cudaStream_t stream)
+static int32_t mg_launch(const SwGeom& g_in, float alpha, const float* w, const float* x, float* bimg, float* y,
+                         int* status, const CUtensorMap& xmap, cudaStream_t stream)
 {
+    SwGeom g = g_in;
+    tc_row_window(g, x_skip(x));
     CUtensorMap ymap;
     std::memset(&ymap, 0, sizeof(ymap));
     const int use_ymap = mg_make_y_map(g, y, &ymap) ? 1 : 0;
@@ -1018,7 +1058,7 @@ int32_t tc_conv_fwd(TcPlan* p, int slot, float alpha, const float* x, const floa
         CUtensorMap xmap;
         std::memset(&xmap, 0, sizeof(xmap));
         if (mg_make_x_map(p->mg[slot], x, &xmap))
-            return mg_launch(p->mg[slot], alpha, w, p->mg_bimg[slot], y, p->status, xmap, stream);
+            return mg_launch(p->mg[slot], alpha, w, x, p->mg_bimg[slot], y, p->status, xmap, stream);
     }
     if (p->has_sw[slot])
     {
@@ -1112,14 +1152,17 @@ int32_t tc_conv_fwd_stats(TcPlan* p, float alpha, const float* x, const float* w
 }
 
 // 5-D map (W, H, D, channels, N) of a strided window with the given box.
+// `skip` floats in front of the window are mapped with it (see x_skip): base - skip must be aligned.
 static bool wg_make_map(const float* base, const int ext[3], int channels, int n, const long long sp[3],
-                        long long s_c, long long s_n, int box_w, int box_h, int box_c, CUtensorMap* map)
+                        long long s_c, long long s_n, int box_w, int box_h, int box_c, CUtensorMap* map,
+                        int skip = 0)
 {
     EncodeTiledFn fn = encode_tiled_fn();
+    base -= skip;
     if (!fn || (reinterpret_cast<uintptr_t>(base) & 15) != 0)
         return false;
-    const cuuint64_t dims[5] = {(cuuint64_t) ext[2], (cuuint64_t) ext[1], (cuuint64_t) ext[0], (cuuint64_t) channels,
-                                (cuuint64_t) n};
+    const cuuint64_t dims[5] = {(cuuint64_t) (ext[2] + skip), (cuuint64_t) ext[1], (cuuint64_t) ext[0],
+                                (cuuint64_t) channels, (cuuint64_t) n};
     const long long s1 = ext[1] > 1 ? sp[1] : ext[2];
     const long long s0 = ext[0] > 1 ? sp[0] : s1 * ext[1];
     const long long sc = channels > 1 ? s_c : s0 * ext[0];
@@ -1141,8 +1184,13 @@ int32_t tc_conv_bwd_filter(TcPlan* p, float alpha, const float* x, const float* 
 {
     if (!p || !p->has_wg)
         return DCB_UNSUPPORTED;
-    const WgGeom& g = p->wg;
+    WgGeom g = p->wg;
     const ConvGeom& cg = p->wg_cg;
+    const int skip = x_skip(x);
+    if ((reinterpret_cast<uintptr_t>(x) & 3) != 0 || g.stride[2] != 1 && skip != 0
+        || !skip_ok(skip, g.pad[2], g.f[2], WG_TW, WG_XW))
+        return DCB_UNSUPPORTED; // the caller falls back to the CUDA-core kernel
+    tc_row_window(g, skip);
     size_t smem = wg_smem_need(g);
     smem = smem < 120 * 1024 ? 120 * 1024 : smem; // one CTA per SM
     long long grid = (long long) num_sms();
@@ -1155,7 +1203,7 @@ int32_t tc_conv_bwd_filter(TcPlan* p, float alpha, const float* x, const float* 
     {
         std::memset(&xmaps[cgp], 0, sizeof(CUtensorMap));
         if (!wg_make_map(x + (size_t) cgp * g.c * cg.xs_c, cg.in, g.c, cg.n, cg.xs, cg.xs_c, cg.xs_n, WG_XW, g.f[1],
-                         g.c, &xmaps[cgp]))
+                         g.c, &xmaps[cgp], skip))
             return DCB_UNSUPPORTED; // the caller falls back to the CUDA-core kernel
     }
     for (int kg = 0; kg < g.kgroups; ++kg)

@@ -26,6 +26,10 @@ struct TcGeom
 {
     int n, c, k;
     int in[3], out[3], f[3], pad[3];
+    // A staged raw row holds the input cells from ow0 + lx on (lx a multiple of 4, what a
+    // bulk copy can start at); tap kw of output ow0 + j sits rx + kw + j cells into it.
+    // Set per launch from the input pointer's alignment (tc_row_window).
+    int lx, rx;
     long long xs_n, xs_c, xs[3];
     long long ys_n, ys_c, ys[3];
     int split;   // 1: 3xTF32, 0: single TF32 pass
@@ -458,7 +462,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     {
         const int part = r / g.crows, rem = r % g.crows;
         const int c = rem / g.f[2], kw = rem % g.f[2];
-        const uint32_t off = (uint32_t) (c * (g.use_tma ? g.chunk_rows * TC_RAW_W : TC_RAW_PRIV) + 4 + kw - g.pad[2]);
+        const uint32_t off = (uint32_t) (c * (g.use_tma ? g.chunk_rows * TC_RAW_W : TC_RAW_PRIV) + g.rx + kw);
         ktab[r] = (part < (g.split ? 2 : 1)) ? (off | ((uint32_t) part << 16)) : ((2u << 16) | 4u);
     }
     for (int i = tid; i < g.b_bytes / 16; i += TC_THREADS)
@@ -531,7 +535,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                     for (int e = lane; e < g.c * TC_RAW_PRIV; e += 32)
                     {
                         const int c = e / TC_RAW_PRIV, j = e - c * TC_RAW_PRIV;
-                        const int iw = t.ow0 + quad * 32 - 4 + j;
+                        const int iw = t.ow0 + quad * 32 + g.lx + j;
                         raw[e] = (iw >= 0 && iw < g.in[2]) ? src[(size_t) c * g.xs_c + iw] : 0.f;
                     }
                     __syncwarp();
@@ -543,8 +547,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                 if (C4F3)
                 {
                     uint32_t v[3][8];
-                    // taps start 4 - pad cells into the staged row: the converter is written for pad 1
-                    convert_c4f3(raw_s + 4u * (uint32_t) (1 - g.pad[2]), (uint32_t) pitch, v);
+                    // the converter is written for taps that start 3 cells into the staged row
+                    convert_c4f3(raw_s + 4u * (uint32_t) (g.rx - 3), (uint32_t) pitch, v);
                     if (!a_first)
                         ok = mbar_wait(&a_empty[a_slot], a_phase, abort_flag);
                     if (!ok)
@@ -663,7 +667,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                             // 4 floats, as the 16-byte rule for the innermost
                             // coordinate demands; rows above or below the
                             // image arrive as zeros and are never converted
-                            tma_load_5d(raw_ring + (size_t) slot * g.raw_slot_bytes, &xmap, t.ow0 - 4,
+                            tma_load_5d(raw_ring + (size_t) slot * g.raw_slot_bytes, &xmap, t.ow0 + g.lx,
                                         t.oh0 - g.pad[1] + ch * Rc, t.od - g.pad[0] + kd, 0, t.n, &raw_full[slot]);
                         }
                         __syncwarp();

@@ -103,6 +103,7 @@ struct SwGeom
     int w_c_off;    // first input channel of this launch's group
     int cgroups;    // launches per convolution = w_c_total / c
     int in[3], out[3], f[3], pad[3];
+    int lx, rx;     // as in TcGeom: where a staged row starts, where its first tap sits
     long long xs_n, xs_c, xs[3];
     long long ys_n, ys_c, ys[3];
     int split;      // 1: 3xTF32, 0: single TF32 pass
@@ -364,7 +365,7 @@ __global__ void __launch_bounds__(sw_threads(EPI), 1)
     {
         const int part = r / g.crows, rem = r % g.crows;
         const int c = rem / g.f[2], kw = rem % g.f[2];
-        const uint32_t off = (uint32_t) (c * g.chunk_rows * TC_RAW_W + 4 + kw - g.pad[2]);
+        const uint32_t off = (uint32_t) (c * g.chunk_rows * TC_RAW_W + g.rx + kw);
         const uint32_t sel = part < (g.split ? 3 : 1) ? (part == 1 ? 1u : 0u) : 2u;
         ktab[r] = sel == 2u ? ((2u << 16) | 4u) : (off | (sel << 16));
     }
@@ -427,8 +428,8 @@ __global__ void __launch_bounds__(sw_threads(EPI), 1)
                         {
                             uint32_t v[5][8];
                             if (!SW_DBG(5))
-                                // taps start 4 - pad cells into the staged row: the converter is written for pad 1
-                                sw_convert_c4f3(raw_s + 4u * (uint32_t) (1 - g.pad[2]), pitch, v);
+                                // the converter is written for taps that start 3 cells into the staged row
+                                sw_convert_c4f3(raw_s + 4u * (uint32_t) (g.rx - 3), pitch, v);
                             else
                             {
 #pragma unroll
@@ -527,7 +528,7 @@ __global__ void __launch_bounds__(sw_threads(EPI), 1)
                     {
                         mbar_expect_tx(&raw_full[slot], bytes);
                         // x starts 4 cells left of the column: a multiple of 4 floats
-                        tma_load_5d(raw_ring + (size_t) slot * g.raw_slot_bytes, &xmap, t.ow0 - 4,
+                        tma_load_5d(raw_ring + (size_t) slot * g.raw_slot_bytes, &xmap, t.ow0 + g.lx,
                                     t.oh0 - g.pad[1] + ch * g.chunk_rows, d, 0, t.n, &raw_full[slot]);
                     }
                     __syncwarp();

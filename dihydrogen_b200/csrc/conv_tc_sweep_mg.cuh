@@ -151,7 +151,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     {
         const int part = r / g.crows, rem = r % g.crows;
         const int c = rem / g.f[2], kw = rem % g.f[2];
-        const uint32_t off = (uint32_t) (c * g.chunk_rows * TC_RAW_W + 4 + kw - g.pad[2]);
+        const uint32_t off = (uint32_t) (c * g.chunk_rows * TC_RAW_W + g.rx + kw);
         const uint32_t sel = part < (g.split ? 3 : 1) ? (part == 1 ? 1u : 0u) : 2u;
         ktab[r] = sel == 2u ? ((2u << 16) | 4u) : (off | (sel << 16));
     }
@@ -220,7 +220,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                         {
                             uint32_t v[5][8];
                             // taps start 4 - pad cells into the staged row: the converter is written for pad 1
-                            sw_convert_c4f3<true>(raw_s + 4u * (uint32_t) (1 - g.pad[2]), pitch, v);
+                            sw_convert_c4f3<true>(raw_s + 4u * (uint32_t) (g.rx - 3), pitch, v);
                             if (!a_first)
                                 ok = mbar_wait(&a_empty[a_slot], a_phase, abort_flag);
                             if (!ok)
@@ -294,7 +294,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                     if (lane == 0)
                     {
                         mbar_expect_tx(&raw_full[slot], bytes);
-                        tma_load_5d(raw_ring + (size_t) slot * g.raw_slot_bytes, &xmap, t.ow0 - 4,
+                        tma_load_5d(raw_ring + (size_t) slot * g.raw_slot_bytes, &xmap, t.ow0 + g.lx,
                                     t.oh0 - g.pad[1] + ch * g.chunk_rows, d, 0, t.n, &raw_full[slot]);
                     }
                     __syncwarp();

@@ -65,6 +65,7 @@ struct WgGeom
 {
     int n, c, k;
     int in[3], out[3], f[3], pad[3];
+    int lx, rx;             // as in TcGeom, for the staged input rows of a unit
     int mrows;              // c * fd * fh * fw
     int tiles_w;
     long long units;        // n * out_d * out_h * tiles_w
@@ -171,7 +172,7 @@ __global__ void __launch_bounds__(WG_THREADS, 1)
             r /= g.f[1];
             const int kd = r % g.f[0];
             const int c = r / g.f[0];
-            src = kd * g.xplane_floats + (c * g.f[1] + kh) * WG_XW + 4 - g.pad[2] + kw;
+            src = kd * g.xplane_floats + (c * g.f[1] + kh) * WG_XW + g.rx + kw;
         }
         // this lane's element of the B tile: filter quad*4 + lane/8, output lane%8
         const int bk = quad * 4 + (lane >> 3), bkk = lane & 7;
@@ -282,12 +283,12 @@ __global__ void __launch_bounds__(WG_THREADS, 1)
                 const int ow0 = (int) tw * WG_TW;
                 uint8_t* dst = ubuf + (size_t) b * unit_bytes;
                 mbar_expect_tx(&u_full[b], bytes);
-                // the window starts 4 cells left of the first tap: a multiple of 4 floats
+                // the window starts at a multiple of 4 floats at or left of the first tap
                 for (int kd = 0; kd < g.f[0]; ++kd)
 #pragma unroll
                     for (int h = 0; h < SW; ++h)
                         tma_load_5d(dst + ((size_t) kd * g.xplane_floats + (size_t) h * g.xhalf_floats) * 4, &xmap,
-                                    ow0 * SW - 4 + h * 128, oh * g.stride[1] - g.pad[1],
+                                    ow0 * SW + g.lx + h * 128, oh * g.stride[1] - g.pad[1],
                                     od * g.stride[0] - g.pad[0] + kd, 0, n, &u_full[b]);
                 tma_load_5d(dst + g.xbuf_bytes, &dymap, ow0, oh, od, 0, n, &u_full[b]);
             }

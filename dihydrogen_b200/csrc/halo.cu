@@ -259,8 +259,10 @@ static bool slab_geom(const dcb_tensor_desc& d, int dim, int side, int width,
     if (dim < 0 || dim >= d.ndims || width <= 0)
         return false;
     // Rows may be padded (desc.pitch): a W face is then `width` cells per row at
-    // stride pitch; H and D faces are whole rows and planes, padding cells
-    // included (nobody reads them).
+    // stride pitch; H and D faces are whole rows and planes, the padding cells
+    // between rows included (nobody reads them) but not those after the last
+    // row: the shard may start a few floats into its allocation (owned cells on
+    // a 16-byte boundary), and then its last row's padding ends beyond it.
     const long long pitch = row_pitch(d);
     long long below = 1, above = 1;
     for (int e = 0; e < dim; ++e)
@@ -277,7 +279,7 @@ static bool slab_geom(const dcb_tensor_desc& d, int dim, int side, int width,
     if (start < 0 || start + width > n)
         return false;
     g->runs = above;
-    g->len = (long long) width * below;
+    g->len = (long long) width * below - (dim > 0 ? pitch - d.real_shape[0] : 0);
     g->stride = (dim == 0 ? pitch : n) * below;
     g->start = start * below;
     return true;

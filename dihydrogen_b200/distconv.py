@@ -216,11 +216,17 @@ class Tensor:
         # of 16 bytes; such rows are padded to PITCH_ALIGN floats so that the
         # bulk-copy fed tensor-core kernels can address them.  Shards without a
         # W halo stay dense.  pitch_align=1 forces dense rows.
+        # Inside a padded row the halo-extended cells start `lead` floats in, so
+        # that the OWNED cells start on a 16-byte boundary: bulk stores and
+        # vector accesses of the kernels that write a shard's interior need
+        # that, while the kernels that read the window with its halo fetch from
+        # the boundary below it.  Row: [lead pad][halo][owned][halo][tail pad].
         if pitch_align is None:
             pitch_align = self.PITCH_ALIGN if self.dist.overlap[0] > 0 else 1
         self.pitch_align = max(1, int(pitch_align))
         real_w = self.local_shape[0] + 2 * self.dist.overlap[0]
-        self.pitch = -(-real_w // self.pitch_align) * self.pitch_align
+        self.lead = (-self.dist.overlap[0]) % self.pitch_align
+        self.pitch = -(-(self.lead + real_w) // self.pitch_align) * self.pitch_align
         self.buffer: Optional[torch.Tensor] = None
         self._storage: Optional[torch.Tensor] = None
 
@@ -328,7 +334,8 @@ class Tensor:
         """Use ``buf`` as the shard's memory (tensor.hpp:604-623 View): either
         a contiguous array of the pitched shape (new_storage) or, for a dense
         shard, of the halo-extended shape.  ``buffer`` is the halo-extended
-        shard without the row padding, a strided view when rows are padded."""
+        shard without the row padding, a strided view when rows are padded
+        (it starts ``lead`` floats into the array)."""
         real_w = self.local_shape[0] + 2 * self.dist.overlap[0]
         if tuple(buf.shape) == self.np_real_shape() and buf.stride(-1) == 1 and (
                 buf.dim() < 2 or buf.stride(-2) == self.pitch):
@@ -339,7 +346,7 @@ class Tensor:
         assert tuple(buf.shape) == tuple(reversed(self.get_local_pitched_shape())) and buf.is_contiguous(), \
             "set_view wants an array of the pitched shape"
         self._storage = buf
-        self.buffer = buf[..., :real_w] if self.pitch != real_w else buf
+        self.buffer = buf[..., self.lead:self.lead + real_w] if self.pitch != real_w else buf
 
     def get_buffer(self) -> int:
         return self.buffer.data_ptr()
@@ -900,13 +907,15 @@ class Convolution:
         self.nsd = num_dims - 2
         self._plan_fwd = ctypes.c_void_p()
         self._plan_bwd = ctypes.c_void_p()
+        self._plan_wgrad = ctypes.c_void_p()
         self.halo_xch_input = None
         self.halo_xch_d_output = None
         self._ready = False
 
     def __del__(self):
         try:
-            for p in [getattr(self, "_plan_fwd", None), getattr(self, "_plan_bwd", None)] + list(
+            for p in [getattr(self, "_plan_fwd", None), getattr(self, "_plan_bwd", None),
+                      getattr(self, "_plan_wgrad", None)] + list(
                     getattr(self, "_ov_plans", [])):
                 if p:
                     _abi.lib().dcb_conv_plan_destroy(p)
@@ -971,9 +980,30 @@ class Convolution:
         self._plan_fwd = self._make_plan(xd, yd, pads_fp)
         self._setup_overlap(input, xd, yd, pads_fp, lo, hi)
         if d_output is not None:
+            # Backward data.  The reference hands cuDNN the halo-extended d_input
+            # (convolution.hpp:2541-2670), whose halo cells then receive partial
+            # sums nobody reads.  Where a partitioned dimension has unit stride
+            # and dilation only the OWNED cells of d_input are computed here:
+            # they start on a 16-byte boundary of a padded row (the halo cells do
+            # not), which the bulk stores of the tensor-core kernels need, and
+            # no work goes into cells that are thrown away.  In the descriptor's
+            # terms the padding grows by d_output's halo width.
             dyd = d_output.full_nd_desc()
-            dxd = (d_input or input).nd_desc(lo, hi)
+            dyov = d_output.get_overlap()
+            dlo, dhi = list(lo), list(hi)
+            for i in range(nsd):
+                if ov[i] > 0 and strides[i] == 1 and dilations[i] == 1:
+                    dlo[i] = dhi[i] = 0
+                    pads_bp[i] = stencil[i] + dyov[i]
+            self._dx_lo = dlo
+            dxd = (d_input or input).nd_desc(dlo, dhi)
             self._plan_bwd = self._make_plan(dxd, dyd, pads_bp)
+            # Backward filter: the forward geometry with d_output's owned cells in
+            # the output's place.  (The reference passes the halo-extended
+            # d_output with its halo cleared, convolution.hpp:878-1107; the owned
+            # cells alone give the same sums, start on a 16-byte boundary and need
+            # no clearing.)
+            self._plan_wgrad = self._make_plan(xd, d_output.nd_desc(), pads_fp)
         self._ready = True
 
     def _setup_overlap(self, input: Tensor, xd: NdDesc, yd: NdDesc, pads_fp, lo, hi):
@@ -1058,16 +1088,18 @@ class Convolution:
         call("dcb_conv_plan_create", ctypes.byref(cd), ctypes.byref(xd), ctypes.byref(yd), ctypes.byref(plan))
         return plan
 
+    def _plan_of(self, which: int):
+        return (self._plan_fwd, self._plan_bwd, self._plan_wgrad)[which]
+
     def kernel_kind(self, which: int) -> int:
-        plan = self._plan_fwd if which == 0 else self._plan_bwd
+        plan = self._plan_of(which)
         return _abi.lib().dcb_conv_plan_kernel_kind(plan, which)
 
     def kernel_variant(self, which: int) -> int:
         """dcb_conv_plan_kernel_variant: 0 fp32 CUDA-core, 1 / 2 tcgen05 row
         kernel (bulk-copy fed / register fed), 3 sweep, 4 multi-group sweep,
         5 tcgen05 backward filter."""
-        plan = self._plan_fwd if which == 0 else self._plan_bwd
-        return _abi.lib().dcb_conv_plan_kernel_variant(plan, which)
+        return _abi.lib().dcb_conv_plan_kernel_variant(self._plan_of(which), which)
 
     # -- halo --
     def _clear_halos(self, t: Tensor, stream):
@@ -1080,7 +1112,8 @@ class Convolution:
         self.halo_xch_input.exchange(stream or self.be.stream)
 
     def backward_data_exchange_halo(self, d_output: Tensor, stream=None, skip_unpack=False):
-        self.halo_xch_d_output.exchange(stream or self.be.stream, skip_unpack=skip_unpack)
+        # d_output's halo cells at the tensor's boundary stand in for the padding
+        self.halo_xch_d_output.exchange(stream or self.be.stream, skip_unpack=skip_unpack, clear_boundary=True)
 
     # -- compute --
     def forward(self, alpha, input: Tensor, filter: torch.Tensor, beta, output: Tensor,
@@ -1139,21 +1172,22 @@ class Convolution:
         if not skip_halo_exchange:
             self.backward_data_exchange_halo(d_output, s)
         call("dcb_conv_bwd_data", self._plan_bwd, float(alpha), _ptr(filter.data_ptr()),
-             _ptr(d_output.get_buffer()), float(beta), _ptr(d_input.nd_ptr(self._x_lo)), _stream_ptr(s))
+             _ptr(d_output.get_buffer()), float(beta), _ptr(d_input.nd_ptr(self._dx_lo)), _stream_ptr(s))
         return 0
 
     def backward_filter(self, alpha, input: Tensor, d_output: Tensor, beta, d_filter: torch.Tensor, reduce=True,
                         skip_chanfilt_comm=False, dump_profile=False):
-        """convolution.hpp:878-1107: zero-clears d_output's halo first, then
-        all-reduces the filter gradient over all ranks."""
+        """convolution.hpp:878-1107, then the all-reduce of the filter gradient
+        over all ranks.  Only d_output's owned cells are read, so its halo is
+        not cleared first (the reference clears it because cuDNN is handed the
+        halo-extended tensor)."""
         s = self.be.stream
         if (input.get_local_size() == 0 or d_output.get_local_size() == 0 or d_filter.numel() == 0
                 or not input.is_split_root()):
             d_filter.zero_()
         else:
-            self._clear_halos(d_output, s)
-            call("dcb_conv_bwd_filter", self._plan_bwd, float(alpha), _ptr(input.nd_ptr(self._x_lo)),
-                 _ptr(d_output.get_buffer()), float(beta), _ptr(d_filter.data_ptr()), _stream_ptr(s))
+            call("dcb_conv_bwd_filter", self._plan_wgrad, float(alpha), _ptr(input.nd_ptr(self._x_lo)),
+                 _ptr(d_output.get_base_ptr()), float(beta), _ptr(d_filter.data_ptr()), _stream_ptr(s))
         if reduce:
             self.allreduce_gradients(d_filter)
         return 0

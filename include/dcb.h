@@ -58,10 +58,19 @@ int32_t dcb_version(void);
  * the buffer, Tensor::get_pitch() of a shard allocated with the reference's
  * CUDAPitchedAllocator (tensor/memory_cuda.hpp:68-104, tensor.hpp:184-192,
  * 483-485): 0 or real_shape[0] for a dense shard, larger when rows are padded.
- * A W-partitioned shard with halo 1 has 258-float rows; padded to 260 its
- * rows start on 16-byte boundaries, which the bulk-copy (TMA) fed tensor-core
- * kernels need.  The padding cells belong to nobody: kernels may copy them
- * along with a face but never interpret them.
+ * A W-partitioned shard with halo 1 has 258-float rows, which no bulk copy
+ * (TMA) can address: the pitch must be a multiple of 4 floats for the
+ * tensor-core kernels to take the shard.  The host mirrors lay such a shard out
+ * with a pitch of 264 and the buffer starting 3 floats above a 16-byte boundary,
+ * so that the OWNED cells of every row start on one: bulk stores into the
+ * interior (backward data) and 16-byte vector accesses (batch-norm) need that,
+ * while the kernels that read the halo-extended window fetch from the boundary
+ * below it and skip the cells in front (they are only read, and lie in the same
+ * allocation since allocations start 16-byte aligned).  Any base alignment of 4
+ * bytes is accepted; other layouts run on slower paths.  The padding cells
+ * between rows belong to nobody: kernels may copy them along with a face but
+ * never interpret them, and nothing is accessed beyond the last row's last real
+ * cell.
  * ------------------------------------------------------------------------ */
 typedef struct dcb_tensor_desc
 {

@@ -563,24 +563,33 @@ public:
     void allgather(const void* in, void* out, size_t n) const { std::memcpy(out, in, n); }
 };
 
-// Allocator tags (tensor/memory_cuda.hpp:28-104).  They decide the row pitch of
+// Allocator tags (tensor/memory_cuda.hpp:28-104).  They decide the row layout of
 // a shard.  CUDAAllocator keeps rows dense unless the shard carries halo cells
 // along W: such rows (local + 2 * overlap floats) are padded to 16 bytes, which
-// the bulk-copy fed tensor-core kernels need and costs at most three floats
-// per row.  CUDAPitchedAllocator pads the rows of every shard to 128 bytes, as
-// cudaMallocPitch-style allocation does in the reference.
+// the bulk-copy fed tensor-core kernels need, and the buffer starts `lead` floats
+// above a 16-byte boundary so that the OWNED cells of every row start on one
+// (bulk stores and vector accesses into a shard's interior need that; readers of
+// the halo-extended window fetch from the boundary below it).  At most six
+// floats per row.  CUDAPitchedAllocator pads the rows of every shard to 128
+// bytes, as cudaMallocPitch-style allocation does in the reference.
 struct CUDAAllocator
 {
-    static index_t pitch(index_t row, bool w_halo) { return w_halo ? (row + 3) / 4 * 4 : row; }
+    static index_t lead(index_t overlap) { return (4 - overlap % 4) % 4; }
+    static index_t pitch(index_t row, index_t overlap)
+    {
+        return overlap > 0 ? (lead(overlap) + row + 3) / 4 * 4 : row;
+    }
 };
 struct CUDAPitchedAllocator
 {
-    static index_t pitch(index_t row, bool) { return (row + 31) / 32 * 32; }
+    static index_t lead(index_t overlap) { return (4 - overlap % 4) % 4; }
+    static index_t pitch(index_t row, index_t overlap) { return (lead(overlap) + row + 31) / 32 * 32; }
 };
 // Host memory (tensor/memory.hpp:25-55); used by the host-side gather of dump_tensor.
 struct BaseAllocator
 {
-    static index_t pitch(index_t row, bool) { return row; }
+    static index_t lead(index_t) { return 0; }
+    static index_t pitch(index_t row, index_t) { return row; }
 };
 
 // Owned or aliased buffer with an allocator's deleter (tensor/memory.hpp:57-300):
@@ -592,19 +601,22 @@ class Memory
 public:
     using allocator_type = Allocator;
     Memory() = default;
-    int allocate(size_t bytes, size_t pitch_bytes = 0, size_t ldim_bytes = 0)
+    // lead_bytes: the buffer (get()) starts this far into the allocation, which is
+    // bytes + lead_bytes long, so that get() + bytes stays inside it
+    int allocate(size_t bytes, size_t pitch_bytes = 0, size_t ldim_bytes = 0, size_t lead_bytes = 0)
     {
         void* p = nullptr;
+        const size_t total = bytes + lead_bytes;
         if (std::is_same<Allocator, BaseAllocator>::value)
         {
-            p = std::malloc(bytes ? bytes : 16);
+            p = std::malloc(total ? total : 16);
             if (!p)
                 return -1;
             m_managed = std::shared_ptr<void>(p, [](void* q) { std::free(q); });
         }
         else
         {
-            if (cudaMalloc(&p, bytes ? bytes : 16) != cudaSuccess)
+            if (cudaMalloc(&p, total ? total : 16) != cudaSuccess)
                 return -1;
             m_managed = std::shared_ptr<void>(p, [](void* q) { cudaFree(q); });
         }
@@ -612,6 +624,7 @@ public:
         m_bytes = bytes;
         m_pitch = pitch_bytes;
         m_ldim = ldim_bytes;
+        m_lead = lead_bytes;
         return 0;
     }
     void alias(void* raw, size_t bytes, size_t pitch_bytes, size_t ldim_bytes)
@@ -621,6 +634,7 @@ public:
         m_bytes = bytes;
         m_pitch = pitch_bytes;
         m_ldim = ldim_bytes;
+        m_lead = 0;
     }
     void alias(const Memory& parent)
     {
@@ -629,6 +643,7 @@ public:
         m_bytes = parent.m_bytes;
         m_pitch = parent.m_pitch;
         m_ldim = parent.m_ldim;
+        m_lead = 0;
     }
     void nullify()
     {
@@ -636,7 +651,12 @@ public:
         m_alias = nullptr;
         m_bytes = 0;
     }
-    void* get() const { return m_alias ? m_alias : m_managed.get(); }
+    void* get() const
+    {
+        if (m_alias)
+            return m_alias;
+        return m_managed ? static_cast<char*>(m_managed.get()) + m_lead : nullptr;
+    }
     bool is_null() const { return get() == nullptr; }
     size_t get_size() const { return m_bytes; }
     size_t get_pitch() const { return m_pitch; }
@@ -645,10 +665,13 @@ public:
     {
         if (is_null())
             return;
+        // an owned allocation is cleared from its start (the lead cells too)
+        void* from = m_alias ? m_alias : m_managed.get();
+        const size_t n = m_alias ? m_bytes : m_bytes + m_lead;
         if (std::is_same<Allocator, BaseAllocator>::value)
-            std::memset(get(), v, m_bytes);
+            std::memset(from, v, n);
         else
-            cudaMemsetAsync(get(), v, m_bytes, stream);
+            cudaMemsetAsync(from, v, n, stream);
     }
     // dense host array <-> this buffer (rows of ldim bytes at pitch bytes)
     void copyin(const void* host)
@@ -673,7 +696,7 @@ public:
 private:
     std::shared_ptr<void> m_managed;
     void* m_alias = nullptr;
-    size_t m_bytes = 0, m_pitch = 0, m_ldim = 0;
+    size_t m_bytes = 0, m_pitch = 0, m_ldim = 0, m_lead = 0;
 };
 
 // Fixed-rank index / extent array with DistConv's negative indexing
@@ -786,7 +809,7 @@ public:
         m_offset = IndexVector(nd, 0);
         for (int d = 0; d < nd; ++d)
             m_offset[d] = get_dimension_rank_offset(d, (int) m_proc_idx[d]);
-        m_pitch = Allocator::pitch(m_local_shape[0] + 2 * m_dist.get_overlap(0), m_dist.get_overlap(0) > 0);
+        m_pitch = Allocator::pitch(m_local_shape[0] + 2 * m_dist.get_overlap(0), m_dist.get_overlap(0));
     }
 
     Shape local_of(const IndexVector& proc_idx) const
@@ -859,7 +882,8 @@ public:
     {
         const size_t bytes = (size_t) get_local_pitched_size() * sizeof(DataType);
         if (m_data.allocate(bytes, (size_t) m_pitch * sizeof(DataType),
-                            (size_t) get_local_real_shape()[0] * sizeof(DataType))
+                            (size_t) get_local_real_shape()[0] * sizeof(DataType),
+                            (size_t) Allocator::lead(m_dist.get_overlap(0)) * sizeof(DataType))
             != 0)
             return -1;
         m_data.memset(0);
@@ -1692,6 +1716,7 @@ public:
     {
         dcb_conv_plan_destroy(m_plan_fwd);
         dcb_conv_plan_destroy(m_plan_bwd);
+        dcb_conv_plan_destroy(m_plan_wgrad);
     }
 
     // convolution.hpp:119-290.  filter_shape is (fw, fh, [fd,] C, K);
@@ -1753,8 +1778,27 @@ public:
         m_has_bwd = d_output != nullptr;
         if (m_has_bwd)
         {
+            // Backward data: the reference hands cuDNN the halo-extended d_input,
+            // whose halo cells then receive partial sums nobody reads.  Where a
+            // partitioned dimension has unit stride and dilation only the OWNED
+            // cells are computed here: they start on a 16-byte boundary of a padded
+            // row (the halo cells do not), which the bulk stores of the tensor-core
+            // kernels need.  In the descriptor's terms the padding grows by
+            // d_output's halo width.
             m_dyd = d_output->full_nd_desc();
-            m_dxd = (d_input ? *d_input : input).nd_desc(m_halo_bwd_recv, m_halo_fwd_recv);
+            tensor::IntVector dlo = m_halo_bwd_recv, dhi = m_halo_fwd_recv;
+            for (int i = 0; i < nsd; ++i)
+                if (input.get_overlap()[i] > 0 && strides[i] == 1 && dilations[i] == 1)
+                {
+                    dlo[i] = dhi[i] = 0;
+                    m_pads_bp[i] = stencil[i] + (int) d_output->get_overlap()[i];
+                }
+            m_dx_lo = dlo;
+            m_dxd = (d_input ? *d_input : input).nd_desc(dlo, dhi);
+            // Backward filter: the forward geometry with d_output's owned cells in the
+            // output's place (the reference passes the halo-extended d_output with its
+            // halo cleared; the owned cells alone give the same sums and need no clearing).
+            m_dyod = d_output->nd_desc();
         }
         m_num_samples = (int) m_xd.n;
         make_plans();
@@ -1772,7 +1816,9 @@ public:
         m_num_samples = n;
         m_xd.n = m_yd.n = n;
         if (m_has_bwd)
-            m_dxd.n = m_dyd.n = n;
+            m_dxd.n = m_dyd.n = m_dyod.n = n;
+        dcb_conv_plan_destroy(m_plan_wgrad);
+        m_plan_wgrad = nullptr;
         dcb_conv_plan_destroy(m_plan_fwd);
         dcb_conv_plan_destroy(m_plan_bwd);
         m_plan_fwd = m_plan_bwd = nullptr;
@@ -1825,17 +1871,19 @@ public:
 
     int kernel_kind(int which) const
     {
-        return dcb_conv_plan_kernel_kind(which == 0 ? m_plan_fwd : m_plan_bwd, which);
+        return dcb_conv_plan_kernel_kind(which == 0 ? m_plan_fwd : (which == 1 ? m_plan_bwd : m_plan_wgrad), which);
     }
     // 0 fp32 CUDA-core, 1 / 2 tcgen05 row kernel, 3 sweep, 4 multi-group sweep, 5 tcgen05 backward filter
     int kernel_variant(int which) const
     {
-        return dcb_conv_plan_kernel_variant(which == 0 ? m_plan_fwd : m_plan_bwd, which);
+        return dcb_conv_plan_kernel_variant(which == 0 ? m_plan_fwd : (which == 1 ? m_plan_bwd : m_plan_wgrad),
+                                            which);
     }
     tensor::HaloExchange<>& input_halo_exchange() { return *m_halo_xch_input; }
     tensor::HaloExchange<>& d_output_halo_exchange() { return *m_halo_xch_d_output; }
     void forward_exchange_halo(TensorF&) { m_halo_xch_input->exchange(m_be.get_stream()); }
-    void backward_data_exchange_halo(TensorF&) { m_halo_xch_d_output->exchange(m_be.get_stream()); }
+    // d_output's halo cells at the tensor's boundary stand in for the padding: cleared by the same launches
+    void backward_data_exchange_halo(TensorF&) { m_halo_xch_d_output->clear_and_exchange(m_be.get_stream()); }
 
     // convolution.hpp:342-639, the branch without interior/boundary overlap
     int forward(float alpha, TensorF& input, const float* filter, float beta, TensorF& output,
@@ -1895,12 +1943,12 @@ public:
             backward_data_exchange_halo(d_output);
         }
         util::check(dcb_conv_bwd_data(m_plan_bwd, alpha, filter, d_output.get_buffer(), beta,
-                                      d_input.nd_ptr(m_x_lo), m_be.get_stream()),
+                                      d_input.nd_ptr(m_dx_lo), m_be.get_stream()),
                     "conv backward data");
         return 0;
     }
-    // convolution.hpp:878-1107: clears d_output's halo, then all-reduces the
-    // filter gradient over every rank.
+    // convolution.hpp:878-1107, then the all-reduce of the filter gradient over every
+    // rank.  Only d_output's owned cells are read, so its halo is not cleared first.
     int backward_filter(float alpha, TensorF& input, TensorF& d_output, float beta, float* d_filter,
                         bool reduce = true)
     {
@@ -1912,8 +1960,7 @@ public:
             cudaMemsetAsync(d_filter, 0, (size_t) count * sizeof(float), m_be.get_stream());
         else
         {
-            clear_halos(d_output);
-            util::check(dcb_conv_bwd_filter(m_plan_bwd, alpha, input.nd_ptr(m_x_lo), d_output.get_buffer(), beta,
+            util::check(dcb_conv_bwd_filter(m_plan_wgrad, alpha, input.nd_ptr(m_x_lo), d_output.get_base_ptr(), beta,
                                             d_filter, m_be.get_stream()),
                         "conv backward filter");
         }
@@ -1983,7 +2030,10 @@ private:
     {
         m_plan_fwd = make_plan(m_xd, m_yd, m_pads_fp);
         if (m_has_bwd)
+        {
             m_plan_bwd = make_plan(m_dxd, m_dyd, m_pads_bp);
+            m_plan_wgrad = make_plan(m_xd, m_dyod, m_pads_fp);
+        }
     }
     dcb_conv_plan* make_plan(const dcb_nd_desc& xd, const dcb_nd_desc& yd, const tensor::IntVector& pads)
     {
@@ -2024,13 +2074,14 @@ private:
     bool m_enable_overlap = false, m_enable_profiling = false;
     bool m_empty = true, m_has_bwd = false;
     int m_num_samples = 0;
-    dcb_nd_desc m_xd{}, m_yd{}, m_dxd{}, m_dyd{};
+    dcb_nd_desc m_xd{}, m_yd{}, m_dxd{}, m_dyd{}, m_dyod{};
     tensor::IntVector m_pads_fp, m_pads_bp;
-    tensor::IntVector m_filter_dims, m_strides, m_dilations, m_x_lo;
+    tensor::IntVector m_filter_dims, m_strides, m_dilations, m_x_lo, m_dx_lo;
     tensor::IntVector m_halo_fwd_send, m_halo_bwd_send, m_halo_fwd_recv, m_halo_bwd_recv;
     std::unique_ptr<tensor::HaloExchange<>> m_halo_xch_input, m_halo_xch_d_output;
     dcb_conv_plan* m_plan_fwd = nullptr;
     dcb_conv_plan* m_plan_bwd = nullptr;
+    dcb_conv_plan* m_plan_wgrad = nullptr;
 };
 
 // BatchNormalization<BackendDNNLib, float> (batchnorm.hpp:100-581).  The

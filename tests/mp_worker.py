@@ -129,6 +129,7 @@ def main():
         assert be.allreducer.status() == _abi.OK
         assert _abi.lib().dcb_conv_plan_status(conv._plan_fwd, None) == _abi.OK
         assert _abi.lib().dcb_conv_plan_status(conv._plan_bwd, None) == _abi.OK
+        assert _abi.lib().dcb_conv_plan_status(conv._plan_wgrad, None) == _abi.OK
         # the halo-extended input shard, bit for bit (edges and corners included)
         sh = O.Shard(shape, locale, list(x.dist.overlap), r)
         assert np.array_equal(x.buffer.cpu().numpy(), O.fill_by_definition(sh, gx)), what + ": halo contents"

@@ -22,6 +22,9 @@ CASES = [
     ([34, 9, 6, 2], [1, 2, 1, 1], [0, 2, 0, 0]),
     ([130, 129, 3, 1], [1, 1, 1, 1], [0, 0, 0, 0]),
     ([64, 64, 64, 16, 1], [1, 1, 1, 1, 1], [0, 0, 0, 0, 0]),
+    # W halo: padded rows, a unit of the kernels packs several rows (16 + 16 + 5 of a plane's 37)
+    ([512, 37, 3, 4, 1], [2, 1, 1, 1, 1], [1, 0, 0, 0, 0]),
+    ([32, 50, 3, 2, 1], [2, 1, 1, 1, 1], [1, 0, 0, 0, 0]),
 ]
 
 

@@ -390,6 +390,65 @@ def test_rows_padded_to_a_pitch_with_odd_extents(W, pad):
             assert bool(torch.isnan(st[..., ext:]).all()), "a store went past the end of a row"
 
 
+@pytest.mark.parametrize("lead", [1, 2, 3])
+@pytest.mark.parametrize("Wl", [32, 64, 35])
+def test_window_that_starts_above_a_16_byte_boundary(lead, Wl):
+    """The layout of a shard with halo cells along W: rows padded to a pitch,
+    the OWNED cells of a row on a 16-byte boundary, so the halo-extended window
+    starts `lead` floats above one (3 with one halo cell).  Forward and backward filter read such a
+    window (no padding along W: the halo stands in for it) and write / read the
+    owned cells; backward data reads the halo-extended dy and writes dx's owned
+    cells (padding f - 1 in the descriptor's terms).  The tensor-core kernels
+    must take all three (the bulk copies fetch from the boundary below the
+    window and skip the cells in front), meet the 1e-5 contract and leave the
+    lead and tail cells of every row alone."""
+    rng = np.random.default_rng(100 * lead + Wl)
+    N, C, K, D, H = 1, 4, 16, 5, 9
+    We = Wl + 2
+
+    def shard(a, off):
+        pitch = -(-(off + a.shape[-1]) // 4) * 4
+        st = torch.full(a.shape[:-1] + (pitch,), float("nan"), device="cuda")
+        v = st[..., off:off + a.shape[-1]]
+        v.copy_(torch.from_numpy(a))
+        return st, v
+
+    w = rng.normal(0, 0.2, (K, C, 3, 3, 3)).astype(np.float32)
+    wt = torch.from_numpy(w).cuda()
+    # forward and backward filter: x window of Wl + 2 cells `lead` floats into the row, y / dy
+    # the Wl owned cells on a boundary
+    x = rng.normal(size=(N, C, D, H, We)).astype(np.float32)
+    dy = rng.normal(size=(N, K, D, H, Wl)).astype(np.float32)
+    xs, xv = shard(x, lead)
+    ys, yv = shard(np.zeros(dy.shape, np.float32), 4)
+    dys, dyv = shard(dy, 4)
+    assert xv.data_ptr() % 16 == 4 * lead and yv.data_ptr() % 16 == 0
+    dw = torch.zeros_like(wt)
+    pads = [1, 1, 0]
+    p = Plan(xv, wt, yv, pads, [1] * 3, [1] * 3, _abi.MATH_FP32)
+    assert _abi.lib().dcb_conv_plan_kernel_variant(p.p, 0) == 3
+    p.fwd(1.0, xv, wt, 0.0, yv)
+    p.bwd_filter(1.0, xv, dyv, 0.0, dw)
+    torch.cuda.synchronize()
+    assert _abi.lib().dcb_conv_plan_status(p.p, None) == _abi.OK
+    emu.assert_close(yv.cpu().numpy(), O.conv_fwd(x, w, pads, [1] * 3), TOL, "y")
+    emu.assert_close(dw.cpu().numpy(), O.conv_bwd_filter(x, dy, (3, 3, 3), pads, [1] * 3), TOL, "dw")
+    assert bool(torch.isnan(ys[..., :4]).all()) and bool(torch.isnan(ys[..., 4 + Wl:]).all())
+    # backward data: dy window with its halo, dx the owned cells
+    dye = rng.normal(size=(N, K, D, H, We)).astype(np.float32)
+    des, dev = shard(dye, lead)
+    dxs, dxv = shard(np.zeros((N, C, D, H, Wl), np.float32), 4)
+    pads_b = [1, 1, 2]
+    pb = Plan(dxv, wt, dev, pads_b, [1] * 3, [1] * 3, _abi.MATH_FP32)
+    pb.bwd_data(1.0, wt, dev, 0.0, dxv)
+    torch.cuda.synchronize()
+    assert _abi.lib().dcb_conv_plan_status(pb.p, None) == _abi.OK
+    dx_ref = np.zeros((N, C, D, H, Wl), np.float32)
+    O.conv_bwd_data(w, dye, dx_ref, pads_b, [1] * 3)
+    emu.assert_close(dxv.cpu().numpy(), dx_ref, TOL, "dx")
+    assert bool(torch.isnan(dxs[..., :4]).all()) and bool(torch.isnan(dxs[..., 4 + Wl:]).all())
+
+
 def test_backward_data_full_shard_16_channels_against_fp64():
     """Backward data of the benchmark layer on its 256^3 shard: dy has 16
     channels, which the multi-group sweep kernel walks as four groups inside one

@@ -155,17 +155,25 @@ def test_clear_halo(shape, overlap):
     assert np.array_equal(t.buffer.cpu().numpy(), ref)
 
 
+@pytest.mark.parametrize("pitched", [False, True])
 @pytest.mark.parametrize("width", [1, 2, 3])
 @pytest.mark.parametrize("dim", [0, 1, 2])
-def test_pack_unpack_slab(dim, width):
+def test_pack_unpack_slab(dim, width, pitched):
     """TraverseHalo + PackFunctor (halo_packing_cuda.hpp:85-167) for every
-    side, inner/outer, widths up to the overlap."""
+    side, inner/outer, widths up to the overlap.  Dense rows: the packed
+    buffer is the slab in memory order.  Padded rows (the default layout of a
+    shard with a W halo: 12 cells one float into a pitch of 16): H and D slabs
+    carry the padding between their rows, so the packed buffer is checked by
+    unpacking it into a second shard."""
     shape, locale, overlap = [12, 10, 14, 2, 1], [2, 2, 2, 1, 1], [3, 3, 3, 0, 0]
-    t = make_ranks(shape, locale, overlap)[0]
+    dist = dc.Distribution.make_overlapped_distribution(locale, overlap)
+    t, t2 = (dc.Tensor(shape, emu.locales(8)[0], dist, pitch_align=None if pitched else 1) for _ in range(2))
+    assert (t.get_pitch(), t.lead) == ((16, 1) if pitched else (12, 0))
     real = t.get_local_real_shape()
     rng = np.random.default_rng(dim * 10 + width)
     src = rng.normal(size=tuple(reversed(real))).astype(np.float32)
     emu.upload(t, src)
+    t2.allocate()
     d = t.desc()
     nd, ov, n = 5, 3, real[dim]
     for side in (0, 1):
@@ -177,10 +185,17 @@ def test_pack_unpack_slab(dim, width):
             sl = [slice(None)] * nd
             sl[nd - 1 - dim] = slice(start, start + width)
             sl = tuple(sl)
-            packed = torch.empty(src[sl].size, dtype=torch.float32, device="cuda")
+            packed = torch.zeros(t._storage[sl].numel(), dtype=torch.float32, device="cuda")
             _abi.call("dcb_halo_pack", ctypes.byref(d), ctypes.c_void_p(t.get_buffer()), dim, side, width, inner,
                       ctypes.c_void_p(packed.data_ptr()), None)
-            assert np.array_equal(packed.cpu().numpy(), src[sl].ravel())
+            if not pitched:
+                assert np.array_equal(packed.cpu().numpy(), src[sl].ravel())
+            t2._storage.zero_()
+            _abi.call("dcb_halo_unpack_slab", ctypes.byref(d), ctypes.c_void_p(t2.get_buffer()), dim, side, width,
+                      inner, ctypes.c_void_p(packed.data_ptr()), _abi.HALO_OPS["ID"], None)
+            ref = np.zeros_like(src)
+            ref[sl] = src[sl]
+            assert np.array_equal(t2.buffer.cpu().numpy(), ref)
             # unpack with SUM doubles the slab
             _abi.call("dcb_halo_unpack_slab", ctypes.byref(d), ctypes.c_void_p(t.get_buffer()), dim, side, width,
                       inner, ctypes.c_void_p(packed.data_ptr()), _abi.HALO_OPS["SUM"], None)

@@ -93,12 +93,18 @@ class Layer:
             bn.backward_stage2(y, dz, st[:K], st[K:], self.scale, a[:K], a[K:], dy)
         self.dscale, self.dbias = gb[0][:K], gb[0][K:]
         self.dmean, self.dvar = ga[0][:K], ga[0][K:]
-        # backward filter first (it zero-clears dy's halo), then exchange, then
-        # backward data -- the driver's order (distconv_benchmark.cpp:569-589)
+        # backward filter first (it reads dy's owned cells only: the halo is still
+        # poisoned here), then exchange, then backward data -- the driver's order
+        # (distconv_benchmark.cpp:569-589)
         self.dw = [torch.zeros_like(self.w) for _ in self.bes]
         for c, x, dy, dw in zip(self.convs, self.x, self.dy, self.dw):
             c.backward_filter(1.0, x, dy, 0.0, dw, reduce=False)
         emu.allreduce_all(self.bes, self.dw)
+        # the halo cells at the tensor's boundary stand in for the padding (the
+        # exchange of Convolution.backward_data clears them in its pack launches)
+        for dy in self.dy:
+            for d in range(self.nd - 2):
+                dy.clear_halo(d)
         emu.exchange_all([c.halo_xch_d_output for c in self.convs])
         for c, dy, dx in zip(self.convs, self.dy, self.dx):
             c.backward_data(1.0, self.w, dy, 0.0, dx, skip_halo_exchange=True)
@@ -182,8 +188,8 @@ def test_w_partitioned_shards_of_the_2x2x2_grid_take_the_tensor_core_kernels():
     bias = rng.normal(0, 0.5, K).astype(np.float32)
     L = Layer(shape, locale, K, f, strides, pad=1)
     for x, dy in zip(L.x, L.dy):
-        assert x.get_local_real_shape()[0] == 134 and x.get_pitch() == 136
-        assert dy.get_pitch() == 136
+        assert x.get_local_real_shape()[0] == 134 and x.get_pitch() == 140
+        assert dy.get_pitch() == 140 and x.owned().data_ptr() % 16 == 0
     for c in L.convs:
         assert [c.kernel_kind(i) for i in range(3)] == [1, 1, 1]
         assert c.kernel_variant(0) == 3 and c.kernel_variant(1) in (3, 4) and c.kernel_variant(2) == 5
@@ -194,6 +200,7 @@ def test_w_partitioned_shards_of_the_2x2x2_grid_take_the_tensor_core_kernels():
     for c in L.convs:
         assert _abi.lib().dcb_conv_plan_status(c._plan_fwd, None) == _abi.OK
         assert _abi.lib().dcb_conv_plan_status(c._plan_bwd, None) == _abi.OK
+        assert _abi.lib().dcb_conv_plan_status(c._plan_wgrad, None) == _abi.OK
     check_layer_stages(L, gx, w, scale, bias, gdz, [1, 1, 1], [1, 1, 1])
 
 

@@ -114,12 +114,14 @@ g = bench.layer_geometry(bench.grid_for(2, "auto"), loc, extent=16)
 assert g["shape"][2] == 32 and g["input"].get_local_shape()[2] == 16
 # a W-partitioned shard pads its rows to 16 bytes (the pitch), others stay dense
 tw = dc.create_input_tensor([36, 8, 4, 2], [2, 1, 1, 1], [3, 3], [1, 1], [1, 1], loc)
-assert tw.get_local_real_shape()[0] == 20 and tw.get_pitch() == 20
+# the owned cells start on a 16-byte boundary: 3 floats of lead, then the halo cell
+assert tw.get_local_real_shape()[0] == 20 and tw.lead == 3 and tw.get_pitch() == 24
 tw = dc.create_input_tensor([34, 8, 4, 2], [2, 1, 1, 1], [3, 3], [1, 1], [1, 1], loc)
-assert tw.get_local_real_shape()[0] == 19 and tw.get_pitch() == 20 and tw.get_strides() == [1, 20, 160, 640]
-assert tw.get_local_pitched_shape() == [20, 8, 4, 2] and tw.desc().pitch == 20
+assert tw.get_local_real_shape()[0] == 19 and tw.get_pitch() == 24 and tw.get_strides() == [1, 24, 192, 768]
+assert tw.get_local_pitched_shape() == [24, 8, 4, 2] and tw.desc().pitch == 24
 tw.allocate(device="cpu")
-assert tuple(tw.buffer.shape) == (2, 4, 8, 19) and tw.buffer.stride() == (640, 160, 20, 1)
+assert tuple(tw.buffer.shape) == (2, 4, 8, 19) and tw.buffer.stride() == (768, 192, 24, 1)
+assert tw.owned().data_ptr() % 16 == 0 and tw.get_buffer() % 16 == 12
 assert t.get_pitch() == 64 and g["input"].get_pitch() == 16
 # dump_tensor: rank 0 writes the global tensor, no halos, dimension 0 fastest
 import numpy as np
