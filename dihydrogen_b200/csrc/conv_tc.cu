@@ -957,7 +957,7 @@ static int32_t sw_launch(const SwGeom& g_in, float alpha, const float* w, const 
 #endif
     if (stats)
     {
-        sw_stats_fold_kernel<<<1, 32, 0, stream>>>(stat_part, (int) grid * epi, g.k, sums, sqsums);
+        sw_stats_fold_kernel<<<1, SW_FOLD_WARPS * 32, 0, stream>>>(stat_part, (int) grid * epi, g.k, sums, sqsums);
         DCB_LAUNCH_CHECK();
     }
     (void) x;

@@ -228,15 +228,28 @@ __device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c)
     return r;
 }
 
-// Adds the epilogue warps' partial sums in index order, in fp64: thread k gives
-// sums[k], thread 16 + k gives sqsums[k].
-__global__ void sw_stats_fold_kernel(const float* __restrict__ part, int nparts, int nk, float* __restrict__ sums,
-                                     float* __restrict__ sqsums)
+// Adds the epilogue warps' partial sums in fp64 and in a fixed order: warp w of
+// the block adds partials w, w + 32, ... (a serial walk by one warp is a chain of
+// ~1800 dependent L2 loads, 70 us), thread (0, k) then adds the 32 warps' sums in
+// warp order and gives sums[k], thread (0, 16 + k) gives sqsums[k].
+constexpr int SW_FOLD_WARPS = 32;
+__global__ void __launch_bounds__(SW_FOLD_WARPS * 32)
+    sw_stats_fold_kernel(const float* __restrict__ part, int nparts, int nk, float* __restrict__ sums,
+                         float* __restrict__ sqsums)
 {
-    const int t = threadIdx.x;
+    __shared__ double sm[SW_FOLD_WARPS][32];
+    const int t = threadIdx.x & 31, w = threadIdx.x >> 5;
     double acc = 0.0;
-    for (int i = 0; i < nparts; ++i)
+    for (int i = w; i < nparts; i += SW_FOLD_WARPS)
         acc += (double) part[(size_t) i * 32 + t];
+    sm[w][t] = acc;
+    __syncthreads();
+    if (w != 0)
+        return;
+    acc = 0.0;
+#pragma unroll
+    for (int i = 0; i < SW_FOLD_WARPS; ++i)
+        acc += sm[i][t];
     if (t < SW_NBK)
     {
         if (t < nk)
