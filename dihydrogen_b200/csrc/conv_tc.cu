@@ -1191,6 +1191,11 @@ int32_t tc_conv_bwd_filter(TcPlan* p, float alpha, const float* x, const float* 
         || !skip_ok(skip, g.pad[2], g.f[2], WG_TW, WG_XW))
         return DCB_UNSUPPORTED; // the caller falls back to the CUDA-core kernel
     tc_row_window(g, skip);
+#if DCB_WG_KNOCKOUT
+    g.dbg = std::getenv("DCB_WG_DBG") ? std::atoi(std::getenv("DCB_WG_DBG")) : 0;
+#else
+    g.dbg = 0;
+#endif
     size_t smem = wg_smem_need(g);
     smem = smem < 120 * 1024 ? 120 * 1024 : smem; // one CTA per SM
     long long grid = (long long) num_sms();

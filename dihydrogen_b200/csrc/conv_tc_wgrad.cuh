@@ -39,18 +39,30 @@ namespace dcb
 namespace
 {
 
-constexpr int WG_THREADS = 20 * 32; // 12 converters, 3 issuers, 1 copy, 4 dump warps
+// A group's chunks go round its WG_SPG slots, and each slot has an issuer warp of its
+// own: issuing a tcgen05.mma (or a commit) occupies its thread for ~160 clocks whatever
+// the instruction's size, a chunk is four instructions and a commit, and with one issuer
+// per group that alone was over 1 ms of the kernel's 1.39 ms on the 256^3 shard.
+#ifndef DCB_WG_SPG
+#define DCB_WG_SPG 2
+#endif
+#ifndef DCB_WG_KS
+#define DCB_WG_KS 2
+#endif
+constexpr int WG_SPG = DCB_WG_SPG;         // slots, and issuers, per converter group
+constexpr int WG_ISSUER2_WARP = 20;        // issuers of the slots after a group's first: warps 20 ..
+constexpr int WG_THREADS = (20 + 3 * (WG_SPG - 1)) * 32; // 12 converters, 3 issuers, 1 copy, 4 dump warps, more issuers
 constexpr int WG_COPY_WARP = 15;
 constexpr int WG_DUMP_WARP = 16;
 constexpr int WG_TW = 128;                 // outputs per unit
-constexpr int WG_KS = 2;                   // k-steps (of eight outputs) per chunk: one hand-off per chunk
+constexpr int WG_KS = DCB_WG_KS;           // k-steps (of eight outputs) per chunk: one hand-off per chunk
 constexpr int WG_CHUNKS = WG_TW / (8 * WG_KS); // chunks per unit
 constexpr int WG_XW = WG_TW + 12;          // staged input row: 4 cells of margin left, 8 right; the 140-float
                                            // pitch keeps the taps of a warp's 32 lanes (about 11 rows x 3
                                            // columns) on different banks, 136 would fold them three deep
-constexpr int WG_A_SLOTS = 6;              // two per group
+constexpr int WG_A_SLOTS = 3 * WG_SPG;     // slot s belongs to group s % 3
 constexpr int WG_A_COLS = 16 * WG_KS;      // an A slot: per k-step 8 hi + 8 lo columns
-constexpr uint32_t WG_TMEM_COLS = 256;     // two accumulator buffers of 32 columns + 6 A slots
+constexpr uint32_t WG_TMEM_COLS = 64 + WG_A_SLOTS * 16 * 2 <= 256 ? 256 : 512; // two accumulator buffers of 32 columns + the A slots
 constexpr int WG_ACC_COLS = 64;            // the A ring starts here
 // The tensor pipe adds into an fp32 accumulator without rounding to nearest: over
 // a chain of n updates the error grows like n^1.5 * 2^-24 and does not average
@@ -61,11 +73,22 @@ constexpr int WG_ACC_COLS = 64;            // the A ring starts here
 constexpr int WG_FLUSH_UNITS = 8;
 constexpr int WG_B_FLOATS = 256 * WG_KS;   // the B tiles of a chunk: per k-step 8 x 32 floats
 
+#ifndef DCB_WG_KNOCKOUT
+#define DCB_WG_KNOCKOUT 0
+#endif
+#if DCB_WG_KNOCKOUT
+#define WG_DBG(bit) ((g.dbg >> (bit)) & 1)
+#else
+#define WG_DBG(bit) 0
+#endif
+
 struct WgGeom
 {
     int n, c, k;
     int in[3], out[3], f[3], pad[3];
     int lx, rx;             // as in TcGeom, for the staged input rows of a unit
+    int dbg;                // timing knock-outs (builds with DCB_WG_KNOCKOUT only): bit 0 no tap loads,
+                            // 1 no tensor-memory stores, 2 no B tile, 3 no MMAs, 4 no input copies
     int mrows;              // c * fd * fh * fw
     int tiles_w;
     long long units;        // n * out_d * out_h * tiles_w
@@ -82,7 +105,7 @@ struct WgGeom
 };
 
 // dw[k_off + kk][c_off + c][tap] (of a [k_total][c_total][taps] filter tensor) from the
-// per-CTA partials of one launch; m = c * taps + tap.
+// per-CTA partials of one launch; m = tap * c + c_index (c = channels of the launch).
 __global__ void wg_fold_kernel(const float* __restrict__ part, int nparts, int mrows, int k, int taps, int c_total,
                                int c_off, int k_off, float alpha, float beta, float* dw)
 {
@@ -93,7 +116,8 @@ __global__ void wg_fold_kernel(const float* __restrict__ part, int nparts, int m
     double s = 0.0;
     for (int p = 0; p < nparts; ++p)
         s += (double) part[((size_t) p * 128 + m) * 16 + kk];
-    float* o = dw + ((size_t) (k_off + kk) * c_total + c_off) * taps + m;
+    const int cl = mrows / taps; // channels of this launch
+    float* o = dw + ((size_t) (k_off + kk) * c_total + c_off + m % cl) * taps + m / cl;
     const float prev = beta != 0.f ? *o : 0.f;
     *o = alpha * (float) s + beta * prev;
 }
@@ -133,7 +157,7 @@ __global__ void __launch_bounds__(WG_THREADS, 1)
         }
         for (int b = 0; b < 2; ++b)
         {
-            mbar_init(&d_full[b], 3);
+            mbar_init(&d_full[b], 3 * WG_SPG);
             mbar_init(&d_empty[b], 4);
         }
         *abort_flag = 0;
@@ -166,12 +190,16 @@ __global__ void __launch_bounds__(WG_THREADS, 1)
         int src = -1;
         if (m < g.mrows)
         {
-            const int kw = m % g.f[2];
-            int r = m / g.f[2];
+            // row m of the partial filter is (tap, channel), channel fastest: with the
+            // channel slowest the lanes of a warp read three filter planes at the same
+            // bank offsets (a plane's rows start on a 128-byte boundary), three deep;
+            // this order is two deep at worst (4 channels x 3 x 3 x 3, 140-float rows)
+            const int c = m % g.c;
+            int r = m / g.c;
+            const int kw = r % g.f[2];
+            r /= g.f[2];
             const int kh = r % g.f[1];
-            r /= g.f[1];
-            const int kd = r % g.f[0];
-            const int c = r / g.f[0];
+            const int kd = r / g.f[1];
             src = kd * g.xplane_floats + (c * g.f[1] + kh) * WG_XW + g.rx + kw;
         }
         // this lane's element of the B tile: filter quad*4 + lane/8, output lane%8
@@ -198,7 +226,7 @@ __global__ void __launch_bounds__(WG_THREADS, 1)
 #pragma unroll
                 for (int ks = 0; ks < WG_KS; ++ks)
                 {
-                    if (src >= 0)
+                    if (src >= 0 && !WG_DBG(0))
                     {
                         // output (q * WG_KS + ks) * 8 of the unit; with SW == 2 the second
                         // 64 outputs read the second half window
@@ -220,7 +248,7 @@ __global__ void __launch_bounds__(WG_THREADS, 1)
                         for (int e = 0; e < 8; ++e)
                             hi[ks][e] = lo[ks][e] = 0u;
                     }
-                    const float dv = dyb[bk * WG_TW + (q * WG_KS + ks) * 8 + bkk];
+                    const float dv = WG_DBG(2) ? 0.f : dyb[bk * WG_TW + (q * WG_KS + ks) * 8 + bkk];
                     dhi[ks] = tf32_rna(dv);
                     dlo[ks] = tf32_rna(dv - __uint_as_float(dhi[ks]));
                 }
@@ -234,10 +262,16 @@ __global__ void __launch_bounds__(WG_THREADS, 1)
 #pragma unroll
                 for (int ks = 0; ks < WG_KS; ++ks)
                 {
-                    tmem_st8(a_addr + (uint32_t) (ks * 16), hi[ks]);
-                    tmem_st8(a_addr + (uint32_t) (ks * 16 + 8), lo[ks]);
-                    bt[ks * 256 + b_off] = __uint_as_float(dhi[ks]);
-                    bt[ks * 256 + b_off + 64] = __uint_as_float(dlo[ks]);
+                    if (!WG_DBG(1))
+                    {
+                        tmem_st8(a_addr + (uint32_t) (ks * 16), hi[ks]);
+                        tmem_st8(a_addr + (uint32_t) (ks * 16 + 8), lo[ks]);
+                    }
+                    if (!WG_DBG(2))
+                    {
+                        bt[ks * 256 + b_off] = __uint_as_float(dhi[ks]);
+                        bt[ks * 256 + b_off + 64] = __uint_as_float(dlo[ks]);
+                    }
                 }
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -245,7 +279,7 @@ __global__ void __launch_bounds__(WG_THREADS, 1)
                 __syncwarp();
                 if (lane == 0)
                     mbar_arrive(&a_full[slot]);
-                if (++lap == 2)
+                if (++lap == WG_SPG)
                 {
                     lap = 0;
                     a_phase ^= 1;
@@ -263,7 +297,7 @@ __global__ void __launch_bounds__(WG_THREADS, 1)
         // ------------------------------------------------------------------
         // bulk tensor copies, one unit ahead
         // ------------------------------------------------------------------
-        const uint32_t bytes = (uint32_t) (g.f[0] * SW * g.xplane_bytes + g.dybuf_bytes);
+        const uint32_t bytes = (uint32_t) ((WG_DBG(4) ? 0 : g.f[0] * SW * g.xplane_bytes) + g.dybuf_bytes);
         uint32_t ul = 0;
         for (uint32_t u = blockIdx.x; u < nunits && ok; u += gridDim.x, ++ul)
         {
@@ -284,7 +318,7 @@ __global__ void __launch_bounds__(WG_THREADS, 1)
                 uint8_t* dst = ubuf + (size_t) b * unit_bytes;
                 mbar_expect_tx(&u_full[b], bytes);
                 // the window starts at a multiple of 4 floats at or left of the first tap
-                for (int kd = 0; kd < g.f[0]; ++kd)
+                for (int kd = 0; kd < g.f[0] && !WG_DBG(4); ++kd)
 #pragma unroll
                     for (int h = 0; h < SW; ++h)
                         tma_load_5d(dst + ((size_t) kd * g.xplane_floats + (size_t) h * g.xhalf_floats) * 4, &xmap,
@@ -295,12 +329,14 @@ __global__ void __launch_bounds__(WG_THREADS, 1)
             __syncwarp();
         }
     }
-    else if (warp >= TC_MMA_WARP && warp < TC_MMA_WARP + 3)
+    else if ((warp >= TC_MMA_WARP && warp < TC_MMA_WARP + 3) || warp >= WG_ISSUER2_WARP)
     {
         // ------------------------------------------------------------------
-        // MMA issue
+        // MMA issue: issuer (mq, mh) serves slot mq + 3 * mh, i.e. every
+        // WG_SPG-th chunk of group mq
         // ------------------------------------------------------------------
-        const int mq = warp - TC_MMA_WARP;
+        const int mq = warp < WG_ISSUER2_WARP ? warp - TC_MMA_WARP : (warp - WG_ISSUER2_WARP) % 3;
+        const int mh = warp < WG_ISSUER2_WARP ? 0 : 1 + (warp - WG_ISSUER2_WARP) / 3;
         // fp32 accumulate, tf32 x tf32, A K-major (tensor memory), B K-major, M = 128
         const uint32_t idesc32 = (1u << 4) | (2u << 7) | (2u << 10) | ((128u >> 4) << 24) | ((32u >> 3) << 17);
         const uint32_t idesc16 = (1u << 4) | (2u << 7) | (2u << 10) | ((128u >> 4) << 24) | ((16u >> 3) << 17);
@@ -325,18 +361,19 @@ __global__ void __launch_bounds__(WG_THREADS, 1)
             for (; q < WG_CHUNKS && ok; q += 3)
             {
                 const int slot = mq + 3 * lap;
-                ok = mbar_wait_t<0>(&a_full[slot], full_phase, abort_flag);
+                if (lap == mh)
+                    ok = mbar_wait_t<0>(&a_full[slot], full_phase, abort_flag);
                 if (!ok)
                     break;
                 tc_fence_after();
-                if (lane == 0)
+                if (lane == 0 && lap == mh)
                 {
                     const uint32_t a_addr = tmem_base + (uint32_t) WG_ACC_COLS + (uint32_t) (slot * WG_A_COLS);
                     // B tile of a k-step: [2 k-chunks][4 filter groups][8][4]: 512 bytes
                     // between the k-chunks, 128 between the filter groups, 1 KiB per tile
                     const uint64_t bd = make_desc(smem_u32(bring + slot * WG_B_FLOATS), 512u, 128u, 0u);
 #pragma unroll
-                    for (int ks = 0; ks < WG_KS; ++ks)
+                    for (int ks = 0; ks < WG_KS && !WG_DBG(3); ++ks)
                     {
                         mma_tf32_ts(d_addr, a_addr + (uint32_t) (ks * 16), bd + (uint64_t) (ks * 64),
                                     idesc32); // A_hi x [B_hi | B_lo]
@@ -347,7 +384,7 @@ __global__ void __launch_bounds__(WG_THREADS, 1)
                     tc_fence_before();
                 }
                 __syncwarp();
-                if (++lap == 2)
+                if (++lap == WG_SPG)
                 {
                     lap = 0;
                     full_phase ^= 1;
