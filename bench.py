@@ -731,8 +731,9 @@ def run_ours(args):
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one conv launch per shard
 # voxel, and where the figure comes from (profiles/).
-CONV_TRAFFIC_BYTES_PER_VOXEL = (69.34e6 + 208.91e6) / (64 * 256 * 256)
-CONV_TRAFFIC_SOURCE = "ncu capture of a 64x256x256 shard scaled by voxels (profiles/)"
+CONV_TRAFFIC_BYTES_PER_VOXEL = (271.2e6 + 1012.1e6) / (256 * 256 * 256)
+CONV_TRAFFIC_SOURCE = ("one-pass ncu capture of a full 256^3 launch (profiles/conv_kernels_dram_bytes_cfg2_256.md); "
+                       "the output lines still dirty in the 126 MB L2 at the kernel's end are not counted")
 
 
 def main():

@@ -45,6 +45,18 @@ def _ptr(v) -> ctypes.c_void_p:
     return ctypes.c_void_p(int(v))
 
 
+def _zero_on(stream, *tensors):
+    """Zero fills that stand in for a kernel (an empty shard's contribution),
+    ordered on the stream that kernel would have run on."""
+    if stream is None or not tensors or not tensors[0].is_cuda:
+        for t in tensors:
+            t.zero_()
+        return
+    with torch.cuda.stream(stream):
+        for t in tensors:
+            t.zero_()
+
+
 def get_dilated_filter_size(f: int, d: int) -> int:
     return f + (f - 1) * (d - 1)
 
@@ -372,7 +384,7 @@ class Tensor:
         return self.buffer[sl]
 
     def zero(self, stream=None):
-        self._storage.zero_()
+        _zero_on(stream, self._storage)
 
     def desc(self) -> TensorDesc:
         d = TensorDesc()
@@ -1184,7 +1196,7 @@ class Convolution:
         s = self.be.stream
         if (input.get_local_size() == 0 or d_output.get_local_size() == 0 or d_filter.numel() == 0
                 or not input.is_split_root()):
-            d_filter.zero_()
+            _zero_on(s, d_filter)
         else:
             call("dcb_conv_bwd_filter", self._plan_wgrad, float(alpha), _ptr(input.nd_ptr(self._x_lo)),
                  _ptr(d_output.get_base_ptr()), float(beta), _ptr(d_filter.data_ptr()), _stream_ptr(s))
@@ -1207,7 +1219,7 @@ class Convolution:
     def backward_bias(self, alpha, d_output: Tensor, beta, bias_gradient: torch.Tensor, reduce=True):
         """convolution.hpp:1109-1142."""
         if d_output.get_local_size() == 0:
-            bias_gradient.zero_()
+            _zero_on(self.be.stream, bias_gradient)
         else:
             yd = d_output.nd_desc()
             call("dcb_bias_bwd", float(alpha), ctypes.byref(yd), _ptr(d_output.get_base_ptr()), float(beta),
@@ -1263,8 +1275,7 @@ class BatchNormalization:
             return 0
         s = self.be.stream
         if input.get_local_size() == 0 or not input.is_split_root():
-            mean.zero_()
-            var.zero_()
+            _zero_on(s, mean, var)
             return 0
         call("dcb_bn_stats", self._plan(input), _ptr(input.get_base_ptr()), _ptr(mean.data_ptr()),
              _ptr(var.data_ptr()), _stream_ptr(s))
@@ -1332,8 +1343,7 @@ class BatchNormalization:
                         mean_gradient, var_gradient):
         s = self.be.stream
         if input.get_local_size() == 0 or not input.is_split_root():
-            for t in (scale_gradient, bias_gradient, mean_gradient, var_gradient):
-                t.zero_()
+            _zero_on(s, scale_gradient, bias_gradient, mean_gradient, var_gradient)
             return 0
         dyd = d_output.nd_desc()
         call("dcb_bn_bwd_reduce", self._plan(input), _ptr(input.get_base_ptr()), ctypes.byref(dyd),

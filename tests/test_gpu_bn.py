@@ -199,3 +199,29 @@ def test_bn_apply_fused_with_leaky_relu_matches_the_two_passes():
     bn.forward_stage2(tx, mean, var, rm, rv, scale, bias, tf, is_training=False, leaky_relu_slope=0.01)
     torch.cuda.synchronize()
     assert torch.equal(tf.buffer, tz.buffer)
+
+
+def test_empty_shard_zero_fills_run_on_the_backend_stream():
+    """A rank without cells contributes zeros to the all-reduces; those fills
+    must be ordered on the backend's stream like the kernels they replace.
+    The stream is kept busy, then writes 5s: a fill on another stream would
+    run first and the 5s would survive."""
+    side = torch.cuda.Stream()
+    locale = dc.Locale(1, 2)
+    be = dc.BackendDNNLib(locale, stream=side, connect=False)
+    # D extent 1 over two ranks: the second one owns nothing
+    t = dc.Tensor([8, 8, 1, 4, 1], locale, dc.Distribution.make_overlapped_distribution([1, 1, 2, 1, 1], [0] * 5))
+    assert t.get_local_size() == 0
+    t.allocate()
+    bn = dc.BatchNormalization(be, 5, 0.9, 1e-5, True)
+    vals = [torch.ones(4, device="cuda") for _ in range(6)]
+    torch.cuda.synchronize()
+    with torch.cuda.stream(side):
+        torch.cuda._sleep(20_000_000)
+        for v in vals:
+            v.fill_(5.0)
+    bn.forward_stage1(t, vals[0], vals[1], True)
+    bn.backward_stage1(t, t, vals[0], vals[1], vals[0], vals[2], vals[3], vals[4], vals[5])
+    torch.cuda.synchronize()
+    for v in vals:
+        assert float(v.abs().max()) == 0.0
