@@ -402,7 +402,8 @@ def run_ours(args):
         # partials, or the separate pass), all-reduce, finalize, apply (--overlap:
         # clear_halo per dim, interior + boundary slabs, each with its filter
         # image, statistics as their own pass)
-        launches["n"] += (3 if overlapped else 2) * n_part + 6 + extra_launches
+        # (the all-reduce over a single rank launches nothing)
+        launches["n"] += (3 if overlapped else 2) * n_part + (6 if world > 1 else 5) + extra_launches
         return got
 
     def bwd_step():

@@ -15,8 +15,9 @@ the HBM figure.  All ranks put before any rank waits, so no kernel ever waits
 for a kernel that has not been launched.
 
 P GPUs (torchrun): real ranks, S^3 split along D; the whole exchange is timed
-(max over ranks) and the bytes each GPU sends per direction (4E) over that time
-is the NVLink figure.
+(max over ranks) and the bytes of one face (4E) over that time is the NVLink
+figure per direction of one neighbour pair; with more than two ranks an interior
+rank sends and receives two faces, which `nvlink_GBs_egress_busiest_gpu` counts.
 
 The payload is the global-offset fill of the reference's halo test, and every
 configuration is checked for exact halo contents after the timed runs.
@@ -174,6 +175,8 @@ def run_ranks(args, torch, dc, dist, world, rank):
                 r = {"mode": f"{world}gpu-D-partition", "C": C, "S": S, "width": width, "dim": "D",
                      "face_MB": 4 * E / 1e6, "exchange_us": 1e3 * float(ms.item()),
                      "nvlink_GBs_per_direction": 4 * E / (float(ms.item()) * 1e-3) / 1e9,
+                     # a rank with a neighbour on both sides sends (and receives) two faces per exchange
+                     "nvlink_GBs_egress_busiest_gpu": (2 if world > 2 else 1) * 4 * E / (float(ms.item()) * 1e-3) / 1e9,
                      "exact": bool(good.item())}
                 if rank == 0:
                     print(json.dumps(r), flush=True)

@@ -328,6 +328,8 @@ int32_t dcb_allreduce_sum(dcb_comm* c, void* data, int64_t count, void* stream)
     int32_t st = peer_ready(c, 0);
     if (st != DCB_OK)
         return st;
+    if (c->nranks == 1)
+        return DCB_OK; // the sum over one rank is the vector itself: nothing to launch
     // A vector longer than the slots (a filter gradient, K*C*taps floats) goes
     // through in max_count-sized pieces, one epoch each.  The slots are double
     // buffered by epoch parity, and a rank can only be one epoch ahead of the
