@@ -25,7 +25,7 @@ HALO_SKIP_UNPACK = 0x2
 HALO_CLEAR_BOUNDARY = 0x4
 HALO_OPS = {"ID": 0 << 4, "SUM": 1 << 4, "MAX": 2 << 4, "MIN": 3 << 4}
 
-MATH_FP32, MATH_TF32, MATH_FP32_SIMT = 0, 1, 2
+MATH_FP32, MATH_TF32, MATH_FP32_SIMT, MATH_BF16 = 0, 1, 2, 3
 
 
 class TensorDesc(ctypes.Structure):

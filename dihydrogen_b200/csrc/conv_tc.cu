@@ -95,7 +95,9 @@ bool tc_geom(const ConvGeom& cg, int math_mode, TcGeom* out)
     g.ys_c = cg.ys_c;
     if ((long long) cg.n * cg.out[0] * cg.out[1] * cg.out[2] == 0 || cg.c == 0 || cg.k == 0)
         return false;
-    g.split = math_mode == DCB_MATH_TF32 ? 0 : 1;
+    g.split = (math_mode == DCB_MATH_TF32 || math_mode == DCB_MATH_BF16) ? 0 : 1;
+    g.rnd_add = math_mode == DCB_MATH_BF16 ? 0x8000u : 0x1000u;
+    g.rnd_mask = math_mode == DCB_MATH_BF16 ? 0xffff0000u : 0xffffe000u;
     const int mult = g.split ? 2 : 1;
     // Filters per launch: the fh accumulator blocks of an input row are one
     // instruction's N (<= 256 columns).
@@ -219,7 +221,9 @@ bool sw_geom(const ConvGeom& cg, int math_mode, SwGeom* out)
     // more input channels than that allows, the channels are taken in equal
     // groups, one launch per group, each adding into the output of the one
     // before (the sum over input channels is what a convolution is).
-    g.split = math_mode == DCB_MATH_TF32 ? 0 : 1;
+    g.split = (math_mode == DCB_MATH_TF32 || math_mode == DCB_MATH_BF16) ? 0 : 1;
+    g.rnd_add = math_mode == DCB_MATH_BF16 ? 0x8000u : 0x1000u;
+    g.rnd_mask = math_mode == DCB_MATH_BF16 ? 0xffff0000u : 0xffffe000u;
     g.w_c_total = cg.c;
     g.c = 0;
     for (int cgp = cg.c; cgp >= 1; --cgp)
@@ -242,9 +246,11 @@ bool sw_geom(const ConvGeom& cg, int math_mode, SwGeom* out)
     if (g.ntot > 256 || (g.f[0] * SW_NBK) % 16)
         return false;
     g.crows = g.c * g.f[2];
-    g.kr = (g.crows * (g.split ? 3 : 1) + 7) / 8 * 8;
-    g.ksteps = g.kr / 8;
-    g.b_rot_bytes = g.kr * g.ntot * 4;
+    g.kr = (g.crows * (g.split ? 2 : 1) + 7) / 8 * 8;
+    g.ks1 = g.kr / 8;
+    g.ksteps = g.ks1 + (g.split ? (g.crows + 7) / 8 : 0);
+    g.kb = g.ksteps * 8;
+    g.b_rot_bytes = g.kb * g.ntot * 4;
     g.b_bytes = g.f[0] * g.b_rot_bytes;
     // an issuer must own one of any fh consecutive rows (see the hand-off
     // notes in the kernel header)
@@ -366,7 +372,9 @@ bool mg_geom(const ConvGeom& cg, int math_mode, SwGeom* out)
         return false;
     if (!(cg.xs[1] % 4 == 0 && cg.xs[0] % 4 == 0 && cg.xs_c % 4 == 0 && cg.xs_n % 4 == 0))
         return false;
-    g.split = math_mode == DCB_MATH_TF32 ? 0 : 1;
+    g.split = (math_mode == DCB_MATH_TF32 || math_mode == DCB_MATH_BF16) ? 0 : 1;
+    g.rnd_add = math_mode == DCB_MATH_BF16 ? 0x8000u : 0x1000u;
+    g.rnd_mask = math_mode == DCB_MATH_BF16 ? 0xffff0000u : 0xffffe000u;
     g.w_c_total = cg.c;
     g.c = 0;
     for (int cgp = cg.c; cgp >= 1; --cgp)
@@ -394,9 +402,11 @@ bool mg_geom(const ConvGeom& cg, int math_mode, SwGeom* out)
     if (g.ntot > 256)
         return false;
     g.crows = g.c * g.f[2];
-    g.kr = (g.crows * (g.split ? 3 : 1) + 7) / 8 * 8;
-    g.ksteps = g.kr / 8;
-    g.b_rot_bytes = g.kr * g.ntot * 4;
+    g.kr = (g.crows * (g.split ? 2 : 1) + 7) / 8 * 8;
+    g.ks1 = g.kr / 8;
+    g.ksteps = g.ks1 + (g.split ? (g.crows + 7) / 8 : 0);
+    g.kb = g.ksteps * 8;
+    g.b_rot_bytes = g.kb * g.ntot * 4;
     g.b_bytes = g.cgroups * MG_SLOTS * g.b_rot_bytes;
     g.groups = TC_GROUPS_MAX;
     g.a_slots = g.groups;

@@ -33,6 +33,9 @@ struct TcGeom
     long long xs_n, xs_c, xs[3];
     long long ys_n, ys_c, ys[3];
     int split;   // 1: 3xTF32, 0: single TF32 pass
+    // rounding of the operands' hi part, (bits + rnd_add) & rnd_mask: to TF32
+    // (0x1000, 0xffffe000) or, in the bf16 mode, to bf16 (0x8000, 0xffff0000)
+    uint32_t rnd_add, rnd_mask;
     int kpad;    // K rounded up to 8, 16 or 32
     int nb;      // accumulator columns per output row = kpad * (split ? 2 : 1)
     int th;      // output rows per tile
@@ -218,7 +221,7 @@ __global__ void tc_pack_filter_kernel(const float* __restrict__ w, float* __rest
         {
             const float wv =
                 w[((((size_t) (ko + g.w_k_off) * g.c_total + (c + g.w_c_off)) * fd + kd) * fh + kh) * fw + kw];
-            const float hi = __uint_as_float(tf32_rna(wv));
+            const float hi = __uint_as_float((__float_as_uint(wv) + g.rnd_add) & g.rnd_mask);
             if (half == 0)
                 val = hi;
             else if (part == 0)
@@ -316,7 +319,8 @@ __device__ __forceinline__ uint32_t lds_u32(uint32_t saddr)
 
 // ktab8 / raw are shared-window addresses; the loads are explicit ld.shared so
 // that they are issued back to back (generic loads were serialised).
-__device__ __forceinline__ void convert_chunk(uint32_t ktab8, uint32_t raw_lane, uint32_t (&v)[8])
+__device__ __forceinline__ void convert_chunk(uint32_t ktab8, uint32_t raw_lane, uint32_t (&v)[8],
+                                              uint32_t rnd_add = 0x1000u, uint32_t rnd_mask = 0xffffe000u)
 {
     // All loads first and unconditional (a padding row reads cell 4 and is
     // zeroed afterwards), so the eight chains run in parallel without branches.
@@ -332,7 +336,7 @@ __device__ __forceinline__ void convert_chunk(uint32_t ktab8, uint32_t raw_lane,
     {
         const uint32_t part = tb[e] >> 16;
         const float xe = part < 2 ? __uint_as_float(xv[e]) : 0.f;
-        const uint32_t hi = tf32_rna(xe);
+        const uint32_t hi = (__float_as_uint(xe) + rnd_add) & rnd_mask;
         const uint32_t lo = tf32_rna(xe - __uint_as_float(hi));
         v[e] = part == 0 ? hi : lo;
     }
@@ -566,7 +570,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
 #pragma unroll
                     for (int ch = 0; ch < 4; ++ch)
                         if (ch * 8 < g.kr)
-                            convert_chunk(ktab_s + 32u * ch, raw_s, v[ch]);
+                            convert_chunk(ktab_s + 32u * ch, raw_s, v[ch], g.rnd_add, g.rnd_mask);
                     if (!a_first)
                         ok = mbar_wait(&a_empty[a_slot], a_phase, abort_flag);
                     if (!ok)
@@ -599,7 +603,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                         for (int r0 = 0; r0 < g.kr; r0 += 8)
                         {
                             uint32_t v[8];
-                            convert_chunk(ktab_s + 4u * r0, raw_s, v);
+                            convert_chunk(ktab_s + 4u * r0, raw_s, v, g.rnd_add, g.rnd_mask);
                             tmem_st8(a_addr + (uint32_t) r0, v);
                         }
                     }

@@ -12,8 +12,10 @@
 //     i-fh+1..i, all slots) are one contiguous column range and ONE
 //     instruction of N = fh * fd * 16 updates all of them.  Which kd lands in
 //     which slot depends on d mod fd: the filter image exists in fd rotations.
-//   * 3xTF32 is folded into the reduction: A k-rows [hi ; lo ; hi] against
-//     B k-rows [w_hi ; w_hi ; w_lo], so one accumulator block per output row.
+//   * 3xTF32 is folded into the reduction: the A columns [hi ; lo] meet the
+//     B k-rows [w_hi ; w_hi], then the k-steps start over at the hi columns
+//     and meet [w_lo ; 0]: one accumulator block per output row, every tap
+//     written into tensor memory twice, not three times.
 //   * After step d the plane od = d + pad - (fd-1) has all its terms: the
 //     epilogue warps store it (if it belongs to the segment), re-zero its
 //     blocks and hand them back, row by row, while the issuers carry on with
@@ -107,10 +109,14 @@ struct SwGeom
     long long xs_n, xs_c, xs[3];
     long long ys_n, ys_c, ys[3];
     int split;      // 1: 3xTF32, 0: single TF32 pass
+    uint32_t rnd_add, rnd_mask; // as in TcGeom
     int th;         // output rows per column
     int rows;       // staged rows per step = th + fh - 1
     int crows;      // c * fw
-    int kr, ksteps; // k-rows per staged row (multiple of 8), kr / 8
+    int kr;         // A columns per slot (multiple of 8): the taps' hi parts, then (3xTF32) their lo parts
+    int ks1, ksteps; // k-steps that read the A columns in order (kr / 8); all k-steps: with 3xTF32 the
+                    // hi parts are read a second time, from column 0, against the filter's lo parts
+    int kb;         // k-rows of the filter image = 8 * ksteps
     int ntot;       // fh * fd * SW_NBK
     int b_rot_bytes, b_bytes; // one rotation of the filter image, all fd of them
     int groups, a_slots;
@@ -164,7 +170,7 @@ __device__ __forceinline__ int sw_mod(int a, int m)
 __global__ void sw_pack_filter_kernel(const float* __restrict__ w, float* __restrict__ b, SwGeom g)
 {
     const int fd = g.f[0], fh = g.f[1], fw = g.f[2];
-    const int per_rot = g.kr * g.ntot;
+    const int per_rot = g.kb * g.ntot;
     const long long total = (long long) fd * per_rot;
     for (long long i = (long long) blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (long long) gridDim.x * blockDim.x)
@@ -183,14 +189,29 @@ __global__ void sw_pack_filter_kernel(const float* __restrict__ w, float* __rest
         const int ko = ncol % SW_NBK;
         const int kh = fh - 1 - j;
         const int kd = sw_mod(rot + g.pad[0] - s, fd);
-        const int part = krow / g.crows; // 0: A_hi x w_hi, 1: A_lo x w_hi, 2: A_hi x w_lo
-        const int rem = krow % g.crows;
+        // k-rows 0 .. kr-1 meet the A columns [hi | lo] (w_hi both times); the k-steps
+        // after them read the A columns from 0 again and meet w_lo (zeros below the
+        // columns that are not hi parts)
+        int part, rem;
+        if (krow < g.kr)
+        {
+            part = krow / g.crows; // 0: A_hi x w_hi, 1: A_lo x w_hi
+            rem = krow % g.crows;
+            if (part >= (g.split ? 2 : 1))
+                part = 3;
+        }
+        else
+        {
+            rem = krow - g.kr;
+            part = (g.split && rem < g.crows) ? 2 : 3; // 2: A_hi x w_lo
+            rem = rem < g.crows ? rem : 0;
+        }
         const int c = rem / fw, kw = rem % fw;
         float val = 0.f;
-        if (ko < g.k && part < (g.split ? 3 : 1))
+        if (ko < g.k && part < 3)
         {
             const float wv = w[((((size_t) ko * g.w_c_total + g.w_c_off + c) * fd + kd) * fh + kh) * fw + kw];
-            const float hi = __uint_as_float(tf32_rna(wv));
+            const float hi = __uint_as_float((__float_as_uint(wv) + g.rnd_add) & g.rnd_mask);
             val = part < 2 ? hi : __uint_as_float(tf32_rna(wv - hi));
         }
         b[i] = val;
@@ -259,13 +280,13 @@ __global__ void __launch_bounds__(SW_FOLD_WARPS * 32)
         sqsums[t - SW_NBK] = (float) acc;
 }
 
-// 4 channels x 3 taps, pad 1, split: k-rows 0..11 hi, 12..23 lo, 24..35 hi, 36..39 zero.
+// 4 channels x 3 taps, split: A columns 0..11 hi, 12..23 lo.
 // ROUND_LO: the lo part rounded to TF32 as well (two more instructions per tap).
 // The multi-group kernel asks for it: its accumulators take 180 and more updates
 // per output, the tensor pipe's accumulation already uses most of the 1e-5 there
 // and the unrounded remainder tipped a case over the bound.
 template <bool ROUND_LO = false>
-__device__ __forceinline__ void sw_convert_c4f3(uint32_t raw_lane, uint32_t pitch, uint32_t (&v)[5][8])
+__device__ __forceinline__ void sw_convert_c4f3(uint32_t raw_lane, uint32_t pitch, uint32_t (&v)[3][8])
 {
     uint32_t xv[12];
 #pragma unroll
@@ -284,11 +305,7 @@ __device__ __forceinline__ void sw_convert_c4f3(uint32_t raw_lane, uint32_t pitc
             ROUND_LO ? tf32_rna(xe - __uint_as_float(hi)) : __float_as_uint(xe - __uint_as_float(hi));
         v[r / 8][r % 8] = hi;
         v[(12 + r) / 8][(12 + r) % 8] = lo;
-        v[(24 + r) / 8][(24 + r) % 8] = hi;
     }
-#pragma unroll
-    for (int r = 36; r < 40; ++r)
-        v[r / 8][r % 8] = 0u;
 }
 
 // ---------------------------------------------------------------------------
@@ -379,7 +396,7 @@ __global__ void __launch_bounds__(sw_threads(EPI), 1)
         const int part = r / g.crows, rem = r % g.crows;
         const int c = rem / g.f[2], kw = rem % g.f[2];
         const uint32_t off = (uint32_t) (c * g.chunk_rows * TC_RAW_W + g.rx + kw);
-        const uint32_t sel = part < (g.split ? 3 : 1) ? (part == 1 ? 1u : 0u) : 2u;
+        const uint32_t sel = part < (g.split ? 2 : 1) ? (uint32_t) part : 2u;
         ktab[r] = sel == 2u ? ((2u << 16) | 4u) : (off | (sel << 16));
     }
     for (int i = tid; i < g.b_bytes / 16; i += sw_threads(EPI))
@@ -439,14 +456,14 @@ __global__ void __launch_bounds__(sw_threads(EPI), 1)
                         const uint32_t raw_s = smem_u32(raw) + 4u * (uint32_t) mcol;
                         if (C4F3)
                         {
-                            uint32_t v[5][8];
+                            uint32_t v[3][8];
                             if (!SW_DBG(5))
                                 // the converter is written for taps that start 3 cells into the staged row
                                 sw_convert_c4f3(raw_s + 4u * (uint32_t) (g.rx - 3), pitch, v);
                             else
                             {
 #pragma unroll
-                                for (int ck = 0; ck < 5; ++ck)
+                                for (int ck = 0; ck < 3; ++ck)
 #pragma unroll
                                     for (int e = 0; e < 8; ++e)
                                         v[ck][e] = 0u;
@@ -461,7 +478,7 @@ __global__ void __launch_bounds__(sw_threads(EPI), 1)
                             if (!SW_DBG(0))
                             {
 #pragma unroll
-                                for (int ck = 0; ck < 5; ++ck)
+                                for (int ck = 0; ck < 3; ++ck)
                                     tmem_st8(a_addr + (uint32_t) (ck * 8), v[ck]);
                             }
                         }
@@ -475,7 +492,7 @@ __global__ void __launch_bounds__(sw_threads(EPI), 1)
                             for (int r0 = 0; r0 < g.kr; r0 += 8)
                             {
                                 uint32_t v[8];
-                                convert_chunk(ktab_s + 4u * r0, raw_s, v);
+                                convert_chunk(ktab_s + 4u * r0, raw_s, v, g.rnd_add, g.rnd_mask);
                                 tmem_st8(a_addr + (uint32_t) r0, v);
                             }
                         }
@@ -636,12 +653,14 @@ __global__ void __launch_bounds__(sw_threads(EPI), 1)
                             tc_fence_after();
                             if (lane == i)
                             {
-                                uint32_t a_addr = a_ring + slot * (uint32_t) g.kr + 8u * (uint32_t) ks_lo;
+                                const uint32_t a_base = a_ring + slot * (uint32_t) g.kr;
+                                uint32_t a_addr = a_base + 8u * (uint32_t) ks_lo;
                                 uint64_t bd = bd0 + (uint64_t) (b_kstep_units * (uint32_t) ks_lo);
                                 for (int ks = ks_lo; ks < (SW_DBG(3) ? ks_lo + 1 : ks_hi); ++ks)
                                 {
                                     mma_tf32_ts(my_d, a_addr, bd, SW_DBG(4) ? ((my_idesc & ~(0x3fu << 17)) | (2u << 17)) : my_idesc);
-                                    a_addr += 8;
+                                    // after the k-steps over [hi | lo] the hi parts are read again
+                                    a_addr = ks + 1 == g.ks1 ? a_base : a_addr + 8;
                                     bd += b_kstep_units;
                                 }
                                 if (SW_DBG(7))

@@ -7,7 +7,7 @@
 //     slots (od & 3; with fd = 3 one of them idles each step), so a row's
 //     blocks are 16 columns and one instruction covers N = fh * 16.
 //   * A staged input row is converted once per channel group ("sub-row" (i, g)):
-//     the group's c * fw taps, [hi ; lo ; hi], go into an A slot and are
+//     the group's c * fw taps, [hi ; lo], go into an A slot and are
 //     multiplied with that group's filter image.  All groups of a row add into
 //     the same accumulators, so nothing is blended in memory and the output is
 //     written once.  Sub-rows are dealt to the converter groups / issuers in
@@ -56,7 +56,7 @@ __device__ __forceinline__ void tmem_st4_zero(uint32_t taddr)
 __global__ void mg_pack_filter_kernel(const float* __restrict__ w, float* __restrict__ b, SwGeom g)
 {
     const int fd = g.f[0], fh = g.f[1], fw = g.f[2];
-    const int per_rot = g.kr * g.ntot;
+    const int per_rot = g.kb * g.ntot;
     const long long total = (long long) g.cgroups * MG_SLOTS * per_rot;
     for (long long i = (long long) blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (long long) gridDim.x * blockDim.x)
@@ -76,14 +76,27 @@ __global__ void mg_pack_filter_kernel(const float* __restrict__ w, float* __rest
         const int ko = ncol % MG_NBK;
         const int kh = fh - 1 - j;
         const int kd = (rot + g.pad[0] - s) & (MG_SLOTS - 1);
-        const int part = krow / g.crows; // 0: A_hi x w_hi, 1: A_lo x w_hi, 2: A_hi x w_lo
-        const int rem = krow % g.crows;
+        // as in sw_pack_filter_kernel: [hi | lo] against w_hi, then the hi columns again against w_lo
+        int part, rem;
+        if (krow < g.kr)
+        {
+            part = krow / g.crows;
+            rem = krow % g.crows;
+            if (part >= (g.split ? 2 : 1))
+                part = 3;
+        }
+        else
+        {
+            rem = krow - g.kr;
+            part = (g.split && rem < g.crows) ? 2 : 3;
+            rem = rem < g.crows ? rem : 0;
+        }
         const int c = grp * g.c + rem / fw, kw = rem % fw;
         float val = 0.f;
-        if (ko < g.k && kd < fd && part < (g.split ? 3 : 1))
+        if (ko < g.k && kd < fd && part < 3)
         {
             const float wv = w[((((size_t) ko * g.w_c_total + c) * fd + kd) * fh + kh) * fw + kw];
-            const float hi = __uint_as_float(tf32_rna(wv));
+            const float hi = __uint_as_float((__float_as_uint(wv) + g.rnd_add) & g.rnd_mask);
             val = part < 2 ? hi : __uint_as_float(tf32_rna(wv - hi));
         }
         b[i] = val;
@@ -152,7 +165,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         const int part = r / g.crows, rem = r % g.crows;
         const int c = rem / g.f[2], kw = rem % g.f[2];
         const uint32_t off = (uint32_t) (c * g.chunk_rows * TC_RAW_W + g.rx + kw);
-        const uint32_t sel = part < (g.split ? 3 : 1) ? (part == 1 ? 1u : 0u) : 2u;
+        const uint32_t sel = part < (g.split ? 2 : 1) ? (uint32_t) part : 2u;
         ktab[r] = sel == 2u ? ((2u << 16) | 4u) : (off | (sel << 16));
     }
     for (int i = tid; i < g.b_bytes / 16; i += TC_THREADS)
@@ -218,8 +231,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                         const uint32_t raw_s = smem_u32(raw) + 4u * (uint32_t) mcol;
                         if (C4F3)
                         {
-                            uint32_t v[5][8];
-                            // taps start 4 - pad cells into the staged row: the converter is written for pad 1
+                            uint32_t v[3][8];
+                            // the converter is written for taps that start 3 cells into the staged row
                             sw_convert_c4f3<true>(raw_s + 4u * (uint32_t) (g.rx - 3), pitch, v);
                             if (!a_first)
                                 ok = mbar_wait(&a_empty[a_slot], a_phase, abort_flag);
@@ -227,7 +240,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                                 break;
                             tc_fence_after();
 #pragma unroll
-                            for (int ck = 0; ck < 5; ++ck)
+                            for (int ck = 0; ck < 3; ++ck)
                                 tmem_st8(a_addr + (uint32_t) (ck * 8), v[ck]);
                         }
                         else
@@ -240,7 +253,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                             for (int r0 = 0; r0 < g.kr; r0 += 8)
                             {
                                 uint32_t v[8];
-                                convert_chunk(ktab_s + 4u * r0, raw_s, v);
+                                convert_chunk(ktab_s + 4u * r0, raw_s, v, g.rnd_add, g.rnd_mask);
                                 tmem_st8(a_addr + (uint32_t) r0, v);
                             }
                         }
@@ -366,7 +379,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                             tc_fence_after();
                             if (lane == i)
                             {
-                                uint32_t a_addr = a_ring + slot * (uint32_t) g.kr;
+                                const uint32_t a_base = a_ring + slot * (uint32_t) g.kr;
+                                uint32_t a_addr = a_base;
                                 uint64_t bd = my_b_desc
                                               + (uint64_t) (((uint32_t) grp * MG_SLOTS + rot) * rot_units);
                                 // the group's accumulator set
@@ -374,7 +388,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                                 for (int ks = 0; ks < ksteps; ++ks)
                                 {
                                     mma_tf32_ts(d_addr, a_addr, bd, my_idesc);
-                                    a_addr += 8;
+                                    a_addr = ks + 1 == g.ks1 ? a_base : a_addr + 8;
                                     bd += b_kstep_units;
                                 }
                                 mma_commit(&a_empty[slot]);

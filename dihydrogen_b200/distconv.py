@@ -868,7 +868,9 @@ class Options:
     """backend::Options (dnn_backend.hpp:46-63) with the environment overrides
     of legacy/src/dnn_backend/options.cpp:13-71: a variable that is SET (to
     anything, as in the reference) turns its option on.  ``math_mode`` has no
-    counterpart there."""
+    counterpart there: ``MATH_FP32`` (3xTF32 on tensor cores, fp32 quality),
+    ``MATH_TF32`` (one TF32 pass), ``MATH_BF16`` (bf16 operands, fp32
+    accumulation) or ``MATH_FP32_SIMT`` (CUDA cores)."""
 
     def __init__(self, overlap_halo_exchange=False, deterministic=True, enable_profiling=False,
                  math_mode=_abi.MATH_FP32, ws_capacity_factor=1.0):

@@ -196,6 +196,12 @@ typedef struct dcb_nd_desc
                                 fp32 FMA where no tensor-core kernel applies */
 #define DCB_MATH_TF32 1      /* single TF32 pass */
 #define DCB_MATH_FP32_SIMT 2 /* force the fp32 CUDA-core kernels */
+#define DCB_MATH_BF16 3      /* bf16 operands, fp32 accumulation: inputs and filters are
+                                rounded to bf16 (ties away from zero) on their way into the
+                                tensor-core kernels and multiplied in one pass; a bf16 value
+                                is a TF32 value, so the TF32 instruction computes exactly what
+                                a bf16 one would.  Backward filter keeps fp32 quality.  Shapes
+                                without a tensor-core kernel run the fp32 CUDA-core kernels. */
 
 typedef struct dcb_conv_desc
 {

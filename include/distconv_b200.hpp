@@ -381,7 +381,8 @@ inline void profile_range_pop()
 // its option on.  The workspace factor and the JIT fields are carried for
 // source compatibility; plans own their workspaces and nothing is compiled at
 // run time.  math_mode has no counterpart: DCB_MATH_FP32 (3xTF32 on tensor
-// cores, fp32 quality), DCB_MATH_TF32 or DCB_MATH_FP32_SIMT.
+// cores, fp32 quality), DCB_MATH_TF32, DCB_MATH_BF16 (bf16 operands, fp32
+// accumulation) or DCB_MATH_FP32_SIMT.
 struct Options
 {
     bool overlap_halo_exchange;

@@ -390,6 +390,48 @@ def test_rows_padded_to_a_pitch_with_odd_extents(W, pad):
             assert bool(torch.isnan(st[..., ext:]).all()), "a store went past the end of a row"
 
 
+def _round_bf16(a):
+    """fp32 -> bf16, ties away from zero, as the kernels' integer rounding does."""
+    b = a.astype(np.float32).view(np.uint32)
+    return ((b + np.uint32(0x8000)) & np.uint32(0xFFFF0000)).view(np.float32)
+
+
+@pytest.mark.parametrize("mode", [_abi.MATH_BF16, _abi.MATH_TF32])
+@pytest.mark.parametrize("shape", [
+    (1, 4, 16, (20, 23, 140), (3, 3, 3)),     # the bench layer's family: sweep kernel, multi-group backward data
+    (2, 16, 8, (40, 70), (3, 3)),             # 2-D: row kernel
+    (1, 12, 16, (9, 17, 33), (3, 3, 3)),      # channel groups
+])
+def test_reduced_precision_modes_equal_the_rounded_operands_product(shape, mode):
+    """DCB_MATH_BF16 / DCB_MATH_TF32: operands rounded to bf16 / TF32 on their way
+    into the tensor cores, products exact, fp32 accumulation.  So forward and
+    backward data must equal the fp64 convolution of the ROUNDED inputs and
+    filters within the fp32 contract; the error against the unrounded operands
+    is the rounding's (2^-9 / 2^-11 relative per operand).  Backward filter keeps
+    fp32 quality in every mode."""
+    N, C, K, sp, f = shape
+    rng = np.random.default_rng(sum(sp) + mode)
+    nsd = len(sp)
+    pads = [1] * nsd
+    x = rng.normal(size=(N, C) + tuple(sp)).astype(np.float32)
+    w = rng.normal(0, 0.2, (K, C) + tuple(f)).astype(np.float32)
+    dy = rng.normal(size=(N, K) + tuple(sp)).astype(np.float32)
+    if mode == _abi.MATH_BF16:
+        rnd = _round_bf16
+    else:
+        rnd = lambda a: ((a.view(np.uint32) + np.uint32(0x1000)) & np.uint32(0xFFFFE000)).view(np.float32)
+    y, dx, dw = run_all(x, w, dy, pads, [1] * nsd, [1] * nsd, mode)
+    emu.assert_close(y, O.conv_fwd(rnd(x), rnd(w), pads, [1] * nsd), TOL, "y")
+    dx_ref = np.zeros_like(x)
+    O.conv_bwd_data(rnd(w), rnd(dy), dx_ref, pads, [1] * nsd)
+    emu.assert_close(dx, dx_ref, TOL, "dx")
+    emu.assert_close(dw, O.conv_bwd_filter(x, dy, tuple(f), pads, [1] * nsd), TOL, "dw")
+    # and the rounding is really there: against the unrounded product the bf16 result is ~1e-3 off
+    full = O.conv_fwd(x, w, pads, [1] * nsd)
+    err = np.abs(y - full).max() / np.abs(full).max()
+    assert (1e-4 < err < 2e-2) if mode == _abi.MATH_BF16 else (1e-5 < err < 5e-3), err
+
+
 @pytest.mark.parametrize("lead", [1, 2, 3])
 @pytest.mark.parametrize("Wl", [32, 64, 35])
 def test_window_that_starts_above_a_16_byte_boundary(lead, Wl):
