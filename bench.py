@@ -304,6 +304,163 @@ def run_reference(args):
 
 
 # --------------------------------------------------------------------------
+# GPU arm, BASELINE configs[0] (the reference's own CPU-runnable case)
+# --------------------------------------------------------------------------
+def run_ours_cfg1(args):
+    """BASELINE configs[0]: x 4 x 16 x 64 x 64 ~ U(-1, 1), w 16 x 16 x 3 x 3 ~ N(0, 0.1),
+    stride 1, pad 1, BN (gamma 1, beta 0, eps 1e-5), seed 0; one GPU
+    (unpartitioned) or two (split along H, the configuration's own locale).  A step
+    is halo exchange + conv forward (statistics from its epilogue where the
+    plan can) + BN forward.  16 384 voxels: the step is launch-latency bound,
+    the line is here so that the same configuration the reference's CPU code can
+    run (`--impl reference --config cfg1`) has a GPU figure beside it."""
+    import torch
+    import torch.distributed as dist
+    import torch.nn.functional as F
+
+    import dihydrogen_b200 as dc
+    from dihydrogen_b200 import _abi
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    if world not in (1, 2) or (world > 1 and world != args.gpus):
+        raise SystemExit("--config cfg1 runs on 1 GPU or on 2 (split along H)")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback for the product path")
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    if world > 1:
+        sys.stdout.flush()
+        saved = os.dup(1)
+        os.dup2(2, 1)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
+        dist.barrier()
+        torch.cuda.synchronize()
+        os.dup2(saved, 1)
+        os.close(saved)
+    c = CFG1
+    rng = np.random.default_rng(0)
+    gx = rng.uniform(-1, 1, (c["N"], c["C"], c["H"], c["W"])).astype(np.float32)
+    gw = rng.normal(0, 0.1, (c["K"], c["C"], c["f"], c["f"])).astype(np.float32)
+    locale = dc.Locale.from_torch_distributed() if world > 1 else dc.Locale(0, 1)
+    grid = [1, world]  # W, H
+    f, pads = [c["f"]] * 2, [1, 1]
+    x = dc.create_input_tensor([c["W"], c["H"], c["C"], c["N"]], grid + [1, 1], f, [1, 1], [1, 1], locale)
+    fshape = f + [c["C"], c["K"]]
+    y = dc.create_convolution_output_tensor(x, fshape, [1, 1], pads, [1, 1])
+    z = dc.Tensor(y.shape, locale, y.dist, y._local_of)
+    for t in (x, y, z):
+        t.allocate()
+    src = tuple(slice(o, o + l) for o, l in reversed(list(zip(x.offset, x.local_shape))))
+    x.owned().copy_(torch.from_numpy(np.ascontiguousarray(gx[src])))
+    w = torch.from_numpy(gw).cuda()
+    be = dc.BackendDNNLib(locale, options=dc.Options(), allreduce="peer", allreduce_max_count=4096)
+    conv = dc.Convolution(be, 4)
+    conv.setup(x, w, y, None, None, None, pads, [1, 1], [1, 1])
+    bn = dc.BatchNormalization(be, 4, DECAY, EPS, True)
+    K = c["K"]
+    stats = torch.zeros(2 * K, device="cuda")
+    mean, var = stats[:K], stats[K:]
+    rm, rv = torch.zeros(K, device="cuda"), torch.ones(K, device="cuda")
+    scale, bias = torch.ones(K, device="cuda"), torch.zeros(K, device="cuda")
+    stream = torch.cuda.current_stream()
+
+    def step():
+        got = conv.forward(1.0, x, w, 0.0, y, statistics=(mean, var))
+        bn.forward(y, mean, var, rm, rv, scale, bias, z, True, statistics_ready=bool(got))
+
+    def max_over_ranks(v):
+        if world == 1:
+            return v
+        t = torch.tensor([v], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def timed(fn, steps, warm):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(steps):
+            fn()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        return max_over_ranks(e0.elapsed_time(e1) / steps)
+
+    sampler = ClockSampler(torch.cuda.current_device())
+    if rank == 0:
+        sampler.start()
+    ms_step = timed(step, args.steps, max(args.warmup, 3))
+    # end to end: pinned host -> device input, the step, device -> pinned host result, every step
+    host_x = torch.empty(x.buffer.shape, dtype=torch.float32).pin_memory()
+    host_x.copy_(x.buffer.cpu())
+    host_z = torch.empty(z.buffer.shape, dtype=torch.float32).pin_memory()
+
+    def e2e_step():
+        x.buffer.copy_(host_x, non_blocking=True)
+        step()
+        host_z.copy_(z.buffer, non_blocking=True)
+        stream.synchronize()
+
+    ms_e2e = timed(e2e_step, max(10, args.steps // 4), 3)
+    # parity: the whole output against fp64 on the device (the configuration is tiny)
+    step()
+    torch.cuda.synchronize()
+    xd, wd = torch.from_numpy(gx).cuda().double(), torch.from_numpy(gw).cuda().double()
+    y64 = F.conv2d(xd, wd, padding=1)
+    m64 = y64.mean(dim=(0, 2, 3))
+    n_el = y64.numel() // K
+    v64 = y64.var(dim=(0, 2, 3), unbiased=True)
+    z64 = (y64 - m64[None, :, None, None]) / torch.sqrt(y64.var(dim=(0, 2, 3), unbiased=False)[None, :, None, None] * n_el / (n_el - 1) + EPS)
+    osl = tuple(slice(o, o + l) for o, l in reversed(list(zip(y.offset, y.local_shape))))
+
+    def rel(a, b):
+        return float(((a.double() - b).abs() / (b.abs() + b.pow(2).mean().sqrt())).max())
+
+    errs = [rel(y.owned(), y64[osl]), rel(z.owned(), z64[osl]), rel(mean, m64), rel(var, v64)]
+    err = max_over_ranks(max(errs))
+    status_ok = (conv.halo_xch_input.status() == _abi.OK and be.allreducer.status() == _abi.OK
+                 and int(_abi.lib().dcb_conv_plan_status(conv._plan_fwd, None)) == _abi.OK)
+    ok = err <= 1e-5 and status_ok
+    vox = c["N"] * c["H"] * c["W"]
+    in_b, out_b = 4 * gx.size, 4 * c["N"] * K * c["H"] * c["W"]
+    peaks, peak_kind = measured_peaks()
+    t_conv = timed(lambda: conv.forward(1.0, x, w, 0.0, y, statistics=(mean, var)), 50, 5)
+    line = {
+        "metric": "voxels/s per halo+conv3d+BN layer", "value": vox / (ms_step * 1e-3), "unit": "voxels/s",
+        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "BASELINE configs[0]: 2-D conv+BN layer, N=4 C=16 64x64 -> K=16 3x3 s1 p1, halo "
+                               "exchange + conv fwd + BN fwd (global stats)",
+                   "partition": f"1x{world} (W,H)", "l2": "the whole problem (2 MB) lives in L2: launch-latency bound, "
+                                                           "not a bandwidth figure"},
+        "e2e": {"value": vox / (ms_e2e * 1e-3), "unit": "voxels/s", "ms_per_step": ms_e2e,
+                "h2d_bytes_per_step": int(host_x.numel() * 4), "d2h_bytes_per_step": int(host_z.numel() * 4)},
+        "gpu_launches": args.steps * ((2 if world > 1 else 0) + (6 if world > 1 else 5)),
+        "roofline": {"kernel": "conv_fwd", "bound": "hbm", "achieved": (in_b + out_b) / world / (t_conv * 1e-3) / 1e9,
+                     "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": (in_b + out_b) / world / (t_conv * 1e-3) / 1e9 / peaks["hbm_gbs"], "peak_source": peak_kind,
+                     "traffic": None, "kernels_ms": {"conv_fwd": round(t_conv, 4)},
+                     "conv_kernel_variant": conv.kernel_variant(0),
+                     "note": "1.3 MB per launch: the kernel's time is its launch and pipeline fill"},
+        "parity_check": {"max_rel_err": err, "tolerance": 1e-5, "kernel_status_ok": status_ok, "ok": ok,
+                         "what": "whole conv output, BN output, mean and variance against fp64 on the device"},
+        "verified": ok, "clocks": sampler.stop() if rank == 0 else None,
+    }
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+    if not ok:
+        raise SystemExit(3)
+
+
+# --------------------------------------------------------------------------
 # GPU arm
 # --------------------------------------------------------------------------
 def run_ours(args):
@@ -747,7 +904,7 @@ def main():
                     help="auto: the weak-scaling ladder D / D x H / 2 x 2 x 2 at 2 / 4 / 8 GPUs; d: split D only; "
                          "or an explicit process grid w,h,d (e.g. 2,1,1: two GPUs split along W)")
     ap.add_argument("--config", default="cfg2", choices=["cfg2", "cfg1"],
-                    help="cfg2 = BASELINE configs[1] (the metric's workload); cfg1 (--impl reference only) = "
+                    help="cfg2 = BASELINE configs[1] (the metric's workload); cfg1 = "
                          "BASELINE configs[0] on the reference's own ref::Backend through oracle/_ref/ref_driver")
     ap.add_argument("--no-fused-stats", action="store_true",
                     help="run the BN statistics as their own pass instead of taking them from the conv epilogue")
@@ -762,9 +919,10 @@ def main():
     if args.impl == "reference":
         run_reference(args)
     else:
-        if args.config != "cfg2":
-            raise SystemExit("--config cfg1 is a reference-arm option")
-        run_ours(args)
+        if args.config == "cfg1":
+            run_ours_cfg1(args)
+        else:
+            run_ours(args)
 
 
 if __name__ == "__main__":
