@@ -1197,8 +1197,9 @@ int32_t tc_conv_bwd_filter(TcPlan* p, float alpha, const float* x, const float* 
     WgGeom g = p->wg;
     const ConvGeom& cg = p->wg_cg;
     const int skip = x_skip(x);
-    if ((reinterpret_cast<uintptr_t>(x) & 3) != 0 || g.stride[2] != 1 && skip != 0
-        || !skip_ok(skip, g.pad[2], g.f[2], WG_TW, WG_XW))
+    // cells one bulk copy's outputs span: 128 at stride 1, 64 outputs at every second cell at stride 2
+    const int span = g.stride[2] == 2 ? 2 * (WG_TW / 2 - 1) + 1 : WG_TW;
+    if ((reinterpret_cast<uintptr_t>(x) & 3) != 0 || !skip_ok(skip, g.pad[2], g.f[2], span, WG_XW))
         return DCB_UNSUPPORTED; // the caller falls back to the CUDA-core kernel
     tc_row_window(g, skip);
 #if DCB_WG_KNOCKOUT

@@ -491,6 +491,41 @@ def test_window_that_starts_above_a_16_byte_boundary(lead, Wl):
     assert bool(torch.isnan(dxs[..., :4]).all()) and bool(torch.isnan(dxs[..., 4 + Wl:]).all())
 
 
+@pytest.mark.parametrize("lead", [1, 3])
+def test_stride_2_backward_filter_on_a_window_above_a_16_byte_boundary(lead):
+    """The stride-2 layer of a W-partitioned tensor: x is read with its halo from
+    `lead` floats above a 16-byte boundary (no padding along W), dy's owned cells
+    sit on one.  The tcgen05 backward filter must take it (two half windows per
+    unit, every second cell) and meet the contract."""
+    rng = np.random.default_rng(lead)
+    N, C, K, Wl = 1, 4, 16, 70
+    D, H = 9, 11
+    We = 2 * Wl + 1
+    Do, Ho = (D + 2 - 3) // 2 + 1, (H + 2 - 3) // 2 + 1
+
+    def shard(a, off):
+        pitch = -(-(off + a.shape[-1]) // 4) * 4
+        st = torch.full(a.shape[:-1] + (pitch,), float("nan"), device="cuda")
+        v = st[..., off:off + a.shape[-1]]
+        v.copy_(torch.from_numpy(a))
+        return st, v
+
+    x = rng.normal(size=(N, C, D, H, We)).astype(np.float32)
+    w = rng.normal(0, 0.2, (K, C, 3, 3, 3)).astype(np.float32)
+    dy = rng.normal(size=(N, K, Do, Ho, Wl)).astype(np.float32)
+    xs, xv = shard(x, lead)
+    dys, dyv = shard(dy, 4)
+    wt = torch.from_numpy(w).cuda()
+    dw = torch.zeros_like(wt)
+    pads, strides = [1, 1, 0], [2, 2, 2]
+    p = Plan(xv, wt, dyv, pads, strides, [1] * 3, _abi.MATH_FP32)
+    assert _abi.lib().dcb_conv_plan_kernel_variant(p.p, 2) == 5
+    p.bwd_filter(1.0, xv, dyv, 0.0, dw)
+    torch.cuda.synchronize()
+    assert _abi.lib().dcb_conv_plan_status(p.p, None) == _abi.OK
+    emu.assert_close(dw.cpu().numpy(), O.conv_bwd_filter(x, dy, (3, 3, 3), pads, strides), TOL, "dw")
+
+
 def test_backward_data_full_shard_16_channels_against_fp64():
     """Backward data of the benchmark layer on its 256^3 shard: dy has 16
     channels, which the multi-group sweep kernel walks as four groups inside one
