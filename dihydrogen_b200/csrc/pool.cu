@@ -73,16 +73,19 @@ constexpr int POOL_TW = POOL_THREADS;
 template <int WD, int W, int S>
 __global__ void __launch_bounds__(POOL_THREADS)
     pool_fwd_kernel(PoolGeom g, float alpha, float beta, const float* __restrict__ x, float* y,
-                    unsigned char* __restrict__ argmax)
+                    unsigned char* __restrict__ argmax, int tw_log2, long long rows)
 {
     // window / stride as compile-time constants where the launch found a match
     // (unrolled loops, shifts for the divisions); 0 = read them from the geometry
     const int w0_ = WD ? WD : g.win[0], w1_ = W ? W : g.win[1], w2_ = W ? W : g.win[2];
     const int s0_ = S ? (WD == 1 ? 1 : S) : g.stride[0], s1_ = S ? S : g.stride[1], s2_ = S ? S : g.stride[2];
-    const int ow = blockIdx.y * POOL_THREADS + threadIdx.x;
-    if (ow >= g.out[2])
+    // a block is 256 >> tw_log2 output rows of (1 << tw_log2) cells: short rows (128
+    // outputs of a 256-cell input row) would otherwise leave half the block idle
+    const int ow = (blockIdx.y << tw_log2) + (threadIdx.x & ((1 << tw_log2) - 1));
+    const long long row = (long long) blockIdx.x * (POOL_THREADS >> tw_log2) + (threadIdx.x >> tw_log2);
+    if (ow >= g.out[2] || row >= rows)
         return;
-    const int oh = blockIdx.x % g.out[1], od = blockIdx.x / g.out[1];
+    const int oh = (int) (row % g.out[1]), od = (int) (row / g.out[1]);
     const int c = blockIdx.z % g.c, n = blockIdx.z / g.c;
     const float* xp = x + (size_t) n * g.xs_n + (size_t) c * g.xs_c;
     const int d0 = od * s0_ - g.pad[0], h0 = oh * s1_ - g.pad[1], w0 = ow * s2_ - g.pad[2];
@@ -127,6 +130,104 @@ __global__ void __launch_bounds__(POOL_THREADS)
     const float r = g.mode == DCB_POOL_MAX ? m : s / fmaxf(pool_count(g, od, oh, ow), 1.f);
     float* yp = y + (size_t) n * g.ys_n + (size_t) c * g.ys_c + (size_t) od * g.ys[0] + (size_t) oh * g.ys[1] + ow;
     *yp = beta != 0.f ? alpha * r + beta * *yp : alpha * r;
+}
+
+// Forward for windows of 3 with stride 2 and pad 1 along W (and H; WD = 3 with stride 2
+// or 1 with stride 1 along D) on rows that start on 16-byte boundaries: a thread takes
+// two neighbouring outputs, i.e. input cells 4t-1 .. 4t+3 of every window row: one
+// 16-byte load and the left neighbour's last cell from a shuffle, where the one-output
+// kernel issues six scalar loads at every second cell.  Same scan order (D, H, W, first
+// maximum wins), same arithmetic.
+template <int WD>
+__global__ void __launch_bounds__(POOL_THREADS)
+    pool_fwd_w3s2_kernel(PoolGeom g, float alpha, float beta, const float* __restrict__ x, float* y,
+                         unsigned char* __restrict__ argmax, int tw_log2, long long rows)
+{
+    const int tq = (blockIdx.y << tw_log2) + (threadIdx.x & ((1 << tw_log2) - 1)); // pair of outputs
+    const long long row = (long long) blockIdx.x * (POOL_THREADS >> tw_log2) + (threadIdx.x >> tw_log2);
+    const bool live = 2 * tq < g.out[2] && row < rows; // dead lanes still take part in the shuffles
+    const int oh = (int) (row % g.out[1]), od = (int) (row / g.out[1]);
+    const int c = blockIdx.z % g.c, n = blockIdx.z / g.c;
+    const float* xp = x + (size_t) n * g.xs_n + (size_t) c * g.xs_c;
+    const int sd = WD == 1 ? 1 : 2;
+    const int d0 = od * sd - g.pad[0], h0 = oh * 2 - g.pad[1];
+    const int w4 = 4 * tq; // cells w4 - 1 .. w4 + 3
+    float m[2] = {-FLT_MAX, -FLT_MAX}, s[2] = {0.f, 0.f};
+    int best[2] = {-1, -1};
+    const int lane = threadIdx.x & 31;
+#pragma unroll
+    for (int kd = 0; kd < WD; ++kd)
+    {
+        const int id = d0 + kd;
+        const bool dok = live && id >= g.lo[0] && id < g.hi[0];
+#pragma unroll
+        for (int kh = 0; kh < 3; ++kh)
+        {
+            const int ih = h0 + kh;
+            const bool rok = dok && ih >= g.lo[1] && ih < g.hi[1];
+            float q[4] = {0.f, 0.f, 0.f, 0.f};
+            if (rok)
+            {
+                const float* rp = xp + (size_t) id * g.xs[0] + (size_t) ih * g.xs[1] + w4;
+                if (w4 + 3 < g.hi[2])
+                {
+                    const float4 t = __ldg(reinterpret_cast<const float4*>(rp));
+                    q[0] = t.x;
+                    q[1] = t.y;
+                    q[2] = t.z;
+                    q[3] = t.w;
+                }
+                else
+                {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+                        if (w4 + e < g.hi[2])
+                            q[e] = __ldg(rp + e);
+                }
+            }
+            // cell w4 - 1: the left neighbour's q[3] (same output row: a tile is 32 lanes or more)
+            float prev = __shfl_up_sync(0xffffffffu, q[3], 1);
+            if (lane == 0 && rok && w4 - 1 >= g.lo[2])
+                prev = __ldg(xp + (size_t) id * g.xs[0] + (size_t) ih * g.xs[1] + w4 - 1);
+            if (!rok)
+                continue;
+            const float v[5] = {prev, q[0], q[1], q[2], q[3]};
+            const int tap0 = (kd * 3 + kh) * 3;
+#pragma unroll
+            for (int o = 0; o < 2; ++o)
+#pragma unroll
+                for (int kw = 0; kw < 3; ++kw)
+                {
+                    const int cell = w4 - 1 + 2 * o + kw;
+                    if (cell < g.lo[2] || cell >= g.hi[2])
+                        continue;
+                    const float val = v[2 * o + kw];
+                    s[o] += val;
+                    if (best[o] < 0 || val > m[o])
+                    {
+                        m[o] = val;
+                        best[o] = tap0 + kw;
+                    }
+                }
+        }
+    }
+    if (!live)
+        return;
+#pragma unroll
+    for (int o = 0; o < 2; ++o)
+    {
+        const int ow = 2 * tq + o;
+        if (ow >= g.out[2])
+            continue;
+        if (argmax)
+            argmax[((((size_t) n * g.c + c) * g.out[0] + od) * g.out[1] + oh) * g.out[2] + ow] = (unsigned char) best[o];
+        if (!y)
+            continue;
+        const float r = g.mode == DCB_POOL_MAX ? m[o] : s[o] / fmaxf(pool_count(g, od, oh, ow), 1.f);
+        float* yp =
+            y + (size_t) n * g.ys_n + (size_t) c * g.ys_c + (size_t) od * g.ys[0] + (size_t) oh * g.ys[1] + ow;
+        *yp = beta != 0.f ? alpha * r + beta * *yp : alpha * r;
+    }
 }
 
 // The outputs whose window holds input coordinate i: o*stride - pad <= i < o*stride - pad + win.
@@ -386,15 +487,38 @@ bool pool_grid(int w, long long rows, long long planes, dim3* grid)
 int32_t launch_pool_fwd(const PoolGeom& g, float alpha, float beta, const float* x, float* y, unsigned char* argmax,
                         cudaStream_t stream)
 {
-    const long long tiles = (g.out[2] + POOL_TW - 1) / POOL_TW;
+    // the two-outputs-per-thread kernel: window 3, stride 2, pad 1 along W and H, the same or
+    // a unit slot along D, input rows on 16-byte boundaries
+    const bool flat = g.win[0] == 1 && g.stride[0] == 1;
+    const bool cube = g.win[0] == 3 && g.stride[0] == 2;
+    const bool pair = g.win[2] == 3 && g.stride[2] == 2 && g.pad[2] == 1 && g.win[1] == 3 && g.stride[1] == 2
+                      && (flat || cube) && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && g.xs[0] % 4 == 0
+                      && g.xs[1] % 4 == 0 && g.xs_c % 4 == 0 && g.xs_n % 4 == 0 && g.out[2] >= 2;
+    const int wcells = pair ? (g.out[2] + 1) / 2 : g.out[2]; // threads a row needs
+    int tw_log2 = 8; // threads of a row per block: 32, 64, 128 or 256
+    while (tw_log2 > 5 && (1 << (tw_log2 - 1)) >= wcells)
+        --tw_log2;
+    const long long tiles = (wcells + (1 << tw_log2) - 1) >> tw_log2;
     const long long rows = (long long) g.out[0] * g.out[1], planes = (long long) g.n * g.c;
-    if (rows > 0x7fffffffll || tiles > 65535 || planes > 65535)
+    const long long rpb = POOL_THREADS >> tw_log2;
+    const long long gx = (rows + rpb - 1) / rpb;
+    if (gx > 0x7fffffffll || tiles > 65535 || planes > 65535)
     {
         set_last_error("tensor too large for the pooling grid");
         return DCB_UNSUPPORTED;
     }
-    const dim3 grid((unsigned) rows, (unsigned) tiles, (unsigned) planes);
-#define DCB_POOL_CALL(WD, W, S) pool_fwd_kernel<WD, W, S><<<grid, POOL_THREADS, 0, stream>>>(g, alpha, beta, x, y, argmax)
+    const dim3 grid((unsigned) gx, (unsigned) tiles, (unsigned) planes);
+    if (pair)
+    {
+        if (cube)
+            pool_fwd_w3s2_kernel<3><<<grid, POOL_THREADS, 0, stream>>>(g, alpha, beta, x, y, argmax, tw_log2, rows);
+        else
+            pool_fwd_w3s2_kernel<1><<<grid, POOL_THREADS, 0, stream>>>(g, alpha, beta, x, y, argmax, tw_log2, rows);
+        DCB_LAUNCH_CHECK();
+        return DCB_OK;
+    }
+#define DCB_POOL_CALL(WD, W, S)                                                                                        \
+    pool_fwd_kernel<WD, W, S><<<grid, POOL_THREADS, 0, stream>>>(g, alpha, beta, x, y, argmax, tw_log2, rows)
     DCB_POOL_DISPATCH(g);
 #undef DCB_POOL_CALL
     DCB_LAUNCH_CHECK();
