@@ -1,7 +1,7 @@
 // Batch-normalisation kernels (and LeakyReLU): HBM-bound streaming kernels.
 //
 // Every (n, c) plane of an NC[D]HW window is a set of contiguous runs (see
-// RunGeom).  A "unit" is up to BN_UNIT_VECS vector elements of one run, or,
+// RunGeom).  A "unit" is up to 256 x (8 or 16) vector elements of one run, or,
 // where runs are short (the rows of a shard with halo cells along W, whose
 // pitch keeps them apart), several consecutive runs; blocks of channel c
 // (blockIdx.y) stride over that channel's units with 16-byte vector accesses
@@ -19,24 +19,30 @@ namespace dcb
 {
 
 constexpr int BN_THREADS = 256;
-constexpr int BN_UNROLL = 4;
-constexpr int BN_UNIT_VECS = BN_THREADS * BN_UNROLL; // vector elements per unit
+// Vector elements a thread has in flight per unit.  The streaming kernels (apply,
+// backward apply, LeakyReLU) want many: 16 x 16 bytes per thread measured 0.341 ms
+// for the 2 GiB of the bench layer's apply against 0.367 ms with 4; the reductions
+// hold accumulators beside the data and are fastest with 8 (0.155 / 0.304 ms against
+// 0.168 / 0.328 ms with 16).
+constexpr int BN_UNROLL_MAP = 16;
+constexpr int BN_UNROLL_RED = 8;
 
 struct UnitGeom
 {
     RunGeom g;
     long long upr;   // units per run (1 when runs are packed)
     long long upc;   // units per channel
-    int unit;        // scalars per unit = BN_UNIT_VECS * vector width
+    int unit;        // scalars per unit = 256 * unroll * vector width
     // Packed short runs: a unit is up to rpu consecutive runs of one outer step,
     // vpr vector elements each.  Unpacked: rpu = 1, vpr = 0, magic = 0.
     int rpu, vpr;
-    unsigned magic;  // ceil(2^32 / vpr): e / vpr = umulhi(e, magic) for the e < BN_UNIT_VECS used here
+    unsigned magic;  // ceil(2^32 / vpr): e / vpr = umulhi(e, magic) for the e < 4096 used here
     long long gpo;   // units per outer step
 };
 
-static UnitGeom make_units(const RunGeom& g, int vec)
+static UnitGeom make_units(const RunGeom& g, int vec, int unroll)
 {
+    const int BN_UNIT_VECS = BN_THREADS * unroll; // vector elements per unit
     UnitGeom u;
     u.g = g;
     u.unit = BN_UNIT_VECS * vec;
@@ -268,10 +274,10 @@ __global__ void __launch_bounds__(BN_THREADS)
         const UnitPos p = decode_unit(ug, u);
         const float* xp = x + unit_offset(xs, ug.g, p, c);
         const int nv = p.count / V;
-        Vec<V> v[BN_UNROLL];
-        bool on[BN_UNROLL];
+        Vec<V> v[BN_UNROLL_RED];
+        bool on[BN_UNROLL_RED];
 #pragma unroll
-        for (int k = 0; k < BN_UNROLL; ++k)
+        for (int k = 0; k < BN_UNROLL_RED; ++k)
         {
             const ElemPos ep = elem_pos<PACKED>(ug, p, threadIdx.x + k * BN_THREADS, nv);
             on[k] = ep.on;
@@ -280,7 +286,7 @@ __global__ void __launch_bounds__(BN_THREADS)
         }
         float s = 0.f, q = 0.f;
 #pragma unroll
-        for (int k = 0; k < BN_UNROLL; ++k)
+        for (int k = 0; k < BN_UNROLL_RED; ++k)
             if (on[k])
 #pragma unroll
                 for (int i = 0; i < V; ++i)
@@ -346,17 +352,17 @@ __global__ void __launch_bounds__(BN_THREADS)
         const float* xp = x + unit_offset(xs, ug.g, p, c);
         float* yp = y + unit_offset(ys, ug.g, p, c);
         const int nv = p.count / V;
-        Vec<V> v[BN_UNROLL];
-        ElemPos ep[BN_UNROLL];
+        Vec<V> v[BN_UNROLL_MAP];
+        ElemPos ep[BN_UNROLL_MAP];
 #pragma unroll
-        for (int k = 0; k < BN_UNROLL; ++k)
+        for (int k = 0; k < BN_UNROLL_MAP; ++k)
         {
             ep[k] = elem_pos<PACKED>(ug, p, threadIdx.x + k * BN_THREADS, nv);
             if (ep[k].on)
                 v[k].load(xp + ep[k].template off<V>(xs));
         }
 #pragma unroll
-        for (int k = 0; k < BN_UNROLL; ++k)
+        for (int k = 0; k < BN_UNROLL_MAP; ++k)
             if (ep[k].on)
             {
 #pragma unroll
@@ -394,10 +400,10 @@ __global__ void __launch_bounds__(BN_THREADS)
         const float* xp = x + unit_offset(xs, ug.g, p, c);
         const float* dp = dy + unit_offset(ds, ug.g, p, c);
         const int nv = p.count / V;
-        Vec<V> vx[BN_UNROLL], vd[BN_UNROLL];
-        bool on[BN_UNROLL];
+        Vec<V> vx[BN_UNROLL_RED], vd[BN_UNROLL_RED];
+        bool on[BN_UNROLL_RED];
 #pragma unroll
-        for (int k = 0; k < BN_UNROLL; ++k)
+        for (int k = 0; k < BN_UNROLL_RED; ++k)
         {
             const ElemPos ep = elem_pos<PACKED>(ug, p, threadIdx.x + k * BN_THREADS, nv);
             on[k] = ep.on;
@@ -409,7 +415,7 @@ __global__ void __launch_bounds__(BN_THREADS)
         }
         float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
-        for (int k = 0; k < BN_UNROLL; ++k)
+        for (int k = 0; k < BN_UNROLL_RED; ++k)
             if (on[k])
 #pragma unroll
                 for (int i = 0; i < V; ++i)
@@ -463,10 +469,10 @@ __global__ void __launch_bounds__(BN_THREADS)
         const float* dp = dy + unit_offset(ds, ug.g, p, c);
         float* op = dx + unit_offset(os, ug.g, p, c);
         const int nv = p.count / V;
-        Vec<V> vx[BN_UNROLL], vd[BN_UNROLL];
-        ElemPos ep[BN_UNROLL];
+        Vec<V> vx[BN_UNROLL_MAP], vd[BN_UNROLL_MAP];
+        ElemPos ep[BN_UNROLL_MAP];
 #pragma unroll
-        for (int k = 0; k < BN_UNROLL; ++k)
+        for (int k = 0; k < BN_UNROLL_MAP; ++k)
         {
             ep[k] = elem_pos<PACKED>(ug, p, threadIdx.x + k * BN_THREADS, nv);
             if (ep[k].on)
@@ -476,7 +482,7 @@ __global__ void __launch_bounds__(BN_THREADS)
             }
         }
 #pragma unroll
-        for (int k = 0; k < BN_UNROLL; ++k)
+        for (int k = 0; k < BN_UNROLL_MAP; ++k)
             if (ep[k].on)
             {
 #pragma unroll
@@ -509,7 +515,7 @@ __global__ void __launch_bounds__(BN_THREADS)
         float* op = out + unit_offset(os, ug.g, p, c);
         const int nv = p.count / V;
 #pragma unroll
-        for (int k = 0; k < BN_UNROLL; ++k)
+        for (int k = 0; k < BN_UNROLL_MAP; ++k)
         {
             const ElemPos ep = elem_pos<PACKED>(ug, p, threadIdx.x + k * BN_THREADS, nv);
             if (ep.on)
@@ -550,7 +556,7 @@ struct MultiView
 };
 
 static int32_t make_multi(const dcb_nd_desc* const* descs,
-                          const void* const* ptrs, int count, MultiView* mv)
+                          const void* const* ptrs, int count, MultiView* mv, int unroll)
 {
     int level = 2;
     for (int i = 0; i < count; ++i)
@@ -576,7 +582,7 @@ static int32_t make_multi(const dcb_nd_desc* const* descs,
         const int v = run_vec(g, mv->s[i], ptrs[i]);
         vec = v < vec ? v : vec;
     }
-    mv->ug = make_units(g, vec);
+    mv->ug = make_units(g, vec, unroll);
     mv->vec = vec;
     DCB_REQUIRE(g.c <= 65535, "too many channels");
     return DCB_OK;
@@ -675,7 +681,7 @@ int32_t dcb_bn_stats(dcb_bn_plan* plan, const void* x, void* sums,
     const dcb_nd_desc* descs[1] = {&plan->xd};
     const void* ptrs[1] = {x};
     MultiView mv;
-    int32_t st = make_multi(descs, ptrs, 1, &mv);
+    int32_t st = make_multi(descs, ptrs, 1, &mv, BN_UNROLL_RED);
     if (st != DCB_OK)
         return st;
     if (mv.ug.upc == 0)
@@ -719,7 +725,7 @@ static int32_t bn_apply_impl(const dcb_nd_desc* xd, const void* x, const void* m
     const dcb_nd_desc* descs[2] = {xd, yd};
     const void* ptrs[2] = {x, y};
     MultiView mv;
-    int32_t st = make_multi(descs, ptrs, 2, &mv);
+    int32_t st = make_multi(descs, ptrs, 2, &mv, BN_UNROLL_MAP);
     if (st != DCB_OK)
         return st;
     if (mv.ug.upc == 0)
@@ -772,7 +778,7 @@ int32_t dcb_bn_bwd_reduce(dcb_bn_plan* plan, const void* x,
     const dcb_nd_desc* descs[2] = {&plan->xd, dyd};
     const void* ptrs[2] = {x, dy};
     MultiView mv;
-    int32_t st = make_multi(descs, ptrs, 2, &mv);
+    int32_t st = make_multi(descs, ptrs, 2, &mv, BN_UNROLL_RED);
     if (st != DCB_OK)
         return st;
     if (mv.ug.upc == 0)
@@ -809,7 +815,7 @@ int32_t dcb_bn_bwd_apply(const dcb_nd_desc* xd, const void* x,
     const dcb_nd_desc* descs[3] = {xd, dyd, dxd};
     const void* ptrs[3] = {x, dy, dx};
     MultiView mv;
-    int32_t st = make_multi(descs, ptrs, 3, &mv);
+    int32_t st = make_multi(descs, ptrs, 3, &mv, BN_UNROLL_MAP);
     if (st != DCB_OK)
         return st;
     if (mv.ug.upc == 0)
@@ -835,7 +841,7 @@ int32_t dcb_leaky_relu_fwd(const dcb_nd_desc* xd, const void* x, float slope,
     const dcb_nd_desc* descs[2] = {xd, yd};
     const void* ptrs[2] = {x, y};
     MultiView mv;
-    int32_t st = make_multi(descs, ptrs, 2, &mv);
+    int32_t st = make_multi(descs, ptrs, 2, &mv, BN_UNROLL_MAP);
     if (st != DCB_OK)
         return st;
     if (mv.ug.upc == 0)
@@ -859,7 +865,7 @@ int32_t dcb_leaky_relu_bwd(const dcb_nd_desc* xd, const void* x,
     const dcb_nd_desc* descs[3] = {xd, dyd, dxd};
     const void* ptrs[3] = {x, dy, dx};
     MultiView mv;
-    int32_t st = make_multi(descs, ptrs, 3, &mv);
+    int32_t st = make_multi(descs, ptrs, 3, &mv, BN_UNROLL_MAP);
     if (st != DCB_OK)
         return st;
     if (mv.ug.upc == 0)
@@ -914,7 +920,7 @@ extern "C" int32_t dcb_bn_stats_noalloc(const dcb_nd_desc* xd, const void* x, vo
     const dcb_nd_desc* descs[1] = {xd};
     const void* ptrs[1] = {x};
     MultiView mv;
-    int32_t st = make_multi(descs, ptrs, 1, &mv);
+    int32_t st = make_multi(descs, ptrs, 1, &mv, BN_UNROLL_RED);
     if (st != DCB_OK)
         return st;
     if (xd->c < 1 || xd->c > NOALLOC_MAX_CHANNELS)
