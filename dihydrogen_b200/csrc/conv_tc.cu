@@ -409,7 +409,9 @@ bool mg_geom(const ConvGeom& cg, int math_mode, SwGeom* out)
     g.b_rot_bytes = g.kb * g.ntot * 4;
     g.b_bytes = g.cgroups * MG_SLOTS * g.b_rot_bytes;
     g.groups = TC_GROUPS_MAX;
-    g.a_slots = g.groups;
+    // two A slots per group, each with an issuer warp of its own, where tensor memory has
+    // the columns (DCB_MG_SLOTS=1: one, for measurements)
+    g.a_slots = g.groups * ((2 * g.groups * g.kr <= 192 && !(std::getenv("DCB_MG_SLOTS") && std::atoi(std::getenv("DCB_MG_SLOTS")) == 1)) ? 2 : 1);
     int th_max = ((int) TC_TMEM_COLS - g.a_slots * g.kr) / (g.nsets * MG_BLK);
     if (th_max + g.f[1] - 1 > 32)
         th_max = 32 - g.f[1] + 1;
@@ -1044,14 +1046,14 @@ static int32_t mg_launch(const SwGeom& g_in, float alpha, const float* w, const 
     {
         DCB_CUDA_TRY(cudaFuncSetAttribute(mg_conv_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           (int) (224 * 1024)));
-        mg_conv_kernel<true><<<(unsigned) grid, TC_THREADS, smem, stream>>>(g, alpha, bimg, y, status, xmap, ymap,
+        mg_conv_kernel<true><<<(unsigned) grid, MG_THREADS, smem, stream>>>(g, alpha, bimg, y, status, xmap, ymap,
                                                                            use_ymap);
     }
     else
     {
         DCB_CUDA_TRY(cudaFuncSetAttribute(mg_conv_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           (int) (224 * 1024)));
-        mg_conv_kernel<false><<<(unsigned) grid, TC_THREADS, smem, stream>>>(g, alpha, bimg, y, status, xmap, ymap,
+        mg_conv_kernel<false><<<(unsigned) grid, MG_THREADS, smem, stream>>>(g, alpha, bimg, y, status, xmap, ymap,
                                                                             use_ymap);
     }
     DCB_LAUNCH_CHECK();

@@ -35,6 +35,8 @@ namespace
 constexpr int MG_NBK = 4;   // filters per accumulator block
 constexpr int MG_SLOTS = 4; // plane slots per output row
 constexpr int MG_BLK = MG_NBK * MG_SLOTS;
+constexpr int MG_ISSUER2_WARP = TC_TMA_WARP + 1 + TC_EPI_WARPS; // second issuers: warps 24..26
+constexpr int MG_THREADS = (MG_ISSUER2_WARP + TC_GROUPS_MAX) * 32;
 
 __device__ __forceinline__ void tmem_ld4(uint32_t taddr, uint32_t (&v)[4])
 {
@@ -106,7 +108,7 @@ __global__ void mg_pack_filter_kernel(const float* __restrict__ w, float* __rest
 // Warps as in the sweep kernel: 0..11 converters, 12..14 issuers, 15 copies,
 // 16..23 epilogue.  TMEM columns: [nsets x accumulators th * 16][A ring].
 template <bool C4F3>
-__global__ void __launch_bounds__(TC_THREADS, 1)
+__global__ void __launch_bounds__(MG_THREADS, 1)
     mg_conv_kernel(SwGeom g, float alpha, const float* __restrict__ bimg, float* y, int* status,
                    const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap ymap, int use_ymap)
 {
@@ -160,7 +162,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     // k-row table for one channel group (the group's first channel is added per sub-row)
-    for (int r = tid; r < g.kr; r += TC_THREADS)
+    for (int r = tid; r < g.kr; r += MG_THREADS)
     {
         const int part = r / g.crows, rem = r % g.crows;
         const int c = rem / g.f[2], kw = rem % g.f[2];
@@ -168,7 +170,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         const uint32_t sel = part < (g.split ? 2 : 1) ? (uint32_t) part : 2u;
         ktab[r] = sel == 2u ? ((2u << 16) | 4u) : (off | (sel << 16));
     }
-    for (int i = tid; i < g.b_bytes / 16; i += TC_THREADS)
+    for (int i = tid; i < g.b_bytes / 16; i += MG_THREADS)
         reinterpret_cast<float4*>(b_smem)[i] = reinterpret_cast<const float4*>(bimg)[i];
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     tc_fence_before();
@@ -321,14 +323,17 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
             }
         }
     }
-    else if (warp >= TC_MMA_WARP && warp < TC_MMA_WARP + TC_GROUPS_MAX)
+    else if ((warp >= TC_MMA_WARP && warp < TC_MMA_WARP + TC_GROUPS_MAX) || warp >= MG_ISSUER2_WARP)
     {
         // ------------------------------------------------------------------
-        // MMA issue: issuer mq takes the sub-rows converter group mq produced.
-        // Lane i issues the sub-rows of staged row i.
+        // MMA issue: issuer (mq, mh) takes the sub-rows converter group mq wrote
+        // into its A slot mq + G * mh (a kernel whose staged row is four sub-rows
+        // of five instructions and two commits each is bound by what one thread
+        // can issue).  Lane i issues the sub-rows of staged row i.
         // ------------------------------------------------------------------
-        const int mq = warp - TC_MMA_WARP;
-        if (mq < G)
+        const int mq = warp < MG_ISSUER2_WARP ? warp - TC_MMA_WARP : warp - MG_ISSUER2_WARP;
+        const int mh = warp < MG_ISSUER2_WARP ? 0 : 1;
+        if (mq < G && mh < g.a_slots / G)
         {
             const int my_i = lane;
             const int j_lo = max(0, fh - 1 - my_i);
@@ -362,6 +367,17 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                         {
                             grp -= CG;
                             ++i;
+                        }
+                        // a real sub-row belongs to the issuer of the slot it was written to,
+                        // a virtual one (nothing to multiply) to the group's first issuer
+                        if (real ? (laps_a > 1 && lap_a != mh) : mh != 0)
+                        {
+                            if (real && ++lap_a == laps_a)
+                            {
+                                lap_a = 0;
+                                full_phase ^= 1;
+                            }
+                            continue;
                         }
                         // only output rows this row adds into may be waited for
                         const int r_hi = min(i, g.th - 1), r_lo = max(0, i - fh + 1);
@@ -416,7 +432,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
             }
         }
     }
-    else if (warp > TC_TMA_WARP)
+    else if (warp > TC_TMA_WARP && warp < MG_ISSUER2_WARP)
     {
         // ------------------------------------------------------------------
         // epilogue: after step d retire output plane d + pad - (fd-1)
