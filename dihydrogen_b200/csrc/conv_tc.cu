@@ -411,7 +411,13 @@ bool mg_geom(const ConvGeom& cg, int math_mode, SwGeom* out)
     g.groups = TC_GROUPS_MAX;
     // two A slots per group, each with an issuer warp of its own, where tensor memory has
     // the columns (DCB_MG_SLOTS=1: one, for measurements)
-    g.a_slots = g.groups * ((2 * g.groups * g.kr <= 192 && !(std::getenv("DCB_MG_SLOTS") && std::atoi(std::getenv("DCB_MG_SLOTS")) == 1)) ? 2 : 1);
+    {
+        int spg = 2 * g.groups * g.kr <= 192 ? 2 : 1;
+        const char* e = std::getenv("DCB_MG_SLOTS");
+        if (e && std::atoi(e) >= 1 && std::atoi(e) <= MG_IPG_MAX && std::atoi(e) * g.groups * g.kr <= 256)
+            spg = std::atoi(e);
+        g.a_slots = g.groups * spg;
+    }
     int th_max = ((int) TC_TMEM_COLS - g.a_slots * g.kr) / (g.nsets * MG_BLK);
     if (th_max + g.f[1] - 1 > 32)
         th_max = 32 - g.f[1] + 1;

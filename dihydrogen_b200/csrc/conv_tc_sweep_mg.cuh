@@ -36,7 +36,8 @@ constexpr int MG_NBK = 4;   // filters per accumulator block
 constexpr int MG_SLOTS = 4; // plane slots per output row
 constexpr int MG_BLK = MG_NBK * MG_SLOTS;
 constexpr int MG_ISSUER2_WARP = TC_TMA_WARP + 1 + TC_EPI_WARPS; // second issuers: warps 24..26
-constexpr int MG_THREADS = (MG_ISSUER2_WARP + TC_GROUPS_MAX) * 32;
+constexpr int MG_IPG_MAX = 2; // issuers (= A slots) per converter group at most
+constexpr int MG_THREADS = (MG_ISSUER2_WARP + (MG_IPG_MAX - 1) * TC_GROUPS_MAX) * 32;
 
 __device__ __forceinline__ void tmem_ld4(uint32_t taddr, uint32_t (&v)[4])
 {
@@ -331,8 +332,8 @@ __global__ void __launch_bounds__(MG_THREADS, 1)
         // of five instructions and two commits each is bound by what one thread
         // can issue).  Lane i issues the sub-rows of staged row i.
         // ------------------------------------------------------------------
-        const int mq = warp < MG_ISSUER2_WARP ? warp - TC_MMA_WARP : warp - MG_ISSUER2_WARP;
-        const int mh = warp < MG_ISSUER2_WARP ? 0 : 1;
+        const int mq = warp < MG_ISSUER2_WARP ? warp - TC_MMA_WARP : (warp - MG_ISSUER2_WARP) % TC_GROUPS_MAX;
+        const int mh = warp < MG_ISSUER2_WARP ? 0 : 1 + (warp - MG_ISSUER2_WARP) / TC_GROUPS_MAX;
         if (mq < G && mh < g.a_slots / G)
         {
             const int my_i = lane;
