@@ -186,7 +186,7 @@ int sw_epi_warps()
 size_t sw_smem_need(const SwGeom& g)
 {
     return (size_t) (g.b_bytes + 127) / 128 * 128 + (size_t) g.raw_slots * g.raw_slot_bytes
-           + (size_t) ((g.kr + 1) & ~1) * 4 + (size_t) (2 * g.a_slots + 64 + 2 * g.raw_slots) * 8 + 64 + 128
+           + (size_t) ((g.kr + 1) & ~1) * 4 + (size_t) (2 * g.a_slots + 64 + 2 * g.raw_slots + TC_GROUPS_MAX) * 8 + 64 + 128
            + (size_t) 12 * 2 * SW_NBK * 32 * 4 + 1024; // staging for up to 12 epilogue warps
 }
 
@@ -306,6 +306,11 @@ bool sw_geom(const ConvGeom& cg, int math_mode, SwGeom* out)
     g.th = best_th;
     g.nseg = best_ns;
     g.rows = g.th + g.f[1] - 1;
+    // Two A slots per group (and with them a second issuer per group in the plain
+    // kernel) where the chosen column height leaves the tensor-memory columns for them.
+    if (!std::getenv("DCB_SW_SLOTS") && 2 * g.groups * g.kr <= 256
+        && 2 * g.groups * g.kr + g.th * g.f[0] * SW_NBK <= (int) TC_TMEM_COLS)
+        g.a_slots = 2 * g.groups;
     // chunks of about 17 KiB, evenly sized
     const int row_bytes = g.c * TC_RAW_W * 4;
     int rc_max = (17 * 1024 + 512) / row_bytes;
@@ -335,7 +340,7 @@ bool sw_geom(const ConvGeom& cg, int math_mode, SwGeom* out)
 size_t mg_smem_need(const SwGeom& g)
 {
     return (size_t) (g.b_bytes + 127) / 128 * 128 + (size_t) g.raw_slots * g.raw_slot_bytes
-           + (size_t) ((g.kr + 1) & ~1) * 4 + (size_t) (2 * g.a_slots + 64 + 2 * g.raw_slots) * 8 + 64 + 128
+           + (size_t) ((g.kr + 1) & ~1) * 4 + (size_t) (2 * g.a_slots + 64 + 2 * g.raw_slots + TC_GROUPS_MAX) * 8 + 64 + 128
            + (size_t) TC_EPI_WARPS * 2 * MG_NBK * 32 * 4 + 1024;
 }
 
@@ -905,23 +910,30 @@ static int32_t sw_launch(const SwGeom& g_in, float alpha, const float* w, const 
         DCB_CUDA_TRY(cudaMemsetAsync(prof, 0, prof_n * sizeof(long long), stream));
     }
 #endif
-    auto launch = [&](auto kernel) -> int32_t {
+    const bool blend = beta != 0.f;
+    // second issuers (and the second A slot of every group) for the plain variant only
+    const bool xiss = !stats && !blend && g.a_slots == 2 * g.groups;
+    if (!xiss)
+        g.a_slots = g.groups;
+    auto launch = [&](auto kernel, int xi) -> int32_t {
         DCB_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) (224 * 1024)));
-        kernel<<<(unsigned) grid, sw_threads(epi), smem, stream>>>(g, alpha, beta, bimg, y, status, map, ymap, use_ymap,
-                                                                   stat_part, prof);
+        kernel<<<(unsigned) grid, sw_threads(epi, xi), smem, stream>>>(g, alpha, beta, bimg, y, status, map, ymap,
+                                                                       use_ymap, stat_part, prof);
         return DCB_OK;
     };
-    const bool blend = beta != 0.f;
     int32_t st;
 #define DCB_SW_PICK(EPI)                                                                                              \
-    if (c4f3)                                                                                                         \
-        st = stats ? launch(sw_conv_kernel<true, true, false, EPI>)                                                   \
-                   : (blend ? launch(sw_conv_kernel<true, false, true, EPI>)                                          \
-                            : launch(sw_conv_kernel<true, false, false, EPI>));                                       \
+    if (xiss)                                                                                                         \
+        st = c4f3 ? launch(sw_conv_kernel<true, false, false, EPI, 1>, 1)                                             \
+                  : launch(sw_conv_kernel<false, false, false, EPI, 1>, 1);                                           \
+    else if (c4f3)                                                                                                    \
+        st = stats ? launch(sw_conv_kernel<true, true, false, EPI, 0>, 0)                                             \
+                   : (blend ? launch(sw_conv_kernel<true, false, true, EPI, 0>, 0)                                    \
+                            : launch(sw_conv_kernel<true, false, false, EPI, 0>, 0));                                 \
     else                                                                                                              \
-        st = stats ? launch(sw_conv_kernel<false, true, false, EPI>)                                                  \
-                   : (blend ? launch(sw_conv_kernel<false, false, true, EPI>)                                         \
-                            : launch(sw_conv_kernel<false, false, false, EPI>));
+        st = stats ? launch(sw_conv_kernel<false, true, false, EPI, 0>, 0)                                            \
+                   : (blend ? launch(sw_conv_kernel<false, false, true, EPI, 0>, 0)                                   \
+                            : launch(sw_conv_kernel<false, false, false, EPI, 0>, 0));
     if (epi == 12)
     {
         DCB_SW_PICK(12)

@@ -326,13 +326,22 @@ __device__ __forceinline__ void sw_convert_c4f3(uint32_t raw_lane, uint32_t pitc
 // in retirement at once, the shorter the step.
 // Warps: converters 0..11, issuers 12..14, the copy warp 15, epilogue 16..16+EPI-1
 // (warp & 3 is the TMEM quadrant).
-__host__ __device__ constexpr int sw_threads(int epi)
+// XISS: the last TC_GROUPS_MAX warps are second issuers.  With two A slots per
+// converter group, issuer (q, 0) takes the group's rows that land in its first slot
+// and issuer (q, 1) those in the second.  Free-running, the three issuers of the
+// plain kernel need as long as its busiest epilogue warps (0.35 ms on the 256^3
+// shard, ~140 clocks per tcgen05.mma or commit, seven per staged row); with six the
+// kernel takes 0.378 ms instead of 0.433.  The variants whose epilogue does more
+// (statistics, blend) are held by their epilogue warps and by registers (the extra
+// warps lower the cap to 66 per thread, their epilogues then spill): they keep
+// three issuers and one slot per group.
+__host__ __device__ constexpr int sw_threads(int epi, int xiss)
 {
-    return (TC_TMA_WARP + 1 + epi) * 32;
+    return (TC_TMA_WARP + 1 + epi + (xiss ? TC_GROUPS_MAX : 0)) * 32;
 }
 
-template <bool C4F3, bool STATS, bool BLEND, int EPI>
-__global__ void __launch_bounds__(sw_threads(EPI), 1)
+template <bool C4F3, bool STATS, bool BLEND, int EPI, int XISS>
+__global__ void __launch_bounds__(sw_threads(EPI, XISS), 1)
     sw_conv_kernel(SwGeom g, float alpha, float beta, const float* __restrict__ bimg, float* y, int* status,
                    const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap ymap, int use_ymap,
                    float* __restrict__ stat_part, long long* prof)
@@ -350,7 +359,8 @@ __global__ void __launch_bounds__(sw_threads(EPI), 1)
     uint64_t* row_free = row_done + 32;             // [32]
     uint64_t* raw_full = row_free + 32;             // [raw_slots]
     uint64_t* raw_empty = raw_full + g.raw_slots;   // [raw_slots]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(raw_empty + g.raw_slots);
+    uint64_t* iss_sync = raw_empty + g.raw_slots;   // [TC_GROUPS_MAX] the issuers of a group, once per step
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(iss_sync + TC_GROUPS_MAX);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     // output staging for bulk stores: two 2 KiB buffers per epilogue warp
     float* stage_base = reinterpret_cast<float*>(
@@ -379,6 +389,8 @@ __global__ void __launch_bounds__(sw_threads(EPI), 1)
             mbar_init(&raw_full[r], 1);
             mbar_init(&raw_empty[r], 4 * g.groups);
         }
+        for (int q = 0; q < TC_GROUPS_MAX; ++q)
+            mbar_init(&iss_sync[q], g.a_slots / g.groups);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -391,7 +403,7 @@ __global__ void __launch_bounds__(sw_threads(EPI), 1)
     }
     // k-row table: offset of the tap inside a raw chunk row, and what the row
     // carries: 0 hi part, 1 lo part, 2 zero
-    for (int r = tid; r < g.kr; r += sw_threads(EPI))
+    for (int r = tid; r < g.kr; r += sw_threads(EPI, XISS))
     {
         const int part = r / g.crows, rem = r % g.crows;
         const int c = rem / g.f[2], kw = rem % g.f[2];
@@ -399,7 +411,7 @@ __global__ void __launch_bounds__(sw_threads(EPI), 1)
         const uint32_t sel = part < (g.split ? 2 : 1) ? (uint32_t) part : 2u;
         ktab[r] = sel == 2u ? ((2u << 16) | 4u) : (off | (sel << 16));
     }
-    for (int i = tid; i < g.b_bytes / 16; i += sw_threads(EPI))
+    for (int i = tid; i < g.b_bytes / 16; i += sw_threads(EPI, XISS))
         reinterpret_cast<float4*>(b_smem)[i] = reinterpret_cast<const float4*>(bimg)[i];
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     tc_fence_before();
@@ -574,14 +586,16 @@ __global__ void __launch_bounds__(sw_threads(EPI), 1)
         }
         SW_PROF_FLUSH(prof)
     }
-    else if (warp >= TC_MMA_WARP && warp < TC_TMA_WARP)
+    else if ((warp >= TC_MMA_WARP && warp < TC_TMA_WARP) || (XISS && warp >= TC_TMA_WARP + 1 + EPI))
     {
         // ------------------------------------------------------------------
-        // MMA issue: issuer mq takes the rows converter group mq produced.
-        // Lane i issues staged row i (its descriptors depend on i only).
+        // MMA issue: issuer (mq, mh) takes the rows converter group mq wrote into
+        // its A slot mq + G * mh.  Lane i issues staged row i (its descriptors
+        // depend on i only).
         // ------------------------------------------------------------------
-        const int mq = warp - TC_MMA_WARP;
-        if (mq < G)
+        const int mq = warp < TC_TMA_WARP ? warp - TC_MMA_WARP : warp - (TC_TMA_WARP + 1 + EPI);
+        const int mh = warp < TC_TMA_WARP ? 0 : 1;
+        if (mq < G && mh < g.a_slots / G)
         {
             const int my_i = lane;
             const int j_lo = max(0, fh - 1 - my_i);
@@ -618,11 +632,30 @@ __global__ void __launch_bounds__(sw_threads(EPI), 1)
                 rot = sw_mod(t.d_first, fd);
                 for (int d = t.d_first; d < t.d_stop && ok; ++d, ++step, rot = rot + 1 == fd ? 0 : rot + 1)
                 {
+                    // The issuers of a group stay within one step of each other: the second
+                    // one skips the rows it does not own without a wait (virtual steps
+                    // entirely), and a parity wait cannot tell a barrier two completions
+                    // away.  The first issuer waits for every row's hand-back in every step,
+                    // so once both have finished a step the barriers this group looks at are
+                    // at most one completion behind what either expects next.
+                    if (laps_a > 1 && step != 0)
+                        ok = mbar_wait_t<0>(&iss_sync[mq], (step - 1) & 1, abort_flag);
                     const bool real = sw_real(g, t, d);
                     const uint32_t par = step & 1;
                     const uint64_t bd0 = my_b_desc + (uint64_t) ((uint32_t) rot * rot_units);
                     for (int i = my_lo; i < my_hi && ok; ++i)
                     {
+                        // a real row belongs to the issuer of the slot it was written to,
+                        // a virtual one (nothing to multiply) to the group's first issuer
+                        if (real ? (laps_a > 1 && lap_a != mh) : mh != 0)
+                        {
+                            if (real && ++lap_a == laps_a)
+                            {
+                                lap_a = 0;
+                                full_phase ^= 1;
+                            }
+                            continue;
+                        }
                         // The blocks this row adds into (output rows r_lo..r_hi) must
                         // have been retired.  Each epilogue warp of a quadrant retires
                         // its rows in ascending order, so the top EPI / 4 rows (one per
@@ -694,12 +727,18 @@ __global__ void __launch_bounds__(sw_threads(EPI), 1)
                             __syncwarp();
                         }
                     }
+                    if (laps_a > 1)
+                    {
+                        __syncwarp();
+                        if (lane == 0)
+                            mbar_arrive(&iss_sync[mq]);
+                    }
                 }
             }
             SW_PROF_FLUSH(prof)
         }
     }
-    else if (warp >= (TC_TMA_WARP + 1))
+    else if (warp >= (TC_TMA_WARP + 1) && warp < TC_TMA_WARP + 1 + EPI)
     {
         // ------------------------------------------------------------------
         // epilogue: after step d retire output plane d + pad - (fd-1)

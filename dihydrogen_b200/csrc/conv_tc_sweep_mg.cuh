@@ -126,7 +126,8 @@ __global__ void __launch_bounds__(MG_THREADS, 1)
     uint64_t* row_free = row_done + 32;           // [32]
     uint64_t* raw_full = row_free + 32;           // [raw_slots]
     uint64_t* raw_empty = raw_full + g.raw_slots; // [raw_slots]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(raw_empty + g.raw_slots);
+    uint64_t* iss_sync = raw_empty + g.raw_slots; // [TC_GROUPS_MAX] the issuers of a group, once per step
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(iss_sync + TC_GROUPS_MAX);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     // output staging for bulk stores: two 512-byte buffers per epilogue warp
     float* stage_base = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(tmem_slot + 2) + 127) & ~uintptr_t(127));
@@ -152,6 +153,8 @@ __global__ void __launch_bounds__(MG_THREADS, 1)
             mbar_init(&raw_full[r], 1);
             mbar_init(&raw_empty[r], 4 * g.groups);
         }
+        for (int q = 0; q < TC_GROUPS_MAX; ++q)
+            mbar_init(&iss_sync[q], g.a_slots / g.groups);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -357,6 +360,14 @@ __global__ void __launch_bounds__(MG_THREADS, 1)
                 const SwUnit t = sw_unit(g, u);
                 for (int d = t.d_first; d < t.d_stop && ok; ++d, ++step)
                 {
+                    // The issuers of a group stay within one step of each other: the second
+                    // one skips the rows it does not own without a wait (virtual steps
+                    // entirely), and a parity wait cannot tell a barrier two completions
+                    // away.  The first issuer waits for every row's hand-back in every step,
+                    // so once both have finished a step the barriers this group looks at are
+                    // at most one completion behind what either expects next.
+                    if (laps_a > 1 && step != 0)
+                        ok = mbar_wait_t<0>(&iss_sync[mq], (step - 1) & 1, abort_flag);
                     const bool real = sw_real(g, t, d);
                     const uint32_t par = step & 1;
                     const uint32_t rot = (uint32_t) (d & (MG_SLOTS - 1));
@@ -429,6 +440,12 @@ __global__ void __launch_bounds__(MG_THREADS, 1)
                     }
                     if (real)
                         base = (base + (uint32_t) subrows) % (uint32_t) G;
+                    if (laps_a > 1)
+                    {
+                        __syncwarp();
+                        if (lane == 0)
+                            mbar_arrive(&iss_sync[mq]);
+                    }
                 }
             }
         }
