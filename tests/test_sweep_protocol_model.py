@@ -18,7 +18,7 @@ import random
 import pytest
 
 
-def simulate(groups, th, fh, steps, seed, virtual, wait_rows, cg=1, nhalf=2, blocked=False):
+def simulate(groups, th, fh, steps, seed, virtual, wait_rows, cg=1, nhalf=2, blocked=False, ipg=1, sync=True):
     """Returns ("ok" | "deadlock", wrong_passes).  cg > 1: the multi-group
     kernel, where row i is cg sub-rows dealt to the issuers in sequence and
     row_done[i] needs all of them."""
@@ -64,6 +64,37 @@ def simulate(groups, th, fh, steps, seed, virtual, wait_rows, cg=1, nhalf=2, blo
                 yield "work"
                 arrive(("done", i))
 
+    iss_done = [[0] * ipg for _ in range(groups)]  # steps finished by issuer (mq, mh)
+
+    def issuer_blocked_pair(mq, mh):
+        # the sweep kernel with two A slots per group: issuer (mq, mh) owns the group's real
+        # rows whose slot is mh (a running count), the first issuer all virtual ones; the
+        # issuers of a group start a step only when all of them have finished the one before
+        rpg = -(-rows // groups)
+        lap = 0
+        for step in range(steps):
+            if sync and step > 0:
+                while min(iss_done[mq]) < step:
+                    yield "wait"
+            parity, real = step & 1, step not in virtual
+            for i in range(mq * rpg, min(rows, (mq + 1) * rpg)):
+                mine = (lap == mh) if real else (mh == 0)
+                if real:
+                    lap = (lap + 1) % ipg
+                if not mine:
+                    continue
+                for j in wait_rows(i, th, fh):
+                    while not passes(("free", j), parity):
+                        yield "wait"
+                    if completions[("free", j)] != step + 1:
+                        wrong.append(("issuer", mq, mh, step, i, j))
+                for j in range(max(0, i - fh + 1), min(i, th - 1) + 1):
+                    if completions[("free", j)] < step + 1:
+                        wrong.append(("issuer adds into an unretired row", mq, mh, step, i, j))
+                yield "work"
+                arrive(("done", i))
+            iss_done[mq][mh] = step + 1
+
     def issuer(mq):
         base = 0
         for step in range(steps):
@@ -99,7 +130,11 @@ def simulate(groups, th, fh, steps, seed, virtual, wait_rows, cg=1, nhalf=2, blo
                 yield "work"
                 arrive(("free", j))
 
-    threads = [(issuer_blocked if blocked else issuer)(m) for m in range(groups)] + [epilogue(h) for h in range(nhalf)]
+    if ipg > 1:
+        threads = [issuer_blocked_pair(m, h) for m in range(groups) for h in range(ipg)]
+    else:
+        threads = [(issuer_blocked if blocked else issuer)(m) for m in range(groups)]
+    threads += [epilogue(h) for h in range(nhalf)]
     alive = [True] * len(threads)
     idle = 0
     while any(alive):
@@ -149,6 +184,25 @@ def test_protocol_with_rows_dealt_in_blocks(nhalf):
                     state, wrong = simulate(groups, th, fh, 10, seed, (), lambda i, t, f: touched_rows(i, t, f, nhalf),
                                             nhalf=nhalf, blocked=True)
                     assert state == "ok" and not wrong, (nhalf, fh, groups, th, seed, state, wrong[:2])
+
+
+@pytest.mark.parametrize("nhalf", [2, 3])
+def test_protocol_with_two_issuers_per_group(nhalf):
+    """Two A slots and two issuer warps per converter group: the second issuer
+    skips the rows it does not own, virtual steps entirely, so the issuers of a
+    group wait for each other once per step; without that wait a parity wait
+    can look at a barrier two completions early (the model must see that too)."""
+    for fh in (1, 2, 3, 5):
+        for groups in range(1, min(fh, 3) + 1):
+            for th in range(2, 12):
+                for seed in range(6):
+                    virtual = (0, 1, 8, 9) if seed % 2 else (0, 5, 6, 11)
+                    state, wrong = simulate(groups, th, fh, 12, seed, virtual,
+                                            lambda i, t, f: touched_rows(i, t, f, nhalf), nhalf=nhalf, ipg=2)
+                    assert state == "ok" and not wrong, (nhalf, fh, groups, th, seed, state, wrong[:2])
+    bad = [simulate(3, 7, 3, 12, seed, (0, 1, 5, 6, 7, 8), lambda i, t, f: touched_rows(i, t, f, 3), nhalf=3, ipg=2,
+                    sync=False) for seed in range(30)]
+    assert any(state != "ok" or wrong for state, wrong in bad)
 
 
 @pytest.mark.parametrize("nhalf", [3, 4])
