@@ -286,8 +286,12 @@ bool sw_geom(const ConvGeom& cg, int math_mode, SwGeom* out)
     const int sms = num_sms();
     long long best_cost = -1;
     int best_th = th_max, best_ns = 1;
+    // measurement knob: a fixed column height
+    const int th_forced = std::getenv("DCB_SW_TH") ? std::atoi(std::getenv("DCB_SW_TH")) : 0;
     for (int th = th_max; th >= 2 && th >= th_max - 3; --th)
     {
+        if (th_forced >= 2 && th_forced <= th_max && th != th_forced)
+            continue;
         const long long cols = (long long) g.n * ((g.out[2] + TC_M - 1) / TC_M) * ((g.out[1] + th - 1) / th);
         for (int ns = 1; ns <= g.out[0] && ns <= 64; ++ns)
         {
