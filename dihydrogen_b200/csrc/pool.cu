@@ -65,6 +65,23 @@ __device__ __forceinline__ float pool_count(const PoolGeom& g, int od, int oh, i
     return (float) cnt;
 }
 
+// row = plane * extent + line, with the 32-bit division when the row count allows it
+// (the 64-bit one is a subroutine of a hundred instructions)
+__device__ __forceinline__ void pool_split_row(long long row, long long rows, int extent, int* plane, int* line)
+{
+    if (rows <= 0x7fffffffll)
+    {
+        const unsigned r = (unsigned) row, e = (unsigned) extent;
+        *plane = (int) (r / e);
+        *line = (int) (r - (r / e) * e);
+    }
+    else
+    {
+        *plane = (int) (row / extent);
+        *line = (int) (row % extent);
+    }
+}
+
 // Forward: one thread per output cell, the window scanned in D, H, W order.
 // `argmax`, if given, receives the tap index kd * fh * fw + kh * fw + kw of the
 // first maximum (dense [n][c][od][oh][ow]); y may then be null.
@@ -146,7 +163,8 @@ __global__ void __launch_bounds__(POOL_THREADS)
     const int tq = (blockIdx.y << tw_log2) + (threadIdx.x & ((1 << tw_log2) - 1)); // pair of outputs
     const long long row = (long long) blockIdx.x * (POOL_THREADS >> tw_log2) + (threadIdx.x >> tw_log2);
     const bool live = 2 * tq < g.out[2] && row < rows; // dead lanes still take part in the shuffles
-    const int oh = (int) (row % g.out[1]), od = (int) (row / g.out[1]);
+    int oh, od;
+    pool_split_row(row, rows, g.out[1], &od, &oh);
     const int c = blockIdx.z % g.c, n = blockIdx.z / g.c;
     const float* xp = x + (size_t) n * g.xs_n + (size_t) c * g.xs_c;
     const int sd = WD == 1 ? 1 : 2;
@@ -402,6 +420,97 @@ __global__ void __launch_bounds__(POOL_THREADS)
     }
 }
 
+// The same for windows of 3 with stride 2 and pad 1 along W (3 / stride 2 along H; WD = 3
+// with stride 2 or 1 with stride 1 along D) and an even output row: cells 4t .. 4t+3 lie
+// in the windows of outputs 2t, 2t+1 and 2t+2 only, so a thread loads two index bytes
+// and two gradients in one access each and takes the third pair from its right-hand
+// neighbour's registers; short rows share a block as in the forward kernel.  The sums
+// run in the same order (D, H, then W ascending) as in the kernel above: same bits.
+template <int WD>
+__global__ void __launch_bounds__(POOL_THREADS)
+    pool_bwd_index_w3s2_kernel(PoolGeom g, float alpha, float beta, const float* __restrict__ dy, float* dx,
+                               const unsigned char* __restrict__ argmax, int tw_log2, long long rows)
+{
+    const int t = (blockIdx.y << tw_log2) + (threadIdx.x & ((1 << tw_log2) - 1));
+    const long long row = (long long) blockIdx.x * (POOL_THREADS >> tw_log2) + (threadIdx.x >> tw_log2);
+    if (row >= rows) // a warp never spans two rows: the whole warp leaves
+        return;
+    const int iw0 = 4 * t, ow0 = 2 * t;
+    int ih, id;
+    pool_split_row(row, rows, g.in[1], &id, &ih);
+    const int c = blockIdx.z % g.c, n = blockIdx.z / g.c;
+    const int sd = WD == 1 ? 1 : 2;
+    int dlo, dhi, hlo, hhi;
+    pool_cover(id, sd, g.pad[0], WD, g.out[0], &dlo, &dhi);
+    pool_cover(ih, 2, g.pad[1], 3, g.out[1], &hlo, &hhi);
+    if (id < g.lo[0] || id >= g.hi[0] || ih < g.lo[1] || ih >= g.hi[1])
+        dhi = dlo - 1; // a row outside the global tensor is padding
+    const int lane = threadIdx.x & 31;
+    const size_t plane = ((size_t) n * g.c + c) * g.out[0];
+    const float* dyp = dy + (size_t) n * g.ys_n + (size_t) c * g.ys_c;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    const bool two = ow0 + 1 < g.out[2], third = ow0 + 2 < g.out[2];
+    for (int od = dlo; od <= dhi; ++od)
+    {
+        // pointers and tap base of window row (od, hlo), moved on by one output row per turn
+        const unsigned char* arow = argmax + ((plane + od) * g.out[1] + hlo) * g.out[2] + ow0;
+        const float* dyrow = dyp + (size_t) od * g.ys[0] + (size_t) hlo * g.ys[1] + ow0;
+        // tap of window (od, oh, ow) at cell i: tb + i - (2 ow - 1)
+        int tb = ((id - (od * sd - g.pad[0])) * 3 + (ih - (hlo * 2 - g.pad[1]))) * 3;
+        for (int oh = hlo; oh <= hhi; ++oh, arow += g.out[2], dyrow += g.ys[1], tb -= 6)
+        {
+            // 255 is the index pass's "empty window" and never a tap
+            int a0 = 255, a1 = 255, a2;
+            float d0 = 0.f, d1 = 0.f, d2;
+            if (two)
+            {
+                const uchar2 a = __ldg(reinterpret_cast<const uchar2*>(arow));
+                const float2 d = __ldg(reinterpret_cast<const float2*>(dyrow));
+                a0 = a.x;
+                a1 = a.y;
+                d0 = d.x;
+                d1 = d.y;
+            }
+            a2 = __shfl_down_sync(0xffffffffu, a0, 1);
+            d2 = __shfl_down_sync(0xffffffffu, d0, 1);
+            if (lane == 31)
+            {
+                a2 = third ? (int) __ldg(arow + 2) : 255;
+                d2 = third ? __ldg(dyrow + 2) : 0.f;
+            }
+            acc[0] += a0 == tb + 1 ? d0 : 0.f;
+            acc[1] += a0 == tb + 2 ? d0 : 0.f;
+            acc[1] += a1 == tb ? d1 : 0.f;
+            acc[2] += a1 == tb + 1 ? d1 : 0.f;
+            acc[3] += a1 == tb + 2 ? d1 : 0.f;
+            acc[3] += a2 == tb ? d2 : 0.f;
+        }
+    }
+    if (iw0 >= g.in[2])
+        return;
+    float* xp = dx + (size_t) n * g.xs_n + (size_t) c * g.xs_c + (size_t) id * g.xs[0] + (size_t) ih * g.xs[1] + iw0;
+    if (iw0 + 4 <= g.in[2] && (reinterpret_cast<uintptr_t>(xp) & 15) == 0)
+    {
+        float4 o = make_float4(alpha * acc[0], alpha * acc[1], alpha * acc[2], alpha * acc[3]);
+        if (beta != 0.f)
+        {
+            const float4 old = *reinterpret_cast<const float4*>(xp);
+            o.x += beta * old.x;
+            o.y += beta * old.y;
+            o.z += beta * old.z;
+            o.w += beta * old.w;
+        }
+        *reinterpret_cast<float4*>(xp) = o;
+    }
+    else
+    {
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+            if (iw0 + e < g.in[2])
+                xp[e] = beta != 0.f ? alpha * acc[e] + beta * xp[e] : alpha * acc[e];
+    }
+}
+
 int32_t pool_geom(const dcb_pool_desc* pd, const dcb_nd_desc* xd, const dcb_nd_desc* yd, PoolGeom* g)
 {
     DCB_REQUIRE(pd && xd && yd, "null descriptor");
@@ -586,6 +695,35 @@ extern "C" int32_t dcb_pool_bwd(const dcb_pool_desc* pd, const dcb_nd_desc* xd, 
         if (st2 != DCB_OK)
             return st2;
         idx = static_cast<const unsigned char*>(workspace);
+    }
+    const bool flat = g.win[0] == 1 && g.stride[0] == 1;
+    const bool cube = g.win[0] == 3 && g.stride[0] == 2;
+    const bool even = g.ys[0] % 2 == 0 && g.ys[1] % 2 == 0 && g.ys_c % 2 == 0 && g.ys_n % 2 == 0 && g.out[2] % 2 == 0
+                      && (reinterpret_cast<uintptr_t>(dy) & 7) == 0 && (reinterpret_cast<uintptr_t>(idx) & 1) == 0;
+    if (idx && g.win[2] == 3 && g.stride[2] == 2 && g.pad[2] == 1 && g.win[1] == 3 && g.stride[1] == 2
+        && (flat || cube) && even)
+    {
+        const int wcells = (g.in[2] + 3) / 4; // threads a row needs
+        int tw_log2 = 8;
+        while (tw_log2 > 5 && (1 << (tw_log2 - 1)) >= wcells)
+            --tw_log2;
+        const long long tiles = (wcells + (1 << tw_log2) - 1) >> tw_log2;
+        const long long rows = (long long) g.in[0] * g.in[1], rpb = POOL_THREADS >> tw_log2;
+        const long long gx = (rows + rpb - 1) / rpb;
+        if (gx <= 0x7fffffffll && tiles <= 65535)
+        {
+            const dim3 gridp((unsigned) gx, (unsigned) tiles, grid.z);
+            if (cube)
+                pool_bwd_index_w3s2_kernel<3><<<gridp, POOL_THREADS, 0, as_stream(stream)>>>(
+                    g, (float) alpha, (float) beta, static_cast<const float*>(dy), static_cast<float*>(dx), idx,
+                    tw_log2, rows);
+            else
+                pool_bwd_index_w3s2_kernel<1><<<gridp, POOL_THREADS, 0, as_stream(stream)>>>(
+                    g, (float) alpha, (float) beta, static_cast<const float*>(dy), static_cast<float*>(dx), idx,
+                    tw_log2, rows);
+            DCB_LAUNCH_CHECK();
+            return DCB_OK;
+        }
     }
     if (idx)
     {

@@ -26,6 +26,10 @@ CASES = [
     (1, 2, (9, 300), (3, 3), (0, 0), (1, 1)),
     (1, 1, (4, 6, 520), (2, 2, 2), (0, 0, 0), (2, 2, 2)),
     (1, 2, (11, 13), (5, 5), (2, 2), (3, 3)),
+    # long rows of window 3 / stride 2 / pad 1: the four-cells-per-thread backward pass over several warps
+    (1, 2, (5, 6, 260), (3, 3, 3), (1, 1, 1), (2, 2, 2)),
+    (1, 2, (9, 64), (3, 3), (1, 1), (2, 2)),
+    (1, 1, (4, 5, 131), (3, 3, 3), (0, 1, 1), (2, 2, 2)),
 ]
 
 
