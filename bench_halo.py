@@ -18,6 +18,9 @@ P GPUs (torchrun): real ranks, S^3 split along D; the whole exchange is timed
 (max over ranks) and the bytes of one face (4E) over that time is the NVLink
 figure per direction of one neighbour pair; with more than two ranks an interior
 rank sends and receives two faces, which `nvlink_GBs_egress_busiest_gpu` counts.
+With `--grid w,h,d` the S^3 volume is partitioned in two or three dimensions and the
+ordered W, H, D exchange is timed as a whole; the figure is the bytes one GPU sends
+over that time.
 
 The payload is the global-offset fill of the reference's halo test, and every
 configuration is checked for exact halo contents after the timed runs.
@@ -152,6 +155,8 @@ def run_ranks(args, torch, dc, dist, world, rank):
                 continue
             for width in args.widths:
                 shape, ls = [S, S, S, C, 1], [1, 1, world, 1, 1]
+                if args.grid:
+                    ls = list(args.grid) + [1, 1]
                 t = make_tensor(dc, shape, ls, width, locale)
                 global_offset_fill(t, torch)
                 hx = dc.HaloExchange(t).setup()
@@ -169,8 +174,35 @@ def run_ranks(args, torch, dc, dist, world, rank):
                         total += e0.elapsed_time(e1)
                 ms = torch.tensor([total / args.reps], device="cuda")
                 dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-                good = torch.tensor([1 if (check_halo(t, 2, torch) and hx.status() == _abi.OK) else 0], device="cuda")
+                parts = [d for d in range(3) if ls[d] > 1]
+                good = torch.tensor([1 if (all(check_halo(t, d, torch) for d in parts)
+                                           and hx.status() == _abi.OK) else 0], device="cuda")
                 dist.all_reduce(good, op=dist.ReduceOp.MIN)
+                if args.grid:
+                    # cells a rank with neighbours on every side sends: the face of dimension d spans the
+                    # owned cells of the later dimensions and the halo-extended ones of the earlier (the
+                    # exchanges run in the order W, H, D, so that edges and corners travel on)
+                    sent = 0
+                    for d in parts:
+                        e = width * C
+                        for o in range(3):
+                            if o != d:
+                                e *= S // ls[o] + (2 * width if (o < d and ls[o] > 1) else 0)
+                        sent += e * (2 if ls[d] > 2 else 1)
+                    r = {"mode": f"{world}gpu-grid-" + "x".join(str(v) for v in ls[:3]), "C": C, "S": S,
+                         "width": width, "dim": "".join("WHD"[d] for d in parts), "sent_MB_per_gpu": 4 * sent / 1e6,
+                         "exchange_us": 1e3 * float(ms.item()),
+                         "nvlink_GBs_per_direction": 4 * sent / (float(ms.item()) * 1e-3) / 1e9,
+                         "exact": bool(good.item())}
+                    if rank == 0:
+                        print(json.dumps(r), flush=True)
+                    results.append(r)
+                    dist.barrier()
+                    del hx, t
+                    torch.cuda.empty_cache()
+                    if not r["exact"]:
+                        raise SystemExit("halo contents differ from the global-offset fill")
+                    continue
                 E = width * C * S * S
                 r = {"mode": f"{world}gpu-D-partition", "C": C, "S": S, "width": width, "dim": "D",
                      "face_MB": 4 * E / 1e6, "exchange_us": 1e3 * float(ms.item()),
@@ -186,7 +218,8 @@ def run_ranks(args, torch, dc, dist, world, rank):
                 torch.cuda.empty_cache()
                 if not r["exact"]:
                     raise SystemExit("halo contents differ from the global-offset fill")
-    results += run_shuffle(args, torch, dc, dist, world, rank, locale)
+    if not args.grid:
+        results += run_shuffle(args, torch, dc, dist, world, rank, locale)
     return results
 
 
@@ -248,6 +281,9 @@ def main():
     ap.add_argument("--sizes", type=int, nargs="+", default=[128, 256, 512])
     ap.add_argument("--widths", type=int, nargs="+", default=[1, 2, 3])
     ap.add_argument("--reps", type=int, default=10)
+    ap.add_argument("--grid", type=lambda v: [int(x) for x in v.split(",")], default=None,
+                    help="ranks along W,H,D (torchrun only; their product is the world size): the whole "
+                         "ordered exchange of a 2-D / 3-D partition instead of the split along D")
     ap.add_argument("--max-gb", type=float, default=20.0,
                     help="skip configurations whose tensors exceed this many GB on one device")
     args = ap.parse_args()
@@ -264,6 +300,8 @@ def main():
         import torch.distributed as dist
 
         dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
+        if args.grid and (len(args.grid) != 3 or args.grid[0] * args.grid[1] * args.grid[2] != world):
+            raise SystemExit("--grid w,h,d must multiply to the world size")
         res = run_ranks(args, torch, dc, dist, world, rank)
         key = "nvlink_GBs_per_direction"
     else:
