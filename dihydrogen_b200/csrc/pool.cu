@@ -173,8 +173,67 @@ __global__ void __launch_bounds__(POOL_THREADS)
     float m[2] = {-FLT_MAX, -FLT_MAX}, s[2] = {0.f, 0.f};
     int best[2] = {-1, -1};
     const int lane = threadIdx.x & 31;
+    // A warp whose windows all lie inside the real cells (every warp but those at the
+    // faces) runs without range checks: tap 0 is then every window's first cell, so the
+    // "first cell always becomes the maximum" rule is an assignment there and a plain
+    // comparison after it.  Same results as the checked loop below.
+    const bool full = live && 2 * tq + 1 < g.out[2] && d0 >= g.lo[0] && d0 + WD <= g.hi[0] && h0 >= g.lo[1]
+                      && h0 + 3 <= g.hi[1] && w4 >= g.lo[2] && w4 + 3 < g.hi[2];
+    const bool fast = __all_sync(0xffffffffu, full);
+    // the first thread of a row: its cell w4 - 1 is the padding, tap 1 its first window's first cell
+    const bool ledge = w4 - 1 < g.lo[2];
+    if (fast)
+    {
+        const float* rp0 = xp + (size_t) d0 * g.xs[0] + (size_t) h0 * g.xs[1] + w4;
+        const bool want_max = g.mode == DCB_POOL_MAX;
 #pragma unroll
-    for (int kd = 0; kd < WD; ++kd)
+        for (int kd = 0; kd < WD; ++kd)
+#pragma unroll
+            for (int kh = 0; kh < 3; ++kh)
+            {
+                const float* rp = rp0 + (size_t) kd * g.xs[0] + (size_t) kh * g.xs[1];
+                const float4 t = __ldg(reinterpret_cast<const float4*>(rp));
+                float prev = __shfl_up_sync(0xffffffffu, t.w, 1);
+                if (lane == 0 && !ledge)
+                    prev = __ldg(rp - 1);
+                const float v[5] = {prev, t.x, t.y, t.z, t.w};
+                const int tap0 = (kd * 3 + kh) * 3;
+                if (want_max)
+                {
+#pragma unroll
+                    for (int o = 0; o < 2; ++o)
+#pragma unroll
+                        for (int kw = 0; kw < 3; ++kw)
+                        {
+                            const float val = v[2 * o + kw];
+                            const bool row0 = kd == 0 && kh == 0;
+                            bool take;
+                            if (o == 0 && kw == 0)
+                                take = !ledge && (row0 || val > m[o]);
+                            else if (o == 0 && kw == 1 && row0)
+                                take = ledge || val > m[o];
+                            else
+                                take = (row0 && kw == 0) || val > m[o];
+                            if (take)
+                            {
+                                m[o] = val;
+                                best[o] = tap0 + kw;
+                            }
+                        }
+                }
+                else
+                {
+                    s[0] += ledge ? 0.f : v[0];
+                    s[0] += v[1];
+                    s[0] += v[2];
+#pragma unroll
+                    for (int kw = 0; kw < 3; ++kw)
+                        s[1] += v[2 + kw];
+                }
+            }
+    }
+#pragma unroll
+    for (int kd = 0; kd < WD && !fast; ++kd)
     {
         const int id = d0 + kd;
         const bool dok = live && id >= g.lo[0] && id < g.hi[0];
