@@ -167,6 +167,8 @@ __global__ void __launch_bounds__(POOL_THREADS)
     pool_split_row(row, rows, g.out[1], &od, &oh);
     const int c = blockIdx.z % g.c, n = blockIdx.z / g.c;
     const float* xp = x + (size_t) n * g.xs_n + (size_t) c * g.xs_c;
+    // offsets inside one (sample, channel) volume fit 32 bits (checked at the launch)
+    const int xs0 = (int) g.xs[0], xs1 = (int) g.xs[1];
     const int sd = WD == 1 ? 1 : 2;
     const int d0 = od * sd - g.pad[0], h0 = oh * 2 - g.pad[1];
     const int w4 = 4 * tq; // cells w4 - 1 .. w4 + 3
@@ -184,14 +186,14 @@ __global__ void __launch_bounds__(POOL_THREADS)
     const bool ledge = w4 - 1 < g.lo[2];
     if (fast)
     {
-        const float* rp0 = xp + (size_t) d0 * g.xs[0] + (size_t) h0 * g.xs[1] + w4;
+        const float* rp0 = xp + (d0 * xs0 + h0 * xs1 + w4);
         const bool want_max = g.mode == DCB_POOL_MAX;
 #pragma unroll
         for (int kd = 0; kd < WD; ++kd)
 #pragma unroll
             for (int kh = 0; kh < 3; ++kh)
             {
-                const float* rp = rp0 + (size_t) kd * g.xs[0] + (size_t) kh * g.xs[1];
+                const float* rp = rp0 + (kd * xs0 + kh * xs1);
                 const float4 t = __ldg(reinterpret_cast<const float4*>(rp));
                 float prev = __shfl_up_sync(0xffffffffu, t.w, 1);
                 if (lane == 0 && !ledge)
@@ -245,7 +247,7 @@ __global__ void __launch_bounds__(POOL_THREADS)
             float q[4] = {0.f, 0.f, 0.f, 0.f};
             if (rok)
             {
-                const float* rp = xp + (size_t) id * g.xs[0] + (size_t) ih * g.xs[1] + w4;
+                const float* rp = xp + (id * xs0 + ih * xs1 + w4);
                 if (w4 + 3 < g.hi[2])
                 {
                     const float4 t = __ldg(reinterpret_cast<const float4*>(rp));
@@ -265,7 +267,7 @@ __global__ void __launch_bounds__(POOL_THREADS)
             // cell w4 - 1: the left neighbour's q[3] (same output row: a tile is 32 lanes or more)
             float prev = __shfl_up_sync(0xffffffffu, q[3], 1);
             if (lane == 0 && rok && w4 - 1 >= g.lo[2])
-                prev = __ldg(xp + (size_t) id * g.xs[0] + (size_t) ih * g.xs[1] + w4 - 1);
+                prev = __ldg(xp + (id * xs0 + ih * xs1 + w4 - 1));
             if (!rok)
                 continue;
             const float v[5] = {prev, q[0], q[1], q[2], q[3]};
@@ -297,12 +299,13 @@ __global__ void __launch_bounds__(POOL_THREADS)
         if (ow >= g.out[2])
             continue;
         if (argmax)
-            argmax[((((size_t) n * g.c + c) * g.out[0] + od) * g.out[1] + oh) * g.out[2] + ow] = (unsigned char) best[o];
+            argmax[((size_t) n * g.c + c) * ((size_t) g.out[0] * g.out[1] * g.out[2]) + ((od * g.out[1] + oh) * g.out[2] + ow)] =
+                (unsigned char) best[o];
         if (!y)
             continue;
         const float r = g.mode == DCB_POOL_MAX ? m[o] : s[o] / fmaxf(pool_count(g, od, oh, ow), 1.f);
         float* yp =
-            y + (size_t) n * g.ys_n + (size_t) c * g.ys_c + (size_t) od * g.ys[0] + (size_t) oh * g.ys[1] + ow;
+            y + (size_t) n * g.ys_n + (size_t) c * g.ys_c + (od * (int) g.ys[0] + oh * (int) g.ys[1] + ow);
         *yp = beta != 0.f ? alpha * r + beta * *yp : alpha * r;
     }
 }
@@ -505,49 +508,72 @@ __global__ void __launch_bounds__(POOL_THREADS)
     if (id < g.lo[0] || id >= g.hi[0] || ih < g.lo[1] || ih >= g.hi[1])
         dhi = dlo - 1; // a row outside the global tensor is padding
     const int lane = threadIdx.x & 31;
-    const size_t plane = ((size_t) n * g.c + c) * g.out[0];
-    const float* dyp = dy + (size_t) n * g.ys_n + (size_t) c * g.ys_c;
+    // offsets inside one (sample, channel) volume fit 32 bits (checked at the launch)
+    const int ys0 = (int) g.ys[0], ys1 = (int) g.ys[1], astep = g.out[1] * g.out[2];
+    const unsigned char* abase =
+        argmax + ((size_t) n * g.c + c) * ((size_t) g.out[0] * astep) + ((dlo * g.out[1] + hlo) * g.out[2] + ow0);
+    const float* dbase = dy + (size_t) n * g.ys_n + (size_t) c * g.ys_c + (dlo * ys0 + hlo * ys1 + ow0);
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     const bool two = ow0 + 1 < g.out[2], third = ow0 + 2 < g.out[2];
-    for (int od = dlo; od <= dhi; ++od)
-    {
-        // pointers and tap base of window row (od, hlo), moved on by one output row per turn
-        const unsigned char* arow = argmax + ((plane + od) * g.out[1] + hlo) * g.out[2] + ow0;
-        const float* dyrow = dyp + (size_t) od * g.ys[0] + (size_t) hlo * g.ys[1] + ow0;
-        // tap of window (od, oh, ow) at cell i: tb + i - (2 ow - 1)
-        int tb = ((id - (od * sd - g.pad[0])) * 3 + (ih - (hlo * 2 - g.pad[1]))) * 3;
-        for (int oh = hlo; oh <= hhi; ++oh, arow += g.out[2], dyrow += g.ys[1], tb -= 6)
+    // at most two output planes and two output rows hold this input row: all their loads
+    // are issued before the first is used (which of the four exist is the same for the
+    // whole warp)
+    constexpr int JD = WD == 1 ? 1 : 2;
+    int a0[JD * 2], a1[JD * 2];
+    float d0[JD * 2], d1[JD * 2];
+#pragma unroll
+    for (int jd = 0; jd < JD; ++jd)
+#pragma unroll
+        for (int jh = 0; jh < 2; ++jh)
         {
+            const int k = jd * 2 + jh;
             // 255 is the index pass's "empty window" and never a tap
-            int a0 = 255, a1 = 255, a2;
-            float d0 = 0.f, d1 = 0.f, d2;
-            if (two)
+            a0[k] = a1[k] = 255;
+            d0[k] = d1[k] = 0.f;
+            if (dlo + jd <= dhi && hlo + jh <= hhi && two)
             {
-                const uchar2 a = __ldg(reinterpret_cast<const uchar2*>(arow));
-                const float2 d = __ldg(reinterpret_cast<const float2*>(dyrow));
-                a0 = a.x;
-                a1 = a.y;
-                d0 = d.x;
-                d1 = d.y;
+                const uchar2 a = __ldg(reinterpret_cast<const uchar2*>(abase + (jd * astep + jh * g.out[2])));
+                const float2 d = __ldg(reinterpret_cast<const float2*>(dbase + (jd * ys0 + jh * ys1)));
+                a0[k] = a.x;
+                a1[k] = a.y;
+                d0[k] = d.x;
+                d1[k] = d.y;
             }
-            a2 = __shfl_down_sync(0xffffffffu, a0, 1);
-            d2 = __shfl_down_sync(0xffffffffu, d0, 1);
+        }
+#pragma unroll
+    for (int jd = 0; jd < JD; ++jd)
+#pragma unroll
+        for (int jh = 0; jh < 2; ++jh)
+        {
+            const int k = jd * 2 + jh;
+            const int od = dlo + jd, oh = hlo + jh;
+            if (od > dhi || oh > hhi)
+                continue;
+            int a2 = __shfl_down_sync(0xffffffffu, a0[k], 1);
+            float d2 = __shfl_down_sync(0xffffffffu, d0[k], 1);
             if (lane == 31)
             {
-                a2 = third ? (int) __ldg(arow + 2) : 255;
-                d2 = third ? __ldg(dyrow + 2) : 0.f;
+                a2 = third ? (int) __ldg(abase + (jd * astep + jh * g.out[2] + 2)) : 255;
+                d2 = third ? __ldg(dbase + (jd * ys0 + jh * ys1 + 2)) : 0.f;
             }
-            acc[0] += a0 == tb + 1 ? d0 : 0.f;
-            acc[1] += a0 == tb + 2 ? d0 : 0.f;
-            acc[1] += a1 == tb ? d1 : 0.f;
-            acc[2] += a1 == tb + 1 ? d1 : 0.f;
-            acc[3] += a1 == tb + 2 ? d1 : 0.f;
-            acc[3] += a2 == tb ? d2 : 0.f;
+            // tap of window (od, oh, ow) at cell i: tb + i - (2 ow - 1)
+            const int tb = ((id - (od * sd - g.pad[0])) * 3 + (ih - (oh * 2 - g.pad[1]))) * 3;
+            if (a0[k] == tb + 1)
+                acc[0] += d0[k];
+            if (a0[k] == tb + 2)
+                acc[1] += d0[k];
+            if (a1[k] == tb)
+                acc[1] += d1[k];
+            if (a1[k] == tb + 1)
+                acc[2] += d1[k];
+            if (a1[k] == tb + 2)
+                acc[3] += d1[k];
+            if (a2 == tb)
+                acc[3] += d2;
         }
-    }
     if (iw0 >= g.in[2])
         return;
-    float* xp = dx + (size_t) n * g.xs_n + (size_t) c * g.xs_c + (size_t) id * g.xs[0] + (size_t) ih * g.xs[1] + iw0;
+    float* xp = dx + (size_t) n * g.xs_n + (size_t) c * g.xs_c + (id * (int) g.xs[0] + ih * (int) g.xs[1] + iw0);
     if (iw0 + 4 <= g.in[2] && (reinterpret_cast<uintptr_t>(xp) & 15) == 0)
     {
         float4 o = make_float4(alpha * acc[0], alpha * acc[1], alpha * acc[2], alpha * acc[3]);
@@ -661,7 +687,10 @@ int32_t launch_pool_fwd(const PoolGeom& g, float alpha, float beta, const float*
     const bool cube = g.win[0] == 3 && g.stride[0] == 2;
     const bool pair = g.win[2] == 3 && g.stride[2] == 2 && g.pad[2] == 1 && g.win[1] == 3 && g.stride[1] == 2
                       && (flat || cube) && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && g.xs[0] % 4 == 0
-                      && g.xs[1] % 4 == 0 && g.xs_c % 4 == 0 && g.xs_n % 4 == 0 && g.out[2] >= 2;
+                      && g.xs[1] % 4 == 0 && g.xs_c % 4 == 0 && g.xs_n % 4 == 0 && g.out[2] >= 2
+                      && (long long) g.out[0] * g.out[1] * g.out[2] < (1ll << 31)
+                      && (g.out[0] - 1) * g.ys[0] + (g.out[1] - 1) * g.ys[1] + g.out[2] < (1ll << 31)
+                      && (g.in[0] - 1) * g.xs[0] + (g.in[1] - 1) * g.xs[1] + g.in[2] < (1ll << 31);
     const int wcells = pair ? (g.out[2] + 1) / 2 : g.out[2]; // threads a row needs
     int tw_log2 = 8; // threads of a row per block: 32, 64, 128 or 256
     while (tw_log2 > 5 && (1 << (tw_log2 - 1)) >= wcells)
@@ -759,8 +788,12 @@ extern "C" int32_t dcb_pool_bwd(const dcb_pool_desc* pd, const dcb_nd_desc* xd, 
     const bool cube = g.win[0] == 3 && g.stride[0] == 2;
     const bool even = g.ys[0] % 2 == 0 && g.ys[1] % 2 == 0 && g.ys_c % 2 == 0 && g.ys_n % 2 == 0 && g.out[2] % 2 == 0
                       && (reinterpret_cast<uintptr_t>(dy) & 7) == 0 && (reinterpret_cast<uintptr_t>(idx) & 1) == 0;
+    // offsets inside one (sample, channel) volume as 32-bit integers
+    const bool small = (long long) g.out[0] * g.out[1] * g.out[2] < (1ll << 31)
+                       && (g.out[0] - 1) * g.ys[0] + (g.out[1] - 1) * g.ys[1] + g.out[2] < (1ll << 31)
+                       && (g.in[0] - 1) * g.xs[0] + (g.in[1] - 1) * g.xs[1] + g.in[2] < (1ll << 31);
     if (idx && g.win[2] == 3 && g.stride[2] == 2 && g.pad[2] == 1 && g.win[1] == 3 && g.stride[1] == 2
-        && (flat || cube) && even)
+        && (flat || cube) && even && small)
     {
         const int wcells = (g.in[2] + 3) / 4; // threads a row needs
         int tw_log2 = 8;
