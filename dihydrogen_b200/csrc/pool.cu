@@ -596,6 +596,133 @@ __global__ void __launch_bounds__(POOL_THREADS)
     }
 }
 
+// The same gather with pad 1 along H (and D, for WD = 3) as well: a thread owns the four
+// cells in each row of a 2 x 2 block of input rows (planes 2p, 2p+1 x rows 2q, 2q+1; one
+// plane for WD = 1).  Those rows lie in the windows of output planes p, p+1 and output
+// rows q, q+1 only, at fixed taps (row 2q is tap 1 of window q; row 2q+1 tap 2 of
+// window q and tap 0 of window q+1), so the index bytes and gradients of the 2 x 2
+// window rows are loaded once for sixteen cells and every comparison is against a
+// constant.  Cells outside the global tensor never were a window's maximum, so they
+// need no mask.  Per cell the sums run in the same order (D, H, then W ascending).
+template <int WD>
+__global__ void __launch_bounds__(POOL_THREADS)
+    pool_bwd_index_block_kernel(PoolGeom g, float alpha, float beta, const float* __restrict__ dy, float* dx,
+                                const unsigned char* __restrict__ argmax, int tw_log2, int blocks_h, long long rows)
+{
+    constexpr int JD = WD == 1 ? 1 : 2;
+    const int t = (blockIdx.y << tw_log2) + (threadIdx.x & ((1 << tw_log2) - 1));
+    const long long row = (long long) blockIdx.x * (POOL_THREADS >> tw_log2) + (threadIdx.x >> tw_log2);
+    if (row >= rows) // a warp never spans two row blocks: the whole warp leaves
+        return;
+    const int iw0 = 4 * t, ow0 = 2 * t;
+    int p, q;
+    pool_split_row(row, rows, blocks_h, &p, &q);
+    const int c = blockIdx.z % g.c, n = blockIdx.z / g.c;
+    const int lane = threadIdx.x & 31;
+    // offsets inside one (sample, channel) volume fit 32 bits (checked at the launch)
+    const int ys0 = (int) g.ys[0], ys1 = (int) g.ys[1], astep = g.out[1] * g.out[2];
+    const unsigned char* abase =
+        argmax + ((size_t) n * g.c + c) * ((size_t) g.out[0] * astep) + ((p * g.out[1] + q) * g.out[2] + ow0);
+    const float* dbase = dy + (size_t) n * g.ys_n + (size_t) c * g.ys_c + (p * ys0 + q * ys1 + ow0);
+    const bool two = ow0 + 1 < g.out[2], third = ow0 + 2 < g.out[2];
+    // window rows (p + jd, q + jh): which exist is the same for the whole warp
+    int a0[JD * 2], a1[JD * 2], a2[JD * 2];
+    float d0[JD * 2], d1[JD * 2], d2[JD * 2];
+#pragma unroll
+    for (int jd = 0; jd < JD; ++jd)
+#pragma unroll
+        for (int jh = 0; jh < 2; ++jh)
+        {
+            const int k = jd * 2 + jh;
+            // 255 is the index pass's "empty window" and never a tap
+            a0[k] = a1[k] = 255;
+            d0[k] = d1[k] = 0.f;
+            if (p + jd < g.out[0] && q + jh < g.out[1] && two)
+            {
+                const uchar2 a = __ldg(reinterpret_cast<const uchar2*>(abase + (jd * astep + jh * g.out[2])));
+                const float2 d = __ldg(reinterpret_cast<const float2*>(dbase + (jd * ys0 + jh * ys1)));
+                a0[k] = a.x;
+                a1[k] = a.y;
+                d0[k] = d.x;
+                d1[k] = d.y;
+            }
+        }
+#pragma unroll
+    for (int jd = 0; jd < JD; ++jd)
+#pragma unroll
+        for (int jh = 0; jh < 2; ++jh)
+        {
+            const int k = jd * 2 + jh;
+            a2[k] = __shfl_down_sync(0xffffffffu, a0[k], 1);
+            d2[k] = __shfl_down_sync(0xffffffffu, d0[k], 1);
+            if (lane == 31)
+            {
+                const bool in = third && p + jd < g.out[0] && q + jh < g.out[1];
+                a2[k] = in ? (int) __ldg(abase + (jd * astep + jh * g.out[2] + 2)) : 255;
+                d2[k] = in ? __ldg(dbase + (jd * ys0 + jh * ys1 + 2)) : 0.f;
+            }
+        }
+    if (iw0 >= g.in[2])
+        return;
+    float* xbase = dx + (size_t) n * g.xs_n + (size_t) c * g.xs_c;
+    const int xs0 = (int) g.xs[0], xs1 = (int) g.xs[1];
+#pragma unroll
+    for (int pa = 0; pa < JD; ++pa)
+#pragma unroll
+        for (int rb = 0; rb < 2; ++rb)
+        {
+            const int id = JD == 2 ? 2 * p + pa : p, ih = 2 * q + rb;
+            if (id >= g.in[0] || ih >= g.in[1])
+                continue;
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int jd = 0; jd < JD; ++jd)
+#pragma unroll
+                for (int jh = 0; jh < 2; ++jh)
+                {
+                    // tap of input (plane pa, row rb) in window (jd, jh): coordinate - (2 * window - 1)
+                    const int kd = JD == 2 ? pa - 2 * jd + 1 : 0, kh = rb - 2 * jh + 1;
+                    if (kd < 0 || kd > 2 || kh < 0 || kh > 2)
+                        continue;
+                    const int k = jd * 2 + jh;
+                    const int tb = (kd * 3 + kh) * 3; // tap at cell i of window ow: tb + i - (2 ow - 1)
+                    if (a0[k] == tb + 1)
+                        acc[0] += d0[k];
+                    if (a0[k] == tb + 2)
+                        acc[1] += d0[k];
+                    if (a1[k] == tb)
+                        acc[1] += d1[k];
+                    if (a1[k] == tb + 1)
+                        acc[2] += d1[k];
+                    if (a1[k] == tb + 2)
+                        acc[3] += d1[k];
+                    if (a2[k] == tb)
+                        acc[3] += d2[k];
+                }
+            float* xp = xbase + (id * xs0 + ih * xs1 + iw0);
+            if (iw0 + 4 <= g.in[2] && (reinterpret_cast<uintptr_t>(xp) & 15) == 0)
+            {
+                float4 o = make_float4(alpha * acc[0], alpha * acc[1], alpha * acc[2], alpha * acc[3]);
+                if (beta != 0.f)
+                {
+                    const float4 old = *reinterpret_cast<const float4*>(xp);
+                    o.x += beta * old.x;
+                    o.y += beta * old.y;
+                    o.z += beta * old.z;
+                    o.w += beta * old.w;
+                }
+                *reinterpret_cast<float4*>(xp) = o;
+            }
+            else
+            {
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    if (iw0 + e < g.in[2])
+                        xp[e] = beta != 0.f ? alpha * acc[e] + beta * xp[e] : alpha * acc[e];
+            }
+        }
+}
+
 int32_t pool_geom(const dcb_pool_desc* pd, const dcb_nd_desc* xd, const dcb_nd_desc* yd, PoolGeom* g)
 {
     DCB_REQUIRE(pd && xd && yd, "null descriptor");
@@ -800,7 +927,27 @@ extern "C" int32_t dcb_pool_bwd(const dcb_pool_desc* pd, const dcb_nd_desc* xd, 
         while (tw_log2 > 5 && (1 << (tw_log2 - 1)) >= wcells)
             --tw_log2;
         const long long tiles = (wcells + (1 << tw_log2) - 1) >> tw_log2;
-        const long long rows = (long long) g.in[0] * g.in[1], rpb = POOL_THREADS >> tw_log2;
+        const long long rpb = POOL_THREADS >> tw_log2;
+        // pad 1 along H (and D): a thread takes a 2 x 2 block of rows
+        const bool block = g.pad[1] == 1 && (cube ? g.pad[0] == 1 : g.pad[0] == 0);
+        if (block && tiles <= 65535)
+        {
+            const int blocks_h = (g.in[1] + 1) / 2;
+            const long long brows = (long long) (cube ? (g.in[0] + 1) / 2 : g.in[0]) * blocks_h;
+            const long long bgx = (brows + rpb - 1) / rpb;
+            const dim3 gridb((unsigned) bgx, (unsigned) tiles, grid.z);
+            if (cube)
+                pool_bwd_index_block_kernel<3><<<gridb, POOL_THREADS, 0, as_stream(stream)>>>(
+                    g, (float) alpha, (float) beta, static_cast<const float*>(dy), static_cast<float*>(dx), idx,
+                    tw_log2, blocks_h, brows);
+            else
+                pool_bwd_index_block_kernel<1><<<gridb, POOL_THREADS, 0, as_stream(stream)>>>(
+                    g, (float) alpha, (float) beta, static_cast<const float*>(dy), static_cast<float*>(dx), idx,
+                    tw_log2, blocks_h, brows);
+            DCB_LAUNCH_CHECK();
+            return DCB_OK;
+        }
+        const long long rows = (long long) g.in[0] * g.in[1];
         const long long gx = (rows + rpb - 1) / rpb;
         if (gx <= 0x7fffffffll && tiles <= 65535)
         {

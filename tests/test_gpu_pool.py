@@ -30,6 +30,8 @@ CASES = [
     (1, 2, (5, 6, 260), (3, 3, 3), (1, 1, 1), (2, 2, 2)),
     (1, 2, (9, 64), (3, 3), (1, 1), (2, 2)),
     (1, 1, (4, 5, 131), (3, 3, 3), (0, 1, 1), (2, 2, 2)),
+    # even extents everywhere: every thread of the 2 x 2-rows backward pass owns a whole block
+    (1, 2, (6, 8, 72), (3, 3, 3), (1, 1, 1), (2, 2, 2)),
 ]
 
 
