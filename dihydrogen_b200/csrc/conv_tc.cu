@@ -1064,21 +1064,72 @@ static int32_t mg_launch(const SwGeom& g_in, float alpha, const float* w, const 
     if (grid > g.units)
         grid = g.units;
     const bool c4f3 = g.c == 4 && g.f[2] == 3 && g.pad[2] <= 1 && g.split;
+    long long* prof = nullptr;
+#if DCB_SW_PROFILE
+    // per-role clock accounting as in the sweep kernel: DCB_MG_PROF_LAUNCHES launches are
+    // measured and printed, synchronously
+    static int prof_left = std::getenv("DCB_MG_PROF_LAUNCHES") ? std::atoi(std::getenv("DCB_MG_PROF_LAUNCHES")) : 0;
+    const size_t prof_n = (size_t) grid * 32 * 8;
+    if (prof_left > 0)
+    {
+        DCB_CUDA_TRY(cudaMalloc(&prof, prof_n * sizeof(long long)));
+        DCB_CUDA_TRY(cudaMemsetAsync(prof, 0, prof_n * sizeof(long long), stream));
+    }
+#endif
     if (c4f3)
     {
         DCB_CUDA_TRY(cudaFuncSetAttribute(mg_conv_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           (int) (224 * 1024)));
         mg_conv_kernel<true><<<(unsigned) grid, MG_THREADS, smem, stream>>>(g, alpha, bimg, y, status, xmap, ymap,
-                                                                           use_ymap);
+                                                                           use_ymap, prof);
     }
     else
     {
         DCB_CUDA_TRY(cudaFuncSetAttribute(mg_conv_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           (int) (224 * 1024)));
         mg_conv_kernel<false><<<(unsigned) grid, MG_THREADS, smem, stream>>>(g, alpha, bimg, y, status, xmap, ymap,
-                                                                            use_ymap);
+                                                                            use_ymap, prof);
     }
     DCB_LAUNCH_CHECK();
+#if DCB_SW_PROFILE
+    if (prof != nullptr)
+    {
+        --prof_left;
+        std::vector<long long> h(prof_n);
+        DCB_CUDA_TRY(cudaStreamSynchronize(stream));
+        DCB_CUDA_TRY(cudaMemcpy(h.data(), prof, prof_n * sizeof(long long), cudaMemcpyDeviceToHost));
+        cudaFree(prof);
+        auto role = [&](const char* name, int w_lo, int w_hi, const char* const* labels) {
+            double acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            long long n = 0;
+            for (long long b = 0; b < grid; ++b)
+                for (int w = w_lo; w < w_hi; ++w)
+                {
+                    const long long* r = &h[((size_t) b * 32 + w) * 8];
+                    if (r[7] == 0)
+                        continue;
+                    for (int i = 0; i < 8; ++i)
+                        acc[i] += (double) r[i];
+                    ++n;
+                }
+            if (n == 0)
+                return;
+            std::fprintf(stderr, "[mg prof] %-10s warps %lld total %.0f:", name, n, acc[7] / n);
+            for (int i = 0; i < 5; ++i)
+                std::fprintf(stderr, " %s %.1f%%", labels[i], 100.0 * acc[i] / acc[7]);
+            std::fprintf(stderr, "\n");
+        };
+        const char* lc[5] = {"wait_raw", "convert", "wait_a_empty", "st+arrive", "other"};
+        const char* li[5] = {"wait_row_free", "wait_a_full", "issue", "wait_iss_sync", "other"};
+        const char* le[5] = {"wait_row_done", "tmem_ld", "zero+arrive", "stage+store", "other"};
+        role("converter", 0, TC_PRODUCERS, lc);
+        role("issuer 1", TC_MMA_WARP, TC_TMA_WARP, li);
+        role("issuer 2", MG_ISSUER2_WARP, MG_THREADS / 32, li);
+        role("epilogue", TC_TMA_WARP + 1, MG_ISSUER2_WARP, le);
+        std::fprintf(stderr, "[mg prof] th %d nsets %d cgroups %d a_slots %d groups %d raw_slots %d chunks_pp %d\n", g.th,
+                     g.nsets, g.cgroups, g.a_slots, g.groups, g.raw_slots, g.chunks_pp);
+    }
+#endif
     return DCB_OK;
 }
 

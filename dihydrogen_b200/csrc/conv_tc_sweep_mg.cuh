@@ -111,7 +111,8 @@ __global__ void mg_pack_filter_kernel(const float* __restrict__ w, float* __rest
 template <bool C4F3>
 __global__ void __launch_bounds__(MG_THREADS, 1)
     mg_conv_kernel(SwGeom g, float alpha, const float* __restrict__ bimg, float* y, int* status,
-                   const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap ymap, int use_ymap)
+                   const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap ymap, int use_ymap,
+                   long long* prof)
 {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -202,6 +203,7 @@ __global__ void __launch_bounds__(MG_THREADS, 1)
         int lap_a = 0;
         uint32_t cslot = 0, cphase = 0, a_phase = 1, base = 0;
         bool a_first = true;
+        SW_PROF_DECL
         for (uint32_t u = blockIdx.x; u < nunits && ok; u += gridDim.x)
         {
             const SwUnit t = sw_unit(g, u);
@@ -226,9 +228,11 @@ __global__ void __launch_bounds__(MG_THREADS, 1)
                             ++i;
                         }
                         const int a_slot = gq + G * lap_a;
+                        SW_PROF_MARK(4)
                         if (!have)
                             ok = mbar_wait(&raw_full[cslot], cphase, abort_flag);
                         have = true;
+                        SW_PROF_MARK(0)
                         if (!ok)
                             break;
                         const float* raw = reinterpret_cast<const float*>(raw_ring + (size_t) cslot * g.raw_slot_bytes)
@@ -240,8 +244,10 @@ __global__ void __launch_bounds__(MG_THREADS, 1)
                             uint32_t v[3][8];
                             // the converter is written for taps that start 3 cells into the staged row
                             sw_convert_c4f3<true>(raw_s + 4u * (uint32_t) (g.rx - 3), pitch, v);
+                            SW_PROF_MARK(1)
                             if (!a_first)
                                 ok = mbar_wait(&a_empty[a_slot], a_phase, abort_flag);
+                            SW_PROF_MARK(2)
                             if (!ok)
                                 break;
                             tc_fence_after();
@@ -268,6 +274,7 @@ __global__ void __launch_bounds__(MG_THREADS, 1)
                         __syncwarp();
                         if (lane == 0)
                             mbar_arrive(&a_full[a_slot]);
+                        SW_PROF_MARK(3)
                         if (++lap_a == laps_a)
                         {
                             lap_a = 0;
@@ -288,6 +295,8 @@ __global__ void __launch_bounds__(MG_THREADS, 1)
                 base = (base + (uint32_t) subrows) % (uint32_t) G;
             }
         }
+        SW_PROF_MARK(4)
+        SW_PROF_FLUSH(prof)
     }
     else if (warp == TC_TMA_WARP)
     {
@@ -355,6 +364,7 @@ __global__ void __launch_bounds__(MG_THREADS, 1)
             const int laps_a = g.a_slots / G;
             int lap_a = 0;
             uint32_t full_phase = 0, step = 0, base = 0;
+            SW_PROF_DECL
             for (uint32_t u = blockIdx.x; u < nunits && ok; u += gridDim.x)
             {
                 const SwUnit t = sw_unit(g, u);
@@ -366,8 +376,10 @@ __global__ void __launch_bounds__(MG_THREADS, 1)
                     // away.  The first issuer waits for every row's hand-back in every step,
                     // so once both have finished a step the barriers this group looks at are
                     // at most one completion behind what either expects next.
+                    SW_PROF_MARK(4)
                     if (laps_a > 1 && step != 0)
                         ok = mbar_wait_t<0>(&iss_sync[mq], (step - 1) & 1, abort_flag);
+                    SW_PROF_MARK(3)
                     const bool real = sw_real(g, t, d);
                     const uint32_t par = step & 1;
                     const uint32_t rot = (uint32_t) (d & (MG_SLOTS - 1));
@@ -393,15 +405,18 @@ __global__ void __launch_bounds__(MG_THREADS, 1)
                         }
                         // only output rows this row adds into may be waited for
                         const int r_hi = min(i, g.th - 1), r_lo = max(0, i - fh + 1);
+                        SW_PROF_MARK(4)
                         ok = mbar_wait_t<0>(&row_free[r_hi], par, abort_flag);
                         if (ok && r_hi - 1 >= r_lo)
                             ok = mbar_wait_t<0>(&row_free[r_hi - 1], par, abort_flag);
+                        SW_PROF_MARK(0)
                         if (!ok)
                             break;
                         if (real)
                         {
                             const uint32_t slot = (uint32_t) (mq + G * lap_a);
                             ok = mbar_wait_t<0>(&a_full[slot], full_phase, abort_flag);
+                            SW_PROF_MARK(1)
                             if (!ok)
                                 break;
                             tc_fence_after();
@@ -424,6 +439,7 @@ __global__ void __launch_bounds__(MG_THREADS, 1)
                                 tc_fence_before();
                             }
                             __syncwarp();
+                            SW_PROF_MARK(2)
                             if (++lap_a == laps_a)
                             {
                                 lap_a = 0;
@@ -448,6 +464,8 @@ __global__ void __launch_bounds__(MG_THREADS, 1)
                     }
                 }
             }
+            SW_PROF_MARK(4)
+            SW_PROF_FLUSH(prof)
         }
     }
     else if (warp > TC_TMA_WARP && warp < MG_ISSUER2_WARP)
@@ -473,6 +491,7 @@ __global__ void __launch_bounds__(MG_THREADS, 1)
             for (int j = half; j < g.th; j += nhalf)
                 mbar_arrive(&row_free[j]);
         uint32_t step = 0;
+        SW_PROF_DECL
         for (uint32_t u = blockIdx.x; u < nunits && ok; u += gridDim.x)
         {
             const SwUnit t = sw_unit(g, u);
@@ -487,8 +506,10 @@ __global__ void __launch_bounds__(MG_THREADS, 1)
                 {
                     const int oh = t.oh0 + j;
                     const bool wr = store && oh < g.out[1];
+                    SW_PROF_MARK(4)
                     for (int i = j; i < j + fh && ok; ++i)
                         ok = mbar_wait(&row_done[i], par, abort_flag);
+                    SW_PROF_MARK(0)
                     if (!ok)
                         break;
                     tc_fence_after();
@@ -510,6 +531,7 @@ __global__ void __launch_bounds__(MG_THREADS, 1)
                         else
                             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                     }
+                    SW_PROF_MARK(1)
                     tmem_st4_zero(addr);
                     if (g.nsets > 1)
                         tmem_st4_zero(addr + set_cols);
@@ -518,6 +540,7 @@ __global__ void __launch_bounds__(MG_THREADS, 1)
                     __syncwarp();
                     if (lane == 0)
                         mbar_arrive(&row_free[j]);
+                    SW_PROF_MARK(2)
                     if (!wr)
                         continue;
                     if (bulk)
@@ -549,6 +572,7 @@ __global__ void __launch_bounds__(MG_THREADS, 1)
                             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                         }
                         ++nstored;
+                        SW_PROF_MARK(3)
                     }
                     else if (ow < g.out[2])
                     {
@@ -564,6 +588,8 @@ __global__ void __launch_bounds__(MG_THREADS, 1)
         }
         if (bulk && lane == 0)
             asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+        SW_PROF_MARK(4)
+        SW_PROF_FLUSH(prof)
     }
 
     if (!ok && lane == 0)
